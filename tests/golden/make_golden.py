@@ -1,0 +1,188 @@
+#!/usr/bin/env python3
+"""Generate the golden vectors under tests/golden/ from the reference's own code.
+
+Run once in a container where the reference checkout is mounted:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+It imports the reference's pure-Python / pure-torch implementations of the
+scan primitives (never its compiled code), runs them on the reference's own
+fixture inputs and on extra seeded inputs, and writes input/output vectors.
+The tests only read the written files.
+
+Sources used (paths inside the reference checkout):
+  experiments/gated_deltanet_reference/generate_fixtures.py   scalar GDN block + scan
+  experiments/mamba3_reference/generate_fixtures.py           scalar Mamba-3 block + scan
+  experiments/gated_deltanet_test/dump_fla_reference_pure.py  torch GDN recurrence
+  train/hf_templates/mamba3_mixlab.py                         torch Mamba-3 scan
+  train/testdata/gated_deltanet_full_block_reference.json     checked-in expected output
+  train/testdata/mamba3_full_block_reference.json             checked-in expected output
+  gpu/gated_delta_scan_test.go:44-83                          closed-form test inputs (restated below)
+"""
+
+from __future__ import annotations
+
+import importlib.util
+import json
+import math
+import random
+import sys
+import types
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+
+
+def _load(path: Path, name: str):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _record(mod, fn_name):
+    calls = []
+    orig = getattr(mod, fn_name)
+
+    def wrapper(*a):
+        r = orig(*a)
+        calls.append((a, r))
+        return r
+
+    setattr(mod, fn_name, wrapper)
+    return calls
+
+
+def gdn_block_fixture(ref: Path):
+    mod = _load(ref / "experiments/gated_deltanet_reference/generate_fixtures.py", "ref_gdn_fix")
+    calls = _record(mod, "gated_delta_scan")
+    fx = mod.fixture()
+    checked = json.loads((ref / "train/testdata/gated_deltanet_full_block_reference.json").read_text())
+    want = checked["fixtures"][0]["expected_hidden"]
+    assert max(abs(a - b) for a, b in zip(fx["expected_hidden"], want)) < 1e-12, "generator != checked-in JSON"
+    (a, r), = calls
+    q, k, v, beta, gate, B, T, H, Dk, Dv = a
+    cases = [dict(name="full_block_fixture_scan", B=B, T=T, H=H, Dk=Dk, Dv=Dv,
+                  q=q, k=k, v=v, beta=beta, gate=gate, out=r,
+                  source="scan call inside experiments/gated_deltanet_reference/generate_fixtures.py fixture(); "
+                         "its block output equals train/testdata/gated_deltanet_full_block_reference.json")]
+    # extra seeded cases through the same scalar reference loops
+    rng = random.Random(1234)
+    for (B, T, H, Dk, Dv) in [(2, 9, 2, 4, 5), (1, 70, 2, 8, 6), (1, 130, 1, 4, 4)]:
+        def vec(n, lo=-1.0, hi=1.0):
+            return [rng.uniform(lo, hi) for _ in range(n)]
+        q = vec(B * T * H * Dk)
+        k = vec(B * T * H * Dk)
+        # normalise k per head vector so the recurrence stays bounded
+        for i in range(B * T * H):
+            nrm = math.sqrt(sum(x * x for x in k[i * Dk:(i + 1) * Dk])) or 1.0
+            k[i * Dk:(i + 1) * Dk] = [x / nrm for x in k[i * Dk:(i + 1) * Dk]]
+        v = vec(B * T * H * Dv)
+        beta = vec(B * T * H, 0.05, 0.95)
+        gate = vec(B * T * H, 0.3, 1.0)
+        out = mod.gated_delta_scan(q, k, v, beta, gate, B, T, H, Dk, Dv)
+        cases.append(dict(name=f"scalar_loops_B{B}_T{T}_H{H}_K{Dk}_V{Dv}", B=B, T=T, H=H, Dk=Dk, Dv=Dv,
+                          q=q, k=k, v=v, beta=beta, gate=gate, out=out,
+                          source="gated_delta_scan() of experiments/gated_deltanet_reference/generate_fixtures.py "
+                                 "on python random.Random(1234) inputs"))
+    (HERE / "gdn_scalar_reference.json").write_text(json.dumps(dict(cases=cases)))
+    print("gdn_scalar_reference.json:", [c["name"] for c in cases])
+
+
+def gdn_torch_recurrence(ref: Path):
+    mod = _load(ref / "experiments/gated_deltanet_test/dump_fla_reference_pure.py", "ref_gdn_pure")
+    g = torch.Generator().manual_seed(7)
+    B, T, H, Dk, Dv = 2, 150, 3, 16, 24
+    q = torch.randn(B, T, H, Dk, generator=g, dtype=torch.float64)
+    k = torch.randn(B, T, H, Dk, generator=g, dtype=torch.float64)
+    v = torch.randn(B, T, H, Dv, generator=g, dtype=torch.float64)
+    q = q / q.norm(dim=-1, keepdim=True)
+    k = k / k.norm(dim=-1, keepdim=True)
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=g, dtype=torch.float64))
+    decay = torch.exp(-torch.nn.functional.softplus(torch.randn(B, T, H, generator=g, dtype=torch.float64)))
+    out = mod.gated_delta_rule_recurrence(q, k, v, beta, decay)
+    np.savez_compressed(HERE / "gdn_torch_recurrence.npz", q=q.numpy(), k=k.numpy(), v=v.numpy(),
+                        beta=beta.numpy(), gate=decay.numpy(), out=out.numpy())
+    print("gdn_torch_recurrence.npz", tuple(out.shape))
+
+
+def gdn_go_test_inputs():
+    """Closed-form inputs of TestGatedDeltaScanChunkedMatchesNaiveForwardAndGrad
+    (gpu/gated_delta_scan_test.go:44-83, :174-190): x and the six weights are
+    sin/cos formulas; q,k,v,beta,gate are x @ w_i with sigmoid / exp(-softplus)."""
+    B, T, H, dk, dv, dm, classes = 2, 97, 3, 8, 12, 16, 7
+    shapes = [(dm, H * dk), (dm, H * dk), (dm, H * dv), (dm, H), (dm, H), (dv, classes)]
+    ws = []
+    for wi, (r, c) in enumerate(shapes):
+        scale = np.float32(0.035 if wi in (2, 5) else 0.05)
+        i = np.arange(r * c)
+        angle = ((wi + 1) * (i % 17 + 1)).astype(np.float64)
+        ws.append((scale * (np.sin(angle) * 0.7 + np.cos(angle * 0.37) * 0.3).astype(np.float32)).reshape(r, c))
+    i = np.arange(B * T * dm)
+    x = (np.float32(0.1) * (np.sin((i % 29).astype(np.float64)) * 0.6
+                            + np.cos((i % 11).astype(np.float64)) * 0.4).astype(np.float32)).reshape(B * T, dm)
+    x64 = x.astype(np.float64)
+    q = (x64 @ ws[0]).reshape(B, T, H, dk)
+    k = (x64 @ ws[1]).reshape(B, T, H, dk)
+    v = (x64 @ ws[2]).reshape(B, T, H, dv)
+    beta = 1.0 / (1.0 + np.exp(-(x64 @ ws[3]))).reshape(B, T, H)
+    gate = np.exp(-np.log1p(np.exp(x64 @ ws[4]))).reshape(B, T, H)
+    np.savez_compressed(HERE / "gdn_go_test_inputs.npz", q=q, k=k, v=v, beta=beta, gate=gate)
+    print("gdn_go_test_inputs.npz", q.shape)
+
+
+def mamba3_block_fixture(ref: Path):
+    mod = _load(ref / "experiments/mamba3_reference/generate_fixtures.py", "ref_m3_fix")
+    calls = _record(mod, "mamba3_scan")
+    fx = mod.fixture()
+    checked = json.loads((ref / "train/testdata/mamba3_full_block_reference.json").read_text())
+    want = checked["fixtures"][0]["expected_hidden"]
+    assert max(abs(a - b) for a, b in zip(fx["expected_hidden"], want)) < 1e-12, "generator != checked-in JSON"
+    (a, r), = calls
+    x, dt_raw, lam, theta, a_log, b, c, B, T, D, N, G = a
+    cases = [dict(name="full_block_fixture_scan", B=B, T=T, D=D, N=N, G=G, x=x, dt_raw=dt_raw, lambda_raw=lam,
+                  theta=theta, a_log=a_log, b=b, c=c, y=r,
+                  source="scan call inside experiments/mamba3_reference/generate_fixtures.py fixture(); its block "
+                         "output equals train/testdata/mamba3_full_block_reference.json")]
+    (HERE / "mamba3_scalar_reference.json").write_text(json.dumps(dict(cases=cases)))
+    print("mamba3_scalar_reference.json:", [c["name"] for c in cases])
+
+
+def mamba3_torch_scan(ref: Path):
+    mod = _load(ref / "train/hf_templates/mamba3_mixlab.py", "ref_m3_hf")
+    out = {}
+    for tag, (B, T, D, N, G, seed) in dict(a=(2, 8, 4, 8, 2, 11), b=(2, 37, 8, 16, 1, 12), c=(1, 20, 4, 128, 2, 13)).items():
+        g = torch.Generator().manual_seed(seed)
+        f64 = dict(generator=g, dtype=torch.float64)
+        x = torch.randn(B, T, D, **f64)
+        dt_raw = -1.0 + 0.7 * torch.randn(B, T, D, **f64)
+        lam = torch.randn(B, T, D, **f64)
+        theta = (2 * torch.rand(B, T, D, N // 2, **f64) - 1) * math.pi
+        a_log = math.log(16.0) * torch.rand(D, N, **f64)
+        b = torch.randn(B, T, G, N, **f64)
+        c = torch.randn(B, T, G, N, **f64)
+        fake = types.SimpleNamespace(state_size=N, inner_dim=D, n_groups=G, channels_per_group=D // G, A_log=a_log)
+        mask = torch.ones(B, T, dtype=torch.bool)
+        y = mod.MixlabMamba3CanonicalBlock._selective_scan(
+            fake, x, dt_raw, lam, theta.reshape(B, T, D * (N // 2)), b.reshape(B, T, G * N), c.reshape(B, T, G * N), mask)
+        for nme, t in dict(x=x, dt_raw=dt_raw, lambda_raw=lam, theta=theta, a_log=a_log, b=b, c=c, y=y).items():
+            out[f"{tag}_{nme}"] = t.numpy()
+    np.savez_compressed(HERE / "mamba3_torch_scan.npz", **out)
+    print("mamba3_torch_scan.npz", sorted({k.split('_')[0] for k in out}))
+
+
+def main():
+    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    gdn_block_fixture(ref)
+    gdn_torch_recurrence(ref)
+    gdn_go_test_inputs()
+    mamba3_block_fixture(ref)
+    mamba3_torch_scan(ref)
+
+
+if __name__ == "__main__":
+    main()
