@@ -1,0 +1,194 @@
+/*
+ * mixlab_b200 - C ABI of the B200 (sm_100a) sequence-mixing primitives.
+ *
+ * Drop-in boundary for the operators mixlab's IR lowers `gated_deltanet` and
+ * `mamba3-canonical` blocks to.  Plain C: pointers, sizes, a stream handle.
+ * No exceptions cross this boundary and the compute entry points never
+ * allocate, free or synchronise: every buffer (inputs, outputs, workspace)
+ * is a caller-owned DEVICE pointer and work is enqueued on the caller's
+ * stream.  The `mxb_host_*` entry points are the exception by design: they
+ * take HOST buffers like the reference bridge does (mlx_tensor_input,
+ * gpu/mlx_bridge.h:92-99) and own a device arena created up front.
+ *
+ * Reference interfaces replaced (paths inside the mixlab checkout):
+ *   OP_GATED_DELTA_SCAN        arch/ir.go:586-603, gpu/ir.cpp:4633-4654
+ *     gated_delta_scan_naive   gpu/ir.cpp:2314-2350
+ *     gated_delta_scan_chunked gpu/ir.cpp:2352-2550
+ *     solve_strictly_lower_cuda_primitive  gpu/gated_delta_cuda_primitive.h:8-11
+ *   OP_MAMBA3_SELECTIVE_SCAN   arch/ir.go:528-553, gpu/ir.cpp:4837-4853
+ *     mamba3_selective_scan_cuda_forward / _vjp  gpu/mamba3_cuda_primitive.h:12-33
+ *
+ * Tensor layouts are the reference operator's (row-major, innermost last):
+ *   q,k [B,T,H,Dk]  v,out [B,T,H,Dv]  beta,gate [B,T,H]  state [B,H,Dk,Dv]
+ *   x,dt,lambda,y [B,T,D]  theta [B,T,D,N/2]  a_log [D,N]  b,c [B,T,G,N]
+ */
+#ifndef MIXLAB_B200_H
+#define MIXLAB_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define MXB_API __attribute__((visibility("default")))
+#else
+#define MXB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t mxb_status;
+enum {
+  MXB_OK = 0,
+  MXB_ERR_INVALID_ARGUMENT = -1, /* null pointer, non-positive extent, bad enum */
+  MXB_ERR_UNSUPPORTED = -2,      /* shape / dtype combination no kernel covers */
+  MXB_ERR_WORKSPACE = -3,        /* workspace missing or smaller than *_workspace_bytes */
+  MXB_ERR_CUDA = -4,             /* a CUDA runtime call failed (see mxb_last_cuda_error) */
+  MXB_ERR_ALIGNMENT = -5,        /* pointer not aligned as the entry point requires */
+  MXB_ERR_NO_DEVICE = -6         /* no sm_100 device; there is no CPU fallback */
+};
+
+/* Element types.  1 = float32 matches the reference's mlx_tensor_input.dtype
+ * (gpu/mlx_bridge.h:94); bf16 is new (the reference computes this path in
+ * fp32 only, gpu/ir.cpp:2372-2376). */
+enum { MXB_F32 = 1, MXB_BF16 = 2 };
+
+/* Operator codes, identical to the reference IR (arch/ir.go:53,56). */
+enum { MXB_OP_GATED_DELTA_SCAN = 60, MXB_OP_MAMBA3_SELECTIVE_SCAN = 63 };
+
+MXB_API const char* mxb_status_string(mxb_status s);
+MXB_API int mxb_version(void);
+/* cudaError_t (as int) of the most recent failing CUDA call on this thread. */
+MXB_API int mxb_last_cuda_error(void);
+/* Number of kernels this library has launched in this process (all threads). */
+MXB_API uint64_t mxb_launch_count(void);
+/* Per-launch tracing with CUDA events on the launching stream (the reference has
+ * only compiled-out section timers for this path, gpu/ir.cpp:2426-2431).
+ * enable(1) clears earlier records and starts recording; enable(0) stops.
+ * summary() waits for the recorded events and writes one line per kernel,
+ * "<name> <launches> <total_ms>\n", returning the untruncated length. */
+MXB_API void mxb_trace_enable(int on);
+MXB_API size_t mxb_trace_summary(char* buf, size_t capacity);
+
+/* ------------------------------------------------------------------------
+ * Gated delta rule.  IntParams of OP_GATED_DELTA_SCAN are [B,T,H,Dk,Dv,chunk]
+ * (arch/ir.go:600-602); chunk <= 1 selects the token-by-token recurrence
+ * (gpu/ir.cpp:4648-4652), chunk in [2,64] the chunked WY/UT form.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int32_t B, T, H, Dk, Dv, chunk;
+  int32_t io_dtype;    /* MXB_F32 | MXB_BF16: q,k,v,out,d_out,dq,dk,dv.  beta, gate,
+                          dbeta, dgate and every state are always float32. */
+  int32_t gate_is_log; /* 0: 5th input is the multiplicative gate in (0,1] (reference
+                          convention, arch/ir.go:593); 1: it is the log decay g <= 0
+                          and dgate is the gradient with respect to g. */
+  int32_t flags;       /* MXB_GDN_* bits */
+} mxb_gdn_desc;
+
+enum {
+  MXB_GDN_FORCE_FP32_PATH = 1 /* use the full-fp32 CUDA-core kernels even where a
+                                 tensor-core path exists for the shape */
+};
+
+MXB_API size_t mxb_gdn_fwd_workspace_bytes(const mxb_gdn_desc* d);
+MXB_API size_t mxb_gdn_bwd_workspace_bytes(const mxb_gdn_desc* d);
+
+/* out [B,T,H,Dv]; h0 (optional) initial state, hT (optional) final state,
+ * both [B,H,Dk,Dv] fp32.  Replaces gated_delta_scan_{naive,chunked}
+ * (gpu/ir.cpp:2314-2550), which start from a zero state and return only out. */
+MXB_API mxb_status mxb_gdn_fwd(const mxb_gdn_desc* d, const void* q, const void* k, const void* v,
+                       const float* beta, const float* gate, const float* h0, void* out,
+                       float* hT, void* workspace, size_t workspace_bytes, void* stream);
+
+/* All gradients of (out, hT) with respect to (q,k,v,beta,gate,h0).  The
+ * reference obtains these by MLX autograd through gpu/ir.cpp:2352-2550 with the
+ * solve VJP of gpu/gated_delta_cuda_primitive.cpp:104-132; this is a
+ * hand-written backward.  d_hT, dh0 may be NULL. */
+MXB_API mxb_status mxb_gdn_bwd(const mxb_gdn_desc* d, const void* q, const void* k, const void* v,
+                       const float* beta, const float* gate, const float* h0,
+                       const void* d_out, const float* d_hT, void* dq, void* dk, void* dv,
+                       float* dbeta, float* dgate, float* dh0, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* One token of the recurrence on a persistent state: the loop body of
+ * gated_delta_scan_naive (gpu/ir.cpp:2334-2345).  desc.T is ignored, desc.B is
+ * the number of sequences.  state [B,H,Dk,Dv] fp32 is updated in place;
+ * q,k [B,H,Dk], v,out [B,H,Dv] in io_dtype; beta,gate [B,H] fp32. */
+MXB_API mxb_status mxb_gdn_decode_step(const mxb_gdn_desc* d, float* state, const void* q,
+                               const void* k, const void* v, const float* beta,
+                               const float* gate, void* out, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Mamba-3 exponential-trapezoidal selective scan.  IntParams of
+ * OP_MAMBA3_SELECTIVE_SCAN are [B,T,D,N,G(,chunk)] (arch/ir.go:541-553).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int32_t B, T, D, N, G;
+  int32_t nheads;   /* 0: reference per-channel layout - dt,lambda [B,T,D], theta
+                       [B,T,D,N/2], a_log [D,N].  >0: head-broadcast layout - dt,
+                       lambda, theta [B,T,nheads], a_log [nheads]; D % nheads == 0 and
+                       every channel and state pair of a head shares the value. */
+  int32_t io_dtype; /* x, b, c, y, dy, dx, db, dc.  dt, lambda, theta, a_log and
+                       their gradients are always float32. */
+  int32_t flags;
+} mxb_mamba3_desc;
+
+MXB_API size_t mxb_mamba3_fwd_workspace_bytes(const mxb_mamba3_desc* d);
+MXB_API size_t mxb_mamba3_bwd_workspace_bytes(const mxb_mamba3_desc* d);
+
+/* Replaces mamba3_selective_scan_cuda_forward (gpu/mamba3_cuda_primitive.h:12-24). */
+MXB_API mxb_status mxb_mamba3_fwd(const mxb_mamba3_desc* d, const void* x, const float* dt,
+                          const float* lambda, const float* theta, const float* a_log,
+                          const void* b, const void* c, void* y, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/* Replaces mamba3_selective_scan_cuda_vjp (gpu/mamba3_cuda_primitive.h:26-33):
+ * gradients in the argument order x, dt, lambda, theta, a_log, b, c. */
+MXB_API mxb_status mxb_mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt,
+                          const float* lambda, const float* theta, const float* a_log,
+                          const void* b, const void* c, const void* dy, void* dx,
+                          float* ddt, float* dlambda, float* dtheta, float* da_log,
+                          void* db, void* dc, void* workspace, size_t workspace_bytes,
+                          void* stream);
+
+/* ------------------------------------------------------------------------
+ * Diagnostics (no counterpart in the reference).  One tcgen05.mma tile
+ * D[128 x ncols] = A * B^T from caller-built shared-memory images (device
+ * pointers, multiples of 16 bytes) and raw descriptor fields:
+ *   fields[0..2] = A leading-byte-offset, stride-byte-offset, swizzle mode
+ *   fields[3..5] = the same for B
+ *   fields[6] = instruction descriptor, [7] = number of K steps,
+ *   fields[8], [9] = byte advance of A / B per K step, [10] = ncols (N)
+ * d_out receives the 128 TMEM lanes x ncols fp32 columns; *status is set to 1
+ * if the completion wait gave up.  Used by the tests to pin the operand
+ * layouts the production kernels rely on.
+ * ---------------------------------------------------------------------- */
+MXB_API mxb_status mxb_selftest_umma(const void* a_img, uint32_t a_bytes, const void* b_img,
+                             uint32_t b_bytes, const uint32_t* fields, float* d_out,
+                             int* status, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Host-buffer evaluation, the shape of the reference bridge's
+ * mlx_ir_eval_program_named_for_output / _grads_named_for_output
+ * (gpu/mlx_bridge.h:163-203): caller-owned HOST tensors in, HOST tensors out,
+ * one blocking call.  A context owns a device arena and a stream; it is
+ * created once (the only place this library allocates device memory).
+ * ---------------------------------------------------------------------- */
+typedef struct mxb_host_ctx mxb_host_ctx;
+
+MXB_API mxb_status mxb_host_ctx_create(int device, size_t arena_bytes, mxb_host_ctx** out);
+MXB_API void mxb_host_ctx_destroy(mxb_host_ctx* ctx);
+
+/* Forward (+ backward when d_out != NULL) of OP_GATED_DELTA_SCAN on host
+ * buffers: H2D of the inputs, the kernels, D2H of the results, then a stream
+ * synchronise.  Gradient pointers are ignored when d_out is NULL. */
+MXB_API mxb_status mxb_host_gdn(mxb_host_ctx* ctx, const mxb_gdn_desc* d, const void* q,
+                        const void* k, const void* v, const float* beta, const float* gate,
+                        void* out, const void* d_out, void* dq, void* dk, void* dv,
+                        float* dbeta, float* dgate);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIXLAB_B200_H */

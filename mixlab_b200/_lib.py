@@ -1,0 +1,83 @@
+"""ctypes binding of libmixlab_b200.so.  Fails loudly when the library is absent:
+there is no Python, torch or CPU fallback for any operator."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libmixlab_b200.so")
+
+MXB_F32, MXB_BF16 = 1, 2
+MXB_GDN_FORCE_FP32_PATH = 1
+
+
+class MxbError(RuntimeError):
+    def __init__(self, status: int, what: str, detail: str = ""):
+        self.status = status
+        super().__init__(f"{what}: status {status} ({detail})")
+
+
+class GdnDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("B", "T", "H", "Dk", "Dv", "chunk", "io_dtype", "gate_is_log", "flags")]
+
+
+class Mamba3Desc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("B", "T", "D", "N", "G", "nheads", "io_dtype", "flags")]
+
+
+# name -> (restype, argtypes); the complete export list of include/mixlab_b200.h
+_P = C.c_void_p
+EXPORTS = {
+    "mxb_status_string": (C.c_char_p, [C.c_int32]),
+    "mxb_version": (C.c_int, []),
+    "mxb_last_cuda_error": (C.c_int, []),
+    "mxb_launch_count": (C.c_uint64, []),
+    "mxb_trace_enable": (None, [C.c_int]),
+    "mxb_trace_summary": (C.c_size_t, [C.c_char_p, C.c_size_t]),
+    "mxb_gdn_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(GdnDesc)]),
+    "mxb_gdn_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(GdnDesc)]),
+    "mxb_gdn_fwd": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 9 + [C.c_size_t, _P]),
+    "mxb_gdn_bwd": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 15 + [C.c_size_t, _P]),
+    "mxb_gdn_decode_step": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 8),
+    "mxb_mamba3_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Mamba3Desc)]),
+    "mxb_mamba3_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(Mamba3Desc)]),
+    "mxb_mamba3_fwd": (C.c_int32, [C.POINTER(Mamba3Desc)] + [_P] * 9 + [C.c_size_t, _P]),
+    "mxb_mamba3_bwd": (C.c_int32, [C.POINTER(Mamba3Desc)] + [_P] * 16 + [C.c_size_t, _P]),
+    "mxb_selftest_umma": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint32, _P, _P, _P, _P]),
+    "mxb_host_ctx_create": (C.c_int32, [C.c_int, C.c_size_t, C.POINTER(_P)]),
+    "mxb_host_ctx_destroy": (None, [_P]),
+    "mxb_host_gdn": (C.c_int32, [_P, C.POINTER(GdnDesc)] + [_P] * 12),
+}
+
+_lib = None
+
+
+def load_library(path: str | None = None):
+    """dlopen the C-ABI library and bind every export; raises if it is missing."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = path or LIB_PATH
+    if not os.path.exists(p):
+        raise ImportError(
+            f"{p} not found: build it with `python -m mixlab_b200.build` "
+            "(the kernels have no Python/CPU fallback)")
+    lib = C.CDLL(p)
+    for name, (res, args) in EXPORTS.items():
+        fn = getattr(lib, name)  # AttributeError if an export is missing
+        fn.restype = res
+        fn.argtypes = args
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def lib():
+    return load_library()
+
+
+def check(status: int, what: str):
+    if status != 0:
+        l = lib()
+        raise MxbError(status, what, l.mxb_status_string(status).decode())

@@ -1,0 +1,368 @@
+// C ABI of libmixlab_b200: argument validation, path selection, host-buffer
+// context.  Declarations and the reference interfaces they replace are in
+// include/mixlab_b200.h.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace mxb {
+
+static std::atomic<uint64_t> g_launches{0};
+static thread_local int g_last_cuda_error = 0;
+
+void note_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+void set_last_cuda_error(int e) { g_last_cuda_error = e; }
+mxb_status check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) return MXB_OK;
+  g_last_cuda_error = (int)e;
+  std::fprintf(stderr, "[mixlab_b200] %s: %s\n", what, cudaGetErrorString(e));
+  return MXB_ERR_CUDA;
+}
+
+// ---- per-launch event tracing -------------------------------------------
+struct TraceRec { const char* name; cudaEvent_t e0, e1; };
+static std::atomic<bool> g_trace_on{false};
+static std::mutex g_trace_mu;
+static std::vector<TraceRec> g_trace;
+static thread_local cudaEvent_t g_open_e0 = nullptr;
+static thread_local const char* g_open_name = nullptr;
+
+void trace_begin(const char* name, cudaStream_t st) {
+  if (!g_trace_on.load(std::memory_order_relaxed)) return;
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, st);
+  g_open_e0 = e;
+  g_open_name = name;
+}
+void trace_end(cudaStream_t st) {
+  if (!g_open_e0) return;
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreate(&e) == cudaSuccess) {
+    cudaEventRecord(e, st);
+    std::lock_guard<std::mutex> lk(g_trace_mu);
+    g_trace.push_back({g_open_name, g_open_e0, e});
+  } else {
+    cudaEventDestroy(g_open_e0);
+  }
+  g_open_e0 = nullptr;
+}
+static void trace_clear() {
+  std::lock_guard<std::mutex> lk(g_trace_mu);
+  for (auto& r : g_trace) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+  g_trace.clear();
+}
+
+// kernels (other translation units)
+mxb_status gdn_decode_dispatch(const mxb_gdn_desc*, float*, const void*, const void*, const void*,
+                               const float*, const float*, void*, cudaStream_t);
+size_t gdn_simt_workspace_bytes(const mxb_gdn_desc*, bool bwd);
+bool gdn_simt_supported(const mxb_gdn_desc*);
+mxb_status gdn_simt_fwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*,
+                        const float*, const float*, void*, float*, void*, cudaStream_t);
+mxb_status gdn_simt_bwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*,
+                        const float*, const float*, const void*, const float*, void*, void*, void*,
+                        float*, float*, float*, void*, cudaStream_t);
+bool gdn_tc_supported(const mxb_gdn_desc*);
+size_t gdn_tc_workspace_bytes(const mxb_gdn_desc*, bool bwd);
+mxb_status gdn_tc_fwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*,
+                      const float*, const float*, void*, float*, void*, cudaStream_t);
+mxb_status gdn_tc_bwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*,
+                      const float*, const float*, const void*, const float*, void*, void*, void*,
+                      float*, float*, float*, void*, cudaStream_t);
+mxb_status umma_selftest(const void*, uint32_t, const void*, uint32_t, const uint32_t*, float*, int*, cudaStream_t);
+bool mamba3_supported(const mxb_mamba3_desc*);
+size_t mamba3_workspace_bytes(const mxb_mamba3_desc*, bool bwd);
+mxb_status mamba3_fwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*,
+                      const float*, const void*, const void*, void*, cudaStream_t);
+mxb_status mamba3_bwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*,
+                      const float*, const void*, const void*, const void*, void*, float*, float*,
+                      float*, float*, void*, void*, void*, cudaStream_t);
+
+static mxb_status check_gdn_desc(const mxb_gdn_desc* d, bool need_T) {
+  if (!d) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->B <= 0 || d->H <= 0 || d->Dk <= 0 || d->Dv <= 0) return MXB_ERR_INVALID_ARGUMENT;
+  if (need_T && d->T <= 0) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->io_dtype != MXB_F32 && d->io_dtype != MXB_BF16) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->gate_is_log != 0 && d->gate_is_log != 1) return MXB_ERR_INVALID_ARGUMENT;
+  return MXB_OK;
+}
+
+static bool use_tc(const mxb_gdn_desc* d) {
+  return !(d->flags & MXB_GDN_FORCE_FP32_PATH) && gdn_tc_supported(d);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace mxb
+
+using namespace mxb;
+
+extern "C" {
+
+const char* mxb_status_string(mxb_status s) {
+  switch (s) {
+    case MXB_OK: return "ok";
+    case MXB_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case MXB_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case MXB_ERR_WORKSPACE: return "workspace missing or too small";
+    case MXB_ERR_CUDA: return "CUDA runtime error";
+    case MXB_ERR_ALIGNMENT: return "pointer not sufficiently aligned";
+    case MXB_ERR_NO_DEVICE: return "no sm_100 CUDA device (there is no CPU fallback)";
+    default: return "unknown status";
+  }
+}
+
+int mxb_version(void) { return 100; }
+int mxb_last_cuda_error(void) { return g_last_cuda_error; }
+uint64_t mxb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+void mxb_trace_enable(int on) {
+  trace_clear();
+  g_trace_on.store(on != 0);
+}
+
+size_t mxb_trace_summary(char* buf, size_t cap) {
+  // one line per kernel name: "<name> <launches> <total_ms>\n"; waits for the recorded events.
+  std::lock_guard<std::mutex> lk(g_trace_mu);
+  std::vector<std::string> names;
+  std::vector<int> counts;
+  std::vector<double> totals;
+  for (auto& r : g_trace) {
+    if (cudaEventSynchronize(r.e1) != cudaSuccess) continue;
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, r.e0, r.e1) != cudaSuccess) continue;
+    size_t i = 0;
+    for (; i < names.size(); ++i) if (names[i] == r.name) break;
+    if (i == names.size()) { names.push_back(r.name); counts.push_back(0); totals.push_back(0.0); }
+    counts[i] += 1;
+    totals[i] += ms;
+  }
+  std::string out;
+  for (size_t i = 0; i < names.size(); ++i) {
+    char line[256];
+    std::snprintf(line, sizeof line, "%s %d %.6f\n", names[i].c_str(), counts[i], totals[i]);
+    out += line;
+  }
+  if (buf && cap > 0) {
+    const size_t n = out.size() < cap - 1 ? out.size() : cap - 1;
+    std::memcpy(buf, out.data(), n);
+    buf[n] = 0;
+  }
+  return out.size();
+}
+
+size_t mxb_gdn_fwd_workspace_bytes(const mxb_gdn_desc* d) {
+  if (check_gdn_desc(d, true) != MXB_OK) return 0;
+  if (use_tc(d)) return gdn_tc_workspace_bytes(d, false);
+  return gdn_simt_workspace_bytes(d, false);
+}
+
+size_t mxb_gdn_bwd_workspace_bytes(const mxb_gdn_desc* d) {
+  if (check_gdn_desc(d, true) != MXB_OK) return 0;
+  if (use_tc(d)) return gdn_tc_workspace_bytes(d, true);
+  return gdn_simt_workspace_bytes(d, true);
+}
+
+mxb_status mxb_gdn_fwd(const mxb_gdn_desc* d, const void* q, const void* k, const void* v,
+                       const float* beta, const float* gate, const float* h0, void* out, float* hT,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  mxb_status s = check_gdn_desc(d, true);
+  if (s != MXB_OK) return s;
+  if (!q || !k || !v || !beta || !gate || !out) return MXB_ERR_INVALID_ARGUMENT;
+  const size_t need = mxb_gdn_fwd_workspace_bytes(d);
+  if (need > 0 && (!workspace || workspace_bytes < need)) return MXB_ERR_WORKSPACE;
+  if (need > 0 && !aligned16(workspace)) return MXB_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_tc(d)) return gdn_tc_fwd(d, q, k, v, beta, gate, h0, out, hT, workspace, st);
+  if (!gdn_simt_supported(d)) return MXB_ERR_UNSUPPORTED;
+  return gdn_simt_fwd(d, q, k, v, beta, gate, h0, out, hT, workspace, st);
+}
+
+mxb_status mxb_gdn_bwd(const mxb_gdn_desc* d, const void* q, const void* k, const void* v,
+                       const float* beta, const float* gate, const float* h0, const void* d_out,
+                       const float* d_hT, void* dq, void* dk, void* dv, float* dbeta, float* dgate,
+                       float* dh0, void* workspace, size_t workspace_bytes, void* stream) {
+  mxb_status s = check_gdn_desc(d, true);
+  if (s != MXB_OK) return s;
+  if (!q || !k || !v || !beta || !gate || !d_out || !dq || !dk || !dv || !dbeta || !dgate)
+    return MXB_ERR_INVALID_ARGUMENT;
+  const size_t need = mxb_gdn_bwd_workspace_bytes(d);
+  if (!workspace || workspace_bytes < need) return MXB_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return MXB_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (use_tc(d))
+    return gdn_tc_bwd(d, q, k, v, beta, gate, h0, d_out, d_hT, dq, dk, dv, dbeta, dgate, dh0, workspace, st);
+  if (!gdn_simt_supported(d)) return MXB_ERR_UNSUPPORTED;
+  return gdn_simt_bwd(d, q, k, v, beta, gate, h0, d_out, d_hT, dq, dk, dv, dbeta, dgate, dh0, workspace, st);
+}
+
+mxb_status mxb_gdn_decode_step(const mxb_gdn_desc* d, float* state, const void* q, const void* k,
+                               const void* v, const float* beta, const float* gate, void* out,
+                               void* stream) {
+  mxb_status s = check_gdn_desc(d, false);
+  if (s != MXB_OK) return s;
+  if (!state || !q || !k || !v || !beta || !gate || !out) return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(state)) return MXB_ERR_ALIGNMENT;
+  return gdn_decode_dispatch(d, state, q, k, v, beta, gate, out, static_cast<cudaStream_t>(stream));
+}
+
+static mxb_status check_m3_desc(const mxb_mamba3_desc* d) {
+  if (!d) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->B <= 0 || d->T <= 0 || d->D <= 0 || d->N <= 0 || d->G <= 0) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->io_dtype != MXB_F32 && d->io_dtype != MXB_BF16) return MXB_ERR_INVALID_ARGUMENT;
+  if (!mamba3_supported(d)) return MXB_ERR_UNSUPPORTED;
+  return MXB_OK;
+}
+
+size_t mxb_mamba3_fwd_workspace_bytes(const mxb_mamba3_desc* d) {
+  return check_m3_desc(d) == MXB_OK ? mamba3_workspace_bytes(d, false) : 0;
+}
+size_t mxb_mamba3_bwd_workspace_bytes(const mxb_mamba3_desc* d) {
+  return check_m3_desc(d) == MXB_OK ? mamba3_workspace_bytes(d, true) : 0;
+}
+
+mxb_status mxb_mamba3_fwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lambda,
+                          const float* theta, const float* a_log, const void* b, const void* c, void* y,
+                          void* workspace, size_t workspace_bytes, void* stream) {
+  mxb_status s = check_m3_desc(d);
+  if (s != MXB_OK) return s;
+  if (!x || !dt || !lambda || !theta || !a_log || !b || !c || !y) return MXB_ERR_INVALID_ARGUMENT;
+  (void)workspace; (void)workspace_bytes;
+  return mamba3_fwd(d, x, dt, lambda, theta, a_log, b, c, y, static_cast<cudaStream_t>(stream));
+}
+
+mxb_status mxb_mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lambda,
+                          const float* theta, const float* a_log, const void* b, const void* c,
+                          const void* dy, void* dx, float* ddt, float* dlambda, float* dtheta,
+                          float* da_log, void* db, void* dc, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  mxb_status s = check_m3_desc(d);
+  if (s != MXB_OK) return s;
+  if (!x || !dt || !lambda || !theta || !a_log || !b || !c || !dy || !dx || !ddt || !dlambda ||
+      !dtheta || !da_log || !db || !dc)
+    return MXB_ERR_INVALID_ARGUMENT;
+  const size_t need = mamba3_workspace_bytes(d, true);
+  if (!workspace || workspace_bytes < need) return MXB_ERR_WORKSPACE;
+  return mamba3_bwd(d, x, dt, lambda, theta, a_log, b, c, dy, dx, ddt, dlambda, dtheta, da_log, db, dc,
+                    workspace, static_cast<cudaStream_t>(stream));
+}
+
+mxb_status mxb_selftest_umma(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,
+                             const uint32_t* fields, float* d_out, int* status, void* stream) {
+  if (!a_img || !b_img || !fields || !d_out || !status) return MXB_ERR_INVALID_ARGUMENT;
+  return umma_selftest(a_img, a_bytes, b_img, b_bytes, fields, d_out, status, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------- host ctx
+struct mxb_host_ctx {
+  int device;
+  char* arena;
+  size_t arena_bytes;
+  cudaStream_t stream;
+};
+
+#define MXB_CUDA_TRY(expr)                          \
+  do {                                              \
+    cudaError_t e__ = (expr);                       \
+    if (e__ != cudaSuccess) {                       \
+      g_last_cuda_error = (int)e__;                 \
+      return MXB_ERR_CUDA;                          \
+    }                                               \
+  } while (0)
+
+mxb_status mxb_host_ctx_create(int device, size_t arena_bytes, mxb_host_ctx** out) {
+  if (!out || arena_bytes == 0) return MXB_ERR_INVALID_ARGUMENT;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) return MXB_ERR_NO_DEVICE;
+  MXB_CUDA_TRY(cudaSetDevice(device));
+  mxb_host_ctx* c = new (std::nothrow) mxb_host_ctx{};
+  if (!c) return MXB_ERR_INVALID_ARGUMENT;
+  c->device = device;
+  c->arena_bytes = arena_bytes;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->arena), arena_bytes);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) {
+    g_last_cuda_error = (int)e;
+    if (c->arena) cudaFree(c->arena);
+    delete c;
+    return MXB_ERR_CUDA;
+  }
+  *out = c;
+  return MXB_OK;
+}
+
+void mxb_host_ctx_destroy(mxb_host_ctx* c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  cudaStreamSynchronize(c->stream);
+  cudaStreamDestroy(c->stream);
+  cudaFree(c->arena);
+  delete c;
+}
+
+mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, const void* k,
+                        const void* v, const float* beta, const float* gate, void* out,
+                        const void* d_out, void* dq, void* dk, void* dv, float* dbeta, float* dgate) {
+  if (!c) return MXB_ERR_INVALID_ARGUMENT;
+  mxb_status s = check_gdn_desc(d, true);
+  if (s != MXB_OK) return s;
+  if (!q || !k || !v || !beta || !gate || !out) return MXB_ERR_INVALID_ARGUMENT;
+  const bool bwd = d_out != nullptr;
+  if (bwd && (!dq || !dk || !dv || !dbeta || !dgate)) return MXB_ERR_INVALID_ARGUMENT;
+  MXB_CUDA_TRY(cudaSetDevice(c->device));
+  const size_t es = d->io_dtype == MXB_F32 ? 4 : 2;
+  const size_t nk = (size_t)d->B * d->T * d->H * d->Dk, nv = (size_t)d->B * d->T * d->H * d->Dv;
+  const size_t ns = (size_t)d->B * d->T * d->H;
+  const size_t ws_f = mxb_gdn_fwd_workspace_bytes(d), ws_b = bwd ? mxb_gdn_bwd_workspace_bytes(d) : 0;
+  Carver cv(c->arena);
+  char* dq_in = cv.take<char>(nk * es);
+  char* dk_in = cv.take<char>(nk * es);
+  char* dv_in = cv.take<char>(nv * es);
+  float* dbeta_in = cv.take<float>(ns);
+  float* dgate_in = cv.take<float>(ns);
+  char* dout = cv.take<char>(nv * es);
+  char *ddo = nullptr, *g_q = nullptr, *g_k = nullptr, *g_v = nullptr;
+  float *g_b = nullptr, *g_g = nullptr;
+  if (bwd) {
+    ddo = cv.take<char>(nv * es);
+    g_q = cv.take<char>(nk * es);
+    g_k = cv.take<char>(nk * es);
+    g_v = cv.take<char>(nv * es);
+    g_b = cv.take<float>(ns);
+    g_g = cv.take<float>(ns);
+  }
+  char* ws = cv.take<char>(ws_f > ws_b ? ws_f : ws_b);
+  if (cv.bytes() > c->arena_bytes) return MXB_ERR_WORKSPACE;
+  cudaStream_t st = c->stream;
+  MXB_CUDA_TRY(cudaMemcpyAsync(dq_in, q, nk * es, cudaMemcpyHostToDevice, st));
+  MXB_CUDA_TRY(cudaMemcpyAsync(dk_in, k, nk * es, cudaMemcpyHostToDevice, st));
+  MXB_CUDA_TRY(cudaMemcpyAsync(dv_in, v, nv * es, cudaMemcpyHostToDevice, st));
+  MXB_CUDA_TRY(cudaMemcpyAsync(dbeta_in, beta, ns * 4, cudaMemcpyHostToDevice, st));
+  MXB_CUDA_TRY(cudaMemcpyAsync(dgate_in, gate, ns * 4, cudaMemcpyHostToDevice, st));
+  if (bwd) MXB_CUDA_TRY(cudaMemcpyAsync(ddo, d_out, nv * es, cudaMemcpyHostToDevice, st));
+  s = mxb_gdn_fwd(d, dq_in, dk_in, dv_in, dbeta_in, dgate_in, nullptr, dout, nullptr, ws, ws_f, st);
+  if (s != MXB_OK) return s;
+  MXB_CUDA_TRY(cudaMemcpyAsync(out, dout, nv * es, cudaMemcpyDeviceToHost, st));
+  if (bwd) {
+    s = mxb_gdn_bwd(d, dq_in, dk_in, dv_in, dbeta_in, dgate_in, nullptr, ddo, nullptr, g_q, g_k, g_v,
+                    g_b, g_g, nullptr, ws, ws_b, st);
+    if (s != MXB_OK) return s;
+    MXB_CUDA_TRY(cudaMemcpyAsync(dq, g_q, nk * es, cudaMemcpyDeviceToHost, st));
+    MXB_CUDA_TRY(cudaMemcpyAsync(dk, g_k, nk * es, cudaMemcpyDeviceToHost, st));
+    MXB_CUDA_TRY(cudaMemcpyAsync(dv, g_v, nv * es, cudaMemcpyDeviceToHost, st));
+    MXB_CUDA_TRY(cudaMemcpyAsync(dbeta, g_b, ns * 4, cudaMemcpyDeviceToHost, st));
+    MXB_CUDA_TRY(cudaMemcpyAsync(dgate, g_g, ns * 4, cudaMemcpyDeviceToHost, st));
+  }
+  MXB_CUDA_TRY(cudaStreamSynchronize(st));
+  return MXB_OK;
+}
+
+}  // extern "C"

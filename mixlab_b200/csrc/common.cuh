@@ -1,0 +1,80 @@
+// Shared device/host helpers for the mixlab_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mixlab_b200.h"
+
+namespace mxb {
+
+// Numeric guards of the reference's chunked scan (gpu/ir.cpp:35-37).
+constexpr float kGateFloor = 1e-30f;
+constexpr float kLogGateFloor = -69.07755278982137f;  // log(1e-30)
+constexpr float kExpClampMin = -80.0f;
+
+// exp(clamp(x, -80, 0)) - stable_exp_nonpos, gpu/ir.cpp:903-905.
+__device__ __forceinline__ float exp_nonpos(float x) {
+  return __expf(fminf(fmaxf(x, kExpClampMin), 0.0f));
+}
+// Full-precision variant for the fp32 parity path.
+__device__ __forceinline__ float exp_nonpos_precise(float x) {
+  return expf(fminf(fmaxf(x, kExpClampMin), 0.0f));
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ---- host side ----------------------------------------------------------
+void note_launch(int n = 1);           // bumps mxb_launch_count()
+mxb_status check_launch(const char* what);  // cudaGetLastError -> status
+void set_last_cuda_error(int e);
+// Optional per-launch CUDA-event tracing (mxb_trace_enable); no-ops when off.
+void trace_begin(const char* name, cudaStream_t st);
+void trace_end(cudaStream_t st);
+
+// Launch wrapper: counts the launch and, when tracing is on, brackets it with events.
+#define MXB_LAUNCH(name, st, ...)   \
+  do {                              \
+    ::mxb::trace_begin(name, st);   \
+    __VA_ARGS__;                    \
+    ::mxb::trace_end(st);           \
+    ::mxb::note_launch();           \
+  } while (0)
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+// Carves a caller-provided workspace into 256-byte aligned pieces.
+struct Carver {
+  char* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+  template <typename T>
+  T* take(size_t count) {
+    off = align_up(off, 256);
+    T* r = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * sizeof(T);
+    return r;
+  }
+  size_t bytes() const { return align_up(off, 256); }
+};
+
+}  // namespace mxb

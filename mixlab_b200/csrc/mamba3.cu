@@ -1,0 +1,431 @@
+// Mamba-3 exponential-trapezoidal selective scan with rotated state pairs,
+// forward and backward - recurrent form.
+//
+// Recurrence (reference: gpu/cuda_kernels/mamba3_selective_scan_fwd_v2_emit.cu:65-115,
+// closed-form VJP gpu/ir.cpp:1526-1623, float64 oracle
+// train/gpu_trainer_mamba3_test.go:612-808):
+//     dt = softplus(dt_raw); lam = sigmoid(lambda_raw); A = -exp(a_log)
+//     phi_t = phi_{t-1} + dt_t theta_t
+//     Brot = R^T(phi) B ; Crot = R^T(phi) C   (even' = c e + s o ; odd' = -s e + c o)
+//     alpha = exp(dt A); beta = (1-lam) dt alpha; gamma = lam dt
+//     h_t = alpha h_{t-1} + gamma Brot_t x_t + [t>0] beta Brot_{t-1} x_{t-1}
+//     y_t = sum_n h_t[n] Crot_t[n]
+//
+// Mapping: one warp per (batch, channel); a lane owns state pairs lane, lane+32,
+// ... (PR of them), so d_state up to 256 is covered (the reference's kernels stop
+// at 64, gpu/mamba3_cuda_primitive.cpp:22).  The cumulative angle is kept wrapped
+// to [-pi, pi] so fp32 keeps its resolution over thousands of steps.
+//
+// Two parameter layouts share the kernels through index helpers: the
+// reference's per-channel one, and a head-broadcast one where dt, lambda, theta
+// and a_log carry one value per (b,t,head) / per head.
+//
+// Backward: a checkpointing forward pass stores (h, phi) every W steps; the
+// reverse pass walks the windows backwards, replays each window into shared
+// memory and applies the closed-form adjoint step by step.  Sums over the
+// channels of a group (dB, dC) or of a head (head-broadcast gradients) and over
+// the batch (da_log) are accumulated with fp32 atomics into zeroed buffers.
+#include "common.cuh"
+
+namespace mxb {
+
+constexpr int kM3Window = 16;
+
+struct M3P {
+  int B, T, D, N, G, NH, Kp, nW;
+  const void *x, *b, *c;
+  const float *dt, *lam, *theta, *a_log;
+  void* y;
+  float *ck_h, *ck_phi;  // checkpoints [B,nW,D,N], [B,nW,D,Kp]
+  const void* dy;
+  void* dx;
+  float *ddt, *dlam, *dtheta, *da_log;
+  float *db32, *dc32;  // fp32 accumulators [B,T,G,N]
+};
+
+__device__ __forceinline__ float m3_softplus(float x) {
+  if (x > 20.f) return x;
+  if (x < -20.f) return expf(x);
+  return log1pf(expf(x));
+}
+__device__ __forceinline__ float m3_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ float m3_wrap(float phi) {
+  // Cody-Waite reduction by 2 pi = 6.28125 + 1.9353071795864769e-3
+  const float k = rintf(phi * 0.15915494309189535f);
+  phi = fmaf(-k, 6.28125f, phi);
+  return fmaf(-k, 1.9353071795864769e-3f, phi);
+}
+
+struct M3Idx {
+  int D, N, G, NH, Kp, cpg, cph;
+  __device__ M3Idx(const M3P& p)
+      : D(p.D), N(p.N), G(p.G), NH(p.NH), Kp(p.Kp), cpg(p.D / p.G), cph(p.NH > 0 ? p.D / p.NH : 1) {}
+  __device__ size_t chan(size_t row, int d) const { return NH > 0 ? row * NH + d / cph : row * D + d; }
+  __device__ size_t theta(size_t row, int d, int kp) const {
+    return NH > 0 ? row * NH + d / cph : (row * D + d) * Kp + kp;
+  }
+  __device__ size_t alog(int d, int n) const { return NH > 0 ? (size_t)(d / cph) : (size_t)d * N + n; }
+  __device__ size_t grp(size_t row, int d, int n) const { return (row * G + d / cpg) * N + n; }
+};
+
+// ------------------------------------------------------------------ forward
+// Also the checkpoint pass of the backward (y == nullptr, ck_h != nullptr).
+template <typename IO, int PR>
+__global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int d = blockIdx.x * 8 + warp, b = blockIdx.y;
+  if (d >= p.D) return;
+  const M3Idx ix(p);
+  const IO* X = static_cast<const IO*>(p.x);
+  const IO* Bp = static_cast<const IO*>(p.b);
+  const IO* Cp = static_cast<const IO*>(p.c);
+  IO* Y = static_cast<IO*>(p.y);
+  float A0[PR], A1[PR], h0[PR], h1[PR], phi[PR], pb0[PR], pb1[PR];
+#pragma unroll
+  for (int r = 0; r < PR; ++r) {
+    const int kp = lane + 32 * r;
+    const bool act = kp < p.Kp;
+    A0[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp)]) : 0.f;
+    A1[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp + 1)]) : 0.f;
+    h0[r] = h1[r] = phi[r] = pb0[r] = pb1[r] = 0.f;
+  }
+  float px = 0.f;
+  for (int t = 0; t < p.T; ++t) {
+    const size_t row = (size_t)b * p.T + t;
+    if (p.ck_h && (t % kM3Window) == 0) {
+      const size_t wrow = ((size_t)b * p.nW + t / kM3Window) * p.D + d;
+#pragma unroll
+      for (int r = 0; r < PR; ++r) {
+        const int kp = lane + 32 * r;
+        if (kp < p.Kp) {
+          p.ck_h[wrow * p.N + 2 * kp] = h0[r];
+          p.ck_h[wrow * p.N + 2 * kp + 1] = h1[r];
+          p.ck_phi[wrow * p.Kp + kp] = phi[r];
+        }
+      }
+    }
+    const float x = to_f32(X[row * p.D + d]);
+    const float dt = m3_softplus(p.dt[ix.chan(row, d)]);
+    const float lam = m3_sigmoid(p.lam[ix.chan(row, d)]);
+    const float gamma = lam * dt, bfac = (1.f - lam) * dt;
+    float part = 0.f;
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) {
+        phi[r] = m3_wrap(fmaf(dt, p.theta[ix.theta(row, d, kp)], phi[r]));
+        float s, c;
+        sincosf(phi[r], &s, &c);
+        const size_t gi = ix.grp(row, d, 2 * kp);
+        const float be = to_f32(Bp[gi]), bo = to_f32(Bp[gi + 1]);
+        const float ce = to_f32(Cp[gi]), co = to_f32(Cp[gi + 1]);
+        const float b0 = c * be + s * bo, b1 = -s * be + c * bo;
+        const float c0 = c * ce + s * co, c1 = -s * ce + c * co;
+        const float al0 = expf(dt * A0[r]), al1 = expf(dt * A1[r]);
+        h0[r] = al0 * h0[r] + gamma * b0 * x + bfac * al0 * pb0[r] * px;
+        h1[r] = al1 * h1[r] + gamma * b1 * x + bfac * al1 * pb1[r] * px;
+        part += h0[r] * c0 + h1[r] * c1;
+        pb0[r] = b0;
+        pb1[r] = b1;
+      }
+    }
+    px = x;  // t = 0 uses px = 0, which realises the [t>0] factor
+    if (Y) {
+      part = warp_sum(part);
+      if (lane == 0) Y[row * p.D + d] = from_f32<IO>(part);
+    }
+  }
+}
+
+// ----------------------------------------------------------------- backward
+template <typename IO, int PR>
+__global__ void __launch_bounds__(128) mamba3_bwd_kernel(M3P p) {
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int d = blockIdx.x * 4 + warp, b = blockIdx.y;
+  if (d >= p.D) return;
+  // per warp: [W][PR][3][32]  (h0_after, h1_after, phi)
+  float* buf = smem + (size_t)warp * kM3Window * PR * 3 * 32;
+  auto slot = [&](int s, int r, int which) -> float& { return buf[((s * PR + r) * 3 + which) * 32 + lane]; };
+  const M3Idx ix(p);
+  const IO* X = static_cast<const IO*>(p.x);
+  const IO* Bp = static_cast<const IO*>(p.b);
+  const IO* Cp = static_cast<const IO*>(p.c);
+  const IO* DY = static_cast<const IO*>(p.dy);
+  IO* DX = static_cast<IO*>(p.dx);
+  const bool per_head = p.NH > 0;
+
+  float A0[PR], A1[PR], dh0[PR], dh1[PR], carry[PR], pgb0[PR], pgb1[PR], dal0[PR], dal1[PR];
+#pragma unroll
+  for (int r = 0; r < PR; ++r) {
+    const int kp = lane + 32 * r;
+    const bool act = kp < p.Kp;
+    A0[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp)]) : 0.f;
+    A1[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp + 1)]) : 0.f;
+    dh0[r] = dh1[r] = carry[r] = pgb0[r] = pgb1[r] = dal0[r] = dal1[r] = 0.f;
+  }
+  float pend_dx = 0.f;  // contribution of step t+1 to dx_t (lane partial)
+
+  for (int w = p.nW - 1; w >= 0; --w) {
+    const int ts = w * kM3Window, te = min(p.T, ts + kM3Window);
+    const size_t wrow = ((size_t)b * p.nW + w) * p.D + d;
+    // ---- replay the window forward, keeping h_after and phi per step ----
+    float h0[PR], h1[PR], phi[PR], pb0[PR], pb1[PR], ck0[PR], ck1[PR], ckphi[PR];
+    float px = ts > 0 ? to_f32(X[((size_t)b * p.T + ts - 1) * p.D + d]) : 0.f;
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      const bool act = kp < p.Kp;
+      ck0[r] = h0[r] = act ? p.ck_h[wrow * p.N + 2 * kp] : 0.f;
+      ck1[r] = h1[r] = act ? p.ck_h[wrow * p.N + 2 * kp + 1] : 0.f;
+      ckphi[r] = phi[r] = act ? p.ck_phi[wrow * p.Kp + kp] : 0.f;
+      pb0[r] = pb1[r] = 0.f;
+      if (act && ts > 0) {  // rotated B of step ts-1 uses the checkpointed angle
+        float s, c;
+        sincosf(phi[r], &s, &c);
+        const size_t gi = ix.grp((size_t)b * p.T + ts - 1, d, 2 * kp);
+        const float be = to_f32(Bp[gi]), bo = to_f32(Bp[gi + 1]);
+        pb0[r] = c * be + s * bo;
+        pb1[r] = -s * be + c * bo;
+      }
+    }
+    for (int t = ts; t < te; ++t) {
+      const size_t row = (size_t)b * p.T + t;
+      const float x = to_f32(X[row * p.D + d]);
+      const float dt = m3_softplus(p.dt[ix.chan(row, d)]);
+      const float lam = m3_sigmoid(p.lam[ix.chan(row, d)]);
+      const float gamma = lam * dt, bfac = (1.f - lam) * dt;
+#pragma unroll
+      for (int r = 0; r < PR; ++r) {
+        const int kp = lane + 32 * r;
+        if (kp < p.Kp) {
+          phi[r] = m3_wrap(fmaf(dt, p.theta[ix.theta(row, d, kp)], phi[r]));
+          float s, c;
+          sincosf(phi[r], &s, &c);
+          const size_t gi = ix.grp(row, d, 2 * kp);
+          const float be = to_f32(Bp[gi]), bo = to_f32(Bp[gi + 1]);
+          const float b0 = c * be + s * bo, b1 = -s * be + c * bo;
+          const float al0 = expf(dt * A0[r]), al1 = expf(dt * A1[r]);
+          h0[r] = al0 * h0[r] + gamma * b0 * x + bfac * al0 * pb0[r] * px;
+          h1[r] = al1 * h1[r] + gamma * b1 * x + bfac * al1 * pb1[r] * px;
+          pb0[r] = b0;
+          pb1[r] = b1;
+          slot(t - ts, r, 0) = h0[r];
+          slot(t - ts, r, 1) = h1[r];
+          slot(t - ts, r, 2) = phi[r];
+        }
+      }
+      px = x;
+    }
+    // ---- reverse over the window ----
+    for (int t = te - 1; t >= ts; --t) {
+      const size_t row = (size_t)b * p.T + t;
+      const float x = to_f32(X[row * p.D + d]);
+      const float xprev = t > 0 ? to_f32(X[(row - 1) * p.D + d]) : 0.f;
+      const float dt_raw = p.dt[ix.chan(row, d)];
+      const float dt = m3_softplus(dt_raw);
+      const float lam = m3_sigmoid(p.lam[ix.chan(row, d)]);
+      const float dy = to_f32(DY[row * p.D + d]);
+      float s_dx = pend_dx, s_pdx = 0.f, s_dlam = 0.f, s_ddelta = 0.f, s_dtheta = 0.f;
+#pragma unroll
+      for (int r = 0; r < PR; ++r) {
+        const int kp = lane + 32 * r;
+        if (kp < p.Kp) {
+          const float ha0 = slot(t - ts, r, 0), ha1 = slot(t - ts, r, 1), ph = slot(t - ts, r, 2);
+          const float hb0 = (t == ts) ? ck0[r] : slot(t - ts - 1, r, 0);
+          const float hb1 = (t == ts) ? ck1[r] : slot(t - ts - 1, r, 1);
+          const float php = (t == ts) ? ckphi[r] : slot(t - ts - 1, r, 2);
+          float s, c, sp, cp;
+          sincosf(ph, &s, &c);
+          sincosf(php, &sp, &cp);
+          const size_t gi = ix.grp(row, d, 2 * kp);
+          const float be = to_f32(Bp[gi]), bo = to_f32(Bp[gi + 1]);
+          const float ce = to_f32(Cp[gi]), co = to_f32(Cp[gi + 1]);
+          const float b0 = c * be + s * bo, b1 = -s * be + c * bo;
+          const float c0 = c * ce + s * co, c1 = -s * ce + c * co;
+          float q0 = 0.f, q1 = 0.f;  // rotated B of step t-1
+          if (t > 0) {
+            const size_t gp = ix.grp(row - 1, d, 2 * kp);
+            const float pe = to_f32(Bp[gp]), po = to_f32(Bp[gp + 1]);
+            q0 = cp * pe + sp * po;
+            q1 = -sp * pe + cp * po;
+          }
+          const float al0 = expf(dt * A0[r]), al1 = expf(dt * A1[r]);
+          const float up0 = dh0[r] + dy * c0, up1 = dh1[r] + dy * c1;
+          s_dx += lam * dt * (b0 * up0 + b1 * up1);
+          const float gb0 = lam * dt * x * up0 + pgb0[r];
+          const float gb1 = lam * dt * x * up1 + pgb1[r];
+          const float gc0 = dy * ha0, gc1 = dy * ha1;
+          const float pin0 = q0 * xprev, pin1 = q1 * xprev;
+          const float bni0 = (1.f - lam) * dt * al0, bni1 = (1.f - lam) * dt * al1;
+          s_pdx += bni0 * q0 * up0 + bni1 * q1 * up1;
+          pgb0[r] = bni0 * xprev * up0;
+          pgb1[r] = bni1 * xprev * up1;
+          s_dlam += (-dt * al0 * pin0 + dt * b0 * x) * up0 + (-dt * al1 * pin1 + dt * b1 * x) * up1;
+          const float dterm0 = A0[r] * al0 * hb0 + (1.f - lam) * (al0 + dt * A0[r] * al0) * pin0 + lam * b0 * x;
+          const float dterm1 = A1[r] * al1 * hb1 + (1.f - lam) * (al1 + dt * A1[r] * al1) * pin1 + lam * b1 * x;
+          s_ddelta += dterm0 * up0 + dterm1 * up1;
+          dal0[r] += (dt * al0 * A0[r] * hb0 + (1.f - lam) * dt * dt * al0 * A0[r] * pin0) * up0;
+          dal1[r] += (dt * al1 * A1[r] * hb1 + (1.f - lam) * dt * dt * al1 * A1[r] * pin1) * up1;
+          dh0[r] = al0 * up0;
+          dh1[r] = al1 * up1;
+          // rotation adjoint
+          atomicAdd(&p.db32[gi], c * gb0 - s * gb1);
+          atomicAdd(&p.db32[gi + 1], s * gb0 + c * gb1);
+          atomicAdd(&p.dc32[gi], c * gc0 - s * gc1);
+          atomicAdd(&p.dc32[gi + 1], s * gc0 + c * gc1);
+          carry[r] += b1 * gb0 - b0 * gb1 + c1 * gc0 - c0 * gc1;
+          const float th = p.theta[ix.theta(row, d, kp)];
+          s_ddelta += carry[r] * th;
+          if (per_head) s_dtheta += carry[r] * dt;
+          else p.dtheta[ix.theta(row, d, kp)] = carry[r] * dt;
+        }
+      }
+      s_dx = warp_sum(s_dx);
+      s_dlam = warp_sum(s_dlam) * lam * (1.f - lam);
+      s_ddelta = warp_sum(s_ddelta) * m3_sigmoid(dt_raw);
+      if (per_head) s_dtheta = warp_sum(s_dtheta);
+      pend_dx = s_pdx;
+      if (lane == 0) {
+        DX[row * p.D + d] = from_f32<IO>(s_dx);
+        if (per_head) {
+          atomicAdd(&p.ddt[ix.chan(row, d)], s_ddelta);
+          atomicAdd(&p.dlam[ix.chan(row, d)], s_dlam);
+          atomicAdd(&p.dtheta[ix.chan(row, d)], s_dtheta);
+        } else {
+          p.ddt[row * p.D + d] = s_ddelta;
+          p.dlam[row * p.D + d] = s_dlam;
+        }
+      }
+    }
+  }
+  // da_log: d/d a_log = d/dA * A  (A = -exp(a_log)); the closed form above already carries A.
+  if (per_head) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < PR; ++r) s += dal0[r] + dal1[r];
+    s = warp_sum(s);
+    if (lane == 0) atomicAdd(&p.da_log[ix.alog(d, 0)], s);
+  } else {
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) {
+        atomicAdd(&p.da_log[(size_t)d * p.N + 2 * kp], dal0[r]);
+        atomicAdd(&p.da_log[(size_t)d * p.N + 2 * kp + 1], dal1[r]);
+      }
+    }
+  }
+}
+
+template <typename IO>
+__global__ void m3_cast_kernel(const float* __restrict__ src, IO* __restrict__ dst, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = from_f32<IO>(src[i]);
+}
+
+// --------------------------------------------------------------------- host
+static M3P make_m3(const mxb_mamba3_desc* d) {
+  M3P p{};
+  p.B = d->B; p.T = d->T; p.D = d->D; p.N = d->N; p.G = d->G; p.NH = d->nheads;
+  p.Kp = d->N / 2;
+  p.nW = (d->T + kM3Window - 1) / kM3Window;
+  return p;
+}
+
+bool mamba3_supported(const mxb_mamba3_desc* d) {
+  if (d->N < 2 || d->N % 2 || d->N > 256) return false;
+  if (d->G < 1 || d->D % d->G) return false;
+  if (d->nheads < 0 || (d->nheads > 0 && d->D % d->nheads)) return false;
+  return true;
+}
+
+static size_t carve_m3(M3P& p, void* ws, bool io_f32) {
+  Carver cv(ws);
+  p.ck_h = cv.take<float>((size_t)p.B * p.nW * p.D * p.N);
+  p.ck_phi = cv.take<float>((size_t)p.B * p.nW * p.D * p.Kp);
+  if (!io_f32) {
+    p.db32 = cv.take<float>((size_t)p.B * p.T * p.G * p.N);
+    p.dc32 = cv.take<float>((size_t)p.B * p.T * p.G * p.N);
+  }
+  return cv.bytes();
+}
+
+size_t mamba3_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
+  if (!bwd) return 0;
+  M3P p = make_m3(d);
+  return carve_m3(p, nullptr, d->io_dtype == MXB_F32);
+}
+
+template <typename IO, int PR>
+static mxb_status m3_fwd_launch(const M3P& p, cudaStream_t st) {
+  MXB_LAUNCH("mamba3_fwd_kernel", st, (mamba3_fwd_kernel<IO, PR><<<dim3((p.D + 7) / 8, p.B), 256, 0, st>>>(p)));
+  return check_launch("mamba3_fwd_kernel");
+}
+template <typename IO>
+static mxb_status m3_fwd_pr(const M3P& p, cudaStream_t st) {
+  if (p.Kp <= 32) return m3_fwd_launch<IO, 1>(p, st);
+  if (p.Kp <= 64) return m3_fwd_launch<IO, 2>(p, st);
+  return m3_fwd_launch<IO, 4>(p, st);
+}
+
+template <typename IO, int PR>
+static mxb_status m3_bwd_launch(const M3P& p, cudaStream_t st) {
+  const size_t sm = sizeof(float) * 4 * kM3Window * PR * 3 * 32;
+  if (sm > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(mamba3_bwd_kernel<IO, PR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
+  }
+  MXB_LAUNCH("mamba3_bwd_kernel", st, (mamba3_bwd_kernel<IO, PR><<<dim3((p.D + 3) / 4, p.B), 128, sm, st>>>(p)));
+  return check_launch("mamba3_bwd_kernel");
+}
+template <typename IO>
+static mxb_status m3_bwd_pr(const M3P& p, cudaStream_t st) {
+  if (p.Kp <= 32) return m3_bwd_launch<IO, 1>(p, st);
+  if (p.Kp <= 64) return m3_bwd_launch<IO, 2>(p, st);
+  return m3_bwd_launch<IO, 4>(p, st);
+}
+
+mxb_status mamba3_fwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
+                      const float* theta, const float* a_log, const void* b, const void* c, void* y,
+                      cudaStream_t st) {
+  M3P p = make_m3(d);
+  p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c; p.y = y;
+  return d->io_dtype == MXB_F32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);
+}
+
+mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
+                      const float* theta, const float* a_log, const void* b, const void* c,
+                      const void* dy, void* dx, float* ddt, float* dlam, float* dtheta, float* da_log,
+                      void* db, void* dc, void* ws, cudaStream_t st) {
+  M3P p = make_m3(d);
+  const bool f32 = d->io_dtype == MXB_F32;
+  p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c;
+  p.dy = dy; p.dx = dx; p.ddt = ddt; p.dlam = dlam; p.dtheta = dtheta; p.da_log = da_log;
+  carve_m3(p, ws, f32);
+  const size_t nbc = (size_t)p.B * p.T * p.G * p.N;
+  if (f32) { p.db32 = static_cast<float*>(db); p.dc32 = static_cast<float*>(dc); }
+  cudaError_t e = cudaMemsetAsync(p.db32, 0, nbc * sizeof(float), st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p.dc32, 0, nbc * sizeof(float), st);
+  const size_t nal = p.NH > 0 ? (size_t)p.NH : (size_t)p.D * p.N;
+  if (e == cudaSuccess) e = cudaMemsetAsync(da_log, 0, nal * sizeof(float), st);
+  if (p.NH > 0) {
+    const size_t nh = (size_t)p.B * p.T * p.NH * sizeof(float);
+    if (e == cudaSuccess) e = cudaMemsetAsync(ddt, 0, nh, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(dlam, 0, nh, st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(dtheta, 0, nh, st);
+  }
+  if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
+  mxb_status s = f32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);  // checkpoint pass (y == nullptr)
+  if (s != MXB_OK) return s;
+  s = f32 ? m3_bwd_pr<float>(p, st) : m3_bwd_pr<__nv_bfloat16>(p, st);
+  if (s != MXB_OK) return s;
+  if (!f32) {
+    MXB_LAUNCH("m3_cast_kernel", st, (m3_cast_kernel<__nv_bfloat16><<<592, 256, 0, st>>>(p.db32, static_cast<__nv_bfloat16*>(db), nbc)));
+    MXB_LAUNCH("m3_cast_kernel", st, (m3_cast_kernel<__nv_bfloat16><<<592, 256, 0, st>>>(p.dc32, static_cast<__nv_bfloat16*>(dc), nbc)));
+    s = check_launch("m3_cast_kernel");
+  }
+  return s;
+}
+
+}  // namespace mxb

@@ -1,0 +1,152 @@
+"""Torch-tensor front end over the C ABI, named after the reference operators.
+
+``gated_delta_scan`` mirrors ``Program.GatedDeltaScan`` (arch/ir.go:586-603):
+inputs q,k [B,T,H,Dk], v [B,T,H,Dv], beta, gate [B,T,H], IntParams
+[B,T,H,Dk,Dv,chunk]; ``mamba3_selective_scan`` mirrors
+``Program.Mamba3SelectiveScan`` (arch/ir.go:528-553).  Every tensor must be a
+contiguous CUDA tensor; nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import GdnDesc, Mamba3Desc, MXB_BF16, MXB_F32
+
+_ws_cache: dict = {}
+
+
+def _io(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return MXB_F32
+    if t.dtype == torch.bfloat16:
+        return MXB_BF16
+    raise TypeError(f"unsupported dtype {t.dtype} (float32 or bfloat16)")
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("mixlab_b200 operators take CUDA tensors only (no CPU fallback)")
+    if not t.is_contiguous():
+        raise ValueError("tensor must be contiguous")
+    return C.c_void_p(t.data_ptr())
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("mixlab_b200 operators take CUDA tensors only (no CPU fallback)")
+
+
+def _f32(t, name):
+    if t is not None and t.dtype != torch.float32:
+        raise TypeError(f"{name} must be float32")
+    return t
+
+
+def workspace(nbytes: int, device) -> torch.Tensor:
+    """A cached byte buffer of at least ``nbytes`` on ``device`` (torch allocator)."""
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        _ws_cache.pop(key, None)
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def gdn_desc(q, v, chunk, gate_is_log, flags=0) -> GdnDesc:
+    B, T, H, Dk = q.shape
+    return GdnDesc(B, T, H, Dk, v.shape[-1], int(chunk), _io(q), int(bool(gate_is_log)), int(flags))
+
+
+def gated_delta_scan(q, k, v, beta, gate, chunk=64, *, gate_is_log=False, h0=None,
+                     return_final_state=False, flags=0):
+    """Forward.  Returns out [B,T,H,Dv] (and the final state [B,H,Dk,Dv] fp32)."""
+    _require_cuda(q, k, v, beta, gate, h0)
+    l = _lib.lib()
+    d = gdn_desc(q, v, chunk, gate_is_log, flags)
+    out = torch.empty_like(v)
+    hT = torch.empty(d.B, d.H, d.Dk, d.Dv, dtype=torch.float32, device=q.device) if return_final_state else None
+    nws = l.mxb_gdn_fwd_workspace_bytes(C.byref(d))
+    ws = workspace(nws, q.device)
+    _lib.check(l.mxb_gdn_fwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(_f32(beta, "beta")),
+                             _ptr(_f32(gate, "gate")), _ptr(_f32(h0, "h0")), _ptr(out), _ptr(hT),
+                             _ptr(ws), ws.numel(), _stream()), "mxb_gdn_fwd")
+    return (out, hT) if return_final_state else out
+
+
+def gated_delta_scan_backward(q, k, v, beta, gate, d_out, chunk=64, *, gate_is_log=False, h0=None,
+                              d_final_state=None, flags=0):
+    """All gradients.  Returns dict(dq, dk, dv, dbeta, dgate, dh0)."""
+    _require_cuda(q, k, v, beta, gate, d_out, h0, d_final_state)
+    l = _lib.lib()
+    d = gdn_desc(q, v, chunk, gate_is_log, flags)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dbeta, dgate = torch.empty_like(beta), torch.empty_like(gate)
+    dh0 = torch.empty(d.B, d.H, d.Dk, d.Dv, dtype=torch.float32, device=q.device) if h0 is not None else None
+    nws = l.mxb_gdn_bwd_workspace_bytes(C.byref(d))
+    ws = workspace(nws, q.device)
+    _lib.check(l.mxb_gdn_bwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(_f32(beta, "beta")),
+                             _ptr(_f32(gate, "gate")), _ptr(_f32(h0, "h0")), _ptr(d_out),
+                             _ptr(_f32(d_final_state, "d_final_state")), _ptr(dq), _ptr(dk), _ptr(dv),
+                             _ptr(dbeta), _ptr(dgate), _ptr(dh0), _ptr(ws), ws.numel(), _stream()),
+               "mxb_gdn_bwd")
+    return dict(dq=dq, dk=dk, dv=dv, dbeta=dbeta, dgate=dgate, dh0=dh0)
+
+
+def gated_delta_decode_step(state, q, k, v, beta, gate, *, gate_is_log=False, out=None):
+    """One token on a persistent state [N,H,Dk,Dv] (updated in place).  Returns out [N,H,Dv]."""
+    _require_cuda(state, q, k, v, beta, gate)
+    l = _lib.lib()
+    N, H, Dk, Dv = state.shape
+    d = GdnDesc(N, 1, H, Dk, Dv, 0, _io(q), int(bool(gate_is_log)), 0)
+    if out is None:
+        out = torch.empty_like(v)
+    _lib.check(l.mxb_gdn_decode_step(C.byref(d), _ptr(_f32(state, "state")), _ptr(q), _ptr(k), _ptr(v),
+                                     _ptr(_f32(beta, "beta")), _ptr(_f32(gate, "gate")), _ptr(out),
+                                     _stream()), "mxb_gdn_decode_step")
+    return out
+
+
+def mamba3_desc(x, b, nheads) -> Mamba3Desc:
+    B, T, D = x.shape
+    G, N = b.shape[-2], b.shape[-1]
+    return Mamba3Desc(B, T, D, N, G, int(nheads), _io(x), 0)
+
+
+def mamba3_selective_scan(x, dt, lam, theta, a_log, b, c, *, nheads=0):
+    """Forward.  x [B,T,D]; b,c [B,T,G,N]; per-channel (nheads=0) or head-broadcast parameters."""
+    _require_cuda(x, dt, lam, theta, a_log, b, c)
+    l = _lib.lib()
+    d = mamba3_desc(x, b, nheads)
+    y = torch.empty_like(x)
+    _lib.check(l.mxb_mamba3_fwd(C.byref(d), _ptr(x), _ptr(_f32(dt, "dt")), _ptr(_f32(lam, "lambda")),
+                                _ptr(_f32(theta, "theta")), _ptr(_f32(a_log, "a_log")), _ptr(b), _ptr(c),
+                                _ptr(y), None, 0, _stream()), "mxb_mamba3_fwd")
+    return y
+
+
+def mamba3_selective_scan_backward(x, dt, lam, theta, a_log, b, c, dy, *, nheads=0):
+    """Gradients in argument order.  Returns dict(dx, ddt, dlambda, dtheta, da_log, db, dc)."""
+    _require_cuda(x, dt, lam, theta, a_log, b, c, dy)
+    l = _lib.lib()
+    d = mamba3_desc(x, b, nheads)
+    dx = torch.empty_like(x)
+    ddt, dlam, dth, dal = (torch.empty_like(t) for t in (dt, lam, theta, a_log))
+    db, dc = torch.empty_like(b), torch.empty_like(c)
+    nws = l.mxb_mamba3_bwd_workspace_bytes(C.byref(d))
+    ws = workspace(nws, x.device)
+    _lib.check(l.mxb_mamba3_bwd(C.byref(d), _ptr(x), _ptr(_f32(dt, "dt")), _ptr(_f32(lam, "lambda")),
+                                _ptr(_f32(theta, "theta")), _ptr(_f32(a_log, "a_log")), _ptr(b), _ptr(c),
+                                _ptr(dy), _ptr(dx), _ptr(ddt), _ptr(dlam), _ptr(dth), _ptr(dal), _ptr(db),
+                                _ptr(dc), _ptr(ws), ws.numel(), _stream()), "mxb_mamba3_bwd")
+    return dict(dx=dx, ddt=ddt, dlambda=dlam, dtheta=dth, da_log=dal, db=db, dc=dc)

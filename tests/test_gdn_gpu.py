@@ -1,0 +1,203 @@
+"""Parity of the CUDA gated-delta kernels (through the C ABI) with the CPU oracle."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import mixlab_b200
+from mixlab_b200 import ops
+from oracle import gdn, inputs
+from tests.util import assert_close
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda"
+TOL_F32 = 1e-4   # fp32 I/O
+TOL_BF16 = 2e-2  # bf16 I/O, fp32 state
+
+
+def _dev(t):
+    return None if t is None else t.to(DEV).contiguous()
+
+
+def _oracle_fwd(a, chunk, h0=None):
+    f = {k: v.double() for k, v in a.items() if torch.is_tensor(v)}
+    return gdn.scan_chunked(f["q"], f["k"], f["v"], f["beta"], torch.exp(f["g"]), chunk,
+                            None if h0 is None else h0.double())
+
+
+@pytest.mark.parametrize("shape", [
+    (2, 256, 4, 64, 64, 64),     # benchmark config 0
+    (2, 97, 3, 8, 12, 64),       # the reference test's ragged shape
+    (1, 1, 1, 4, 4, 64),         # a single token
+    (1, 63, 2, 16, 8, 64), (1, 65, 2, 16, 8, 64), (1, 130, 1, 32, 20, 16),
+    (1, 200, 2, 128, 128, 64),
+    (1, 50, 2, 8, 8, 0),         # token-by-token recurrence
+])
+@pytest.mark.parametrize("gate_is_log", [True, False])
+def test_forward_fp32(shape, gate_is_log):
+    B, T, H, K, V, C = shape
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=0, with_h0=True)
+    want_o, want_s = _oracle_fwd(a, C, a["h0"])
+    gate = a["g"] if gate_is_log else torch.exp(a["g"])
+    o, s = ops.gated_delta_scan(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(gate), C,
+                                gate_is_log=gate_is_log, h0=_dev(a["h0"]), return_final_state=True)
+    assert_close(o, want_o, TOL_F32, "out")
+    assert_close(s, want_s, TOL_F32, "final_state")
+
+
+def test_forward_config0_zero_state():
+    """B=2,T=256,H=4,d=64, chunk 64, seed 0, zero initial state (benchmark config 0)."""
+    a = inputs.gdn_inputs(2, 256, 4, 64, 64, seed=0)
+    want_o, want_s = _oracle_fwd(a, 64)
+    o, s = ops.gated_delta_scan(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]), 64,
+                                gate_is_log=True, return_final_state=True)
+    assert o.shape == (2, 256, 4, 64) and s.shape == (2, 4, 64, 64)
+    assert_close(o, want_o, TOL_F32, "out")
+    assert_close(s, want_s, TOL_F32, "final_state")
+
+
+@pytest.mark.parametrize("shape", [
+    (2, 256, 4, 64, 64, 64), (2, 97, 3, 8, 12, 64), (1, 130, 2, 32, 20, 16), (1, 70, 1, 128, 128, 64),
+    (1, 40, 2, 8, 8, 0),
+])
+@pytest.mark.parametrize("gate_is_log", [True, False])
+def test_backward_fp32(shape, gate_is_log):
+    B, T, H, K, V, C = shape
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=1, with_grad_out=True, with_h0=True)
+    f = {k: v.double() for k, v in a.items()}
+    gate64 = f["g"] if gate_is_log else torch.exp(f["g"])
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], gate64, f["d_out"], f["d_state"], f["h0"],
+                          gate_is_log=gate_is_log)
+    gate = a["g"] if gate_is_log else torch.exp(a["g"])
+    got = ops.gated_delta_scan_backward(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(gate),
+                                        _dev(a["d_out"]), C, gate_is_log=gate_is_log, h0=_dev(a["h0"]),
+                                        d_final_state=_dev(a["d_state"]))
+    for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
+        assert_close(got[name], want[name], TOL_F32, name)
+
+
+def test_reference_golden_vectors():
+    """The reference's own scalar/torch scan outputs (tests/golden) through the CUDA path."""
+    with open(os.path.join(G, "gdn_scalar_reference.json")) as f:
+        cases = json.load(f)["cases"]
+    for c in cases:
+        B, T, H, K, V = (c[x] for x in ("B", "T", "H", "Dk", "Dv"))
+        t = lambda key, *s: torch.tensor(c[key], dtype=torch.float32).reshape(*s)
+        for chunk in (0, 64):
+            o = ops.gated_delta_scan(_dev(t("q", B, T, H, K)), _dev(t("k", B, T, H, K)), _dev(t("v", B, T, H, V)),
+                                     _dev(t("beta", B, T, H)), _dev(t("gate", B, T, H)), chunk)
+            assert_close(o, torch.tensor(c["out"], dtype=torch.float64).reshape(B, T, H, V), TOL_F32, c["name"])
+    z = np.load(os.path.join(G, "gdn_torch_recurrence.npz"))
+    a = {k: torch.from_numpy(z[k]) for k in z.files}
+    o = ops.gated_delta_scan(*(_dev(a[k].float()) for k in ("q", "k", "v", "beta", "gate")), 64)
+    assert_close(o, a["out"], TOL_F32, "torch_recurrence")
+
+
+def test_go_test_inputs_chunked_matches_naive():
+    """gpu/gated_delta_scan_test.go:174-263 on the CUDA path: chunk 64 vs chunk 0, tol 1e-4."""
+    z = np.load(os.path.join(G, "gdn_go_test_inputs.npz"))
+    a = [_dev(torch.from_numpy(z[k]).float()) for k in ("q", "k", "v", "beta", "gate")]
+    o0 = ops.gated_delta_scan(*a, 0)
+    o64 = ops.gated_delta_scan(*a, 64)
+    assert (o0 - o64).abs().max().item() <= 1e-4
+
+
+@pytest.mark.parametrize("shape", [(1, 256, 2, 128, 128, 64), (2, 100, 2, 64, 64, 64)])
+def test_forward_backward_bf16_io(shape):
+    """bf16 q,k,v,dO with fp32 state: 2e-2 against the float64 oracle on the bf16-rounded inputs."""
+    B, T, H, K, V, C = shape
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=1, io_dtype=torch.bfloat16, with_grad_out=True)
+    f = {k: v.double() for k, v in a.items()}
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], f["g"], f["d_out"], gate_is_log=True)
+    o, s = ops.gated_delta_scan(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]), C,
+                                gate_is_log=True, return_final_state=True)
+    assert o.dtype == torch.bfloat16
+    assert_close(o, want["out"], TOL_BF16, "out")
+    assert_close(s, want["state"], TOL_BF16, "final_state")
+    got = ops.gated_delta_scan_backward(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]),
+                                        _dev(a["d_out"]), C, gate_is_log=True)
+    for name in ("dq", "dk", "dv", "dbeta", "dgate"):
+        assert_close(got[name], want[name], TOL_BF16, name)
+
+
+def test_decode_steps():
+    """Recurrent decode: parity after 1, 16 and 64 steps on 4 sequences (config 2 dims)."""
+    N, H, K, V, steps = 4, 16, 128, 128, 64
+    a = inputs.gdn_decode_inputs(N, H, K, V, steps, seed=2, io_dtype=torch.bfloat16)
+    st_ref = a["state"].double()
+    st = _dev(a["state"].clone())
+    for t in range(steps):
+        o_ref, st_ref = gdn.decode_step(st_ref, a["q"][t].double(), a["k"][t].double(), a["v"][t].double(),
+                                        a["beta"][t].double(), torch.exp(a["g"][t].double()))
+        o = ops.gated_delta_decode_step(st, _dev(a["q"][t]), _dev(a["k"][t]), _dev(a["v"][t]), _dev(a["beta"][t]),
+                                        _dev(a["g"][t]), gate_is_log=True)
+        if t + 1 in (1, 16, 64):
+            assert_close(o, o_ref, TOL_BF16, f"out@{t + 1}")
+            assert_close(st, st_ref, 1e-4, f"state@{t + 1}")
+
+
+@pytest.mark.parametrize("dims", [(3, 2, 64, 64), (2, 3, 8, 12), (1, 1, 200, 256), (2, 2, 40, 132)])
+def test_decode_fp32_shapes(dims):
+    N, H, K, V = dims
+    a = inputs.gdn_decode_inputs(N, H, K, V, 3, seed=5, io_dtype=torch.float32)
+    st_ref = a["state"].double()
+    st = _dev(a["state"].clone())
+    for t in range(3):
+        gate = torch.exp(a["g"][t])
+        o_ref, st_ref = gdn.decode_step(st_ref, a["q"][t].double(), a["k"][t].double(), a["v"][t].double(),
+                                        a["beta"][t].double(), gate.double())
+        o = ops.gated_delta_decode_step(st, _dev(a["q"][t]), _dev(a["k"][t]), _dev(a["v"][t]), _dev(a["beta"][t]),
+                                        _dev(gate))
+        assert_close(o, o_ref, TOL_F32, "out")
+    assert_close(st, st_ref, TOL_F32, "state")
+
+
+def test_decode_equals_scan():
+    """T decode steps from a zero state reproduce the scan output (same recurrence)."""
+    a = inputs.gdn_inputs(2, 24, 2, 64, 64, seed=4)
+    o_scan, s_scan = ops.gated_delta_scan(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]), 64,
+                                          gate_is_log=True, return_final_state=True)
+    st = torch.zeros(2, 2, 64, 64, device=DEV)
+    for t in range(24):
+        o = ops.gated_delta_decode_step(st, _dev(a["q"][:, t]), _dev(a["k"][:, t]), _dev(a["v"][:, t]),
+                                        _dev(a["beta"][:, t]), _dev(a["g"][:, t]), gate_is_log=True)
+        assert_close(o, o_scan[:, t], TOL_F32, f"o[{t}]")
+    assert_close(st, s_scan, TOL_F32, "state")
+
+
+def test_host_buffer_entry_point():
+    """mxb_host_gdn: host tensors in, host tensors out, forward + backward."""
+    import ctypes as C
+    lib = mixlab_b200.lib()
+    B, T, H, K, V = 1, 100, 2, 32, 32
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=6, with_grad_out=True)
+    f = {k: v.double() for k, v in a.items()}
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], f["g"], f["d_out"], gate_is_log=True)
+    ctx = C.c_void_p()
+    assert lib.mxb_host_ctx_create(0, 64 << 20, C.byref(ctx)) == 0
+    try:
+        d = mixlab_b200.GdnDesc(B, T, H, K, V, 64, mixlab_b200.MXB_F32, 1, 0)
+        out = torch.empty_like(a["v"])
+        dq, dk, dv = torch.empty_like(a["q"]), torch.empty_like(a["k"]), torch.empty_like(a["v"])
+        db, dg = torch.empty_like(a["beta"]), torch.empty_like(a["g"])
+        p = lambda t: C.c_void_p(t.data_ptr())
+        st = lib.mxb_host_gdn(ctx, C.byref(d), p(a["q"]), p(a["k"]), p(a["v"]), p(a["beta"]), p(a["g"]), p(out),
+                              p(a["d_out"]), p(dq), p(dk), p(dv), p(db), p(dg))
+        assert st == 0
+    finally:
+        lib.mxb_host_ctx_destroy(ctx)
+    assert_close(out, want["out"], TOL_F32, "out")
+    for name, t in (("dq", dq), ("dk", dk), ("dv", dv), ("dbeta", db), ("dgate", dg)):
+        assert_close(t, want[name], TOL_F32, name)
+
+
+def test_launch_counter_moves():
+    lib = mixlab_b200.lib()
+    n0 = lib.mxb_launch_count()
+    a = inputs.gdn_inputs(1, 8, 1, 8, 8, seed=0)
+    ops.gated_delta_scan(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]), 64, gate_is_log=True)
+    torch.cuda.synchronize()
+    assert lib.mxb_launch_count() >= n0 + 2

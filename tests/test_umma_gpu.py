@@ -1,0 +1,102 @@
+"""Pins the tcgen05 operand layouts used by the tensor-core kernels: builds shared-memory
+images on the host for each layout convention, runs one D = A B^T tile through
+mxb_selftest_umma and compares with a plain matrix product."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import mixlab_b200
+
+pytestmark = pytest.mark.gpu
+SWZ_NONE, SWZ_128 = 0, 2
+
+
+def idesc(M, N, a_mn, b_mn):
+    return (1 << 4) | (1 << 7) | (1 << 10) | (a_mn << 15) | (b_mn << 16) | ((N >> 3) << 17) | ((M >> 4) << 24)
+
+
+def bf16_bits(x: torch.Tensor) -> np.ndarray:
+    return x.to(torch.bfloat16).view(torch.int16).numpy().astype(np.uint16)
+
+
+def image(x, offset_fn, nbytes):
+    """x [R, Kt] -> byte image with element (r,k) at offset_fn(r,k)."""
+    bits = bf16_bits(x)
+    img = np.zeros(nbytes // 2, dtype=np.uint16)
+    R, Kt = bits.shape
+    r, k = np.meshgrid(np.arange(R), np.arange(Kt), indexing="ij")
+    off = offset_fn(r, k)
+    assert off.max() + 2 <= nbytes and len(np.unique(off)) == off.size
+    img[off // 2] = bits
+    return img.view(np.uint8)
+
+
+def layout(kind, R, Kt):
+    """Returns (offset_fn, lbo, sbo, swizzle, kstep_bytes, mn_major, nbytes)."""
+    if kind == "k_none":      # K-major, no swizzle: 8x8 core matrices, K-adjacent cores 128 B apart
+        lbo, sbo = 128, (Kt // 8) * 128
+        return (lambda r, k: (r // 8) * sbo + (k // 8) * lbo + (r % 8) * 16 + (k % 8) * 2), lbo, sbo, SWZ_NONE, 2 * lbo, 0, R * Kt * 2
+    if kind == "k_sw128":     # K-major, 128B swizzle, rows of 64 elements
+        assert Kt == 64
+        return (lambda r, k: r * 128 + (((k // 8) ^ (r % 8)) * 16) + (k % 8) * 2), 16, 1024, SWZ_128, 32, 0, R * 128
+    if kind == "mn_none":     # MN-major, no swizzle: core = 8 k-rows x 16 B (8 MN elements)
+        sbo, lbo = 128, (R // 8) * 128
+        return (lambda r, k: (r // 8) * sbo + (k // 8) * lbo + (k % 8) * 16 + (r % 8) * 2), lbo, sbo, SWZ_NONE, 2 * lbo, 1, R * Kt * 2
+    if kind == "mn_sw128":    # MN-major, 128B swizzle: what a [k rows][64 MN elements] swizzled box looks like
+        sbo, lbo = 1024, (Kt // 8) * 1024
+        return (lambda r, k: (r // 64) * lbo + (k // 8) * sbo + (k % 8) * 128 + ((((r % 64) // 8) ^ (k % 8)) * 16) + (r % 8) * 2), \
+            lbo, sbo, SWZ_128, 2 * sbo, 1, R * Kt * 2
+    raise ValueError(kind)
+
+
+def run_case(lib, M, N, Kt, akind, bkind, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randn(M, Kt, generator=g).to(torch.bfloat16)
+    B = torch.randn(N, Kt, generator=g).to(torch.bfloat16)
+    fa, albo, asbo, aswz, astep, amn, abytes = layout(akind, M, Kt)
+    fb, blbo, bsbo, bswz, bstep, bmn, bbytes = layout(bkind, N, Kt)
+    a_img = torch.from_numpy(image(A, fa, abytes).copy()).cuda()
+    b_img = torch.from_numpy(image(B, fb, bbytes).copy()).cuda()
+    fields = (C.c_uint32 * 11)(albo, asbo, aswz, blbo, bsbo, bswz, idesc(M, N, amn, bmn), Kt // 16, astep, bstep, N)
+    d_out = torch.full((128, N), float("nan"), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = lib.mxb_selftest_umma(C.c_void_p(a_img.data_ptr()), abytes, C.c_void_p(b_img.data_ptr()), bbytes, fields,
+                               C.c_void_p(d_out.data_ptr()), C.c_void_p(status.data_ptr()), None)
+    torch.cuda.synchronize()
+    if st != 0 or status.item() != 0:
+        return dict(ok=False, why=f"status {st}/{status.item()}")
+    want = A.double() @ B.double().T
+    got = d_out.double().cpu()
+    rows = torch.arange(M)
+    lanes = rows if M == 128 else (rows % 16) + 32 * (rows // 16)
+    err = (got[lanes] - want).abs().max().item()
+    res = dict(ok=bool(err < 1e-2 * max(1.0, want.abs().max().item())), err=err)
+    if not res["ok"] and M == 64:  # help diagnosing: does any other lane mapping fit?
+        alt = (got[:64] - want).abs().max().item()
+        res["err_if_lanes_0_63"] = alt
+    return res
+
+
+def test_umma_operand_layouts():
+    lib = mixlab_b200.lib()
+    cases = [
+        (128, 64, 64, "k_none", "k_none"), (128, 64, 64, "k_sw128", "k_sw128"),
+        (128, 64, 64, "mn_none", "k_none"), (128, 64, 64, "k_none", "mn_none"),
+        (128, 64, 64, "mn_sw128", "k_none"), (128, 64, 64, "k_none", "mn_sw128"),
+        (128, 128, 128, "k_none", "k_none"), (128, 32, 128, "k_none", "mn_none"),
+        (128, 128, 64, "mn_sw128", "mn_sw128"),
+        (64, 64, 64, "k_none", "k_none"), (64, 32, 128, "k_none", "mn_none"), (64, 128, 64, "k_sw128", "k_none"),
+    ]
+    results = {}
+    for c in cases:
+        results["M%d_N%d_K%d_A:%s_B:%s" % c] = run_case(lib, *c)
+    os.makedirs("gpurun_out", exist_ok=True)
+    with open("gpurun_out/umma_selftest.json", "w") as f:
+        json.dump(results, f, indent=1)
+    bad = {k: v for k, v in results.items() if not v["ok"]}
+    print(json.dumps(results, indent=1))
+    assert not bad, bad
