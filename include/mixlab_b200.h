@@ -111,6 +111,12 @@ MXB_API mxb_status mxb_gdn_bwd(const mxb_gdn_desc* d, const void* q, const void*
                        float* dbeta, float* dgate, float* dh0, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* The tensor-core kernels bound every wait on an mbarrier; a wait that gives up
+ * makes the kernel leave in an orderly way and write a nonzero code into the first
+ * word of the workspace.  This BLOCKING call copies that word to *out (0 = no
+ * device-side error).  Workspaces of the fp32 path never set it. */
+MXB_API mxb_status mxb_gdn_device_status(const void* workspace, int32_t* out);
+
 /* One token of the recurrence on a persistent state: the loop body of
  * gated_delta_scan_naive (gpu/ir.cpp:2334-2345).  desc.T is ignored, desc.B is
  * the number of sequences.  state [B,H,Dk,Dv] fp32 is updated in place;

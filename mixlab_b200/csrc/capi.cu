@@ -204,6 +204,13 @@ mxb_status mxb_gdn_bwd(const mxb_gdn_desc* d, const void* q, const void* k, cons
   return gdn_simt_bwd(d, q, k, v, beta, gate, h0, d_out, d_hT, dq, dk, dv, dbeta, dgate, dh0, workspace, st);
 }
 
+mxb_status mxb_gdn_device_status(const void* workspace, int32_t* out) {
+  if (!workspace || !out) return MXB_ERR_INVALID_ARGUMENT;
+  cudaError_t e = cudaMemcpy(out, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) { g_last_cuda_error = (int)e; return MXB_ERR_CUDA; }
+  return MXB_OK;
+}
+
 mxb_status mxb_gdn_decode_step(const mxb_gdn_desc* d, float* state, const void* q, const void* k,
                                const void* v, const float* beta, const float* gate, void* out,
                                void* stream) {

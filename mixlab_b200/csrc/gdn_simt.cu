@@ -636,6 +636,7 @@ __global__ void __launch_bounds__(256) gdn_recurrent_fwd_kernel(GdnP p) {
 static size_t carve(GdnP& p, void* ws, bool bwd) {
   Carver cv(ws);
   const size_t nc = (size_t)p.B * p.H * p.n, C = p.C, K = p.K, V = p.V;
+  cv.take<int>(64);  // device status header (always zero on this path)
   p.gam = cv.take<float>(nc * C);
   p.Tm = cv.take<float>(nc * C * C);
   p.w = cv.take<float>(nc * C * K);
@@ -735,7 +736,10 @@ mxb_status gdn_simt_fwd(const mxb_gdn_desc* d, const void* q, const void* k, con
   GdnP p = make_params(d);
   p.q = q; p.k = k; p.v = v; p.beta = beta; p.gate = gate; p.h0 = h0; p.out = out; p.hT = hT;
   const bool chunked = d->chunk > 1;
-  if (chunked) carve(p, ws, false);
+  if (chunked) {
+    carve(p, ws, false);
+    if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
+  }
   return d->io_dtype == MXB_F32 ? run_fwd<float>(p, chunked, st) : run_fwd<__nv_bfloat16>(p, chunked, st);
 }
 
@@ -747,6 +751,7 @@ mxb_status gdn_simt_bwd(const mxb_gdn_desc* d, const void* q, const void* k, con
   p.q = q; p.k = k; p.v = v; p.beta = beta; p.gate = gate; p.h0 = h0;
   p.dO = dO; p.dhT_in = dhT; p.dq = dq; p.dk = dk; p.dv = dv; p.dbeta = dbeta; p.dgate = dgate; p.dh0 = dh0;
   carve(p, ws, true);
+  if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
   return d->io_dtype == MXB_F32 ? run_bwd<float>(p, st) : run_bwd<__nv_bfloat16>(p, st);
 }
 

@@ -1,18 +1,487 @@
-// Gated delta rule - tensor-core (tcgen05/TMEM) path for bf16 I/O.
+// Gated delta rule, chunked WY/UT form - tensor-core path (tcgen05.mma, TMEM
+// accumulators) for bf16 I/O with fp32 state, chunk 64, Dk = Dv = 128.
+//
+// Same mathematics as the fp32 path (gdn_simt.cu; reference
+// gated_delta_scan_chunked, gpu/ir.cpp:2352-2550).  Every contraction runs as
+// tcgen05.mma.kind::f16 on bf16 operands staged in shared memory in the
+// un-swizzled canonical layouts (umma_tiles.cuh) with fp32 accumulation in
+// tensor memory; the triangular inverse, all decay factors, the recurrent state
+// and every reduction stay in fp32.
+//
+//   gdn_tc_prep_kernel       one CTA per chunk: [k;q] k^T (M=128), fp32 solve,
+//                            T [v beta | k beta E(gam)] (M=64, N=256) -> u, w, P, T
+//   gdn_tc_state_fwd_kernel  one CTA per (64-column slab of Dv, b*H+h), sequential over
+//                            chunks, fp32 state in registers (thread = state row):
+//                            [w;q] S (M=128) -> v_new, then [0;P] v_new and k^T (r v_new)
 #include "common.cuh"
+#include "umma_tiles.cuh"
 
 namespace mxb {
 
-bool gdn_tc_supported(const mxb_gdn_desc*) { return false; }
-size_t gdn_tc_workspace_bytes(const mxb_gdn_desc*, bool) { return 0; }
-mxb_status gdn_tc_fwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*,
-                      const float*, const float*, void*, float*, void*, cudaStream_t) {
-  return MXB_ERR_UNSUPPORTED;
+namespace {
+constexpr int C = 64;     // chunk
+constexpr int KD = 128;   // Dk = Dv
+constexpr int VS = 64;    // Dv columns per state CTA
+constexpr int LDA = 68;   // fp32 row pitch of the 64x64 solve matrix (16-byte aligned rows)
+using bf16 = __nv_bfloat16;
+
+struct TcP {
+  int B, T, H, n, gate_is_log, save;
+  const bf16 *q, *k, *v;
+  const float *beta, *gate, *h0;
+  bf16* out;
+  float* hT;
+  const bf16* dO;
+  const float* dhT_in;
+  bf16 *dq, *dk, *dv;
+  float *dbeta, *dgate, *dh0;
+  int* status;   // device word: nonzero when a bounded wait gave up
+  // workspace, indexed by ci = (b*H+h)*n + chunk
+  float* gam;    // [C]
+  bf16* Tm;      // [C][C]
+  bf16* w;       // [C][KD]
+  bf16* u;       // [C][KD]
+  bf16* P;       // [C][C]
+  bf16* hs;      // [KD][KD]  state at chunk start   (backward only)
+  bf16* vn;      // [C][KD]
+  bf16* dhs;     // [KD][KD]  dS at chunk end
+  bf16* dvn;     // [C][KD]
+};
+
+__device__ __forceinline__ float log_gate_tc(float g, int gate_is_log) {
+  return gate_is_log ? fmaxf(g, kLogGateFloor) : __logf(fmaxf(g, kGateFloor));
 }
-mxb_status gdn_tc_bwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*,
-                      const float*, const float*, const void*, const float*, void*, void*, void*,
-                      float*, float*, float*, void*, cudaStream_t) {
-  return MXB_ERR_UNSUPPORTED;
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void sts16(uint8_t* base, uint32_t off, uint4 v) {
+  *reinterpret_cast<uint4*>(base + off) = v;
+}
+__device__ __forceinline__ uint4 zero16() { return make_uint4(0u, 0u, 0u, 0u); }
+
+// Loads 32 fp32 accumulator columns [c0, c0+32) of this thread's TMEM lane.
+__device__ __forceinline__ void ld_acc32(uint32_t taddr, int warp, int c0, float (&f)[32]) {
+  uint32_t r[32];
+  tc::tmem_ld_32x32b_x32(taddr + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0, r);
+  tc::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+}
+}  // namespace
+
+// ------------------------------------------------------------------ prep
+constexpr int kPrepSmem = 32768 + 32768 + 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 128;
+
+__global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* Akq = sm;                    // K-major [128: k rows 0-63, q rows 64-127][128]
+  uint8_t* Bvk = Akq + 32768;           // MN-major [64 m][256: v beta | k beta E(gam)]
+  uint8_t* Tt = Bvk + 32768;            // K-major [64 i][64 m]
+  float* Am = reinterpret_cast<float*>(Tt + 8192);  // [64][LDA]
+  float* gam = Am + C * LDA;
+  float* bet = gam + C;
+  float* bd = bet + C;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(bd + C);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
+  const size_t ci = (size_t)bh * p.n + c;
+  auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
+  const int imax = min(C, p.T - t0);
+
+  if (warp == 0) {
+    tc::tmem_alloc(tslot, 256);
+    tc::tmem_relinquish();
+  }
+  if (tid == 0) {
+    tc::mbar_init(mbar, 1);
+    tc::mbar_fence_init();
+  }
+  if (tid < C) {
+    const bool ok = tid < imax;
+    bet[tid] = ok ? p.beta[row(tid)] : 0.f;
+    gam[tid] = ok ? log_gate_tc(p.gate[row(tid)], p.gate_is_log) : 0.f;
+  }
+  // stage [k;q] (K-major)
+  for (int u = tid; u < 128 * 16; u += 128) {
+    const int r = u >> 4, c8 = u & 15, i = r & 63;
+    uint4 val = zero16();
+    if (i < imax) val = ldg16((r < 64 ? p.k : p.q) + row(i) * KD + c8 * 8);
+    sts16(Akq, tc::kmajor_unit(r, c8, KD), val);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float acc = 0.f;
+    for (int i = 0; i < C; ++i) { acc += gam[i]; gam[i] = acc; }
+  }
+  __syncthreads();
+  if (tid < C) {
+    bd[tid] = bet[tid] * exp_nonpos(gam[tid]);
+    p.gam[ci * C + tid] = gam[tid];
+  }
+  __syncthreads();
+  // stage [v beta | k beta E(gam)] (MN-major, contraction over the chunk row m)
+  for (int u = tid; u < 64 * 32; u += 128) {
+    const int m = u >> 5, c8 = u & 31;
+    uint4 val = zero16();
+    if (m < imax) {
+      if (c8 < 16) val = tc::scale_bf16x8(ldg16(p.v + row(m) * KD + c8 * 8), bet[m]);
+      else val = tc::scale_bf16x8(ldg16(p.k + row(m) * KD + (c8 - 16) * 8), bd[m]);
+    }
+    sts16(Bvk, tc::mnmajor_unit(m, c8, 256), val);
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t taddr = *tslot;
+  bool ok = true;
+  // D0[128 x 64] = [k;q] k^T
+  if (tid == 0) {
+    const tc::Tile a = tc::kmajor_tile(Akq, KD);
+    tc::issue_gemm(taddr, a, a, 128, 64, KD, false);  // B = first 64 rows of the same tile
+    tc::mma_commit(mbar);
+  }
+  ok = tc::mbar_wait(mbar, 0);
+  tc::fence_after_sync();
+  if (ok) {
+    const int i = tid & 63;
+    const float gi = gam[i];
+    for (int c0 = 0; c0 < 64; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr, warp, c0, f);
+      if (tid < 64) {  // A = -(k beta k^T) Gamma, strictly lower
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const int j = c0 + jj;
+          Am[i * LDA + j] = (j < i) ? -bet[i] * f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
+        }
+      } else {         // P = (q k^T) Gamma, lower incl. diagonal -> workspace
+        uint32_t pk[16];
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 2) {
+          const int j = c0 + jj;
+          const float x0 = (j <= i) ? f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
+          const float x1 = (j + 1 <= i) ? f[jj + 1] * exp_nonpos(gi - gam[j + 1]) : 0.f;
+          pk[jj >> 1] = tc::pack_bf16(x0, x1);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(p.P + (ci * C + i) * C + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
+      }
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  // T = (I - A)^-1 in fp32: thread = column, rows by forward substitution, column kept in registers
+  if (ok && tid < C) {
+    float Tc[C];
+#pragma unroll
+    for (int i = 0; i < C; ++i) {
+      float s = (i == tid) ? 1.f : 0.f;
+#pragma unroll
+      for (int j = 0; j < i; ++j) s = fmaf(Am[i * LDA + j], Tc[j], s);
+      Tc[i] = (i < tid) ? 0.f : s;
+    }
+#pragma unroll
+    for (int i = 0; i < C; ++i)
+      *reinterpret_cast<bf16*>(Tt + tc::kmajor_unit(i, tid >> 3, C) + (tid & 7) * 2) = __float2bfloat16_rn(Tc[i]);
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  // D1[64 x 256] = T [v beta | k beta E(gam)]  -> u | w
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr, tc::kmajor_tile(Tt, C), tc::mnmajor_tile(Bvk, 256), 64, 256, C, false);
+    tc::mma_commit(mbar);
+  }
+  // T -> workspace (bf16, row-major) while the MMA runs
+  for (int u = tid; u < 64 * 8; u += 128) {
+    const int i = u >> 3, c8 = u & 7;
+    *reinterpret_cast<uint4*>(p.Tm + (ci * C + i) * C + c8 * 8) =
+        *reinterpret_cast<const uint4*>(Tt + tc::kmajor_unit(i, c8, C));
+  }
+  if (ok) ok = tc::mbar_wait(mbar, 1);
+  tc::fence_after_sync();
+  if (ok) {
+    const int i = 16 * warp + (lane & 15);  // M=64: row m sits in TMEM lane (m%16) + 32*(m/16)
+    for (int c0 = 0; c0 < 256; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr, warp, c0, f);
+      if (lane < 16) {
+        bf16* base = (c0 < 128) ? p.u + (ci * C + i) * KD + c0 : p.w + (ci * C + i) * KD + (c0 - 128);
+        uint4* dst = reinterpret_cast<uint4*>(base);
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+          dst[x] = make_uint4(tc::pack_bf16(f[8 * x], f[8 * x + 1]), tc::pack_bf16(f[8 * x + 2], f[8 * x + 3]),
+                              tc::pack_bf16(f[8 * x + 4], f[8 * x + 5]), tc::pack_bf16(f[8 * x + 6], f[8 * x + 7]));
+      }
+    }
+  } else if (tid == 0) {
+    atomicExch(p.status, 1);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+}
+
+// ------------------------------------------------------------ state forward
+constexpr int kStateFwdSmem = 32768 + 16384 + 16384 + 8192 + 8192 + 16384 + 2 * C * 4 + 64 + 128;
+
+__global__ void __launch_bounds__(128) gdn_tc_state_fwd_kernel(TcP p) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* A1 = sm;                 // K-major [128: w rows 0-63, q rows 64-127][128 kk]
+  uint8_t* Sop = A1 + 32768;        // MN-major [128 kk][64 j]   bf16 copy of the state
+  uint8_t* A2 = Sop + 16384;        // K-major [128: zero rows 0-63, P rows 64-127][64 m]
+  uint8_t* Vn = A2 + 16384;         // MN-major [64 i][64 j]     v_new
+  uint8_t* Vr = Vn + 8192;          // MN-major [64 i][64 j]     E(gam_last-gam_i) v_new
+  uint8_t* A3 = Vr + 8192;          // MN-major [64 i][128 kk]   k  (A = k^T)
+  float* dd = reinterpret_cast<float*>(A3 + 16384);
+  float* rr = dd + C;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int jv0 = blockIdx.x * VS;
+
+  if (warp == 0) {
+    tc::tmem_alloc(tslot, 256);
+    tc::tmem_relinquish();
+  }
+  if (tid == 0) {
+    tc::mbar_init(mbar, 1);
+    tc::mbar_fence_init();
+  }
+  float S[VS];  // state row kk = tid, columns jv0 .. jv0+63
+  if (p.h0) {
+    const float4* src = reinterpret_cast<const float4*>(p.h0 + ((size_t)bh * KD + tid) * KD + jv0);
+#pragma unroll
+    for (int x = 0; x < VS / 4; ++x) {
+      const float4 t4 = __ldg(src + x);
+      S[4 * x] = t4.x; S[4 * x + 1] = t4.y; S[4 * x + 2] = t4.z; S[4 * x + 3] = t4.w;
+    }
+  } else {
+#pragma unroll
+    for (int x = 0; x < VS; ++x) S[x] = 0.f;
+  }
+  for (int u = tid; u < 64 * 8; u += 128) sts16(A2, tc::kmajor_unit(u >> 3, u & 7, C), zero16());
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t taddr = *tslot;
+  uint32_t ph = 0;
+  bool ok = true;
+
+  for (int c = 0; c < p.n && ok; ++c) {
+    const size_t ci = (size_t)bh * p.n + c;
+    const int t0 = c * C, imax = min(C, p.T - t0);
+    auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
+    const float* gam = p.gam + ci * C;
+    const float glast = gam[C - 1];
+    const float L = exp_nonpos(glast);
+    if (tid < C) {
+      const float g = gam[tid];
+      dd[tid] = exp_nonpos(g);
+      rr[tid] = exp_nonpos(glast - g);
+    }
+    // state as the MMA operand (and saved for the backward)
+#pragma unroll
+    for (int c8 = 0; c8 < VS / 8; ++c8) {
+      const uint4 val = make_uint4(tc::pack_bf16(S[8 * c8], S[8 * c8 + 1]), tc::pack_bf16(S[8 * c8 + 2], S[8 * c8 + 3]),
+                                   tc::pack_bf16(S[8 * c8 + 4], S[8 * c8 + 5]), tc::pack_bf16(S[8 * c8 + 6], S[8 * c8 + 7]));
+      sts16(Sop, tc::mnmajor_unit(tid, c8, VS), val);
+      if (p.save) *reinterpret_cast<uint4*>(p.hs + (ci * KD + tid) * KD + jv0 + c8 * 8) = val;
+    }
+    for (int u = tid; u < 128 * 16; u += 128) {  // [w;q]
+      const int r = u >> 4, c8 = u & 15, i = r & 63;
+      uint4 val = zero16();
+      if (r < 64) val = ldg16(p.w + (ci * C + i) * KD + c8 * 8);
+      else if (i < imax) val = ldg16(p.q + row(i) * KD + c8 * 8);
+      sts16(A1, tc::kmajor_unit(r, c8, KD), val);
+    }
+    for (int u = tid; u < 64 * 16; u += 128) {   // k (A = k^T, contraction over the chunk row)
+      const int i = u >> 4, c8 = u & 15;
+      sts16(A3, tc::mnmajor_unit(i, c8, KD), i < imax ? ldg16(p.k + row(i) * KD + c8 * 8) : zero16());
+    }
+    for (int u = tid; u < 64 * 8; u += 128) {    // P into rows 64..127
+      const int i = u >> 3, c8 = u & 7;
+      sts16(A2, tc::kmajor_unit(64 + i, c8, C), ldg16(p.P + (ci * C + i) * C + c8 * 8));
+    }
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    if (tid == 0) {  // D1 = [w;q] S
+      tc::issue_gemm(taddr, tc::kmajor_tile(A1, KD), tc::mnmajor_tile(Sop, VS), 128, VS, KD, false);
+      tc::mma_commit(mbar);
+    }
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+    tc::fence_after_sync();
+    float qs[VS];
+    if (ok) {
+      const int i = tid & 63;
+      for (int c0 = 0; c0 < VS; c0 += 32) {
+        float f[32];
+        ld_acc32(taddr, warp, c0, f);
+        if (tid < 64) {  // v_new = u - w S
+          const float ri = rr[i];
+          const uint4* usrc = reinterpret_cast<const uint4*>(p.u + (ci * C + i) * KD + jv0 + c0);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const uint4 uu = __ldg(usrc + x);
+            float e[8];
+            tc::unpack_bf16(uu.x, e[0], e[1]); tc::unpack_bf16(uu.y, e[2], e[3]);
+            tc::unpack_bf16(uu.z, e[4], e[5]); tc::unpack_bf16(uu.w, e[6], e[7]);
+#pragma unroll
+            for (int y = 0; y < 8; ++y) e[y] -= f[8 * x + y];
+            const uint4 vv = make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
+                                        tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7]));
+            const int c8 = (c0 >> 3) + x;
+            sts16(Vn, tc::mnmajor_unit(i, c8, VS), vv);
+            sts16(Vr, tc::mnmajor_unit(i, c8, VS), tc::scale_bf16x8(vv, ri));
+            if (p.save) *reinterpret_cast<uint4*>(p.vn + (ci * C + i) * KD + jv0 + c0 + 8 * x) = vv;
+          }
+        } else {         // E(gam_i) (q S), kept until P v_new arrives
+          const float di = dd[i];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) qs[c0 + jj] = di * f[jj];
+        }
+      }
+    }
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    if (ok && tid == 0) {
+      // D2 = [0;P] v_new          D3 = k^T (r v_new)
+      tc::issue_gemm(taddr + 64, tc::kmajor_tile(A2, C), tc::mnmajor_tile(Vn, VS), 128, VS, C, false);
+      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(A3, KD), tc::mnmajor_tile(Vr, VS), 128, VS, C, false);
+      tc::mma_commit(mbar);
+    }
+    if (ok) {
+      ok = tc::mbar_wait(mbar, ph);
+      ph ^= 1;
+    }
+    tc::fence_after_sync();
+    if (ok) {
+      const int i = tid & 63;
+      for (int c0 = 0; c0 < VS; c0 += 32) {
+        float f[32];
+        if (warp >= 2) {  // out = E(gam)(q S) + P v_new
+          ld_acc32(taddr + 64, warp, c0, f);
+          if (i < imax) {
+            uint4* dst = reinterpret_cast<uint4*>(p.out + row(i) * KD + jv0 + c0);
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+              dst[x] = make_uint4(tc::pack_bf16(qs[c0 + 8 * x] + f[8 * x], qs[c0 + 8 * x + 1] + f[8 * x + 1]),
+                                  tc::pack_bf16(qs[c0 + 8 * x + 2] + f[8 * x + 2], qs[c0 + 8 * x + 3] + f[8 * x + 3]),
+                                  tc::pack_bf16(qs[c0 + 8 * x + 4] + f[8 * x + 4], qs[c0 + 8 * x + 5] + f[8 * x + 5]),
+                                  tc::pack_bf16(qs[c0 + 8 * x + 6] + f[8 * x + 6], qs[c0 + 8 * x + 7] + f[8 * x + 7]));
+          }
+        }
+        ld_acc32(taddr + 128, warp, c0, f);  // S <- E(gam_last) S + k^T (r v_new)
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) S[c0 + jj] = fmaf(L, S[c0 + jj], f[jj]);
+      }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+  }
+  if (!ok && tid == 0) atomicExch(p.status, 2);
+  if (ok && p.hT) {
+    float4* dst = reinterpret_cast<float4*>(p.hT + ((size_t)bh * KD + tid) * KD + jv0);
+#pragma unroll
+    for (int x = 0; x < VS / 4; ++x) dst[x] = make_float4(S[4 * x], S[4 * x + 1], S[4 * x + 2], S[4 * x + 3]);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+}
+
+// ------------------------------------------------------------------ host
+size_t gdn_simt_workspace_bytes(const mxb_gdn_desc* d, bool bwd);
+mxb_status gdn_simt_bwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*,
+                        const float*, const float*, const void*, const float*, void*, void*, void*,
+                        float*, float*, float*, void*, cudaStream_t);
+
+bool gdn_tc_supported(const mxb_gdn_desc* d) {
+  return d->io_dtype == MXB_BF16 && d->Dk == KD && d->Dv == KD && d->chunk == C;
+}
+
+static size_t carve_tc(TcP& p, void* ws, bool bwd) {
+  Carver cv(ws);
+  const size_t nc = (size_t)p.B * p.H * p.n;
+  p.status = cv.take<int>(64);
+  p.gam = cv.take<float>(nc * C);
+  p.Tm = cv.take<bf16>(nc * C * C);
+  p.w = cv.take<bf16>(nc * C * KD);
+  p.u = cv.take<bf16>(nc * C * KD);
+  p.P = cv.take<bf16>(nc * C * C);
+  if (bwd) {
+    p.hs = cv.take<bf16>(nc * KD * KD);
+    p.vn = cv.take<bf16>(nc * C * KD);
+    p.dhs = cv.take<bf16>(nc * KD * KD);
+    p.dvn = cv.take<bf16>(nc * C * KD);
+  }
+  return cv.bytes();
+}
+
+static TcP make_tc(const mxb_gdn_desc* d) {
+  TcP p{};
+  p.B = d->B; p.T = d->T; p.H = d->H;
+  p.n = (d->T + C - 1) / C;
+  p.gate_is_log = d->gate_is_log;
+  return p;
+}
+
+size_t gdn_tc_workspace_bytes(const mxb_gdn_desc* d, bool bwd) {
+  TcP p = make_tc(d);
+  const size_t own = carve_tc(p, nullptr, bwd);
+  if (!bwd) return own;
+  const size_t simt = gdn_simt_workspace_bytes(d, true);
+  return own > simt ? own : simt;
+}
+
+template <typename KernelT>
+static mxb_status tc_set_smem(KernelT kern, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
+  return MXB_OK;
+}
+
+static mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(p.status, 0, 256, st);
+  if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
+  if (tc_set_smem(gdn_tc_prep_kernel, kPrepSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("gdn_tc_prep_kernel", st, (gdn_tc_prep_kernel<<<dim3(p.n, p.B * p.H), 128, kPrepSmem, st>>>(p)));
+  mxb_status s = check_launch("gdn_tc_prep_kernel");
+  if (s != MXB_OK) return s;
+  if (tc_set_smem(gdn_tc_state_fwd_kernel, kStateFwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("gdn_tc_state_fwd_kernel", st,
+             (gdn_tc_state_fwd_kernel<<<dim3(KD / VS, p.B * p.H), 128, kStateFwdSmem, st>>>(p)));
+  return check_launch("gdn_tc_state_fwd_kernel");
+}
+
+mxb_status gdn_tc_fwd(const mxb_gdn_desc* d, const void* q, const void* k, const void* v, const float* beta,
+                      const float* gate, const float* h0, void* out, float* hT, void* ws, cudaStream_t st) {
+  TcP p = make_tc(d);
+  p.q = static_cast<const bf16*>(q); p.k = static_cast<const bf16*>(k); p.v = static_cast<const bf16*>(v);
+  p.beta = beta; p.gate = gate; p.h0 = h0; p.out = static_cast<bf16*>(out); p.hT = hT;
+  carve_tc(p, ws, false);
+  return tc_run_fwd(p, st);
+}
+
+mxb_status gdn_tc_bwd(const mxb_gdn_desc* d, const void* q, const void* k, const void* v, const float* beta,
+                      const float* gate, const float* h0, const void* dO, const float* dhT, void* dq, void* dk,
+                      void* dv, float* dbeta, float* dgate, float* dh0, void* ws, cudaStream_t st) {
+  // Tensor-core backward kernels are not in place yet: the full-fp32 kernels compute it.
+  return gdn_simt_bwd(d, q, k, v, beta, gate, h0, dO, dhT, dq, dk, dv, dbeta, dgate, dh0, ws, st);
 }
 
 }  // namespace mxb

@@ -103,6 +103,15 @@ def gated_delta_scan_backward(q, k, v, beta, gate, d_out, chunk=64, *, gate_is_l
     return dict(dq=dq, dk=dk, dv=dv, dbeta=dbeta, dgate=dgate, dh0=dh0)
 
 
+def device_status(device=None) -> int:
+    """Blocking read of the device-side error word of the cached workspace (0 = ok)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    ws = workspace(256, dev)
+    out = C.c_int32(0)
+    _lib.check(_lib.lib().mxb_gdn_device_status(_ptr(ws), C.byref(out)), "mxb_gdn_device_status")
+    return out.value
+
+
 def gated_delta_decode_step(state, q, k, v, beta, gate, *, gate_is_log=False, out=None):
     """One token on a persistent state [N,H,Dk,Dv] (updated in place).  Returns out [N,H,Dv]."""
     _require_cuda(state, q, k, v, beta, gate)

@@ -201,3 +201,32 @@ def test_launch_counter_moves():
     ops.gated_delta_scan(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]), 64, gate_is_log=True)
     torch.cuda.synchronize()
     assert lib.mxb_launch_count() >= n0 + 2
+
+
+# ---------------------------------------------------------------- tensor-core path (bf16, d=128, chunk 64)
+@pytest.mark.parametrize("shape", [(1, 64, 1), (1, 200, 2), (2, 512, 3), (1, 1, 1), (1, 65, 1)])
+@pytest.mark.parametrize("with_h0", [False, True])
+def test_tensor_core_forward(shape, with_h0):
+    """tcgen05 forward vs the float64 oracle on the bf16-rounded inputs, and vs the fp32 CUDA-core kernels."""
+    from mixlab_b200 import _lib
+    B, T, H = shape
+    a = inputs.gdn_inputs(B, T, H, 128, 128, seed=11, io_dtype=torch.bfloat16, with_h0=with_h0)
+    h0 = a.get("h0")
+    want_o, want_s = _oracle_fwd(a, 64, h0)
+    args = (_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]), 64)
+    o, s = ops.gated_delta_scan(*args, gate_is_log=True, h0=_dev(h0), return_final_state=True)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(o, want_o, TOL_BF16, "out")
+    assert_close(s, want_s, TOL_BF16, "final_state")
+    o32, s32 = ops.gated_delta_scan(*args, gate_is_log=True, h0=_dev(h0), return_final_state=True,
+                                    flags=_lib.MXB_GDN_FORCE_FP32_PATH)
+    assert_close(o, o32.float(), TOL_BF16, "out vs fp32 kernels")
+    assert_close(s, s32, TOL_BF16, "state vs fp32 kernels")
+
+
+def test_tensor_core_forward_multiplicative_gate():
+    a = inputs.gdn_inputs(1, 130, 2, 128, 128, seed=12, io_dtype=torch.bfloat16)
+    want_o, _ = _oracle_fwd(a, 64)
+    o = ops.gated_delta_scan(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(torch.exp(a["g"])), 64)
+    assert_close(o, want_o, TOL_BF16, "out")
