@@ -87,8 +87,10 @@ typedef struct {
 } mxb_gdn_desc;
 
 enum {
-  MXB_GDN_FORCE_FP32_PATH = 1 /* use the full-fp32 CUDA-core kernels even where a
-                                 tensor-core path exists for the shape */
+  MXB_GDN_FORCE_FP32_PATH = 1, /* use the full-fp32 CUDA-core kernels even where a
+                                  tensor-core path exists for the shape */
+  MXB_GDN_BWD_FP32_KERNELS = 2 /* tensor-core forward, but backward through the fp32
+                                  CUDA-core kernels (a cross-check of the two backwards) */
 };
 
 MXB_API size_t mxb_gdn_fwd_workspace_bytes(const mxb_gdn_desc* d);

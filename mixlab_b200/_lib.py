@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(_PKG, "libmixlab_b200.so")
 
 MXB_F32, MXB_BF16 = 1, 2
 MXB_GDN_FORCE_FP32_PATH = 1
+MXB_GDN_BWD_FP32_KERNELS = 2
 
 
 class MxbError(RuntimeError):

@@ -13,59 +13,9 @@
 //   gdn_tc_state_fwd_kernel  one CTA per (64-column slab of Dv, b*H+h), sequential over
 //                            chunks, fp32 state in registers (thread = state row):
 //                            [w;q] S (M=128) -> v_new, then [0;P] v_new and k^T (r v_new)
-#include "common.cuh"
-#include "umma_tiles.cuh"
+#include "gdn_tc.cuh"
 
 namespace mxb {
-
-namespace {
-constexpr int C = 64;     // chunk
-constexpr int KD = 128;   // Dk = Dv
-constexpr int VS = 64;    // Dv columns per state CTA
-constexpr int LDA = 68;   // fp32 row pitch of the 64x64 solve matrix (16-byte aligned rows)
-using bf16 = __nv_bfloat16;
-
-struct TcP {
-  int B, T, H, n, gate_is_log, save;
-  const bf16 *q, *k, *v;
-  const float *beta, *gate, *h0;
-  bf16* out;
-  float* hT;
-  const bf16* dO;
-  const float* dhT_in;
-  bf16 *dq, *dk, *dv;
-  float *dbeta, *dgate, *dh0;
-  int* status;   // device word: nonzero when a bounded wait gave up
-  // workspace, indexed by ci = (b*H+h)*n + chunk
-  float* gam;    // [C]
-  bf16* Tm;      // [C][C]
-  bf16* w;       // [C][KD]
-  bf16* u;       // [C][KD]
-  bf16* P;       // [C][C]
-  bf16* hs;      // [KD][KD]  state at chunk start   (backward only)
-  bf16* vn;      // [C][KD]
-  bf16* dhs;     // [KD][KD]  dS at chunk end
-  bf16* dvn;     // [C][KD]
-};
-
-__device__ __forceinline__ float log_gate_tc(float g, int gate_is_log) {
-  return gate_is_log ? fmaxf(g, kLogGateFloor) : __logf(fmaxf(g, kGateFloor));
-}
-__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
-__device__ __forceinline__ void sts16(uint8_t* base, uint32_t off, uint4 v) {
-  *reinterpret_cast<uint4*>(base + off) = v;
-}
-__device__ __forceinline__ uint4 zero16() { return make_uint4(0u, 0u, 0u, 0u); }
-
-// Loads 32 fp32 accumulator columns [c0, c0+32) of this thread's TMEM lane.
-__device__ __forceinline__ void ld_acc32(uint32_t taddr, int warp, int c0, float (&f)[32]) {
-  uint32_t r[32];
-  tc::tmem_ld_32x32b_x32(taddr + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0, r);
-  tc::tmem_ld_wait();
-#pragma unroll
-  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
-}
-}  // namespace
 
 // ------------------------------------------------------------------ prep
 constexpr int kPrepSmem = 32768 + 32768 + 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 128;
@@ -455,7 +405,9 @@ static mxb_status tc_set_smem(KernelT kern, int bytes) {
   return MXB_OK;
 }
 
-static mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
+mxb_status tc_run_bwd(TcP& p, cudaStream_t st);
+
+mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(p.status, 0, 256, st);
   if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
   if (tc_set_smem(gdn_tc_prep_kernel, kPrepSmem) != MXB_OK) return MXB_ERR_CUDA;
@@ -480,8 +432,16 @@ mxb_status gdn_tc_fwd(const mxb_gdn_desc* d, const void* q, const void* k, const
 mxb_status gdn_tc_bwd(const mxb_gdn_desc* d, const void* q, const void* k, const void* v, const float* beta,
                       const float* gate, const float* h0, const void* dO, const float* dhT, void* dq, void* dk,
                       void* dv, float* dbeta, float* dgate, float* dh0, void* ws, cudaStream_t st) {
-  // Tensor-core backward kernels are not in place yet: the full-fp32 kernels compute it.
-  return gdn_simt_bwd(d, q, k, v, beta, gate, h0, dO, dhT, dq, dk, dv, dbeta, dgate, dh0, ws, st);
+  if (d->flags & MXB_GDN_BWD_FP32_KERNELS)
+    return gdn_simt_bwd(d, q, k, v, beta, gate, h0, dO, dhT, dq, dk, dv, dbeta, dgate, dh0, ws, st);
+  TcP p = make_tc(d);
+  p.q = static_cast<const bf16*>(q); p.k = static_cast<const bf16*>(k); p.v = static_cast<const bf16*>(v);
+  p.beta = beta; p.gate = gate; p.h0 = h0;
+  p.dO = static_cast<const bf16*>(dO); p.dhT_in = dhT;
+  p.dq = static_cast<bf16*>(dq); p.dk = static_cast<bf16*>(dk); p.dv = static_cast<bf16*>(dv);
+  p.dbeta = dbeta; p.dgate = dgate; p.dh0 = dh0;
+  carve_tc(p, ws, true);
+  return tc_run_bwd(p, st);
 }
 
 }  // namespace mxb

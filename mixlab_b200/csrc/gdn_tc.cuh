@@ -1,0 +1,60 @@
+// Shared declarations of the tensor-core gated-delta kernels (forward: gdn_tc.cu,
+// backward: gdn_tc_bwd.cu).
+#pragma once
+
+#include "common.cuh"
+#include "umma_tiles.cuh"
+
+namespace mxb {
+
+namespace tcg {
+constexpr int C = 64;     // chunk
+constexpr int KD = 128;   // Dk = Dv
+constexpr int VS = 64;    // Dv columns per state CTA
+constexpr int LDA = 68;   // fp32 row pitch of the 64x64 solve matrix (16-byte aligned rows)
+using bf16 = __nv_bfloat16;
+
+struct TcP {
+  int B, T, H, n, gate_is_log, save;
+  const bf16 *q, *k, *v;
+  const float *beta, *gate, *h0;
+  bf16* out;
+  float* hT;
+  const bf16* dO;
+  const float* dhT_in;
+  bf16 *dq, *dk, *dv;
+  float *dbeta, *dgate, *dh0;
+  int* status;   // device word: nonzero when a bounded wait gave up
+  // workspace, indexed by ci = (b*H+h)*n + chunk
+  float* gam;    // [C]
+  bf16* Tm;      // [C][C]
+  bf16* w;       // [C][KD]
+  bf16* u;       // [C][KD]
+  bf16* P;       // [C][C]
+  bf16* hs;      // [KD][KD]  state at chunk start   (backward only)
+  bf16* vn;      // [C][KD]
+  bf16* dhs;     // [KD][KD]  dS at chunk end
+  bf16* dvn;     // [C][KD]
+};
+
+__device__ __forceinline__ float log_gate_tc(float g, int gate_is_log) {
+  return gate_is_log ? fmaxf(g, kLogGateFloor) : __logf(fmaxf(g, kGateFloor));
+}
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void sts16(uint8_t* base, uint32_t off, uint4 v) {
+  *reinterpret_cast<uint4*>(base + off) = v;
+}
+__device__ __forceinline__ uint4 zero16() { return make_uint4(0u, 0u, 0u, 0u); }
+
+// Loads 32 fp32 accumulator columns [c0, c0+32) of this thread's TMEM lane.
+__device__ __forceinline__ void ld_acc32(uint32_t taddr, int warp, int c0, float (&f)[32]) {
+  uint32_t r[32];
+  tc::tmem_ld_32x32b_x32(taddr + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0, r);
+  tc::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+}
+}  // namespace tcg
+using namespace tcg;
+
+}  // namespace mxb

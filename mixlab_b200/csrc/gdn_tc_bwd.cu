@@ -1,0 +1,637 @@
+// Gated delta rule - tensor-core backward (tcgen05.mma, TMEM accumulators),
+// bf16 I/O, fp32 state gradient, chunk 64, Dk = Dv = 128.
+//
+// Hand-derived backward of the chunked form (the reference differentiates
+// gpu/ir.cpp:2352-2550 with MLX autograd; its only VJP, tril(T^T dT T^T,-1) of the
+// triangular solve, gpu/gated_delta_cuda_primitive.cpp:104-132, is phase C below).
+// With d = E(gam), r = E(gam_last-gam), L = E(gam_last), S0 the state at chunk start
+// and dS the state gradient at chunk end:
+//
+//   gdn_tc_state_bwd_kernel  reverse over chunks, one CTA per (64-column slab, b*H+h):
+//       dv_new = P^T dO + r (k dS)
+//       dS    <- L dS + q^T (d dO) - w^T dv_new
+//   gdn_tc_chunk_bwd_kernel  one CTA per chunk, everything else:
+//       dq = d (dO S0^T) + (dP*Gamma) k                      dP = tril(dO v_new^T)
+//       dw = -dv_new S0^T ; dT = dv_new (v beta)^T + dw (k beta d)^T ; dA = tril(T^T dT T^T,-1)
+//       dk = (dP*Gamma)^T q + r (v_new dS^T) + beta d (T^T dw) + (Mb + Mb^T) k,  Mb = -beta dA*Gamma
+//       dv = beta (T^T dv_new) ; dbeta, dgam from the same pieces ; dg = reverse cumsum of dgam
+//
+// A 64 x W bf16 tile stored as 8x8-element blocks ("blocked row-major", umma_tiles.cuh)
+// can be read by tcgen05.mma either with the contraction along its columns (K-major) or
+// along its rows (MN-major); both views are used on the same staged bytes.
+#include "gdn_tc.cuh"
+
+namespace mxb {
+
+constexpr int kStateBwdSmem = 16384 + 16384 + 8192 + 8192 + 32768 + 16384 + 2 * C * 4 + 64 + 128;
+
+__global__ void __launch_bounds__(128) gdn_tc_state_bwd_kernel(TcP p) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* Ak = sm;                 // [64 i][128 kk]      k
+  uint8_t* dSop = Ak + 16384;       // [128 kk][64 j]      bf16 copy of dS
+  uint8_t* Pt = dSop + 16384;       // [64 m][64 i]        P   (A = P^T: contraction over rows)
+  uint8_t* dOop = Pt + 8192;        // [64 m][64 j]        dO slab
+  uint8_t* Aqw = dOop + 8192;       // [128: q rows, w rows][128 kk]   (A = [q^T | w^T])
+  uint8_t* Bdd = Aqw + 32768;       // [128: d dO rows, -dv_new rows][64 j]
+  float* dd = reinterpret_cast<float*>(Bdd + 16384);
+  float* rr = dd + C;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
+  const int jv0 = blockIdx.x * VS;
+
+  if (warp == 0) {
+    tc::tmem_alloc(tslot, 256);
+    tc::tmem_relinquish();
+  }
+  if (tid == 0) {
+    tc::mbar_init(mbar, 1);
+    tc::mbar_fence_init();
+  }
+  float dS[VS];  // row kk = tid of dS, columns jv0 .. jv0+63
+  if (p.dhT_in) {
+    const float4* src = reinterpret_cast<const float4*>(p.dhT_in + ((size_t)bh * KD + tid) * KD + jv0);
+#pragma unroll
+    for (int x = 0; x < VS / 4; ++x) {
+      const float4 t4 = __ldg(src + x);
+      dS[4 * x] = t4.x; dS[4 * x + 1] = t4.y; dS[4 * x + 2] = t4.z; dS[4 * x + 3] = t4.w;
+    }
+  } else {
+#pragma unroll
+    for (int x = 0; x < VS; ++x) dS[x] = 0.f;
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t taddr = *tslot;
+  uint32_t ph = 0;
+  bool ok = true;
+
+  for (int c = p.n - 1; c >= 0 && ok; --c) {
+    const size_t ci = (size_t)bh * p.n + c;
+    const int t0 = c * C, imax = min(C, p.T - t0);
+    auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
+    const float* gam = p.gam + ci * C;
+    const float glast = gam[C - 1];
+    const float L = exp_nonpos(glast);
+    if (tid < C) {
+      const float g = gam[tid];
+      dd[tid] = exp_nonpos(g);
+      rr[tid] = exp_nonpos(glast - g);
+    }
+#pragma unroll
+    for (int c8 = 0; c8 < VS / 8; ++c8) {  // dS at chunk end: MMA operand + saved for the chunk kernel
+      const uint4 val = make_uint4(tc::pack_bf16(dS[8 * c8], dS[8 * c8 + 1]), tc::pack_bf16(dS[8 * c8 + 2], dS[8 * c8 + 3]),
+                                   tc::pack_bf16(dS[8 * c8 + 4], dS[8 * c8 + 5]), tc::pack_bf16(dS[8 * c8 + 6], dS[8 * c8 + 7]));
+      sts16(dSop, tc::mnmajor_unit(tid, c8, VS), val);
+      *reinterpret_cast<uint4*>(p.dhs + (ci * KD + tid) * KD + jv0 + c8 * 8) = val;
+    }
+    __syncthreads();  // dd, rr visible
+    for (int u = tid; u < 64 * 16; u += 128) {   // k
+      const int i = u >> 4, c8 = u & 15;
+      sts16(Ak, tc::kmajor_unit(i, c8, KD), i < imax ? ldg16(p.k + row(i) * KD + c8 * 8) : zero16());
+    }
+    for (int u = tid; u < 64 * 8; u += 128) {    // P ; dO slab and d dO
+      const int i = u >> 3, c8 = u & 7;
+      sts16(Pt, tc::kmajor_unit(i, c8, C), ldg16(p.P + (ci * C + i) * C + c8 * 8));
+      const uint4 g = i < imax ? ldg16(p.dO + row(i) * KD + jv0 + c8 * 8) : zero16();
+      sts16(dOop, tc::kmajor_unit(i, c8, VS), g);
+      sts16(Bdd, tc::kmajor_unit(i, c8, VS), tc::scale_bf16x8(g, dd[i]));
+    }
+    for (int u = tid; u < 128 * 16; u += 128) {  // [q; w]
+      const int r = u >> 4, c8 = u & 15, i = r & 63;
+      uint4 val = zero16();
+      if (r >= 64) val = ldg16(p.w + (ci * C + i) * KD + c8 * 8);
+      else if (i < imax) val = ldg16(p.q + row(i) * KD + c8 * 8);
+      sts16(Aqw, tc::kmajor_unit(r, c8, KD), val);
+    }
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    if (tid == 0) {
+      tc::issue_gemm(taddr, tc::kmajor_tile(Ak, KD), tc::mnmajor_tile(dSop, VS), 64, VS, KD, false);          // k dS
+      tc::issue_gemm(taddr + 64, tc::mnmajor_tile(Pt, C), tc::mnmajor_tile(dOop, VS), 64, VS, C, false);      // P^T dO
+      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Aqw, KD), tc::mnmajor_tile(Bdd, VS), 128, VS, C, false);   // q^T (d dO)
+      tc::mma_commit(mbar);
+    }
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+    tc::fence_after_sync();
+    if (ok) {
+      const int i = 16 * warp + (lane & 15);  // M=64 accumulators: row i sits in TMEM lane (i%16) + 32*(i/16)
+      const float ri = rr[i];
+      for (int c0 = 0; c0 < VS; c0 += 32) {
+        float fa[32], fb[32];
+        ld_acc32(taddr, warp, c0, fa);
+        ld_acc32(taddr + 64, warp, c0, fb);
+        if (lane < 16) {
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            float e[8];
+#pragma unroll
+            for (int y = 0; y < 8; ++y) e[y] = fmaf(ri, fa[8 * x + y], fb[8 * x + y]);
+            const uint4 vv = make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
+                                        tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7]));
+            *reinterpret_cast<uint4*>(p.dvn + (ci * C + i) * KD + jv0 + c0 + 8 * x) = vv;
+            sts16(Bdd, tc::kmajor_unit(64 + i, (c0 >> 3) + x, VS), tc::scale_bf16x8(vv, -1.f));
+          }
+        }
+      }
+    }
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    if (ok && tid == 0) {  // ... - w^T dv_new
+      tc::issue_gemm(taddr + 128, tc::skip_k(tc::mnmajor_tile(Aqw, KD), 64), tc::skip_k(tc::mnmajor_tile(Bdd, VS), 64),
+                     128, VS, C, true);
+      tc::mma_commit(mbar);
+    }
+    if (ok) {
+      ok = tc::mbar_wait(mbar, ph);
+      ph ^= 1;
+    }
+    tc::fence_after_sync();
+    if (ok) {
+      for (int c0 = 0; c0 < VS; c0 += 32) {
+        float f[32];
+        ld_acc32(taddr + 128, warp, c0, f);
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) dS[c0 + jj] = fmaf(L, dS[c0 + jj], f[jj]);
+      }
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+  }
+  if (!ok && tid == 0) atomicExch(p.status, 3);
+  if (ok && p.dh0) {
+    float4* dst = reinterpret_cast<float4*>(p.dh0 + ((size_t)bh * KD + tid) * KD + jv0);
+#pragma unroll
+    for (int x = 0; x < VS / 4; ++x) dst[x] = make_float4(dS[4 * x], dS[4 * x + 1], dS[4 * x + 2], dS[4 * x + 3]);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+}
+
+// ------------------------------------------------------------ chunk backward
+// TMEM column map (fp32 columns; all accumulators are M=64, so row i of every result
+// sits in TMEM lane (i%16) + 32*(i/16) and is handled by thread (warp i/16, lane i%16)):
+//   [  0,128) dqi = dO S0^T            -> later z = T^T dw
+//   [128,256) dv_new S0^T (= -dw)      -> dT [128,192), Y [192,256) -> dA [128,192) -> dk part
+//   [256,384) dkt = v_new dS^T
+//   [384,448) dP                       -> k k^T     } -> [384,512) (dP*Gamma) k -> T^T dv_new
+//   [448,512)                             q k^T     }
+constexpr int kChunkBwdSmem = 49152 + 65536 + 16384 + 4 * 8192 + 8 * C * 4 + 64 + 256;
+
+__device__ __forceinline__ void unpack8(uint4 v, float (&e)[8]) {
+  tc::unpack_bf16(v.x, e[0], e[1]); tc::unpack_bf16(v.y, e[2], e[3]);
+  tc::unpack_bf16(v.z, e[4], e[5]); tc::unpack_bf16(v.w, e[6], e[7]);
+}
+__device__ __forceinline__ uint4 pack8(const float* e) {
+  return make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]), tc::pack_bf16(e[4], e[5]),
+                    tc::pack_bf16(e[6], e[7]));
+}
+// sum_k tile[row][c0 + k] * f[k], k < 32, for a blocked [.][128] bf16 tile in shared memory
+__device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
+  float s = 0.f;
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    float e[8];
+    unpack8(*reinterpret_cast<const uint4*>(tile + tc::kmajor_unit(r, (c0 >> 3) + x, KD)), e);
+#pragma unroll
+    for (int y = 0; y < 8; ++y) s = fmaf(e[y], f[8 * x + y], s);
+  }
+  return s;
+}
+
+__global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* Xdo = sm;                // [64][128] dO
+  uint8_t* Xdvn = Xdo + 16384;      // [64][128] dv_new
+  uint8_t* Xvn = Xdvn + 16384;      // [64][128] v_new
+  uint8_t* Sreg = Xvn + 16384;      // 64 KB: phase A  S0 [128][128] | dS [128][128]
+  uint8_t* Xs0 = Sreg;              //        later    k | q | v beta | k beta d   ([64][128] each)
+  uint8_t* Xds = Sreg + 32768;
+  uint8_t* Xk = Sreg;
+  uint8_t* Xq = Sreg + 16384;
+  uint8_t* Xvb = Sreg + 32768;
+  uint8_t* Xkbd = Sreg + 49152;
+  uint8_t* Xdw = Sreg + 65536;      // [64][128] dw
+  uint8_t* Xt = Xdw + 16384;        // [64][64]  T
+  uint8_t* Xpg = Xt + 8192;         // [64][64]  dP*Gamma
+  uint8_t* X1 = Xpg + 8192;         // [64][64]  dT, later Mb + Mb^T
+  uint8_t* X2 = X1 + 8192;          // [64][64]  Y = T^T dT
+  float* gam = reinterpret_cast<float*>(X2 + 8192);
+  float* bet = gam + C;
+  float* dd = bet + C;
+  float* rr = dd + C;
+  float* csum = rr + C;             // cross-row contributions to dgam (shared atomics)
+  float* dgo = csum + C;            // per-row dgam / dbeta handed over at the end
+  float* dbo = dgo + C;
+  float* red = dbo + C;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + C);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
+  const size_t ci = (size_t)bh * p.n + c;
+  const int imax = min(C, p.T - t0);
+  auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
+  const bool own = lane < 16;
+  const int i = 16 * warp + (lane & 15);  // the row this thread owns in every epilogue
+
+  if (warp == 0) {
+    tc::tmem_alloc(tslot, 512);
+    tc::tmem_relinquish();
+  }
+  if (tid == 0) {
+    tc::mbar_init(mbar, 1);
+    tc::mbar_fence_init();
+  }
+  if (tid < C) {
+    gam[tid] = p.gam[ci * C + tid];
+    bet[tid] = tid < imax ? p.beta[row(tid)] : 0.f;
+    csum[tid] = 0.f;
+  }
+  // ---- phase A staging: dO, dv_new, v_new, S0, dS, T ----
+  for (int u = tid; u < 64 * 16; u += 128) {
+    const int r = u >> 4, c8 = u & 15;
+    const uint32_t off = tc::kmajor_unit(r, c8, KD);
+    sts16(Xdo, off, r < imax ? ldg16(p.dO + row(r) * KD + c8 * 8) : zero16());
+    sts16(Xdvn, off, ldg16(p.dvn + (ci * C + r) * KD + c8 * 8));
+    sts16(Xvn, off, ldg16(p.vn + (ci * C + r) * KD + c8 * 8));
+  }
+  for (int u = tid; u < 128 * 16; u += 128) {
+    const int r = u >> 4, c8 = u & 15;
+    const uint32_t off = tc::kmajor_unit(r, c8, KD);
+    sts16(Xs0, off, ldg16(p.hs + (ci * KD + r) * KD + c8 * 8));
+    sts16(Xds, off, ldg16(p.dhs + (ci * KD + r) * KD + c8 * 8));
+  }
+  for (int u = tid; u < 64 * 8; u += 128) {
+    const int r = u >> 3, c8 = u & 7;
+    sts16(Xt, tc::kmajor_unit(r, c8, C), ldg16(p.Tm + (ci * C + r) * C + c8 * 8));
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t taddr = *tslot;
+  uint32_t ph = 0;
+  bool ok = true;
+  const float glast = gam[C - 1], L = exp_nonpos(glast);
+  if (tid < C) {
+    dd[tid] = exp_nonpos(gam[tid]);
+    rr[tid] = exp_nonpos(glast - gam[tid]);
+  }
+  if (tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xs0, KD), 64, 128, KD, false);
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xs0, KD), 64, 128, KD, false);
+    tc::issue_gemm(taddr + 256, tc::kmajor_tile(Xvn, KD), tc::kmajor_tile(Xds, KD), 64, 128, KD, false);
+    tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xvn, KD), 64, 64, KD, false);
+    tc::mma_commit(mbar);
+  }
+  {  // <dS, S0> while the tensor core works
+    float part = 0.f;
+    for (int u = tid; u < 128 * 16; u += 128) {
+      float a[8], bq[8];
+      unpack8(*reinterpret_cast<const uint4*>(Xs0 + u * 16), a);
+      unpack8(*reinterpret_cast<const uint4*>(Xds + u * 16), bq);
+#pragma unroll
+      for (int y = 0; y < 8; ++y) part = fmaf(a[y], bq[y], part);
+    }
+    part = warp_sum(part);
+    if (lane == 0) red[warp] = part;
+  }
+  __syncthreads();  // dd, rr, red visible
+  ok = tc::mbar_wait(mbar, ph);
+  ph ^= 1;
+  tc::fence_after_sync();
+  float dg_own = 0.f, db_own = 0.f;
+  const float gi = gam[i], bi = bet[i], di = dd[i], ri = rr[i];
+  if (ok) {
+    for (int c0 = 0; c0 < 64; c0 += 32) {  // dP * Gamma, lower incl. diagonal
+      float f[32];
+      ld_acc32(taddr + 384, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const int j = c0 + jj;
+          f[jj] = (j <= i) ? f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Xpg, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
+      }
+    }
+    for (int c0 = 0; c0 < KD; c0 += 32) {  // dw = -dv_new S0^T
+      float f[32];
+      ld_acc32(taddr + 128, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) f[jj] = -f[jj];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Xdw, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
+      }
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();  // S0 / dS no longer read by anyone: the region is restaged
+  tc::fence_after_sync();
+  // ---- phase B staging: k, q, v beta, k beta d ----
+  for (int u = tid; u < 64 * 16; u += 128) {
+    const int r = u >> 4, c8 = u & 15;
+    const uint32_t off = tc::kmajor_unit(r, c8, KD);
+    uint4 kk = zero16(), qq = zero16(), vv = zero16();
+    if (r < imax) {
+      kk = ldg16(p.k + row(r) * KD + c8 * 8);
+      qq = ldg16(p.q + row(r) * KD + c8 * 8);
+      vv = ldg16(p.v + row(r) * KD + c8 * 8);
+    }
+    sts16(Xk, off, kk);
+    sts16(Xq, off, qq);
+    sts16(Xvb, off, tc::scale_bf16x8(vv, bet[r]));
+    sts16(Xkbd, off, tc::scale_bf16x8(kk, bet[r] * dd[r]));
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xk, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);    // k k^T
+    tc::issue_gemm(taddr + 448, tc::kmajor_tile(Xq, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);    // q k^T
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xvb, KD), 64, 64, KD, false); // dT
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdw, KD), tc::kmajor_tile(Xkbd, KD), 64, 64, KD, true);
+    tc::mma_commit(mbar);
+  }
+  if (ok) {
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+  }
+  tc::fence_after_sync();
+  float KKr[C];  // (k_i . k_j), j < i
+  if (ok) {
+    for (int c0 = 0; c0 < 64; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr + 448, warp, c0, f);  // q k^T: dgam from P
+      if (own) {
+        float rs = 0.f;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float e[8];
+          unpack8(*reinterpret_cast<const uint4*>(Xpg + tc::kmajor_unit(i, (c0 >> 3) + x, C)), e);
+#pragma unroll
+          for (int y = 0; y < 8; ++y) {
+            const int j = c0 + 8 * x + y;
+            if (j <= i) {
+              const float X = e[y] * f[8 * x + y];
+              rs += X;
+              atomicAdd(&csum[j], -X);
+            }
+          }
+        }
+        dg_own += rs;
+      }
+      ld_acc32(taddr + 384, warp, c0, f);  // k k^T
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) KKr[c0 + jj] = f[jj];
+      ld_acc32(taddr + 128, warp, c0, f);  // dT row -> X1
+      if (own) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(X1, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
+      }
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  // ---- phase C: dA = tril(T^T dT T^T, -1) ----
+  if (ok && tid == 0) {  // Y = T^T dT  (both operands contracted over their rows)
+    tc::issue_gemm(taddr + 192, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(X1, C), 64, 64, C, false);
+    tc::mma_commit(mbar);
+  }
+  if (ok) {
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+  }
+  tc::fence_after_sync();
+  if (ok) {
+    for (int c0 = 0; c0 < 64; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr + 192, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(X2, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
+      }
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  if (ok && tid == 0) {  // dA = Y T^T
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(X2, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
+    tc::mma_commit(mbar);
+  }
+  if (ok) {
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+  }
+  tc::fence_after_sync();
+  if (ok) {
+    bf16* ms = reinterpret_cast<bf16*>(X1);  // X1 <- Mb + Mb^T (dT has been consumed)
+    auto ms_at = [&](int r, int cc) -> bf16& {
+      return ms[(tc::kmajor_unit(r, cc >> 3, C) >> 1) + (cc & 7)];
+    };
+    for (int c0 = 0; c0 < 64; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr + 128, warp, c0, f);
+      if (own) {
+        float rs = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const int j = c0 + jj;
+          if (j < i) {
+            const float M = -f[jj] * exp_nonpos(gi - gam[j]);  // -dA * Gamma
+            const float t = M * KKr[j];
+            rs += t;
+            atomicAdd(&csum[j], -bi * t);
+            const bf16 mb = __float2bfloat16_rn(bi * M);
+            ms_at(i, j) = mb;
+            ms_at(j, i) = mb;
+          } else if (j == i) {
+            ms_at(i, i) = __float2bfloat16_rn(0.f);
+          }
+        }
+        db_own += rs;
+        dg_own += bi * rs;
+      }
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  // ---- phase D1: (dP*Gamma) k  and  (dP*Gamma)^T q + (Mb + Mb^T) k ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xpg, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, false);
+    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xpg, C), tc::mnmajor_tile(Xq, KD), 64, 128, C, false);
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(X1, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, true);
+    tc::mma_commit(mbar);
+  }
+  if (ok) {
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+  }
+  tc::fence_after_sync();
+  if (ok) {
+    float qdot = 0.f, kdot = 0.f;
+    for (int c0 = 0; c0 < KD; c0 += 32) {
+      float f[32], g2[32];
+      ld_acc32(taddr + 0, warp, c0, f);     // dqi
+      ld_acc32(taddr + 384, warp, c0, g2);  // (dP*Gamma) k
+      if (own) {
+        qdot += row_dot32(Xq, i, c0, f);
+        if (i < imax) {
+          float e[32];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) e[jj] = fmaf(di, f[jj], g2[jj]);
+          uint4* dst = reinterpret_cast<uint4*>(p.dq + row(i) * KD + c0);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
+        }
+      }
+      ld_acc32(taddr + 256, warp, c0, f);   // dkt
+      if (own) kdot += row_dot32(Xk, i, c0, f);
+    }
+    if (own) {
+      const float rho = ri * kdot;
+      dg_own += di * qdot - rho;
+      atomicAdd(&csum[C - 1], rho);
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();  // columns [0,128) and [384,512) are free again
+  tc::fence_after_sync();
+  // ---- phase D2: T^T dv_new  and  z = T^T dw ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 384, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdvn, KD), 64, 128, C, false);
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdw, KD), 64, 128, C, false);
+    tc::mma_commit(mbar);
+  }
+  if (ok) {
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+  }
+  tc::fence_after_sync();
+  if (ok) {
+    float vdot = 0.f, kz = 0.f;
+    const float bd_i = bi * di;
+    for (int c0 = 0; c0 < KD; c0 += 32) {
+      float f[32], g2[32], g3[32];
+      ld_acc32(taddr + 384, warp, c0, f);  // T^T dv_new
+      if (own && i < imax) {
+        float e[32];
+        const uint4* vsrc = reinterpret_cast<const uint4*>(p.v + row(i) * KD + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float vv[8];
+          unpack8(__ldg(vsrc + x), vv);
+#pragma unroll
+          for (int y = 0; y < 8; ++y) {
+            vdot = fmaf(vv[y], f[8 * x + y], vdot);
+            e[8 * x + y] = bi * f[8 * x + y];
+          }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(p.dv + row(i) * KD + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
+      }
+      ld_acc32(taddr + 0, warp, c0, f);     // z
+      ld_acc32(taddr + 128, warp, c0, g2);  // (dP*Gamma)^T q + (Mb+Mb^T) k
+      ld_acc32(taddr + 256, warp, c0, g3);  // dkt
+      if (own) {
+        kz += row_dot32(Xk, i, c0, f);
+        if (i < imax) {
+          float e[32];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) e[jj] = g2[jj] + ri * g3[jj] + bd_i * f[jj];
+          uint4* dst = reinterpret_cast<uint4*>(p.dk + row(i) * KD + c0);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
+        }
+      }
+    }
+    if (own) {
+      db_own += vdot + di * kz;
+      dg_own += bd_i * kz;
+    }
+  }
+  if (own) {
+    dgo[i] = dg_own;
+    dbo[i] = db_own;
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (tid == 0) {  // dg = reverse cumulative sum of dgam within the chunk
+    float acc = L * (red[0] + red[1] + red[2] + red[3]);  // d/dgam_last of E(gam_last) <dS, S0>
+    for (int r = C - 1; r >= 0; --r) {
+      acc += dgo[r] + csum[r];
+      dgo[r] = acc;
+    }
+  }
+  __syncthreads();
+  if (!ok && tid == 0) atomicExch(p.status, 4);
+  if (ok && tid < imax) {
+    p.dbeta[row(tid)] = dbo[tid];
+    float dg = dgo[tid];
+    const float gin = p.gate[row(tid)];
+    if (p.gate_is_log) {
+      if (gin < kLogGateFloor) dg = 0.f;
+    } else {
+      dg = (gin > kGateFloor) ? dg / gin : 0.f;
+    }
+    p.dgate[row(tid)] = dg;
+  }
+  if (warp == 0) tc::tmem_dealloc(taddr, 512);
+}
+
+// ------------------------------------------------------------------ host
+mxb_status tc_run_fwd(TcP& p, cudaStream_t st);
+
+template <typename KernelT>
+static mxb_status bwd_set_smem(KernelT kern, int bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
+  return MXB_OK;
+}
+
+// Forward recompute (saving per-chunk states and v_new), reverse state pass, per-chunk pass.
+mxb_status tc_run_bwd(TcP& p, cudaStream_t st) {
+  p.save = 1;
+  bf16* keep_out = p.out;
+  float* keep_hT = p.hT;
+  p.out = p.dv;  // the recomputed forward output is not needed; dv is overwritten afterwards
+  p.hT = nullptr;
+  mxb_status s = tc_run_fwd(p, st);
+  p.out = keep_out;
+  p.hT = keep_hT;
+  if (s != MXB_OK) return s;
+  if (bwd_set_smem(gdn_tc_state_bwd_kernel, kStateBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("gdn_tc_state_bwd_kernel", st,
+             (gdn_tc_state_bwd_kernel<<<dim3(KD / VS, p.B * p.H), 128, kStateBwdSmem, st>>>(p)));
+  s = check_launch("gdn_tc_state_bwd_kernel");
+  if (s != MXB_OK) return s;
+  if (bwd_set_smem(gdn_tc_chunk_bwd_kernel, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
+             (gdn_tc_chunk_bwd_kernel<<<dim3(p.n, p.B * p.H), 128, kChunkBwdSmem, st>>>(p)));
+  return check_launch("gdn_tc_chunk_bwd_kernel");
+}
+
+}  // namespace mxb

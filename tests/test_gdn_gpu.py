@@ -230,3 +230,40 @@ def test_tensor_core_forward_multiplicative_gate():
     want_o, _ = _oracle_fwd(a, 64)
     o = ops.gated_delta_scan(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(torch.exp(a["g"])), 64)
     assert_close(o, want_o, TOL_BF16, "out")
+
+
+@pytest.mark.parametrize("shape", [(1, 64, 1), (1, 200, 2), (2, 320, 2), (1, 1, 1)])
+@pytest.mark.parametrize("with_h0", [False, True])
+@pytest.mark.parametrize("gate_is_log", [True, False])
+def test_tensor_core_backward(shape, with_h0, gate_is_log):
+    """tcgen05 backward vs float64 autograd on the bf16-rounded inputs (2e-2 on every gradient)."""
+    B, T, H = shape
+    a = inputs.gdn_inputs(B, T, H, 128, 128, seed=21, io_dtype=torch.bfloat16, with_grad_out=True, with_h0=with_h0)
+    f = {k: v.double() for k, v in a.items()}
+    gate64 = f["g"] if gate_is_log else torch.exp(f["g"])
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], gate64, f["d_out"], f.get("d_state"), f.get("h0"),
+                          gate_is_log=gate_is_log)
+    gate = a["g"] if gate_is_log else torch.exp(a["g"])
+    got = ops.gated_delta_scan_backward(_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(gate),
+                                        _dev(a["d_out"]), 64, gate_is_log=gate_is_log, h0=_dev(a.get("h0")),
+                                        d_final_state=_dev(a.get("d_state")))
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    names = ["dq", "dk", "dv", "dbeta", "dgate"] + (["dh0"] if with_h0 else [])
+    errs = {}
+    for name in names:
+        try:
+            errs[name] = assert_close(got[name], want[name], TOL_BF16, name)
+        except AssertionError as e:
+            errs[name] = str(e)
+    assert all(not isinstance(v, str) for v in errs.values()), errs
+
+
+def test_tensor_core_backward_matches_fp32_kernels():
+    from mixlab_b200 import _lib
+    a = inputs.gdn_inputs(1, 256, 2, 128, 128, seed=22, io_dtype=torch.bfloat16, with_grad_out=True)
+    args = (_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]), _dev(a["d_out"]), 64)
+    g_tc = ops.gated_delta_scan_backward(*args, gate_is_log=True)
+    g_32 = ops.gated_delta_scan_backward(*args, gate_is_log=True, flags=_lib.MXB_GDN_BWD_FP32_KERNELS)
+    for name in ("dq", "dk", "dv", "dbeta", "dgate"):
+        assert_close(g_tc[name], g_32[name].float(), TOL_BF16, name)
