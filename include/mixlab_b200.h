@@ -113,6 +113,23 @@ MXB_API mxb_status mxb_gdn_bwd(const mxb_gdn_desc* d, const void* q, const void*
                        float* dbeta, float* dgate, float* dh0, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* Forward without a workspace argument, for hosts that cannot allocate device
+ * memory: programs living inside a runtime that has reserved the whole GPU for its
+ * own pool, or loops where a call into an allocator (which may block or synchronise)
+ * is not acceptable.  No counterpart in the reference.  The scratch is a fixed array
+ * of MXB_GDN_STATIC_SCRATCH_BYTES inside the library (present once per GPU while the
+ * library is loaded); problems whose workspace (mxb_gdn_fwd_workspace_bytes with
+ * MXB_GDN_FORCE_FP32_PATH) is larger return MXB_ERR_WORKSPACE.  Always runs the
+ * full-fp32 CUDA-core kernels; same arguments and results as mxb_gdn_fwd with that
+ * flag.  Calls no cudaMalloc/cudaFree.  All calls on a GPU share the one array: do
+ * not let two of them overlap on the device.  The first call on each device looks up
+ * the array's address; make that call before any stream capture begins. */
+#define MXB_GDN_STATIC_SCRATCH_BYTES (16u << 20)
+MXB_API size_t mxb_gdn_static_scratch_bytes(void);
+MXB_API mxb_status mxb_gdn_fwd_static_scratch(const mxb_gdn_desc* d, const void* q, const void* k,
+                                      const void* v, const float* beta, const float* gate,
+                                      const float* h0, void* out, float* hT, void* stream);
+
 /* The tensor-core kernels bound every wait on an mbarrier; a wait that gives up
  * makes the kernel leave in an orderly way and write a nonzero code into the first
  * word of the workspace.  This BLOCKING call copies that word to *out (0 = no

@@ -40,6 +40,8 @@ EXPORTS = {
     "mxb_gdn_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(GdnDesc)]),
     "mxb_gdn_fwd": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 9 + [C.c_size_t, _P]),
     "mxb_gdn_bwd": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 15 + [C.c_size_t, _P]),
+    "mxb_gdn_static_scratch_bytes": (C.c_size_t, []),
+    "mxb_gdn_fwd_static_scratch": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 9),
     "mxb_gdn_device_status": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
     "mxb_gdn_decode_step": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 8),
     "mxb_mamba3_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Mamba3Desc)]),
