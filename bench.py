@@ -201,9 +201,10 @@ def main():
         bound = "hbm"
 
         def step():
-            ops.gated_delta_scan(d["q"], d["k"], d["v"], d["beta"], d["g"], Cc, gate_is_log=True, flags=flags)
+            ops.gated_delta_scan(d["q"], d["k"], d["v"], d["beta"], d["g"], Cc, gate_is_log=True, flags=flags,
+                                 save_for_backward=True)
             ops.gated_delta_scan_backward(d["q"], d["k"], d["v"], d["beta"], d["g"], d["d_out"], Cc,
-                                          gate_is_log=True, flags=flags)
+                                          gate_is_log=True, flags=flags, use_saved=True)
 
         cfg = {"workload": "gdn_train", **w, "io": "bf16", "state": "fp32", "per_gpu_batch": B,
                "parallelism": f"batch-sharded x{world}, no collective",

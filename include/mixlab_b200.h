@@ -89,8 +89,14 @@ typedef struct {
 enum {
   MXB_GDN_FORCE_FP32_PATH = 1, /* use the full-fp32 CUDA-core kernels even where a
                                   tensor-core path exists for the shape */
-  MXB_GDN_BWD_FP32_KERNELS = 2 /* tensor-core forward, but backward through the fp32
-                                  CUDA-core kernels (a cross-check of the two backwards) */
+  MXB_GDN_BWD_FP32_KERNELS = 2, /* tensor-core forward, but backward through the fp32
+                                   CUDA-core kernels (a cross-check of the two backwards) */
+  MXB_GDN_SAVE_FOR_BWD = 4,     /* forward: also keep the per-chunk states and v_new in the
+                                   workspace, which must then have the BACKWARD size */
+  MXB_GDN_BWD_USE_SAVED = 8     /* backward: the workspace still holds what a forward with
+                                   MXB_GDN_SAVE_FOR_BWD on the same inputs left there, so the
+                                   forward recompute is skipped (the reference keeps its forward
+                                   intermediates alive through MLX autograd in the same way) */
 };
 
 MXB_API size_t mxb_gdn_fwd_workspace_bytes(const mxb_gdn_desc* d);

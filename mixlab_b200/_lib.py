@@ -11,6 +11,8 @@ LIB_PATH = os.path.join(_PKG, "libmixlab_b200.so")
 MXB_F32, MXB_BF16 = 1, 2
 MXB_GDN_FORCE_FP32_PATH = 1
 MXB_GDN_BWD_FP32_KERNELS = 2
+MXB_GDN_SAVE_FOR_BWD = 4
+MXB_GDN_BWD_USE_SAVED = 8
 
 
 class MxbError(RuntimeError):

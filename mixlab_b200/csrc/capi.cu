@@ -161,8 +161,9 @@ size_t mxb_trace_summary(char* buf, size_t cap) {
 
 size_t mxb_gdn_fwd_workspace_bytes(const mxb_gdn_desc* d) {
   if (check_gdn_desc(d, true) != MXB_OK) return 0;
-  if (use_tc(d)) return gdn_tc_workspace_bytes(d, false);
-  return gdn_simt_workspace_bytes(d, false);
+  const bool save = (d->flags & MXB_GDN_SAVE_FOR_BWD) != 0;
+  if (use_tc(d)) return gdn_tc_workspace_bytes(d, save);
+  return gdn_simt_workspace_bytes(d, save);
 }
 
 size_t mxb_gdn_bwd_workspace_bytes(const mxb_gdn_desc* d) {
@@ -355,11 +356,16 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
   MXB_CUDA_TRY(cudaMemcpyAsync(dbeta_in, beta, ns * 4, cudaMemcpyHostToDevice, st));
   MXB_CUDA_TRY(cudaMemcpyAsync(dgate_in, gate, ns * 4, cudaMemcpyHostToDevice, st));
   if (bwd) MXB_CUDA_TRY(cudaMemcpyAsync(ddo, d_out, nv * es, cudaMemcpyHostToDevice, st));
-  s = mxb_gdn_fwd(d, dq_in, dk_in, dv_in, dbeta_in, dgate_in, nullptr, dout, nullptr, ws, ws_f, st);
+  mxb_gdn_desc df = *d, db = *d;
+  if (bwd) {  // keep the forward intermediates in the arena for the backward that follows
+    df.flags |= MXB_GDN_SAVE_FOR_BWD;
+    db.flags |= MXB_GDN_BWD_USE_SAVED;
+  }
+  s = mxb_gdn_fwd(&df, dq_in, dk_in, dv_in, dbeta_in, dgate_in, nullptr, dout, nullptr, ws, bwd ? ws_b : ws_f, st);
   if (s != MXB_OK) return s;
   MXB_CUDA_TRY(cudaMemcpyAsync(out, dout, nv * es, cudaMemcpyDeviceToHost, st));
   if (bwd) {
-    s = mxb_gdn_bwd(d, dq_in, dk_in, dv_in, dbeta_in, dgate_in, nullptr, ddo, nullptr, g_q, g_k, g_v,
+    s = mxb_gdn_bwd(&db, dq_in, dk_in, dv_in, dbeta_in, dgate_in, nullptr, ddo, nullptr, g_q, g_k, g_v,
                     g_b, g_g, nullptr, ws, ws_b, st);
     if (s != MXB_OK) return s;
     MXB_CUDA_TRY(cudaMemcpyAsync(dq, g_q, nk * es, cudaMemcpyDeviceToHost, st));

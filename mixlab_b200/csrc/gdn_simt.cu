@@ -705,18 +705,21 @@ static mxb_status run_fwd(GdnP& p, bool chunked, cudaStream_t st) {
 }
 
 template <typename IO>
-static mxb_status run_bwd(GdnP& p, cudaStream_t st) {
+static mxb_status run_bwd(GdnP& p, bool recompute, cudaStream_t st) {
   const int C = p.C, K = p.K, V = p.V;
   p.save = 1;
-  // forward recompute into the workspace; out is not needed -> write into dv (overwritten later)
-  void* keep_out = p.out;
-  float* keep_hT = p.hT;
-  p.out = p.dv;
-  p.hT = nullptr;
-  mxb_status s = run_fwd<IO>(p, true, st);
-  p.out = keep_out;
-  p.hT = keep_hT;
-  if (s != MXB_OK) return s;
+  mxb_status s = MXB_OK;
+  if (recompute) {
+    // forward recompute into the workspace; out is not needed -> write into dv (overwritten later)
+    void* keep_out = p.out;
+    float* keep_hT = p.hT;
+    p.out = p.dv;
+    p.hT = nullptr;
+    s = run_fwd<IO>(p, true, st);
+    p.out = keep_out;
+    p.hT = keep_hT;
+    if (s != MXB_OK) return s;
+  }
   dim3 gslab((V + 31) / 32, p.B * p.H);
   size_t sm3 = sizeof(float) * (K * 33 + 3 * C * 32 + 2 * C);
   if (set_smem(gdn_state_bwd_kernel<IO>, sm3) != MXB_OK) return MXB_ERR_CUDA;
@@ -737,7 +740,8 @@ mxb_status gdn_simt_fwd(const mxb_gdn_desc* d, const void* q, const void* k, con
   p.q = q; p.k = k; p.v = v; p.beta = beta; p.gate = gate; p.h0 = h0; p.out = out; p.hT = hT;
   const bool chunked = d->chunk > 1;
   if (chunked) {
-    carve(p, ws, false);
+    p.save = (d->flags & MXB_GDN_SAVE_FOR_BWD) ? 1 : 0;
+    carve(p, ws, p.save != 0);
     if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
   }
   return d->io_dtype == MXB_F32 ? run_fwd<float>(p, chunked, st) : run_fwd<__nv_bfloat16>(p, chunked, st);
@@ -752,7 +756,9 @@ mxb_status gdn_simt_bwd(const mxb_gdn_desc* d, const void* q, const void* k, con
   p.dO = dO; p.dhT_in = dhT; p.dq = dq; p.dk = dk; p.dv = dv; p.dbeta = dbeta; p.dgate = dgate; p.dh0 = dh0;
   carve(p, ws, true);
   if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
-  return d->io_dtype == MXB_F32 ? run_bwd<float>(p, st) : run_bwd<__nv_bfloat16>(p, st);
+  // saved intermediates exist only for the chunked forward
+  const bool recompute = !(d->flags & MXB_GDN_BWD_USE_SAVED) || d->chunk <= 1;
+  return d->io_dtype == MXB_F32 ? run_bwd<float>(p, recompute, st) : run_bwd<__nv_bfloat16>(p, recompute, st);
 }
 
 }  // namespace mxb

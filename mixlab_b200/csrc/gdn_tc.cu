@@ -405,7 +405,7 @@ static mxb_status tc_set_smem(KernelT kern, int bytes) {
   return MXB_OK;
 }
 
-mxb_status tc_run_bwd(TcP& p, cudaStream_t st);
+mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st);
 
 mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(p.status, 0, 256, st);
@@ -425,7 +425,8 @@ mxb_status gdn_tc_fwd(const mxb_gdn_desc* d, const void* q, const void* k, const
   TcP p = make_tc(d);
   p.q = static_cast<const bf16*>(q); p.k = static_cast<const bf16*>(k); p.v = static_cast<const bf16*>(v);
   p.beta = beta; p.gate = gate; p.h0 = h0; p.out = static_cast<bf16*>(out); p.hT = hT;
-  carve_tc(p, ws, false);
+  p.save = (d->flags & MXB_GDN_SAVE_FOR_BWD) ? 1 : 0;
+  carve_tc(p, ws, p.save != 0);
   return tc_run_fwd(p, st);
 }
 
@@ -441,7 +442,7 @@ mxb_status gdn_tc_bwd(const mxb_gdn_desc* d, const void* q, const void* k, const
   p.dq = static_cast<bf16*>(dq); p.dk = static_cast<bf16*>(dk); p.dv = static_cast<bf16*>(dv);
   p.dbeta = dbeta; p.dgate = dgate; p.dh0 = dh0;
   carve_tc(p, ws, true);
-  return tc_run_bwd(p, st);
+  return tc_run_bwd(p, !(d->flags & MXB_GDN_BWD_USE_SAVED), st);
 }
 
 }  // namespace mxb

@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(128) gdn_tc_state_bwd_kernel(TcP p) {
 //   [256,384) dkt = v_new dS^T
 //   [384,448) dP                       -> k k^T     } -> [384,512) (dP*Gamma) k -> T^T dv_new
 //   [448,512)                             q k^T     }
-constexpr int kChunkBwdSmem = 49152 + 65536 + 16384 + 4 * 8192 + 8 * C * 4 + 64 + 256;
+constexpr int kChunkBwdSmem = 49152 + 65536 + 16384 + 4 * 8192 + 12 * C * 4 + 64 + 256;
 
 __device__ __forceinline__ void unpack8(uint4 v, float (&e)[8]) {
   tc::unpack_bf16(v.x, e[0], e[1]); tc::unpack_bf16(v.y, e[2], e[3]);
@@ -236,7 +236,8 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   float* dgo = csum + C;            // per-row dgam / dbeta handed over at the end
   float* dbo = dgo + C;
   float* red = dbo + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + C);
+  float* csw = red + C;             // [4 warps][C] per-warp column sums (no atomics)
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(csw + 4 * C);
   uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -260,6 +261,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
     bet[tid] = tid < imax ? p.beta[row(tid)] : 0.f;
     csum[tid] = 0.f;
   }
+  for (int u = tid; u < 4 * C; u += 128) csw[u] = 0.f;
   // ---- phase A staging: dO, dv_new, v_new, S0, dS, T ----
   for (int u = tid; u < 64 * 16; u += 128) {
     const int r = u >> 4, c8 = u & 15;
@@ -379,7 +381,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
     for (int c0 = 0; c0 < 64; c0 += 32) {
       float f[32];
       ld_acc32(taddr + 448, warp, c0, f);  // q k^T: dgam from P
-      if (own) {
+      {
         float rs = 0.f;
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
@@ -388,11 +390,10 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
 #pragma unroll
           for (int y = 0; y < 8; ++y) {
             const int j = c0 + 8 * x + y;
-            if (j <= i) {
-              const float X = e[y] * f[8 * x + y];
-              rs += X;
-              atomicAdd(&csum[j], -X);
-            }
+            const float X = (own && j <= i) ? e[y] * f[8 * x + y] : 0.f;
+            rs += X;
+            const float colsum = warp_sum(X);  // over the 16 rows this warp owns
+            if (lane == 0) csw[warp * C + j] -= colsum;
           }
         }
         dg_own += rs;
@@ -452,22 +453,24 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
     for (int c0 = 0; c0 < 64; c0 += 32) {
       float f[32];
       ld_acc32(taddr + 128, warp, c0, f);
-      if (own) {
+      {
         float rs = 0.f;
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
           const int j = c0 + jj;
-          if (j < i) {
+          float t = 0.f;
+          if (own && j < i) {
             const float M = -f[jj] * exp_nonpos(gi - gam[j]);  // -dA * Gamma
-            const float t = M * KKr[j];
-            rs += t;
-            atomicAdd(&csum[j], -bi * t);
+            t = M * KKr[j];
             const bf16 mb = __float2bfloat16_rn(bi * M);
             ms_at(i, j) = mb;
             ms_at(j, i) = mb;
-          } else if (j == i) {
+          } else if (own && j == i) {
             ms_at(i, i) = __float2bfloat16_rn(0.f);
           }
+          rs += t;
+          const float colsum = warp_sum(bi * t);
+          if (lane == 0) csw[warp * C + j] -= colsum;
         }
         db_own += rs;
         dg_own += bi * rs;
@@ -510,10 +513,11 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
       ld_acc32(taddr + 256, warp, c0, f);   // dkt
       if (own) kdot += row_dot32(Xk, i, c0, f);
     }
-    if (own) {
-      const float rho = ri * kdot;
-      dg_own += di * qdot - rho;
-      atomicAdd(&csum[C - 1], rho);
+    {
+      const float rho = own ? ri * kdot : 0.f;
+      if (own) dg_own += di * qdot - rho;
+      const float tot = warp_sum(rho);
+      if (lane == 0) atomicAdd(&csum[C - 1], tot);
     }
   }
   tc::fence_before_sync();
@@ -582,7 +586,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   if (tid == 0) {  // dg = reverse cumulative sum of dgam within the chunk
     float acc = L * (red[0] + red[1] + red[2] + red[3]);  // d/dgam_last of E(gam_last) <dS, S0>
     for (int r = C - 1; r >= 0; --r) {
-      acc += dgo[r] + csum[r];
+      acc += dgo[r] + csum[r] + csw[r] + csw[C + r] + csw[2 * C + r] + csw[3 * C + r];
       dgo[r] = acc;
     }
   }
@@ -613,16 +617,19 @@ static mxb_status bwd_set_smem(KernelT kern, int bytes) {
 }
 
 // Forward recompute (saving per-chunk states and v_new), reverse state pass, per-chunk pass.
-mxb_status tc_run_bwd(TcP& p, cudaStream_t st) {
+mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
   p.save = 1;
-  bf16* keep_out = p.out;
-  float* keep_hT = p.hT;
-  p.out = p.dv;  // the recomputed forward output is not needed; dv is overwritten afterwards
-  p.hT = nullptr;
-  mxb_status s = tc_run_fwd(p, st);
-  p.out = keep_out;
-  p.hT = keep_hT;
-  if (s != MXB_OK) return s;
+  mxb_status s = MXB_OK;
+  if (recompute) {
+    bf16* keep_out = p.out;
+    float* keep_hT = p.hT;
+    p.out = p.dv;  // the recomputed forward output is not needed; dv is overwritten afterwards
+    p.hT = nullptr;
+    s = tc_run_fwd(p, st);
+    p.out = keep_out;
+    p.hT = keep_hT;
+    if (s != MXB_OK) return s;
+  }
   if (bwd_set_smem(gdn_tc_state_bwd_kernel, kStateBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("gdn_tc_state_bwd_kernel", st,
              (gdn_tc_state_bwd_kernel<<<dim3(KD / VS, p.B * p.H), 128, kStateBwdSmem, st>>>(p)));

@@ -69,8 +69,12 @@ def gdn_desc(q, v, chunk, gate_is_log, flags=0) -> GdnDesc:
 
 
 def gated_delta_scan(q, k, v, beta, gate, chunk=64, *, gate_is_log=False, h0=None,
-                     return_final_state=False, flags=0):
-    """Forward.  Returns out [B,T,H,Dv] (and the final state [B,H,Dk,Dv] fp32)."""
+                     return_final_state=False, flags=0, save_for_backward=False):
+    """Forward.  Returns out [B,T,H,Dv] (and the final state [B,H,Dk,Dv] fp32).
+    ``save_for_backward`` keeps the forward intermediates in the cached workspace for a
+    following ``gated_delta_scan_backward(..., use_saved=True)`` on the same inputs."""
+    if save_for_backward:
+        flags |= _lib.MXB_GDN_SAVE_FOR_BWD
     _require_cuda(q, k, v, beta, gate, h0)
     l = _lib.lib()
     d = gdn_desc(q, v, chunk, gate_is_log, flags)
@@ -85,8 +89,10 @@ def gated_delta_scan(q, k, v, beta, gate, chunk=64, *, gate_is_log=False, h0=Non
 
 
 def gated_delta_scan_backward(q, k, v, beta, gate, d_out, chunk=64, *, gate_is_log=False, h0=None,
-                              d_final_state=None, flags=0):
+                              d_final_state=None, flags=0, use_saved=False):
     """All gradients.  Returns dict(dq, dk, dv, dbeta, dgate, dh0)."""
+    if use_saved:
+        flags |= _lib.MXB_GDN_BWD_USE_SAVED
     _require_cuda(q, k, v, beta, gate, d_out, h0, d_final_state)
     l = _lib.lib()
     d = gdn_desc(q, v, chunk, gate_is_log, flags)

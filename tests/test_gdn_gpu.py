@@ -267,3 +267,20 @@ def test_tensor_core_backward_matches_fp32_kernels():
     g_32 = ops.gated_delta_scan_backward(*args, gate_is_log=True, flags=_lib.MXB_GDN_BWD_FP32_KERNELS)
     for name in ("dq", "dk", "dv", "dbeta", "dgate"):
         assert_close(g_tc[name], g_32[name].float(), TOL_BF16, name)
+
+
+@pytest.mark.parametrize("case", [(2, 200, 2, 128, 128, torch.bfloat16), (1, 130, 2, 32, 20, torch.float32)])
+def test_backward_from_saved_forward(case):
+    """Forward with save_for_backward + backward with use_saved == backward with its own recompute."""
+    B, T, H, K, V, io = case
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=31, io_dtype=io, with_grad_out=True, with_h0=True)
+    args = (_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]))
+    kw = dict(gate_is_log=True, h0=_dev(a["h0"]))
+    ref = ops.gated_delta_scan_backward(*args, _dev(a["d_out"]), 64, d_final_state=_dev(a["d_state"]), **kw)
+    o_plain = ops.gated_delta_scan(*args, 64, **kw)
+    o = ops.gated_delta_scan(*args, 64, save_for_backward=True, **kw)
+    got = ops.gated_delta_scan_backward(*args, _dev(a["d_out"]), 64, d_final_state=_dev(a["d_state"]),
+                                        use_saved=True, **kw)
+    assert torch.equal(o, o_plain)
+    for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
+        assert torch.equal(got[name], ref[name]), name
