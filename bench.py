@@ -159,6 +159,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--fp32-path", action="store_true", help="force the CUDA-core fp32 kernels")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the per-GPU batch (sequences) - small cases for profiler captures only")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -187,7 +189,9 @@ def main():
     flags = _lib.MXB_GDN_FORCE_FP32_PATH if args.fp32_path else 0
     e2e = None
     if args.workload == "gdn_train":
-        w = WORKLOADS["gdn_train"]
+        w = dict(WORKLOADS["gdn_train"])
+        if args.batch > 0:
+            w["B"] = args.batch
         B, T, H, K, V, Cc = w["B"], w["T"], w["H"], w["Dk"], w["Dv"], w["chunk"]
         # seeded inputs, generated one sequence at a time to bound host memory
         parts = [inputs.gdn_inputs(1, T, H, K, V, seed=1000 * (rank + 1) + b, io_dtype=torch.bfloat16,
@@ -210,7 +214,9 @@ def main():
                "parallelism": f"batch-sharded x{world}, no collective",
                "l2": "inputs (q,k,v,dO = 4 x 134 MB) exceed the 126 MB L2"}
     elif args.workload == "gdn_decode":
-        w = WORKLOADS["gdn_decode"]
+        w = dict(WORKLOADS["gdn_decode"])
+        if args.batch > 0:
+            w["N"] = args.batch
         N, H, K, V, tps = w["N"], w["H"], w["Dk"], w["Dv"], w["tokens_per_step"]
         a = inputs.gdn_decode_inputs(N, H, K, V, 16, seed=2 + rank, io_dtype=torch.bfloat16)
         d = {k: v.to(dev) for k, v in a.items()}
@@ -231,7 +237,9 @@ def main():
         cfg = {"workload": "gdn_decode", **w, "io": "bf16", "state": "fp32 268 MB (exceeds L2)",
                "inputs": "ring of 16 pre-generated token inputs"}
     else:
-        w = WORKLOADS["mamba3_train"]
+        w = dict(WORKLOADS["mamba3_train"])
+        if args.batch > 0:
+            w["B"] = args.batch
         B, T, NH, P, N, G = w["B"], w["T"], w["nheads"], w["headdim"], w["N"], w["G"]
         parts = [inputs.mamba3_inputs(1, T, NH, P, N, G=G, seed=3000 * (rank + 1) + b, io_dtype=torch.bfloat16)
                  for b in range(B)]
