@@ -176,7 +176,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     import mixlab_b200
-    from mixlab_b200 import ops, _lib
+    from mixlab_b200 import ops, _lib, sharding
     from oracle import inputs  # seeded input generators only (no compute)
     lib = mixlab_b200.lib()
     pk = peaks()
@@ -283,10 +283,7 @@ def main():
     lib.mxb_trace_summary(buf, len(buf))
     lib.mxb_trace_enable(0)
     clocks = sampler.stop(t_wall0, t_wall1)
-    if world > 1:
-        tms = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
-        ms = tms.item()
+    ms = sharding.max_over_ranks(ms, dev)
     kernels = {}
     for line in buf.value.decode().splitlines():
         name, cnt, tot = line.split()
@@ -298,7 +295,7 @@ def main():
     top = max(kernels, key=lambda n: kernels[n]["total_ms"]) if kernels else None
 
     ms_step = ms / args.steps
-    value = world * units / (ms_step * 1e-3)
+    value = sharding.whole_job_rate(units, world, ms_step * 1e-3)
     # roofline of the step, taken as one launch: algorithmic bytes / summed kernel time
     kern_ms_step = ksum / args.steps
     achieved = alg_bytes / (kern_ms_step * 1e-3) / 1e9
@@ -337,10 +334,7 @@ def main():
                 host_step()  # blocking: H2D + kernels + D2H + stream sync
             barrier()
             dt = (time.perf_counter() - t0) / nst
-            if world > 1:
-                tt = torch.tensor([dt], dtype=torch.float64, device=dev)
-                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-                dt = tt.item()
+            dt = sharding.max_over_ranks(dt, dev)
             lib.mxb_host_ctx_destroy(ctx)
             h2d = sum(host[k].numel() * host[k].element_size() for k in ("q", "k", "v", "beta", "g", "d_out"))
             d2h = sum(t.numel() * t.element_size() for t in res.values())

@@ -13,6 +13,7 @@ MXB_GDN_FORCE_FP32_PATH = 1
 MXB_GDN_BWD_FP32_KERNELS = 2
 MXB_GDN_SAVE_FOR_BWD = 4
 MXB_GDN_BWD_USE_SAVED = 8
+MXB_GDN_DECODE_REGISTER_KERNEL = 16
 
 
 class MxbError(RuntimeError):

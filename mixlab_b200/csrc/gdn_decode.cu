@@ -119,10 +119,16 @@ static mxb_status launch_decode(const mxb_gdn_desc* d, float* state, const void*
   return check_launch("gdn_decode_kernel");
 }
 
+bool gdn_decode_bulk_supported(const mxb_gdn_desc* d);
+mxb_status gdn_decode_bulk_dispatch(const mxb_gdn_desc*, float*, const void*, const void*, const void*, const float*,
+                                    const float*, void*, cudaStream_t);
+
 mxb_status gdn_decode_dispatch(const mxb_gdn_desc* d, float* state, const void* q, const void* k,
                                const void* v, const float* beta, const float* gate, void* out,
                                cudaStream_t st) {
   if (d->Dv % 4 != 0 || d->Dk > 256) return MXB_ERR_UNSUPPORTED;
+  if (!(d->flags & MXB_GDN_DECODE_REGISTER_KERNEL) && gdn_decode_bulk_supported(d))
+    return gdn_decode_bulk_dispatch(d, state, q, k, v, beta, gate, out, st);
   if (d->io_dtype == MXB_F32) return launch_decode<float>(d, state, q, k, v, beta, gate, out, st);
   return launch_decode<__nv_bfloat16>(d, state, q, k, v, beta, gate, out, st);
 }

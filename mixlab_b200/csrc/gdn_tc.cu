@@ -18,15 +18,20 @@
 namespace mxb {
 
 // ------------------------------------------------------------------ prep
-constexpr int kPrepSmem = 32768 + 32768 + 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 128;
+// u = T (v beta) and w = T (k beta E(gam)) are evaluated as (T diag(beta)) v and
+// (T diag(beta E(gam))) k: the scaling goes into two column-scaled bf16 copies of T written
+// straight from the solve's registers, so k, q and v are staged raw with cp.async.
+constexpr int kPrepSmem = 32768 + 16384 + 3 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 128;
 
 __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
-  uint8_t* Akq = sm;                    // K-major [128: k rows 0-63, q rows 64-127][128]
-  uint8_t* Bvk = Akq + 32768;           // MN-major [64 m][256: v beta | k beta E(gam)]
-  uint8_t* Tt = Bvk + 32768;            // K-major [64 i][64 m]
-  float* Am = reinterpret_cast<float*>(Tt + 8192);  // [64][LDA]
+  uint8_t* Akq = sm;                    // [128: k rows 0-63, q rows 64-127][128]
+  uint8_t* Vt = Akq + 32768;            // [64 m][128]  v
+  uint8_t* Tt = Vt + 16384;             // [64 i][64 m] T
+  uint8_t* Tb = Tt + 8192;              // [64 i][64 m] T diag(beta)
+  uint8_t* Tbd = Tb + 8192;             // [64 i][64 m] T diag(beta E(gam))
+  float* Am = reinterpret_cast<float*>(Tbd + 8192);  // [64][LDA]
   float* gam = Am + C * LDA;
   float* bet = gam + C;
   float* bd = bet + C;
@@ -39,6 +44,22 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
   auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
   const int imax = min(C, p.T - t0);
 
+  {  // group 0: [k;q]   group 1: v
+    const uint32_t sa = tc::smem_u32(Akq), sv = tc::smem_u32(Vt);
+    for (int u = tid; u < 128 * 16; u += 128) {
+      const int r = u >> 4, c8 = u & 15, i = r & 63;
+      const bool ok = i < imax;
+      const bf16* src = r < 64 ? p.k : p.q;
+      tc::cp_async16(sa + tc::kmajor_unit(r, c8, KD), ok ? src + row(i) * KD + c8 * 8 : src, ok);
+    }
+    tc::cp_async_commit();
+    for (int u = tid; u < 64 * 16; u += 128) {
+      const int i = u >> 4, c8 = u & 15;
+      const bool ok = i < imax;
+      tc::cp_async16(sv + tc::kmajor_unit(i, c8, KD), ok ? p.v + row(i) * KD + c8 * 8 : p.v, ok);
+    }
+    tc::cp_async_commit();
+  }
   if (warp == 0) {
     tc::tmem_alloc(tslot, 256);
     tc::tmem_relinquish();
@@ -47,39 +68,25 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
     tc::mbar_init(mbar, 1);
     tc::mbar_fence_init();
   }
-  if (tid < C) {
-    const bool ok = tid < imax;
-    bet[tid] = ok ? p.beta[row(tid)] : 0.f;
-    gam[tid] = ok ? log_gate_tc(p.gate[row(tid)], p.gate_is_log) : 0.f;
-  }
-  // stage [k;q] (K-major)
-  for (int u = tid; u < 128 * 16; u += 128) {
-    const int r = u >> 4, c8 = u & 15, i = r & 63;
-    uint4 val = zero16();
-    if (i < imax) val = ldg16((r < 64 ? p.k : p.q) + row(i) * KD + c8 * 8);
-    sts16(Akq, tc::kmajor_unit(r, c8, KD), val);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    float acc = 0.f;
-    for (int i = 0; i < C; ++i) { acc += gam[i]; gam[i] = acc; }
-  }
-  __syncthreads();
-  if (tid < C) {
-    bd[tid] = bet[tid] * exp_nonpos(gam[tid]);
-    p.gam[ci * C + tid] = gam[tid];
-  }
-  __syncthreads();
-  // stage [v beta | k beta E(gam)] (MN-major, contraction over the chunk row m)
-  for (int u = tid; u < 64 * 32; u += 128) {
-    const int m = u >> 5, c8 = u & 31;
-    uint4 val = zero16();
-    if (m < imax) {
-      if (c8 < 16) val = tc::scale_bf16x8(ldg16(p.v + row(m) * KD + c8 * 8), bet[m]);
-      else val = tc::scale_bf16x8(ldg16(p.k + row(m) * KD + (c8 - 16) * 8), bd[m]);
+  if (warp == 1) {  // in-chunk inclusive cumulative sum of the log gate: two elements per lane
+    const bool ok0 = 2 * lane < imax, ok1 = 2 * lane + 1 < imax;
+    const float g0 = ok0 ? log_gate_tc(p.gate[row(2 * lane)], p.gate_is_log) : 0.f;
+    const float g1 = ok1 ? log_gate_tc(p.gate[row(2 * lane + 1)], p.gate_is_log) : 0.f;
+    float s = g0 + g1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += t;
     }
-    sts16(Bvk, tc::mnmajor_unit(m, c8, 256), val);
+    const float c1 = s, c0 = s - g1;
+    const float b0 = ok0 ? p.beta[row(2 * lane)] : 0.f, b1 = ok1 ? p.beta[row(2 * lane + 1)] : 0.f;
+    gam[2 * lane] = c0; gam[2 * lane + 1] = c1;
+    bet[2 * lane] = b0; bet[2 * lane + 1] = b1;
+    bd[2 * lane] = b0 * exp_nonpos(c0); bd[2 * lane + 1] = b1 * exp_nonpos(c1);
+    p.gam[ci * C + 2 * lane] = c0;
+    p.gam[ci * C + 2 * lane + 1] = c1;
   }
+  tc::cp_async_wait<1>();  // [k;q]
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -134,17 +141,24 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
       for (int j = 0; j < i; ++j) s = fmaf(Am[i * LDA + j], Tc[j], s);
       Tc[i] = (i < tid) ? 0.f : s;
     }
+    const float bm = bet[tid], bdm = bd[tid];
 #pragma unroll
-    for (int i = 0; i < C; ++i)
-      *reinterpret_cast<bf16*>(Tt + tc::kmajor_unit(i, tid >> 3, C) + (tid & 7) * 2) = __float2bfloat16_rn(Tc[i]);
+    for (int i = 0; i < C; ++i) {
+      const uint32_t off = tc::kmajor_unit(i, tid >> 3, C) + (tid & 7) * 2;
+      *reinterpret_cast<bf16*>(Tt + off) = __float2bfloat16_rn(Tc[i]);
+      *reinterpret_cast<bf16*>(Tb + off) = __float2bfloat16_rn(Tc[i] * bm);
+      *reinterpret_cast<bf16*>(Tbd + off) = __float2bfloat16_rn(Tc[i] * bdm);
+    }
   }
+  tc::cp_async_wait<0>();  // v
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  // D1[64 x 256] = T [v beta | k beta E(gam)]  -> u | w
+  // D1[64 x 256] = [ (T beta) v | (T beta d) k ]  -> u | w     (v, k contracted over their rows)
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr, tc::kmajor_tile(Tt, C), tc::mnmajor_tile(Bvk, 256), 64, 256, C, false);
+    tc::issue_gemm(taddr, tc::kmajor_tile(Tb, C), tc::mnmajor_tile(Vt, KD), 64, KD, C, false);
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Tbd, C), tc::mnmajor_tile(Akq, KD), 64, KD, C, false);
     tc::mma_commit(mbar);
   }
   // T -> workspace (bf16, row-major) while the MMA runs
@@ -178,47 +192,99 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
 }
 
 // ------------------------------------------------------------ state forward
-constexpr int kStateFwdSmem = 32768 + 16384 + 16384 + 8192 + 8192 + 16384 + 2 * C * 4 + 64 + 128;
+// One CTA (256 threads) per (batch, head).  Thread t owns state row kk = t & 127 and the
+// 64 columns of half t >> 7.  The operands of chunk c+1 are fetched with cp.async as soon
+// as the MMA that last read the buffer for chunk c has completed, so their latency hides
+// behind the epilogues and MMAs of chunk c:
+//   group A  [w;q]      buffer free after MMA1      needed before MMA1 of the next chunk
+//   group U  u          free after epilogue 1       needed before epilogue 1
+//   group PK P and k    free after MMA2/MMA3        needed before MMA2/MMA3
+// Exactly three groups are outstanding at the top of every chunk, in the order A, U, PK.
+constexpr int kStateFwdSmem = 32768 + 32768 + 16384 + 16384 + 16384 + 16384 + 16384 + 2 * C * 4 + 64 + 128;
 
-__global__ void __launch_bounds__(128) gdn_tc_state_fwd_kernel(TcP p) {
+__global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
-  uint8_t* A1 = sm;                 // K-major [128: w rows 0-63, q rows 64-127][128 kk]
-  uint8_t* Sop = A1 + 32768;        // MN-major [128 kk][64 j]   bf16 copy of the state
-  uint8_t* A2 = Sop + 16384;        // K-major [128: zero rows 0-63, P rows 64-127][64 m]
-  uint8_t* Vn = A2 + 16384;         // MN-major [64 i][64 j]     v_new
-  uint8_t* Vr = Vn + 8192;          // MN-major [64 i][64 j]     E(gam_last-gam_i) v_new
-  uint8_t* A3 = Vr + 8192;          // MN-major [64 i][128 kk]   k  (A = k^T)
-  float* dd = reinterpret_cast<float*>(A3 + 16384);
+  uint8_t* A1 = sm;                 // [128: w rows 0-63, q rows 64-127][128 kk]
+  uint8_t* Sop = A1 + 32768;        // [128 kk][128 j]   bf16 copy of the state
+  uint8_t* A2 = Sop + 32768;        // [128: zero rows 0-63, P rows 64-127][64 m]
+  uint8_t* Vn = A2 + 16384;         // [64 i][128 j]     v_new
+  uint8_t* Vr = Vn + 16384;         // [64 i][128 j]     E(gam_last-gam_i) v_new
+  uint8_t* A3 = Vr + 16384;         // [64 i][128 kk]    k  (A = k^T)
+  uint8_t* Ut = A3 + 16384;         // [64 i][128 j]     u
+  float* dd = reinterpret_cast<float*>(Ut + 16384);
   float* rr = dd + C;
   uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);
   uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-  const int jv0 = blockIdx.x * VS;
+  const int kk = tid & 127, half = tid >> 7, j0 = 64 * half;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const uint32_t sA1 = tc::smem_u32(A1), sA2 = tc::smem_u32(A2), sA3 = tc::smem_u32(A3), sU = tc::smem_u32(Ut);
+
+  auto grow = [&](int c, int i) { return ((size_t)(b * p.T + c * C + i) * p.H + h); };
+  auto issue_A = [&](int c) {  // [w;q] of chunk c
+    if (c < p.n) {
+      const size_t ci = (size_t)bh * p.n + c;
+      const int imax = min(C, p.T - c * C);
+      for (int u = tid; u < 128 * 16; u += 256) {
+        const int r = u >> 4, c8 = u & 15, i = r & 63;
+        if (r < 64) tc::cp_async16(sA1 + tc::kmajor_unit(r, c8, KD), p.w + (ci * C + i) * KD + c8 * 8);
+        else tc::cp_async16(sA1 + tc::kmajor_unit(r, c8, KD), i < imax ? p.q + grow(c, i) * KD + c8 * 8 : p.q, i < imax);
+      }
+    }
+    tc::cp_async_commit();
+  };
+  auto issue_U = [&](int c) {
+    if (c < p.n) {
+      const size_t ci = (size_t)bh * p.n + c;
+      for (int u = tid; u < 64 * 16; u += 256) {
+        const int i = u >> 4, c8 = u & 15;
+        tc::cp_async16(sU + tc::kmajor_unit(i, c8, KD), p.u + (ci * C + i) * KD + c8 * 8);
+      }
+    }
+    tc::cp_async_commit();
+  };
+  auto issue_PK = [&](int c) {
+    if (c < p.n) {
+      const size_t ci = (size_t)bh * p.n + c;
+      const int imax = min(C, p.T - c * C);
+      for (int u = tid; u < 64 * 8; u += 256) {
+        const int i = u >> 3, c8 = u & 7;
+        tc::cp_async16(sA2 + tc::kmajor_unit(64 + i, c8, C), p.P + (ci * C + i) * C + c8 * 8);
+      }
+      for (int u = tid; u < 64 * 16; u += 256) {
+        const int i = u >> 4, c8 = u & 15;
+        tc::cp_async16(sA3 + tc::kmajor_unit(i, c8, KD), i < imax ? p.k + grow(c, i) * KD + c8 * 8 : p.k, i < imax);
+      }
+    }
+    tc::cp_async_commit();
+  };
 
   if (warp == 0) {
-    tc::tmem_alloc(tslot, 256);
+    tc::tmem_alloc(tslot, 512);
     tc::tmem_relinquish();
   }
   if (tid == 0) {
     tc::mbar_init(mbar, 1);
     tc::mbar_fence_init();
   }
-  float S[VS];  // state row kk = tid, columns jv0 .. jv0+63
+  issue_A(0);
+  issue_U(0);
+  issue_PK(0);
+  float S[64];  // state row kk, columns j0 .. j0+63
   if (p.h0) {
-    const float4* src = reinterpret_cast<const float4*>(p.h0 + ((size_t)bh * KD + tid) * KD + jv0);
+    const float4* src = reinterpret_cast<const float4*>(p.h0 + ((size_t)bh * KD + kk) * KD + j0);
 #pragma unroll
-    for (int x = 0; x < VS / 4; ++x) {
+    for (int x = 0; x < 16; ++x) {
       const float4 t4 = __ldg(src + x);
       S[4 * x] = t4.x; S[4 * x + 1] = t4.y; S[4 * x + 2] = t4.z; S[4 * x + 3] = t4.w;
     }
   } else {
 #pragma unroll
-    for (int x = 0; x < VS; ++x) S[x] = 0.f;
+    for (int x = 0; x < 64; ++x) S[x] = 0.f;
   }
-  for (int u = tid; u < 64 * 8; u += 128) sts16(A2, tc::kmajor_unit(u >> 3, u & 7, C), zero16());
+  for (int u = tid; u < 64 * 8; u += 256) sts16(A2, tc::kmajor_unit(u >> 3, u & 7, C), zero16());
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -229,7 +295,6 @@ __global__ void __launch_bounds__(128) gdn_tc_state_fwd_kernel(TcP p) {
   for (int c = 0; c < p.n && ok; ++c) {
     const size_t ci = (size_t)bh * p.n + c;
     const int t0 = c * C, imax = min(C, p.T - t0);
-    auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
     const float* gam = p.gam + ci * C;
     const float glast = gam[C - 1];
     const float L = exp_nonpos(glast);
@@ -238,52 +303,40 @@ __global__ void __launch_bounds__(128) gdn_tc_state_fwd_kernel(TcP p) {
       dd[tid] = exp_nonpos(g);
       rr[tid] = exp_nonpos(glast - g);
     }
-    // state as the MMA operand (and saved for the backward)
 #pragma unroll
-    for (int c8 = 0; c8 < VS / 8; ++c8) {
+    for (int c8 = 0; c8 < 8; ++c8) {  // state as the MMA operand (and saved for the backward)
       const uint4 val = make_uint4(tc::pack_bf16(S[8 * c8], S[8 * c8 + 1]), tc::pack_bf16(S[8 * c8 + 2], S[8 * c8 + 3]),
                                    tc::pack_bf16(S[8 * c8 + 4], S[8 * c8 + 5]), tc::pack_bf16(S[8 * c8 + 6], S[8 * c8 + 7]));
-      sts16(Sop, tc::mnmajor_unit(tid, c8, VS), val);
-      if (p.save) *reinterpret_cast<uint4*>(p.hs + (ci * KD + tid) * KD + jv0 + c8 * 8) = val;
+      sts16(Sop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
+      if (p.save) *reinterpret_cast<uint4*>(p.hs + (ci * KD + kk) * KD + j0 + c8 * 8) = val;
     }
-    for (int u = tid; u < 128 * 16; u += 128) {  // [w;q]
-      const int r = u >> 4, c8 = u & 15, i = r & 63;
-      uint4 val = zero16();
-      if (r < 64) val = ldg16(p.w + (ci * C + i) * KD + c8 * 8);
-      else if (i < imax) val = ldg16(p.q + row(i) * KD + c8 * 8);
-      sts16(A1, tc::kmajor_unit(r, c8, KD), val);
-    }
-    for (int u = tid; u < 64 * 16; u += 128) {   // k (A = k^T, contraction over the chunk row)
-      const int i = u >> 4, c8 = u & 15;
-      sts16(A3, tc::mnmajor_unit(i, c8, KD), i < imax ? ldg16(p.k + row(i) * KD + c8 * 8) : zero16());
-    }
-    for (int u = tid; u < 64 * 8; u += 128) {    // P into rows 64..127
-      const int i = u >> 3, c8 = u & 7;
-      sts16(A2, tc::kmajor_unit(64 + i, c8, C), ldg16(p.P + (ci * C + i) * C + c8 * 8));
-    }
+    tc::cp_async_wait<2>();  // group A of this chunk has landed
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     if (tid == 0) {  // D1 = [w;q] S
-      tc::issue_gemm(taddr, tc::kmajor_tile(A1, KD), tc::mnmajor_tile(Sop, VS), 128, VS, KD, false);
+      tc::issue_gemm(taddr, tc::kmajor_tile(A1, KD), tc::mnmajor_tile(Sop, KD), 128, KD, KD, false);
       tc::mma_commit(mbar);
     }
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
-    float qs[VS];
+    issue_A(c + 1);
+    tc::cp_async_wait<2>();  // group U of this chunk
+    __syncthreads();
+    float qs[64];
     if (ok) {
-      const int i = tid & 63;
-      for (int c0 = 0; c0 < VS; c0 += 32) {
+      const int i = kk & 63;
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         float f[32];
-        ld_acc32(taddr, warp, c0, f);
-        if (tid < 64) {  // v_new = u - w S
+        ld_acc32(taddr + j0, warp, c0, f);
+        if (kk < 64) {  // v_new = u - w S
           const float ri = rr[i];
-          const uint4* usrc = reinterpret_cast<const uint4*>(p.u + (ci * C + i) * KD + jv0 + c0);
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
-            const uint4 uu = __ldg(usrc + x);
+            const int c8 = 8 * half + (c0 >> 3) + x;
+            const uint4 uu = *reinterpret_cast<const uint4*>(Ut + tc::kmajor_unit(i, c8, KD));
             float e[8];
             tc::unpack_bf16(uu.x, e[0], e[1]); tc::unpack_bf16(uu.y, e[2], e[3]);
             tc::unpack_bf16(uu.z, e[4], e[5]); tc::unpack_bf16(uu.w, e[6], e[7]);
@@ -291,26 +344,27 @@ __global__ void __launch_bounds__(128) gdn_tc_state_fwd_kernel(TcP p) {
             for (int y = 0; y < 8; ++y) e[y] -= f[8 * x + y];
             const uint4 vv = make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
                                         tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7]));
-            const int c8 = (c0 >> 3) + x;
-            sts16(Vn, tc::mnmajor_unit(i, c8, VS), vv);
-            sts16(Vr, tc::mnmajor_unit(i, c8, VS), tc::scale_bf16x8(vv, ri));
-            if (p.save) *reinterpret_cast<uint4*>(p.vn + (ci * C + i) * KD + jv0 + c0 + 8 * x) = vv;
+            sts16(Vn, tc::mnmajor_unit(i, c8, KD), vv);
+            sts16(Vr, tc::mnmajor_unit(i, c8, KD), tc::scale_bf16x8(vv, ri));
+            if (p.save) *reinterpret_cast<uint4*>(p.vn + (ci * C + i) * KD + c8 * 8) = vv;
           }
-        } else {         // E(gam_i) (q S), kept until P v_new arrives
+        } else {        // E(gam_i) (q S), kept until P v_new arrives
           const float di = dd[i];
 #pragma unroll
           for (int jj = 0; jj < 32; ++jj) qs[c0 + jj] = di * f[jj];
         }
       }
     }
+    tc::cp_async_wait<1>();  // group PK of this chunk (group A of the next one may still fly)
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
+    issue_U(c + 1);  // u has been consumed by every thread
     if (ok && tid == 0) {
       // D2 = [0;P] v_new          D3 = k^T (r v_new)
-      tc::issue_gemm(taddr + 64, tc::kmajor_tile(A2, C), tc::mnmajor_tile(Vn, VS), 128, VS, C, false);
-      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(A3, KD), tc::mnmajor_tile(Vr, VS), 128, VS, C, false);
+      tc::issue_gemm(taddr + 128, tc::kmajor_tile(A2, C), tc::mnmajor_tile(Vn, KD), 128, KD, C, false);
+      tc::issue_gemm(taddr + 256, tc::mnmajor_tile(A3, KD), tc::mnmajor_tile(Vr, KD), 128, KD, C, false);
       tc::mma_commit(mbar);
     }
     if (ok) {
@@ -318,14 +372,15 @@ __global__ void __launch_bounds__(128) gdn_tc_state_fwd_kernel(TcP p) {
       ph ^= 1;
     }
     tc::fence_after_sync();
+    issue_PK(c + 1);
     if (ok) {
-      const int i = tid & 63;
-      for (int c0 = 0; c0 < VS; c0 += 32) {
+      const int i = kk & 63;
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         float f[32];
-        if (warp >= 2) {  // out = E(gam)(q S) + P v_new
-          ld_acc32(taddr + 64, warp, c0, f);
+        if (kk >= 64) {  // out = E(gam)(q S) + P v_new      (warp-uniform branch)
+          ld_acc32(taddr + 128 + j0, warp, c0, f);
           if (i < imax) {
-            uint4* dst = reinterpret_cast<uint4*>(p.out + row(i) * KD + jv0 + c0);
+            uint4* dst = reinterpret_cast<uint4*>(p.out + grow(c, i) * KD + j0 + c0);
 #pragma unroll
             for (int x = 0; x < 4; ++x)
               dst[x] = make_uint4(tc::pack_bf16(qs[c0 + 8 * x] + f[8 * x], qs[c0 + 8 * x + 1] + f[8 * x + 1]),
@@ -334,24 +389,23 @@ __global__ void __launch_bounds__(128) gdn_tc_state_fwd_kernel(TcP p) {
                                   tc::pack_bf16(qs[c0 + 8 * x + 6] + f[8 * x + 6], qs[c0 + 8 * x + 7] + f[8 * x + 7]));
           }
         }
-        ld_acc32(taddr + 128, warp, c0, f);  // S <- E(gam_last) S + k^T (r v_new)
+        ld_acc32(taddr + 256 + j0, warp, c0, f);  // S <- E(gam_last) S + k^T (r v_new)
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) S[c0 + jj] = fmaf(L, S[c0 + jj], f[jj]);
       }
     }
     tc::fence_before_sync();
-    __syncthreads();
-    tc::fence_after_sync();
   }
+  tc::cp_async_wait<0>();
   if (!ok && tid == 0) atomicExch(p.status, 2);
   if (ok && p.hT) {
-    float4* dst = reinterpret_cast<float4*>(p.hT + ((size_t)bh * KD + tid) * KD + jv0);
+    float4* dst = reinterpret_cast<float4*>(p.hT + ((size_t)bh * KD + kk) * KD + j0);
 #pragma unroll
-    for (int x = 0; x < VS / 4; ++x) dst[x] = make_float4(S[4 * x], S[4 * x + 1], S[4 * x + 2], S[4 * x + 3]);
+    for (int x = 0; x < 16; ++x) dst[x] = make_float4(S[4 * x], S[4 * x + 1], S[4 * x + 2], S[4 * x + 3]);
   }
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+  if (warp == 0) tc::tmem_dealloc(taddr, 512);
 }
 
 // ------------------------------------------------------------------ host
@@ -416,7 +470,7 @@ mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
   if (s != MXB_OK) return s;
   if (tc_set_smem(gdn_tc_state_fwd_kernel, kStateFwdSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("gdn_tc_state_fwd_kernel", st,
-             (gdn_tc_state_fwd_kernel<<<dim3(KD / VS, p.B * p.H), 128, kStateFwdSmem, st>>>(p)));
+             (gdn_tc_state_fwd_kernel<<<dim3(p.B * p.H), 256, kStateFwdSmem, st>>>(p)));
   return check_launch("gdn_tc_state_fwd_kernel");
 }
 

@@ -23,45 +23,84 @@
 
 namespace mxb {
 
-constexpr int kStateBwdSmem = 16384 + 16384 + 8192 + 8192 + 32768 + 16384 + 2 * C * 4 + 64 + 128;
+// One CTA (256 threads) per (batch, head); thread t owns row kk = t & 127 of dS and the 64
+// columns of half t >> 7.  cp.async prefetch of the next (earlier) chunk:
+//   group A  k, P, dO, q   buffers free after the first MMA batch
+//   group B  w             free after the second MMA batch
+// Two groups are outstanding at the top of every chunk, in the order A, B.
+constexpr int kStateBwdSmem = 16384 + 32768 + 8192 + 16384 + 32768 + 32768 + 2 * C * 4 + 64 + 128;
 
-__global__ void __launch_bounds__(128) gdn_tc_state_bwd_kernel(TcP p) {
+__global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
   uint8_t* Ak = sm;                 // [64 i][128 kk]      k
-  uint8_t* dSop = Ak + 16384;       // [128 kk][64 j]      bf16 copy of dS
-  uint8_t* Pt = dSop + 16384;       // [64 m][64 i]        P   (A = P^T: contraction over rows)
-  uint8_t* dOop = Pt + 8192;        // [64 m][64 j]        dO slab
-  uint8_t* Aqw = dOop + 8192;       // [128: q rows, w rows][128 kk]   (A = [q^T | w^T])
-  uint8_t* Bdd = Aqw + 32768;       // [128: d dO rows, -dv_new rows][64 j]
-  float* dd = reinterpret_cast<float*>(Bdd + 16384);
+  uint8_t* dSop = Ak + 16384;       // [128 kk][128 j]     bf16 copy of dS
+  uint8_t* Pt = dSop + 32768;       // [64 m][64 i]        P   (A = P^T: contraction over rows)
+  uint8_t* dOop = Pt + 8192;        // [64 m][128 j]       dO
+  uint8_t* Aqw = dOop + 16384;      // [128: q rows, w rows][128 kk]   (A = [q^T | w^T])
+  uint8_t* Bdd = Aqw + 32768;       // [128: d dO rows, -dv_new rows][128 j]
+  float* dd = reinterpret_cast<float*>(Bdd + 32768);
   float* rr = dd + C;
   uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);
   uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int bh = blockIdx.y, b = bh / p.H, h = bh % p.H;
-  const int jv0 = blockIdx.x * VS;
+  const int kk = tid & 127, half = tid >> 7, j0 = 64 * half;
+  const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
+  const uint32_t sAk = tc::smem_u32(Ak), sPt = tc::smem_u32(Pt), sdO = tc::smem_u32(dOop), sAqw = tc::smem_u32(Aqw);
+
+  auto grow = [&](int c, int i) { return ((size_t)(b * p.T + c * C + i) * p.H + h); };
+  auto issue_A = [&](int c) {
+    if (c >= 0) {
+      const size_t ci = (size_t)bh * p.n + c;
+      const int imax = min(C, p.T - c * C);
+      for (int u = tid; u < 64 * 16; u += 256) {
+        const int i = u >> 4, c8 = u & 15;
+        const bool v = i < imax;
+        const size_t g = v ? grow(c, i) * KD + c8 * 8 : 0;
+        tc::cp_async16(sAk + tc::kmajor_unit(i, c8, KD), p.k + g, v);
+        tc::cp_async16(sdO + tc::kmajor_unit(i, c8, KD), p.dO + g, v);
+        tc::cp_async16(sAqw + tc::kmajor_unit(i, c8, KD), p.q + g, v);
+      }
+      for (int u = tid; u < 64 * 8; u += 256) {
+        const int i = u >> 3, c8 = u & 7;
+        tc::cp_async16(sPt + tc::kmajor_unit(i, c8, C), p.P + (ci * C + i) * C + c8 * 8);
+      }
+    }
+    tc::cp_async_commit();
+  };
+  auto issue_B = [&](int c) {
+    if (c >= 0) {
+      const size_t ci = (size_t)bh * p.n + c;
+      for (int u = tid; u < 64 * 16; u += 256) {
+        const int i = u >> 4, c8 = u & 15;
+        tc::cp_async16(sAqw + tc::kmajor_unit(64 + i, c8, KD), p.w + (ci * C + i) * KD + c8 * 8);
+      }
+    }
+    tc::cp_async_commit();
+  };
 
   if (warp == 0) {
-    tc::tmem_alloc(tslot, 256);
+    tc::tmem_alloc(tslot, 512);
     tc::tmem_relinquish();
   }
   if (tid == 0) {
     tc::mbar_init(mbar, 1);
     tc::mbar_fence_init();
   }
-  float dS[VS];  // row kk = tid of dS, columns jv0 .. jv0+63
+  issue_A(p.n - 1);
+  issue_B(p.n - 1);
+  float dS[64];  // row kk of dS, columns j0 .. j0+63
   if (p.dhT_in) {
-    const float4* src = reinterpret_cast<const float4*>(p.dhT_in + ((size_t)bh * KD + tid) * KD + jv0);
+    const float4* src = reinterpret_cast<const float4*>(p.dhT_in + ((size_t)bh * KD + kk) * KD + j0);
 #pragma unroll
-    for (int x = 0; x < VS / 4; ++x) {
+    for (int x = 0; x < 16; ++x) {
       const float4 t4 = __ldg(src + x);
       dS[4 * x] = t4.x; dS[4 * x + 1] = t4.y; dS[4 * x + 2] = t4.z; dS[4 * x + 3] = t4.w;
     }
   } else {
 #pragma unroll
-    for (int x = 0; x < VS; ++x) dS[x] = 0.f;
+    for (int x = 0; x < 64; ++x) dS[x] = 0.f;
   }
   tc::fence_before_sync();
   __syncthreads();
@@ -72,8 +111,6 @@ __global__ void __launch_bounds__(128) gdn_tc_state_bwd_kernel(TcP p) {
 
   for (int c = p.n - 1; c >= 0 && ok; --c) {
     const size_t ci = (size_t)bh * p.n + c;
-    const int t0 = c * C, imax = min(C, p.T - t0);
-    auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
     const float* gam = p.gam + ci * C;
     const float glast = gam[C - 1];
     const float L = exp_nonpos(glast);
@@ -83,51 +120,40 @@ __global__ void __launch_bounds__(128) gdn_tc_state_bwd_kernel(TcP p) {
       rr[tid] = exp_nonpos(glast - g);
     }
 #pragma unroll
-    for (int c8 = 0; c8 < VS / 8; ++c8) {  // dS at chunk end: MMA operand + saved for the chunk kernel
+    for (int c8 = 0; c8 < 8; ++c8) {  // dS at chunk end: MMA operand + saved for the chunk kernel
       const uint4 val = make_uint4(tc::pack_bf16(dS[8 * c8], dS[8 * c8 + 1]), tc::pack_bf16(dS[8 * c8 + 2], dS[8 * c8 + 3]),
                                    tc::pack_bf16(dS[8 * c8 + 4], dS[8 * c8 + 5]), tc::pack_bf16(dS[8 * c8 + 6], dS[8 * c8 + 7]));
-      sts16(dSop, tc::mnmajor_unit(tid, c8, VS), val);
-      *reinterpret_cast<uint4*>(p.dhs + (ci * KD + tid) * KD + jv0 + c8 * 8) = val;
+      sts16(dSop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
+      *reinterpret_cast<uint4*>(p.dhs + (ci * KD + kk) * KD + j0 + c8 * 8) = val;
     }
-    __syncthreads();  // dd, rr visible
-    for (int u = tid; u < 64 * 16; u += 128) {   // k
+    tc::cp_async_wait<1>();  // group A of this chunk
+    __syncthreads();         // dO tile and dd visible to every thread
+    for (int u = tid; u < 64 * 16; u += 256) {  // d dO
       const int i = u >> 4, c8 = u & 15;
-      sts16(Ak, tc::kmajor_unit(i, c8, KD), i < imax ? ldg16(p.k + row(i) * KD + c8 * 8) : zero16());
-    }
-    for (int u = tid; u < 64 * 8; u += 128) {    // P ; dO slab and d dO
-      const int i = u >> 3, c8 = u & 7;
-      sts16(Pt, tc::kmajor_unit(i, c8, C), ldg16(p.P + (ci * C + i) * C + c8 * 8));
-      const uint4 g = i < imax ? ldg16(p.dO + row(i) * KD + jv0 + c8 * 8) : zero16();
-      sts16(dOop, tc::kmajor_unit(i, c8, VS), g);
-      sts16(Bdd, tc::kmajor_unit(i, c8, VS), tc::scale_bf16x8(g, dd[i]));
-    }
-    for (int u = tid; u < 128 * 16; u += 128) {  // [q; w]
-      const int r = u >> 4, c8 = u & 15, i = r & 63;
-      uint4 val = zero16();
-      if (r >= 64) val = ldg16(p.w + (ci * C + i) * KD + c8 * 8);
-      else if (i < imax) val = ldg16(p.q + row(i) * KD + c8 * 8);
-      sts16(Aqw, tc::kmajor_unit(r, c8, KD), val);
+      const uint32_t off = tc::kmajor_unit(i, c8, KD);
+      sts16(Bdd, off, tc::scale_bf16x8(*reinterpret_cast<const uint4*>(dOop + off), dd[i]));
     }
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     if (tid == 0) {
-      tc::issue_gemm(taddr, tc::kmajor_tile(Ak, KD), tc::mnmajor_tile(dSop, VS), 64, VS, KD, false);          // k dS
-      tc::issue_gemm(taddr + 64, tc::mnmajor_tile(Pt, C), tc::mnmajor_tile(dOop, VS), 64, VS, C, false);      // P^T dO
-      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Aqw, KD), tc::mnmajor_tile(Bdd, VS), 128, VS, C, false);   // q^T (d dO)
+      tc::issue_gemm(taddr, tc::kmajor_tile(Ak, KD), tc::mnmajor_tile(dSop, KD), 64, KD, KD, false);          // k dS
+      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Pt, C), tc::mnmajor_tile(dOop, KD), 64, KD, C, false);     // P^T dO
+      tc::issue_gemm(taddr + 256, tc::mnmajor_tile(Aqw, KD), tc::mnmajor_tile(Bdd, KD), 128, KD, C, false);   // q^T (d dO)
       tc::mma_commit(mbar);
     }
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
+    issue_A(c - 1);
     if (ok) {
-      const int i = 16 * warp + (lane & 15);  // M=64 accumulators: row i sits in TMEM lane (i%16) + 32*(i/16)
+      const int i = 16 * (warp & 3) + (lane & 15);  // M=64 accumulators: row i in TMEM lane (i%16) + 32*(i/16)
       const float ri = rr[i];
-      for (int c0 = 0; c0 < VS; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         float fa[32], fb[32];
-        ld_acc32(taddr, warp, c0, fa);
-        ld_acc32(taddr + 64, warp, c0, fb);
+        ld_acc32(taddr + j0, warp, c0, fa);
+        ld_acc32(taddr + 128 + j0, warp, c0, fb);
         if (lane < 16) {
 #pragma unroll
           for (int x = 0; x < 4; ++x) {
@@ -136,19 +162,21 @@ __global__ void __launch_bounds__(128) gdn_tc_state_bwd_kernel(TcP p) {
             for (int y = 0; y < 8; ++y) e[y] = fmaf(ri, fa[8 * x + y], fb[8 * x + y]);
             const uint4 vv = make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
                                         tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7]));
-            *reinterpret_cast<uint4*>(p.dvn + (ci * C + i) * KD + jv0 + c0 + 8 * x) = vv;
-            sts16(Bdd, tc::kmajor_unit(64 + i, (c0 >> 3) + x, VS), tc::scale_bf16x8(vv, -1.f));
+            const int c8 = 8 * half + (c0 >> 3) + x;
+            *reinterpret_cast<uint4*>(p.dvn + (ci * C + i) * KD + c8 * 8) = vv;
+            sts16(Bdd, tc::kmajor_unit(64 + i, c8, KD), tc::scale_bf16x8(vv, -1.f));
           }
         }
       }
     }
+    tc::cp_async_wait<1>();  // group B (w) of this chunk
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     if (ok && tid == 0) {  // ... - w^T dv_new
-      tc::issue_gemm(taddr + 128, tc::skip_k(tc::mnmajor_tile(Aqw, KD), 64), tc::skip_k(tc::mnmajor_tile(Bdd, VS), 64),
-                     128, VS, C, true);
+      tc::issue_gemm(taddr + 256, tc::skip_k(tc::mnmajor_tile(Aqw, KD), 64), tc::skip_k(tc::mnmajor_tile(Bdd, KD), 64),
+                     128, KD, C, true);
       tc::mma_commit(mbar);
     }
     if (ok) {
@@ -156,27 +184,27 @@ __global__ void __launch_bounds__(128) gdn_tc_state_bwd_kernel(TcP p) {
       ph ^= 1;
     }
     tc::fence_after_sync();
+    issue_B(c - 1);
     if (ok) {
-      for (int c0 = 0; c0 < VS; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         float f[32];
-        ld_acc32(taddr + 128, warp, c0, f);
+        ld_acc32(taddr + 256 + j0, warp, c0, f);
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) dS[c0 + jj] = fmaf(L, dS[c0 + jj], f[jj]);
       }
     }
     tc::fence_before_sync();
-    __syncthreads();
-    tc::fence_after_sync();
   }
+  tc::cp_async_wait<0>();
   if (!ok && tid == 0) atomicExch(p.status, 3);
   if (ok && p.dh0) {
-    float4* dst = reinterpret_cast<float4*>(p.dh0 + ((size_t)bh * KD + tid) * KD + jv0);
+    float4* dst = reinterpret_cast<float4*>(p.dh0 + ((size_t)bh * KD + kk) * KD + j0);
 #pragma unroll
-    for (int x = 0; x < VS / 4; ++x) dst[x] = make_float4(dS[4 * x], dS[4 * x + 1], dS[4 * x + 2], dS[4 * x + 3]);
+    for (int x = 0; x < 16; ++x) dst[x] = make_float4(dS[4 * x], dS[4 * x + 1], dS[4 * x + 2], dS[4 * x + 3]);
   }
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+  if (warp == 0) tc::tmem_dealloc(taddr, 512);
 }
 
 // ------------------------------------------------------------ chunk backward
@@ -217,12 +245,11 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   uint8_t* Xdvn = Xdo + 16384;      // [64][128] dv_new
   uint8_t* Xvn = Xdvn + 16384;      // [64][128] v_new
   uint8_t* Sreg = Xvn + 16384;      // 64 KB: phase A  S0 [128][128] | dS [128][128]
-  uint8_t* Xs0 = Sreg;              //        later    k | q | v beta | k beta d   ([64][128] each)
+  uint8_t* Xs0 = Sreg;              //        later    k | q | v   ([64][128] each)
   uint8_t* Xds = Sreg + 32768;
   uint8_t* Xk = Sreg;
   uint8_t* Xq = Sreg + 16384;
-  uint8_t* Xvb = Sreg + 32768;
-  uint8_t* Xkbd = Sreg + 49152;
+  uint8_t* Xv = Sreg + 32768;
   uint8_t* Xdw = Sreg + 65536;      // [64][128] dw
   uint8_t* Xt = Xdw + 16384;        // [64][64]  T
   uint8_t* Xpg = Xt + 8192;         // [64][64]  dP*Gamma
@@ -262,23 +289,29 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
     csum[tid] = 0.f;
   }
   for (int u = tid; u < 4 * C; u += 128) csw[u] = 0.f;
-  // ---- phase A staging: dO, dv_new, v_new, S0, dS, T ----
-  for (int u = tid; u < 64 * 16; u += 128) {
-    const int r = u >> 4, c8 = u & 15;
-    const uint32_t off = tc::kmajor_unit(r, c8, KD);
-    sts16(Xdo, off, r < imax ? ldg16(p.dO + row(r) * KD + c8 * 8) : zero16());
-    sts16(Xdvn, off, ldg16(p.dvn + (ci * C + r) * KD + c8 * 8));
-    sts16(Xvn, off, ldg16(p.vn + (ci * C + r) * KD + c8 * 8));
-  }
-  for (int u = tid; u < 128 * 16; u += 128) {
-    const int r = u >> 4, c8 = u & 15;
-    const uint32_t off = tc::kmajor_unit(r, c8, KD);
-    sts16(Xs0, off, ldg16(p.hs + (ci * KD + r) * KD + c8 * 8));
-    sts16(Xds, off, ldg16(p.dhs + (ci * KD + r) * KD + c8 * 8));
-  }
-  for (int u = tid; u < 64 * 8; u += 128) {
-    const int r = u >> 3, c8 = u & 7;
-    sts16(Xt, tc::kmajor_unit(r, c8, C), ldg16(p.Tm + (ci * C + r) * C + c8 * 8));
+  // ---- phase A staging (cp.async): dO, dv_new, v_new, S0, dS, T ----
+  {
+    const uint32_t sdo = tc::smem_u32(Xdo), sdvn = tc::smem_u32(Xdvn), svn = tc::smem_u32(Xvn);
+    const uint32_t ss0 = tc::smem_u32(Xs0), sds = tc::smem_u32(Xds), st = tc::smem_u32(Xt);
+    for (int u = tid; u < 64 * 16; u += 128) {
+      const int r = u >> 4, c8 = u & 15;
+      const uint32_t off = tc::kmajor_unit(r, c8, KD);
+      tc::cp_async16(sdo + off, r < imax ? p.dO + row(r) * KD + c8 * 8 : p.dO, r < imax);
+      tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
+      tc::cp_async16(svn + off, p.vn + (ci * C + r) * KD + c8 * 8);
+    }
+    for (int u = tid; u < 128 * 16; u += 128) {
+      const int r = u >> 4, c8 = u & 15;
+      const uint32_t off = tc::kmajor_unit(r, c8, KD);
+      tc::cp_async16(ss0 + off, p.hs + (ci * KD + r) * KD + c8 * 8);
+      tc::cp_async16(sds + off, p.dhs + (ci * KD + r) * KD + c8 * 8);
+    }
+    for (int u = tid; u < 64 * 8; u += 128) {
+      const int r = u >> 3, c8 = u & 7;
+      tc::cp_async16(st + tc::kmajor_unit(r, c8, C), p.Tm + (ci * C + r) * C + c8 * 8);
+    }
+    tc::cp_async_commit();
+    tc::cp_async_wait<0>();
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
@@ -311,10 +344,23 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
     part = warp_sum(part);
     if (lane == 0) red[warp] = part;
   }
-  __syncthreads();  // dd, rr, red visible
+  __syncthreads();  // dd, rr, red visible; every thread is done reading S0 / dS from shared memory
   ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
+  {  // the S0/dS region is free (MMAs done): fetch raw k, q, v behind the phase A epilogue
+    const uint32_t sk = tc::smem_u32(Xk), sq = tc::smem_u32(Xq), sv = tc::smem_u32(Xv);
+    for (int u = tid; u < 64 * 16; u += 128) {
+      const int r = u >> 4, c8 = u & 15;
+      const uint32_t off = tc::kmajor_unit(r, c8, KD);
+      const bool v = r < imax;
+      const size_t g = v ? row(r) * KD + c8 * 8 : 0;
+      tc::cp_async16(sk + off, p.k + g, v);
+      tc::cp_async16(sq + off, p.q + g, v);
+      tc::cp_async16(sv + off, p.v + g, v);
+    }
+    tc::cp_async_commit();
+  }
   float dg_own = 0.f, db_own = 0.f;
   const float gi = gam[i], bi = bet[i], di = dd[i], ri = rr[i];
   if (ok) {
@@ -342,24 +388,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
       }
     }
   }
-  tc::fence_before_sync();
-  __syncthreads();  // S0 / dS no longer read by anyone: the region is restaged
-  tc::fence_after_sync();
-  // ---- phase B staging: k, q, v beta, k beta d ----
-  for (int u = tid; u < 64 * 16; u += 128) {
-    const int r = u >> 4, c8 = u & 15;
-    const uint32_t off = tc::kmajor_unit(r, c8, KD);
-    uint4 kk = zero16(), qq = zero16(), vv = zero16();
-    if (r < imax) {
-      kk = ldg16(p.k + row(r) * KD + c8 * 8);
-      qq = ldg16(p.q + row(r) * KD + c8 * 8);
-      vv = ldg16(p.v + row(r) * KD + c8 * 8);
-    }
-    sts16(Xk, off, kk);
-    sts16(Xq, off, qq);
-    sts16(Xvb, off, tc::scale_bf16x8(vv, bet[r]));
-    sts16(Xkbd, off, tc::scale_bf16x8(kk, bet[r] * dd[r]));
-  }
+  tc::cp_async_wait<0>();  // k, q, v
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -367,8 +396,8 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   if (ok && tid == 0) {
     tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xk, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);    // k k^T
     tc::issue_gemm(taddr + 448, tc::kmajor_tile(Xq, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);    // q k^T
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xvb, KD), 64, 64, KD, false); // dT
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdw, KD), tc::kmajor_tile(Xkbd, KD), 64, 64, KD, true);
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xv, KD), 64, 64, KD, false);  // dv_new v^T
+    tc::issue_gemm(taddr + 192, tc::kmajor_tile(Xdw, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);   // dw k^T
     tc::mma_commit(mbar);
   }
   if (ok) {
@@ -401,10 +430,16 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
       ld_acc32(taddr + 384, warp, c0, f);  // k k^T
 #pragma unroll
       for (int jj = 0; jj < 32; ++jj) KKr[c0 + jj] = f[jj];
-      ld_acc32(taddr + 128, warp, c0, f);  // dT row -> X1
-      if (own) {
+      {  // dT[i][m] = beta_m (dv_new_i . v_m) + beta_m d_m (dw_i . k_m)   -> X1
+        float f2[32];
+        ld_acc32(taddr + 128, warp, c0, f);
+        ld_acc32(taddr + 192, warp, c0, f2);
+        if (own) {
 #pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(X1, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
+          for (int jj = 0; jj < 32; ++jj) f[jj] = bet[c0 + jj] * fmaf(dd[c0 + jj], f2[jj], f[jj]);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) sts16(X1, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
+        }
       }
     }
   }
@@ -542,11 +577,10 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
       ld_acc32(taddr + 384, warp, c0, f);  // T^T dv_new
       if (own && i < imax) {
         float e[32];
-        const uint4* vsrc = reinterpret_cast<const uint4*>(p.v + row(i) * KD + c0);
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float vv[8];
-          unpack8(__ldg(vsrc + x), vv);
+          unpack8(*reinterpret_cast<const uint4*>(Xv + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), vv);
 #pragma unroll
           for (int y = 0; y < 8; ++y) {
             vdot = fmaf(vv[y], f[8 * x + y], vdot);
@@ -632,7 +666,7 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
   }
   if (bwd_set_smem(gdn_tc_state_bwd_kernel, kStateBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("gdn_tc_state_bwd_kernel", st,
-             (gdn_tc_state_bwd_kernel<<<dim3(KD / VS, p.B * p.H), 128, kStateBwdSmem, st>>>(p)));
+             (gdn_tc_state_bwd_kernel<<<dim3(p.B * p.H), 256, kStateBwdSmem, st>>>(p)));
   s = check_launch("gdn_tc_state_bwd_kernel");
   if (s != MXB_OK) return s;
   if (bwd_set_smem(gdn_tc_chunk_bwd_kernel, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;

@@ -118,12 +118,12 @@ def device_status(device=None) -> int:
     return out.value
 
 
-def gated_delta_decode_step(state, q, k, v, beta, gate, *, gate_is_log=False, out=None):
+def gated_delta_decode_step(state, q, k, v, beta, gate, *, gate_is_log=False, out=None, flags=0):
     """One token on a persistent state [N,H,Dk,Dv] (updated in place).  Returns out [N,H,Dv]."""
     _require_cuda(state, q, k, v, beta, gate)
     l = _lib.lib()
     N, H, Dk, Dv = state.shape
-    d = GdnDesc(N, 1, H, Dk, Dv, 0, _io(q), int(bool(gate_is_log)), 0)
+    d = GdnDesc(N, 1, H, Dk, Dv, 0, _io(q), int(bool(gate_is_log)), int(flags))
     if out is None:
         out = torch.empty_like(v)
     _lib.check(l.mxb_gdn_decode_step(C.byref(d), _ptr(_f32(state, "state")), _ptr(q), _ptr(k), _ptr(v),

@@ -284,3 +284,27 @@ def test_backward_from_saved_forward(case):
     assert torch.equal(o, o_plain)
     for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
         assert torch.equal(got[name], ref[name]), name
+
+
+@pytest.mark.parametrize("dims", [(40, 16, 128, 128, torch.bfloat16), (10, 3, 64, 128, torch.float32),
+                                  (150, 4, 128, 128, torch.float32)])
+def test_decode_bulk_pipeline(dims):
+    """The bulk-copy pipelined decode kernel with several tiles per CTA, against the oracle and
+    against the register-resident kernel."""
+    from mixlab_b200 import _lib
+    N, H, K, V, io = dims
+    a = inputs.gdn_decode_inputs(N, H, K, V, 3, seed=7, io_dtype=io)
+    st_ref = a["state"].double()
+    st = _dev(a["state"].clone())
+    st_reg = _dev(a["state"].clone())
+    tol = TOL_F32 if io == torch.float32 else TOL_BF16
+    for t in range(3):
+        o_ref, st_ref = gdn.decode_step(st_ref, a["q"][t].double(), a["k"][t].double(), a["v"][t].double(),
+                                        a["beta"][t].double(), torch.exp(a["g"][t].double()))
+        args = (_dev(a["q"][t]), _dev(a["k"][t]), _dev(a["v"][t]), _dev(a["beta"][t]), _dev(a["g"][t]))
+        o = ops.gated_delta_decode_step(st, *args, gate_is_log=True)
+        o_reg = ops.gated_delta_decode_step(st_reg, *args, gate_is_log=True, flags=_lib.MXB_GDN_DECODE_REGISTER_KERNEL)
+        assert_close(o, o_ref, tol, f"out@{t}")
+        assert_close(o, o_reg.double(), tol, f"out vs register kernel@{t}")
+    assert_close(st, st_ref, TOL_F32, "state")
+    assert_close(st, st_reg.double(), 1e-5, "state vs register kernel")
