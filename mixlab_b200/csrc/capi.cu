@@ -274,7 +274,9 @@ struct mxb_host_ctx {
   int device;
   char* arena;
   size_t arena_bytes;
-  cudaStream_t stream;
+  cudaStream_t stream;           // kernels
+  cudaStream_t s_h2d, s_d2h;     // copy engines, one per direction
+  cudaEvent_t h2d_done[2], comp_done[2], d2h_done[2];
 };
 
 #define MXB_CUDA_TRY(expr)                          \
@@ -297,10 +299,16 @@ mxb_status mxb_host_ctx_create(int device, size_t arena_bytes, mxb_host_ctx** ou
   c->arena_bytes = arena_bytes;
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->arena), arena_bytes);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_h2d, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_d2h, cudaStreamNonBlocking);
+  for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+    e = cudaEventCreateWithFlags(&c->h2d_done[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->comp_done[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->d2h_done[i], cudaEventDisableTiming);
+  }
   if (e != cudaSuccess) {
     g_last_cuda_error = (int)e;
-    if (c->arena) cudaFree(c->arena);
-    delete c;
+    mxb_host_ctx_destroy(c);
     return MXB_ERR_CUDA;
   }
   *out = c;
@@ -310,12 +318,21 @@ mxb_status mxb_host_ctx_create(int device, size_t arena_bytes, mxb_host_ctx** ou
 void mxb_host_ctx_destroy(mxb_host_ctx* c) {
   if (!c) return;
   cudaSetDevice(c->device);
-  cudaStreamSynchronize(c->stream);
-  cudaStreamDestroy(c->stream);
-  cudaFree(c->arena);
+  cudaDeviceSynchronize();
+  for (int i = 0; i < 2; ++i) {
+    if (c->h2d_done[i]) cudaEventDestroy(c->h2d_done[i]);
+    if (c->comp_done[i]) cudaEventDestroy(c->comp_done[i]);
+    if (c->d2h_done[i]) cudaEventDestroy(c->d2h_done[i]);
+  }
+  if (c->stream) cudaStreamDestroy(c->stream);
+  if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
+  if (c->s_d2h) cudaStreamDestroy(c->s_d2h);
+  if (c->arena) cudaFree(c->arena);
   delete c;
 }
 
+// The batch is cut into single sequences; sequence b+1 is uploaded and sequence b-1 downloaded
+// while sequence b computes (two device slots per tensor, three streams, events between them).
 mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, const void* k,
                         const void* v, const float* beta, const float* gate, void* out,
                         const void* d_out, void* dq, void* dk, void* dv, float* dbeta, float* dgate) {
@@ -327,54 +344,70 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
   if (bwd && (!dq || !dk || !dv || !dbeta || !dgate)) return MXB_ERR_INVALID_ARGUMENT;
   MXB_CUDA_TRY(cudaSetDevice(c->device));
   const size_t es = d->io_dtype == MXB_F32 ? 4 : 2;
-  const size_t nk = (size_t)d->B * d->T * d->H * d->Dk, nv = (size_t)d->B * d->T * d->H * d->Dv;
-  const size_t ns = (size_t)d->B * d->T * d->H;
-  const size_t ws_f = mxb_gdn_fwd_workspace_bytes(d), ws_b = bwd ? mxb_gdn_bwd_workspace_bytes(d) : 0;
-  Carver cv(c->arena);
-  char* dq_in = cv.take<char>(nk * es);
-  char* dk_in = cv.take<char>(nk * es);
-  char* dv_in = cv.take<char>(nv * es);
-  float* dbeta_in = cv.take<float>(ns);
-  float* dgate_in = cv.take<float>(ns);
-  char* dout = cv.take<char>(nv * es);
-  char *ddo = nullptr, *g_q = nullptr, *g_k = nullptr, *g_v = nullptr;
-  float *g_b = nullptr, *g_g = nullptr;
-  if (bwd) {
-    ddo = cv.take<char>(nv * es);
-    g_q = cv.take<char>(nk * es);
-    g_k = cv.take<char>(nk * es);
-    g_v = cv.take<char>(nv * es);
-    g_b = cv.take<float>(ns);
-    g_g = cv.take<float>(ns);
-  }
-  char* ws = cv.take<char>(ws_f > ws_b ? ws_f : ws_b);
-  if (cv.bytes() > c->arena_bytes) return MXB_ERR_WORKSPACE;
-  cudaStream_t st = c->stream;
-  MXB_CUDA_TRY(cudaMemcpyAsync(dq_in, q, nk * es, cudaMemcpyHostToDevice, st));
-  MXB_CUDA_TRY(cudaMemcpyAsync(dk_in, k, nk * es, cudaMemcpyHostToDevice, st));
-  MXB_CUDA_TRY(cudaMemcpyAsync(dv_in, v, nv * es, cudaMemcpyHostToDevice, st));
-  MXB_CUDA_TRY(cudaMemcpyAsync(dbeta_in, beta, ns * 4, cudaMemcpyHostToDevice, st));
-  MXB_CUDA_TRY(cudaMemcpyAsync(dgate_in, gate, ns * 4, cudaMemcpyHostToDevice, st));
-  if (bwd) MXB_CUDA_TRY(cudaMemcpyAsync(ddo, d_out, nv * es, cudaMemcpyHostToDevice, st));
-  mxb_gdn_desc df = *d, db = *d;
+  // per-sequence element counts
+  const size_t nk = (size_t)d->T * d->H * d->Dk, nv = (size_t)d->T * d->H * d->Dv, ns = (size_t)d->T * d->H;
+  mxb_gdn_desc d1 = *d;
+  d1.B = 1;
+  mxb_gdn_desc df = d1, db = d1;
   if (bwd) {  // keep the forward intermediates in the arena for the backward that follows
     df.flags |= MXB_GDN_SAVE_FOR_BWD;
     db.flags |= MXB_GDN_BWD_USE_SAVED;
   }
-  s = mxb_gdn_fwd(&df, dq_in, dk_in, dv_in, dbeta_in, dgate_in, nullptr, dout, nullptr, ws, bwd ? ws_b : ws_f, st);
-  if (s != MXB_OK) return s;
-  MXB_CUDA_TRY(cudaMemcpyAsync(out, dout, nv * es, cudaMemcpyDeviceToHost, st));
-  if (bwd) {
-    s = mxb_gdn_bwd(&db, dq_in, dk_in, dv_in, dbeta_in, dgate_in, nullptr, ddo, nullptr, g_q, g_k, g_v,
-                    g_b, g_g, nullptr, ws, ws_b, st);
-    if (s != MXB_OK) return s;
-    MXB_CUDA_TRY(cudaMemcpyAsync(dq, g_q, nk * es, cudaMemcpyDeviceToHost, st));
-    MXB_CUDA_TRY(cudaMemcpyAsync(dk, g_k, nk * es, cudaMemcpyDeviceToHost, st));
-    MXB_CUDA_TRY(cudaMemcpyAsync(dv, g_v, nv * es, cudaMemcpyDeviceToHost, st));
-    MXB_CUDA_TRY(cudaMemcpyAsync(dbeta, g_b, ns * 4, cudaMemcpyDeviceToHost, st));
-    MXB_CUDA_TRY(cudaMemcpyAsync(dgate, g_g, ns * 4, cudaMemcpyDeviceToHost, st));
+  const size_t ws_f = mxb_gdn_fwd_workspace_bytes(&df), ws_b = bwd ? mxb_gdn_bwd_workspace_bytes(&db) : 0;
+  const size_t ws_bytes = ws_f > ws_b ? ws_f : ws_b;
+  Carver cv(c->arena);
+  char *i_q[2], *i_k[2], *i_v[2], *i_do[2], *o_out[2], *o_q[2], *o_k[2], *o_v[2];
+  float *i_b[2], *i_g[2], *o_b[2], *o_g[2];
+  for (int sl = 0; sl < 2; ++sl) {
+    i_q[sl] = cv.take<char>(nk * es); i_k[sl] = cv.take<char>(nk * es); i_v[sl] = cv.take<char>(nv * es);
+    i_b[sl] = cv.take<float>(ns); i_g[sl] = cv.take<float>(ns);
+    o_out[sl] = cv.take<char>(nv * es);
+    i_do[sl] = o_q[sl] = o_k[sl] = o_v[sl] = nullptr;
+    o_b[sl] = o_g[sl] = nullptr;
+    if (bwd) {
+      i_do[sl] = cv.take<char>(nv * es);
+      o_q[sl] = cv.take<char>(nk * es); o_k[sl] = cv.take<char>(nk * es); o_v[sl] = cv.take<char>(nv * es);
+      o_b[sl] = cv.take<float>(ns); o_g[sl] = cv.take<float>(ns);
+    }
   }
-  MXB_CUDA_TRY(cudaStreamSynchronize(st));
+  char* ws = cv.take<char>(ws_bytes);
+  if (cv.bytes() > c->arena_bytes) return MXB_ERR_WORKSPACE;
+  auto hp = [](const void* base, size_t off) { return static_cast<const char*>(base) + off; };
+  auto hpw = [](void* base, size_t off) { return static_cast<char*>(base) + off; };
+  const cudaMemcpyKind H2D = cudaMemcpyHostToDevice, D2H = cudaMemcpyDeviceToHost;
+  for (int bi = 0; bi < d->B; ++bi) {
+    const int sl = bi & 1;
+    if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_h2d, c->comp_done[sl], 0));  // slot inputs consumed
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_q[sl], hp(q, bi * nk * es), nk * es, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_k[sl], hp(k, bi * nk * es), nk * es, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_v[sl], hp(v, bi * nv * es), nv * es, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_b[sl], hp(beta, bi * ns * 4), ns * 4, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_g[sl], hp(gate, bi * ns * 4), ns * 4, H2D, c->s_h2d));
+    if (bwd) MXB_CUDA_TRY(cudaMemcpyAsync(i_do[sl], hp(d_out, bi * nv * es), nv * es, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaEventRecord(c->h2d_done[sl], c->s_h2d));
+    MXB_CUDA_TRY(cudaStreamWaitEvent(c->stream, c->h2d_done[sl], 0));
+    if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(c->stream, c->d2h_done[sl], 0));  // slot outputs drained
+    s = mxb_gdn_fwd(&df, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, o_out[sl], nullptr, ws, ws_bytes, c->stream);
+    if (s != MXB_OK) return s;
+    if (bwd) {
+      s = mxb_gdn_bwd(&db, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, i_do[sl], nullptr, o_q[sl], o_k[sl],
+                      o_v[sl], o_b[sl], o_g[sl], nullptr, ws, ws_bytes, c->stream);
+      if (s != MXB_OK) return s;
+    }
+    MXB_CUDA_TRY(cudaEventRecord(c->comp_done[sl], c->stream));
+    MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[sl], 0));
+    MXB_CUDA_TRY(cudaMemcpyAsync(hpw(out, bi * nv * es), o_out[sl], nv * es, D2H, c->s_d2h));
+    if (bwd) {
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dq, bi * nk * es), o_q[sl], nk * es, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dk, bi * nk * es), o_k[sl], nk * es, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dv, bi * nv * es), o_v[sl], nv * es, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dbeta, bi * ns * 4), o_b[sl], ns * 4, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dgate, bi * ns * 4), o_g[sl], ns * 4, D2H, c->s_d2h));
+    }
+    MXB_CUDA_TRY(cudaEventRecord(c->d2h_done[sl], c->s_d2h));
+  }
+  MXB_CUDA_TRY(cudaStreamSynchronize(c->s_d2h));
+  MXB_CUDA_TRY(cudaStreamSynchronize(c->stream));
   return MXB_OK;
 }
 

@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
 //   [256,384) dkt = v_new dS^T
 //   [384,448) dP                       -> k k^T     } -> [384,512) (dP*Gamma) k -> T^T dv_new
 //   [448,512)                             q k^T     }
-constexpr int kChunkBwdSmem = 49152 + 65536 + 16384 + 4 * 8192 + 12 * C * 4 + 64 + 256;
+constexpr int kChunkBwdSmem = 49152 + 65536 + 16384 + 4 * 8192 + 14 * C * 4 + 64 + 256;
 
 __device__ __forceinline__ void unpack8(uint4 v, float (&e)[8]) {
   tc::unpack_bf16(v.x, e[0], e[1]); tc::unpack_bf16(v.y, e[2], e[3]);
@@ -238,7 +238,7 @@ __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, c
   return s;
 }
 
-__global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
+__global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
   uint8_t* Xdo = sm;                // [64][128] dO
@@ -260,9 +260,9 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   float* dd = bet + C;
   float* rr = dd + C;
   float* csum = rr + C;             // cross-row contributions to dgam (shared atomics)
-  float* dgo = csum + C;            // per-row dgam / dbeta handed over at the end
-  float* dbo = dgo + C;
-  float* red = dbo + C;
+  float* dgo = csum + C;            // [2][C] per-row dgam / dbeta partials of the two column halves
+  float* dbo = dgo + 2 * C;
+  float* red = dbo + 2 * C;
   float* csw = red + C;             // [4 warps][C] per-warp column sums (no atomics)
   uint64_t* mbar = reinterpret_cast<uint64_t*>(csw + 4 * C);
   uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
@@ -273,7 +273,8 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   const int imax = min(C, p.T - t0);
   auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
   const bool own = lane < 16;
-  const int i = 16 * warp + (lane & 15);  // the row this thread owns in every epilogue
+  const int i = 16 * (warp & 3) + (lane & 15);  // the row this thread owns in every epilogue
+  const int hc = warp >> 2;  // warps 0-3 take the first half of an accumulator's columns, warps 4-7 the second
 
   if (warp == 0) {
     tc::tmem_alloc(tslot, 512);
@@ -288,25 +289,25 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
     bet[tid] = tid < imax ? p.beta[row(tid)] : 0.f;
     csum[tid] = 0.f;
   }
-  for (int u = tid; u < 4 * C; u += 128) csw[u] = 0.f;
+  for (int u = tid; u < 4 * C; u += 256) csw[u] = 0.f;
   // ---- phase A staging (cp.async): dO, dv_new, v_new, S0, dS, T ----
   {
     const uint32_t sdo = tc::smem_u32(Xdo), sdvn = tc::smem_u32(Xdvn), svn = tc::smem_u32(Xvn);
     const uint32_t ss0 = tc::smem_u32(Xs0), sds = tc::smem_u32(Xds), st = tc::smem_u32(Xt);
-    for (int u = tid; u < 64 * 16; u += 128) {
+    for (int u = tid; u < 64 * 16; u += 256) {
       const int r = u >> 4, c8 = u & 15;
       const uint32_t off = tc::kmajor_unit(r, c8, KD);
       tc::cp_async16(sdo + off, r < imax ? p.dO + row(r) * KD + c8 * 8 : p.dO, r < imax);
       tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
       tc::cp_async16(svn + off, p.vn + (ci * C + r) * KD + c8 * 8);
     }
-    for (int u = tid; u < 128 * 16; u += 128) {
+    for (int u = tid; u < 128 * 16; u += 256) {
       const int r = u >> 4, c8 = u & 15;
       const uint32_t off = tc::kmajor_unit(r, c8, KD);
       tc::cp_async16(ss0 + off, p.hs + (ci * KD + r) * KD + c8 * 8);
       tc::cp_async16(sds + off, p.dhs + (ci * KD + r) * KD + c8 * 8);
     }
-    for (int u = tid; u < 64 * 8; u += 128) {
+    for (int u = tid; u < 64 * 8; u += 256) {
       const int r = u >> 3, c8 = u & 7;
       tc::cp_async16(st + tc::kmajor_unit(r, c8, C), p.Tm + (ci * C + r) * C + c8 * 8);
     }
@@ -334,7 +335,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   }
   {  // <dS, S0> while the tensor core works
     float part = 0.f;
-    for (int u = tid; u < 128 * 16; u += 128) {
+    for (int u = tid; u < 128 * 16; u += 256) {
       float a[8], bq[8];
       unpack8(*reinterpret_cast<const uint4*>(Xs0 + u * 16), a);
       unpack8(*reinterpret_cast<const uint4*>(Xds + u * 16), bq);
@@ -350,7 +351,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_after_sync();
   {  // the S0/dS region is free (MMAs done): fetch raw k, q, v behind the phase A epilogue
     const uint32_t sk = tc::smem_u32(Xk), sq = tc::smem_u32(Xq), sv = tc::smem_u32(Xv);
-    for (int u = tid; u < 64 * 16; u += 128) {
+    for (int u = tid; u < 64 * 16; u += 256) {
       const int r = u >> 4, c8 = u & 15;
       const uint32_t off = tc::kmajor_unit(r, c8, KD);
       const bool v = r < imax;
@@ -364,7 +365,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   float dg_own = 0.f, db_own = 0.f;
   const float gi = gam[i], bi = bet[i], di = dd[i], ri = rr[i];
   if (ok) {
-    for (int c0 = 0; c0 < 64; c0 += 32) {  // dP * Gamma, lower incl. diagonal
+    for (int c0 = 32 * hc; c0 < 32 * hc + 32; c0 += 32) {  // dP * Gamma, lower incl. diagonal
       float f[32];
       ld_acc32(taddr + 384, warp, c0, f);
       if (own) {
@@ -377,7 +378,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
         for (int x = 0; x < 4; ++x) sts16(Xpg, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
       }
     }
-    for (int c0 = 0; c0 < KD; c0 += 32) {  // dw = -dv_new S0^T
+    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {  // dw = -dv_new S0^T
       float f[32];
       ld_acc32(taddr + 128, warp, c0, f);
       if (own) {
@@ -407,7 +408,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_after_sync();
   float KKr[C];  // (k_i . k_j), j < i
   if (ok) {
-    for (int c0 = 0; c0 < 64; c0 += 32) {
+    for (int c0 = 32 * hc; c0 < 32 * hc + 32; c0 += 32) {
       float f[32];
       ld_acc32(taddr + 448, warp, c0, f);  // q k^T: dgam from P
       {
@@ -422,7 +423,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
             const float X = (own && j <= i) ? e[y] * f[8 * x + y] : 0.f;
             rs += X;
             const float colsum = warp_sum(X);  // over the 16 rows this warp owns
-            if (lane == 0) csw[warp * C + j] -= colsum;
+            if (lane == 0) csw[(warp & 3) * C + j] -= colsum;
           }
         }
         dg_own += rs;
@@ -458,7 +459,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   }
   tc::fence_after_sync();
   if (ok) {
-    for (int c0 = 0; c0 < 64; c0 += 32) {
+    for (int c0 = 32 * hc; c0 < 32 * hc + 32; c0 += 32) {
       float f[32];
       ld_acc32(taddr + 192, warp, c0, f);
       if (own) {
@@ -485,7 +486,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
     auto ms_at = [&](int r, int cc) -> bf16& {
       return ms[(tc::kmajor_unit(r, cc >> 3, C) >> 1) + (cc & 7)];
     };
-    for (int c0 = 0; c0 < 64; c0 += 32) {
+    for (int c0 = 32 * hc; c0 < 32 * hc + 32; c0 += 32) {
       float f[32];
       ld_acc32(taddr + 128, warp, c0, f);
       {
@@ -505,7 +506,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
           }
           rs += t;
           const float colsum = warp_sum(bi * t);
-          if (lane == 0) csw[warp * C + j] -= colsum;
+          if (lane == 0) csw[(warp & 3) * C + j] -= colsum;
         }
         db_own += rs;
         dg_own += bi * rs;
@@ -530,7 +531,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_after_sync();
   if (ok) {
     float qdot = 0.f, kdot = 0.f;
-    for (int c0 = 0; c0 < KD; c0 += 32) {
+    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
       float f[32], g2[32];
       ld_acc32(taddr + 0, warp, c0, f);     // dqi
       ld_acc32(taddr + 384, warp, c0, g2);  // (dP*Gamma) k
@@ -552,7 +553,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
       const float rho = own ? ri * kdot : 0.f;
       if (own) dg_own += di * qdot - rho;
       const float tot = warp_sum(rho);
-      if (lane == 0) atomicAdd(&csum[C - 1], tot);
+      if (lane == 0) red[8 + warp] = tot;  // summed in a fixed order at the end (deterministic)
     }
   }
   tc::fence_before_sync();
@@ -572,7 +573,7 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
   if (ok) {
     float vdot = 0.f, kz = 0.f;
     const float bd_i = bi * di;
-    for (int c0 = 0; c0 < KD; c0 += 32) {
+    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
       float f[32], g2[32], g3[32];
       ld_acc32(taddr + 384, warp, c0, f);  // T^T dv_new
       if (own && i < imax) {
@@ -611,23 +612,25 @@ __global__ void __launch_bounds__(128) gdn_tc_chunk_bwd_kernel(TcP p) {
       dg_own += bd_i * kz;
     }
   }
-  if (own) {
-    dgo[i] = dg_own;
-    dbo[i] = db_own;
+  if (own) {  // the two column halves hold partial sums of the same row
+    dgo[hc * C + i] = dg_own;
+    dbo[hc * C + i] = db_own;
   }
   tc::fence_before_sync();
   __syncthreads();
   if (tid == 0) {  // dg = reverse cumulative sum of dgam within the chunk
-    float acc = L * (red[0] + red[1] + red[2] + red[3]);  // d/dgam_last of E(gam_last) <dS, S0>
+    // d/dgam_last: E(gam_last) <dS, S0> and the sum of rho over the rows
+    float acc = L * (red[0] + red[1] + red[2] + red[3] + red[4] + red[5] + red[6] + red[7]);
+    for (int wv = 0; wv < 8; ++wv) acc += red[8 + wv];
     for (int r = C - 1; r >= 0; --r) {
-      acc += dgo[r] + csum[r] + csw[r] + csw[C + r] + csw[2 * C + r] + csw[3 * C + r];
+      acc += dgo[r] + dgo[C + r] + csum[r] + csw[r] + csw[C + r] + csw[2 * C + r] + csw[3 * C + r];
       dgo[r] = acc;
     }
   }
   __syncthreads();
   if (!ok && tid == 0) atomicExch(p.status, 4);
   if (ok && tid < imax) {
-    p.dbeta[row(tid)] = dbo[tid];
+    p.dbeta[row(tid)] = dbo[tid] + dbo[C + tid];
     float dg = dgo[tid];
     const float gin = p.gate[row(tid)];
     if (p.gate_is_log) {
@@ -671,7 +674,7 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
   if (s != MXB_OK) return s;
   if (bwd_set_smem(gdn_tc_chunk_bwd_kernel, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
-             (gdn_tc_chunk_bwd_kernel<<<dim3(p.n, p.B * p.H), 128, kChunkBwdSmem, st>>>(p)));
+             (gdn_tc_chunk_bwd_kernel<<<dim3(p.n, p.B * p.H), 256, kChunkBwdSmem, st>>>(p)));
   return check_launch("gdn_tc_chunk_bwd_kernel");
 }
 

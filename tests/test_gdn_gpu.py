@@ -168,11 +168,13 @@ def test_decode_equals_scan():
     assert_close(st, s_scan, TOL_F32, "state")
 
 
-def test_host_buffer_entry_point():
-    """mxb_host_gdn: host tensors in, host tensors out, forward + backward."""
+@pytest.mark.parametrize("B", [1, 3, 4])
+def test_host_buffer_entry_point(B):
+    """mxb_host_gdn: host tensors in, host tensors out, forward + backward (sequences are
+    pipelined through two device slots, so B > 2 exercises slot reuse)."""
     import ctypes as C
     lib = mixlab_b200.lib()
-    B, T, H, K, V = 1, 100, 2, 32, 32
+    T, H, K, V = 100, 2, 32, 32
     a = inputs.gdn_inputs(B, T, H, K, V, seed=6, with_grad_out=True)
     f = {k: v.double() for k, v in a.items()}
     want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], f["g"], f["d_out"], gate_is_log=True)
