@@ -167,6 +167,11 @@ typedef struct {
   int32_t flags;
 } mxb_mamba3_desc;
 
+enum {
+  MXB_MAMBA3_CHANNEL_KERNELS = 1 /* head-broadcast layout: use the warp-per-channel kernels even
+                                    where the CTA-per-head kernels cover the shape */
+};
+
 MXB_API size_t mxb_mamba3_fwd_workspace_bytes(const mxb_mamba3_desc* d);
 MXB_API size_t mxb_mamba3_bwd_workspace_bytes(const mxb_mamba3_desc* d);
 

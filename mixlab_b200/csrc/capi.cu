@@ -3,6 +3,7 @@
 // include/mixlab_b200.h.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -345,9 +346,15 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
   MXB_CUDA_TRY(cudaSetDevice(c->device));
   const size_t es = d->io_dtype == MXB_F32 ? 4 : 2;
   // per-sequence element counts
-  const size_t nk = (size_t)d->T * d->H * d->Dk, nv = (size_t)d->T * d->H * d->Dv, ns = (size_t)d->T * d->H;
+  const size_t sk = (size_t)d->T * d->H * d->Dk, sv = (size_t)d->T * d->H * d->Dv, ss = (size_t)d->T * d->H;
+  // sequences per pipeline slice (MXB_HOST_SLICE_SEQS overrides the default of 1)
+  int per = 1;
+  if (const char* ev = std::getenv("MXB_HOST_SLICE_SEQS")) per = std::atoi(ev);
+  if (per < 1) per = 1;
+  if (per > d->B) per = d->B;
+  const int nslices = (d->B + per - 1) / per;
   mxb_gdn_desc d1 = *d;
-  d1.B = 1;
+  d1.B = per;
   mxb_gdn_desc df = d1, db = d1;
   if (bwd) {  // keep the forward intermediates in the arena for the backward that follows
     df.flags |= MXB_GDN_SAVE_FOR_BWD;
@@ -355,6 +362,7 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
   }
   const size_t ws_f = mxb_gdn_fwd_workspace_bytes(&df), ws_b = bwd ? mxb_gdn_bwd_workspace_bytes(&db) : 0;
   const size_t ws_bytes = ws_f > ws_b ? ws_f : ws_b;
+  const size_t nk = sk * per, nv = sv * per, ns = ss * per;  // slot capacities
   Carver cv(c->arena);
   char *i_q[2], *i_k[2], *i_v[2], *i_do[2], *o_out[2], *o_q[2], *o_k[2], *o_v[2];
   float *i_b[2], *i_g[2], *o_b[2], *o_g[2];
@@ -375,15 +383,19 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
   auto hp = [](const void* base, size_t off) { return static_cast<const char*>(base) + off; };
   auto hpw = [](void* base, size_t off) { return static_cast<char*>(base) + off; };
   const cudaMemcpyKind H2D = cudaMemcpyHostToDevice, D2H = cudaMemcpyDeviceToHost;
-  for (int bi = 0; bi < d->B; ++bi) {
+  for (int bi = 0; bi < nslices; ++bi) {
     const int sl = bi & 1;
+    const int b0 = bi * per, nb = (b0 + per <= d->B) ? per : d->B - b0;
+    const size_t ck = sk * nb * es, cvb = sv * nb * es, cs = ss * nb * 4;   // bytes of this slice
+    const size_t ok_ = (size_t)b0 * sk * es, ov_ = (size_t)b0 * sv * es, os_ = (size_t)b0 * ss * 4;
+    df.B = db.B = nb;
     if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_h2d, c->comp_done[sl], 0));  // slot inputs consumed
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_q[sl], hp(q, bi * nk * es), nk * es, H2D, c->s_h2d));
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_k[sl], hp(k, bi * nk * es), nk * es, H2D, c->s_h2d));
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_v[sl], hp(v, bi * nv * es), nv * es, H2D, c->s_h2d));
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_b[sl], hp(beta, bi * ns * 4), ns * 4, H2D, c->s_h2d));
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_g[sl], hp(gate, bi * ns * 4), ns * 4, H2D, c->s_h2d));
-    if (bwd) MXB_CUDA_TRY(cudaMemcpyAsync(i_do[sl], hp(d_out, bi * nv * es), nv * es, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_q[sl], hp(q, ok_), ck, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_k[sl], hp(k, ok_), ck, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_v[sl], hp(v, ov_), cvb, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_b[sl], hp(beta, os_), cs, H2D, c->s_h2d));
+    MXB_CUDA_TRY(cudaMemcpyAsync(i_g[sl], hp(gate, os_), cs, H2D, c->s_h2d));
+    if (bwd) MXB_CUDA_TRY(cudaMemcpyAsync(i_do[sl], hp(d_out, ov_), cvb, H2D, c->s_h2d));
     MXB_CUDA_TRY(cudaEventRecord(c->h2d_done[sl], c->s_h2d));
     MXB_CUDA_TRY(cudaStreamWaitEvent(c->stream, c->h2d_done[sl], 0));
     if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(c->stream, c->d2h_done[sl], 0));  // slot outputs drained
@@ -396,13 +408,13 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
     }
     MXB_CUDA_TRY(cudaEventRecord(c->comp_done[sl], c->stream));
     MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[sl], 0));
-    MXB_CUDA_TRY(cudaMemcpyAsync(hpw(out, bi * nv * es), o_out[sl], nv * es, D2H, c->s_d2h));
+    MXB_CUDA_TRY(cudaMemcpyAsync(hpw(out, ov_), o_out[sl], cvb, D2H, c->s_d2h));
     if (bwd) {
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dq, bi * nk * es), o_q[sl], nk * es, D2H, c->s_d2h));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dk, bi * nk * es), o_k[sl], nk * es, D2H, c->s_d2h));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dv, bi * nv * es), o_v[sl], nv * es, D2H, c->s_d2h));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dbeta, bi * ns * 4), o_b[sl], ns * 4, D2H, c->s_d2h));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dgate, bi * ns * 4), o_g[sl], ns * 4, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dq, ok_), o_q[sl], ck, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dk, ok_), o_k[sl], ck, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dv, ov_), o_v[sl], cvb, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dbeta, os_), o_b[sl], cs, D2H, c->s_d2h));
+      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dgate, os_), o_g[sl], cs, D2H, c->s_d2h));
     }
     MXB_CUDA_TRY(cudaEventRecord(c->d2h_done[sl], c->s_d2h));
   }

@@ -325,6 +325,12 @@ __global__ void m3_cast_kernel(const float* __restrict__ src, IO* __restrict__ d
 }
 
 // --------------------------------------------------------------------- host
+bool mamba3_head_supported(const mxb_mamba3_desc* d);
+bool mamba3_head_bwd_supported(const mxb_mamba3_desc* d);
+size_t mamba3_head_partial_floats(const mxb_mamba3_desc* d);
+mxb_status mamba3_head_bwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
+                           const void*, const void*, const void*, void*, float*, float*, float*, float*, void*, void*,
+                           float*, float*, float*, float*, cudaStream_t);
 static M3P make_m3(const mxb_mamba3_desc* d) {
   M3P p{};
   p.B = d->B; p.T = d->T; p.D = d->D; p.N = d->N; p.G = d->G; p.NH = d->nheads;
@@ -340,8 +346,15 @@ bool mamba3_supported(const mxb_mamba3_desc* d) {
   return true;
 }
 
-static size_t carve_m3(M3P& p, void* ws, bool io_f32) {
+static size_t carve_m3(M3P& p, void* ws, bool io_f32, size_t partial_floats = 0, float** pb = nullptr,
+                       float** pc = nullptr) {
   Carver cv(ws);
+  if (partial_floats) {
+    float* a = cv.take<float>(partial_floats);
+    float* b2 = cv.take<float>(partial_floats);
+    if (pb) *pb = a;
+    if (pc) *pc = b2;
+  }
   p.ck_h = cv.take<float>((size_t)p.B * p.nW * p.D * p.N);
   p.ck_phi = cv.take<float>((size_t)p.B * p.nW * p.D * p.Kp);
   if (!io_f32) {
@@ -354,7 +367,8 @@ static size_t carve_m3(M3P& p, void* ws, bool io_f32) {
 size_t mamba3_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
   if (!bwd) return 0;
   M3P p = make_m3(d);
-  return carve_m3(p, nullptr, d->io_dtype == MXB_F32);
+  const bool head = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
+  return carve_m3(p, nullptr, d->io_dtype == MXB_F32, head ? mamba3_head_partial_floats(d) : 0);
 }
 
 template <typename IO, int PR>
@@ -386,9 +400,15 @@ static mxb_status m3_bwd_pr(const M3P& p, cudaStream_t st) {
   return m3_bwd_launch<IO, 4>(p, st);
 }
 
+
+mxb_status mamba3_head_fwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
+                           const void*, const void*, void*, float*, float*, cudaStream_t);
+
 mxb_status mamba3_fwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
                       const float* theta, const float* a_log, const void* b, const void* c, void* y,
                       cudaStream_t st) {
+  if (!(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_supported(d))
+    return mamba3_head_fwd(d, x, dt, lam, theta, a_log, b, c, y, nullptr, nullptr, st);
   M3P p = make_m3(d);
   p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c; p.y = y;
   return d->io_dtype == MXB_F32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);
@@ -402,7 +422,9 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
   const bool f32 = d->io_dtype == MXB_F32;
   p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c;
   p.dy = dy; p.dx = dx; p.ddt = ddt; p.dlam = dlam; p.dtheta = dtheta; p.da_log = da_log;
-  carve_m3(p, ws, f32);
+  const bool head_bwd = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
+  float *pb = nullptr, *pc = nullptr;
+  carve_m3(p, ws, f32, head_bwd ? mamba3_head_partial_floats(d) : 0, &pb, &pc);
   const size_t nbc = (size_t)p.B * p.T * p.G * p.N;
   if (f32) { p.db32 = static_cast<float*>(db); p.dc32 = static_cast<float*>(dc); }
   cudaError_t e = cudaMemsetAsync(p.db32, 0, nbc * sizeof(float), st);
@@ -416,9 +438,18 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
     if (e == cudaSuccess) e = cudaMemsetAsync(dtheta, 0, nh, st);
   }
   if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
-  mxb_status s = f32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);  // checkpoint pass (y == nullptr)
-  if (s != MXB_OK) return s;
-  s = f32 ? m3_bwd_pr<float>(p, st) : m3_bwd_pr<__nv_bfloat16>(p, st);
+  mxb_status s;
+  if (head_bwd) {
+    // CTA-per-head kernels: checkpoint pass (y == nullptr), reverse pass, reduction of the dB/dC partials
+    s = mamba3_head_fwd(d, x, dt, lam, theta, a_log, b, c, nullptr, p.ck_h, p.ck_phi, st);
+    if (s != MXB_OK) return s;
+    return mamba3_head_bwd(d, x, dt, lam, theta, a_log, b, c, dy, dx, ddt, dlam, dtheta, da_log, db, dc, pb, pc,
+                           p.ck_h, p.ck_phi, st);
+  } else {
+    s = f32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);  // checkpoint pass (y == nullptr)
+    if (s != MXB_OK) return s;
+    s = f32 ? m3_bwd_pr<float>(p, st) : m3_bwd_pr<__nv_bfloat16>(p, st);
+  }
   if (s != MXB_OK) return s;
   if (!f32) {
     MXB_LAUNCH("m3_cast_kernel", st, (m3_cast_kernel<__nv_bfloat16><<<592, 256, 0, st>>>(p.db32, static_cast<__nv_bfloat16*>(db), nbc)));

@@ -132,17 +132,17 @@ def gated_delta_decode_step(state, q, k, v, beta, gate, *, gate_is_log=False, ou
     return out
 
 
-def mamba3_desc(x, b, nheads) -> Mamba3Desc:
+def mamba3_desc(x, b, nheads, flags=0) -> Mamba3Desc:
     B, T, D = x.shape
     G, N = b.shape[-2], b.shape[-1]
-    return Mamba3Desc(B, T, D, N, G, int(nheads), _io(x), 0)
+    return Mamba3Desc(B, T, D, N, G, int(nheads), _io(x), int(flags))
 
 
-def mamba3_selective_scan(x, dt, lam, theta, a_log, b, c, *, nheads=0):
+def mamba3_selective_scan(x, dt, lam, theta, a_log, b, c, *, nheads=0, flags=0):
     """Forward.  x [B,T,D]; b,c [B,T,G,N]; per-channel (nheads=0) or head-broadcast parameters."""
     _require_cuda(x, dt, lam, theta, a_log, b, c)
     l = _lib.lib()
-    d = mamba3_desc(x, b, nheads)
+    d = mamba3_desc(x, b, nheads, flags)
     y = torch.empty_like(x)
     _lib.check(l.mxb_mamba3_fwd(C.byref(d), _ptr(x), _ptr(_f32(dt, "dt")), _ptr(_f32(lam, "lambda")),
                                 _ptr(_f32(theta, "theta")), _ptr(_f32(a_log, "a_log")), _ptr(b), _ptr(c),
@@ -150,11 +150,11 @@ def mamba3_selective_scan(x, dt, lam, theta, a_log, b, c, *, nheads=0):
     return y
 
 
-def mamba3_selective_scan_backward(x, dt, lam, theta, a_log, b, c, dy, *, nheads=0):
+def mamba3_selective_scan_backward(x, dt, lam, theta, a_log, b, c, dy, *, nheads=0, flags=0):
     """Gradients in argument order.  Returns dict(dx, ddt, dlambda, dtheta, da_log, db, dc)."""
     _require_cuda(x, dt, lam, theta, a_log, b, c, dy)
     l = _lib.lib()
-    d = mamba3_desc(x, b, nheads)
+    d = mamba3_desc(x, b, nheads, flags)
     dx = torch.empty_like(x)
     ddt, dlam, dth, dal = (torch.empty_like(t) for t in (dt, lam, theta, a_log))
     db, dc = torch.empty_like(b), torch.empty_like(c)
