@@ -328,6 +328,7 @@ __global__ void m3_cast_kernel(const float* __restrict__ src, IO* __restrict__ d
 bool mamba3_head_supported(const mxb_mamba3_desc* d);
 bool mamba3_head_bwd_supported(const mxb_mamba3_desc* d);
 size_t mamba3_head_partial_floats(const mxb_mamba3_desc* d);
+int mamba3_head_window();
 mxb_status mamba3_head_bwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
                            const void*, const void*, const void*, void*, float*, float*, float*, float*, void*, void*,
                            float*, float*, float*, float*, cudaStream_t);
@@ -368,6 +369,7 @@ size_t mamba3_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
   if (!bwd) return 0;
   M3P p = make_m3(d);
   const bool head = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
+  if (head) p.nW = (d->T + mamba3_head_window() - 1) / mamba3_head_window();  // checkpoint spacing of the head kernels
   return carve_m3(p, nullptr, d->io_dtype == MXB_F32, head ? mamba3_head_partial_floats(d) : 0);
 }
 
@@ -424,6 +426,7 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
   p.dy = dy; p.dx = dx; p.ddt = ddt; p.dlam = dlam; p.dtheta = dtheta; p.da_log = da_log;
   const bool head_bwd = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
   float *pb = nullptr, *pc = nullptr;
+  if (head_bwd) p.nW = (d->T + mamba3_head_window() - 1) / mamba3_head_window();
   carve_m3(p, ws, f32, head_bwd ? mamba3_head_partial_floats(d) : 0, &pb, &pc);
   const size_t nbc = (size_t)p.B * p.T * p.G * p.N;
   if (f32) { p.db32 = static_cast<float*>(db); p.dc32 = static_cast<float*>(dc); }

@@ -15,7 +15,7 @@
 
 namespace mxb {
 
-constexpr int kHB = 16;  // steps per block (= checkpoint window of the backward)
+constexpr int kHB = 8;   // steps per block (= checkpoint window of the backward)
 
 struct M3H {
   int B, T, D, N, G, NH, P, nW;
@@ -500,6 +500,8 @@ static mxb_status m3hb_launch(const M3HB& q, cudaStream_t st) {
                                                                             q.f.G, nchunks)));
   return check_launch("m3h_reduce_kernel");
 }
+
+int mamba3_head_window() { return kHB; }
 
 size_t mamba3_head_partial_floats(const mxb_mamba3_desc* d) {
   return (size_t)d->B * (d->D / 16) * d->T * d->N;
