@@ -95,6 +95,8 @@ enum {
                                    workspace, which must then have the BACKWARD size */
   MXB_GDN_DECODE_REGISTER_KERNEL = 16, /* decode step: use the register-resident kernel even where
                                           the bulk-copy pipelined kernel covers the shape */
+  MXB_GDN_NO_TMA = 32,          /* tensor-core path: stage k, q, v of the prep kernel with cp.async instead
+                                   of TMA tensor copies (a cross-check of the two staging paths) */
   MXB_GDN_BWD_USE_SAVED = 8     /* backward: the workspace still holds what a forward with
                                    MXB_GDN_SAVE_FOR_BWD on the same inputs left there, so the
                                    forward recompute is skipped (the reference keeps its forward

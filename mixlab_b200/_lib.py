@@ -14,6 +14,7 @@ MXB_GDN_BWD_FP32_KERNELS = 2
 MXB_GDN_SAVE_FOR_BWD = 4
 MXB_GDN_BWD_USE_SAVED = 8
 MXB_GDN_DECODE_REGISTER_KERNEL = 16
+MXB_GDN_NO_TMA = 32
 MXB_MAMBA3_CHANNEL_KERNELS = 1
 
 

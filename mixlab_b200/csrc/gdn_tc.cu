@@ -13,6 +13,10 @@
 //   gdn_tc_state_fwd_kernel  one CTA per (64-column slab of Dv, b*H+h), sequential over
 //                            chunks, fp32 state in registers (thread = state row):
 //                            [w;q] S (M=128) -> v_new, then [0;P] v_new and k^T (r v_new)
+#include <cuda.h>
+
+#include <cstring>
+
 #include "gdn_tc.cuh"
 
 namespace mxb {
@@ -21,11 +25,21 @@ namespace mxb {
 // u = T (v beta) and w = T (k beta E(gam)) are evaluated as (T diag(beta)) v and
 // (T diag(beta E(gam))) k: the scaling goes into two column-scaled bf16 copies of T written
 // straight from the solve's registers, so k, q and v are staged raw with cp.async.
-constexpr int kPrepSmem = 32768 + 16384 + 3 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 128;
+//
+// TMA = true: k, q, v arrive as cp.async.bulk.tensor tiles (boxes of 64 rows x 64 columns, 128-byte
+// swizzle; rows past the end of the sequence are zero-filled by the copy engine) and the MMAs read
+// them through swizzled descriptors.  TMA = false: the same tiles staged with cp.async in the
+// un-swizzled layout (kept as a cross-check and for drivers without the tensor-map entry point).
+constexpr int kPrepSmem = 32768 + 16384 + 3 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 1024;
 
-__global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
+struct alignas(64) PrepMaps {
+  CUtensorMap k, q, v;  // [B,T,H,128] bf16 viewed as (D, H, T, B), box (64, 1, 64, 1)
+};
+
+template <bool TMA>
+__global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_constant__ PrepMaps maps) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
   uint8_t* Akq = sm;                    // [128: k rows 0-63, q rows 64-127][128]
   uint8_t* Vt = Akq + 32768;            // [64 m][128]  v
   uint8_t* Tt = Vt + 16384;             // [64 i][64 m] T
@@ -35,8 +49,8 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
   float* gam = Am + C * LDA;
   float* bet = gam + C;
   float* bd = bet + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(bd + C);
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(bd + C);  // [0] MMA completion, [1] k,q landed, [2] v landed
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
@@ -44,7 +58,25 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
   auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
   const int imax = min(C, p.T - t0);
 
-  {  // group 0: [k;q]   group 1: v
+  if (tid == 0) {
+    tc::mbar_init(&mbar[0], 1);
+    tc::mbar_init(&mbar[1], 1);
+    tc::mbar_init(&mbar[2], 1);
+    tc::mbar_fence_init();
+  }
+  if (TMA) {
+    __syncthreads();  // barriers initialised before the copies can complete on them
+    if (tid == 0) {
+      // slab s (columns 64 s ..) of [k;q]: k box then q box; v: one box per slab
+      tc::mbar_expect_tx(&mbar[1], 32768);
+      for (int sl = 0; sl < 2; ++sl) {
+        tc::tma_load_4d(tc::smem_u32(Akq + sl * 16384), &maps.k, 64 * sl, h, t0, b, &mbar[1]);
+        tc::tma_load_4d(tc::smem_u32(Akq + sl * 16384 + 8192), &maps.q, 64 * sl, h, t0, b, &mbar[1]);
+      }
+      tc::mbar_expect_tx(&mbar[2], 16384);
+      for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(tc::smem_u32(Vt + sl * 8192), &maps.v, 64 * sl, h, t0, b, &mbar[2]);
+    }
+  } else {  // group 0: [k;q]   group 1: v
     const uint32_t sa = tc::smem_u32(Akq), sv = tc::smem_u32(Vt);
     for (int u = tid; u < 128 * 16; u += 128) {
       const int r = u >> 4, c8 = u & 15, i = r & 63;
@@ -64,10 +96,6 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
     tc::tmem_alloc(tslot, 256);
     tc::tmem_relinquish();
   }
-  if (tid == 0) {
-    tc::mbar_init(mbar, 1);
-    tc::mbar_fence_init();
-  }
   if (warp == 1) {  // in-chunk inclusive cumulative sum of the log gate: two elements per lane
     const bool ok0 = 2 * lane < imax, ok1 = 2 * lane + 1 < imax;
     const float g0 = ok0 ? log_gate_tc(p.gate[row(2 * lane)], p.gate_is_log) : 0.f;
@@ -86,20 +114,21 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
     p.gam[ci * C + 2 * lane] = c0;
     p.gam[ci * C + 2 * lane + 1] = c1;
   }
-  tc::cp_async_wait<1>();  // [k;q]
+  bool ok = true;
+  if (TMA) ok = tc::mbar_wait(&mbar[1], 0);  // [k;q]
+  else tc::cp_async_wait<1>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t taddr = *tslot;
-  bool ok = true;
   // D0[128 x 64] = [k;q] k^T
   if (tid == 0) {
-    const tc::Tile a = tc::kmajor_tile(Akq, KD);
+    const tc::Tile a = TMA ? tc::kmajor_sw128_tile(Akq, 16384) : tc::kmajor_tile(Akq, KD);
     tc::issue_gemm(taddr, a, a, 128, 64, KD, false);  // B = first 64 rows of the same tile
     tc::mma_commit(mbar);
   }
-  ok = tc::mbar_wait(mbar, 0);
+  if (ok) ok = tc::mbar_wait(mbar, 0);
   tc::fence_after_sync();
   if (ok) {
     const int i = tid & 63;
@@ -150,15 +179,18 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p) {
       *reinterpret_cast<bf16*>(Tbd + off) = __float2bfloat16_rn(Tc[i] * bdm);
     }
   }
-  tc::cp_async_wait<0>();  // v
+  if (TMA) { if (ok) ok = tc::mbar_wait(&mbar[2], 0); }  // v
+  else tc::cp_async_wait<0>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   // D1[64 x 256] = [ (T beta) v | (T beta d) k ]  -> u | w     (v, k contracted over their rows)
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr, tc::kmajor_tile(Tb, C), tc::mnmajor_tile(Vt, KD), 64, KD, C, false);
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Tbd, C), tc::mnmajor_tile(Akq, KD), 64, KD, C, false);
+    const tc::Tile bv = TMA ? tc::mnmajor_sw128_tile(Vt, 8192) : tc::mnmajor_tile(Vt, KD);
+    const tc::Tile bk = TMA ? tc::mnmajor_sw128_tile(Akq, 16384) : tc::mnmajor_tile(Akq, KD);
+    tc::issue_gemm(taddr, tc::kmajor_tile(Tb, C), bv, 64, KD, C, false);
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Tbd, C), bk, 64, KD, C, false);
     tc::mma_commit(mbar);
   }
   // T -> workspace (bf16, row-major) while the MMA runs
@@ -461,11 +493,52 @@ static mxb_status tc_set_smem(KernelT kern, int bytes) {
 
 mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st);
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+// [B,T,H,128] bf16 as a 4-d tensor (D, H, T, B) with boxes of 64 columns x 64 time steps, 128-byte swizzle.
+static bool make_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15)) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)KD, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)KD * 2, (cuuint64_t)H * KD * 2, (cuuint64_t)T * H * KD * 2};
+  const cuuint32_t box[4] = {64, 1, 64, 1}, estr[4] = {1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool g_tc_use_tma = true;
+void gdn_tc_set_tma(bool on) { g_tc_use_tma = on; }
+
 mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
   cudaError_t e = cudaMemsetAsync(p.status, 0, 256, st);
   if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
-  if (tc_set_smem(gdn_tc_prep_kernel, kPrepSmem) != MXB_OK) return MXB_ERR_CUDA;
-  MXB_LAUNCH("gdn_tc_prep_kernel", st, (gdn_tc_prep_kernel<<<dim3(p.n, p.B * p.H), 128, kPrepSmem, st>>>(p)));
+  PrepMaps maps;
+  std::memset(&maps, 0, sizeof maps);
+  const bool tma = g_tc_use_tma && !p.no_tma && make_map_bthd(&maps.k, p.k, p.B, p.T, p.H) &&
+                   make_map_bthd(&maps.q, p.q, p.B, p.T, p.H) && make_map_bthd(&maps.v, p.v, p.B, p.T, p.H);
+  if (tma) {
+    if (tc_set_smem(gdn_tc_prep_kernel<true>, kPrepSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_prep_kernel", st,
+               (gdn_tc_prep_kernel<true><<<dim3(p.n, p.B * p.H), 128, kPrepSmem, st>>>(p, maps)));
+  } else {
+    if (tc_set_smem(gdn_tc_prep_kernel<false>, kPrepSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_prep_kernel", st,
+               (gdn_tc_prep_kernel<false><<<dim3(p.n, p.B * p.H), 128, kPrepSmem, st>>>(p, maps)));
+  }
   mxb_status s = check_launch("gdn_tc_prep_kernel");
   if (s != MXB_OK) return s;
   if (tc_set_smem(gdn_tc_state_fwd_kernel, kStateFwdSmem) != MXB_OK) return MXB_ERR_CUDA;
@@ -480,6 +553,7 @@ mxb_status gdn_tc_fwd(const mxb_gdn_desc* d, const void* q, const void* k, const
   p.q = static_cast<const bf16*>(q); p.k = static_cast<const bf16*>(k); p.v = static_cast<const bf16*>(v);
   p.beta = beta; p.gate = gate; p.h0 = h0; p.out = static_cast<bf16*>(out); p.hT = hT;
   p.save = (d->flags & MXB_GDN_SAVE_FOR_BWD) ? 1 : 0;
+  p.no_tma = (d->flags & MXB_GDN_NO_TMA) ? 1 : 0;
   carve_tc(p, ws, p.save != 0);
   return tc_run_fwd(p, st);
 }
@@ -495,6 +569,7 @@ mxb_status gdn_tc_bwd(const mxb_gdn_desc* d, const void* q, const void* k, const
   p.dO = static_cast<const bf16*>(dO); p.dhT_in = dhT;
   p.dq = static_cast<bf16*>(dq); p.dk = static_cast<bf16*>(dk); p.dv = static_cast<bf16*>(dv);
   p.dbeta = dbeta; p.dgate = dgate; p.dh0 = dh0;
+  p.no_tma = (d->flags & MXB_GDN_NO_TMA) ? 1 : 0;
   carve_tc(p, ws, true);
   return tc_run_bwd(p, !(d->flags & MXB_GDN_BWD_USE_SAVED), st);
 }

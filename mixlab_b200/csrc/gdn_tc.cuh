@@ -15,7 +15,7 @@ constexpr int LDA = 68;   // fp32 row pitch of the 64x64 solve matrix (16-byte a
 using bf16 = __nv_bfloat16;
 
 struct TcP {
-  int B, T, H, n, gate_is_log, save;
+  int B, T, H, n, gate_is_log, save, no_tma;
   const bf16 *q, *k, *v;
   const float *beta, *gate, *h0;
   bf16* out;

@@ -130,6 +130,17 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- TMA: tiled tensor copy global -> shared, completion on an mbarrier ------------------
+// tmap: address of a CUtensorMap (kernel parameter declared __grid_constant__); the innermost
+// coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, int c0, int c1, int c2, int c3,
+                                            uint64_t* mbar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(mbar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 // ---- asynchronous 16-byte global -> shared copies (cp.async) ----------------------
 // valid == false writes 16 zero bytes (source size 0); gptr must still be a mapped address.
 __device__ __forceinline__ void cp_async16(uint32_t saddr, const void* gptr, bool valid = true) {

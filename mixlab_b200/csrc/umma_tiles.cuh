@@ -19,6 +19,9 @@ struct Tile {
   uint32_t saddr;  // shared-memory byte address of the tile
   uint32_t lbo, sbo, kstep;
   int mn_major;
+  uint32_t swizzle = kSwizzleNone;
+  uint32_t slab_ksteps = 0;   // K-steps per slab (0: the tile is one piece)
+  uint32_t slab_stride = 0;   // byte distance between consecutive slabs along K
 };
 
 __device__ __forceinline__ Tile kmajor_tile(const void* smem, int kcols) {
@@ -27,6 +30,23 @@ __device__ __forceinline__ Tile kmajor_tile(const void* smem, int kcols) {
 __device__ __forceinline__ Tile mnmajor_tile(const void* smem, int mn) {
   const uint32_t lbo = (uint32_t)(mn / 8) * 128u;
   return Tile{smem_u32(smem), lbo, 128u, 2u * lbo, 1};
+}
+// Tiles written by TMA with 128-byte swizzle: slabs of [rows][64 bf16] (128-byte rows, 8-row groups
+// 1024 bytes apart), slab s holding columns 64 s .. 64 s + 63; slabs are slab_bytes apart and 1024-byte
+// aligned.  K-major view: contraction along the columns (4 K-steps of 32 bytes per slab, then the next slab).
+__device__ __forceinline__ Tile kmajor_sw128_tile(const void* smem, uint32_t slab_bytes) {
+  Tile t{smem_u32(smem), 16u, 1024u, 32u, 0};
+  t.swizzle = kSwizzle128;
+  t.slab_ksteps = 4;
+  t.slab_stride = slab_bytes;
+  return t;
+}
+// MN-major view of the same bytes: contraction along the rows (a K-step = 16 rows = 2048 bytes); the
+// 64-column slabs are consecutive blocks of the M/N extent, slab_bytes apart (leading byte offset).
+__device__ __forceinline__ Tile mnmajor_sw128_tile(const void* smem, uint32_t slab_bytes) {
+  Tile t{smem_u32(smem), slab_bytes, 1024u, 2048u, 1};
+  t.swizzle = kSwizzle128;
+  return t;
 }
 // Sub-tile starting at row r0 (multiple of 8) of a K-major tile / at column m0 (multiple
 // of 8) of an MN-major tile.
@@ -48,10 +68,13 @@ __device__ __forceinline__ uint32_t mnmajor_unit(int k, int c8, int mn) {
 __device__ __forceinline__ void issue_gemm(uint32_t tmem_d, const Tile& a, const Tile& b, int M, int N, int ktotal,
                                            bool accumulate) {
   const uint32_t idesc = make_idesc_bf16(M, N, a.mn_major, b.mn_major);
-  const uint64_t da = make_smem_desc(a.saddr, a.lbo, a.sbo, kSwizzleNone);
-  const uint64_t db = make_smem_desc(b.saddr, b.lbo, b.sbo, kSwizzleNone);
+  const uint64_t da = make_smem_desc(a.saddr, a.lbo, a.sbo, a.swizzle);
+  const uint64_t db = make_smem_desc(b.saddr, b.lbo, b.sbo, b.swizzle);
+  auto koff = [](const Tile& t, uint32_t ks) {
+    return t.slab_ksteps ? (ks / t.slab_ksteps) * t.slab_stride + (ks % t.slab_ksteps) * t.kstep : ks * t.kstep;
+  };
   for (int ks = 0; ks < ktotal / 16; ++ks)
-    mma_ss(tmem_d, da + (uint64_t)((ks * a.kstep) >> 4), db + (uint64_t)((ks * b.kstep) >> 4), idesc,
+    mma_ss(tmem_d, da + (uint64_t)(koff(a, ks) >> 4), db + (uint64_t)(koff(b, ks) >> 4), idesc,
            (accumulate || ks > 0) ? 1u : 0u);
 }
 
