@@ -39,6 +39,9 @@ GDN_BYTES_PER_TOKEN_HEAD = 2840          # fwd 1032 + bwd read 1032 + bwd write 
 GDN_FLOPS_PER_TOKEN_HEAD = 3 * 182955    # fwd + 2x for bwd
 M3_BYTES_PER_TOKEN = 23168
 M3_FLOPS_PER_TOKEN = 5.50e6
+# DRAM traffic per unit from the committed ncu captures (profiles/): dram__bytes_read.sum + dram__bytes_write.sum
+GDN_NCU_TRAFFIC_PER_CHUNK = 1051.4e6 / 2048    # B=2 capture: 1051.4 MB over 2048 (batch, head, chunk) units
+DECODE_NCU_TRAFFIC_PER_TILE = 482.8e6 / 4096   # full-size capture: 482.8 MB over 256 x 16 (sequence, head) tiles
 
 
 def peaks():
@@ -206,6 +209,8 @@ def main():
         alg_bytes = units * H * GDN_BYTES_PER_TOKEN_HEAD
         alg_flops = units * H * GDN_FLOPS_PER_TOKEN_HEAD
         bound = "hbm"
+        traffic = B * H * ((T + Cc - 1) // Cc) * GDN_NCU_TRAFFIC_PER_CHUNK if not args.fp32_path else None
+        traffic_note = "ncu capture at B=2 scaled by the number of (batch, head, chunk) units"
 
         def step():
             ops.gated_delta_scan(d["q"], d["k"], d["v"], d["beta"], d["g"], Cc, gate_is_log=True, flags=flags,
@@ -230,6 +235,8 @@ def main():
         alg_bytes = units * per_tok_bytes
         alg_flops = units * H * 7 * K * V
         bound = "hbm"
+        traffic = tps * N * H * DECODE_NCU_TRAFFIC_PER_TILE if (K, V) == (128, 128) else None
+        traffic_note = "ncu capture of one launch at config 2, per launch x launches per step"
 
         def step():
             for t in range(tps):
@@ -254,6 +261,7 @@ def main():
         alg_bytes = units * M3_BYTES_PER_TOKEN
         alg_flops = units * M3_FLOPS_PER_TOKEN
         bound = "hbm"
+        traffic, traffic_note = None, "not captured"
         margs = [d[k] for k in ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")]
 
         def step():
@@ -303,7 +311,7 @@ def main():
     kern_ms_step = ksum / args.steps
     achieved = alg_bytes / (kern_ms_step * 1e-3) / 1e9
     roofline = {"bound": bound, "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                "frac": achieved / pk["hbm"], "traffic": None, "peak_source": pk["src"],
+                "frac": achieved / pk["hbm"], "traffic": traffic, "traffic_note": traffic_note, "peak_source": pk["src"],
                 "scope": "all kernels of one step (algorithmic bytes of the step / summed kernel time)",
                 "top_kernel": top, "kernels": kernels,
                 "tensor_tflops": alg_flops / (kern_ms_step * 1e-3) / 1e12,
