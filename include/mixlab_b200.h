@@ -170,8 +170,10 @@ typedef struct {
 } mxb_mamba3_desc;
 
 enum {
-  MXB_MAMBA3_CHANNEL_KERNELS = 1 /* head-broadcast layout: use the warp-per-channel kernels even
-                                    where the CTA-per-head kernels cover the shape */
+  MXB_MAMBA3_CHANNEL_KERNELS = 1,  /* head-broadcast layout: use the warp-per-channel kernels even
+                                      where the CTA-per-head kernels cover the shape */
+  MXB_MAMBA3_RECURRENT_KERNELS = 2 /* use the recurrent (CTA-per-head) kernels even where the chunked
+                                      tensor-core kernels cover the shape */
 };
 
 MXB_API size_t mxb_mamba3_fwd_workspace_bytes(const mxb_mamba3_desc* d);

@@ -82,7 +82,7 @@ mxb_status umma_selftest(const void*, uint32_t, const void*, uint32_t, const uin
 bool mamba3_supported(const mxb_mamba3_desc*);
 size_t mamba3_workspace_bytes(const mxb_mamba3_desc*, bool bwd);
 mxb_status mamba3_fwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*,
-                      const float*, const void*, const void*, void*, cudaStream_t);
+                      const float*, const void*, const void*, void*, void*, cudaStream_t);
 mxb_status mamba3_bwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*,
                       const float*, const void*, const void*, const void*, void*, float*, float*,
                       float*, float*, void*, void*, void*, cudaStream_t);
@@ -244,8 +244,9 @@ mxb_status mxb_mamba3_fwd(const mxb_mamba3_desc* d, const void* x, const float* 
   mxb_status s = check_m3_desc(d);
   if (s != MXB_OK) return s;
   if (!x || !dt || !lambda || !theta || !a_log || !b || !c || !y) return MXB_ERR_INVALID_ARGUMENT;
-  (void)workspace; (void)workspace_bytes;
-  return mamba3_fwd(d, x, dt, lambda, theta, a_log, b, c, y, static_cast<cudaStream_t>(stream));
+  const size_t need = mamba3_workspace_bytes(d, false);
+  if (need > 0 && (!workspace || workspace_bytes < need)) return MXB_ERR_WORKSPACE;
+  return mamba3_fwd(d, x, dt, lambda, theta, a_log, b, c, y, workspace, static_cast<cudaStream_t>(stream));
 }
 
 mxb_status mxb_mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lambda,

@@ -328,6 +328,16 @@ __global__ void m3_cast_kernel(const float* __restrict__ src, IO* __restrict__ d
 bool mamba3_head_supported(const mxb_mamba3_desc* d);
 bool mamba3_head_bwd_supported(const mxb_mamba3_desc* d);
 size_t mamba3_head_partial_floats(const mxb_mamba3_desc* d);
+bool mamba3_ssd_supported(const mxb_mamba3_desc* d);
+size_t mamba3_ssd_workspace_bytes(const mxb_mamba3_desc* d, bool bwd);
+mxb_status mamba3_ssd_fwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
+                          const void*, const void*, void*, void*, cudaStream_t);
+mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
+                          const void*, const void*, const void*, void*, float*, float*, float*, float*, void*, void*,
+                          void*, cudaStream_t);
+static bool use_ssd(const mxb_mamba3_desc* d) {
+  return !(d->flags & (MXB_MAMBA3_CHANNEL_KERNELS | MXB_MAMBA3_RECURRENT_KERNELS)) && mamba3_ssd_supported(d);
+}
 int mamba3_head_window();
 mxb_status mamba3_head_bwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
                            const void*, const void*, const void*, void*, float*, float*, float*, float*, void*, void*,
@@ -366,6 +376,7 @@ static size_t carve_m3(M3P& p, void* ws, bool io_f32, size_t partial_floats = 0,
 }
 
 size_t mamba3_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
+  if (use_ssd(d)) return mamba3_ssd_workspace_bytes(d, bwd);
   if (!bwd) return 0;
   M3P p = make_m3(d);
   const bool head = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
@@ -407,8 +418,9 @@ mxb_status mamba3_head_fwd(const mxb_mamba3_desc*, const void*, const float*, co
                            const void*, const void*, void*, float*, float*, cudaStream_t);
 
 mxb_status mamba3_fwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
-                      const float* theta, const float* a_log, const void* b, const void* c, void* y,
+                      const float* theta, const float* a_log, const void* b, const void* c, void* y, void* ws,
                       cudaStream_t st) {
+  if (use_ssd(d)) return mamba3_ssd_fwd(d, x, dt, lam, theta, a_log, b, c, y, ws, st);
   if (!(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_supported(d))
     return mamba3_head_fwd(d, x, dt, lam, theta, a_log, b, c, y, nullptr, nullptr, st);
   M3P p = make_m3(d);
@@ -420,6 +432,8 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
                       const float* theta, const float* a_log, const void* b, const void* c,
                       const void* dy, void* dx, float* ddt, float* dlam, float* dtheta, float* da_log,
                       void* db, void* dc, void* ws, cudaStream_t st) {
+  if (use_ssd(d))
+    return mamba3_ssd_bwd(d, x, dt, lam, theta, a_log, b, c, dy, dx, ddt, dlam, dtheta, da_log, db, dc, ws, st);
   M3P p = make_m3(d);
   const bool f32 = d->io_dtype == MXB_F32;
   p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c;

@@ -1,0 +1,752 @@
+// Mamba-3 selective scan in chunked dual ("SSD") form on tensor cores - head-broadcast
+// layout (dt, lambda, theta per (b,t,head), A per head), head dim 64, d_state 128, bf16 I/O.
+//
+// With scalar decay per (step, head) the exponential-trapezoidal recurrence
+//     h_t = alpha_t h_{t-1} + gamma_t Brot_t x_t^T + beta_t Brot_{t-1} x_{t-1}^T ,  y_t = Crot_t^T h_t
+// (reference: gpu/cuda_kernels/mamba3_selective_scan_fwd_v2_emit.cu:65-115) has the closed form
+//     y_t = sum_{s<=t} (Crot_t . Brot_s) exp(Lam_t - Lam_s) w_ts x_s ,   Lam = cumsum(dt A),
+//     w_ts = e_s = gamma_s + (1-lambda_{s+1}) dt_{s+1}  for s < t,   w_tt = gamma_t,
+// because beta_{s+1} exp(Lam_t - Lam_{s+1}) = (1-lambda_{s+1}) dt_{s+1} exp(Lam_t - Lam_s).  Per chunk of
+// 64 steps (M_ts = exp(Lam_t-Lam_s) w_ts [s<=t], r_s = exp(Lam_end - Lam_s), L = exp(Lam_end)):
+//     Y  = (Crot Brot^T * M) X + diag(exp(Lam)) Crot H0          H1 = L H0 + Brot^T diag(r e) X
+// so the only sequential part is the elementwise chunk scan H1 = L H0 + Hc.  The backward is the
+// hand-derived adjoint of these two lines (checked against float64 autograd of the recurrence
+// before it was written); its sequential part is the mirrored scan dH0 = L dH1 + Dc.
+//
+//   m3s_scalars_kernel      per (b, head): dt, lambda, wrapped cumulative angle (fp64 prefix sum)
+//   m3s_chunk_outer_kernel  per chunk: Hc = Brot^T diag(r e) X   or   Dc = Crot^T diag(exp(Lam)) dY
+//   m3s_scan_kernel         per (b, head): elementwise scan over the chunks, forward or reverse
+//   m3s_chunk_out_kernel    per chunk: Y
+//   m3s_chunk_grad_kernel   per chunk: dx, rotated-row gradients -> dB, dC partials, per-token scalars
+//   m3s_final_kernel        per (b, head): suffix sum of the angle gradient, ddt, dlambda, dtheta, da_log
+#include "common.cuh"
+#include "umma_tiles.cuh"
+
+namespace mxb {
+namespace m3s {
+
+constexpr int Q = 64;    // chunk
+constexpr int P = 64;    // head dim
+constexpr int N = 128;   // d_state
+using bf16 = __nv_bfloat16;
+
+struct SsdP {
+  int B, T, D, G, NH, n;   // n = chunks
+  const bf16 *x, *b, *c, *dy;
+  const float *dt_raw, *lam_raw, *theta, *a_log;
+  bf16 *y, *dx;
+  float *ddt, *dlam, *dtheta, *da_log;
+  int* status;
+  // workspace
+  float *dt, *lam, *phi;        // [B,NH,T]
+  float *Lc;                    // [B,NH,n]  exp(Lam_end) per chunk
+  float *Hc;                    // [B,NH,n,N,P] fp32 chunk contributions (forward: Hc, backward: Dc)
+  bf16 *H0, *dH1;               // [B,NH,n,N,P] state at chunk start / state gradient at chunk end
+  float *dphi, *da, *de, *dgam; // [B,NH,T] per-token scalar gradients
+  float *pb, *pc;               // [B,NH,T,N] per-head partial dB, dC
+};
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : (x < -20.f ? expf(x) : log1pf(expf(x))); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void sts16(uint8_t* base, uint32_t off, uint4 v) { *reinterpret_cast<uint4*>(base + off) = v; }
+__device__ __forceinline__ void unpack8(uint4 v, float (&e)[8]) {
+  tc::unpack_bf16(v.x, e[0], e[1]); tc::unpack_bf16(v.y, e[2], e[3]);
+  tc::unpack_bf16(v.z, e[4], e[5]); tc::unpack_bf16(v.w, e[6], e[7]);
+}
+__device__ __forceinline__ uint4 pack8(const float* e) {
+  return make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]), tc::pack_bf16(e[4], e[5]),
+                    tc::pack_bf16(e[6], e[7]));
+}
+__device__ __forceinline__ void ld_acc32(uint32_t taddr, int warp, int c0, float (&f)[32]) {
+  uint32_t r[32];
+  tc::tmem_ld_32x32b_x32(taddr + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0, r);
+  tc::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+}
+
+// Per-chunk scalars in shared memory (128 threads; call by all, ends with a barrier).
+struct ChunkScal {
+  float dt[Q], lam[Q], Lam[Q], gam[Q], e[Q], sn[Q], cs[Q], dexp[Q], r[Q];
+  float L, A;
+};
+__device__ __forceinline__ void load_chunk_scalars(const SsdP& p, int b, int head, int c, ChunkScal& s) {
+  const int tid = threadIdx.x, t0 = c * Q;
+  const size_t base = ((size_t)b * p.NH + head) * p.T;
+  if (tid == 0) s.A = -expf(p.a_log[head]);
+  if (tid < Q) {
+    const int t = t0 + tid;
+    const bool ok = t < p.T;
+    const float dt = ok ? p.dt[base + t] : 0.f, lam = ok ? p.lam[base + t] : 0.f;
+    const float nxt = (t + 1 < p.T) ? (1.f - p.lam[base + t + 1]) * p.dt[base + t + 1] : 0.f;
+    s.dt[tid] = dt; s.lam[tid] = lam;
+    s.gam[tid] = lam * dt;
+    s.e[tid] = lam * dt + nxt;
+    float sn = 0.f, cs = 1.f;
+    if (ok) sincosf(p.phi[base + t], &sn, &cs);
+    s.sn[tid] = sn; s.cs[tid] = cs;
+  }
+  __syncthreads();
+  if (tid < 32) {  // inclusive in-chunk cumulative sum of a = dt A, two per lane
+    const float a0 = s.dt[2 * tid] * s.A, a1 = s.dt[2 * tid + 1] * s.A;
+    float v = a0 + a1;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, v, o);
+      if (tid >= o) v += t;
+    }
+    s.Lam[2 * tid] = v - a1;
+    s.Lam[2 * tid + 1] = v;
+  }
+  __syncthreads();
+  if (tid < Q) {
+    const float last = s.Lam[Q - 1];
+    s.dexp[tid] = __expf(s.Lam[tid]);
+    s.r[tid] = __expf(last - s.Lam[tid]);
+    if (tid == 0) s.L = __expf(last);
+  }
+  __syncthreads();
+}
+
+// Rotated (and optionally row-scaled) copy of 64 rows of B or C -> blocked [64][128] bf16 tile.
+__device__ __forceinline__ void build_rot_tile(uint8_t* dst, const bf16* src, const SsdP& p, int b, int g, int t0,
+                                               const float* sn, const float* cs, const float* rowscale) {
+  for (int u = threadIdx.x; u < Q * 16; u += blockDim.x) {
+    const int t = u >> 4, c8 = u & 15;
+    float e[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (t0 + t < p.T) {
+      unpack8(ldg16(src + (((size_t)b * p.T + t0 + t) * p.G + g) * N + c8 * 8), e);
+      const float s_ = sn[t], c_ = cs[t], sc = rowscale ? rowscale[t] : 1.f;
+#pragma unroll
+      for (int k = 0; k < 8; k += 2) {
+        const float ev = e[k], od = e[k + 1];
+        e[k] = sc * (c_ * ev + s_ * od);
+        e[k + 1] = sc * (-s_ * ev + c_ * od);
+      }
+    }
+    sts16(dst, tc::kmajor_unit(t, c8, N), pack8(e));
+  }
+}
+// 64 rows x 64 channels of x or dy (optionally row-scaled) -> blocked [64][64] bf16 tile.
+__device__ __forceinline__ void build_x_tile(uint8_t* dst, const bf16* src, const SsdP& p, int b, int d0, int t0,
+                                             const float* rowscale) {
+  for (int u = threadIdx.x; u < Q * 8; u += blockDim.x) {
+    const int t = u >> 3, c8 = u & 7;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (t0 + t < p.T) {
+      v = ldg16(src + ((size_t)b * p.T + t0 + t) * p.D + d0 + c8 * 8);
+      if (rowscale) v = tc::scale_bf16x8(v, rowscale[t]);
+    }
+    sts16(dst, tc::kmajor_unit(t, c8, P), v);
+  }
+}
+
+// ------------------------------------------------------------ per-(b,head) scalars
+__global__ void __launch_bounds__(256) m3s_scalars_kernel(SsdP p) {
+  __shared__ double part[256];
+  const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const size_t base = ((size_t)b * p.NH + head) * p.T;
+  const int per = (p.T + 255) / 256, lo = tid * per, hi = min(p.T, lo + per);
+  double acc = 0.0;
+  for (int t = lo; t < hi; ++t) {
+    const size_t r = ((size_t)b * p.T + t) * p.NH + head;
+    const float dt = softplus_f(p.dt_raw[r]);
+    p.dt[base + t] = dt;
+    p.lam[base + t] = sigmoid_f(p.lam_raw[r]);
+    acc += (double)dt * (double)p.theta[r];
+  }
+  part[tid] = acc;
+  __syncthreads();
+  if (tid == 0) {
+    double run = 0.0;
+    for (int i = 0; i < 256; ++i) { const double v = part[i]; part[i] = run; run += v; }
+  }
+  __syncthreads();
+  double phi = part[tid];
+  const double two_pi = 6.283185307179586476925;
+  for (int t = lo; t < hi; ++t) {
+    const size_t r = ((size_t)b * p.T + t) * p.NH + head;
+    phi += (double)p.dt[base + t] * (double)p.theta[r];
+    p.phi[base + t] = (float)(phi - two_pi * rint(phi / two_pi));
+  }
+}
+
+// ------------------------------------------------------------ chunk outer products
+// mode 0: Hc = Brot^T diag(r e) X        mode 1: Dc = Crot^T diag(exp(Lam)) dY
+constexpr int kOuterSmem = 16384 + 8192 + sizeof(ChunkScal) + 64 + 256;
+
+__global__ void __launch_bounds__(128) m3s_chunk_outer_kernel(SsdP p, int mode) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* Rt = sm;                // [64 s][128 n] rotated B or C
+  uint8_t* Xt = Rt + 16384;        // [64 s][64 p]  scaled x or dy
+  ChunkScal& s = *reinterpret_cast<ChunkScal*>(Xt + 8192);
+  float* sc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(&s) + sizeof(ChunkScal));  // [64] row scale... reuse below
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(sc);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int c = blockIdx.x, head = blockIdx.y, b = blockIdx.z, t0 = c * Q;
+  const int d0 = head * P, g = d0 / (p.D / p.G);
+  const size_t ci = ((size_t)b * p.NH + head) * p.n + c;
+
+  if (warp == 0) { tc::tmem_alloc(tslot, 64); tc::tmem_relinquish(); }
+  if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
+  load_chunk_scalars(p, b, head, c, s);
+  if (mode == 0) {
+    if (tid < Q) s.gam[tid] = s.r[tid] * s.e[tid];  // row scale of x (gam is not needed here)
+    __syncthreads();
+    build_rot_tile(Rt, p.b, p, b, g, t0, s.sn, s.cs, nullptr);
+    build_x_tile(Xt, p.x, p, b, d0, t0, s.gam);
+    if (tid == 0) p.Lc[ci] = s.L;
+  } else {
+    build_rot_tile(Rt, p.c, p, b, g, t0, s.sn, s.cs, nullptr);
+    build_x_tile(Xt, p.dy, p, b, d0, t0, s.dexp);
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t taddr = *tslot;
+  if (tid == 0) {  // [128 n x 64 p] = R^T X, both contracted over their rows
+    tc::issue_gemm(taddr, tc::mnmajor_tile(Rt, N), tc::mnmajor_tile(Xt, P), 128, P, Q, false);
+    tc::mma_commit(mbar);
+  }
+  const bool ok = tc::mbar_wait(mbar, 0);
+  tc::fence_after_sync();
+  if (ok) {
+    float* dst = p.Hc + (ci * N + tid) * P;
+    for (int c0 = 0; c0 < P; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr, warp, c0, f);
+#pragma unroll
+      for (int x = 0; x < 8; ++x)
+        *reinterpret_cast<float4*>(dst + c0 + 4 * x) = make_float4(f[4 * x], f[4 * x + 1], f[4 * x + 2], f[4 * x + 3]);
+    }
+  } else if (tid == 0) {
+    atomicExch(p.status, 11);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(taddr, 64);
+}
+
+// ------------------------------------------------------------ elementwise chunk scan
+// forward (rev = 0): H0_c = H; H = L_c H + Hc_c          reverse (rev = 1): dH1_c = dH; dH = L_c dH + Dc_c
+__global__ void __launch_bounds__(256) m3s_scan_kernel(SsdP p, int rev) {
+  const int bh = blockIdx.x, tid = threadIdx.x;
+  const size_t cbase = (size_t)bh * p.n;
+  bf16* out = rev ? p.dH1 : p.H0;
+  float h[32];  // elements tid*4 + 1024*k .. (float4 granules, coalesced)
+#pragma unroll
+  for (int k = 0; k < 32; ++k) h[k] = 0.f;
+  for (int i = 0; i < p.n; ++i) {
+    const int c = rev ? p.n - 1 - i : i;
+    const float L = p.Lc[cbase + c];
+    const float* src = p.Hc + (cbase + c) * (N * P);
+    bf16* dst = out + (cbase + c) * (N * P);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int off = (k * 256 + tid) * 4;
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src + off));
+      *reinterpret_cast<uint2*>(dst + off) =
+          make_uint2(tc::pack_bf16(h[4 * k], h[4 * k + 1]), tc::pack_bf16(h[4 * k + 2], h[4 * k + 3]));
+      h[4 * k] = fmaf(L, h[4 * k], v.x); h[4 * k + 1] = fmaf(L, h[4 * k + 1], v.y);
+      h[4 * k + 2] = fmaf(L, h[4 * k + 2], v.z); h[4 * k + 3] = fmaf(L, h[4 * k + 3], v.w);
+    }
+  }
+}
+
+
+// Copies a [128 n][64 p] bf16 workspace matrix into a blocked shared-memory tile.
+__device__ __forceinline__ void build_state_tile(uint8_t* dst, const bf16* src) {
+  for (int u = threadIdx.x; u < N * 8; u += blockDim.x) {
+    const int r = u >> 3, c8 = u & 7;
+    sts16(dst, tc::kmajor_unit(r, c8, P), ldg16(src + r * P + c8 * 8));
+  }
+}
+
+// ------------------------------------------------------------ chunk output
+constexpr int kOutSmem = 16384 * 3 + 8192 * 2 + sizeof(ChunkScal) + 64 + 256;
+
+__global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* Bt = sm;               // [64][128] Brot
+  uint8_t* Ct = Bt + 16384;       // [64][128] Crot
+  uint8_t* Ht = Ct + 16384;       // [128][64] H0
+  uint8_t* Xt = Ht + 16384;       // [64][64]  x
+  uint8_t* Gm = Xt + 8192;        // [64][64]  (Crot Brot^T) * M
+  ChunkScal& s = *reinterpret_cast<ChunkScal*>(Gm + 8192);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(&s + 1);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, head = blockIdx.y, b = blockIdx.z, t0 = c * Q;
+  const int d0 = head * P, g = d0 / (p.D / p.G);
+  const size_t ci = ((size_t)b * p.NH + head) * p.n + c;
+
+  if (warp == 0) { tc::tmem_alloc(tslot, 256); tc::tmem_relinquish(); }
+  if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
+  load_chunk_scalars(p, b, head, c, s);
+  build_rot_tile(Bt, p.b, p, b, g, t0, s.sn, s.cs, nullptr);
+  build_rot_tile(Ct, p.c, p, b, g, t0, s.sn, s.cs, nullptr);
+  build_x_tile(Xt, p.x, p, b, d0, t0, nullptr);
+  build_state_tile(Ht, p.H0 + ci * (N * P));
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t taddr = *tslot;
+  if (tid == 0) {
+    tc::issue_gemm(taddr, tc::kmajor_tile(Ct, N), tc::kmajor_tile(Bt, N), 64, Q, N, false);        // G = Crot Brot^T
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);  // Crot H0
+    tc::mma_commit(mbar);
+  }
+  bool ok = tc::mbar_wait(mbar, 0);
+  tc::fence_after_sync();
+  const int t = 16 * warp + (lane & 15);
+  const bool own = lane < 16;
+  if (ok) {
+    const float lt = s.Lam[t], gt = s.gam[t];
+    for (int c0 = 0; c0 < Q; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const int sx = c0 + jj;
+          f[jj] = (sx <= t) ? f[jj] * __expf(lt - s.Lam[sx]) * (sx < t ? s.e[sx] : gt) : 0.f;
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Gm, tc::kmajor_unit(t, (c0 >> 3) + x, Q), pack8(&f[8 * x]));
+      }
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Gm, Q), tc::mnmajor_tile(Xt, P), 64, P, Q, false);  // (G*M) X
+    tc::mma_commit(mbar);
+  }
+  if (ok) ok = tc::mbar_wait(mbar, 1);
+  tc::fence_after_sync();
+  if (ok) {
+    const float de = s.dexp[t];
+    for (int c0 = 0; c0 < P; c0 += 32) {
+      float f[32], f2[32];
+      ld_acc32(taddr + 128, warp, c0, f);
+      ld_acc32(taddr + 64, warp, c0, f2);
+      if (own && t0 + t < p.T) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) f[jj] = fmaf(de, f2[jj], f[jj]);
+        uint4* dst = reinterpret_cast<uint4*>(p.y + ((size_t)b * p.T + t0 + t) * p.D + d0 + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+      }
+    }
+  } else if (tid == 0) {
+    atomicExch(p.status, 12);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+}
+
+// ------------------------------------------------------------ chunk gradients
+// TMEM columns: G [0,64) -> dx ; dY X^T [64,128) ; Crot H0 [128,192) ; Brot dH1 [192,256) ;
+//               dCrot [256,384) ; dBrot [384,512).  All accumulators are M=64: row i of every result is in
+//               TMEM lane (i%16)+32*(i/16); warps 0-3 take the first half of the columns, warps 4-7 the second.
+constexpr int kGradSmem = 16384 * 4 + 8192 * 6 + sizeof(ChunkScal) + (4 * Q + 4 * Q + 8 * Q + 32) * 4 + 64 + 256;
+
+__device__ __forceinline__ float row_dot32_64(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
+  float acc = 0.f;  // sum_k tile[r][c0 + k] f[k] for a blocked [.][64] tile
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    float e[8];
+    unpack8(*reinterpret_cast<const uint4*>(tile + tc::kmajor_unit(r, (c0 >> 3) + x, P)), e);
+#pragma unroll
+    for (int y = 0; y < 8; ++y) acc = fmaf(e[y], f[8 * x + y], acc);
+  }
+  return acc;
+}
+
+__global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* Bt = sm;                // [64][128] Brot
+  uint8_t* Ct = Bt + 16384;        // [64][128] Crot
+  uint8_t* Ht = Ct + 16384;        // [128][64] H0
+  uint8_t* Dt = Ht + 16384;        // [128][64] dH1
+  uint8_t* Xt = Dt + 16384;        // [64][64]  x
+  uint8_t* Yt = Xt + 8192;         // [64][64]  dY
+  uint8_t* Xs = Yt + 8192;         // [64][64]  r e x
+  uint8_t* Ys = Xs + 8192;         // [64][64]  exp(Lam) dY
+  uint8_t* GMt = Ys + 8192;        // [64][64]  G*M
+  uint8_t* dGt = GMt + 8192;       // [64][64]  dG
+  ChunkScal& s = *reinterpret_cast<ChunkScal*>(dGt + 8192);
+  float* csw_e = reinterpret_cast<float*>(&s + 1);  // [4][Q] per-warp column sums for de
+  float* csw_l = csw_e + 4 * Q;                     // [4][Q] per-warp column sums for dLam
+  float* part = csw_l + 4 * Q;                      // [2][4][Q]: per half: dLam, de, dgam, dphi row partials
+  float* red = part + 8 * Q;                        // [32]
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + 32);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, head = blockIdx.y, b = blockIdx.z, t0 = c * Q;
+  const int d0 = head * P, g = d0 / (p.D / p.G);
+  const size_t ci = ((size_t)b * p.NH + head) * p.n + c;
+  const bool own = lane < 16;
+  const int t = 16 * (warp & 3) + (lane & 15), hc = warp >> 2;
+
+  if (warp == 0) { tc::tmem_alloc(tslot, 512); tc::tmem_relinquish(); }
+  if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
+  load_chunk_scalars(p, b, head, c, s);
+  for (int u = tid; u < 8 * Q; u += 256) { csw_e[u] = 0.f; }  // csw_e and csw_l are contiguous
+  float* re = part;  // [Q] row scale r e of x (part itself is written only at the end)
+  if (tid < Q) re[tid] = s.r[tid] * s.e[tid];
+  __syncthreads();
+  build_rot_tile(Bt, p.b, p, b, g, t0, s.sn, s.cs, nullptr);
+  build_rot_tile(Ct, p.c, p, b, g, t0, s.sn, s.cs, nullptr);
+  build_x_tile(Xt, p.x, p, b, d0, t0, nullptr);
+  build_x_tile(Xs, p.x, p, b, d0, t0, re);
+  build_x_tile(Yt, p.dy, p, b, d0, t0, nullptr);
+  build_x_tile(Ys, p.dy, p, b, d0, t0, s.dexp);
+  build_state_tile(Ht, p.H0 + ci * (N * P));
+  build_state_tile(Dt, p.dH1 + ci * (N * P));
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t taddr = *tslot;
+  if (tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Ct, N), tc::kmajor_tile(Bt, N), 64, Q, N, false);       // G
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Yt, P), tc::kmajor_tile(Xt, P), 64, Q, P, false);      // dY X^T
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);    // Crot H0
+    tc::issue_gemm(taddr + 192, tc::kmajor_tile(Bt, N), tc::mnmajor_tile(Dt, P), 64, P, N, false);    // Brot dH1
+    tc::issue_gemm(taddr + 256, tc::kmajor_tile(Ys, P), tc::kmajor_tile(Ht, P), 64, N, P, false);     // (e^Lam dY) H0^T
+    tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xs, P), tc::kmajor_tile(Dt, P), 64, N, P, false);     // (r e x) dH1^T
+    tc::mma_commit(mbar);
+  }
+  {  // <dH1, H0> while the tensor core works
+    float acc = 0.f;
+    for (int u = tid; u < N * 8; u += 256) {
+      float a[8], d[8];
+      unpack8(*reinterpret_cast<const uint4*>(Ht + u * 16), a);
+      unpack8(*reinterpret_cast<const uint4*>(Dt + u * 16), d);
+#pragma unroll
+      for (int y = 0; y < 8; ++y) acc = fmaf(a[y], d[y], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) red[warp] = acc;
+  }
+  bool ok = tc::mbar_wait(mbar, 0);
+  tc::fence_after_sync();
+  float dl_own = 0.f, de_own = 0.f, dg_own = 0.f, zsum = 0.f;
+  const float lt = s.Lam[t], gt = s.gam[t], et = s.e[t], rt = s.r[t], dxt = s.dexp[t];
+  if (ok) {
+    {  // G and dY X^T: 32 columns per half
+      const int c0 = 32 * hc;
+      float fg[32], fd[32];
+      ld_acc32(taddr + 0, warp, c0, fg);
+      ld_acc32(taddr + 64, warp, c0, fd);
+      float rs = 0.f;
+      float gm[32], dg[32];
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) {
+        const int sx = c0 + jj;
+        float Mv = 0.f, Dv = 0.f;
+        const bool in = own && sx <= t;
+        if (in) {
+          Dv = __expf(lt - s.Lam[sx]);
+          Mv = Dv * (sx < t ? s.e[sx] : gt);
+        }
+        const float dGM = in ? fd[jj] : 0.f;
+        gm[jj] = fg[jj] * Mv;             // (G*M)_ts
+        dg[jj] = dGM * Mv;                // dG_ts
+        const float dM = dGM * fg[jj];
+        const float dw = dM * Dv;
+        const float ml = dM * Mv;
+        rs += ml;
+        if (in && sx == t) dg_own += dw;
+        const float ce = warp_sum((in && sx < t) ? dw : 0.f);   // de_s: column sums over the rows of this warp
+        const float cl = warp_sum(ml);
+        if (lane == 0) { csw_e[(warp & 3) * Q + sx] += ce; csw_l[(warp & 3) * Q + sx] -= cl; }
+      }
+      dl_own += rs;
+      if (own) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          sts16(GMt, tc::kmajor_unit(t, (c0 >> 3) + x, Q), pack8(&gm[8 * x]));
+          sts16(dGt, tc::kmajor_unit(t, (c0 >> 3) + x, Q), pack8(&dg[8 * x]));
+        }
+      }
+    }
+    {  // kappa_t = exp(Lam_t) dY_t . (Crot H0)_t   and   zeta_s = (Brot dH1)_s . x_s   (32 channels per half)
+      const int c0 = 32 * hc;
+      float f[32];
+      ld_acc32(taddr + 128, warp, c0, f);
+      if (own) dl_own += dxt * row_dot32_64(Yt, t, c0, f);
+      ld_acc32(taddr + 192, warp, c0, f);
+      if (own) {
+        const float zeta = row_dot32_64(Xt, t, c0, f);
+        de_own += rt * zeta;
+        dl_own -= rt * et * zeta;
+        zsum = rt * et * zeta;
+      }
+    }
+  }
+  {
+    const float tot = warp_sum(own ? zsum : 0.f);
+    if (lane == 0) red[8 + warp] = tot;
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(GMt, Q), tc::mnmajor_tile(Yt, P), 64, P, Q, false);    // (G*M)^T dY
+    tc::issue_gemm(taddr + 256, tc::kmajor_tile(dGt, Q), tc::mnmajor_tile(Bt, N), 64, N, Q, true);    // + dG Brot
+    tc::issue_gemm(taddr + 384, tc::mnmajor_tile(dGt, Q), tc::mnmajor_tile(Ct, N), 64, N, Q, true);   // + dG^T Crot
+    tc::mma_commit(mbar);
+  }
+  if (ok) ok = tc::mbar_wait(mbar, 1);
+  tc::fence_after_sync();
+  float dphi_own = 0.f;
+  if (ok) {
+    {  // dx_s = (G*M)^T dY + r e (Brot dH1)
+      const int c0 = 32 * hc;
+      float f[32], f2[32];
+      ld_acc32(taddr + 0, warp, c0, f);
+      ld_acc32(taddr + 192, warp, c0, f2);
+      if (own && t0 + t < p.T) {
+        const float sc = rt * et;
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) f[jj] = fmaf(sc, f2[jj], f[jj]);
+        uint4* dst = reinterpret_cast<uint4*>(p.dx + ((size_t)b * p.T + t0 + t) * p.D + d0 + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+      }
+    }
+    // rotated-row gradients: un-rotate into the per-head partial rows, and the angle gradient
+    const float sn = s.sn[t], cs = s.cs[t];
+    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
+      float gc[32], gb[32];
+      ld_acc32(taddr + 256, warp, c0, gc);
+      ld_acc32(taddr + 384, warp, c0, gb);
+      if (own && t0 + t < p.T) {
+        float* pbr = p.pb + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
+        float* pcr = p.pc + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float br[8], cr[8], ob[8], oc[8];
+          unpack8(*reinterpret_cast<const uint4*>(Bt + tc::kmajor_unit(t, (c0 >> 3) + x, N)), br);
+          unpack8(*reinterpret_cast<const uint4*>(Ct + tc::kmajor_unit(t, (c0 >> 3) + x, N)), cr);
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) {
+            const float b0 = gb[8 * x + k], b1 = gb[8 * x + k + 1], c0v = gc[8 * x + k], c1v = gc[8 * x + k + 1];
+            ob[k] = cs * b0 - sn * b1; ob[k + 1] = sn * b0 + cs * b1;
+            oc[k] = cs * c0v - sn * c1v; oc[k + 1] = sn * c0v + cs * c1v;
+            dphi_own += br[k + 1] * b0 - br[k] * b1 + cr[k + 1] * c0v - cr[k] * c1v;
+          }
+          *reinterpret_cast<float4*>(pbr + 8 * x) = make_float4(ob[0], ob[1], ob[2], ob[3]);
+          *reinterpret_cast<float4*>(pbr + 8 * x + 4) = make_float4(ob[4], ob[5], ob[6], ob[7]);
+          *reinterpret_cast<float4*>(pcr + 8 * x) = make_float4(oc[0], oc[1], oc[2], oc[3]);
+          *reinterpret_cast<float4*>(pcr + 8 * x + 4) = make_float4(oc[4], oc[5], oc[6], oc[7]);
+        }
+      }
+    }
+  }
+  if (own) {
+    part[(hc * 4 + 0) * Q + t] = dl_own;
+    part[(hc * 4 + 1) * Q + t] = de_own;
+    part[(hc * 4 + 2) * Q + t] = dg_own;
+    part[(hc * 4 + 3) * Q + t] = dphi_own;
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (tid == 0) {  // dLam -> da: reverse in-chunk cumulative sum (fixed order)
+    float zs = 0.f, hh = 0.f;
+    for (int wv = 0; wv < 8; ++wv) { zs += red[8 + wv]; hh += red[wv]; }
+    float acc = zs + s.L * hh;  // d/dLam_end
+    for (int r = Q - 1; r >= 0; --r) {
+      acc += part[0 * Q + r] + part[4 * Q + r] + csw_l[r] + csw_l[Q + r] + csw_l[2 * Q + r] + csw_l[3 * Q + r];
+      s.Lam[r] = acc;  // Lam is dead by now: reuse for da
+    }
+  }
+  __syncthreads();
+  if (!ok && tid == 0) atomicExch(p.status, 13);
+  if (ok && tid < Q && t0 + tid < p.T) {
+    const size_t o = ((size_t)b * p.NH + head) * p.T + t0 + tid;
+    p.da[o] = s.Lam[tid];
+    p.de[o] = part[1 * Q + tid] + part[5 * Q + tid] + csw_e[tid] + csw_e[Q + tid] + csw_e[2 * Q + tid] + csw_e[3 * Q + tid];
+    p.dgam[o] = part[2 * Q + tid] + part[6 * Q + tid];
+    p.dphi[o] = part[3 * Q + tid] + part[7 * Q + tid];
+  }
+  if (warp == 0) tc::tmem_dealloc(taddr, 512);
+}
+
+
+// ------------------------------------------------------------ final per-token scalars
+__global__ void __launch_bounds__(256) m3s_final_kernel(SsdP p) {
+  __shared__ double part[256];
+  __shared__ float wsum[8];
+  const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  const size_t base = ((size_t)b * p.NH + head) * p.T;
+  const float A = -expf(p.a_log[head]);
+  const int per = (p.T + 255) / 256, lo = tid * per, hi = min(p.T, lo + per);
+  double acc = 0.0;
+  for (int t = lo; t < hi; ++t) acc += (double)p.dphi[base + t];
+  part[tid] = acc;
+  __syncthreads();
+  if (tid == 0) {  // exclusive suffix sums of the per-thread totals
+    double run = 0.0;
+    for (int i = 255; i >= 0; --i) { const double v = part[i]; part[i] = run; run += v; }
+  }
+  __syncthreads();
+  double suf = part[tid];
+  float dal = 0.f;
+  for (int t = hi - 1; t >= lo; --t) {
+    suf += (double)p.dphi[base + t];
+    const float dinc = (float)suf;
+    const size_t r = ((size_t)b * p.T + t) * p.NH + head;
+    const float dt = p.dt[base + t], lam = p.lam[base + t], th = p.theta[r];
+    const float dgam = p.dgam[base + t] + p.de[base + t];
+    const float dnxt = t > 0 ? p.de[base + t - 1] : 0.f;
+    const float da = p.da[base + t];
+    const float ddelta = A * da + lam * dgam + (1.f - lam) * dnxt + th * dinc;
+    p.ddt[r] = ddelta * sigmoid_f(p.dt_raw[r]);
+    p.dlam[r] = dt * (dgam - dnxt) * lam * (1.f - lam);
+    p.dtheta[r] = dt * dinc;
+    dal = fmaf(dt, da, dal);
+  }
+  dal = warp_sum(dal);
+  if ((tid & 31) == 0) wsum[tid >> 5] = dal;
+  __syncthreads();
+  if (tid == 0) {
+    float tot = 0.f;
+    for (int i = 0; i < 8; ++i) tot += wsum[i];
+    atomicAdd(&p.da_log[head], A * tot);  // sum over the batch
+  }
+}
+
+// dB[b,t,g,:] = sum over the heads of group g of the per-head partial rows (fixed order).
+__global__ void __launch_bounds__(128) m3s_reduce_kernel(const float* __restrict__ pb, const float* __restrict__ pc,
+                                                         bf16* __restrict__ db, bf16* __restrict__ dc, int T, int G, int NH) {
+  const int t = blockIdx.x, g = blockIdx.y, b = blockIdx.z, per = NH / G, n = threadIdx.x;
+  float sb = 0.f, sc = 0.f;
+  for (int h = g * per; h < (g + 1) * per; ++h) {
+    const size_t pi = (((size_t)b * NH + h) * T + t) * N + n;
+    sb += pb[pi];
+    sc += pc[pi];
+  }
+  const size_t gi = (((size_t)b * T + t) * G + g) * N + n;
+  db[gi] = __float2bfloat16_rn(sb);
+  dc[gi] = __float2bfloat16_rn(sc);
+}
+
+}  // namespace m3s
+
+// ------------------------------------------------------------------ host
+using m3s::SsdP;
+
+bool mamba3_ssd_supported(const mxb_mamba3_desc* d) {
+  if (d->io_dtype != MXB_BF16 || d->nheads <= 0 || d->D % d->nheads) return false;
+  if (d->D / d->nheads != m3s::P || d->N != m3s::N) return false;
+  if ((d->D / d->G) % m3s::P || d->nheads % d->G) return false;
+  return true;
+}
+
+static size_t carve_ssd(SsdP& p, void* ws, bool bwd) {
+  Carver cv(ws);
+  const size_t bh = (size_t)p.B * p.NH, nst = bh * p.n * m3s::N * m3s::P;
+  p.status = cv.take<int>(64);
+  p.dt = cv.take<float>(bh * p.T);
+  p.lam = cv.take<float>(bh * p.T);
+  p.phi = cv.take<float>(bh * p.T);
+  p.Lc = cv.take<float>(bh * p.n);
+  p.Hc = cv.take<float>(nst);
+  p.H0 = cv.take<m3s::bf16>(nst);
+  if (bwd) {
+    p.dH1 = cv.take<m3s::bf16>(nst);
+    p.dphi = cv.take<float>(bh * p.T);
+    p.da = cv.take<float>(bh * p.T);
+    p.de = cv.take<float>(bh * p.T);
+    p.dgam = cv.take<float>(bh * p.T);
+    p.pb = cv.take<float>(bh * p.T * m3s::N);
+    p.pc = cv.take<float>(bh * p.T * m3s::N);
+  }
+  return cv.bytes();
+}
+
+static SsdP make_ssd(const mxb_mamba3_desc* d) {
+  SsdP p{};
+  p.B = d->B; p.T = d->T; p.D = d->D; p.G = d->G; p.NH = d->nheads;
+  p.n = (d->T + m3s::Q - 1) / m3s::Q;
+  return p;
+}
+
+size_t mamba3_ssd_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
+  SsdP p = make_ssd(d);
+  return carve_ssd(p, nullptr, bwd);
+}
+
+template <typename KernelT>
+static mxb_status ssd_smem(KernelT k, size_t bytes) {
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
+  return MXB_OK;
+}
+
+static mxb_status ssd_forward(SsdP& p, cudaStream_t st) {
+  const dim3 gc(p.n, p.NH, p.B);
+  if (cudaMemsetAsync(p.status, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
+  MXB_LAUNCH("m3s_scalars_kernel", st, (m3s::m3s_scalars_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
+  if (ssd_smem(m3s::m3s_chunk_outer_kernel, m3s::kOuterSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("m3s_chunk_outer_kernel", st, (m3s::m3s_chunk_outer_kernel<<<gc, 128, m3s::kOuterSmem, st>>>(p, 0)));
+  MXB_LAUNCH("m3s_scan_kernel", st, (m3s::m3s_scan_kernel<<<p.B * p.NH, 256, 0, st>>>(p, 0)));
+  if (p.y) {
+    if (ssd_smem(m3s::m3s_chunk_out_kernel, m3s::kOutSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("m3s_chunk_out_kernel", st, (m3s::m3s_chunk_out_kernel<<<gc, 128, m3s::kOutSmem, st>>>(p)));
+  }
+  return check_launch("mamba3 ssd forward");
+}
+
+mxb_status mamba3_ssd_fwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
+                          const float* theta, const float* a_log, const void* b, const void* c, void* y, void* ws,
+                          cudaStream_t st) {
+  SsdP p = make_ssd(d);
+  p.x = static_cast<const m3s::bf16*>(x); p.b = static_cast<const m3s::bf16*>(b); p.c = static_cast<const m3s::bf16*>(c);
+  p.dt_raw = dt; p.lam_raw = lam; p.theta = theta; p.a_log = a_log; p.y = static_cast<m3s::bf16*>(y);
+  carve_ssd(p, ws, false);
+  return ssd_forward(p, st);
+}
+
+mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
+                          const float* theta, const float* a_log, const void* b, const void* c, const void* dy,
+                          void* dx, float* ddt, float* dlam, float* dtheta, float* da_log, void* db, void* dc, void* ws,
+                          cudaStream_t st) {
+  SsdP p = make_ssd(d);
+  p.x = static_cast<const m3s::bf16*>(x); p.b = static_cast<const m3s::bf16*>(b); p.c = static_cast<const m3s::bf16*>(c);
+  p.dy = static_cast<const m3s::bf16*>(dy); p.dx = static_cast<m3s::bf16*>(dx);
+  p.dt_raw = dt; p.lam_raw = lam; p.theta = theta; p.a_log = a_log;
+  p.ddt = ddt; p.dlam = dlam; p.dtheta = dtheta; p.da_log = da_log;
+  carve_ssd(p, ws, true);
+  p.y = nullptr;  // the forward recompute stops at the chunk states
+  mxb_status s = ssd_forward(p, st);
+  if (s != MXB_OK) return s;
+  if (cudaMemsetAsync(da_log, 0, (size_t)p.NH * sizeof(float), st) != cudaSuccess) return MXB_ERR_CUDA;
+  const dim3 gc(p.n, p.NH, p.B);
+  MXB_LAUNCH("m3s_chunk_outer_kernel", st, (m3s::m3s_chunk_outer_kernel<<<gc, 128, m3s::kOuterSmem, st>>>(p, 1)));
+  MXB_LAUNCH("m3s_scan_kernel", st, (m3s::m3s_scan_kernel<<<p.B * p.NH, 256, 0, st>>>(p, 1)));
+  if (ssd_smem(m3s::m3s_chunk_grad_kernel, m3s::kGradSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<<<gc, 256, m3s::kGradSmem, st>>>(p)));
+  MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
+  MXB_LAUNCH("m3s_reduce_kernel", st,
+             (m3s::m3s_reduce_kernel<<<dim3(p.T, p.G, p.B), m3s::N, 0, st>>>(p.pb, p.pc, static_cast<m3s::bf16*>(db),
+                                                                            static_cast<m3s::bf16*>(dc), p.T, p.G, p.NH)));
+  return check_launch("mamba3 ssd backward");
+}
+
+}  // namespace mxb

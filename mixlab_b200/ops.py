@@ -144,9 +144,11 @@ def mamba3_selective_scan(x, dt, lam, theta, a_log, b, c, *, nheads=0, flags=0):
     l = _lib.lib()
     d = mamba3_desc(x, b, nheads, flags)
     y = torch.empty_like(x)
+    nws = l.mxb_mamba3_fwd_workspace_bytes(C.byref(d))
+    ws = workspace(nws, x.device)
     _lib.check(l.mxb_mamba3_fwd(C.byref(d), _ptr(x), _ptr(_f32(dt, "dt")), _ptr(_f32(lam, "lambda")),
                                 _ptr(_f32(theta, "theta")), _ptr(_f32(a_log, "a_log")), _ptr(b), _ptr(c),
-                                _ptr(y), None, 0, _stream()), "mxb_mamba3_fwd")
+                                _ptr(y), _ptr(ws), ws.numel(), _stream()), "mxb_mamba3_fwd")
     return y
 
 
