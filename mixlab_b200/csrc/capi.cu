@@ -276,7 +276,8 @@ struct mxb_host_ctx {
   int device;
   char* arena;
   size_t arena_bytes;
-  cudaStream_t stream;           // kernels
+  cudaStream_t stream;           // kernels of the even slices
+  cudaStream_t stream2;          // kernels of the odd slices (small slices do not fill the GPU: let two overlap)
   cudaStream_t s_h2d, s_d2h;     // copy engines, one per direction
   cudaEvent_t h2d_done[2], comp_done[2], d2h_done[2];
 };
@@ -301,6 +302,7 @@ mxb_status mxb_host_ctx_create(int device, size_t arena_bytes, mxb_host_ctx** ou
   c->arena_bytes = arena_bytes;
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->arena), arena_bytes);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->stream2, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_h2d, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->s_d2h, cudaStreamNonBlocking);
   for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
@@ -327,6 +329,7 @@ void mxb_host_ctx_destroy(mxb_host_ctx* c) {
     if (c->d2h_done[i]) cudaEventDestroy(c->d2h_done[i]);
   }
   if (c->stream) cudaStreamDestroy(c->stream);
+  if (c->stream2) cudaStreamDestroy(c->stream2);
   if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
   if (c->s_d2h) cudaStreamDestroy(c->s_d2h);
   if (c->arena) cudaFree(c->arena);
@@ -379,7 +382,7 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
       o_b[sl] = cv.take<float>(ns); o_g[sl] = cv.take<float>(ns);
     }
   }
-  char* ws = cv.take<char>(ws_bytes);
+  char* wss[2] = {cv.take<char>(ws_bytes), cv.take<char>(ws_bytes)};  // one workspace per slot
   if (cv.bytes() > c->arena_bytes) return MXB_ERR_WORKSPACE;
   auto hp = [](const void* base, size_t off) { return static_cast<const char*>(base) + off; };
   auto hpw = [](void* base, size_t off) { return static_cast<char*>(base) + off; };
@@ -398,16 +401,18 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
     MXB_CUDA_TRY(cudaMemcpyAsync(i_g[sl], hp(gate, os_), cs, H2D, c->s_h2d));
     if (bwd) MXB_CUDA_TRY(cudaMemcpyAsync(i_do[sl], hp(d_out, ov_), cvb, H2D, c->s_h2d));
     MXB_CUDA_TRY(cudaEventRecord(c->h2d_done[sl], c->s_h2d));
-    MXB_CUDA_TRY(cudaStreamWaitEvent(c->stream, c->h2d_done[sl], 0));
-    if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(c->stream, c->d2h_done[sl], 0));  // slot outputs drained
-    s = mxb_gdn_fwd(&df, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, o_out[sl], nullptr, ws, ws_bytes, c->stream);
+    cudaStream_t kst = sl ? c->stream2 : c->stream;
+    char* ws = wss[sl];
+    MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->h2d_done[sl], 0));
+    if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->d2h_done[sl], 0));  // slot outputs drained
+    s = mxb_gdn_fwd(&df, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, o_out[sl], nullptr, ws, ws_bytes, kst);
     if (s != MXB_OK) return s;
     if (bwd) {
       s = mxb_gdn_bwd(&db, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, i_do[sl], nullptr, o_q[sl], o_k[sl],
-                      o_v[sl], o_b[sl], o_g[sl], nullptr, ws, ws_bytes, c->stream);
+                      o_v[sl], o_b[sl], o_g[sl], nullptr, ws, ws_bytes, kst);
       if (s != MXB_OK) return s;
     }
-    MXB_CUDA_TRY(cudaEventRecord(c->comp_done[sl], c->stream));
+    MXB_CUDA_TRY(cudaEventRecord(c->comp_done[sl], kst));
     MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[sl], 0));
     MXB_CUDA_TRY(cudaMemcpyAsync(hpw(out, ov_), o_out[sl], cvb, D2H, c->s_d2h));
     if (bwd) {
@@ -421,6 +426,7 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
   }
   MXB_CUDA_TRY(cudaStreamSynchronize(c->s_d2h));
   MXB_CUDA_TRY(cudaStreamSynchronize(c->stream));
+  MXB_CUDA_TRY(cudaStreamSynchronize(c->stream2));
   return MXB_OK;
 }
 
