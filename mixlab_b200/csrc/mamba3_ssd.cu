@@ -285,7 +285,7 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   const int d0 = head * P, g = d0 / (p.D / p.G);
   const size_t ci = ((size_t)b * p.NH + head) * p.n + c;
 
-  if (warp == 0) { tc::tmem_alloc(tslot, 256); tc::tmem_relinquish(); }
+  if (warp == 0) { tc::tmem_alloc(tslot, 128); tc::tmem_relinquish(); }
   if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
   load_chunk_scalars(p, b, head, c, s);
   build_rot_tile(Bt, p.b, p, b, g, t0, s.sn, s.cs, nullptr);
@@ -327,7 +327,7 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   __syncthreads();
   tc::fence_after_sync();
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Gm, Q), tc::mnmajor_tile(Xt, P), 64, P, Q, false);  // (G*M) X
+    tc::issue_gemm(taddr, tc::kmajor_tile(Gm, Q), tc::mnmajor_tile(Xt, P), 64, P, Q, false);  // (G*M) X, over the consumed G
     tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar, 1);
@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
     const float de = s.dexp[t];
     for (int c0 = 0; c0 < P; c0 += 32) {
       float f[32], f2[32];
-      ld_acc32(taddr + 128, warp, c0, f);
+      ld_acc32(taddr, warp, c0, f);
       ld_acc32(taddr + 64, warp, c0, f2);
       if (own && t0 + t < p.T) {
 #pragma unroll
@@ -351,14 +351,17 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   }
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+  if (warp == 0) tc::tmem_dealloc(taddr, 128);
 }
 
 // ------------------------------------------------------------ chunk gradients
-// TMEM columns: G [0,64) -> dx ; dY X^T [64,128) ; Crot H0 [128,192) ; Brot dH1 [192,256) ;
-//               dCrot [256,384) ; dBrot [384,512).  All accumulators are M=64: row i of every result is in
-//               TMEM lane (i%16)+32*(i/16); warps 0-3 take the first half of the columns, warps 4-7 the second.
-constexpr int kGradSmem = 16384 * 4 + 8192 * 6 + sizeof(ChunkScal) + (4 * Q + 4 * Q + 8 * Q + 32) * 4 + 64 + 256;
+// 256 TMEM columns and < 113 KB of shared memory, so two CTAs share an SM:
+//   phase 1: G [0,64), dY X^T [64,128), Crot H0 [128,192), Brot dH1 [192,256)
+//   phase 2: dx [0,64), dCrot [64,192)           (Brot dH1 still live in [192,256))
+//   phase 3: dBrot [0,128)
+// All accumulators are M=64: row i of every result is in TMEM lane (i%16)+32*(i/16); warps 0-3 take the
+// first half of the columns, warps 4-7 the second.  The G*M tile reuses the x tile once x is dead.
+constexpr int kGradSmem = 16384 * 4 + 8192 * 5 + sizeof(ChunkScal) + (4 * Q + 4 * Q + 8 * Q + 32) * 4 + 64 + 256;
 
 __device__ __forceinline__ float row_dot32_64(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
   float acc = 0.f;  // sum_k tile[r][c0 + k] f[k] for a blocked [.][64] tile
@@ -383,8 +386,8 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   uint8_t* Yt = Xt + 8192;         // [64][64]  dY
   uint8_t* Xs = Yt + 8192;         // [64][64]  r e x
   uint8_t* Ys = Xs + 8192;         // [64][64]  exp(Lam) dY
-  uint8_t* GMt = Ys + 8192;        // [64][64]  G*M
-  uint8_t* dGt = GMt + 8192;       // [64][64]  dG
+  uint8_t* GMt = Xt;               // [64][64]  G*M  (written after the last read of x)
+  uint8_t* dGt = Ys + 8192;        // [64][64]  dG
   ChunkScal& s = *reinterpret_cast<ChunkScal*>(dGt + 8192);
   float* csw_e = reinterpret_cast<float*>(&s + 1);  // [4][Q] per-warp column sums for de
   float* csw_l = csw_e + 4 * Q;                     // [4][Q] per-warp column sums for dLam
@@ -400,7 +403,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   const bool own = lane < 16;
   const int t = 16 * (warp & 3) + (lane & 15), hc = warp >> 2;
 
-  if (warp == 0) { tc::tmem_alloc(tslot, 512); tc::tmem_relinquish(); }
+  if (warp == 0) { tc::tmem_alloc(tslot, 256); tc::tmem_relinquish(); }
   if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
   load_chunk_scalars(p, b, head, c, s);
   for (int u = tid; u < 8 * Q; u += 256) { csw_e[u] = 0.f; }  // csw_e and csw_l are contiguous
@@ -425,8 +428,6 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
     tc::issue_gemm(taddr + 64, tc::kmajor_tile(Yt, P), tc::kmajor_tile(Xt, P), 64, Q, P, false);      // dY X^T
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);    // Crot H0
     tc::issue_gemm(taddr + 192, tc::kmajor_tile(Bt, N), tc::mnmajor_tile(Dt, P), 64, P, N, false);    // Brot dH1
-    tc::issue_gemm(taddr + 256, tc::kmajor_tile(Ys, P), tc::kmajor_tile(Ht, P), 64, N, P, false);     // (e^Lam dY) H0^T
-    tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xs, P), tc::kmajor_tile(Dt, P), 64, N, P, false);     // (r e x) dH1^T
     tc::mma_commit(mbar);
   }
   {  // <dH1, H0> while the tensor core works
@@ -445,6 +446,22 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   tc::fence_after_sync();
   float dl_own = 0.f, de_own = 0.f, dg_own = 0.f, zsum = 0.f;
   const float lt = s.Lam[t], gt = s.gam[t], et = s.e[t], rt = s.r[t], dxt = s.dexp[t];
+  if (ok) {
+    {  // kappa_t = exp(Lam_t) dY_t . (Crot H0)_t   and   zeta_s = (Brot dH1)_s . x_s   (32 channels per half)
+      const int c0 = 32 * hc;
+      float f[32];
+      ld_acc32(taddr + 128, warp, c0, f);
+      if (own) dl_own += dxt * row_dot32_64(Yt, t, c0, f);
+      ld_acc32(taddr + 192, warp, c0, f);
+      if (own) {
+        const float zeta = row_dot32_64(Xt, t, c0, f);
+        de_own += rt * zeta;
+        dl_own -= rt * et * zeta;
+        zsum = rt * et * zeta;
+      }
+    }
+  }
+  __syncthreads();  // every read of the x tile is done: G*M may overwrite it
   if (ok) {
     {  // G and dY X^T: 32 columns per half
       const int c0 = 32 * hc;
@@ -483,19 +500,6 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
         }
       }
     }
-    {  // kappa_t = exp(Lam_t) dY_t . (Crot H0)_t   and   zeta_s = (Brot dH1)_s . x_s   (32 channels per half)
-      const int c0 = 32 * hc;
-      float f[32];
-      ld_acc32(taddr + 128, warp, c0, f);
-      if (own) dl_own += dxt * row_dot32_64(Yt, t, c0, f);
-      ld_acc32(taddr + 192, warp, c0, f);
-      if (own) {
-        const float zeta = row_dot32_64(Xt, t, c0, f);
-        de_own += rt * zeta;
-        dl_own -= rt * et * zeta;
-        zsum = rt * et * zeta;
-      }
-    }
   }
   {
     const float tot = warp_sum(own ? zsum : 0.f);
@@ -507,8 +511,8 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   tc::fence_after_sync();
   if (ok && tid == 0) {
     tc::issue_gemm(taddr + 0, tc::mnmajor_tile(GMt, Q), tc::mnmajor_tile(Yt, P), 64, P, Q, false);    // (G*M)^T dY
-    tc::issue_gemm(taddr + 256, tc::kmajor_tile(dGt, Q), tc::mnmajor_tile(Bt, N), 64, N, Q, true);    // + dG Brot
-    tc::issue_gemm(taddr + 384, tc::mnmajor_tile(dGt, Q), tc::mnmajor_tile(Ct, N), 64, N, Q, true);   // + dG^T Crot
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Ys, P), tc::kmajor_tile(Ht, P), 64, N, P, false);      // (e^Lam dY) H0^T
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(dGt, Q), tc::mnmajor_tile(Bt, N), 64, N, Q, true);     // + dG Brot
     tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar, 1);
@@ -529,31 +533,58 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
         for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
       }
     }
-    // rotated-row gradients: un-rotate into the per-head partial rows, and the angle gradient
+    // dCrot rows: un-rotate into the per-head partial rows of dC, and their share of the angle gradient
     const float sn = s.sn[t], cs = s.cs[t];
     for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
-      float gc[32], gb[32];
-      ld_acc32(taddr + 256, warp, c0, gc);
-      ld_acc32(taddr + 384, warp, c0, gb);
+      float gc[32];
+      ld_acc32(taddr + 64, warp, c0, gc);
       if (own && t0 + t < p.T) {
-        float* pbr = p.pb + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
         float* pcr = p.pc + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-          float br[8], cr[8], ob[8], oc[8];
-          unpack8(*reinterpret_cast<const uint4*>(Bt + tc::kmajor_unit(t, (c0 >> 3) + x, N)), br);
+          float cr[8], oc[8];
           unpack8(*reinterpret_cast<const uint4*>(Ct + tc::kmajor_unit(t, (c0 >> 3) + x, N)), cr);
 #pragma unroll
           for (int k = 0; k < 8; k += 2) {
-            const float b0 = gb[8 * x + k], b1 = gb[8 * x + k + 1], c0v = gc[8 * x + k], c1v = gc[8 * x + k + 1];
-            ob[k] = cs * b0 - sn * b1; ob[k + 1] = sn * b0 + cs * b1;
+            const float c0v = gc[8 * x + k], c1v = gc[8 * x + k + 1];
             oc[k] = cs * c0v - sn * c1v; oc[k + 1] = sn * c0v + cs * c1v;
-            dphi_own += br[k + 1] * b0 - br[k] * b1 + cr[k + 1] * c0v - cr[k] * c1v;
+            dphi_own += cr[k + 1] * c0v - cr[k] * c1v;
+          }
+          *reinterpret_cast<float4*>(pcr + 8 * x) = make_float4(oc[0], oc[1], oc[2], oc[3]);
+          *reinterpret_cast<float4*>(pcr + 8 * x + 4) = make_float4(oc[4], oc[5], oc[6], oc[7]);
+        }
+      }
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();  // columns [0,192) are free again
+  tc::fence_after_sync();
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xs, P), tc::kmajor_tile(Dt, P), 64, N, P, false);       // (r e x) dH1^T
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(dGt, Q), tc::mnmajor_tile(Ct, N), 64, N, Q, true);     // + dG^T Crot
+    tc::mma_commit(mbar);
+  }
+  if (ok) ok = tc::mbar_wait(mbar, 0);
+  tc::fence_after_sync();
+  if (ok) {
+    const float sn = s.sn[t], cs = s.cs[t];
+    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
+      float gb[32];
+      ld_acc32(taddr + 0, warp, c0, gb);
+      if (own && t0 + t < p.T) {
+        float* pbr = p.pb + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float br[8], ob[8];
+          unpack8(*reinterpret_cast<const uint4*>(Bt + tc::kmajor_unit(t, (c0 >> 3) + x, N)), br);
+#pragma unroll
+          for (int k = 0; k < 8; k += 2) {
+            const float b0 = gb[8 * x + k], b1 = gb[8 * x + k + 1];
+            ob[k] = cs * b0 - sn * b1; ob[k + 1] = sn * b0 + cs * b1;
+            dphi_own += br[k + 1] * b0 - br[k] * b1;
           }
           *reinterpret_cast<float4*>(pbr + 8 * x) = make_float4(ob[0], ob[1], ob[2], ob[3]);
           *reinterpret_cast<float4*>(pbr + 8 * x + 4) = make_float4(ob[4], ob[5], ob[6], ob[7]);
-          *reinterpret_cast<float4*>(pcr + 8 * x) = make_float4(oc[0], oc[1], oc[2], oc[3]);
-          *reinterpret_cast<float4*>(pcr + 8 * x + 4) = make_float4(oc[4], oc[5], oc[6], oc[7]);
         }
       }
     }
@@ -584,7 +615,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
     p.dgam[o] = part[2 * Q + tid] + part[6 * Q + tid];
     p.dphi[o] = part[3 * Q + tid] + part[7 * Q + tid];
   }
-  if (warp == 0) tc::tmem_dealloc(taddr, 512);
+  if (warp == 0) tc::tmem_dealloc(taddr, 256);
 }
 
 
