@@ -79,14 +79,14 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   } else {  // group 0: [k;q]   group 1: v
     const uint32_t sa = tc::smem_u32(Akq), sv = tc::smem_u32(Vt);
     for (int u = tid; u < 128 * 16; u += 128) {
-      const int r = u >> 4, c8 = u & 15, i = r & 63;
+      const int r = urow16(u), c8 = ucol16(u), i = r & 63;
       const bool ok = i < imax;
       const bf16* src = r < 64 ? p.k : p.q;
       tc::cp_async16(sa + tc::kmajor_unit(r, c8, KD), ok ? src + row(i) * KD + c8 * 8 : src, ok);
     }
     tc::cp_async_commit();
     for (int u = tid; u < 64 * 16; u += 128) {
-      const int i = u >> 4, c8 = u & 15;
+      const int i = urow16(u), c8 = ucol16(u);
       const bool ok = i < imax;
       tc::cp_async16(sv + tc::kmajor_unit(i, c8, KD), ok ? p.v + row(i) * KD + c8 * 8 : p.v, ok);
     }
@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   }
   // T -> workspace (bf16, row-major) while the MMA runs
   for (int u = tid; u < 64 * 8; u += 128) {
-    const int i = u >> 3, c8 = u & 7;
+    const int i = urow8(u), c8 = ucol8(u);
     *reinterpret_cast<uint4*>(p.Tm + (ci * C + i) * C + c8 * 8) =
         *reinterpret_cast<const uint4*>(Tt + tc::kmajor_unit(i, c8, C));
   }
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       const size_t ci = (size_t)bh * p.n + c;
       const int imax = min(C, p.T - c * C);
       for (int u = tid; u < 128 * 16; u += 256) {
-        const int r = u >> 4, c8 = u & 15, i = r & 63;
+        const int r = urow16(u), c8 = ucol16(u), i = r & 63;
         if (r < 64) tc::cp_async16(sA1 + tc::kmajor_unit(r, c8, KD), p.w + (ci * C + i) * KD + c8 * 8);
         else tc::cp_async16(sA1 + tc::kmajor_unit(r, c8, KD), i < imax ? p.q + grow(c, i) * KD + c8 * 8 : p.q, i < imax);
       }
@@ -271,7 +271,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
     if (c < p.n) {
       const size_t ci = (size_t)bh * p.n + c;
       for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = u >> 4, c8 = u & 15;
+        const int i = urow16(u), c8 = ucol16(u);
         tc::cp_async16(sU + tc::kmajor_unit(i, c8, KD), p.u + (ci * C + i) * KD + c8 * 8);
       }
     }
@@ -282,11 +282,11 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       const size_t ci = (size_t)bh * p.n + c;
       const int imax = min(C, p.T - c * C);
       for (int u = tid; u < 64 * 8; u += 256) {
-        const int i = u >> 3, c8 = u & 7;
+        const int i = urow8(u), c8 = ucol8(u);
         tc::cp_async16(sA2 + tc::kmajor_unit(64 + i, c8, C), p.P + (ci * C + i) * C + c8 * 8);
       }
       for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = u >> 4, c8 = u & 15;
+        const int i = urow16(u), c8 = ucol16(u);
         tc::cp_async16(sA3 + tc::kmajor_unit(i, c8, KD), i < imax ? p.k + grow(c, i) * KD + c8 * 8 : p.k, i < imax);
       }
     }
@@ -464,6 +464,11 @@ static size_t carve_tc(TcP& p, void* ws, bool bwd) {
     p.vn = cv.take<bf16>(nc * C * KD);
     p.dhs = cv.take<bf16>(nc * KD * KD);
     p.dvn = cv.take<bf16>(nc * C * KD);
+    p.dqp = cv.take<bf16>(nc * C * KD);
+    p.dkp = cv.take<bf16>(nc * C * KD);
+    p.dw = cv.take<bf16>(nc * C * KD);
+    p.dpg = cv.take<bf16>(nc * C * C);
+    p.ls = cv.take<float>(nc);
   }
   return cv.bytes();
 }

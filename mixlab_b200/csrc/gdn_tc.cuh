@@ -35,6 +35,11 @@ struct TcP {
   bf16* vn;      // [C][KD]
   bf16* dhs;     // [KD][KD]  dS at chunk end
   bf16* dvn;     // [C][KD]
+  bf16* dqp;     // [C][KD]   d (dO S0^T)        } state contractions of the chunk backward,
+  bf16* dkp;     // [C][KD]   r (v_new dS^T)     } handed from its first kernel to its second
+  bf16* dw;      // [C][KD]   -dv_new S0^T       }
+  bf16* dpg;     // [C][C]    (dO v_new^T) * Gamma, lower triangle incl. diagonal
+  float* ls;     // [1]       E(gam_last) <dS, S0>
 };
 
 __device__ __forceinline__ float log_gate_tc(float g, int gate_is_log) {
@@ -44,6 +49,13 @@ __device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret
 __device__ __forceinline__ void sts16(uint8_t* base, uint32_t off, uint4 v) {
   *reinterpret_cast<uint4*>(base + off) = v;
 }
+// Staging-loop index u -> (row, 16-byte unit) of a tile with 16 (or 8) units per row, ordered so that the
+// eight lanes of one shared-memory write phase fill one contiguous 128-byte row group of the blocked layout
+// (no bank conflicts) while each row is still read from global memory in 64-byte pieces.
+__device__ __forceinline__ int urow16(int u) { return ((u >> 7) << 3) | (u & 7); }
+__device__ __forceinline__ int ucol16(int u) { return (u >> 3) & 15; }
+__device__ __forceinline__ int urow8(int u) { return ((u >> 6) << 3) | (u & 7); }
+__device__ __forceinline__ int ucol8(int u) { return (u >> 3) & 7; }
 __device__ __forceinline__ uint4 zero16() { return make_uint4(0u, 0u, 0u, 0u); }
 
 // Loads 32 fp32 accumulator columns [c0, c0+32) of this thread's TMEM lane.

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       const size_t ci = (size_t)bh * p.n + c;
       const int imax = min(C, p.T - c * C);
       for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = u >> 4, c8 = u & 15;
+        const int i = urow16(u), c8 = ucol16(u);
         const bool v = i < imax;
         const size_t g = v ? grow(c, i) * KD + c8 * 8 : 0;
         tc::cp_async16(sAk + tc::kmajor_unit(i, c8, KD), p.k + g, v);
@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
         tc::cp_async16(sAqw + tc::kmajor_unit(i, c8, KD), p.q + g, v);
       }
       for (int u = tid; u < 64 * 8; u += 256) {
-        const int i = u >> 3, c8 = u & 7;
+        const int i = urow8(u), c8 = ucol8(u);
         tc::cp_async16(sPt + tc::kmajor_unit(i, c8, C), p.P + (ci * C + i) * C + c8 * 8);
       }
     }
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
     if (c >= 0) {
       const size_t ci = (size_t)bh * p.n + c;
       for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = u >> 4, c8 = u & 15;
+        const int i = urow16(u), c8 = ucol16(u);
         tc::cp_async16(sAqw + tc::kmajor_unit(64 + i, c8, KD), p.w + (ci * C + i) * KD + c8 * 8);
       }
     }
@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
     tc::cp_async_wait<1>();  // group A of this chunk
     __syncthreads();         // dO tile and dd visible to every thread
     for (int u = tid; u < 64 * 16; u += 256) {  // d dO
-      const int i = u >> 4, c8 = u & 15;
+      const int i = urow16(u), c8 = ucol16(u);
       const uint32_t off = tc::kmajor_unit(i, c8, KD);
       sts16(Bdd, off, tc::scale_bf16x8(*reinterpret_cast<const uint4*>(dOop + off), dd[i]));
     }
@@ -207,15 +207,15 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
   if (warp == 0) tc::tmem_dealloc(taddr, 512);
 }
 
-// ------------------------------------------------------------ chunk backward
-// TMEM column map (fp32 columns; all accumulators are M=64, so row i of every result
-// sits in TMEM lane (i%16) + 32*(i/16) and is handled by thread (warp i/16, lane i%16)):
-//   [  0,128) dqi = dO S0^T            -> later z = T^T dw
-//   [128,256) dv_new S0^T (= -dw)      -> dT [128,192), Y [192,256) -> dA [128,192) -> dk part
-//   [256,384) dkt = v_new dS^T
-//   [384,448) dP                       -> k k^T     } -> [384,512) (dP*Gamma) k -> T^T dv_new
-//   [448,512)                             q k^T     }
-constexpr int kChunkBwdSmem = 49152 + 65536 + 16384 + 4 * 8192 + 14 * C * 4 + 64 + 256;
+// ------------------------------------------------- chunk backward, part 2: everything else
+// 256 TMEM columns and 108 KB of shared memory: two CTAs share an SM.  TMEM column map (fp32 columns; all
+// accumulators are M=64, so row i of every result sits in TMEM lane (i%16) + 32*(i/16) and is handled by
+// thread (warp i/16, lane i%16); warps 4-7 take the second half of the columns):
+//   B : k k^T [0,64)  q k^T [64,128)  dv_new v^T [128,192)  dw k^T [192,256)
+//   C1: Y = T^T dT [0,64)             C2: Y T^T [64,128)
+//   D1: (dP*Gamma) k [0,128)          (dP*Gamma)^T q + (Mb + Mb^T) k [128,256)  (kept until the end)
+//   D2: T^T dv_new [0,128)            D3: z = T^T dw [0,128)
+constexpr int kChunkBwdSmem = 5 * 16384 + 3 * 8192 + 13 * C * 4 + 64 + 256;
 
 __device__ __forceinline__ void unpack8(uint4 v, float (&e)[8]) {
   tc::unpack_bf16(v.x, e[0], e[1]); tc::unpack_bf16(v.y, e[2], e[3]);
@@ -238,29 +238,195 @@ __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, c
   return s;
 }
 
-__global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
+// ------------------------------------------------- chunk backward, part 1: state contractions
+// Per chunk: everything that needs the saved states.  256 TMEM columns and 81 KB of shared memory, so two
+// CTAs share an SM.  S0 and dS use the same shared-memory buffer one after the other.
+//   phase 1: dO S0^T [0,128), dv_new S0^T [128,256)   -> dqp = d (dO S0^T), dw = -dv_new S0^T
+//   phase 2: v_new dS^T [0,128), dO v_new^T [128,192) -> dkp = r (v_new dS^T), dP*Gamma, L <dS, S0>
+constexpr int kChunkBwdStateSmem = 3 * 16384 + 32768 + 4 * C * 4 + 64 + 256;
+
+__global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
   uint8_t* Xdo = sm;                // [64][128] dO
   uint8_t* Xdvn = Xdo + 16384;      // [64][128] dv_new
   uint8_t* Xvn = Xdvn + 16384;      // [64][128] v_new
-  uint8_t* Sreg = Xvn + 16384;      // 64 KB: phase A  S0 [128][128] | dS [128][128]
-  uint8_t* Xs0 = Sreg;              //        later    k | q | v   ([64][128] each)
-  uint8_t* Xds = Sreg + 32768;
-  uint8_t* Xk = Sreg;
-  uint8_t* Xq = Sreg + 16384;
-  uint8_t* Xv = Sreg + 32768;
-  uint8_t* Xdw = Sreg + 65536;      // [64][128] dw
+  uint8_t* Xs = Xvn + 16384;        // [128][128] S0, then dS
+  float* gam = reinterpret_cast<float*>(Xs + 32768);
+  float* dd = gam + C;
+  float* rr = dd + C;
+  float* red = rr + C;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + C);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
+  const size_t ci = (size_t)bh * p.n + c;
+  const int imax = min(C, p.T - t0);
+  auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
+  const bool own = lane < 16;
+  const int i = 16 * (warp & 3) + (lane & 15), hc = warp >> 2;
+
+  {  // group 0: dO, dv_new, S0   group 1: v_new
+    const uint32_t sdo = tc::smem_u32(Xdo), sdvn = tc::smem_u32(Xdvn), svn = tc::smem_u32(Xvn), ss = tc::smem_u32(Xs);
+    for (int u = tid; u < 64 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      const uint32_t off = tc::kmajor_unit(r, c8, KD);
+      tc::cp_async16(sdo + off, r < imax ? p.dO + row(r) * KD + c8 * 8 : p.dO, r < imax);
+      tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
+    }
+    for (int u = tid; u < 128 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      tc::cp_async16(ss + tc::kmajor_unit(r, c8, KD), p.hs + (ci * KD + r) * KD + c8 * 8);
+    }
+    tc::cp_async_commit();
+    for (int u = tid; u < 64 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      tc::cp_async16(svn + tc::kmajor_unit(r, c8, KD), p.vn + (ci * C + r) * KD + c8 * 8);
+    }
+    tc::cp_async_commit();
+  }
+  if (warp == 0) {
+    tc::tmem_alloc(tslot, 256);
+    tc::tmem_relinquish();
+  }
+  if (tid == 0) {
+    tc::mbar_init(mbar, 1);
+    tc::mbar_fence_init();
+  }
+  if (tid < C) gam[tid] = p.gam[ci * C + tid];
+  __syncthreads();
+  const float glast = gam[C - 1], L = exp_nonpos(glast);
+  if (tid < C) {
+    dd[tid] = exp_nonpos(gam[tid]);
+    rr[tid] = exp_nonpos(glast - gam[tid]);
+  }
+  tc::cp_async_wait<1>();
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t taddr = *tslot;
+  bool ok = true;
+  if (tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);     // dO S0^T
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);  // dv_new S0^T
+    tc::mma_commit(mbar);
+  }
+  ok = tc::mbar_wait(mbar, 0);
+  tc::fence_after_sync();
+  {  // S0 is dead in shared memory: fetch dS into the same buffer behind the epilogue
+    const uint32_t ss = tc::smem_u32(Xs);
+    for (int u = tid; u < 128 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      tc::cp_async16(ss + tc::kmajor_unit(r, c8, KD), p.dhs + (ci * KD + r) * KD + c8 * 8);
+    }
+    tc::cp_async_commit();
+  }
+  const float di = dd[i], ri = rr[i], gi = gam[i];
+  if (ok) {
+    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr + 0, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) f[jj] *= di;
+        uint4* dst = reinterpret_cast<uint4*>(p.dqp + (ci * C + i) * KD + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+      }
+      ld_acc32(taddr + 128, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) f[jj] = -f[jj];
+        uint4* dst = reinterpret_cast<uint4*>(p.dw + (ci * C + i) * KD + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+      }
+    }
+  }
+  tc::cp_async_wait<0>();  // v_new and dS
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);    // v_new dS^T
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xvn, KD), 64, 64, KD, false);  // dO v_new^T
+    tc::mma_commit(mbar);
+  }
+  {  // <dS, S0>: dS from shared memory, S0 once more from global (L2-resident)
+    float part = 0.f;
+    for (int u = tid; u < 128 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      float a[8], bq[8];
+      unpack8(*reinterpret_cast<const uint4*>(Xs + tc::kmajor_unit(r, c8, KD)), a);
+      unpack8(ldg16(p.hs + (ci * KD + r) * KD + c8 * 8), bq);
+#pragma unroll
+      for (int y = 0; y < 8; ++y) part = fmaf(a[y], bq[y], part);
+    }
+    part = warp_sum(part);
+    if (lane == 0) red[warp] = part;
+  }
+  if (ok) ok = tc::mbar_wait(mbar, 1);
+  tc::fence_after_sync();
+  if (ok) {
+    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {  // dkp = r (v_new dS^T)
+      float f[32];
+      ld_acc32(taddr + 0, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) f[jj] *= ri;
+        uint4* dst = reinterpret_cast<uint4*>(p.dkp + (ci * C + i) * KD + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+      }
+    }
+    {  // dP * Gamma, lower incl. diagonal (32 columns per half)
+      const int c0 = 32 * hc;
+      float f[32];
+      ld_acc32(taddr + 128, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const int j = c0 + jj;
+          f[jj] = (j <= i) ? f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(p.dpg + (ci * C + i) * C + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+      }
+    }
+  } else if (tid == 0) {
+    atomicExch(p.status, 5);
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  if (tid == 0) {
+    float s = 0.f;
+    for (int wv = 0; wv < 8; ++wv) s += red[wv];
+    p.ls[ci] = L * s;  // d/dgam_last of E(gam_last) <dS, S0>
+  }
+  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+}
+
+__global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
+  extern __shared__ uint8_t raw[];
+  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* Xk = sm;                 // [64][128] k
+  uint8_t* Xq = Xk + 16384;         // [64][128] q
+  uint8_t* Xv = Xq + 16384;         // [64][128] v; its first half is reused for Y = T^T dT
+  uint8_t* X2 = Xv;
+  uint8_t* Xdvn = Xv + 16384;       // [64][128] dv_new
+  uint8_t* Xdw = Xdvn + 16384;      // [64][128] dw
   uint8_t* Xt = Xdw + 16384;        // [64][64]  T
   uint8_t* Xpg = Xt + 8192;         // [64][64]  dP*Gamma
   uint8_t* X1 = Xpg + 8192;         // [64][64]  dT, later Mb + Mb^T
-  uint8_t* X2 = X1 + 8192;          // [64][64]  Y = T^T dT
-  float* gam = reinterpret_cast<float*>(X2 + 8192);
+  float* gam = reinterpret_cast<float*>(X1 + 8192);
   float* bet = gam + C;
   float* dd = bet + C;
   float* rr = dd + C;
-  float* csum = rr + C;             // cross-row contributions to dgam (shared atomics)
-  float* dgo = csum + C;            // [2][C] per-row dgam / dbeta partials of the two column halves
+  float* dgo = rr + C;              // [2][C] per-row dgam / dbeta partials of the two column halves
   float* dbo = dgo + 2 * C;
   float* red = dbo + 2 * C;
   float* csw = red + C;             // [4 warps][C] per-warp column sums (no atomics)
@@ -276,8 +442,32 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   const int i = 16 * (warp & 3) + (lane & 15);  // the row this thread owns in every epilogue
   const int hc = warp >> 2;  // warps 0-3 take the first half of an accumulator's columns, warps 4-7 the second
 
+  {  // group 0: k, q, v, dv_new, dw   group 1: T, dP*Gamma
+    const uint32_t sk = tc::smem_u32(Xk), sq = tc::smem_u32(Xq), sv = tc::smem_u32(Xv);
+    const uint32_t sdvn = tc::smem_u32(Xdvn), sdw = tc::smem_u32(Xdw);
+    const uint32_t st = tc::smem_u32(Xt), spg = tc::smem_u32(Xpg);
+    for (int u = tid; u < 64 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      const uint32_t off = tc::kmajor_unit(r, c8, KD);
+      const bool v = r < imax;
+      const size_t g = v ? row(r) * KD + c8 * 8 : 0;
+      tc::cp_async16(sk + off, p.k + g, v);
+      tc::cp_async16(sq + off, p.q + g, v);
+      tc::cp_async16(sv + off, p.v + g, v);
+      tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
+      tc::cp_async16(sdw + off, p.dw + (ci * C + r) * KD + c8 * 8);
+    }
+    tc::cp_async_commit();
+    for (int u = tid; u < 64 * 8; u += 256) {
+      const int r = urow8(u), c8 = ucol8(u);
+      const uint32_t off = tc::kmajor_unit(r, c8, C);
+      tc::cp_async16(st + off, p.Tm + (ci * C + r) * C + c8 * 8);
+      tc::cp_async16(spg + off, p.dpg + (ci * C + r) * C + c8 * 8);
+    }
+    tc::cp_async_commit();
+  }
   if (warp == 0) {
-    tc::tmem_alloc(tslot, 512);
+    tc::tmem_alloc(tslot, 256);
     tc::tmem_relinquish();
   }
   if (tid == 0) {
@@ -287,33 +477,15 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   if (tid < C) {
     gam[tid] = p.gam[ci * C + tid];
     bet[tid] = tid < imax ? p.beta[row(tid)] : 0.f;
-    csum[tid] = 0.f;
   }
   for (int u = tid; u < 4 * C; u += 256) csw[u] = 0.f;
-  // ---- phase A staging (cp.async): dO, dv_new, v_new, S0, dS, T ----
-  {
-    const uint32_t sdo = tc::smem_u32(Xdo), sdvn = tc::smem_u32(Xdvn), svn = tc::smem_u32(Xvn);
-    const uint32_t ss0 = tc::smem_u32(Xs0), sds = tc::smem_u32(Xds), st = tc::smem_u32(Xt);
-    for (int u = tid; u < 64 * 16; u += 256) {
-      const int r = u >> 4, c8 = u & 15;
-      const uint32_t off = tc::kmajor_unit(r, c8, KD);
-      tc::cp_async16(sdo + off, r < imax ? p.dO + row(r) * KD + c8 * 8 : p.dO, r < imax);
-      tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
-      tc::cp_async16(svn + off, p.vn + (ci * C + r) * KD + c8 * 8);
-    }
-    for (int u = tid; u < 128 * 16; u += 256) {
-      const int r = u >> 4, c8 = u & 15;
-      const uint32_t off = tc::kmajor_unit(r, c8, KD);
-      tc::cp_async16(ss0 + off, p.hs + (ci * KD + r) * KD + c8 * 8);
-      tc::cp_async16(sds + off, p.dhs + (ci * KD + r) * KD + c8 * 8);
-    }
-    for (int u = tid; u < 64 * 8; u += 256) {
-      const int r = u >> 3, c8 = u & 7;
-      tc::cp_async16(st + tc::kmajor_unit(r, c8, C), p.Tm + (ci * C + r) * C + c8 * 8);
-    }
-    tc::cp_async_commit();
-    tc::cp_async_wait<0>();
+  __syncthreads();
+  const float glast = gam[C - 1];
+  if (tid < C) {
+    dd[tid] = exp_nonpos(gam[tid]);
+    rr[tid] = exp_nonpos(glast - gam[tid]);
   }
+  tc::cp_async_wait<1>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -321,126 +493,54 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   const uint32_t taddr = *tslot;
   uint32_t ph = 0;
   bool ok = true;
-  const float glast = gam[C - 1], L = exp_nonpos(glast);
-  if (tid < C) {
-    dd[tid] = exp_nonpos(gam[tid]);
-    rr[tid] = exp_nonpos(glast - gam[tid]);
-  }
+  // ---- phase B ----
   if (tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xs0, KD), 64, 128, KD, false);
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xs0, KD), 64, 128, KD, false);
-    tc::issue_gemm(taddr + 256, tc::kmajor_tile(Xvn, KD), tc::kmajor_tile(Xds, KD), 64, 128, KD, false);
-    tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xvn, KD), 64, 64, KD, false);
-    tc::mma_commit(mbar);
-  }
-  {  // <dS, S0> while the tensor core works
-    float part = 0.f;
-    for (int u = tid; u < 128 * 16; u += 256) {
-      float a[8], bq[8];
-      unpack8(*reinterpret_cast<const uint4*>(Xs0 + u * 16), a);
-      unpack8(*reinterpret_cast<const uint4*>(Xds + u * 16), bq);
-#pragma unroll
-      for (int y = 0; y < 8; ++y) part = fmaf(a[y], bq[y], part);
-    }
-    part = warp_sum(part);
-    if (lane == 0) red[warp] = part;
-  }
-  __syncthreads();  // dd, rr, red visible; every thread is done reading S0 / dS from shared memory
-  ok = tc::mbar_wait(mbar, ph);
-  ph ^= 1;
-  tc::fence_after_sync();
-  {  // the S0/dS region is free (MMAs done): fetch raw k, q, v behind the phase A epilogue
-    const uint32_t sk = tc::smem_u32(Xk), sq = tc::smem_u32(Xq), sv = tc::smem_u32(Xv);
-    for (int u = tid; u < 64 * 16; u += 256) {
-      const int r = u >> 4, c8 = u & 15;
-      const uint32_t off = tc::kmajor_unit(r, c8, KD);
-      const bool v = r < imax;
-      const size_t g = v ? row(r) * KD + c8 * 8 : 0;
-      tc::cp_async16(sk + off, p.k + g, v);
-      tc::cp_async16(sq + off, p.q + g, v);
-      tc::cp_async16(sv + off, p.v + g, v);
-    }
-    tc::cp_async_commit();
-  }
-  float dg_own = 0.f, db_own = 0.f;
-  const float gi = gam[i], bi = bet[i], di = dd[i], ri = rr[i];
-  if (ok) {
-    for (int c0 = 32 * hc; c0 < 32 * hc + 32; c0 += 32) {  // dP * Gamma, lower incl. diagonal
-      float f[32];
-      ld_acc32(taddr + 384, warp, c0, f);
-      if (own) {
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          const int j = c0 + jj;
-          f[jj] = (j <= i) ? f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
-        }
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xpg, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
-      }
-    }
-    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {  // dw = -dv_new S0^T
-      float f[32];
-      ld_acc32(taddr + 128, warp, c0, f);
-      if (own) {
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) f[jj] = -f[jj];
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xdw, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
-      }
-    }
-  }
-  tc::cp_async_wait<0>();  // k, q, v
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xk, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);    // k k^T
-    tc::issue_gemm(taddr + 448, tc::kmajor_tile(Xq, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);    // q k^T
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xk, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);      // k k^T
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Xq, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);     // q k^T
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xv, KD), 64, 64, KD, false);  // dv_new v^T
     tc::issue_gemm(taddr + 192, tc::kmajor_tile(Xdw, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);   // dw k^T
     tc::mma_commit(mbar);
   }
-  if (ok) {
-    ok = tc::mbar_wait(mbar, ph);
-    ph ^= 1;
-  }
+  tc::cp_async_wait<0>();  // T, dP*Gamma
+  tc::fence_async_smem();
+  __syncthreads();
+  ok = tc::mbar_wait(mbar, ph);
+  ph ^= 1;
   tc::fence_after_sync();
-  float KKr[C];  // (k_i . k_j), j < i
+  float dg_own = 0.f, db_own = 0.f;
+  const float gi = gam[i], bi = bet[i], di = dd[i], ri = rr[i];
+  const int cb = 32 * hc;  // this thread's 32 columns of every [64][64] accumulator
+  float KKr[32];           // (k_i . k_j) for j in [cb, cb+32)
   if (ok) {
-    for (int c0 = 32 * hc; c0 < 32 * hc + 32; c0 += 32) {
-      float f[32];
-      ld_acc32(taddr + 448, warp, c0, f);  // q k^T: dgam from P
-      {
-        float rs = 0.f;
+    float f[32];
+    ld_acc32(taddr + 64, warp, cb, f);  // q k^T: dgam from P
+    {
+      float rs = 0.f;
 #pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          float e[8];
-          unpack8(*reinterpret_cast<const uint4*>(Xpg + tc::kmajor_unit(i, (c0 >> 3) + x, C)), e);
+      for (int x = 0; x < 4; ++x) {
+        float e[8];
+        unpack8(*reinterpret_cast<const uint4*>(Xpg + tc::kmajor_unit(i, (cb >> 3) + x, C)), e);
 #pragma unroll
-          for (int y = 0; y < 8; ++y) {
-            const int j = c0 + 8 * x + y;
-            const float X = (own && j <= i) ? e[y] * f[8 * x + y] : 0.f;
-            rs += X;
-            const float colsum = warp_sum(X);  // over the 16 rows this warp owns
-            if (lane == 0) csw[(warp & 3) * C + j] -= colsum;
-          }
+        for (int y = 0; y < 8; ++y) {
+          const int j = cb + 8 * x + y;
+          const float X = (own && j <= i) ? e[y] * f[8 * x + y] : 0.f;
+          rs += X;
+          const float colsum = warp_sum(X);  // over the 16 rows this warp owns
+          if (lane == 0) csw[(warp & 3) * C + j] -= colsum;
         }
-        dg_own += rs;
       }
-      ld_acc32(taddr + 384, warp, c0, f);  // k k^T
+      dg_own += rs;
+    }
+    ld_acc32(taddr + 0, warp, cb, KKr);  // k k^T
+    {  // dT[i][m] = beta_m (dv_new_i . v_m) + beta_m d_m (dw_i . k_m)   -> X1
+      float f2[32];
+      ld_acc32(taddr + 128, warp, cb, f);
+      ld_acc32(taddr + 192, warp, cb, f2);
+      if (own) {
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) KKr[c0 + jj] = f[jj];
-      {  // dT[i][m] = beta_m (dv_new_i . v_m) + beta_m d_m (dw_i . k_m)   -> X1
-        float f2[32];
-        ld_acc32(taddr + 128, warp, c0, f);
-        ld_acc32(taddr + 192, warp, c0, f2);
-        if (own) {
+        for (int jj = 0; jj < 32; ++jj) f[jj] = bet[cb + jj] * fmaf(dd[cb + jj], f2[jj], f[jj]);
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) f[jj] = bet[c0 + jj] * fmaf(dd[c0 + jj], f2[jj], f[jj]);
-#pragma unroll
-          for (int x = 0; x < 4; ++x) sts16(X1, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
-        }
+        for (int x = 0; x < 4; ++x) sts16(X1, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
       }
     }
   }
@@ -450,7 +550,7 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_after_sync();
   // ---- phase C: dA = tril(T^T dT T^T, -1) ----
   if (ok && tid == 0) {  // Y = T^T dT  (both operands contracted over their rows)
-    tc::issue_gemm(taddr + 192, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(X1, C), 64, 64, C, false);
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(X1, C), 64, 64, C, false);
     tc::mma_commit(mbar);
   }
   if (ok) {
@@ -459,13 +559,11 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   }
   tc::fence_after_sync();
   if (ok) {
-    for (int c0 = 32 * hc; c0 < 32 * hc + 32; c0 += 32) {
-      float f[32];
-      ld_acc32(taddr + 192, warp, c0, f);
-      if (own) {
+    float f[32];
+    ld_acc32(taddr + 0, warp, cb, f);
+    if (own) {
 #pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(X2, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
-      }
+      for (int x = 0; x < 4; ++x) sts16(X2, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
     }
   }
   tc::fence_async_smem();
@@ -473,7 +571,7 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   __syncthreads();
   tc::fence_after_sync();
   if (ok && tid == 0) {  // dA = Y T^T
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(X2, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(X2, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
     tc::mma_commit(mbar);
   }
   if (ok) {
@@ -486,32 +584,28 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
     auto ms_at = [&](int r, int cc) -> bf16& {
       return ms[(tc::kmajor_unit(r, cc >> 3, C) >> 1) + (cc & 7)];
     };
-    for (int c0 = 32 * hc; c0 < 32 * hc + 32; c0 += 32) {
-      float f[32];
-      ld_acc32(taddr + 128, warp, c0, f);
-      {
-        float rs = 0.f;
+    float f[32];
+    ld_acc32(taddr + 64, warp, cb, f);
+    float rs = 0.f;
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          const int j = c0 + jj;
-          float t = 0.f;
-          if (own && j < i) {
-            const float M = -f[jj] * exp_nonpos(gi - gam[j]);  // -dA * Gamma
-            t = M * KKr[j];
-            const bf16 mb = __float2bfloat16_rn(bi * M);
-            ms_at(i, j) = mb;
-            ms_at(j, i) = mb;
-          } else if (own && j == i) {
-            ms_at(i, i) = __float2bfloat16_rn(0.f);
-          }
-          rs += t;
-          const float colsum = warp_sum(bi * t);
-          if (lane == 0) csw[(warp & 3) * C + j] -= colsum;
-        }
-        db_own += rs;
-        dg_own += bi * rs;
+    for (int jj = 0; jj < 32; ++jj) {
+      const int j = cb + jj;
+      float t = 0.f;
+      if (own && j < i) {
+        const float M = -f[jj] * exp_nonpos(gi - gam[j]);  // -dA * Gamma
+        t = M * KKr[jj];
+        const bf16 mb = __float2bfloat16_rn(bi * M);
+        ms_at(i, j) = mb;
+        ms_at(j, i) = mb;
+      } else if (own && j == i) {
+        ms_at(i, i) = __float2bfloat16_rn(0.f);
       }
+      rs += t;
+      const float colsum = warp_sum(bi * t);
+      if (lane == 0) csw[(warp & 3) * C + j] -= colsum;
     }
+    db_own += rs;
+    dg_own += bi * rs;
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
@@ -519,11 +613,15 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_after_sync();
   // ---- phase D1: (dP*Gamma) k  and  (dP*Gamma)^T q + (Mb + Mb^T) k ----
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 384, tc::kmajor_tile(Xpg, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, false);
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xpg, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, false);
     tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xpg, C), tc::mnmajor_tile(Xq, KD), 64, 128, C, false);
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(X1, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, true);
     tc::mma_commit(mbar);
   }
+  // the state contractions of this row, from the first kernel (issued ahead of the wait)
+  const int cw = 64 * hc;  // this thread's 64 columns of every [64][128] accumulator
+  const uint4* gq = reinterpret_cast<const uint4*>(p.dqp + (ci * C + i) * KD + cw);
+  const uint4* gk = reinterpret_cast<const uint4*>(p.dkp + (ci * C + i) * KD + cw);
   if (ok) {
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
@@ -531,38 +629,52 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_after_sync();
   if (ok) {
     float qdot = 0.f, kdot = 0.f;
-    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
+    for (int s = 0; s < 2; ++s) {
+      const int c0 = cw + 32 * s;
       float f[32], g2[32];
-      ld_acc32(taddr + 0, warp, c0, f);     // dqi
-      ld_acc32(taddr + 384, warp, c0, g2);  // (dP*Gamma) k
       if (own) {
-        qdot += row_dot32(Xq, i, c0, f);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float e[8];
+          unpack8(__ldg(gq + 4 * s + x), e);
+#pragma unroll
+          for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
+        }
+      }
+      ld_acc32(taddr + 0, warp, c0, g2);  // (dP*Gamma) k
+      if (own) {
+        qdot += row_dot32(Xq, i, c0, f);  // q_i . d_i dqi_i
         if (i < imax) {
           float e[32];
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) e[jj] = fmaf(di, f[jj], g2[jj]);
+          for (int jj = 0; jj < 32; ++jj) e[jj] = f[jj] + g2[jj];
           uint4* dst = reinterpret_cast<uint4*>(p.dq + row(i) * KD + c0);
 #pragma unroll
           for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
         }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float e[8];
+          unpack8(__ldg(gk + 4 * s + x), e);
+#pragma unroll
+          for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
+        }
+        kdot += row_dot32(Xk, i, c0, f);  // k_i . r_i dkt_i
       }
-      ld_acc32(taddr + 256, warp, c0, f);   // dkt
-      if (own) kdot += row_dot32(Xk, i, c0, f);
     }
     {
-      const float rho = own ? ri * kdot : 0.f;
-      if (own) dg_own += di * qdot - rho;
+      const float rho = own ? kdot : 0.f;
+      if (own) dg_own += qdot - rho;
       const float tot = warp_sum(rho);
       if (lane == 0) red[8 + warp] = tot;  // summed in a fixed order at the end (deterministic)
     }
   }
   tc::fence_before_sync();
-  __syncthreads();  // columns [0,128) and [384,512) are free again
+  __syncthreads();  // columns [0,128) are free again
   tc::fence_after_sync();
-  // ---- phase D2: T^T dv_new  and  z = T^T dw ----
+  // ---- phase D2: T^T dv_new ----
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 384, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdvn, KD), 64, 128, C, false);
-    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdw, KD), 64, 128, C, false);
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdvn, KD), 64, 128, C, false);
     tc::mma_commit(mbar);
   }
   if (ok) {
@@ -570,18 +682,19 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
     ph ^= 1;
   }
   tc::fence_after_sync();
+  float vdot = 0.f;
   if (ok) {
-    float vdot = 0.f, kz = 0.f;
-    const float bd_i = bi * di;
-    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
-      float f[32], g2[32], g3[32];
-      ld_acc32(taddr + 384, warp, c0, f);  // T^T dv_new
+    const uint4* gv = reinterpret_cast<const uint4*>(p.v + (i < imax ? row(i) * KD + cw : 0));
+    for (int s = 0; s < 2; ++s) {
+      const int c0 = cw + 32 * s;
+      float f[32];
+      ld_acc32(taddr + 0, warp, c0, f);
       if (own && i < imax) {
         float e[32];
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float vv[8];
-          unpack8(*reinterpret_cast<const uint4*>(Xv + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), vv);
+          unpack8(__ldg(gv + 4 * s + x), vv);
 #pragma unroll
           for (int y = 0; y < 8; ++y) {
             vdot = fmaf(vv[y], f[8 * x + y], vdot);
@@ -592,15 +705,40 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
       }
+    }
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  // ---- phase D3: z = T^T dw ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdw, KD), 64, 128, C, false);
+    tc::mma_commit(mbar);
+  }
+  if (ok) {
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+  }
+  tc::fence_after_sync();
+  if (ok) {
+    float kz = 0.f;
+    const float bd_i = bi * di;
+    for (int s = 0; s < 2; ++s) {
+      const int c0 = cw + 32 * s;
+      float f[32], g2[32];
       ld_acc32(taddr + 0, warp, c0, f);     // z
       ld_acc32(taddr + 128, warp, c0, g2);  // (dP*Gamma)^T q + (Mb+Mb^T) k
-      ld_acc32(taddr + 256, warp, c0, g3);  // dkt
       if (own) {
         kz += row_dot32(Xk, i, c0, f);
         if (i < imax) {
           float e[32];
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) e[jj] = g2[jj] + ri * g3[jj] + bd_i * f[jj];
+          for (int x = 0; x < 4; ++x) {
+            float kp[8];
+            unpack8(__ldg(gk + 4 * s + x), kp);
+#pragma unroll
+            for (int y = 0; y < 8; ++y) e[8 * x + y] = g2[8 * x + y] + kp[y] + bd_i * f[8 * x + y];
+          }
           uint4* dst = reinterpret_cast<uint4*>(p.dk + row(i) * KD + c0);
 #pragma unroll
           for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
@@ -619,11 +757,11 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_before_sync();
   __syncthreads();
   if (tid == 0) {  // dg = reverse cumulative sum of dgam within the chunk
-    // d/dgam_last: E(gam_last) <dS, S0> and the sum of rho over the rows
-    float acc = L * (red[0] + red[1] + red[2] + red[3] + red[4] + red[5] + red[6] + red[7]);
+    // d/dgam_last: E(gam_last) <dS, S0> (from the first kernel) and the sum of rho over the rows
+    float acc = p.ls[ci];
     for (int wv = 0; wv < 8; ++wv) acc += red[8 + wv];
     for (int r = C - 1; r >= 0; --r) {
-      acc += dgo[r] + dgo[C + r] + csum[r] + csw[r] + csw[C + r] + csw[2 * C + r] + csw[3 * C + r];
+      acc += dgo[r] + dgo[C + r] + csw[r] + csw[C + r] + csw[2 * C + r] + csw[3 * C + r];
       dgo[r] = acc;
     }
   }
@@ -640,7 +778,7 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_kernel(TcP p) {
     }
     p.dgate[row(tid)] = dg;
   }
-  if (warp == 0) tc::tmem_dealloc(taddr, 512);
+  if (warp == 0) tc::tmem_dealloc(taddr, 256);
 }
 
 // ------------------------------------------------------------------ host
@@ -671,6 +809,11 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
   MXB_LAUNCH("gdn_tc_state_bwd_kernel", st,
              (gdn_tc_state_bwd_kernel<<<dim3(p.B * p.H), 256, kStateBwdSmem, st>>>(p)));
   s = check_launch("gdn_tc_state_bwd_kernel");
+  if (s != MXB_OK) return s;
+  if (bwd_set_smem(gdn_tc_chunk_bwd_state_kernel, kChunkBwdStateSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("gdn_tc_chunk_bwd_state_kernel", st,
+             (gdn_tc_chunk_bwd_state_kernel<<<dim3(p.n, p.B * p.H), 256, kChunkBwdStateSmem, st>>>(p)));
+  s = check_launch("gdn_tc_chunk_bwd_state_kernel");
   if (s != MXB_OK) return s;
   if (bwd_set_smem(gdn_tc_chunk_bwd_kernel, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,

@@ -113,7 +113,7 @@ __device__ __forceinline__ void load_chunk_scalars(const SsdP& p, int b, int hea
 __device__ __forceinline__ void build_rot_tile(uint8_t* dst, const bf16* src, const SsdP& p, int b, int g, int t0,
                                                const float* sn, const float* cs, const float* rowscale) {
   for (int u = threadIdx.x; u < Q * 16; u += blockDim.x) {
-    const int t = u >> 4, c8 = u & 15;
+    const int t = ((u >> 7) << 3) | (u & 7), c8 = (u >> 3) & 15;  // 8 lanes fill one 128-byte row group: no bank conflicts
     float e[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (t0 + t < p.T) {
       unpack8(ldg16(src + (((size_t)b * p.T + t0 + t) * p.G + g) * N + c8 * 8), e);
@@ -132,7 +132,7 @@ __device__ __forceinline__ void build_rot_tile(uint8_t* dst, const bf16* src, co
 __device__ __forceinline__ void build_x_tile(uint8_t* dst, const bf16* src, const SsdP& p, int b, int d0, int t0,
                                              const float* rowscale) {
   for (int u = threadIdx.x; u < Q * 8; u += blockDim.x) {
-    const int t = u >> 3, c8 = u & 7;
+    const int t = ((u >> 6) << 3) | (u & 7), c8 = (u >> 3) & 7;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (t0 + t < p.T) {
       v = ldg16(src + ((size_t)b * p.T + t0 + t) * p.D + d0 + c8 * 8);
@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(256) m3s_scan_kernel(SsdP p, int rev) {
 // Copies a [128 n][64 p] bf16 workspace matrix into a blocked shared-memory tile.
 __device__ __forceinline__ void build_state_tile(uint8_t* dst, const bf16* src) {
   for (int u = threadIdx.x; u < N * 8; u += blockDim.x) {
-    const int r = u >> 3, c8 = u & 7;
+    const int r = ((u >> 6) << 3) | (u & 7), c8 = (u >> 3) & 7;
     sts16(dst, tc::kmajor_unit(r, c8, P), ldg16(src + r * P + c8 * 8));
   }
 }
