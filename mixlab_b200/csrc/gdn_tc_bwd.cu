@@ -211,10 +211,10 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
 // 256 TMEM columns and 108 KB of shared memory: two CTAs share an SM.  TMEM column map (fp32 columns; all
 // accumulators are M=64, so row i of every result sits in TMEM lane (i%16) + 32*(i/16) and is handled by
 // thread (warp i/16, lane i%16); warps 4-7 take the second half of the columns):
-//   B : k k^T [0,64)  q k^T [64,128)  dv_new v^T [128,192)  dw k^T [192,256)
-//   C1: Y = T^T dT [0,64)             C2: Y T^T [64,128)
-//   D1: (dP*Gamma) k [0,128)          (dP*Gamma)^T q + (Mb + Mb^T) k [128,256)  (kept until the end)
-//   D2: T^T dv_new [0,128)            D3: z = T^T dw [0,128)
+//   1: T^T dv_new [0,128)             z = T^T dw [128,256)      (both rewritten to shared memory as bf16)
+//   2: (T^T dv_new) v^T [0,64)        z k^T [64,128)            k k^T [128,192)   q k^T [192,256)
+//   3: Y T^T [0,64)   with Y = T^T dT assembled from phase 2
+//   4: (dP*Gamma) k [0,128)           (dP*Gamma)^T q + (Mb + Mb^T) k [128,256)
 constexpr int kChunkBwdSmem = 5 * 16384 + 3 * 8192 + 13 * C * 4 + 64 + 256;
 
 __device__ __forceinline__ void unpack8(uint4 v, float (&e)[8]) {
@@ -417,11 +417,11 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   uint8_t* Xq = Xk + 16384;         // [64][128] q
   uint8_t* Xv = Xq + 16384;         // [64][128] v; its first half is reused for Y = T^T dT
   uint8_t* X2 = Xv;
-  uint8_t* Xdvn = Xv + 16384;       // [64][128] dv_new
-  uint8_t* Xdw = Xdvn + 16384;      // [64][128] dw
+  uint8_t* Xdvn = Xv + 16384;       // [64][128] dv_new, then T^T dv_new in place
+  uint8_t* Xdw = Xdvn + 16384;      // [64][128] dw, then z = T^T dw in place
   uint8_t* Xt = Xdw + 16384;        // [64][64]  T
   uint8_t* Xpg = Xt + 8192;         // [64][64]  dP*Gamma
-  uint8_t* X1 = Xpg + 8192;         // [64][64]  dT, later Mb + Mb^T
+  uint8_t* X1 = Xpg + 8192;         // [64][64]  Mb + Mb^T
   float* gam = reinterpret_cast<float*>(X1 + 8192);
   float* bet = gam + C;
   float* dd = bet + C;
@@ -442,10 +442,21 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   const int i = 16 * (warp & 3) + (lane & 15);  // the row this thread owns in every epilogue
   const int hc = warp >> 2;  // warps 0-3 take the first half of an accumulator's columns, warps 4-7 the second
 
-  {  // group 0: k, q, v, dv_new, dw   group 1: T, dP*Gamma
+  {  // group 0: dv_new, dw, T   group 1: k, q, v, dP*Gamma
     const uint32_t sk = tc::smem_u32(Xk), sq = tc::smem_u32(Xq), sv = tc::smem_u32(Xv);
     const uint32_t sdvn = tc::smem_u32(Xdvn), sdw = tc::smem_u32(Xdw);
     const uint32_t st = tc::smem_u32(Xt), spg = tc::smem_u32(Xpg);
+    for (int u = tid; u < 64 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      const uint32_t off = tc::kmajor_unit(r, c8, KD);
+      tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
+      tc::cp_async16(sdw + off, p.dw + (ci * C + r) * KD + c8 * 8);
+    }
+    for (int u = tid; u < 64 * 8; u += 256) {
+      const int r = urow8(u), c8 = ucol8(u);
+      tc::cp_async16(st + tc::kmajor_unit(r, c8, C), p.Tm + (ci * C + r) * C + c8 * 8);
+    }
+    tc::cp_async_commit();
     for (int u = tid; u < 64 * 16; u += 256) {
       const int r = urow16(u), c8 = ucol16(u);
       const uint32_t off = tc::kmajor_unit(r, c8, KD);
@@ -454,15 +465,10 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
       tc::cp_async16(sk + off, p.k + g, v);
       tc::cp_async16(sq + off, p.q + g, v);
       tc::cp_async16(sv + off, p.v + g, v);
-      tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
-      tc::cp_async16(sdw + off, p.dw + (ci * C + r) * KD + c8 * 8);
     }
-    tc::cp_async_commit();
     for (int u = tid; u < 64 * 8; u += 256) {
       const int r = urow8(u), c8 = ucol8(u);
-      const uint32_t off = tc::kmajor_unit(r, c8, C);
-      tc::cp_async16(st + off, p.Tm + (ci * C + r) * C + c8 * 8);
-      tc::cp_async16(spg + off, p.dpg + (ci * C + r) * C + c8 * 8);
+      tc::cp_async16(spg + tc::kmajor_unit(r, c8, C), p.dpg + (ci * C + r) * C + c8 * 8);
     }
     tc::cp_async_commit();
   }
@@ -493,27 +499,77 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   const uint32_t taddr = *tslot;
   uint32_t ph = 0;
   bool ok = true;
-  // ---- phase B ----
+  // ---- phase 1: T^T dv_new and z = T^T dw (both operands contracted over their rows) ----
   if (tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xk, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);      // k k^T
-    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Xq, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);     // q k^T
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xv, KD), 64, 64, KD, false);  // dv_new v^T
-    tc::issue_gemm(taddr + 192, tc::kmajor_tile(Xdw, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);   // dw k^T
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdvn, KD), 64, 128, C, false);
+    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdw, KD), 64, 128, C, false);
     tc::mma_commit(mbar);
   }
-  tc::cp_async_wait<0>();  // T, dP*Gamma
-  tc::fence_async_smem();
+  tc::cp_async_wait<0>();  // k, q, v, dP*Gamma
   __syncthreads();
   ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
   float dg_own = 0.f, db_own = 0.f;
   const float gi = gam[i], bi = bet[i], di = dd[i], ri = rr[i];
+  const float bd_i = bi * di;
   const int cb = 32 * hc;  // this thread's 32 columns of every [64][64] accumulator
-  float KKr[32];           // (k_i . k_j) for j in [cb, cb+32)
+  const int cw = 64 * hc;  // this thread's 64 columns of every [64][128] accumulator
+  if (ok) {
+    // dv = beta (T^T dv_new); both products go back to shared memory as bf16 operands of phase 2, over the
+    // operands they were computed from (their MMAs are complete).
+    float vdot = 0.f, kz = 0.f;
+    for (int s = 0; s < 2; ++s) {
+      const int c0 = cw + 32 * s;
+      float f[32];
+      ld_acc32(taddr + 0, warp, c0, f);
+      if (own) {
+        vdot += row_dot32(Xv, i, c0, f);
+        if (i < imax) {
+          float e[32];
+#pragma unroll
+          for (int jj = 0; jj < 32; ++jj) e[jj] = bi * f[jj];
+          uint4* dst = reinterpret_cast<uint4*>(p.dv + row(i) * KD + c0);
+#pragma unroll
+          for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
+      }
+      ld_acc32(taddr + 128, warp, c0, f);
+      if (own) {
+        kz += row_dot32(Xk, i, c0, f);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Xdw, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
+      }
+    }
+    if (own) {
+      db_own += vdot + di * kz;
+      dg_own += bd_i * kz;
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  // ---- phase 2: Y = T^T dT = (T^T dv_new)(v beta)^T + z (k beta d)^T, with the column scales applied in the
+  //      epilogue; k k^T and q k^T ride along ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xv, KD), 64, 64, KD, false);
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Xdw, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xk, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);  // k k^T
+    tc::issue_gemm(taddr + 192, tc::kmajor_tile(Xq, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);  // q k^T
+    tc::mma_commit(mbar);
+  }
+  if (ok) {
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+  }
+  tc::fence_after_sync();
+  float KKr[32];  // (k_i . k_j) for j in [cb, cb+32)
   if (ok) {
     float f[32];
-    ld_acc32(taddr + 64, warp, cb, f);  // q k^T: dgam from P
+    ld_acc32(taddr + 192, warp, cb, f);  // q k^T: dgam from P
     {
       float rs = 0.f;
 #pragma unroll
@@ -531,16 +587,16 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
       }
       dg_own += rs;
     }
-    ld_acc32(taddr + 0, warp, cb, KKr);  // k k^T
-    {  // dT[i][m] = beta_m (dv_new_i . v_m) + beta_m d_m (dw_i . k_m)   -> X1
+    ld_acc32(taddr + 128, warp, cb, KKr);  // k k^T
+    {  // Y[i][m] = beta_m ((T^T dv_new)_i . v_m) + beta_m d_m (z_i . k_m)   -> X2 (v is dead)
       float f2[32];
-      ld_acc32(taddr + 128, warp, cb, f);
-      ld_acc32(taddr + 192, warp, cb, f2);
+      ld_acc32(taddr + 0, warp, cb, f);
+      ld_acc32(taddr + 64, warp, cb, f2);
       if (own) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) f[jj] = bet[cb + jj] * fmaf(dd[cb + jj], f2[jj], f[jj]);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(X1, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
+        for (int x = 0; x < 4; ++x) sts16(X2, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
       }
     }
   }
@@ -548,9 +604,9 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  // ---- phase C: dA = tril(T^T dT T^T, -1) ----
-  if (ok && tid == 0) {  // Y = T^T dT  (both operands contracted over their rows)
-    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(X1, C), 64, 64, C, false);
+  // ---- phase 3: dA = tril(Y T^T, -1) ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(X2, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
     tc::mma_commit(mbar);
   }
   if (ok) {
@@ -559,33 +615,12 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   }
   tc::fence_after_sync();
   if (ok) {
-    float f[32];
-    ld_acc32(taddr + 0, warp, cb, f);
-    if (own) {
-#pragma unroll
-      for (int x = 0; x < 4; ++x) sts16(X2, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
-    }
-  }
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  if (ok && tid == 0) {  // dA = Y T^T
-    tc::issue_gemm(taddr + 64, tc::kmajor_tile(X2, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
-    tc::mma_commit(mbar);
-  }
-  if (ok) {
-    ok = tc::mbar_wait(mbar, ph);
-    ph ^= 1;
-  }
-  tc::fence_after_sync();
-  if (ok) {
-    bf16* ms = reinterpret_cast<bf16*>(X1);  // X1 <- Mb + Mb^T (dT has been consumed)
+    bf16* ms = reinterpret_cast<bf16*>(X1);  // X1 <- Mb + Mb^T
     auto ms_at = [&](int r, int cc) -> bf16& {
       return ms[(tc::kmajor_unit(r, cc >> 3, C) >> 1) + (cc & 7)];
     };
     float f[32];
-    ld_acc32(taddr + 64, warp, cb, f);
+    ld_acc32(taddr + 0, warp, cb, f);
     float rs = 0.f;
 #pragma unroll
     for (int jj = 0; jj < 32; ++jj) {
@@ -611,15 +646,14 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  // ---- phase D1: (dP*Gamma) k  and  (dP*Gamma)^T q + (Mb + Mb^T) k ----
+  // ---- phase 4: (dP*Gamma) k  and  (dP*Gamma)^T q + (Mb + Mb^T) k ----
   if (ok && tid == 0) {
     tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xpg, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, false);
     tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xpg, C), tc::mnmajor_tile(Xq, KD), 64, 128, C, false);
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(X1, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, true);
     tc::mma_commit(mbar);
   }
-  // the state contractions of this row, from the first kernel (issued ahead of the wait)
-  const int cw = 64 * hc;  // this thread's 64 columns of every [64][128] accumulator
+  // the state contractions of this row, from the first kernel
   const uint4* gq = reinterpret_cast<const uint4*>(p.dqp + (ci * C + i) * KD + cw);
   const uint4* gk = reinterpret_cast<const uint4*>(p.dkp + (ci * C + i) * KD + cw);
   if (ok) {
@@ -661,6 +695,20 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
         }
         kdot += row_dot32(Xk, i, c0, f);  // k_i . r_i dkt_i
       }
+      ld_acc32(taddr + 128, warp, c0, g2);  // (dP*Gamma)^T q + (Mb+Mb^T) k
+      if (own && i < imax) {
+        float e[32];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          float z[8];
+          unpack8(*reinterpret_cast<const uint4*>(Xdw + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), z);
+#pragma unroll
+          for (int y = 0; y < 8; ++y) e[8 * x + y] = g2[8 * x + y] + f[8 * x + y] + bd_i * z[y];
+        }
+        uint4* dst = reinterpret_cast<uint4*>(p.dk + row(i) * KD + c0);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
+      }
     }
     {
       const float rho = own ? kdot : 0.f;
@@ -669,87 +717,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
       if (lane == 0) red[8 + warp] = tot;  // summed in a fixed order at the end (deterministic)
     }
   }
-  tc::fence_before_sync();
-  __syncthreads();  // columns [0,128) are free again
-  tc::fence_after_sync();
-  // ---- phase D2: T^T dv_new ----
-  if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdvn, KD), 64, 128, C, false);
-    tc::mma_commit(mbar);
-  }
-  if (ok) {
-    ok = tc::mbar_wait(mbar, ph);
-    ph ^= 1;
-  }
-  tc::fence_after_sync();
-  float vdot = 0.f;
-  if (ok) {
-    const uint4* gv = reinterpret_cast<const uint4*>(p.v + (i < imax ? row(i) * KD + cw : 0));
-    for (int s = 0; s < 2; ++s) {
-      const int c0 = cw + 32 * s;
-      float f[32];
-      ld_acc32(taddr + 0, warp, c0, f);
-      if (own && i < imax) {
-        float e[32];
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          float vv[8];
-          unpack8(__ldg(gv + 4 * s + x), vv);
-#pragma unroll
-          for (int y = 0; y < 8; ++y) {
-            vdot = fmaf(vv[y], f[8 * x + y], vdot);
-            e[8 * x + y] = bi * f[8 * x + y];
-          }
-        }
-        uint4* dst = reinterpret_cast<uint4*>(p.dv + row(i) * KD + c0);
-#pragma unroll
-        for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
-      }
-    }
-  }
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  // ---- phase D3: z = T^T dw ----
-  if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdw, KD), 64, 128, C, false);
-    tc::mma_commit(mbar);
-  }
-  if (ok) {
-    ok = tc::mbar_wait(mbar, ph);
-    ph ^= 1;
-  }
-  tc::fence_after_sync();
-  if (ok) {
-    float kz = 0.f;
-    const float bd_i = bi * di;
-    for (int s = 0; s < 2; ++s) {
-      const int c0 = cw + 32 * s;
-      float f[32], g2[32];
-      ld_acc32(taddr + 0, warp, c0, f);     // z
-      ld_acc32(taddr + 128, warp, c0, g2);  // (dP*Gamma)^T q + (Mb+Mb^T) k
-      if (own) {
-        kz += row_dot32(Xk, i, c0, f);
-        if (i < imax) {
-          float e[32];
-#pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            float kp[8];
-            unpack8(__ldg(gk + 4 * s + x), kp);
-#pragma unroll
-            for (int y = 0; y < 8; ++y) e[8 * x + y] = g2[8 * x + y] + kp[y] + bd_i * f[8 * x + y];
-          }
-          uint4* dst = reinterpret_cast<uint4*>(p.dk + row(i) * KD + c0);
-#pragma unroll
-          for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
-        }
-      }
-    }
-    if (own) {
-      db_own += vdot + di * kz;
-      dg_own += bd_i * kz;
-    }
-  }
+  (void)ri;
   if (own) {  // the two column halves hold partial sums of the same row
     dgo[hc * C + i] = dg_own;
     dbo[hc * C + i] = db_own;
