@@ -238,20 +238,44 @@ __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, c
   return s;
 }
 
+// Column sums over the 16 rows that lanes 0-15 of a warp hold (lanes 16-31 must pass zeros): v[c] is this
+// lane's value for column c.  Recursive halving: 30 shuffles instead of 32 x 4.  On return lane l holds in
+// v[0], v[1] the sums of columns colsum16_col(l) and colsum16_col(l) + 1.
+template <int M, int N>
+__device__ __forceinline__ void colsum16_step(float (&v)[32], int lane) {
+  const bool up = (lane & M) != 0;
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+    const float send = up ? v[k] : v[k + N];
+    const float keep = up ? v[k + N] : v[k];
+    v[k] = keep + __shfl_xor_sync(0xffffffffu, send, M);
+  }
+}
+__device__ __forceinline__ void colsum16(float (&v)[32], int lane) {
+  colsum16_step<8, 16>(v, lane);
+  colsum16_step<4, 8>(v, lane);
+  colsum16_step<2, 4>(v, lane);
+  colsum16_step<1, 2>(v, lane);
+}
+__device__ __forceinline__ int colsum16_col(int lane) { return 2 * (lane & 15); }
+
 // ------------------------------------------------- chunk backward, part 1: state contractions
-// Per chunk: everything that needs the saved states.  256 TMEM columns and 81 KB of shared memory, so two
-// CTAs share an SM.  S0 and dS use the same shared-memory buffer one after the other.
+// Per chunk: everything that needs the saved states.  256 TMEM columns and 97 KB of shared memory, so two
+// CTAs share an SM.  S0 and dS use the same shared-memory buffer one after the other.  The four results are
+// assembled in shared memory in the blocked operand layout and leave as contiguous 16 KB / 8 KB bulk
+// copies; the second kernel loads those byte images back unchanged.
 //   phase 1: dO S0^T [0,128), dv_new S0^T [128,256)   -> dqp = d (dO S0^T), dw = -dv_new S0^T
 //   phase 2: v_new dS^T [0,128), dO v_new^T [128,192) -> dkp = r (v_new dS^T), dP*Gamma, L <dS, S0>
-constexpr int kChunkBwdStateSmem = 3 * 16384 + 32768 + 4 * C * 4 + 64 + 256;
+constexpr int kChunkBwdStateSmem = 4 * 16384 + 32768 + 4 * C * 4 + 64 + 256;
 
-__global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_state_kernel(TcP p) {
+__global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
-  uint8_t* Xdo = sm;                // [64][128] dO
-  uint8_t* Xdvn = Xdo + 16384;      // [64][128] dv_new
-  uint8_t* Xvn = Xdvn + 16384;      // [64][128] v_new
-  uint8_t* Xs = Xvn + 16384;        // [128][128] S0, then dS
+  uint8_t* Xdo = sm;                // [64][128] dO            -> later the dkp image
+  uint8_t* Xdvn = Xdo + 16384;      // [64][128] dv_new        -> later the dqp image
+  uint8_t* Xvn = Xdvn + 16384;      // [64][128] v_new         -> later the dP*Gamma image (first half)
+  uint8_t* Xst = Xvn + 16384;       // the dw image
+  uint8_t* Xs = Xst + 16384;        // [128][128] S0, then dS
   float* gam = reinterpret_cast<float*>(Xs + 32768);
   float* dd = gam + C;
   float* rr = dd + C;
@@ -313,6 +337,9 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_state_kernel(TcP p) {
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);  // dv_new S0^T
     tc::mma_commit(mbar);
   }
+  uint4 s0u[8];  // this thread's 8 units of S0, kept for <dS, S0> (the buffer is about to be reused)
+#pragma unroll
+  for (int x = 0; x < 8; ++x) s0u[x] = *reinterpret_cast<const uint4*>(Xs + (tid + 256 * x) * 16);
   ok = tc::mbar_wait(mbar, 0);
   tc::fence_after_sync();
   {  // S0 is dead in shared memory: fetch dS into the same buffer behind the epilogue
@@ -331,17 +358,15 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_state_kernel(TcP p) {
       if (own) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) f[jj] *= di;
-        uint4* dst = reinterpret_cast<uint4*>(p.dqp + (ci * C + i) * KD + c0);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+        for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
       ld_acc32(taddr + 128, warp, c0, f);
       if (own) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) f[jj] = -f[jj];
-        uint4* dst = reinterpret_cast<uint4*>(p.dw + (ci * C + i) * KD + c0);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+        for (int x = 0; x < 4; ++x) sts16(Xst, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
     }
   }
@@ -354,14 +379,17 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_state_kernel(TcP p) {
     tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);    // v_new dS^T
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xvn, KD), 64, 64, KD, false);  // dO v_new^T
     tc::mma_commit(mbar);
+    tc::bulk_store(p.dqp + ci * C * KD, tc::smem_u32(Xdvn), 16384);
+    tc::bulk_store(p.dw + ci * C * KD, tc::smem_u32(Xst), 16384);
+    tc::bulk_commit();
   }
-  {  // <dS, S0>: dS from shared memory, S0 once more from global (L2-resident)
+  {  // <dS, S0>
     float part = 0.f;
-    for (int u = tid; u < 128 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
       float a[8], bq[8];
-      unpack8(*reinterpret_cast<const uint4*>(Xs + tc::kmajor_unit(r, c8, KD)), a);
-      unpack8(ldg16(p.hs + (ci * KD + r) * KD + c8 * 8), bq);
+      unpack8(*reinterpret_cast<const uint4*>(Xs + (tid + 256 * x) * 16), a);
+      unpack8(s0u[x], bq);
 #pragma unroll
       for (int y = 0; y < 8; ++y) part = fmaf(a[y], bq[y], part);
     }
@@ -371,18 +399,17 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   if (ok) ok = tc::mbar_wait(mbar, 1);
   tc::fence_after_sync();
   if (ok) {
-    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {  // dkp = r (v_new dS^T)
+    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {  // dkp = r (v_new dS^T)   (dO is dead: reuse its tile)
       float f[32];
       ld_acc32(taddr + 0, warp, c0, f);
       if (own) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) f[jj] *= ri;
-        uint4* dst = reinterpret_cast<uint4*>(p.dkp + (ci * C + i) * KD + c0);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+        for (int x = 0; x < 4; ++x) sts16(Xdo, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
     }
-    {  // dP * Gamma, lower incl. diagonal (32 columns per half)
+    {  // dP * Gamma, lower incl. diagonal (32 columns per half)   (v_new is dead: reuse its tile)
       const int c0 = 32 * hc;
       float f[32];
       ld_acc32(taddr + 128, warp, c0, f);
@@ -392,20 +419,26 @@ __global__ void __launch_bounds__(256) gdn_tc_chunk_bwd_state_kernel(TcP p) {
           const int j = c0 + jj;
           f[jj] = (j <= i) ? f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
         }
-        uint4* dst = reinterpret_cast<uint4*>(p.dpg + (ci * C + i) * C + c0);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+        for (int x = 0; x < 4; ++x) sts16(Xvn, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
       }
     }
   } else if (tid == 0) {
     atomicExch(p.status, 5);
   }
+  tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   if (tid == 0) {
+    if (ok) {
+      tc::bulk_store(p.dkp + ci * C * KD, tc::smem_u32(Xdo), 16384);
+      tc::bulk_store(p.dpg + ci * C * C, tc::smem_u32(Xvn), 8192);
+      tc::bulk_commit();
+    }
     float s = 0.f;
     for (int wv = 0; wv < 8; ++wv) s += red[wv];
     p.ls[ci] = L * s;  // d/dgam_last of E(gam_last) <dS, S0>
+    tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   }
   if (warp == 0) tc::tmem_dealloc(taddr, 256);
 }
@@ -415,9 +448,9 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
   uint8_t* Xk = sm;                 // [64][128] k
   uint8_t* Xq = Xk + 16384;         // [64][128] q
-  uint8_t* Xv = Xq + 16384;         // [64][128] v; its first half is reused for Y = T^T dT
+  uint8_t* Xv = Xq + 16384;         // [64][128] v; then Y = T^T dT (first half); then the dqp image -> dq
   uint8_t* X2 = Xv;
-  uint8_t* Xdvn = Xv + 16384;       // [64][128] dv_new, then T^T dv_new in place
+  uint8_t* Xdvn = Xv + 16384;       // [64][128] dv_new, then T^T dv_new in place; then the dkp image -> dk
   uint8_t* Xdw = Xdvn + 16384;      // [64][128] dw, then z = T^T dw in place
   uint8_t* Xt = Xdw + 16384;        // [64][64]  T
   uint8_t* Xpg = Xt + 8192;         // [64][64]  dP*Gamma
@@ -450,7 +483,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
       const int r = urow16(u), c8 = ucol16(u);
       const uint32_t off = tc::kmajor_unit(r, c8, KD);
       tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
-      tc::cp_async16(sdw + off, p.dw + (ci * C + r) * KD + c8 * 8);
+      tc::cp_async16(sdw + 16 * u, p.dw + ci * C * KD + 8 * u);  // written in the blocked layout already
     }
     for (int u = tid; u < 64 * 8; u += 256) {
       const int r = urow8(u), c8 = ucol8(u);
@@ -468,7 +501,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
     }
     for (int u = tid; u < 64 * 8; u += 256) {
       const int r = urow8(u), c8 = ucol8(u);
-      tc::cp_async16(spg + tc::kmajor_unit(r, c8, C), p.dpg + (ci * C + r) * C + c8 * 8);
+      tc::cp_async16(spg + 16 * u, p.dpg + ci * C * C + 8 * u);
+      (void)r; (void)c8;
     }
     tc::cp_async_commit();
   }
@@ -516,8 +550,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   const int cb = 32 * hc;  // this thread's 32 columns of every [64][64] accumulator
   const int cw = 64 * hc;  // this thread's 64 columns of every [64][128] accumulator
   if (ok) {
-    // dv = beta (T^T dv_new); both products go back to shared memory as bf16 operands of phase 2, over the
-    // operands they were computed from (their MMAs are complete).
+    // Both products go back to shared memory as bf16 operands of phase 2, over the operands they were
+    // computed from (their MMAs are complete); dv = beta (T^T dv_new) leaves from there after phase 2.
     float vdot = 0.f, kz = 0.f;
     for (int s = 0; s < 2; ++s) {
       const int c0 = cw + 32 * s;
@@ -525,14 +559,6 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
       ld_acc32(taddr + 0, warp, c0, f);
       if (own) {
         vdot += row_dot32(Xv, i, c0, f);
-        if (i < imax) {
-          float e[32];
-#pragma unroll
-          for (int jj = 0; jj < 32; ++jj) e[jj] = bi * f[jj];
-          uint4* dst = reinterpret_cast<uint4*>(p.dv + row(i) * KD + c0);
-#pragma unroll
-          for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
-        }
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
@@ -581,11 +607,16 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
           const int j = cb + 8 * x + y;
           const float X = (own && j <= i) ? e[y] * f[8 * x + y] : 0.f;
           rs += X;
-          const float colsum = warp_sum(X);  // over the 16 rows this warp owns
-          if (lane == 0) csw[(warp & 3) * C + j] -= colsum;
+          f[8 * x + y] = X;
         }
       }
       dg_own += rs;
+      colsum16(f, lane);  // over the 16 rows this warp owns
+      if (own) {
+        float* dst = csw + (warp & 3) * C + cb + colsum16_col(lane);
+        dst[0] -= f[0];
+        dst[1] -= f[1];
+      }
     }
     ld_acc32(taddr + 128, warp, cb, KKr);  // k k^T
     {  // Y[i][m] = beta_m ((T^T dv_new)_i . v_m) + beta_m d_m (z_i . k_m)   -> X2 (v is dead)
@@ -609,39 +640,55 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
     tc::issue_gemm(taddr + 0, tc::kmajor_tile(X2, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
     tc::mma_commit(mbar);
   }
+  if (ok) {  // dv = beta (T^T dv_new), from the bf16 tile, in 64-byte row pieces
+    for (int u = tid; u < 64 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      if (r < imax)
+        *reinterpret_cast<uint4*>(p.dv + row(r) * KD + c8 * 8) =
+            tc::scale_bf16x8(*reinterpret_cast<const uint4*>(Xdvn + tc::kmajor_unit(r, c8, KD)), bet[r]);
+    }
+  }
   if (ok) {
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
   }
   tc::fence_after_sync();
-  if (ok) {
-    bf16* ms = reinterpret_cast<bf16*>(X1);  // X1 <- Mb + Mb^T
-    auto ms_at = [&](int r, int cc) -> bf16& {
-      return ms[(tc::kmajor_unit(r, cc >> 3, C) >> 1) + (cc & 7)];
-    };
+  __syncthreads();  // every thread is done with the T^T dv_new tile; Y (over v) has been consumed by the MMA
+  {  // the state contractions from the first kernel land over v and T^T dv_new while phase 3's epilogue runs
+    const uint32_t sqp = tc::smem_u32(Xv), skp = tc::smem_u32(Xdvn);
+    for (int u = tid; u < 64 * 16; u += 256) {
+      tc::cp_async16(sqp + 16 * u, p.dqp + ci * C * KD + 8 * u);
+      tc::cp_async16(skp + 16 * u, p.dkp + ci * C * KD + 8 * u);
+    }
+    tc::cp_async_commit();
+  }
+  if (ok) {  // X1 <- Mb = beta_i M, strictly lower triangle, zeros elsewhere
     float f[32];
     ld_acc32(taddr + 0, warp, cb, f);
     float rs = 0.f;
 #pragma unroll
     for (int jj = 0; jj < 32; ++jj) {
       const int j = cb + jj;
-      float t = 0.f;
-      if (own && j < i) {
-        const float M = -f[jj] * exp_nonpos(gi - gam[j]);  // -dA * Gamma
-        t = M * KKr[jj];
-        const bf16 mb = __float2bfloat16_rn(bi * M);
-        ms_at(i, j) = mb;
-        ms_at(j, i) = mb;
-      } else if (own && j == i) {
-        ms_at(i, i) = __float2bfloat16_rn(0.f);
-      }
+      const float M = (own && j < i) ? -f[jj] * exp_nonpos(gi - gam[j]) : 0.f;  // -dA * Gamma
+      const float t = M * KKr[jj];
       rs += t;
-      const float colsum = warp_sum(bi * t);
-      if (lane == 0) csw[(warp & 3) * C + j] -= colsum;
+      KKr[jj] = bi * t;
+      f[jj] = bi * M;
+    }
+    if (own) {
+#pragma unroll
+      for (int x = 0; x < 4; ++x) sts16(X1, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
     }
     db_own += rs;
     dg_own += bi * rs;
+    colsum16(KKr, lane);
+    if (own) {
+      float* dst = csw + (warp & 3) * C + cb + colsum16_col(lane);
+      dst[0] -= KKr[0];
+      dst[1] -= KKr[1];
+    }
   }
+  tc::cp_async_wait<0>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -651,63 +698,54 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
     tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xpg, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, false);
     tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xpg, C), tc::mnmajor_tile(Xq, KD), 64, 128, C, false);
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(X1, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, true);
+    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(X1, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, true);
     tc::mma_commit(mbar);
   }
-  // the state contractions of this row, from the first kernel
-  const uint4* gq = reinterpret_cast<const uint4*>(p.dqp + (ci * C + i) * KD + cw);
-  const uint4* gk = reinterpret_cast<const uint4*>(p.dkp + (ci * C + i) * KD + cw);
   if (ok) {
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
   }
   tc::fence_after_sync();
   if (ok) {
+    // dq and dk are assembled over the dqp / dkp images (each thread rewrites the units it read)
     float qdot = 0.f, kdot = 0.f;
     for (int s = 0; s < 2; ++s) {
       const int c0 = cw + 32 * s;
       float f[32], g2[32];
+      ld_acc32(taddr + 0, warp, c0, g2);  // (dP*Gamma) k
       if (own) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float e[8];
-          unpack8(__ldg(gq + 4 * s + x), e);
+          unpack8(*reinterpret_cast<const uint4*>(Xv + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), e);
 #pragma unroll
           for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
         }
-      }
-      ld_acc32(taddr + 0, warp, c0, g2);  // (dP*Gamma) k
-      if (own) {
         qdot += row_dot32(Xq, i, c0, f);  // q_i . d_i dqi_i
-        if (i < imax) {
-          float e[32];
 #pragma unroll
-          for (int jj = 0; jj < 32; ++jj) e[jj] = f[jj] + g2[jj];
-          uint4* dst = reinterpret_cast<uint4*>(p.dq + row(i) * KD + c0);
+        for (int jj = 0; jj < 32; ++jj) g2[jj] += f[jj];
 #pragma unroll
-          for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
-        }
+        for (int x = 0; x < 4; ++x) sts16(Xv, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&g2[8 * x]));
+      }
+      ld_acc32(taddr + 128, warp, c0, g2);  // (dP*Gamma)^T q + (Mb+Mb^T) k
+      if (own) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float e[8];
-          unpack8(__ldg(gk + 4 * s + x), e);
+          unpack8(*reinterpret_cast<const uint4*>(Xdvn + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), e);
 #pragma unroll
           for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
         }
         kdot += row_dot32(Xk, i, c0, f);  // k_i . r_i dkt_i
-      }
-      ld_acc32(taddr + 128, warp, c0, g2);  // (dP*Gamma)^T q + (Mb+Mb^T) k
-      if (own && i < imax) {
-        float e[32];
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float z[8];
           unpack8(*reinterpret_cast<const uint4*>(Xdw + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), z);
 #pragma unroll
-          for (int y = 0; y < 8; ++y) e[8 * x + y] = g2[8 * x + y] + f[8 * x + y] + bd_i * z[y];
+          for (int y = 0; y < 8; ++y) g2[8 * x + y] += f[8 * x + y] + bd_i * z[y];
         }
-        uint4* dst = reinterpret_cast<uint4*>(p.dk + row(i) * KD + c0);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) dst[x] = pack8(&e[8 * x]);
+        for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&g2[8 * x]));
       }
     }
     {
@@ -724,6 +762,16 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   }
   tc::fence_before_sync();
   __syncthreads();
+  if (ok) {  // dq, dk leave in 64-byte row pieces
+    for (int u = tid; u < 64 * 16; u += 256) {
+      const int r = urow16(u), c8 = ucol16(u);
+      if (r < imax) {
+        const uint32_t off = tc::kmajor_unit(r, c8, KD);
+        *reinterpret_cast<uint4*>(p.dq + row(r) * KD + c8 * 8) = *reinterpret_cast<const uint4*>(Xv + off);
+        *reinterpret_cast<uint4*>(p.dk + row(r) * KD + c8 * 8) = *reinterpret_cast<const uint4*>(Xdvn + off);
+      }
+    }
+  }
   if (tid == 0) {  // dg = reverse cumulative sum of dgam within the chunk
     // d/dgam_last: E(gam_last) <dS, S0> (from the first kernel) and the sum of rho over the rows
     float acc = p.ls[ci];
