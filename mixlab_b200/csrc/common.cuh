@@ -43,6 +43,35 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// Column sums over the 16 rows that lanes 0-15 of a warp hold (lanes 16-31 must pass zeros): v[c] is this
+// lane's value for column c.  Recursive halving: 30 shuffles instead of 32 x 4.  On return lane l holds in
+// v[0], v[1] the sums of columns colsum16_col(l) and colsum16_col(l) + 1.
+template <int M, int N, int W>
+__device__ __forceinline__ void colsum16_step(float (&v)[W], int lane) {
+  const bool up = (lane & M) != 0;
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+    const float send = up ? v[k] : v[k + N];
+    const float keep = up ? v[k + N] : v[k];
+    v[k] = keep + __shfl_xor_sync(0xffffffffu, send, M);
+  }
+}
+__device__ __forceinline__ void colsum16(float (&v)[32], int lane) {
+  colsum16_step<8, 16, 32>(v, lane);
+  colsum16_step<4, 8, 32>(v, lane);
+  colsum16_step<2, 4, 32>(v, lane);
+  colsum16_step<1, 2, 32>(v, lane);
+}
+__device__ __forceinline__ int colsum16_col(int lane) { return 2 * (lane & 15); }
+
+// Same for 16 columns: on return lane l holds in v[0] the sum of column (l & 15).  15 shuffles.
+__device__ __forceinline__ void colsum16(float (&v)[16], int lane) {
+  colsum16_step<8, 8, 16>(v, lane);
+  colsum16_step<4, 4, 16>(v, lane);
+  colsum16_step<2, 2, 16>(v, lane);
+  colsum16_step<1, 1, 16>(v, lane);
+}
+
 // ---- host side ----------------------------------------------------------
 void note_launch(int n = 1);           // bumps mxb_launch_count()
 mxb_status check_launch(const char* what);  // cudaGetLastError -> status

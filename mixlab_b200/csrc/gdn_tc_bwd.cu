@@ -238,27 +238,6 @@ __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, c
   return s;
 }
 
-// Column sums over the 16 rows that lanes 0-15 of a warp hold (lanes 16-31 must pass zeros): v[c] is this
-// lane's value for column c.  Recursive halving: 30 shuffles instead of 32 x 4.  On return lane l holds in
-// v[0], v[1] the sums of columns colsum16_col(l) and colsum16_col(l) + 1.
-template <int M, int N>
-__device__ __forceinline__ void colsum16_step(float (&v)[32], int lane) {
-  const bool up = (lane & M) != 0;
-#pragma unroll
-  for (int k = 0; k < N; ++k) {
-    const float send = up ? v[k] : v[k + N];
-    const float keep = up ? v[k + N] : v[k];
-    v[k] = keep + __shfl_xor_sync(0xffffffffu, send, M);
-  }
-}
-__device__ __forceinline__ void colsum16(float (&v)[32], int lane) {
-  colsum16_step<8, 16>(v, lane);
-  colsum16_step<4, 8>(v, lane);
-  colsum16_step<2, 4>(v, lane);
-  colsum16_step<1, 2>(v, lane);
-}
-__device__ __forceinline__ int colsum16_col(int lane) { return 2 * (lane & 15); }
-
 // ------------------------------------------------- chunk backward, part 1: state contractions
 // Per chunk: everything that needs the saved states.  256 TMEM columns and 97 KB of shared memory, so two
 // CTAs share an SM.  S0 and dS use the same shared-memory buffer one after the other.  The four results are

@@ -109,36 +109,56 @@ __device__ __forceinline__ void load_chunk_scalars(const SsdP& p, int b, int hea
   __syncthreads();
 }
 
-// Rotated (and optionally row-scaled) copy of 64 rows of B or C -> blocked [64][128] bf16 tile.
-__device__ __forceinline__ void build_rot_tile(uint8_t* dst, const bf16* src, const SsdP& p, int b, int g, int t0,
-                                               const float* sn, const float* cs, const float* rowscale) {
+// ---- asynchronous staging: raw cp.async copies into the blocked layout, then in-place fix-ups ----
+// With t = 8 (u / 128) + u % 8 and c8 = (u / 8) % 16 the unit of a [64][128] tile sits at byte 16 u, and
+// likewise for [.][64] tiles with t = 8 (u / 64) + u % 8, c8 = (u / 8) % 8: eight consecutive lanes fill one
+// 128-byte row group (no bank conflicts) and read 64-byte pieces of a row.
+__device__ __forceinline__ void issue_rows_tile(uint8_t* dst, const bf16* src, const SsdP& p, int b, int g, int t0) {
+  const uint32_t sd = tc::smem_u32(dst);
   for (int u = threadIdx.x; u < Q * 16; u += blockDim.x) {
-    const int t = ((u >> 7) << 3) | (u & 7), c8 = (u >> 3) & 15;  // 8 lanes fill one 128-byte row group: no bank conflicts
-    float e[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (t0 + t < p.T) {
-      unpack8(ldg16(src + (((size_t)b * p.T + t0 + t) * p.G + g) * N + c8 * 8), e);
-      const float s_ = sn[t], c_ = cs[t], sc = rowscale ? rowscale[t] : 1.f;
-#pragma unroll
-      for (int k = 0; k < 8; k += 2) {
-        const float ev = e[k], od = e[k + 1];
-        e[k] = sc * (c_ * ev + s_ * od);
-        e[k + 1] = sc * (-s_ * ev + c_ * od);
-      }
-    }
-    sts16(dst, tc::kmajor_unit(t, c8, N), pack8(e));
+    const int t = ((u >> 7) << 3) | (u & 7), c8 = (u >> 3) & 15;
+    const bool ok = t0 + t < p.T;
+    tc::cp_async16(sd + 16 * u, ok ? src + (((size_t)b * p.T + t0 + t) * p.G + g) * N + c8 * 8 : src, ok);
   }
 }
-// 64 rows x 64 channels of x or dy (optionally row-scaled) -> blocked [64][64] bf16 tile.
-__device__ __forceinline__ void build_x_tile(uint8_t* dst, const bf16* src, const SsdP& p, int b, int d0, int t0,
-                                             const float* rowscale) {
+__device__ __forceinline__ void issue_x_tile(uint8_t* dst, const bf16* src, const SsdP& p, int b, int d0, int t0) {
+  const uint32_t sd = tc::smem_u32(dst);
   for (int u = threadIdx.x; u < Q * 8; u += blockDim.x) {
     const int t = ((u >> 6) << 3) | (u & 7), c8 = (u >> 3) & 7;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (t0 + t < p.T) {
-      v = ldg16(src + ((size_t)b * p.T + t0 + t) * p.D + d0 + c8 * 8);
-      if (rowscale) v = tc::scale_bf16x8(v, rowscale[t]);
+    const bool ok = t0 + t < p.T;
+    tc::cp_async16(sd + 16 * u, ok ? src + ((size_t)b * p.T + t0 + t) * p.D + d0 + c8 * 8 : src, ok);
+  }
+}
+// [128 n][64 p] bf16 workspace matrix (row-major) -> blocked tile
+__device__ __forceinline__ void issue_state_tile(uint8_t* dst, const bf16* src) {
+  const uint32_t sd = tc::smem_u32(dst);
+  for (int u = threadIdx.x; u < N * 8; u += blockDim.x) {
+    const int r = ((u >> 6) << 3) | (u & 7), c8 = (u >> 3) & 7;
+    tc::cp_async16(sd + 16 * u, src + r * P + c8 * 8);
+  }
+}
+// Rotates the (even, odd) pairs of every row of a landed [64][128] tile in place.
+__device__ __forceinline__ void rotate_tile(uint8_t* tile, const float* sn, const float* cs) {
+  for (int u = threadIdx.x; u < Q * 16; u += blockDim.x) {
+    const int t = ((u >> 7) << 3) | (u & 7);
+    float e[8];
+    unpack8(*reinterpret_cast<const uint4*>(tile + 16 * u), e);
+    const float s_ = sn[t], c_ = cs[t];
+#pragma unroll
+    for (int k = 0; k < 8; k += 2) {
+      const float ev = e[k], od = e[k + 1];
+      e[k] = c_ * ev + s_ * od;
+      e[k + 1] = -s_ * ev + c_ * od;
     }
-    sts16(dst, tc::kmajor_unit(t, c8, P), v);
+    *reinterpret_cast<uint4*>(tile + 16 * u) = pack8(e);
+  }
+}
+// dst = diag(rowscale) src for [64][64] tiles (dst may be src).
+__device__ __forceinline__ void scale_x_tile(uint8_t* dst, const uint8_t* src, const float* rowscale) {
+  for (int u = threadIdx.x; u < Q * 8; u += blockDim.x) {
+    const int t = ((u >> 6) << 3) | (u & 7);
+    *reinterpret_cast<uint4*>(dst + 16 * u) =
+        tc::scale_bf16x8(*reinterpret_cast<const uint4*>(src + 16 * u), rowscale[t]);
   }
 }
 
@@ -192,17 +212,18 @@ __global__ void __launch_bounds__(128) m3s_chunk_outer_kernel(SsdP p, int mode) 
 
   if (warp == 0) { tc::tmem_alloc(tslot, 64); tc::tmem_relinquish(); }
   if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
+  issue_rows_tile(Rt, mode == 0 ? p.b : p.c, p, b, g, t0);
+  issue_x_tile(Xt, mode == 0 ? p.x : p.dy, p, b, d0, t0);
+  tc::cp_async_commit();
   load_chunk_scalars(p, b, head, c, s);
   if (mode == 0) {
     if (tid < Q) s.gam[tid] = s.r[tid] * s.e[tid];  // row scale of x (gam is not needed here)
-    __syncthreads();
-    build_rot_tile(Rt, p.b, p, b, g, t0, s.sn, s.cs, nullptr);
-    build_x_tile(Xt, p.x, p, b, d0, t0, s.gam);
     if (tid == 0) p.Lc[ci] = s.L;
-  } else {
-    build_rot_tile(Rt, p.c, p, b, g, t0, s.sn, s.cs, nullptr);
-    build_x_tile(Xt, p.dy, p, b, d0, t0, s.dexp);
   }
+  tc::cp_async_wait<0>();
+  __syncthreads();
+  rotate_tile(Rt, s.sn, s.cs);
+  scale_x_tile(Xt, Xt, mode == 0 ? s.gam : s.dexp);
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -258,14 +279,6 @@ __global__ void __launch_bounds__(256) m3s_scan_kernel(SsdP p, int rev) {
 }
 
 
-// Copies a [128 n][64 p] bf16 workspace matrix into a blocked shared-memory tile.
-__device__ __forceinline__ void build_state_tile(uint8_t* dst, const bf16* src) {
-  for (int u = threadIdx.x; u < N * 8; u += blockDim.x) {
-    const int r = ((u >> 6) << 3) | (u & 7), c8 = (u >> 3) & 7;
-    sts16(dst, tc::kmajor_unit(r, c8, P), ldg16(src + r * P + c8 * 8));
-  }
-}
-
 // ------------------------------------------------------------ chunk output
 constexpr int kOutSmem = 16384 * 3 + 8192 * 2 + sizeof(ChunkScal) + 64 + 256;
 
@@ -287,11 +300,16 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
 
   if (warp == 0) { tc::tmem_alloc(tslot, 128); tc::tmem_relinquish(); }
   if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
+  issue_rows_tile(Bt, p.b, p, b, g, t0);
+  issue_rows_tile(Ct, p.c, p, b, g, t0);
+  issue_x_tile(Xt, p.x, p, b, d0, t0);
+  issue_state_tile(Ht, p.H0 + ci * (N * P));
+  tc::cp_async_commit();
   load_chunk_scalars(p, b, head, c, s);
-  build_rot_tile(Bt, p.b, p, b, g, t0, s.sn, s.cs, nullptr);
-  build_rot_tile(Ct, p.c, p, b, g, t0, s.sn, s.cs, nullptr);
-  build_x_tile(Xt, p.x, p, b, d0, t0, nullptr);
-  build_state_tile(Ht, p.H0 + ci * (N * P));
+  tc::cp_async_wait<0>();
+  __syncthreads();
+  rotate_tile(Bt, s.sn, s.cs);
+  rotate_tile(Ct, s.sn, s.cs);
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -405,19 +423,25 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
 
   if (warp == 0) { tc::tmem_alloc(tslot, 256); tc::tmem_relinquish(); }
   if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
+  issue_rows_tile(Bt, p.b, p, b, g, t0);
+  issue_rows_tile(Ct, p.c, p, b, g, t0);
+  issue_x_tile(Xt, p.x, p, b, d0, t0);
+  issue_x_tile(Yt, p.dy, p, b, d0, t0);
+  tc::cp_async_commit();
+  issue_state_tile(Ht, p.H0 + ci * (N * P));
+  issue_state_tile(Dt, p.dH1 + ci * (N * P));
+  tc::cp_async_commit();
   load_chunk_scalars(p, b, head, c, s);
   for (int u = tid; u < 8 * Q; u += 256) { csw_e[u] = 0.f; }  // csw_e and csw_l are contiguous
   float* re = part;  // [Q] row scale r e of x (part itself is written only at the end)
   if (tid < Q) re[tid] = s.r[tid] * s.e[tid];
+  tc::cp_async_wait<1>();
   __syncthreads();
-  build_rot_tile(Bt, p.b, p, b, g, t0, s.sn, s.cs, nullptr);
-  build_rot_tile(Ct, p.c, p, b, g, t0, s.sn, s.cs, nullptr);
-  build_x_tile(Xt, p.x, p, b, d0, t0, nullptr);
-  build_x_tile(Xs, p.x, p, b, d0, t0, re);
-  build_x_tile(Yt, p.dy, p, b, d0, t0, nullptr);
-  build_x_tile(Ys, p.dy, p, b, d0, t0, s.dexp);
-  build_state_tile(Ht, p.H0 + ci * (N * P));
-  build_state_tile(Dt, p.dH1 + ci * (N * P));
+  rotate_tile(Bt, s.sn, s.cs);
+  rotate_tile(Ct, s.sn, s.cs);
+  scale_x_tile(Xs, Xt, re);
+  scale_x_tile(Ys, Yt, s.dexp);
+  tc::cp_async_wait<0>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -469,36 +493,45 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
       ld_acc32(taddr + 0, warp, c0, fg);
       ld_acc32(taddr + 64, warp, c0, fd);
       float rs = 0.f;
-      float gm[32], dg[32];
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) {
-        const int sx = c0 + jj;
-        float Mv = 0.f, Dv = 0.f;
-        const bool in = own && sx <= t;
-        if (in) {
-          Dv = __expf(lt - s.Lam[sx]);
-          Mv = Dv * (sx < t ? s.e[sx] : gt);
+      for (int hx = 0; hx < 2; ++hx) {  // 16 columns at a time keeps the live registers low
+        float gm[16], dg[16], ce[16], cl[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const int jj = 16 * hx + q, sx = c0 + jj;
+          float Mv = 0.f, Dv = 0.f;
+          const bool in = own && sx <= t;
+          if (in) {
+            Dv = __expf(lt - s.Lam[sx]);
+            Mv = Dv * (sx < t ? s.e[sx] : gt);
+          }
+          const float dGM = in ? fd[jj] : 0.f;
+          gm[q] = fg[jj] * Mv;             // (G*M)_ts
+          dg[q] = dGM * Mv;                // dG_ts
+          const float dM = dGM * fg[jj];
+          const float dw = dM * Dv;
+          const float ml = dM * Mv;
+          rs += ml;
+          if (in && sx == t) dg_own += dw;
+          ce[q] = (in && sx < t) ? dw : 0.f;   // de_s and dLam_s: column sums over the rows of this warp
+          cl[q] = ml;
         }
-        const float dGM = in ? fd[jj] : 0.f;
-        gm[jj] = fg[jj] * Mv;             // (G*M)_ts
-        dg[jj] = dGM * Mv;                // dG_ts
-        const float dM = dGM * fg[jj];
-        const float dw = dM * Dv;
-        const float ml = dM * Mv;
-        rs += ml;
-        if (in && sx == t) dg_own += dw;
-        const float ce = warp_sum((in && sx < t) ? dw : 0.f);   // de_s: column sums over the rows of this warp
-        const float cl = warp_sum(ml);
-        if (lane == 0) { csw_e[(warp & 3) * Q + sx] += ce; csw_l[(warp & 3) * Q + sx] -= cl; }
+        if (own) {
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            sts16(GMt, tc::kmajor_unit(t, (c0 >> 3) + 2 * hx + x, Q), pack8(&gm[8 * x]));
+            sts16(dGt, tc::kmajor_unit(t, (c0 >> 3) + 2 * hx + x, Q), pack8(&dg[8 * x]));
+          }
+        }
+        colsum16(ce, lane);
+        colsum16(cl, lane);
+        if (own) {
+          const int sx = c0 + 16 * hx + (lane & 15);
+          csw_e[(warp & 3) * Q + sx] += ce[0];
+          csw_l[(warp & 3) * Q + sx] -= cl[0];
+        }
       }
       dl_own += rs;
-      if (own) {
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          sts16(GMt, tc::kmajor_unit(t, (c0 >> 3) + x, Q), pack8(&gm[8 * x]));
-          sts16(dGt, tc::kmajor_unit(t, (c0 >> 3) + x, Q), pack8(&dg[8 * x]));
-        }
-      }
     }
   }
   {
