@@ -66,6 +66,14 @@ __device__ __forceinline__ void ld_acc32(uint32_t taddr, int warp, int c0, float
   for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void ld_acc16(uint32_t taddr, int warp, int c0, float (&f)[16]) {
+  uint32_t r[16];
+  tc::tmem_ld_32x32b_x16(taddr + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0, r);
+  tc::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(r[i]);
+}
+
 // Per-chunk scalars in shared memory (128 threads; call by all, ends with a barrier).
 struct ChunkScal {
   float dt[Q], lam[Q], Lam[Q], gam[Q], e[Q], sn[Q], cs[Q], dexp[Q], r[Q];
@@ -333,7 +341,8 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
           const int sx = c0 + jj;
-          f[jj] = (sx <= t) ? f[jj] * __expf(lt - s.Lam[sx]) * (sx < t ? s.e[sx] : gt) : 0.f;
+          const float mv = __expf(fminf(lt - s.Lam[sx], 0.f)) * (sx < t ? s.e[sx] : gt);  // no branch
+          f[jj] = (sx <= t) ? f[jj] * mv : 0.f;
         }
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Gm, tc::kmajor_unit(t, (c0 >> 3) + x, Q), pack8(&f[8 * x]));
@@ -487,51 +496,62 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   }
   __syncthreads();  // every read of the x tile is done: G*M may overwrite it
   if (ok) {
-    {  // G and dY X^T: 32 columns per half
-      const int c0 = 32 * hc;
-      float fg[32], fd[32];
-      ld_acc32(taddr + 0, warp, c0, fg);
-      ld_acc32(taddr + 64, warp, c0, fd);
-      float rs = 0.f;
-#pragma unroll
-      for (int hx = 0; hx < 2; ++hx) {  // 16 columns at a time keeps the live registers low
-        float gm[16], dg[16], ce[16], cl[16];
+    {  // G and dY X^T: 32 columns per half.  Lanes 16-31 hold no accumulator rows; they take over columns
+       // 16..31 of the row of lane - 16, so all 32 lanes share the mask arithmetic.
+      const int c0 = 32 * hc, hx = lane >> 4;
+      float fg[16], fd[16];
+      {
+        float fa[32];
+        ld_acc32(taddr + 0, warp, c0, fa);
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
-          const int jj = 16 * hx + q, sx = c0 + jj;
-          float Mv = 0.f, Dv = 0.f;
-          const bool in = own && sx <= t;
-          if (in) {
-            Dv = __expf(lt - s.Lam[sx]);
-            Mv = Dv * (sx < t ? s.e[sx] : gt);
-          }
-          const float dGM = in ? fd[jj] : 0.f;
-          gm[q] = fg[jj] * Mv;             // (G*M)_ts
-          dg[q] = dGM * Mv;                // dG_ts
-          const float dM = dGM * fg[jj];
-          const float dw = dM * Dv;
-          const float ml = dM * Mv;
-          rs += ml;
-          if (in && sx == t) dg_own += dw;
-          ce[q] = (in && sx < t) ? dw : 0.f;   // de_s and dLam_s: column sums over the rows of this warp
-          cl[q] = ml;
+          const float up = __shfl_sync(0xffffffffu, fa[16 + q], lane & 15);
+          fg[q] = hx ? up : fa[q];
         }
-        if (own) {
+        ld_acc32(taddr + 64, warp, c0, fa);
 #pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            sts16(GMt, tc::kmajor_unit(t, (c0 >> 3) + 2 * hx + x, Q), pack8(&gm[8 * x]));
-            sts16(dGt, tc::kmajor_unit(t, (c0 >> 3) + 2 * hx + x, Q), pack8(&dg[8 * x]));
-          }
-        }
-        colsum16(ce, lane);
-        colsum16(cl, lane);
-        if (own) {
-          const int sx = c0 + 16 * hx + (lane & 15);
-          csw_e[(warp & 3) * Q + sx] += ce[0];
-          csw_l[(warp & 3) * Q + sx] -= cl[0];
+        for (int q = 0; q < 16; ++q) {
+          const float up = __shfl_sync(0xffffffffu, fa[16 + q], lane & 15);
+          fd[q] = hx ? up : fa[q];
         }
       }
+      float rs = 0.f, dgc = 0.f;
+      float gm[16], dg[16], ce[16], cl[16];
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        const int sx = c0 + 16 * hx + q;
+        // branch-free so that the exponentials of different columns overlap
+        const bool in = sx <= t;
+        const float Dv = in ? __expf(fminf(lt - s.Lam[sx], 0.f)) : 0.f;
+        const float Mv = Dv * (sx < t ? s.e[sx] : gt);
+        const float dGM = in ? fd[q] : 0.f;
+        const float gv = in ? fg[q] : 0.f;
+        gm[q] = gv * Mv;                 // (G*M)_ts
+        dg[q] = dGM * Mv;                // dG_ts
+        const float dM = dGM * gv;
+        const float dw = dM * Dv;
+        const float ml = dM * Mv;
+        rs += ml;
+        dgc += (sx == t) ? dw : 0.f;
+        ce[q] = (sx < t) ? dw : 0.f;     // de_s and dLam_s: column sums over the 16 rows of this warp
+        cl[q] = ml;
+      }
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        sts16(GMt, tc::kmajor_unit(t, (c0 >> 3) + 2 * hx + x, Q), pack8(&gm[8 * x]));
+        sts16(dGt, tc::kmajor_unit(t, (c0 >> 3) + 2 * hx + x, Q), pack8(&dg[8 * x]));
+      }
+      colsum16(ce, lane);  // the two 16-lane halves reduce their own 16 columns side by side
+      colsum16(cl, lane);
+      {
+        const int sx = c0 + 16 * hx + (lane & 15);
+        csw_e[(warp & 3) * Q + sx] += ce[0];
+        csw_l[(warp & 3) * Q + sx] -= cl[0];
+      }
+      rs += __shfl_xor_sync(0xffffffffu, rs, 16);
+      dgc += __shfl_xor_sync(0xffffffffu, dgc, 16);
       dl_own += rs;
+      dg_own += dgc;
     }
   }
   {
