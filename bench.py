@@ -265,8 +265,8 @@ def main():
         margs = [d[k] for k in ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")]
 
         def step():
-            ops.mamba3_selective_scan(*margs, nheads=NH)
-            ops.mamba3_selective_scan_backward(*margs, d["dy"], nheads=NH)
+            ops.mamba3_selective_scan(*margs, nheads=NH, save_for_backward=True)
+            ops.mamba3_selective_scan_backward(*margs, d["dy"], nheads=NH, use_saved=True)
 
         cfg = {"workload": "mamba3_train", **w, "io": "bf16", "layout": "head-broadcast dt/lambda/theta/a_log"}
 

@@ -172,8 +172,14 @@ typedef struct {
 enum {
   MXB_MAMBA3_CHANNEL_KERNELS = 1,  /* head-broadcast layout: use the warp-per-channel kernels even
                                       where the CTA-per-head kernels cover the shape */
-  MXB_MAMBA3_RECURRENT_KERNELS = 2 /* use the recurrent (CTA-per-head) kernels even where the chunked
+  MXB_MAMBA3_RECURRENT_KERNELS = 2,/* use the recurrent (CTA-per-head) kernels even where the chunked
                                       tensor-core kernels cover the shape */
+  MXB_MAMBA3_SAVE_FOR_BWD = 4,     /* forward: mxb_mamba3_fwd_workspace_bytes returns the backward size and
+                                      the chunk states and per-token scalars stay in the workspace */
+  MXB_MAMBA3_BWD_USE_SAVED = 8     /* backward: the workspace is the one a forward call with
+                                      MXB_MAMBA3_SAVE_FOR_BWD just filled for the same inputs; the forward
+                                      recompute is skipped.  Honoured by the chunked tensor-core kernels;
+                                      the other kernel families recompute as always. */
 };
 
 MXB_API size_t mxb_mamba3_fwd_workspace_bytes(const mxb_mamba3_desc* d);

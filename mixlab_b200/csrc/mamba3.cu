@@ -376,7 +376,7 @@ static size_t carve_m3(M3P& p, void* ws, bool io_f32, size_t partial_floats = 0,
 }
 
 size_t mamba3_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
-  if (use_ssd(d)) return mamba3_ssd_workspace_bytes(d, bwd);
+  if (use_ssd(d)) return mamba3_ssd_workspace_bytes(d, bwd || (d->flags & MXB_MAMBA3_SAVE_FOR_BWD));
   if (!bwd) return 0;
   M3P p = make_m3(d);
   const bool head = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);

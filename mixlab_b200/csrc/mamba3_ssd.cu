@@ -818,8 +818,13 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
   p.ddt = ddt; p.dlam = dlam; p.dtheta = dtheta; p.da_log = da_log;
   carve_ssd(p, ws, true);
   p.y = nullptr;  // the forward recompute stops at the chunk states
-  mxb_status s = ssd_forward(p, st);
-  if (s != MXB_OK) return s;
+  if (d->flags & MXB_MAMBA3_BWD_USE_SAVED) {  // dt, lambda, phi, the chunk decays and H0 are still in place
+    if (cudaMemsetAsync(p.status, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
+    if (ssd_smem(m3s::m3s_chunk_outer_kernel, m3s::kOuterSmem) != MXB_OK) return MXB_ERR_CUDA;
+  } else {
+    mxb_status s = ssd_forward(p, st);
+    if (s != MXB_OK) return s;
+  }
   if (cudaMemsetAsync(da_log, 0, (size_t)p.NH * sizeof(float), st) != cudaSuccess) return MXB_ERR_CUDA;
   const dim3 gc(p.n, p.NH, p.B);
   MXB_LAUNCH("m3s_chunk_outer_kernel", st, (m3s::m3s_chunk_outer_kernel<<<gc, 128, m3s::kOuterSmem, st>>>(p, 1)));

@@ -138,8 +138,12 @@ def mamba3_desc(x, b, nheads, flags=0) -> Mamba3Desc:
     return Mamba3Desc(B, T, D, N, G, int(nheads), _io(x), int(flags))
 
 
-def mamba3_selective_scan(x, dt, lam, theta, a_log, b, c, *, nheads=0, flags=0):
-    """Forward.  x [B,T,D]; b,c [B,T,G,N]; per-channel (nheads=0) or head-broadcast parameters."""
+def mamba3_selective_scan(x, dt, lam, theta, a_log, b, c, *, nheads=0, flags=0, save_for_backward=False):
+    """Forward.  x [B,T,D]; b,c [B,T,G,N]; per-channel (nheads=0) or head-broadcast parameters.
+    ``save_for_backward`` keeps the chunk states in the cached workspace for a following
+    ``mamba3_selective_scan_backward(..., use_saved=True)`` on the same inputs."""
+    if save_for_backward:
+        flags |= _lib.MXB_MAMBA3_SAVE_FOR_BWD
     _require_cuda(x, dt, lam, theta, a_log, b, c)
     l = _lib.lib()
     d = mamba3_desc(x, b, nheads, flags)
@@ -152,8 +156,10 @@ def mamba3_selective_scan(x, dt, lam, theta, a_log, b, c, *, nheads=0, flags=0):
     return y
 
 
-def mamba3_selective_scan_backward(x, dt, lam, theta, a_log, b, c, dy, *, nheads=0, flags=0):
+def mamba3_selective_scan_backward(x, dt, lam, theta, a_log, b, c, dy, *, nheads=0, flags=0, use_saved=False):
     """Gradients in argument order.  Returns dict(dx, ddt, dlambda, dtheta, da_log, db, dc)."""
+    if use_saved:
+        flags |= _lib.MXB_MAMBA3_BWD_USE_SAVED
     _require_cuda(x, dt, lam, theta, a_log, b, c, dy)
     l = _lib.lib()
     d = mamba3_desc(x, b, nheads, flags)

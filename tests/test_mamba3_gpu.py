@@ -155,3 +155,20 @@ def test_chunked_tensor_core_kernels(cfg):
         except AssertionError as e:
             errs[name] = str(e)[:200]
     assert all(not isinstance(v, str) for v in errs.values()), errs
+
+
+@pytest.mark.parametrize("cfg", [(2, 200, 2, 1), (1, 330, 4, 2)])
+def test_chunked_backward_from_saved_forward(cfg):
+    """Forward with save_for_backward + backward with use_saved == backward with its own recompute, bit for bit
+    (the same kernels run on the same chunk states)."""
+    B, T, H, Gr = cfg
+    a = inputs.mamba3_inputs(B, T, H, 64, 128, G=Gr, seed=8, io_dtype=torch.bfloat16, per_head=True)
+    dev = [_dev(a[k]) for k in ARGS]
+    dy = _dev(a["dy"])
+    want = ops.mamba3_selective_scan_backward(*dev, dy, nheads=H)
+    y0 = ops.mamba3_selective_scan(*dev, nheads=H)
+    y = ops.mamba3_selective_scan(*dev, nheads=H, save_for_backward=True)
+    got = ops.mamba3_selective_scan_backward(*dev, dy, nheads=H, use_saved=True)
+    assert torch.equal(y, y0)
+    for name in GRADS:
+        assert torch.equal(got[name], want[name]), name
