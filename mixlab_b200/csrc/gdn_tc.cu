@@ -30,11 +30,16 @@ namespace mxb {
 // swizzle; rows past the end of the sequence are zero-filled by the copy engine) and the MMAs read
 // them through swizzled descriptors.  TMA = false: the same tiles staged with cp.async in the
 // un-swizzled layout (kept as a cross-check and for drivers without the tensor-map entry point).
-constexpr int kPrepSmem = 32768 + 16384 + 3 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 1024;
+constexpr int kPrepSmem = 32768 + 16384 + 4 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 1024;
 
 struct alignas(64) PrepMaps {
   CUtensorMap k, q, v;  // [B,T,H,128] bf16 viewed as (D, H, T, B), box (64, 1, 64, 1)
 };
+
+__device__ __forceinline__ uint4 pack8f(const float* e) {
+  return make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]), tc::pack_bf16(e[4], e[5]),
+                    tc::pack_bf16(e[6], e[7]));
+}
 
 template <bool TMA>
 __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_constant__ PrepMaps maps) {
@@ -45,7 +50,8 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   uint8_t* Tt = Vt + 16384;             // [64 i][64 m] T
   uint8_t* Tb = Tt + 8192;              // [64 i][64 m] T diag(beta)
   uint8_t* Tbd = Tb + 8192;             // [64 i][64 m] T diag(beta E(gam))
-  float* Am = reinterpret_cast<float*>(Tbd + 8192);  // [64][LDA]
+  uint8_t* Pt = Tbd + 8192;             // [64 i][64 m] P image on its way to the workspace
+  float* Am = reinterpret_cast<float*>(Pt + 8192);   // [64][LDA]  A, then T in place
   float* gam = Am + C * LDA;
   float* bet = gam + C;
   float* bd = bet + C;
@@ -151,32 +157,91 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
           const float x1 = (j + 1 <= i) ? f[jj + 1] * exp_nonpos(gi - gam[j + 1]) : 0.f;
           pk[jj >> 1] = tc::pack_bf16(x0, x1);
         }
-        uint4* dst = reinterpret_cast<uint4*>(p.P + (ci * C + i) * C + c0);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
+        for (int x = 0; x < 4; ++x)
+          sts16(Pt, tc::kmajor_unit(i, (c0 >> 3) + x, C), make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]));
       }
     }
   }
+  tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  // T = (I - A)^-1 in fp32: thread = column, rows by forward substitution, column kept in registers
-  if (ok && tid < C) {
-    float Tc[C];
+  if (ok && tid == 0) {  // P leaves as the byte image of its operand tile
+    tc::bulk_store(p.P + ci * C * C, tc::smem_u32(Pt), 8192);
+    tc::bulk_commit();
+  }
+  // T = (I - A)^-1 in fp32, in place over A.  The two 32 x 32 diagonal blocks by forward substitution
+  // (thread = block and column, the column in registers), then the off-diagonal block
+  // T21 = T22 (A21 T11) as two small fp32 products over all 128 threads.
+  {
+    float Tc[32];
+    const int blk = (tid >> 5) & 1, cc = tid & 31, r0 = 32 * blk;
+    if (ok && tid < C) {
 #pragma unroll
-    for (int i = 0; i < C; ++i) {
-      float s = (i == tid) ? 1.f : 0.f;
+      for (int i = 0; i < 32; ++i) {
+        const float* arow = Am + (r0 + i) * LDA + r0;
+        float s0 = (i == cc) ? 1.f : 0.f, s1 = 0.f;
 #pragma unroll
-      for (int j = 0; j < i; ++j) s = fmaf(Am[i * LDA + j], Tc[j], s);
-      Tc[i] = (i < tid) ? 0.f : s;
+        for (int j = 0; j + 1 < i; j += 2) {
+          s0 = fmaf(arow[j], Tc[j], s0);
+          s1 = fmaf(arow[j + 1], Tc[j + 1], s1);
+        }
+        if (i & 1) s0 = fmaf(arow[i - 1], Tc[i - 1], s0);
+        Tc[i] = (i < cc) ? 0.f : s0 + s1;
+      }
     }
-    const float bm = bet[tid], bdm = bd[tid];
+    __syncthreads();  // every thread has read its block of A
+    if (ok && tid < C) {
 #pragma unroll
-    for (int i = 0; i < C; ++i) {
-      const uint32_t off = tc::kmajor_unit(i, tid >> 3, C) + (tid & 7) * 2;
-      *reinterpret_cast<bf16*>(Tt + off) = __float2bfloat16_rn(Tc[i]);
-      *reinterpret_cast<bf16*>(Tb + off) = __float2bfloat16_rn(Tc[i] * bm);
-      *reinterpret_cast<bf16*>(Tbd + off) = __float2bfloat16_rn(Tc[i] * bdm);
+      for (int i = 0; i < 32; ++i) Am[(r0 + i) * LDA + r0 + cc] = Tc[i];
+    }
+    __syncthreads();
+    const int i2 = tid >> 2, jb = (tid & 3) * 8;  // row i2 of the lower-left block, 8 of its columns
+    {  // X = A21 T11 -> the unused upper-right block
+      float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+      for (int k = 0; k < 32; ++k) {
+        const float a = Am[(32 + i2) * LDA + k];
+        const float4 t0 = *reinterpret_cast<const float4*>(Am + k * LDA + jb);
+        const float4 t1 = *reinterpret_cast<const float4*>(Am + k * LDA + jb + 4);
+        x[0] = fmaf(a, t0.x, x[0]); x[1] = fmaf(a, t0.y, x[1]); x[2] = fmaf(a, t0.z, x[2]); x[3] = fmaf(a, t0.w, x[3]);
+        x[4] = fmaf(a, t1.x, x[4]); x[5] = fmaf(a, t1.y, x[5]); x[6] = fmaf(a, t1.z, x[6]); x[7] = fmaf(a, t1.w, x[7]);
+      }
+      *reinterpret_cast<float4*>(Am + i2 * LDA + 32 + jb) = make_float4(x[0], x[1], x[2], x[3]);
+      *reinterpret_cast<float4*>(Am + i2 * LDA + 32 + jb + 4) = make_float4(x[4], x[5], x[6], x[7]);
+    }
+    __syncthreads();
+    {  // T21 = T22 X -> over A21 (nothing reads A21 any more)
+      float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 8
+      for (int k = 0; k < 32; ++k) {
+        const float a = Am[(32 + i2) * LDA + 32 + k];
+        const float4 t0 = *reinterpret_cast<const float4*>(Am + k * LDA + 32 + jb);
+        const float4 t1 = *reinterpret_cast<const float4*>(Am + k * LDA + 32 + jb + 4);
+        y[0] = fmaf(a, t0.x, y[0]); y[1] = fmaf(a, t0.y, y[1]); y[2] = fmaf(a, t0.z, y[2]); y[3] = fmaf(a, t0.w, y[3]);
+        y[4] = fmaf(a, t1.x, y[4]); y[5] = fmaf(a, t1.y, y[5]); y[6] = fmaf(a, t1.z, y[6]); y[7] = fmaf(a, t1.w, y[7]);
+      }
+      *reinterpret_cast<float4*>(Am + (32 + i2) * LDA + jb) = make_float4(y[0], y[1], y[2], y[3]);
+      *reinterpret_cast<float4*>(Am + (32 + i2) * LDA + jb + 4) = make_float4(y[4], y[5], y[6], y[7]);
+    }
+    __syncthreads();
+    // bf16 operand tiles T, T diag(beta), T diag(beta E(gam)); the upper triangle (it holds X) reads as zero
+    for (int u = tid; u < 64 * 8; u += 128) {
+      const int i = urow8(u), c8 = ucol8(u);
+      const float4 a0 = *reinterpret_cast<const float4*>(Am + i * LDA + 8 * c8);
+      const float4 a1 = *reinterpret_cast<const float4*>(Am + i * LDA + 8 * c8 + 4);
+      float e[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, eb[8], ed[8];
+#pragma unroll
+      for (int y = 0; y < 8; ++y) {
+        const int m = 8 * c8 + y;
+        e[y] = (m <= i) ? e[y] : 0.f;
+        eb[y] = e[y] * bet[m];
+        ed[y] = e[y] * bd[m];
+      }
+      sts16(Tt, 16 * u, pack8f(e));
+      sts16(Tb, 16 * u, pack8f(eb));
+      sts16(Tbd, 16 * u, pack8f(ed));
     }
   }
   if (TMA) { if (ok) ok = tc::mbar_wait(&mbar[2], 0); }  // v
@@ -193,30 +258,37 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(Tbd, C), bk, 64, KD, C, false);
     tc::mma_commit(mbar);
   }
-  // T -> workspace (bf16, row-major) while the MMA runs
-  for (int u = tid; u < 64 * 8; u += 128) {
-    const int i = urow8(u), c8 = ucol8(u);
-    *reinterpret_cast<uint4*>(p.Tm + (ci * C + i) * C + c8 * 8) =
-        *reinterpret_cast<const uint4*>(Tt + tc::kmajor_unit(i, c8, C));
+  if (ok && tid == 0) {  // T leaves as the byte image of its operand tile while the MMA runs
+    tc::bulk_store(p.Tm + ci * C * C, tc::smem_u32(Tt), 8192);
+    tc::bulk_commit();
   }
   if (ok) ok = tc::mbar_wait(mbar, 1);
   tc::fence_after_sync();
   if (ok) {
+    // u and w are assembled as operand-layout images over v and [k;q] (dead once the MMA has completed)
     const int i = 16 * warp + (lane & 15);  // M=64: row m sits in TMEM lane (m%16) + 32*(m/16)
     for (int c0 = 0; c0 < 256; c0 += 32) {
       float f[32];
       ld_acc32(taddr, warp, c0, f);
       if (lane < 16) {
-        bf16* base = (c0 < 128) ? p.u + (ci * C + i) * KD + c0 : p.w + (ci * C + i) * KD + (c0 - 128);
-        uint4* dst = reinterpret_cast<uint4*>(base);
+        uint8_t* tile = (c0 < 128) ? Vt : Akq;
 #pragma unroll
-        for (int x = 0; x < 4; ++x)
-          dst[x] = make_uint4(tc::pack_bf16(f[8 * x], f[8 * x + 1]), tc::pack_bf16(f[8 * x + 2], f[8 * x + 3]),
-                              tc::pack_bf16(f[8 * x + 4], f[8 * x + 5]), tc::pack_bf16(f[8 * x + 6], f[8 * x + 7]));
+        for (int x = 0; x < 4; ++x) sts16(tile, tc::kmajor_unit(i, ((c0 & 127) >> 3) + x, KD), pack8f(&f[8 * x]));
       }
     }
   } else if (tid == 0) {
     atomicExch(p.status, 1);
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  if (tid == 0) {
+    if (ok) {
+      tc::bulk_store(p.u + ci * C * KD, tc::smem_u32(Vt), 16384);
+      tc::bulk_store(p.w + ci * C * KD, tc::smem_u32(Akq), 16384);
+      tc::bulk_commit();
+    }
+    tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   }
   tc::fence_before_sync();
   __syncthreads();
@@ -261,7 +333,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       const int imax = min(C, p.T - c * C);
       for (int u = tid; u < 128 * 16; u += 256) {
         const int r = urow16(u), c8 = ucol16(u), i = r & 63;
-        if (r < 64) tc::cp_async16(sA1 + tc::kmajor_unit(r, c8, KD), p.w + (ci * C + i) * KD + c8 * 8);
+        if (r < 64) tc::cp_async16(sA1 + 16 * u, p.w + ci * C * KD + 8 * u);  // byte image of the operand tile
         else tc::cp_async16(sA1 + tc::kmajor_unit(r, c8, KD), i < imax ? p.q + grow(c, i) * KD + c8 * 8 : p.q, i < imax);
       }
     }
@@ -272,7 +344,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       const size_t ci = (size_t)bh * p.n + c;
       for (int u = tid; u < 64 * 16; u += 256) {
         const int i = urow16(u), c8 = ucol16(u);
-        tc::cp_async16(sU + tc::kmajor_unit(i, c8, KD), p.u + (ci * C + i) * KD + c8 * 8);
+        tc::cp_async16(sU + 16 * u, p.u + ci * C * KD + 8 * u);
       }
     }
     tc::cp_async_commit();
@@ -283,7 +355,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       const int imax = min(C, p.T - c * C);
       for (int u = tid; u < 64 * 8; u += 256) {
         const int i = urow8(u), c8 = ucol8(u);
-        tc::cp_async16(sA2 + tc::kmajor_unit(64 + i, c8, C), p.P + (ci * C + i) * C + c8 * 8);
+        tc::cp_async16(sA2 + 8192 + 16 * u, p.P + ci * C * C + 8 * u);  // rows 64..127 of the [128][64] tile
       }
       for (int u = tid; u < 64 * 16; u += 256) {
         const int i = urow16(u), c8 = ucol16(u);

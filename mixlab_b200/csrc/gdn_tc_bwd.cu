@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       }
       for (int u = tid; u < 64 * 8; u += 256) {
         const int i = urow8(u), c8 = ucol8(u);
-        tc::cp_async16(sPt + tc::kmajor_unit(i, c8, C), p.P + (ci * C + i) * C + c8 * 8);
+        tc::cp_async16(sPt + 16 * u, p.P + ci * C * C + 8 * u);  // byte image of the operand tile
       }
     }
     tc::cp_async_commit();
@@ -74,7 +74,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       const size_t ci = (size_t)bh * p.n + c;
       for (int u = tid; u < 64 * 16; u += 256) {
         const int i = urow16(u), c8 = ucol16(u);
-        tc::cp_async16(sAqw + tc::kmajor_unit(64 + i, c8, KD), p.w + (ci * C + i) * KD + c8 * 8);
+        tc::cp_async16(sAqw + 16384 + 16 * u, p.w + ci * C * KD + 8 * u);  // rows 64..127 of the [128][128] tile
       }
     }
     tc::cp_async_commit();
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
     }
     for (int u = tid; u < 64 * 8; u += 256) {
       const int r = urow8(u), c8 = ucol8(u);
-      tc::cp_async16(st + tc::kmajor_unit(r, c8, C), p.Tm + (ci * C + r) * C + c8 * 8);
+      tc::cp_async16(st + 16 * u, p.Tm + ci * C * C + 8 * u);
     }
     tc::cp_async_commit();
     for (int u = tid; u < 64 * 16; u += 256) {
