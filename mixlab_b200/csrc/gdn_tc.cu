@@ -412,8 +412,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       const uint4 val = make_uint4(tc::pack_bf16(S[8 * c8], S[8 * c8 + 1]), tc::pack_bf16(S[8 * c8 + 2], S[8 * c8 + 3]),
                                    tc::pack_bf16(S[8 * c8 + 4], S[8 * c8 + 5]), tc::pack_bf16(S[8 * c8 + 6], S[8 * c8 + 7]));
       sts16(Sop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
-      if (p.save) *reinterpret_cast<uint4*>(p.hs + (ci * KD + kk) * KD + j0 + c8 * 8) = val;
     }
+    if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's v_new image has left its tile
     tc::cp_async_wait<2>();  // group A of this chunk has landed
     tc::fence_async_smem();
     tc::fence_before_sync();
@@ -422,6 +422,10 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
     if (tid == 0) {  // D1 = [w;q] S
       tc::issue_gemm(taddr, tc::kmajor_tile(A1, KD), tc::mnmajor_tile(Sop, KD), 128, KD, KD, false);
       tc::mma_commit(mbar);
+      if (p.save) {  // the state at chunk start, saved for the backward as the byte image of the operand tile
+        tc::bulk_store(p.hs + ci * KD * KD, tc::smem_u32(Sop), 32768);
+        tc::bulk_commit();
+      }
     }
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
@@ -450,7 +454,6 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
                                         tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7]));
             sts16(Vn, tc::mnmajor_unit(i, c8, KD), vv);
             sts16(Vr, tc::mnmajor_unit(i, c8, KD), tc::scale_bf16x8(vv, ri));
-            if (p.save) *reinterpret_cast<uint4*>(p.vn + (ci * C + i) * KD + c8 * 8) = vv;
           }
         } else {        // E(gam_i) (q S), kept until P v_new arrives
           const float di = dd[i];
@@ -459,6 +462,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
         }
       }
     }
+    if (tid == 0) tc::bulk_wait_read<0>();  // the state image has left its tile
     tc::cp_async_wait<1>();  // group PK of this chunk (group A of the next one may still fly)
     tc::fence_async_smem();
     tc::fence_before_sync();
@@ -470,6 +474,10 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       tc::issue_gemm(taddr + 128, tc::kmajor_tile(A2, C), tc::mnmajor_tile(Vn, KD), 128, KD, C, false);
       tc::issue_gemm(taddr + 256, tc::mnmajor_tile(A3, KD), tc::mnmajor_tile(Vr, KD), 128, KD, C, false);
       tc::mma_commit(mbar);
+      if (p.save) {
+        tc::bulk_store(p.vn + ci * C * KD, tc::smem_u32(Vn), 16384);
+        tc::bulk_commit();
+      }
     }
     if (ok) {
       ok = tc::mbar_wait(mbar, ph);
@@ -501,6 +509,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
     tc::fence_before_sync();
   }
   tc::cp_async_wait<0>();
+  if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 2);
   if (ok && p.hT) {
     float4* dst = reinterpret_cast<float4*>(p.hT + ((size_t)bh * KD + kk) * KD + j0);

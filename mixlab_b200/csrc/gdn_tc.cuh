@@ -31,10 +31,11 @@ struct TcP {
   bf16* w;       // [C][KD]
   bf16* u;       // [C][KD]
   bf16* P;       // [C][C]
+  // Everything below is stored as the byte image of the blocked shared-memory operand tile it is read into.
   bf16* hs;      // [KD][KD]  state at chunk start   (backward only)
   bf16* vn;      // [C][KD]
   bf16* dhs;     // [KD][KD]  dS at chunk end
-  bf16* dvn;     // [C][KD]
+  bf16* dvn;     // [C][KD]   -dv_new (the sign the state pass needs as an operand)
   bf16* dqp;     // [C][KD]   d (dO S0^T)        } state contractions of the chunk backward,
   bf16* dkp;     // [C][KD]   r (v_new dS^T)     } handed from its first kernel to its second
   bf16* dw;      // [C][KD]   -dv_new S0^T       }

@@ -124,8 +124,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       const uint4 val = make_uint4(tc::pack_bf16(dS[8 * c8], dS[8 * c8 + 1]), tc::pack_bf16(dS[8 * c8 + 2], dS[8 * c8 + 3]),
                                    tc::pack_bf16(dS[8 * c8 + 4], dS[8 * c8 + 5]), tc::pack_bf16(dS[8 * c8 + 6], dS[8 * c8 + 7]));
       sts16(dSop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
-      *reinterpret_cast<uint4*>(p.dhs + (ci * KD + kk) * KD + j0 + c8 * 8) = val;
     }
+    if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's -dv_new image has left its tile
     tc::cp_async_wait<1>();  // group A of this chunk
     __syncthreads();         // dO tile and dd visible to every thread
     for (int u = tid; u < 64 * 16; u += 256) {  // d dO
@@ -142,6 +142,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Pt, C), tc::mnmajor_tile(dOop, KD), 64, KD, C, false);     // P^T dO
       tc::issue_gemm(taddr + 256, tc::mnmajor_tile(Aqw, KD), tc::mnmajor_tile(Bdd, KD), 128, KD, C, false);   // q^T (d dO)
       tc::mma_commit(mbar);
+      tc::bulk_store(p.dhs + ci * KD * KD, tc::smem_u32(dSop), 32768);  // dS at chunk end, as the operand-tile image
+      tc::bulk_commit();
     }
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
@@ -163,12 +165,12 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
             const uint4 vv = make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
                                         tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7]));
             const int c8 = 8 * half + (c0 >> 3) + x;
-            *reinterpret_cast<uint4*>(p.dvn + (ci * C + i) * KD + c8 * 8) = vv;
             sts16(Bdd, tc::kmajor_unit(64 + i, c8, KD), tc::scale_bf16x8(vv, -1.f));
           }
         }
       }
     }
+    if (tid == 0) tc::bulk_wait_read<0>();  // the dS image has left its tile
     tc::cp_async_wait<1>();  // group B (w) of this chunk
     tc::fence_async_smem();
     tc::fence_before_sync();
@@ -178,6 +180,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       tc::issue_gemm(taddr + 256, tc::skip_k(tc::mnmajor_tile(Aqw, KD), 64), tc::skip_k(tc::mnmajor_tile(Bdd, KD), 64),
                      128, KD, C, true);
       tc::mma_commit(mbar);
+      tc::bulk_store(p.dvn + ci * C * KD, tc::smem_u32(Bdd) + 16384, 16384);  // -dv_new: rows 64..127 of the operand tile
+      tc::bulk_commit();
     }
     if (ok) {
       ok = tc::mbar_wait(mbar, ph);
@@ -196,6 +200,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
     tc::fence_before_sync();
   }
   tc::cp_async_wait<0>();
+  if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 3);
   if (ok && p.dh0) {
     float4* dst = reinterpret_cast<float4*>(p.dh0 + ((size_t)bh * KD + kk) * KD + j0);
@@ -243,7 +248,7 @@ __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, c
 // CTAs share an SM.  S0 and dS use the same shared-memory buffer one after the other.  The four results are
 // assembled in shared memory in the blocked operand layout and leave as contiguous 16 KB / 8 KB bulk
 // copies; the second kernel loads those byte images back unchanged.
-//   phase 1: dO S0^T [0,128), dv_new S0^T [128,256)   -> dqp = d (dO S0^T), dw = -dv_new S0^T
+//   phase 1: dO S0^T [0,128), (-dv_new) S0^T [128,256) -> dqp = d (dO S0^T), dw = -dv_new S0^T
 //   phase 2: v_new dS^T [0,128), dO v_new^T [128,192) -> dkp = r (v_new dS^T), dP*Gamma, L <dS, S0>
 constexpr int kChunkBwdStateSmem = 4 * 16384 + 32768 + 4 * C * 4 + 64 + 256;
 
@@ -251,7 +256,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
   uint8_t* Xdo = sm;                // [64][128] dO            -> later the dkp image
-  uint8_t* Xdvn = Xdo + 16384;      // [64][128] dv_new        -> later the dqp image
+  uint8_t* Xdvn = Xdo + 16384;      // [64][128] -dv_new       -> later the dqp image
   uint8_t* Xvn = Xdvn + 16384;      // [64][128] v_new         -> later the dP*Gamma image (first half)
   uint8_t* Xst = Xvn + 16384;       // the dw image
   uint8_t* Xs = Xst + 16384;        // [128][128] S0, then dS
@@ -276,17 +281,11 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
       const int r = urow16(u), c8 = ucol16(u);
       const uint32_t off = tc::kmajor_unit(r, c8, KD);
       tc::cp_async16(sdo + off, r < imax ? p.dO + row(r) * KD + c8 * 8 : p.dO, r < imax);
-      tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
+      tc::cp_async16(sdvn + 16 * u, p.dvn + ci * C * KD + 8 * u);  // byte images of the operand tiles from here on
     }
-    for (int u = tid; u < 128 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
-      tc::cp_async16(ss + tc::kmajor_unit(r, c8, KD), p.hs + (ci * KD + r) * KD + c8 * 8);
-    }
+    for (int u = tid; u < 128 * 16; u += 256) tc::cp_async16(ss + 16 * u, p.hs + ci * KD * KD + 8 * u);
     tc::cp_async_commit();
-    for (int u = tid; u < 64 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
-      tc::cp_async16(svn + tc::kmajor_unit(r, c8, KD), p.vn + (ci * C + r) * KD + c8 * 8);
-    }
+    for (int u = tid; u < 64 * 16; u += 256) tc::cp_async16(svn + 16 * u, p.vn + ci * C * KD + 8 * u);
     tc::cp_async_commit();
   }
   if (warp == 0) {
@@ -313,7 +312,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   bool ok = true;
   if (tid == 0) {
     tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);     // dO S0^T
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);  // dv_new S0^T
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);  // -dv_new S0^T
     tc::mma_commit(mbar);
   }
   uint4 s0u[8];  // this thread's 8 units of S0, kept for <dS, S0> (the buffer is about to be reused)
@@ -323,10 +322,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   tc::fence_after_sync();
   {  // S0 is dead in shared memory: fetch dS into the same buffer behind the epilogue
     const uint32_t ss = tc::smem_u32(Xs);
-    for (int u = tid; u < 128 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
-      tc::cp_async16(ss + tc::kmajor_unit(r, c8, KD), p.dhs + (ci * KD + r) * KD + c8 * 8);
-    }
+    for (int u = tid; u < 128 * 16; u += 256) tc::cp_async16(ss + 16 * u, p.dhs + ci * KD * KD + 8 * u);
     tc::cp_async_commit();
   }
   const float di = dd[i], ri = rr[i], gi = gam[i];
@@ -341,9 +337,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
         for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
       ld_acc32(taddr + 128, warp, c0, f);
-      if (own) {
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) f[jj] = -f[jj];
+      if (own) {  // the workspace holds -dv_new, so this is dw = -dv_new S0^T already
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Xst, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
@@ -429,7 +423,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   uint8_t* Xq = Xk + 16384;         // [64][128] q
   uint8_t* Xv = Xq + 16384;         // [64][128] v; then Y = T^T dT (first half); then the dqp image -> dq
   uint8_t* X2 = Xv;
-  uint8_t* Xdvn = Xv + 16384;       // [64][128] dv_new, then T^T dv_new in place; then the dkp image -> dk
+  uint8_t* Xdvn = Xv + 16384;       // [64][128] -dv_new, then T^T dv_new in place; then the dkp image -> dk
   uint8_t* Xdw = Xdvn + 16384;      // [64][128] dw, then z = T^T dw in place
   uint8_t* Xt = Xdw + 16384;        // [64][64]  T
   uint8_t* Xpg = Xt + 8192;         // [64][64]  dP*Gamma
@@ -461,8 +455,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
     for (int u = tid; u < 64 * 16; u += 256) {
       const int r = urow16(u), c8 = ucol16(u);
       const uint32_t off = tc::kmajor_unit(r, c8, KD);
-      tc::cp_async16(sdvn + off, p.dvn + (ci * C + r) * KD + c8 * 8);
-      tc::cp_async16(sdw + 16 * u, p.dw + ci * C * KD + 8 * u);  // written in the blocked layout already
+      tc::cp_async16(sdvn + 16 * u, p.dvn + ci * C * KD + 8 * u);  // byte images of the operand tiles (-dv_new, dw)
+      tc::cp_async16(sdw + 16 * u, p.dw + ci * C * KD + 8 * u);
     }
     for (int u = tid; u < 64 * 8; u += 256) {
       const int r = urow8(u), c8 = ucol8(u);
@@ -537,6 +531,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
       float f[32];
       ld_acc32(taddr + 0, warp, c0, f);
       if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) f[jj] = -f[jj];  // the workspace holds -dv_new
         vdot += row_dot32(Xv, i, c0, f);
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
