@@ -333,21 +333,29 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   const int t = 16 * warp + (lane & 15);
   const bool own = lane < 16;
   if (ok) {
+    // Lanes 16-31 hold no accumulator rows: they take over columns 32..63 of the row of lane - 16, so all 32
+    // lanes share the mask arithmetic (branch-free, so the exponentials of different columns overlap).
     const float lt = s.Lam[t], gt = s.gam[t];
-    for (int c0 = 0; c0 < Q; c0 += 32) {
-      float f[32];
-      ld_acc32(taddr, warp, c0, f);
-      if (own) {
+    const int hx = lane >> 4;
+    float f[32];
+    {
+      float fa[32], fb[32];
+      ld_acc32(taddr, warp, 0, fa);
+      ld_acc32(taddr, warp, 32, fb);
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          const int sx = c0 + jj;
-          const float mv = __expf(fminf(lt - s.Lam[sx], 0.f)) * (sx < t ? s.e[sx] : gt);  // no branch
-          f[jj] = (sx <= t) ? f[jj] * mv : 0.f;
-        }
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Gm, tc::kmajor_unit(t, (c0 >> 3) + x, Q), pack8(&f[8 * x]));
+      for (int q = 0; q < 32; ++q) {
+        const float up = __shfl_sync(0xffffffffu, fb[q], lane & 15);
+        f[q] = hx ? up : fa[q];
       }
     }
+#pragma unroll
+    for (int jj = 0; jj < 32; ++jj) {
+      const int sx = 32 * hx + jj;
+      const float mv = __expf(fminf(lt - s.Lam[sx], 0.f)) * (sx < t ? s.e[sx] : gt);
+      f[jj] = (sx <= t) ? f[jj] * mv : 0.f;
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) sts16(Gm, tc::kmajor_unit(t, 4 * hx + x, Q), pack8(&f[8 * x]));
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
@@ -359,18 +367,17 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   }
   if (ok) ok = tc::mbar_wait(mbar, 1);
   tc::fence_after_sync();
-  if (ok) {
+  if (ok) {  // y = (G*M) X + exp(Lam) Crot H0, assembled over the x tile (dead) and written out in full rows
     const float de = s.dexp[t];
     for (int c0 = 0; c0 < P; c0 += 32) {
       float f[32], f2[32];
       ld_acc32(taddr, warp, c0, f);
       ld_acc32(taddr + 64, warp, c0, f2);
-      if (own && t0 + t < p.T) {
+      if (own) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) f[jj] = fmaf(de, f2[jj], f[jj]);
-        uint4* dst = reinterpret_cast<uint4*>(p.y + ((size_t)b * p.T + t0 + t) * p.D + d0 + c0);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) dst[x] = pack8(&f[8 * x]);
+        for (int x = 0; x < 4; ++x) sts16(Xt, tc::kmajor_unit(t, (c0 >> 3) + x, P), pack8(&f[8 * x]));
       }
     }
   } else if (tid == 0) {
@@ -378,6 +385,14 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   }
   tc::fence_before_sync();
   __syncthreads();
+  if (ok) {
+    for (int u = tid; u < Q * 8; u += 128) {  // 64-byte row pieces, conflict-free shared-memory reads
+      const int r = ((u >> 6) << 3) | (u & 7), c8 = (u >> 3) & 7;
+      if (t0 + r < p.T)
+        *reinterpret_cast<uint4*>(p.y + ((size_t)b * p.T + t0 + r) * p.D + d0 + c8 * 8) =
+            *reinterpret_cast<const uint4*>(Xt + 16 * u);
+    }
+  }
   if (warp == 0) tc::tmem_dealloc(taddr, 128);
 }
 
