@@ -43,7 +43,7 @@ struct SsdP {
   float *Hc;                    // [B,NH,n,N,P] fp32 chunk contributions (forward: Hc, backward: Dc)
   bf16 *H0, *dH1;               // [B,NH,n,N,P] state at chunk start / state gradient at chunk end
   float *dphi, *da, *de, *dgam; // [B,NH,T] per-token scalar gradients
-  float *pb, *pc;               // [B,NH,T,N] per-head partial dB, dC
+  bf16 *pb, *pc;                // [B,NH,T,N] per-head partial dB, dC (summed in fp32 by the reduce kernel)
 };
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : (x < -20.f ? expf(x) : log1pf(expf(x))); }
@@ -607,7 +607,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
       float gc[32];
       ld_acc32(taddr + 64, warp, c0, gc);
       if (own && t0 + t < p.T) {
-        float* pcr = p.pc + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
+        bf16* pcr = p.pc + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float cr[8], oc[8];
@@ -618,8 +618,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
             oc[k] = cs * c0v - sn * c1v; oc[k + 1] = sn * c0v + cs * c1v;
             dphi_own += cr[k + 1] * c0v - cr[k] * c1v;
           }
-          *reinterpret_cast<float4*>(pcr + 8 * x) = make_float4(oc[0], oc[1], oc[2], oc[3]);
-          *reinterpret_cast<float4*>(pcr + 8 * x + 4) = make_float4(oc[4], oc[5], oc[6], oc[7]);
+          *reinterpret_cast<uint4*>(pcr + 8 * x) = pack8(oc);
         }
       }
     }
@@ -640,7 +639,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
       float gb[32];
       ld_acc32(taddr + 0, warp, c0, gb);
       if (own && t0 + t < p.T) {
-        float* pbr = p.pb + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
+        bf16* pbr = p.pb + ((((size_t)b * p.NH + head) * p.T) + t0 + t) * N + c0;
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float br[8], ob[8];
@@ -651,8 +650,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
             ob[k] = cs * b0 - sn * b1; ob[k + 1] = sn * b0 + cs * b1;
             dphi_own += br[k + 1] * b0 - br[k] * b1;
           }
-          *reinterpret_cast<float4*>(pbr + 8 * x) = make_float4(ob[0], ob[1], ob[2], ob[3]);
-          *reinterpret_cast<float4*>(pbr + 8 * x + 4) = make_float4(ob[4], ob[5], ob[6], ob[7]);
+          *reinterpret_cast<uint4*>(pbr + 8 * x) = pack8(ob);
         }
       }
     }
@@ -730,19 +728,27 @@ __global__ void __launch_bounds__(256) m3s_final_kernel(SsdP p) {
   }
 }
 
-// dB[b,t,g,:] = sum over the heads of group g of the per-head partial rows (fixed order).
-__global__ void __launch_bounds__(128) m3s_reduce_kernel(const float* __restrict__ pb, const float* __restrict__ pc,
+// dB[b,t,g,:] = sum over the heads of group g of the per-head partial rows (fp32, fixed order).
+// One warp per (b, t, g): a lane owns 4 consecutive states.
+__global__ void __launch_bounds__(128) m3s_reduce_kernel(const bf16* __restrict__ pb, const bf16* __restrict__ pc,
                                                          bf16* __restrict__ db, bf16* __restrict__ dc, int T, int G, int NH) {
-  const int t = blockIdx.x, g = blockIdx.y, b = blockIdx.z, per = NH / G, n = threadIdx.x;
-  float sb = 0.f, sc = 0.f;
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), g = blockIdx.y, b = blockIdx.z, per = NH / G;
+  if (t >= T) return;
+  float sb[4] = {0.f, 0.f, 0.f, 0.f}, sc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int h = g * per; h < (g + 1) * per; ++h) {
-    const size_t pi = (((size_t)b * NH + h) * T + t) * N + n;
-    sb += pb[pi];
-    sc += pc[pi];
+    const size_t pi = (((size_t)b * NH + h) * T + t) * N + 4 * lane;
+    const uint2 vb = __ldg(reinterpret_cast<const uint2*>(pb + pi));
+    const uint2 vc = __ldg(reinterpret_cast<const uint2*>(pc + pi));
+    float a0, a1;
+    tc::unpack_bf16(vb.x, a0, a1); sb[0] += a0; sb[1] += a1;
+    tc::unpack_bf16(vb.y, a0, a1); sb[2] += a0; sb[3] += a1;
+    tc::unpack_bf16(vc.x, a0, a1); sc[0] += a0; sc[1] += a1;
+    tc::unpack_bf16(vc.y, a0, a1); sc[2] += a0; sc[3] += a1;
   }
-  const size_t gi = (((size_t)b * T + t) * G + g) * N + n;
-  db[gi] = __float2bfloat16_rn(sb);
-  dc[gi] = __float2bfloat16_rn(sc);
+  const size_t gi = (((size_t)b * T + t) * G + g) * N + 4 * lane;
+  *reinterpret_cast<uint2*>(db + gi) = make_uint2(tc::pack_bf16(sb[0], sb[1]), tc::pack_bf16(sb[2], sb[3]));
+  *reinterpret_cast<uint2*>(dc + gi) = make_uint2(tc::pack_bf16(sc[0], sc[1]), tc::pack_bf16(sc[2], sc[3]));
 }
 
 }  // namespace m3s
@@ -773,8 +779,8 @@ static size_t carve_ssd(SsdP& p, void* ws, bool bwd) {
     p.da = cv.take<float>(bh * p.T);
     p.de = cv.take<float>(bh * p.T);
     p.dgam = cv.take<float>(bh * p.T);
-    p.pb = cv.take<float>(bh * p.T * m3s::N);
-    p.pc = cv.take<float>(bh * p.T * m3s::N);
+    p.pb = cv.take<m3s::bf16>(bh * p.T * m3s::N);
+    p.pc = cv.take<m3s::bf16>(bh * p.T * m3s::N);
   }
   return cv.bytes();
 }
@@ -848,7 +854,7 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
   MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<<<gc, 256, m3s::kGradSmem, st>>>(p)));
   MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
   MXB_LAUNCH("m3s_reduce_kernel", st,
-             (m3s::m3s_reduce_kernel<<<dim3(p.T, p.G, p.B), m3s::N, 0, st>>>(p.pb, p.pc, static_cast<m3s::bf16*>(db),
+             (m3s::m3s_reduce_kernel<<<dim3((p.T + 3) / 4, p.G, p.B), 128, 0, st>>>(p.pb, p.pc, static_cast<m3s::bf16*>(db),
                                                                             static_cast<m3s::bf16*>(dc), p.T, p.G, p.NH)));
   return check_launch("mamba3 ssd backward");
 }
