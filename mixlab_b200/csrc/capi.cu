@@ -280,6 +280,7 @@ struct mxb_host_ctx {
   cudaStream_t stream2;          // kernels of the odd slices (small slices do not fill the GPU: let two overlap)
   cudaStream_t s_h2d, s_d2h;     // copy engines, one per direction
   cudaEvent_t h2d_done[2], comp_done[2], d2h_done[2];
+  cudaEvent_t do_done[2], fwd_done[2];  // dO uploaded / forward finished: the forward need not wait for dO, nor out for the backward
 };
 
 #define MXB_CUDA_TRY(expr)                          \
@@ -309,6 +310,8 @@ mxb_status mxb_host_ctx_create(int device, size_t arena_bytes, mxb_host_ctx** ou
     e = cudaEventCreateWithFlags(&c->h2d_done[i], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->comp_done[i], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->d2h_done[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->do_done[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->fwd_done[i], cudaEventDisableTiming);
   }
   if (e != cudaSuccess) {
     g_last_cuda_error = (int)e;
@@ -327,6 +330,8 @@ void mxb_host_ctx_destroy(mxb_host_ctx* c) {
     if (c->h2d_done[i]) cudaEventDestroy(c->h2d_done[i]);
     if (c->comp_done[i]) cudaEventDestroy(c->comp_done[i]);
     if (c->d2h_done[i]) cudaEventDestroy(c->d2h_done[i]);
+    if (c->do_done[i]) cudaEventDestroy(c->do_done[i]);
+    if (c->fwd_done[i]) cudaEventDestroy(c->fwd_done[i]);
   }
   if (c->stream) cudaStreamDestroy(c->stream);
   if (c->stream2) cudaStreamDestroy(c->stream2);
@@ -399,23 +404,29 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
     MXB_CUDA_TRY(cudaMemcpyAsync(i_v[sl], hp(v, ov_), cvb, H2D, c->s_h2d));
     MXB_CUDA_TRY(cudaMemcpyAsync(i_b[sl], hp(beta, os_), cs, H2D, c->s_h2d));
     MXB_CUDA_TRY(cudaMemcpyAsync(i_g[sl], hp(gate, os_), cs, H2D, c->s_h2d));
-    if (bwd) MXB_CUDA_TRY(cudaMemcpyAsync(i_do[sl], hp(d_out, ov_), cvb, H2D, c->s_h2d));
     MXB_CUDA_TRY(cudaEventRecord(c->h2d_done[sl], c->s_h2d));
+    if (bwd) {
+      MXB_CUDA_TRY(cudaMemcpyAsync(i_do[sl], hp(d_out, ov_), cvb, H2D, c->s_h2d));
+      MXB_CUDA_TRY(cudaEventRecord(c->do_done[sl], c->s_h2d));
+    }
     cudaStream_t kst = sl ? c->stream2 : c->stream;
     char* ws = wss[sl];
     MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->h2d_done[sl], 0));
     if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->d2h_done[sl], 0));  // slot outputs drained
     s = mxb_gdn_fwd(&df, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, o_out[sl], nullptr, ws, ws_bytes, kst);
     if (s != MXB_OK) return s;
+    MXB_CUDA_TRY(cudaEventRecord(c->fwd_done[sl], kst));
     if (bwd) {
+      MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->do_done[sl], 0));
       s = mxb_gdn_bwd(&db, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, i_do[sl], nullptr, o_q[sl], o_k[sl],
                       o_v[sl], o_b[sl], o_g[sl], nullptr, ws, ws_bytes, kst);
       if (s != MXB_OK) return s;
     }
     MXB_CUDA_TRY(cudaEventRecord(c->comp_done[sl], kst));
-    MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[sl], 0));
+    MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->fwd_done[sl], 0));
     MXB_CUDA_TRY(cudaMemcpyAsync(hpw(out, ov_), o_out[sl], cvb, D2H, c->s_d2h));
     if (bwd) {
+      MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[sl], 0));
       MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dq, ok_), o_q[sl], ck, D2H, c->s_d2h));
       MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dk, ok_), o_k[sl], ck, D2H, c->s_d2h));
       MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dv, ov_), o_v[sl], cvb, D2H, c->s_d2h));
