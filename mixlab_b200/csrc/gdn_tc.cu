@@ -318,8 +318,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
   uint8_t* Ut = A3 + 16384;         // [64 i][128 j]     u
   float* dd = reinterpret_cast<float*>(Ut + 16384);
   float* rr = dd + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);  // [0] MMA completion, [1] w, [2] u, [3] P images landed
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int kk = tid & 127, half = tid >> 7, j0 = 64 * half;
@@ -327,39 +327,42 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
   const uint32_t sA1 = tc::smem_u32(A1), sA2 = tc::smem_u32(A2), sA3 = tc::smem_u32(A3), sU = tc::smem_u32(Ut);
 
   auto grow = [&](int c, int i) { return ((size_t)(b * p.T + c * C + i) * p.H + h); };
+  // The workspace tiles (w, u, P) are byte images of the operand layout: one bulk copy each, issued by one
+  // thread, completing on an mbarrier.  The raw q and k rows come by cp.async.
   auto issue_A = [&](int c) {  // [w;q] of chunk c
     if (c < p.n) {
       const size_t ci = (size_t)bh * p.n + c;
       const int imax = min(C, p.T - c * C);
-      for (int u = tid; u < 128 * 16; u += 256) {
-        const int r = urow16(u), c8 = ucol16(u), i = r & 63;
-        if (r < 64) tc::cp_async16(sA1 + 16 * u, p.w + ci * C * KD + 8 * u);  // byte image of the operand tile
-        else tc::cp_async16(sA1 + tc::kmajor_unit(r, c8, KD), i < imax ? p.q + grow(c, i) * KD + c8 * 8 : p.q, i < imax);
+      if (tid == 0) {
+        tc::mbar_expect_tx(&mbar[1], 16384);
+        tc::bulk_load(sA1, p.w + ci * C * KD, 16384, &mbar[1]);
+      }
+      for (int u = tid; u < 64 * 16; u += 256) {
+        const int i = urow16(u), c8 = ucol16(u);
+        tc::cp_async16(sA1 + 16384 + 16 * u, i < imax ? p.q + grow(c, i) * KD + c8 * 8 : p.q, i < imax);
       }
     }
     tc::cp_async_commit();
   };
   auto issue_U = [&](int c) {
-    if (c < p.n) {
+    if (c < p.n && tid == 0) {
       const size_t ci = (size_t)bh * p.n + c;
-      for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = urow16(u), c8 = ucol16(u);
-        tc::cp_async16(sU + 16 * u, p.u + ci * C * KD + 8 * u);
-      }
+      tc::mbar_expect_tx(&mbar[2], 16384);
+      tc::bulk_load(sU, p.u + ci * C * KD, 16384, &mbar[2]);
     }
-    tc::cp_async_commit();
+    tc::cp_async_commit();  // (empty: keeps the group count of the schedule below)
   };
   auto issue_PK = [&](int c) {
     if (c < p.n) {
       const size_t ci = (size_t)bh * p.n + c;
       const int imax = min(C, p.T - c * C);
-      for (int u = tid; u < 64 * 8; u += 256) {
-        const int i = urow8(u), c8 = ucol8(u);
-        tc::cp_async16(sA2 + 8192 + 16 * u, p.P + ci * C * C + 8 * u);  // rows 64..127 of the [128][64] tile
+      if (tid == 0) {
+        tc::mbar_expect_tx(&mbar[3], 8192);
+        tc::bulk_load(sA2 + 8192, p.P + ci * C * C, 8192, &mbar[3]);  // rows 64..127 of the [128][64] tile
       }
       for (int u = tid; u < 64 * 16; u += 256) {
         const int i = urow16(u), c8 = ucol16(u);
-        tc::cp_async16(sA3 + tc::kmajor_unit(i, c8, KD), i < imax ? p.k + grow(c, i) * KD + c8 * 8 : p.k, i < imax);
+        tc::cp_async16(sA3 + 16 * u, i < imax ? p.k + grow(c, i) * KD + c8 * 8 : p.k, i < imax);
       }
     }
     tc::cp_async_commit();
@@ -370,9 +373,10 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
     tc::tmem_relinquish();
   }
   if (tid == 0) {
-    tc::mbar_init(mbar, 1);
+    for (int m = 0; m < 4; ++m) tc::mbar_init(&mbar[m], 1);
     tc::mbar_fence_init();
   }
+  __syncthreads();  // barriers initialised before the copies can complete on them
   issue_A(0);
   issue_U(0);
   issue_PK(0);
@@ -396,14 +400,20 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
   uint32_t ph = 0;
   bool ok = true;
 
+  // in-chunk cumulative log decay of the chunk ahead, fetched one chunk early (its latency would otherwise sit
+  // at the top of every link of the chain)
+  float g_nxt = p.gam[(size_t)bh * p.n * C + (tid & 63)], gl_nxt = p.gam[(size_t)bh * p.n * C + C - 1];
   for (int c = 0; c < p.n && ok; ++c) {
     const size_t ci = (size_t)bh * p.n + c;
     const int t0 = c * C, imax = min(C, p.T - t0);
-    const float* gam = p.gam + ci * C;
-    const float glast = gam[C - 1];
+    const uint32_t lph = c & 1;  // phase of the image barriers
+    const float glast = gl_nxt, g = g_nxt;
+    if (c + 1 < p.n) {
+      g_nxt = p.gam[(ci + 1) * C + (tid & 63)];
+      gl_nxt = p.gam[(ci + 1) * C + C - 1];
+    }
     const float L = exp_nonpos(glast);
     if (tid < C) {
-      const float g = gam[tid];
       dd[tid] = exp_nonpos(g);
       rr[tid] = exp_nonpos(glast - g);
     }
@@ -414,7 +424,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       sts16(Sop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's v_new image has left its tile
-    tc::cp_async_wait<2>();  // group A of this chunk has landed
+    tc::cp_async_wait<2>();  // group A of this chunk has landed (q rows; the w image on its barrier)
+    ok = tc::mbar_wait(&mbar[1], lph);
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
@@ -427,11 +438,11 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
         tc::bulk_commit();
       }
     }
-    ok = tc::mbar_wait(mbar, ph);
+    if (ok) ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
     issue_A(c + 1);
-    tc::cp_async_wait<2>();  // group U of this chunk
+    if (ok) ok = tc::mbar_wait(&mbar[2], lph);  // u image of this chunk
     __syncthreads();
     float qs[64];
     if (ok) {
@@ -464,6 +475,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the state image has left its tile
     tc::cp_async_wait<1>();  // group PK of this chunk (group A of the next one may still fly)
+    if (ok) ok = tc::mbar_wait(&mbar[3], lph);
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();

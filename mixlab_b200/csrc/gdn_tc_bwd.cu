@@ -41,8 +41,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
   uint8_t* Bdd = Aqw + 32768;       // [128: d dO rows, -dv_new rows][128 j]
   float* dd = reinterpret_cast<float*>(Bdd + 32768);
   float* rr = dd + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);  // [0] MMA completion, [1] P image, [2] w image landed
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kk = tid & 127, half = tid >> 7, j0 = 64 * half;
@@ -58,26 +58,24 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
         const int i = urow16(u), c8 = ucol16(u);
         const bool v = i < imax;
         const size_t g = v ? grow(c, i) * KD + c8 * 8 : 0;
-        tc::cp_async16(sAk + tc::kmajor_unit(i, c8, KD), p.k + g, v);
-        tc::cp_async16(sdO + tc::kmajor_unit(i, c8, KD), p.dO + g, v);
-        tc::cp_async16(sAqw + tc::kmajor_unit(i, c8, KD), p.q + g, v);
+        tc::cp_async16(sAk + 16 * u, p.k + g, v);
+        tc::cp_async16(sdO + 16 * u, p.dO + g, v);
+        tc::cp_async16(sAqw + 16 * u, p.q + g, v);
       }
-      for (int u = tid; u < 64 * 8; u += 256) {
-        const int i = urow8(u), c8 = ucol8(u);
-        tc::cp_async16(sPt + 16 * u, p.P + ci * C * C + 8 * u);  // byte image of the operand tile
+      if (tid == 0) {  // P is a byte image of its operand tile: one bulk copy, completing on its barrier
+        tc::mbar_expect_tx(&mbar[1], 8192);
+        tc::bulk_load(sPt, p.P + ci * C * C, 8192, &mbar[1]);
       }
     }
     tc::cp_async_commit();
   };
   auto issue_B = [&](int c) {
-    if (c >= 0) {
+    if (c >= 0 && tid == 0) {
       const size_t ci = (size_t)bh * p.n + c;
-      for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = urow16(u), c8 = ucol16(u);
-        tc::cp_async16(sAqw + 16384 + 16 * u, p.w + ci * C * KD + 8 * u);  // rows 64..127 of the [128][128] tile
-      }
+      tc::mbar_expect_tx(&mbar[2], 16384);
+      tc::bulk_load(sAqw + 16384, p.w + ci * C * KD, 16384, &mbar[2]);  // rows 64..127 of the [128][128] tile
     }
-    tc::cp_async_commit();
+    tc::cp_async_commit();  // (empty: keeps the group count of the schedule)
   };
 
   if (warp == 0) {
@@ -85,9 +83,10 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
     tc::tmem_relinquish();
   }
   if (tid == 0) {
-    tc::mbar_init(mbar, 1);
+    for (int m = 0; m < 3; ++m) tc::mbar_init(&mbar[m], 1);
     tc::mbar_fence_init();
   }
+  __syncthreads();  // barriers initialised before the copies can complete on them
   issue_A(p.n - 1);
   issue_B(p.n - 1);
   float dS[64];  // row kk of dS, columns j0 .. j0+63
@@ -109,13 +108,18 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
   uint32_t ph = 0;
   bool ok = true;
 
+  // in-chunk cumulative log decay of the chunk ahead, fetched one chunk early
+  float g_nxt = p.gam[((size_t)bh * p.n + p.n - 1) * C + (tid & 63)], gl_nxt = p.gam[((size_t)bh * p.n + p.n - 1) * C + C - 1];
   for (int c = p.n - 1; c >= 0 && ok; --c) {
     const size_t ci = (size_t)bh * p.n + c;
-    const float* gam = p.gam + ci * C;
-    const float glast = gam[C - 1];
+    const uint32_t lph = (p.n - 1 - c) & 1;  // phase of the image barriers
+    const float glast = gl_nxt, g = g_nxt;
+    if (c > 0) {
+      g_nxt = p.gam[(ci - 1) * C + (tid & 63)];
+      gl_nxt = p.gam[(ci - 1) * C + C - 1];
+    }
     const float L = exp_nonpos(glast);
     if (tid < C) {
-      const float g = gam[tid];
       dd[tid] = exp_nonpos(g);
       rr[tid] = exp_nonpos(glast - g);
     }
@@ -126,7 +130,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       sts16(dSop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's -dv_new image has left its tile
-    tc::cp_async_wait<1>();  // group A of this chunk
+    tc::cp_async_wait<1>();  // group A of this chunk (k, dO, q rows; the P image on its barrier)
+    ok = tc::mbar_wait(&mbar[1], lph);
     __syncthreads();         // dO tile and dd visible to every thread
     for (int u = tid; u < 64 * 16; u += 256) {  // d dO
       const int i = urow16(u), c8 = ucol16(u);
@@ -145,7 +150,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       tc::bulk_store(p.dhs + ci * KD * KD, tc::smem_u32(dSop), 32768);  // dS at chunk end, as the operand-tile image
       tc::bulk_commit();
     }
-    ok = tc::mbar_wait(mbar, ph);
+    if (ok) ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
     issue_A(c - 1);
@@ -171,7 +176,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       }
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the dS image has left its tile
-    tc::cp_async_wait<1>();  // group B (w) of this chunk
+    if (ok) ok = tc::mbar_wait(&mbar[2], lph);  // w image of this chunk
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
