@@ -43,6 +43,7 @@ struct SsdP {
   float *Hc;                    // [B,NH,n,N,P] fp32 chunk contributions (forward: Hc, backward: Dc)
   bf16 *H0, *dH1;               // [B,NH,n,N,P] state at chunk start / state gradient at chunk end
   float *dphi, *da, *de, *dgam; // [B,NH,T] per-token scalar gradients
+  float* cs;                    // [B,NH,n] ChunkScal records
   bf16 *pb, *pc;                // [B,NH,T,N] per-head partial dB, dC (summed in fp32 by the reduce kernel)
 };
 
@@ -74,21 +75,34 @@ __device__ __forceinline__ void ld_acc16(uint32_t taddr, int warp, int c0, float
   for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(r[i]);
 }
 
-// Per-chunk scalars in shared memory (128 threads; call by all, ends with a barrier).
+// Per-chunk scalars: computed once per (batch, head, chunk) by m3s_chunk_scalars_kernel into a workspace record
+// and fetched by every chunk kernel with its operand tiles (the record is a whole number of 16-byte units).
 struct ChunkScal {
-  float dt[Q], lam[Q], Lam[Q], gam[Q], e[Q], sn[Q], cs[Q], dexp[Q], r[Q];
-  float L, A;
+  float Lam[Q];   // in-chunk inclusive cumulative sum of dt A
+  float gam[Q];   // lambda dt
+  float e[Q];     // gam_s + (1 - lambda_{s+1}) dt_{s+1}
+  float sn[Q], cs[Q];  // sine / cosine of the cumulative rotation angle
+  float dexp[Q];  // exp(Lam)
+  float r[Q];     // exp(Lam_last - Lam)
+  float re[Q];    // r e
+  float L, A, pad[2];
 };
-__device__ __forceinline__ void load_chunk_scalars(const SsdP& p, int b, int head, int c, ChunkScal& s) {
-  const int tid = threadIdx.x, t0 = c * Q;
+static_assert(sizeof(ChunkScal) % 16 == 0, "record moves in 16-byte units");
+constexpr int kScalUnits = sizeof(ChunkScal) / 16;
+
+__global__ void __launch_bounds__(64) m3s_chunk_scalars_kernel(SsdP p) {
+  __shared__ __align__(16) ChunkScal s;
+  __shared__ float sdt[Q];
+  const int tid = threadIdx.x, c = blockIdx.x, head = blockIdx.y, b = blockIdx.z, t0 = c * Q;
   const size_t base = ((size_t)b * p.NH + head) * p.T;
-  if (tid == 0) s.A = -expf(p.a_log[head]);
-  if (tid < Q) {
+  const size_t ci = ((size_t)b * p.NH + head) * p.n + c;
+  const float A = -expf(p.a_log[head]);
+  {
     const int t = t0 + tid;
     const bool ok = t < p.T;
     const float dt = ok ? p.dt[base + t] : 0.f, lam = ok ? p.lam[base + t] : 0.f;
     const float nxt = (t + 1 < p.T) ? (1.f - p.lam[base + t + 1]) * p.dt[base + t + 1] : 0.f;
-    s.dt[tid] = dt; s.lam[tid] = lam;
+    sdt[tid] = dt;
     s.gam[tid] = lam * dt;
     s.e[tid] = lam * dt + nxt;
     float sn = 0.f, cs = 1.f;
@@ -97,7 +111,7 @@ __device__ __forceinline__ void load_chunk_scalars(const SsdP& p, int b, int hea
   }
   __syncthreads();
   if (tid < 32) {  // inclusive in-chunk cumulative sum of a = dt A, two per lane
-    const float a0 = s.dt[2 * tid] * s.A, a1 = s.dt[2 * tid + 1] * s.A;
+    const float a0 = sdt[2 * tid] * A, a1 = sdt[2 * tid + 1] * A;
     float v = a0 + a1;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -108,13 +122,23 @@ __device__ __forceinline__ void load_chunk_scalars(const SsdP& p, int b, int hea
     s.Lam[2 * tid + 1] = v;
   }
   __syncthreads();
-  if (tid < Q) {
+  {
     const float last = s.Lam[Q - 1];
+    const float r = __expf(last - s.Lam[tid]);
     s.dexp[tid] = __expf(s.Lam[tid]);
-    s.r[tid] = __expf(last - s.Lam[tid]);
-    if (tid == 0) s.L = __expf(last);
+    s.r[tid] = r;
+    s.re[tid] = r * s.e[tid];
+    if (tid == 0) { s.L = __expf(last); s.A = A; s.pad[0] = s.pad[1] = 0.f; p.Lc[ci] = s.L; }
   }
   __syncthreads();
+  uint4* dst = reinterpret_cast<uint4*>(p.cs + ci * (sizeof(ChunkScal) / 4));
+  for (int u = tid; u < kScalUnits; u += 64) dst[u] = reinterpret_cast<const uint4*>(&s)[u];
+}
+// cp.async of the record of chunk ci into shared memory (part of the caller's current cp.async group)
+__device__ __forceinline__ void issue_chunk_scalars(const SsdP& p, size_t ci, ChunkScal& s) {
+  const uint32_t sd = tc::smem_u32(&s);
+  const float* src = p.cs + ci * (sizeof(ChunkScal) / 4);
+  for (int u = threadIdx.x; u < kScalUnits; u += blockDim.x) tc::cp_async16(sd + 16 * u, src + 4 * u);
 }
 
 // ---- asynchronous staging: raw cp.async copies into the blocked layout, then in-place fix-ups ----
@@ -222,16 +246,12 @@ __global__ void __launch_bounds__(128) m3s_chunk_outer_kernel(SsdP p, int mode) 
   if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
   issue_rows_tile(Rt, mode == 0 ? p.b : p.c, p, b, g, t0);
   issue_x_tile(Xt, mode == 0 ? p.x : p.dy, p, b, d0, t0);
+  issue_chunk_scalars(p, ci, s);
   tc::cp_async_commit();
-  load_chunk_scalars(p, b, head, c, s);
-  if (mode == 0) {
-    if (tid < Q) s.gam[tid] = s.r[tid] * s.e[tid];  // row scale of x (gam is not needed here)
-    if (tid == 0) p.Lc[ci] = s.L;
-  }
   tc::cp_async_wait<0>();
   __syncthreads();
   rotate_tile(Rt, s.sn, s.cs);
-  scale_x_tile(Xt, Xt, mode == 0 ? s.gam : s.dexp);
+  scale_x_tile(Xt, Xt, mode == 0 ? s.re : s.dexp);
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
@@ -312,8 +332,8 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   issue_rows_tile(Ct, p.c, p, b, g, t0);
   issue_x_tile(Xt, p.x, p, b, d0, t0);
   issue_state_tile(Ht, p.H0 + ci * (N * P));
+  issue_chunk_scalars(p, ci, s);
   tc::cp_async_commit();
-  load_chunk_scalars(p, b, head, c, s);
   tc::cp_async_wait<0>();
   __syncthreads();
   rotate_tile(Bt, s.sn, s.cs);
@@ -451,19 +471,17 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   issue_rows_tile(Ct, p.c, p, b, g, t0);
   issue_x_tile(Xt, p.x, p, b, d0, t0);
   issue_x_tile(Yt, p.dy, p, b, d0, t0);
+  issue_chunk_scalars(p, ci, s);
   tc::cp_async_commit();
   issue_state_tile(Ht, p.H0 + ci * (N * P));
   issue_state_tile(Dt, p.dH1 + ci * (N * P));
   tc::cp_async_commit();
-  load_chunk_scalars(p, b, head, c, s);
   for (int u = tid; u < 8 * Q; u += 256) { csw_e[u] = 0.f; }  // csw_e and csw_l are contiguous
-  float* re = part;  // [Q] row scale r e of x (part itself is written only at the end)
-  if (tid < Q) re[tid] = s.r[tid] * s.e[tid];
   tc::cp_async_wait<1>();
   __syncthreads();
   rotate_tile(Bt, s.sn, s.cs);
   rotate_tile(Ct, s.sn, s.cs);
-  scale_x_tile(Xs, Xt, re);
+  scale_x_tile(Xs, Xt, s.re);
   scale_x_tile(Ys, Yt, s.dexp);
   tc::cp_async_wait<0>();
   tc::fence_async_smem();
@@ -771,6 +789,7 @@ static size_t carve_ssd(SsdP& p, void* ws, bool bwd) {
   p.lam = cv.take<float>(bh * p.T);
   p.phi = cv.take<float>(bh * p.T);
   p.Lc = cv.take<float>(bh * p.n);
+  p.cs = cv.take<float>(bh * p.n * (sizeof(m3s::ChunkScal) / 4));
   p.Hc = cv.take<float>(nst);
   p.H0 = cv.take<m3s::bf16>(nst);
   if (bwd) {
@@ -808,6 +827,7 @@ static mxb_status ssd_forward(SsdP& p, cudaStream_t st) {
   const dim3 gc(p.n, p.NH, p.B);
   if (cudaMemsetAsync(p.status, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
   MXB_LAUNCH("m3s_scalars_kernel", st, (m3s::m3s_scalars_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
+  MXB_LAUNCH("m3s_chunk_scalars_kernel", st, (m3s::m3s_chunk_scalars_kernel<<<gc, 64, 0, st>>>(p)));
   if (ssd_smem(m3s::m3s_chunk_outer_kernel, m3s::kOuterSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("m3s_chunk_outer_kernel", st, (m3s::m3s_chunk_outer_kernel<<<gc, 128, m3s::kOuterSmem, st>>>(p, 0)));
   MXB_LAUNCH("m3s_scan_kernel", st, (m3s::m3s_scan_kernel<<<p.B * p.NH, 256, 0, st>>>(p, 0)));
