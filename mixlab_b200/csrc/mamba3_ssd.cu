@@ -14,8 +14,9 @@
 // before it was written); its sequential part is the mirrored scan dH0 = L dH1 + Dc.
 //
 //   m3s_scalars_kernel      per (b, head): dt, lambda, wrapped cumulative angle (fp64 prefix sum)
-//   m3s_chunk_outer_kernel  per chunk: Hc = Brot^T diag(r e) X   or   Dc = Crot^T diag(exp(Lam)) dY
-//   m3s_scan_kernel         per (b, head): elementwise scan over the chunks, forward or reverse
+//   m3s_chunk_scalars_kernel per chunk: decay sums, trapezoid weights, rotation sines/cosines (one record)
+//   m3s_state_pass_kernel   per (b, head), sequential over the chunks, forward or reverse: the chunk contribution
+//                           Brot^T diag(r e) X (or Crot^T diag(exp(Lam)) dY) folded into the running state
 //   m3s_chunk_out_kernel    per chunk: Y
 //   m3s_chunk_grad_kernel   per chunk: dx, rotated-row gradients -> dB, dC partials, per-token scalars
 //   m3s_final_kernel        per (b, head): suffix sum of the angle gradient, ddt, dlambda, dtheta, da_log
@@ -39,8 +40,6 @@ struct SsdP {
   int* status;
   // workspace
   float *dt, *lam, *phi;        // [B,NH,T]
-  float *Lc;                    // [B,NH,n]  exp(Lam_end) per chunk
-  float *Hc;                    // [B,NH,n,N,P] fp32 chunk contributions (forward: Hc, backward: Dc)
   bf16 *H0, *dH1;               // [B,NH,n,N,P] state at chunk start / state gradient at chunk end
   float *dphi, *da, *de, *dgam; // [B,NH,T] per-token scalar gradients
   float* cs;                    // [B,NH,n] ChunkScal records
@@ -128,7 +127,7 @@ __global__ void __launch_bounds__(64) m3s_chunk_scalars_kernel(SsdP p) {
     s.dexp[tid] = __expf(s.Lam[tid]);
     s.r[tid] = r;
     s.re[tid] = r * s.e[tid];
-    if (tid == 0) { s.L = __expf(last); s.A = A; s.pad[0] = s.pad[1] = 0.f; p.Lc[ci] = s.L; }
+    if (tid == 0) { s.L = __expf(last); s.A = A; s.pad[0] = s.pad[1] = 0.f; }
   }
   __syncthreads();
   uint4* dst = reinterpret_cast<uint4*>(p.cs + ci * (sizeof(ChunkScal) / 4));
@@ -161,13 +160,10 @@ __device__ __forceinline__ void issue_x_tile(uint8_t* dst, const bf16* src, cons
     tc::cp_async16(sd + 16 * u, ok ? src + ((size_t)b * p.T + t0 + t) * p.D + d0 + c8 * 8 : src, ok);
   }
 }
-// [128 n][64 p] bf16 workspace matrix (row-major) -> blocked tile
+// [128 n][64 p] bf16 state saved by the state pass as the byte image of the blocked tile
 __device__ __forceinline__ void issue_state_tile(uint8_t* dst, const bf16* src) {
   const uint32_t sd = tc::smem_u32(dst);
-  for (int u = threadIdx.x; u < N * 8; u += blockDim.x) {
-    const int r = ((u >> 6) << 3) | (u & 7), c8 = (u >> 3) & 7;
-    tc::cp_async16(sd + 16 * u, src + r * P + c8 * 8);
-  }
+  for (int u = threadIdx.x; u < N * 8; u += blockDim.x) tc::cp_async16(sd + 16 * u, src + 8 * u);
 }
 // Rotates the (even, odd) pairs of every row of a landed [64][128] tile in place.
 __device__ __forceinline__ void rotate_tile(uint8_t* tile, const float* sn, const float* cs) {
@@ -224,88 +220,96 @@ __global__ void __launch_bounds__(256) m3s_scalars_kernel(SsdP p) {
   }
 }
 
-// ------------------------------------------------------------ chunk outer products
-// mode 0: Hc = Brot^T diag(r e) X        mode 1: Dc = Crot^T diag(exp(Lam)) dY
-constexpr int kOuterSmem = 16384 + 8192 + sizeof(ChunkScal) + 64 + 256;
+// ------------------------------------------------------------ state pass
+// One CTA per (batch, head) walks the chunks in order (mode 0) or in reverse (mode 1) and keeps the running
+// state in registers (thread = state row n, 64 fp32 columns):
+//   mode 0: H0_c = H;  H = L_c H + Brot_c^T diag(r e) X_c          (states at chunk start, for y and the backward)
+//   mode 1: dH1_c = dH; dH = L_c dH + Crot_c^T diag(exp(Lam)) dY_c  (state gradients at chunk end)
+// The chunk contribution is one M=128 tcgen05 tile that never leaves the SM; the operands of the next two
+// chunks are in flight (cp.async, two buffers) while the current one is rotated, multiplied and folded in.
+// The saved state leaves as the byte image of the [128][64] operand tile (one bulk copy per chunk).
+constexpr int kPassBuf = 16384 + 8192 + sizeof(ChunkScal);
+constexpr int kPassSmem = 2 * kPassBuf + 16384 + 64 + 256;
 
-__global__ void __launch_bounds__(128) m3s_chunk_outer_kernel(SsdP p, int mode) {
+__global__ void __launch_bounds__(128) m3s_state_pass_kernel(SsdP p, int mode) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
-  uint8_t* Rt = sm;                // [64 s][128 n] rotated B or C
-  uint8_t* Xt = Rt + 16384;        // [64 s][64 p]  scaled x or dy
-  ChunkScal& s = *reinterpret_cast<ChunkScal*>(Xt + 8192);
-  float* sc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(&s) + sizeof(ChunkScal));  // [64] row scale... reuse below
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(sc);
+  uint8_t* Himg = sm + 2 * kPassBuf;  // [128 n][64 p] bf16 image of the state on its way out
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(Himg + 16384);
   uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int c = blockIdx.x, head = blockIdx.y, b = blockIdx.z, t0 = c * Q;
+  const int head = blockIdx.x, b = blockIdx.y;
   const int d0 = head * P, g = d0 / (p.D / p.G);
-  const size_t ci = ((size_t)b * p.NH + head) * p.n + c;
-
+  const size_t cbase = ((size_t)b * p.NH + head) * p.n;
+  auto Rt = [&](int buf) { return sm + buf * kPassBuf; };             // [64 s][128 n] B or C rows, rotated in place
+  auto Xt = [&](int buf) { return sm + buf * kPassBuf + 16384; };     // [64 s][64 p]  x or dy, scaled in place
+  auto Sc = [&](int buf) -> ChunkScal& { return *reinterpret_cast<ChunkScal*>(sm + buf * kPassBuf + 24576); };
+  auto chunk_at = [&](int it) { return mode == 0 ? it : p.n - 1 - it; };
+  auto issue = [&](int it) {
+    if (it < p.n) {
+      const int c = chunk_at(it), buf = it & 1;
+      issue_rows_tile(Rt(buf), mode == 0 ? p.b : p.c, p, b, g, c * Q);
+      issue_x_tile(Xt(buf), mode == 0 ? p.x : p.dy, p, b, d0, c * Q);
+      issue_chunk_scalars(p, cbase + c, Sc(buf));
+    }
+    tc::cp_async_commit();
+  };
   if (warp == 0) { tc::tmem_alloc(tslot, 64); tc::tmem_relinquish(); }
   if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
-  issue_rows_tile(Rt, mode == 0 ? p.b : p.c, p, b, g, t0);
-  issue_x_tile(Xt, mode == 0 ? p.x : p.dy, p, b, d0, t0);
-  issue_chunk_scalars(p, ci, s);
-  tc::cp_async_commit();
-  tc::cp_async_wait<0>();
-  __syncthreads();
-  rotate_tile(Rt, s.sn, s.cs);
-  scale_x_tile(Xt, Xt, mode == 0 ? s.re : s.dexp);
-  tc::fence_async_smem();
+  issue(0);
+  issue(1);
+  float H[P];
+#pragma unroll
+  for (int x = 0; x < P; ++x) H[x] = 0.f;
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t taddr = *tslot;
-  if (tid == 0) {  // [128 n x 64 p] = R^T X, both contracted over their rows
-    tc::issue_gemm(taddr, tc::mnmajor_tile(Rt, N), tc::mnmajor_tile(Xt, P), 128, P, Q, false);
-    tc::mma_commit(mbar);
-  }
-  const bool ok = tc::mbar_wait(mbar, 0);
-  tc::fence_after_sync();
-  if (ok) {
-    float* dst = p.Hc + (ci * N + tid) * P;
-    for (int c0 = 0; c0 < P; c0 += 32) {
-      float f[32];
-      ld_acc32(taddr, warp, c0, f);
+  bf16* out = mode == 0 ? p.H0 : p.dH1;
+  uint32_t ph = 0;
+  bool ok = true;
+  for (int it = 0; it < p.n && ok; ++it) {
+    const int c = chunk_at(it), buf = it & 1;
+    ChunkScal& s = Sc(buf);
+    if (tid == 0) tc::bulk_wait_read<0>();  // the previous state image has left its tile
+    tc::cp_async_wait<1>();                 // operands of this chunk have landed
+    __syncthreads();
+    const float L = s.L;
+    rotate_tile(Rt(buf), s.sn, s.cs);
+    scale_x_tile(Xt(buf), Xt(buf), mode == 0 ? s.re : s.dexp);
 #pragma unroll
-      for (int x = 0; x < 8; ++x)
-        *reinterpret_cast<float4*>(dst + c0 + 4 * x) = make_float4(f[4 * x], f[4 * x + 1], f[4 * x + 2], f[4 * x + 3]);
+    for (int c8 = 0; c8 < 8; ++c8) sts16(Himg, tc::kmajor_unit(tid, c8, P), pack8(&H[8 * c8]));
+    tc::fence_async_smem();
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    if (tid == 0) {  // [128 n x 64 p] = R^T X, both contracted over their rows
+      tc::issue_gemm(taddr, tc::mnmajor_tile(Rt(buf), N), tc::mnmajor_tile(Xt(buf), P), 128, P, Q, false);
+      tc::mma_commit(mbar);
+      tc::bulk_store(out + (cbase + c) * (N * P), tc::smem_u32(Himg), 16384);
+      tc::bulk_commit();
     }
-  } else if (tid == 0) {
-    atomicExch(p.status, 11);
+    ok = tc::mbar_wait(mbar, ph);
+    ph ^= 1;
+    tc::fence_after_sync();
+    issue(it + 2);  // this buffer is free: the MMA has read the tiles, every thread has read L
+    if (ok) {
+      for (int c0 = 0; c0 < P; c0 += 32) {
+        float f[32];
+        ld_acc32(taddr, warp, c0, f);
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) H[c0 + jj] = fmaf(L, H[c0 + jj], f[jj]);
+      }
+    }
+    tc::fence_before_sync();
   }
+  tc::cp_async_wait<0>();
+  if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
+  if (!ok && tid == 0) atomicExch(p.status, 11);
   tc::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc::tmem_dealloc(taddr, 64);
 }
-
-// ------------------------------------------------------------ elementwise chunk scan
-// forward (rev = 0): H0_c = H; H = L_c H + Hc_c          reverse (rev = 1): dH1_c = dH; dH = L_c dH + Dc_c
-__global__ void __launch_bounds__(256) m3s_scan_kernel(SsdP p, int rev) {
-  const int bh = blockIdx.x, tid = threadIdx.x;
-  const size_t cbase = (size_t)bh * p.n;
-  bf16* out = rev ? p.dH1 : p.H0;
-  float h[32];  // elements tid*4 + 1024*k .. (float4 granules, coalesced)
-#pragma unroll
-  for (int k = 0; k < 32; ++k) h[k] = 0.f;
-  for (int i = 0; i < p.n; ++i) {
-    const int c = rev ? p.n - 1 - i : i;
-    const float L = p.Lc[cbase + c];
-    const float* src = p.Hc + (cbase + c) * (N * P);
-    bf16* dst = out + (cbase + c) * (N * P);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const int off = (k * 256 + tid) * 4;
-      const float4 v = __ldg(reinterpret_cast<const float4*>(src + off));
-      *reinterpret_cast<uint2*>(dst + off) =
-          make_uint2(tc::pack_bf16(h[4 * k], h[4 * k + 1]), tc::pack_bf16(h[4 * k + 2], h[4 * k + 3]));
-      h[4 * k] = fmaf(L, h[4 * k], v.x); h[4 * k + 1] = fmaf(L, h[4 * k + 1], v.y);
-      h[4 * k + 2] = fmaf(L, h[4 * k + 2], v.z); h[4 * k + 3] = fmaf(L, h[4 * k + 3], v.w);
-    }
-  }
-}
-
 
 // ------------------------------------------------------------ chunk output
 constexpr int kOutSmem = 16384 * 3 + 8192 * 2 + sizeof(ChunkScal) + 64 + 256;
@@ -788,9 +792,7 @@ static size_t carve_ssd(SsdP& p, void* ws, bool bwd) {
   p.dt = cv.take<float>(bh * p.T);
   p.lam = cv.take<float>(bh * p.T);
   p.phi = cv.take<float>(bh * p.T);
-  p.Lc = cv.take<float>(bh * p.n);
   p.cs = cv.take<float>(bh * p.n * (sizeof(m3s::ChunkScal) / 4));
-  p.Hc = cv.take<float>(nst);
   p.H0 = cv.take<m3s::bf16>(nst);
   if (bwd) {
     p.dH1 = cv.take<m3s::bf16>(nst);
@@ -828,9 +830,9 @@ static mxb_status ssd_forward(SsdP& p, cudaStream_t st) {
   if (cudaMemsetAsync(p.status, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
   MXB_LAUNCH("m3s_scalars_kernel", st, (m3s::m3s_scalars_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
   MXB_LAUNCH("m3s_chunk_scalars_kernel", st, (m3s::m3s_chunk_scalars_kernel<<<gc, 64, 0, st>>>(p)));
-  if (ssd_smem(m3s::m3s_chunk_outer_kernel, m3s::kOuterSmem) != MXB_OK) return MXB_ERR_CUDA;
-  MXB_LAUNCH("m3s_chunk_outer_kernel", st, (m3s::m3s_chunk_outer_kernel<<<gc, 128, m3s::kOuterSmem, st>>>(p, 0)));
-  MXB_LAUNCH("m3s_scan_kernel", st, (m3s::m3s_scan_kernel<<<p.B * p.NH, 256, 0, st>>>(p, 0)));
+  if (ssd_smem(m3s::m3s_state_pass_kernel, m3s::kPassSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("m3s_state_pass_kernel", st,
+             (m3s::m3s_state_pass_kernel<<<dim3(p.NH, p.B), 128, m3s::kPassSmem, st>>>(p, 0)));
   if (p.y) {
     if (ssd_smem(m3s::m3s_chunk_out_kernel, m3s::kOutSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("m3s_chunk_out_kernel", st, (m3s::m3s_chunk_out_kernel<<<gc, 128, m3s::kOutSmem, st>>>(p)));
@@ -861,15 +863,15 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
   p.y = nullptr;  // the forward recompute stops at the chunk states
   if (d->flags & MXB_MAMBA3_BWD_USE_SAVED) {  // dt, lambda, phi, the chunk decays and H0 are still in place
     if (cudaMemsetAsync(p.status, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
-    if (ssd_smem(m3s::m3s_chunk_outer_kernel, m3s::kOuterSmem) != MXB_OK) return MXB_ERR_CUDA;
+    if (ssd_smem(m3s::m3s_state_pass_kernel, m3s::kPassSmem) != MXB_OK) return MXB_ERR_CUDA;
   } else {
     mxb_status s = ssd_forward(p, st);
     if (s != MXB_OK) return s;
   }
   if (cudaMemsetAsync(da_log, 0, (size_t)p.NH * sizeof(float), st) != cudaSuccess) return MXB_ERR_CUDA;
   const dim3 gc(p.n, p.NH, p.B);
-  MXB_LAUNCH("m3s_chunk_outer_kernel", st, (m3s::m3s_chunk_outer_kernel<<<gc, 128, m3s::kOuterSmem, st>>>(p, 1)));
-  MXB_LAUNCH("m3s_scan_kernel", st, (m3s::m3s_scan_kernel<<<p.B * p.NH, 256, 0, st>>>(p, 1)));
+  MXB_LAUNCH("m3s_state_pass_kernel", st,
+             (m3s::m3s_state_pass_kernel<<<dim3(p.NH, p.B), 128, m3s::kPassSmem, st>>>(p, 1)));
   if (ssd_smem(m3s::m3s_chunk_grad_kernel, m3s::kGradSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<<<gc, 256, m3s::kGradSmem, st>>>(p)));
   MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
