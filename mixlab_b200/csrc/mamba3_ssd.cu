@@ -222,22 +222,23 @@ __global__ void __launch_bounds__(256) m3s_scalars_kernel(SsdP p) {
 
 // ------------------------------------------------------------ state pass
 // One CTA per (batch, head) walks the chunks in order (mode 0) or in reverse (mode 1) and keeps the running
-// state in registers (thread = state row n, 64 fp32 columns):
+// state in registers (thread = state row n and 32 of its 64 fp32 columns):
 //   mode 0: H0_c = H;  H = L_c H + Brot_c^T diag(r e) X_c          (states at chunk start, for y and the backward)
 //   mode 1: dH1_c = dH; dH = L_c dH + Crot_c^T diag(exp(Lam)) dY_c  (state gradients at chunk end)
 // The chunk contribution is one M=128 tcgen05 tile that never leaves the SM; the operands of the next two
 // chunks are in flight (cp.async, two buffers) while the current one is rotated, multiplied and folded in.
 // The saved state leaves as the byte image of the [128][64] operand tile (one bulk copy per chunk).
 constexpr int kPassBuf = 16384 + 8192 + sizeof(ChunkScal);
-constexpr int kPassSmem = 2 * kPassBuf + 16384 + 64 + 256;
+constexpr int kPassSmem = 2 * kPassBuf + 2 * 16384 + 64 + 256;
 
-__global__ void __launch_bounds__(128) m3s_state_pass_kernel(SsdP p, int mode) {
+__global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
-  uint8_t* Himg = sm + 2 * kPassBuf;  // [128 n][64 p] bf16 image of the state on its way out
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(Himg + 16384);
+  uint8_t* Himg = sm + 2 * kPassBuf;  // 2 x [128 n][64 p] bf16 images of the state on their way out
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(Himg + 2 * 16384);
   uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int nrow = tid & 127, half = tid >> 7;  // thread = state row n, 32 of its 64 columns
   const int head = blockIdx.x, b = blockIdx.y;
   const int d0 = head * P, g = d0 / (p.D / p.G);
   const size_t cbase = ((size_t)b * p.NH + head) * p.n;
@@ -258,9 +259,10 @@ __global__ void __launch_bounds__(128) m3s_state_pass_kernel(SsdP p, int mode) {
   if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
   issue(0);
   issue(1);
-  float H[P];
+  float H[32];
 #pragma unroll
-  for (int x = 0; x < P; ++x) H[x] = 0.f;
+  for (int x = 0; x < 32; ++x) H[x] = 0.f;
+  tc::cp_async_wait<1>();  // operands of the first chunk
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -268,38 +270,40 @@ __global__ void __launch_bounds__(128) m3s_state_pass_kernel(SsdP p, int mode) {
   bf16* out = mode == 0 ? p.H0 : p.dH1;
   uint32_t ph = 0;
   bool ok = true;
+  rotate_tile(Rt(0), Sc(0).sn, Sc(0).cs);
+  scale_x_tile(Xt(0), Xt(0), mode == 0 ? Sc(0).re : Sc(0).dexp);
   for (int it = 0; it < p.n && ok; ++it) {
     const int c = chunk_at(it), buf = it & 1;
-    ChunkScal& s = Sc(buf);
-    if (tid == 0) tc::bulk_wait_read<0>();  // the previous state image has left its tile
-    tc::cp_async_wait<1>();                 // operands of this chunk have landed
-    __syncthreads();
-    const float L = s.L;
-    rotate_tile(Rt(buf), s.sn, s.cs);
-    scale_x_tile(Xt(buf), Xt(buf), mode == 0 ? s.re : s.dexp);
+    const float L = Sc(buf).L;
+    uint8_t* Hi = Himg + buf * 16384;  // the image written two chunks ago has left this tile (checked below)
 #pragma unroll
-    for (int c8 = 0; c8 < 8; ++c8) sts16(Himg, tc::kmajor_unit(tid, c8, P), pack8(&H[8 * c8]));
+    for (int x = 0; x < 4; ++x) sts16(Hi, tc::kmajor_unit(nrow, 4 * half + x, P), pack8(&H[8 * x]));
     tc::fence_async_smem();
     tc::fence_before_sync();
-    __syncthreads();
+    __syncthreads();  // tiles of this chunk rotated and scaled (during the previous chunk's MMA), image staged
     tc::fence_after_sync();
     if (tid == 0) {  // [128 n x 64 p] = R^T X, both contracted over their rows
       tc::issue_gemm(taddr, tc::mnmajor_tile(Rt(buf), N), tc::mnmajor_tile(Xt(buf), P), 128, P, Q, false);
       tc::mma_commit(mbar);
-      tc::bulk_store(out + (cbase + c) * (N * P), tc::smem_u32(Himg), 16384);
+      tc::bulk_store(out + (cbase + c) * (N * P), tc::smem_u32(Hi), 16384);
       tc::bulk_commit();
+      tc::bulk_wait_read<1>();  // all but the copy just issued have been read out of shared memory
+    }
+    if (it + 1 < p.n) {  // while the tensor core works: the next chunk's tiles
+      tc::cp_async_wait<0>();
+      __syncthreads();
+      rotate_tile(Rt(buf ^ 1), Sc(buf ^ 1).sn, Sc(buf ^ 1).cs);
+      scale_x_tile(Xt(buf ^ 1), Xt(buf ^ 1), mode == 0 ? Sc(buf ^ 1).re : Sc(buf ^ 1).dexp);
     }
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
     issue(it + 2);  // this buffer is free: the MMA has read the tiles, every thread has read L
     if (ok) {
-      for (int c0 = 0; c0 < P; c0 += 32) {
-        float f[32];
-        ld_acc32(taddr, warp, c0, f);
+      float f[32];
+      ld_acc32(taddr, warp, 32 * half, f);
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) H[c0 + jj] = fmaf(L, H[c0 + jj], f[jj]);
-      }
+      for (int jj = 0; jj < 32; ++jj) H[jj] = fmaf(L, H[jj], f[jj]);
     }
     tc::fence_before_sync();
   }
@@ -832,7 +836,7 @@ static mxb_status ssd_forward(SsdP& p, cudaStream_t st) {
   MXB_LAUNCH("m3s_chunk_scalars_kernel", st, (m3s::m3s_chunk_scalars_kernel<<<gc, 64, 0, st>>>(p)));
   if (ssd_smem(m3s::m3s_state_pass_kernel, m3s::kPassSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("m3s_state_pass_kernel", st,
-             (m3s::m3s_state_pass_kernel<<<dim3(p.NH, p.B), 128, m3s::kPassSmem, st>>>(p, 0)));
+             (m3s::m3s_state_pass_kernel<<<dim3(p.NH, p.B), 256, m3s::kPassSmem, st>>>(p, 0)));
   if (p.y) {
     if (ssd_smem(m3s::m3s_chunk_out_kernel, m3s::kOutSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("m3s_chunk_out_kernel", st, (m3s::m3s_chunk_out_kernel<<<gc, 128, m3s::kOutSmem, st>>>(p)));
@@ -871,7 +875,7 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
   if (cudaMemsetAsync(da_log, 0, (size_t)p.NH * sizeof(float), st) != cudaSuccess) return MXB_ERR_CUDA;
   const dim3 gc(p.n, p.NH, p.B);
   MXB_LAUNCH("m3s_state_pass_kernel", st,
-             (m3s::m3s_state_pass_kernel<<<dim3(p.NH, p.B), 128, m3s::kPassSmem, st>>>(p, 1)));
+             (m3s::m3s_state_pass_kernel<<<dim3(p.NH, p.B), 256, m3s::kPassSmem, st>>>(p, 1)));
   if (ssd_smem(m3s::m3s_chunk_grad_kernel, m3s::kGradSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<<<gc, 256, m3s::kGradSmem, st>>>(p)));
   MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
