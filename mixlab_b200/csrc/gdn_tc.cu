@@ -606,16 +606,20 @@ static EncodeTiledFn encode_tiled_fn() {
   }();
   return fn;
 }
-// [B,T,H,128] bf16 as a 4-d tensor (D, H, T, B) with boxes of 64 columns x 64 time steps, 128-byte swizzle.
-static bool make_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H) {
+// [B,T,H,D] bf16 as a 4-d tensor (D, H, T, B) with boxes of 64 columns x 64 time steps, 128-byte swizzle
+// (D a multiple of 64; rows past T are zero-filled by the copy engine).  Shared with the Mamba-3 kernels.
+bool make_tma_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, int D) {
   EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15)) return false;
-  const cuuint64_t dims[4] = {(cuuint64_t)KD, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
-  const cuuint64_t strides[3] = {(cuuint64_t)KD * 2, (cuuint64_t)H * KD * 2, (cuuint64_t)T * H * KD * 2};
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || D % 64) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2, (cuuint64_t)T * H * D * 2};
   const cuuint32_t box[4] = {64, 1, 64, 1}, estr[4] = {1, 1, 1, 1};
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+static bool make_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H) {
+  return make_tma_map_bthd(m, base, B, T, H, KD);
 }
 
 static bool g_tc_use_tma = true;

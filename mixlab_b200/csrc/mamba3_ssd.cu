@@ -20,6 +20,10 @@
 //   m3s_chunk_out_kernel    per chunk: Y
 //   m3s_chunk_grad_kernel   per chunk: dx, rotated-row gradients -> dB, dC partials, per-token scalars
 //   m3s_final_kernel        per (b, head): suffix sum of the angle gradient, ddt, dlambda, dtheta, da_log
+#include <cuda.h>
+
+#include <cstring>
+
 #include "common.cuh"
 #include "umma_tiles.cuh"
 
@@ -228,50 +232,99 @@ __global__ void __launch_bounds__(256) m3s_scalars_kernel(SsdP p) {
 // The chunk contribution is one M=128 tcgen05 tile that never leaves the SM; the operands of the next two
 // chunks are in flight (cp.async, two buffers) while the current one is rotated, multiplied and folded in.
 // The saved state leaves as the byte image of the [128][64] operand tile (one bulk copy per chunk).
-constexpr int kPassBuf = 16384 + 8192 + sizeof(ChunkScal);
-constexpr int kPassSmem = 2 * kPassBuf + 2 * 16384 + 64 + 256;
+constexpr int kPassSmem = 2 * (16384 + 8192) + 2 * sizeof(ChunkScal) + 2 * 16384 + 64 + 1024;
 
-__global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode) {
+struct PassMaps {
+  CUtensorMap r;  // b or c: [B,T,G,128] viewed as (N, G, T, B), boxes of 64 columns x 64 steps, 128-byte swizzle
+  CUtensorMap x;  // x or dy: [B,T,heads,64] viewed as (P, heads, T, B)
+};
+
+// TMA = true: the three operand boxes of a chunk and its scalar record arrive by the copy engine on one mbarrier
+// per buffer (tiles in the 128-byte-swizzled layout); TMA = false: cp.async staging into the un-swizzled layout.
+template <bool TMA>
+__global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, const __grid_constant__ PassMaps maps) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
-  uint8_t* Himg = sm + 2 * kPassBuf;  // 2 x [128 n][64 p] bf16 images of the state on their way out
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(Himg + 2 * 16384);
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
+  uint8_t* Himg = sm + 2 * (16384 + 8192);  // 2 x [128 n][64 p] bf16 images of the state on their way out
+  uint8_t* scal = Himg + 2 * 16384;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(scal + 2 * sizeof(ChunkScal));  // [0] MMA, [1], [2] buffers full
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int nrow = tid & 127, half = tid >> 7;  // thread = state row n, 32 of its 64 columns
   const int head = blockIdx.x, b = blockIdx.y;
   const int d0 = head * P, g = d0 / (p.D / p.G);
   const size_t cbase = ((size_t)b * p.NH + head) * p.n;
-  auto Rt = [&](int buf) { return sm + buf * kPassBuf; };             // [64 s][128 n] B or C rows, rotated in place
-  auto Xt = [&](int buf) { return sm + buf * kPassBuf + 16384; };     // [64 s][64 p]  x or dy, scaled in place
-  auto Sc = [&](int buf) -> ChunkScal& { return *reinterpret_cast<ChunkScal*>(sm + buf * kPassBuf + 24576); };
+  auto Rt = [&](int buf) { return sm + buf * 16384; };             // [64 s][128 n] B or C rows, rotated in place
+  auto Xt = [&](int buf) { return sm + 32768 + buf * 8192; };      // [64 s][64 p]  x or dy, scaled in place
+  auto Sc = [&](int buf) -> ChunkScal& { return *reinterpret_cast<ChunkScal*>(scal + buf * sizeof(ChunkScal)); };
   auto chunk_at = [&](int it) { return mode == 0 ? it : p.n - 1 - it; };
   auto issue = [&](int it) {
     if (it < p.n) {
       const int c = chunk_at(it), buf = it & 1;
-      issue_rows_tile(Rt(buf), mode == 0 ? p.b : p.c, p, b, g, c * Q);
-      issue_x_tile(Xt(buf), mode == 0 ? p.x : p.dy, p, b, d0, c * Q);
-      issue_chunk_scalars(p, cbase + c, Sc(buf));
+      if (TMA) {
+        if (tid == 0) {
+          tc::mbar_expect_tx(&mbar[1 + buf], 16384 + 8192 + (uint32_t)sizeof(ChunkScal));
+          tc::tma_load_4d(tc::smem_u32(Rt(buf)), &maps.r, 0, g, c * Q, b, &mbar[1 + buf]);
+          tc::tma_load_4d(tc::smem_u32(Rt(buf)) + 8192, &maps.r, 64, g, c * Q, b, &mbar[1 + buf]);
+          tc::tma_load_4d(tc::smem_u32(Xt(buf)), &maps.x, 0, head, c * Q, b, &mbar[1 + buf]);
+          tc::bulk_load(tc::smem_u32(&Sc(buf)), p.cs + (cbase + c) * (sizeof(ChunkScal) / 4), (uint32_t)sizeof(ChunkScal),
+                        &mbar[1 + buf]);
+        }
+      } else {
+        issue_rows_tile(Rt(buf), mode == 0 ? p.b : p.c, p, b, g, c * Q);
+        issue_x_tile(Xt(buf), mode == 0 ? p.x : p.dy, p, b, d0, c * Q);
+        issue_chunk_scalars(p, cbase + c, Sc(buf));
+      }
     }
-    tc::cp_async_commit();
+    if (!TMA) tc::cp_async_commit();
+  };
+  // rows of the landed tiles: rotate B/C pairs, scale x/dy (16-byte units; a unit never straddles a pair)
+  auto fix_tiles = [&](int buf) {
+    const ChunkScal& s = Sc(buf);
+    const float* rowscale = mode == 0 ? s.re : s.dexp;
+    if (TMA) {  // swizzled slabs of [64 rows][128 bytes]: unit w of a slab belongs to row w / 8
+      for (int w = tid; w < 1024; w += 256) {
+        const int t = (w >> 3) & 63;
+        float e[8];
+        unpack8(*reinterpret_cast<const uint4*>(Rt(buf) + 16 * w), e);
+        const float s_ = s.sn[t], c_ = s.cs[t];
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) {
+          const float ev = e[k], od = e[k + 1];
+          e[k] = c_ * ev + s_ * od;
+          e[k + 1] = -s_ * ev + c_ * od;
+        }
+        *reinterpret_cast<uint4*>(Rt(buf) + 16 * w) = pack8(e);
+      }
+      for (int w = tid; w < 512; w += 256)
+        *reinterpret_cast<uint4*>(Xt(buf) + 16 * w) =
+            tc::scale_bf16x8(*reinterpret_cast<const uint4*>(Xt(buf) + 16 * w), rowscale[w >> 3]);
+    } else {
+      rotate_tile(Rt(buf), s.sn, s.cs);
+      scale_x_tile(Xt(buf), Xt(buf), rowscale);
+    }
   };
   if (warp == 0) { tc::tmem_alloc(tslot, 64); tc::tmem_relinquish(); }
-  if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
+  if (tid == 0) {
+    for (int m = 0; m < 3; ++m) tc::mbar_init(&mbar[m], 1);
+    tc::mbar_fence_init();
+  }
+  __syncthreads();  // barriers initialised before the copies can complete on them
   issue(0);
   issue(1);
   float H[32];
 #pragma unroll
   for (int x = 0; x < 32; ++x) H[x] = 0.f;
-  tc::cp_async_wait<1>();  // operands of the first chunk
+  bool ok = true;
+  if (TMA) ok = tc::mbar_wait(&mbar[1], 0);
+  else tc::cp_async_wait<1>();  // operands of the first chunk
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t taddr = *tslot;
   bf16* out = mode == 0 ? p.H0 : p.dH1;
   uint32_t ph = 0;
-  bool ok = true;
-  rotate_tile(Rt(0), Sc(0).sn, Sc(0).cs);
-  scale_x_tile(Xt(0), Xt(0), mode == 0 ? Sc(0).re : Sc(0).dexp);
+  fix_tiles(0);
   for (int it = 0; it < p.n && ok; ++it) {
     const int c = chunk_at(it), buf = it & 1;
     const float L = Sc(buf).L;
@@ -283,19 +336,22 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode) {
     __syncthreads();  // tiles of this chunk rotated and scaled (during the previous chunk's MMA), image staged
     tc::fence_after_sync();
     if (tid == 0) {  // [128 n x 64 p] = R^T X, both contracted over their rows
-      tc::issue_gemm(taddr, tc::mnmajor_tile(Rt(buf), N), tc::mnmajor_tile(Xt(buf), P), 128, P, Q, false);
+      if (TMA)
+        tc::issue_gemm(taddr, tc::mnmajor_sw128_tile(Rt(buf), 8192), tc::mnmajor_sw128_tile(Xt(buf), 8192), 128, P, Q, false);
+      else
+        tc::issue_gemm(taddr, tc::mnmajor_tile(Rt(buf), N), tc::mnmajor_tile(Xt(buf), P), 128, P, Q, false);
       tc::mma_commit(mbar);
       tc::bulk_store(out + (cbase + c) * (N * P), tc::smem_u32(Hi), 16384);
       tc::bulk_commit();
       tc::bulk_wait_read<1>();  // all but the copy just issued have been read out of shared memory
     }
     if (it + 1 < p.n) {  // while the tensor core works: the next chunk's tiles
-      tc::cp_async_wait<0>();
+      if (TMA) ok = tc::mbar_wait(&mbar[1 + (buf ^ 1)], ((it + 1) >> 1) & 1);
+      else tc::cp_async_wait<0>();
       __syncthreads();
-      rotate_tile(Rt(buf ^ 1), Sc(buf ^ 1).sn, Sc(buf ^ 1).cs);
-      scale_x_tile(Xt(buf ^ 1), Xt(buf ^ 1), mode == 0 ? Sc(buf ^ 1).re : Sc(buf ^ 1).dexp);
+      fix_tiles(buf ^ 1);
     }
-    ok = tc::mbar_wait(mbar, ph);
+    if (ok) ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
     issue(it + 2);  // this buffer is free: the MMA has read the tiles, every thread has read L
@@ -307,7 +363,7 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode) {
     }
     tc::fence_before_sync();
   }
-  tc::cp_async_wait<0>();
+  if (!TMA) tc::cp_async_wait<0>();
   if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 11);
   tc::fence_before_sync();
@@ -829,14 +885,34 @@ static mxb_status ssd_smem(KernelT k, size_t bytes) {
   return MXB_OK;
 }
 
+bool make_tma_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, int D);
+
+// Sequential pass over the chunks (mode 0: forward states, mode 1: reverse state gradients); the copy engine
+// feeds it when tensor maps can be made for the operands (16-byte aligned bases), cp.async otherwise.
+static mxb_status ssd_state_pass(SsdP& p, int mode, cudaStream_t st) {
+  m3s::PassMaps maps;
+  std::memset(&maps, 0, sizeof maps);
+  const bool tma = make_tma_map_bthd(&maps.r, mode == 0 ? p.b : p.c, p.B, p.T, p.G, m3s::N) &&
+                   make_tma_map_bthd(&maps.x, mode == 0 ? p.x : p.dy, p.B, p.T, p.NH, m3s::P);
+  if (tma) {
+    if (ssd_smem(m3s::m3s_state_pass_kernel<true>, m3s::kPassSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("m3s_state_pass_kernel", st,
+               (m3s::m3s_state_pass_kernel<true><<<dim3(p.NH, p.B), 256, m3s::kPassSmem, st>>>(p, mode, maps)));
+  } else {
+    if (ssd_smem(m3s::m3s_state_pass_kernel<false>, m3s::kPassSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("m3s_state_pass_kernel", st,
+               (m3s::m3s_state_pass_kernel<false><<<dim3(p.NH, p.B), 256, m3s::kPassSmem, st>>>(p, mode, maps)));
+  }
+  return check_launch("m3s_state_pass_kernel");
+}
+
 static mxb_status ssd_forward(SsdP& p, cudaStream_t st) {
   const dim3 gc(p.n, p.NH, p.B);
   if (cudaMemsetAsync(p.status, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
   MXB_LAUNCH("m3s_scalars_kernel", st, (m3s::m3s_scalars_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
   MXB_LAUNCH("m3s_chunk_scalars_kernel", st, (m3s::m3s_chunk_scalars_kernel<<<gc, 64, 0, st>>>(p)));
-  if (ssd_smem(m3s::m3s_state_pass_kernel, m3s::kPassSmem) != MXB_OK) return MXB_ERR_CUDA;
-  MXB_LAUNCH("m3s_state_pass_kernel", st,
-             (m3s::m3s_state_pass_kernel<<<dim3(p.NH, p.B), 256, m3s::kPassSmem, st>>>(p, 0)));
+  mxb_status ps = ssd_state_pass(p, 0, st);
+  if (ps != MXB_OK) return ps;
   if (p.y) {
     if (ssd_smem(m3s::m3s_chunk_out_kernel, m3s::kOutSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("m3s_chunk_out_kernel", st, (m3s::m3s_chunk_out_kernel<<<gc, 128, m3s::kOutSmem, st>>>(p)));
@@ -867,15 +943,14 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
   p.y = nullptr;  // the forward recompute stops at the chunk states
   if (d->flags & MXB_MAMBA3_BWD_USE_SAVED) {  // dt, lambda, phi, the chunk decays and H0 are still in place
     if (cudaMemsetAsync(p.status, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
-    if (ssd_smem(m3s::m3s_state_pass_kernel, m3s::kPassSmem) != MXB_OK) return MXB_ERR_CUDA;
   } else {
     mxb_status s = ssd_forward(p, st);
     if (s != MXB_OK) return s;
   }
   if (cudaMemsetAsync(da_log, 0, (size_t)p.NH * sizeof(float), st) != cudaSuccess) return MXB_ERR_CUDA;
   const dim3 gc(p.n, p.NH, p.B);
-  MXB_LAUNCH("m3s_state_pass_kernel", st,
-             (m3s::m3s_state_pass_kernel<<<dim3(p.NH, p.B), 256, m3s::kPassSmem, st>>>(p, 1)));
+  mxb_status ps = ssd_state_pass(p, 1, st);
+  if (ps != MXB_OK) return ps;
   if (ssd_smem(m3s::m3s_chunk_grad_kernel, m3s::kGradSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<<<gc, 256, m3s::kGradSmem, st>>>(p)));
   MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
