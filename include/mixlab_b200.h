@@ -176,6 +176,9 @@ enum {
                                       tensor-core kernels cover the shape */
   MXB_MAMBA3_SAVE_FOR_BWD = 4,     /* forward: mxb_mamba3_fwd_workspace_bytes returns the backward size and
                                       the chunk states and per-token scalars stay in the workspace */
+  MXB_MAMBA3_NO_TMA = 16,          /* chunked kernels: stage the operand tiles with cp.async instead of
+                                      the copy engine (the path taken anyway when a tensor map cannot be
+                                      made, e.g. a base pointer that is not 16-byte aligned) */
   MXB_MAMBA3_BWD_USE_SAVED = 8     /* backward: the workspace is the one a forward call with
                                       MXB_MAMBA3_SAVE_FOR_BWD just filled for the same inputs; the forward
                                       recompute is skipped.  Honoured by the chunked tensor-core kernels;

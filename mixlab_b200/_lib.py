@@ -19,6 +19,7 @@ MXB_MAMBA3_CHANNEL_KERNELS = 1
 MXB_MAMBA3_RECURRENT_KERNELS = 2
 MXB_MAMBA3_SAVE_FOR_BWD = 4
 MXB_MAMBA3_BWD_USE_SAVED = 8
+MXB_MAMBA3_NO_TMA = 16
 
 
 class MxbError(RuntimeError):

@@ -37,6 +37,7 @@ using bf16 = __nv_bfloat16;
 
 struct SsdP {
   int B, T, D, G, NH, n;   // n = chunks
+  int no_tma;              // stage operands with cp.async even where tensor maps can be made
   const bf16 *x, *b, *c, *dy;
   const float *dt_raw, *lam_raw, *theta, *a_log;
   bf16 *y, *dx;
@@ -193,6 +194,48 @@ __device__ __forceinline__ void scale_x_tile(uint8_t* dst, const uint8_t* src, c
         tc::scale_bf16x8(*reinterpret_cast<const uint4*>(src + 16 * u), rowscale[t]);
   }
 }
+
+// ---- the same fix-ups and views for tiles that the copy engine wrote with 128-byte swizzle (SW = true) ----
+template <bool SW>
+__device__ __forceinline__ uint32_t in_unit(int t, int c8, int W) {
+  return SW ? tc::sw128_unit(t, c8) : tc::kmajor_unit(t, c8, W);
+}
+template <bool SW>
+__device__ __forceinline__ tc::Tile in_kmajor(const void* ptr, int W) {
+  return SW ? tc::kmajor_sw128_tile(ptr, 8192) : tc::kmajor_tile(ptr, W);
+}
+template <bool SW>
+__device__ __forceinline__ tc::Tile in_mnmajor(const void* ptr, int W) {
+  return SW ? tc::mnmajor_sw128_tile(ptr, 8192) : tc::mnmajor_tile(ptr, W);
+}
+template <bool SW>
+__device__ __forceinline__ void rotate_in_tile(uint8_t* tile, const float* sn, const float* cs) {
+  if (!SW) { rotate_tile(tile, sn, cs); return; }
+  for (int w = threadIdx.x; w < Q * 16; w += blockDim.x) {  // unit w of a slab belongs to row w / 8
+    const int t = (w >> 3) & 63;
+    float e[8];
+    unpack8(*reinterpret_cast<const uint4*>(tile + 16 * w), e);
+    const float s_ = sn[t], c_ = cs[t];
+#pragma unroll
+    for (int k = 0; k < 8; k += 2) {
+      const float ev = e[k], od = e[k + 1];
+      e[k] = c_ * ev + s_ * od;
+      e[k + 1] = -s_ * ev + c_ * od;
+    }
+    *reinterpret_cast<uint4*>(tile + 16 * w) = pack8(e);
+  }
+}
+template <bool SW>
+__device__ __forceinline__ void scale_in_tile(uint8_t* dst, const uint8_t* src, const float* rowscale) {
+  if (!SW) { scale_x_tile(dst, src, rowscale); return; }
+  for (int w = threadIdx.x; w < Q * 8; w += blockDim.x)
+    *reinterpret_cast<uint4*>(dst + 16 * w) =
+        tc::scale_bf16x8(*reinterpret_cast<const uint4*>(src + 16 * w), rowscale[w >> 3]);
+}
+struct ChunkMaps {
+  CUtensorMap b, c;   // [B,T,G,128] viewed as (N, G, T, B), boxes of 64 columns x 64 steps, 128-byte swizzle
+  CUtensorMap x, dy;  // [B,T,heads,64] viewed as (P, heads, T, B)
+};
 
 // ------------------------------------------------------------ per-(b,head) scalars
 __global__ void __launch_bounds__(256) m3s_scalars_kernel(SsdP p) {
@@ -372,11 +415,12 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
 }
 
 // ------------------------------------------------------------ chunk output
-constexpr int kOutSmem = 16384 * 3 + 8192 * 2 + sizeof(ChunkScal) + 64 + 256;
+constexpr int kOutSmem = 16384 * 3 + 8192 * 2 + sizeof(ChunkScal) + 64 + 1024;
 
-__global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
+template <bool TMA>
+__global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p, const __grid_constant__ ChunkMaps maps) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
   uint8_t* Bt = sm;               // [64][128] Brot
   uint8_t* Ct = Bt + 16384;       // [64][128] Crot
   uint8_t* Ht = Ct + 16384;       // [128][64] H0
@@ -391,28 +435,44 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   const size_t ci = ((size_t)b * p.NH + head) * p.n + c;
 
   if (warp == 0) { tc::tmem_alloc(tslot, 128); tc::tmem_relinquish(); }
-  if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
-  issue_rows_tile(Bt, p.b, p, b, g, t0);
-  issue_rows_tile(Ct, p.c, p, b, g, t0);
-  issue_x_tile(Xt, p.x, p, b, d0, t0);
-  issue_state_tile(Ht, p.H0 + ci * (N * P));
-  issue_chunk_scalars(p, ci, s);
-  tc::cp_async_commit();
-  tc::cp_async_wait<0>();
+  if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_init(mbar + 1, 1); tc::mbar_fence_init(); }
+  bool ok = true;
+  if (TMA) {  // every operand by the copy engine, one barrier
+    __syncthreads();
+    if (tid == 0) {
+      tc::mbar_expect_tx(mbar + 1, 3 * 16384 + 8192 + (uint32_t)sizeof(ChunkScal));
+      for (int sl = 0; sl < 2; ++sl) {
+        tc::tma_load_4d(tc::smem_u32(Bt) + 8192 * sl, &maps.b, 64 * sl, g, t0, b, mbar + 1);
+        tc::tma_load_4d(tc::smem_u32(Ct) + 8192 * sl, &maps.c, 64 * sl, g, t0, b, mbar + 1);
+      }
+      tc::tma_load_4d(tc::smem_u32(Xt), &maps.x, 0, head, t0, b, mbar + 1);
+      tc::bulk_load(tc::smem_u32(Ht), p.H0 + ci * (N * P), 16384, mbar + 1);
+      tc::bulk_load(tc::smem_u32(&s), p.cs + ci * (sizeof(ChunkScal) / 4), (uint32_t)sizeof(ChunkScal), mbar + 1);
+    }
+    ok = tc::mbar_wait(mbar + 1, 0);
+  } else {
+    issue_rows_tile(Bt, p.b, p, b, g, t0);
+    issue_rows_tile(Ct, p.c, p, b, g, t0);
+    issue_x_tile(Xt, p.x, p, b, d0, t0);
+    issue_state_tile(Ht, p.H0 + ci * (N * P));
+    issue_chunk_scalars(p, ci, s);
+    tc::cp_async_commit();
+    tc::cp_async_wait<0>();
+  }
   __syncthreads();
-  rotate_tile(Bt, s.sn, s.cs);
-  rotate_tile(Ct, s.sn, s.cs);
+  rotate_in_tile<TMA>(Bt, s.sn, s.cs);
+  rotate_in_tile<TMA>(Ct, s.sn, s.cs);
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t taddr = *tslot;
   if (tid == 0) {
-    tc::issue_gemm(taddr, tc::kmajor_tile(Ct, N), tc::kmajor_tile(Bt, N), 64, Q, N, false);        // G = Crot Brot^T
-    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);  // Crot H0
+    tc::issue_gemm(taddr, in_kmajor<TMA>(Ct, N), in_kmajor<TMA>(Bt, N), 64, Q, N, false);           // G = Crot Brot^T
+    tc::issue_gemm(taddr + 64, in_kmajor<TMA>(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);    // Crot H0
     tc::mma_commit(mbar);
   }
-  bool ok = tc::mbar_wait(mbar, 0);
+  if (ok) ok = tc::mbar_wait(mbar, 0);
   tc::fence_after_sync();
   const int t = 16 * warp + (lane & 15);
   const bool own = lane < 16;
@@ -446,7 +506,7 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
   __syncthreads();
   tc::fence_after_sync();
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr, tc::kmajor_tile(Gm, Q), tc::mnmajor_tile(Xt, P), 64, P, Q, false);  // (G*M) X, over the consumed G
+    tc::issue_gemm(taddr, tc::kmajor_tile(Gm, Q), in_mnmajor<TMA>(Xt, P), 64, P, Q, false);  // (G*M) X, over the consumed G
     tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar, 1);
@@ -487,23 +547,25 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p) {
 //   phase 3: dBrot [0,128)
 // All accumulators are M=64: row i of every result is in TMEM lane (i%16)+32*(i/16); warps 0-3 take the
 // first half of the columns, warps 4-7 the second.  The G*M tile reuses the x tile once x is dead.
-constexpr int kGradSmem = 16384 * 4 + 8192 * 5 + sizeof(ChunkScal) + (4 * Q + 4 * Q + 8 * Q + 32) * 4 + 64 + 256;
+constexpr int kGradSmem = 16384 * 4 + 8192 * 5 + sizeof(ChunkScal) + (4 * Q + 4 * Q + 8 * Q + 32) * 4 + 64 + 1024;
 
+template <bool SW>
 __device__ __forceinline__ float row_dot32_64(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
   float acc = 0.f;  // sum_k tile[r][c0 + k] f[k] for a blocked [.][64] tile
 #pragma unroll
   for (int x = 0; x < 4; ++x) {
     float e[8];
-    unpack8(*reinterpret_cast<const uint4*>(tile + tc::kmajor_unit(r, (c0 >> 3) + x, P)), e);
+    unpack8(*reinterpret_cast<const uint4*>(tile + in_unit<SW>(r, (c0 >> 3) + x, P)), e);
 #pragma unroll
     for (int y = 0; y < 8; ++y) acc = fmaf(e[y], f[8 * x + y], acc);
   }
   return acc;
 }
 
-__global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
+template <bool TMA>
+__global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p, const __grid_constant__ ChunkMaps maps) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
   uint8_t* Bt = sm;                // [64][128] Brot
   uint8_t* Ct = Bt + 16384;        // [64][128] Crot
   uint8_t* Ht = Ct + 16384;        // [128][64] H0
@@ -519,8 +581,8 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   float* csw_l = csw_e + 4 * Q;                     // [4][Q] per-warp column sums for dLam
   float* part = csw_l + 4 * Q;                      // [2][4][Q]: per half: dLam, de, dgam, dphi row partials
   float* red = part + 8 * Q;                        // [32]
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + 32);
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + 32);  // [0] MMA completion, [1] token tiles, [2] state images
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, head = blockIdx.y, b = blockIdx.z, t0 = c * Q;
@@ -530,34 +592,57 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   const int t = 16 * (warp & 3) + (lane & 15), hc = warp >> 2;
 
   if (warp == 0) { tc::tmem_alloc(tslot, 256); tc::tmem_relinquish(); }
-  if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_fence_init(); }
-  issue_rows_tile(Bt, p.b, p, b, g, t0);
-  issue_rows_tile(Ct, p.c, p, b, g, t0);
-  issue_x_tile(Xt, p.x, p, b, d0, t0);
-  issue_x_tile(Yt, p.dy, p, b, d0, t0);
-  issue_chunk_scalars(p, ci, s);
-  tc::cp_async_commit();
-  issue_state_tile(Ht, p.H0 + ci * (N * P));
-  issue_state_tile(Dt, p.dH1 + ci * (N * P));
-  tc::cp_async_commit();
+  if (tid == 0) {
+    for (int m = 0; m < 3; ++m) tc::mbar_init(mbar + m, 1);
+    tc::mbar_fence_init();
+  }
+  bool ok = true;
+  if (TMA) {  // every operand by the copy engine: token tiles on one barrier, the state images on another
+    __syncthreads();
+    if (tid == 0) {
+      tc::mbar_expect_tx(mbar + 1, 2 * 16384 + 2 * 8192 + (uint32_t)sizeof(ChunkScal));
+      for (int sl = 0; sl < 2; ++sl) {
+        tc::tma_load_4d(tc::smem_u32(Bt) + 8192 * sl, &maps.b, 64 * sl, g, t0, b, mbar + 1);
+        tc::tma_load_4d(tc::smem_u32(Ct) + 8192 * sl, &maps.c, 64 * sl, g, t0, b, mbar + 1);
+      }
+      tc::tma_load_4d(tc::smem_u32(Xt), &maps.x, 0, head, t0, b, mbar + 1);
+      tc::tma_load_4d(tc::smem_u32(Yt), &maps.dy, 0, head, t0, b, mbar + 1);
+      tc::bulk_load(tc::smem_u32(&s), p.cs + ci * (sizeof(ChunkScal) / 4), (uint32_t)sizeof(ChunkScal), mbar + 1);
+      tc::mbar_expect_tx(mbar + 2, 2 * 16384);
+      tc::bulk_load(tc::smem_u32(Ht), p.H0 + ci * (N * P), 16384, mbar + 2);
+      tc::bulk_load(tc::smem_u32(Dt), p.dH1 + ci * (N * P), 16384, mbar + 2);
+    }
+  } else {
+    issue_rows_tile(Bt, p.b, p, b, g, t0);
+    issue_rows_tile(Ct, p.c, p, b, g, t0);
+    issue_x_tile(Xt, p.x, p, b, d0, t0);
+    issue_x_tile(Yt, p.dy, p, b, d0, t0);
+    issue_chunk_scalars(p, ci, s);
+    tc::cp_async_commit();
+    issue_state_tile(Ht, p.H0 + ci * (N * P));
+    issue_state_tile(Dt, p.dH1 + ci * (N * P));
+    tc::cp_async_commit();
+  }
   for (int u = tid; u < 8 * Q; u += 256) { csw_e[u] = 0.f; }  // csw_e and csw_l are contiguous
-  tc::cp_async_wait<1>();
+  if (TMA) ok = tc::mbar_wait(mbar + 1, 0);
+  else tc::cp_async_wait<1>();
   __syncthreads();
-  rotate_tile(Bt, s.sn, s.cs);
-  rotate_tile(Ct, s.sn, s.cs);
-  scale_x_tile(Xs, Xt, s.re);
-  scale_x_tile(Ys, Yt, s.dexp);
-  tc::cp_async_wait<0>();
+  rotate_in_tile<TMA>(Bt, s.sn, s.cs);
+  rotate_in_tile<TMA>(Ct, s.sn, s.cs);
+  scale_in_tile<TMA>(Xs, Xt, s.re);
+  scale_in_tile<TMA>(Ys, Yt, s.dexp);
+  if (TMA) { if (ok) ok = tc::mbar_wait(mbar + 2, 0); }
+  else tc::cp_async_wait<0>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t taddr = *tslot;
   if (tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Ct, N), tc::kmajor_tile(Bt, N), 64, Q, N, false);       // G
-    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Yt, P), tc::kmajor_tile(Xt, P), 64, Q, P, false);      // dY X^T
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);    // Crot H0
-    tc::issue_gemm(taddr + 192, tc::kmajor_tile(Bt, N), tc::mnmajor_tile(Dt, P), 64, P, N, false);    // Brot dH1
+    tc::issue_gemm(taddr + 0, in_kmajor<TMA>(Ct, N), in_kmajor<TMA>(Bt, N), 64, Q, N, false);         // G
+    tc::issue_gemm(taddr + 64, in_kmajor<TMA>(Yt, P), in_kmajor<TMA>(Xt, P), 64, Q, P, false);        // dY X^T
+    tc::issue_gemm(taddr + 128, in_kmajor<TMA>(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);     // Crot H0
+    tc::issue_gemm(taddr + 192, in_kmajor<TMA>(Bt, N), tc::mnmajor_tile(Dt, P), 64, P, N, false);     // Brot dH1
     tc::mma_commit(mbar);
   }
   {  // <dH1, H0> while the tensor core works
@@ -572,7 +657,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
     acc = warp_sum(acc);
     if (lane == 0) red[warp] = acc;
   }
-  bool ok = tc::mbar_wait(mbar, 0);
+  if (ok) ok = tc::mbar_wait(mbar, 0);
   tc::fence_after_sync();
   float dl_own = 0.f, de_own = 0.f, dg_own = 0.f, zsum = 0.f;
   const float lt = s.Lam[t], gt = s.gam[t], et = s.e[t], rt = s.r[t], dxt = s.dexp[t];
@@ -581,10 +666,10 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
       const int c0 = 32 * hc;
       float f[32];
       ld_acc32(taddr + 128, warp, c0, f);
-      if (own) dl_own += dxt * row_dot32_64(Yt, t, c0, f);
+      if (own) dl_own += dxt * row_dot32_64<TMA>(Yt, t, c0, f);
       ld_acc32(taddr + 192, warp, c0, f);
       if (own) {
-        const float zeta = row_dot32_64(Xt, t, c0, f);
+        const float zeta = row_dot32_64<TMA>(Xt, t, c0, f);
         de_own += rt * zeta;
         dl_own -= rt * et * zeta;
         zsum = rt * et * zeta;
@@ -660,9 +745,9 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   __syncthreads();
   tc::fence_after_sync();
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(GMt, Q), tc::mnmajor_tile(Yt, P), 64, P, Q, false);    // (G*M)^T dY
-    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Ys, P), tc::kmajor_tile(Ht, P), 64, N, P, false);      // (e^Lam dY) H0^T
-    tc::issue_gemm(taddr + 64, tc::kmajor_tile(dGt, Q), tc::mnmajor_tile(Bt, N), 64, N, Q, true);     // + dG Brot
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(GMt, Q), in_mnmajor<TMA>(Yt, P), 64, P, Q, false);     // (G*M)^T dY
+    tc::issue_gemm(taddr + 64, in_kmajor<TMA>(Ys, P), tc::kmajor_tile(Ht, P), 64, N, P, false);       // (e^Lam dY) H0^T
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(dGt, Q), in_mnmajor<TMA>(Bt, N), 64, N, Q, true);      // + dG Brot
     tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar, 1);
@@ -693,7 +778,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float cr[8], oc[8];
-          unpack8(*reinterpret_cast<const uint4*>(Ct + tc::kmajor_unit(t, (c0 >> 3) + x, N)), cr);
+          unpack8(*reinterpret_cast<const uint4*>(Ct + in_unit<TMA>(t, (c0 >> 3) + x, N)), cr);
 #pragma unroll
           for (int k = 0; k < 8; k += 2) {
             const float c0v = gc[8 * x + k], c1v = gc[8 * x + k + 1];
@@ -709,8 +794,8 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
   __syncthreads();  // columns [0,192) are free again
   tc::fence_after_sync();
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xs, P), tc::kmajor_tile(Dt, P), 64, N, P, false);       // (r e x) dH1^T
-    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(dGt, Q), tc::mnmajor_tile(Ct, N), 64, N, Q, true);     // + dG^T Crot
+    tc::issue_gemm(taddr + 0, in_kmajor<TMA>(Xs, P), tc::kmajor_tile(Dt, P), 64, N, P, false);        // (r e x) dH1^T
+    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(dGt, Q), in_mnmajor<TMA>(Ct, N), 64, N, Q, true);      // + dG^T Crot
     tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar, 0);
@@ -725,7 +810,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float br[8], ob[8];
-          unpack8(*reinterpret_cast<const uint4*>(Bt + tc::kmajor_unit(t, (c0 >> 3) + x, N)), br);
+          unpack8(*reinterpret_cast<const uint4*>(Bt + in_unit<TMA>(t, (c0 >> 3) + x, N)), br);
 #pragma unroll
           for (int k = 0; k < 8; k += 2) {
             const float b0 = gb[8 * x + k], b1 = gb[8 * x + k + 1];
@@ -870,6 +955,7 @@ static SsdP make_ssd(const mxb_mamba3_desc* d) {
   SsdP p{};
   p.B = d->B; p.T = d->T; p.D = d->D; p.G = d->G; p.NH = d->nheads;
   p.n = (d->T + m3s::Q - 1) / m3s::Q;
+  p.no_tma = (d->flags & MXB_MAMBA3_NO_TMA) ? 1 : 0;
   return p;
 }
 
@@ -887,12 +973,23 @@ static mxb_status ssd_smem(KernelT k, size_t bytes) {
 
 bool make_tma_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, int D);
 
+// Tensor maps for the token-indexed operands of the chunk kernels (dy only in the backward); false when one
+// cannot be made (a base that is not 16-byte aligned): the kernels then stage with cp.async.
+static bool ssd_chunk_maps(const SsdP& p, m3s::ChunkMaps& maps) {
+  std::memset(&maps, 0, sizeof maps);
+  if (p.no_tma) return false;
+  bool ok = make_tma_map_bthd(&maps.b, p.b, p.B, p.T, p.G, m3s::N) && make_tma_map_bthd(&maps.c, p.c, p.B, p.T, p.G, m3s::N) &&
+            make_tma_map_bthd(&maps.x, p.x, p.B, p.T, p.NH, m3s::P);
+  if (ok && p.dy) ok = make_tma_map_bthd(&maps.dy, p.dy, p.B, p.T, p.NH, m3s::P);
+  return ok;
+}
+
 // Sequential pass over the chunks (mode 0: forward states, mode 1: reverse state gradients); the copy engine
 // feeds it when tensor maps can be made for the operands (16-byte aligned bases), cp.async otherwise.
 static mxb_status ssd_state_pass(SsdP& p, int mode, cudaStream_t st) {
   m3s::PassMaps maps;
   std::memset(&maps, 0, sizeof maps);
-  const bool tma = make_tma_map_bthd(&maps.r, mode == 0 ? p.b : p.c, p.B, p.T, p.G, m3s::N) &&
+  const bool tma = !p.no_tma && make_tma_map_bthd(&maps.r, mode == 0 ? p.b : p.c, p.B, p.T, p.G, m3s::N) &&
                    make_tma_map_bthd(&maps.x, mode == 0 ? p.x : p.dy, p.B, p.T, p.NH, m3s::P);
   if (tma) {
     if (ssd_smem(m3s::m3s_state_pass_kernel<true>, m3s::kPassSmem) != MXB_OK) return MXB_ERR_CUDA;
@@ -914,8 +1011,14 @@ static mxb_status ssd_forward(SsdP& p, cudaStream_t st) {
   mxb_status ps = ssd_state_pass(p, 0, st);
   if (ps != MXB_OK) return ps;
   if (p.y) {
-    if (ssd_smem(m3s::m3s_chunk_out_kernel, m3s::kOutSmem) != MXB_OK) return MXB_ERR_CUDA;
-    MXB_LAUNCH("m3s_chunk_out_kernel", st, (m3s::m3s_chunk_out_kernel<<<gc, 128, m3s::kOutSmem, st>>>(p)));
+    m3s::ChunkMaps maps;
+    if (ssd_chunk_maps(p, maps)) {
+      if (ssd_smem(m3s::m3s_chunk_out_kernel<true>, m3s::kOutSmem) != MXB_OK) return MXB_ERR_CUDA;
+      MXB_LAUNCH("m3s_chunk_out_kernel", st, (m3s::m3s_chunk_out_kernel<true><<<gc, 128, m3s::kOutSmem, st>>>(p, maps)));
+    } else {
+      if (ssd_smem(m3s::m3s_chunk_out_kernel<false>, m3s::kOutSmem) != MXB_OK) return MXB_ERR_CUDA;
+      MXB_LAUNCH("m3s_chunk_out_kernel", st, (m3s::m3s_chunk_out_kernel<false><<<gc, 128, m3s::kOutSmem, st>>>(p, maps)));
+    }
   }
   return check_launch("mamba3 ssd forward");
 }
@@ -951,8 +1054,14 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
   const dim3 gc(p.n, p.NH, p.B);
   mxb_status ps = ssd_state_pass(p, 1, st);
   if (ps != MXB_OK) return ps;
-  if (ssd_smem(m3s::m3s_chunk_grad_kernel, m3s::kGradSmem) != MXB_OK) return MXB_ERR_CUDA;
-  MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<<<gc, 256, m3s::kGradSmem, st>>>(p)));
+  m3s::ChunkMaps maps;
+  if (ssd_chunk_maps(p, maps)) {
+    if (ssd_smem(m3s::m3s_chunk_grad_kernel<true>, m3s::kGradSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<true><<<gc, 256, m3s::kGradSmem, st>>>(p, maps)));
+  } else {
+    if (ssd_smem(m3s::m3s_chunk_grad_kernel<false>, m3s::kGradSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<false><<<gc, 256, m3s::kGradSmem, st>>>(p, maps)));
+  }
   MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
   MXB_LAUNCH("m3s_reduce_kernel", st,
              (m3s::m3s_reduce_kernel<<<dim3((p.T + 3) / 4, p.G, p.B), 128, 0, st>>>(p.pb, p.pc, static_cast<m3s::bf16*>(db),

@@ -59,6 +59,12 @@ __device__ __forceinline__ Tile skip_k(Tile t, int k0) { t.saddr += (uint32_t)(k
 __device__ __forceinline__ uint32_t kmajor_unit(int r, int c8, int kcols) {
   return (uint32_t)(r >> 3) * (uint32_t)(kcols / 8) * 128u + (uint32_t)c8 * 128u + (uint32_t)(r & 7) * 16u;
 }
+// Byte offset of the 16-byte unit holding elements (r, 8*c8 .. 8*c8+7) of a 64-row tile written by TMA with
+// 128-byte swizzle (8 KB slabs of 64 columns, 1024-byte aligned): the unit index within a 128-byte row is
+// XORed with the row's position in its 8-row group.
+__device__ __forceinline__ uint32_t sw128_unit(int r, int c8) {
+  return (uint32_t)(c8 >> 3) * 8192u + (uint32_t)r * 128u + (uint32_t)(((c8 & 7) ^ (r & 7)) << 4);
+}
 // Byte offset of the 16-byte unit holding elements (k, 8*c8 .. 8*c8+7) of an MN-major tile.
 __device__ __forceinline__ uint32_t mnmajor_unit(int k, int c8, int mn) {
   return (uint32_t)c8 * 128u + (uint32_t)(k >> 3) * (uint32_t)(mn / 8) * 128u + (uint32_t)(k & 7) * 16u;
