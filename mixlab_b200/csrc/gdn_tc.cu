@@ -32,9 +32,7 @@ namespace mxb {
 // un-swizzled layout (kept as a cross-check and for drivers without the tensor-map entry point).
 constexpr int kPrepSmem = 32768 + 16384 + 4 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 1024;
 
-struct alignas(64) PrepMaps {
-  CUtensorMap k, q, v;  // [B,T,H,128] bf16 viewed as (D, H, T, B), box (64, 1, 64, 1)
-};
+using PrepMaps = RowMaps;
 
 __device__ __forceinline__ uint4 pack8f(const float* e) {
   return make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]), tc::pack_bf16(e[4], e[5]),

@@ -2,10 +2,15 @@
 // backward: gdn_tc_bwd.cu).
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 #include "umma_tiles.cuh"
 
 namespace mxb {
+
+// [B,T,H,D] bf16 -> tensor map over (D, H, T, B) with 64 x 64 boxes and 128-byte swizzle; false if it cannot be made.
+bool make_tma_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, int D);
 
 namespace tcg {
 constexpr int C = 64;     // chunk
@@ -42,6 +47,27 @@ struct TcP {
   bf16* dpg;     // [C][C]    (dO v_new^T) * Gamma, lower triangle incl. diagonal
   float* ls;     // [1]       E(gam_last) <dS, S0>
 };
+
+// Tensor maps of the token-indexed operands: [B,T,H,128] bf16 viewed as (D, H, T, B), boxes of 64 columns x
+// 64 time steps with 128-byte swizzle; rows past the end of the sequence are zero-filled by the copy engine.
+struct alignas(64) RowMaps {
+  CUtensorMap k, q, v, dO;
+};
+
+// Views of a [64][128] tile for tcgen05 and for 16-byte unit access: written by the copy engine with 128-byte
+// swizzle (SW = true: two 8 KB slabs of 64 columns) or staged un-swizzled in the blocked layout.
+template <bool SW>
+__device__ __forceinline__ tc::Tile in_kmajor(const void* ptr) {
+  return SW ? tc::kmajor_sw128_tile(ptr, 8192) : tc::kmajor_tile(ptr, KD);
+}
+template <bool SW>
+__device__ __forceinline__ tc::Tile in_mnmajor(const void* ptr) {
+  return SW ? tc::mnmajor_sw128_tile(ptr, 8192) : tc::mnmajor_tile(ptr, KD);
+}
+template <bool SW>
+__device__ __forceinline__ uint32_t in_unit(int r, int c8) {
+  return SW ? tc::sw128_unit(r, c8) : tc::kmajor_unit(r, c8, KD);
+}
 
 __device__ __forceinline__ float log_gate_tc(float g, int gate_is_log) {
   return gate_is_log ? fmaxf(g, kLogGateFloor) : __logf(fmaxf(g, kGateFloor));

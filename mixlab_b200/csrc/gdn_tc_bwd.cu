@@ -19,6 +19,8 @@
 // A 64 x W bf16 tile stored as 8x8-element blocks ("blocked row-major", umma_tiles.cuh)
 // can be read by tcgen05.mma either with the contraction along its columns (K-major) or
 // along its rows (MN-major); both views are used on the same staged bytes.
+#include <cstring>
+
 #include "gdn_tc.cuh"
 
 namespace mxb {
@@ -225,7 +227,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
 //   2: (T^T dv_new) v^T [0,64)        z k^T [64,128)            k k^T [128,192)   q k^T [192,256)
 //   3: Y T^T [0,64)   with Y = T^T dT assembled from phase 2
 //   4: (dP*Gamma) k [0,128)           (dP*Gamma)^T q + (Mb + Mb^T) k [128,256)
-constexpr int kChunkBwdSmem = 5 * 16384 + 3 * 8192 + 13 * C * 4 + 64 + 256;
+constexpr int kChunkBwdSmem = 5 * 16384 + 3 * 8192 + 13 * C * 4 + 64 + 1024;
 
 __device__ __forceinline__ void unpack8(uint4 v, float (&e)[8]) {
   tc::unpack_bf16(v.x, e[0], e[1]); tc::unpack_bf16(v.y, e[2], e[3]);
@@ -236,12 +238,13 @@ __device__ __forceinline__ uint4 pack8(const float* e) {
                     tc::pack_bf16(e[6], e[7]));
 }
 // sum_k tile[row][c0 + k] * f[k], k < 32, for a blocked [.][128] bf16 tile in shared memory
+template <bool SW>
 __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
   float s = 0.f;
 #pragma unroll
   for (int x = 0; x < 4; ++x) {
     float e[8];
-    unpack8(*reinterpret_cast<const uint4*>(tile + tc::kmajor_unit(r, (c0 >> 3) + x, KD)), e);
+    unpack8(*reinterpret_cast<const uint4*>(tile + in_unit<SW>(r, (c0 >> 3) + x)), e);
 #pragma unroll
     for (int y = 0; y < 8; ++y) s = fmaf(e[y], f[8 * x + y], s);
   }
@@ -421,9 +424,12 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   if (warp == 0) tc::tmem_dealloc(taddr, 256);
 }
 
-__global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
+// TMA = true: k, q, v by the copy engine (128-byte-swizzled tiles) and every workspace image by bulk copies, all
+// completing on mbarriers; TMA = false: cp.async staging in the un-swizzled layout.
+template <bool TMA>
+__global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const __grid_constant__ RowMaps maps) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
   uint8_t* Xk = sm;                 // [64][128] k
   uint8_t* Xq = Xk + 16384;         // [64][128] q
   uint8_t* Xv = Xq + 16384;         // [64][128] v; then Y = T^T dT (first half); then the dqp image -> dq
@@ -441,8 +447,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   float* dbo = dgo + 2 * C;
   float* red = dbo + 2 * C;
   float* csw = red + C;             // [4 warps][C] per-warp column sums (no atomics)
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(csw + 4 * C);
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(csw + 4 * C);  // [0] MMA, [1] dv_new/dw/T, [2] k/q/v/dP*Gamma, [3] dqp/dkp
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
@@ -453,7 +459,24 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   const int i = 16 * (warp & 3) + (lane & 15);  // the row this thread owns in every epilogue
   const int hc = warp >> 2;  // warps 0-3 take the first half of an accumulator's columns, warps 4-7 the second
 
-  {  // group 0: dv_new, dw, T   group 1: k, q, v, dP*Gamma
+  if (tid == 0) {
+    for (int m = 0; m < 4; ++m) tc::mbar_init(mbar + m, 1);
+    tc::mbar_fence_init();
+    if (TMA) {
+      tc::mbar_expect_tx(mbar + 1, 2 * 16384 + 8192);
+      tc::bulk_load(tc::smem_u32(Xdvn), p.dvn + ci * C * KD, 16384, mbar + 1);  // byte images of the operand tiles
+      tc::bulk_load(tc::smem_u32(Xdw), p.dw + ci * C * KD, 16384, mbar + 1);
+      tc::bulk_load(tc::smem_u32(Xt), p.Tm + ci * C * C, 8192, mbar + 1);
+      tc::mbar_expect_tx(mbar + 2, 3 * 16384 + 8192);
+      for (int sl = 0; sl < 2; ++sl) {
+        tc::tma_load_4d(tc::smem_u32(Xk) + 8192 * sl, &maps.k, 64 * sl, h, t0, b, mbar + 2);
+        tc::tma_load_4d(tc::smem_u32(Xq) + 8192 * sl, &maps.q, 64 * sl, h, t0, b, mbar + 2);
+        tc::tma_load_4d(tc::smem_u32(Xv) + 8192 * sl, &maps.v, 64 * sl, h, t0, b, mbar + 2);
+      }
+      tc::bulk_load(tc::smem_u32(Xpg), p.dpg + ci * C * C, 8192, mbar + 2);
+    }
+  }
+  if (!TMA) {  // group 0: dv_new, dw, T   group 1: k, q, v, dP*Gamma
     const uint32_t sk = tc::smem_u32(Xk), sq = tc::smem_u32(Xq), sv = tc::smem_u32(Xv);
     const uint32_t sdvn = tc::smem_u32(Xdvn), sdw = tc::smem_u32(Xdw);
     const uint32_t st = tc::smem_u32(Xt), spg = tc::smem_u32(Xpg);
@@ -488,10 +511,6 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
     tc::tmem_alloc(tslot, 256);
     tc::tmem_relinquish();
   }
-  if (tid == 0) {
-    tc::mbar_init(mbar, 1);
-    tc::mbar_fence_init();
-  }
   if (tid < C) {
     gam[tid] = p.gam[ci * C + tid];
     bet[tid] = tid < imax ? p.beta[row(tid)] : 0.f;
@@ -503,23 +522,25 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
     dd[tid] = exp_nonpos(gam[tid]);
     rr[tid] = exp_nonpos(glast - gam[tid]);
   }
-  tc::cp_async_wait<1>();
+  bool ok = true;
+  if (TMA) ok = tc::mbar_wait(mbar + 1, 0);
+  else tc::cp_async_wait<1>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t taddr = *tslot;
   uint32_t ph = 0;
-  bool ok = true;
   // ---- phase 1: T^T dv_new and z = T^T dw (both operands contracted over their rows) ----
   if (tid == 0) {
     tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdvn, KD), 64, 128, C, false);
     tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdw, KD), 64, 128, C, false);
     tc::mma_commit(mbar);
   }
-  tc::cp_async_wait<0>();  // k, q, v, dP*Gamma
+  if (TMA) { if (ok) ok = tc::mbar_wait(mbar + 2, 0); }  // k, q, v, dP*Gamma
+  else tc::cp_async_wait<0>();
   __syncthreads();
-  ok = tc::mbar_wait(mbar, ph);
+  if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
   float dg_own = 0.f, db_own = 0.f;
@@ -538,13 +559,13 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
       if (own) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) f[jj] = -f[jj];  // the workspace holds -dv_new
-        vdot += row_dot32(Xv, i, c0, f);
+        vdot += row_dot32<TMA>(Xv, i, c0, f);
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
       ld_acc32(taddr + 128, warp, c0, f);
       if (own) {
-        kz += row_dot32(Xk, i, c0, f);
+        kz += row_dot32<TMA>(Xk, i, c0, f);
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Xdw, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
@@ -561,10 +582,10 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
   // ---- phase 2: Y = T^T dT = (T^T dv_new)(v beta)^T + z (k beta d)^T, with the column scales applied in the
   //      epilogue; k k^T and q k^T ride along ----
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xv, KD), 64, 64, KD, false);
-    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Xdw, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xk, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);  // k k^T
-    tc::issue_gemm(taddr + 192, tc::kmajor_tile(Xq, KD), tc::kmajor_tile(Xk, KD), 64, 64, KD, false);  // q k^T
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdvn, KD), in_kmajor<TMA>(Xv), 64, 64, KD, false);
+    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Xdw, KD), in_kmajor<TMA>(Xk), 64, 64, KD, false);
+    tc::issue_gemm(taddr + 128, in_kmajor<TMA>(Xk), in_kmajor<TMA>(Xk), 64, 64, KD, false);  // k k^T
+    tc::issue_gemm(taddr + 192, in_kmajor<TMA>(Xq), in_kmajor<TMA>(Xk), 64, 64, KD, false);  // q k^T
     tc::mma_commit(mbar);
   }
   if (ok) {
@@ -633,8 +654,16 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
     ph ^= 1;
   }
   tc::fence_after_sync();
+  tc::fence_async_smem();
   __syncthreads();  // every thread is done with the T^T dv_new tile; Y (over v) has been consumed by the MMA
-  {  // the state contractions from the first kernel land over v and T^T dv_new while phase 3's epilogue runs
+  // the state contractions from the first kernel land over v and T^T dv_new while phase 3's epilogue runs
+  if (TMA) {
+    if (tid == 0) {
+      tc::mbar_expect_tx(mbar + 3, 2 * 16384);
+      tc::bulk_load(tc::smem_u32(Xv), p.dqp + ci * C * KD, 16384, mbar + 3);
+      tc::bulk_load(tc::smem_u32(Xdvn), p.dkp + ci * C * KD, 16384, mbar + 3);
+    }
+  } else {
     const uint32_t sqp = tc::smem_u32(Xv), skp = tc::smem_u32(Xdvn);
     for (int u = tid; u < 64 * 16; u += 256) {
       tc::cp_async16(sqp + 16 * u, p.dqp + ci * C * KD + 8 * u);
@@ -668,17 +697,18 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
       dst[1] -= KKr[1];
     }
   }
-  tc::cp_async_wait<0>();
+  if (TMA) { if (ok) ok = tc::mbar_wait(mbar + 3, 0); }
+  else tc::cp_async_wait<0>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   // ---- phase 4: (dP*Gamma) k  and  (dP*Gamma)^T q + (Mb + Mb^T) k ----
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xpg, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, false);
-    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xpg, C), tc::mnmajor_tile(Xq, KD), 64, 128, C, false);
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(X1, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, true);
-    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(X1, C), tc::mnmajor_tile(Xk, KD), 64, 128, C, true);
+    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xpg, C), in_mnmajor<TMA>(Xk), 64, 128, C, false);
+    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xpg, C), in_mnmajor<TMA>(Xq), 64, 128, C, false);
+    tc::issue_gemm(taddr + 128, tc::kmajor_tile(X1, C), in_mnmajor<TMA>(Xk), 64, 128, C, true);
+    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(X1, C), in_mnmajor<TMA>(Xk), 64, 128, C, true);
     tc::mma_commit(mbar);
   }
   if (ok) {
@@ -701,7 +731,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
 #pragma unroll
           for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
         }
-        qdot += row_dot32(Xq, i, c0, f);  // q_i . d_i dqi_i
+        qdot += row_dot32<TMA>(Xq, i, c0, f);  // q_i . d_i dqi_i
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) g2[jj] += f[jj];
 #pragma unroll
@@ -716,7 +746,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p) {
 #pragma unroll
           for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
         }
-        kdot += row_dot32(Xk, i, c0, f);  // k_i . r_i dkt_i
+        kdot += row_dot32<TMA>(Xk, i, c0, f);  // k_i . r_i dkt_i
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float z[8];
@@ -811,9 +841,20 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
              (gdn_tc_chunk_bwd_state_kernel<<<dim3(p.n, p.B * p.H), 256, kChunkBwdStateSmem, st>>>(p)));
   s = check_launch("gdn_tc_chunk_bwd_state_kernel");
   if (s != MXB_OK) return s;
-  if (bwd_set_smem(gdn_tc_chunk_bwd_kernel, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
-  MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
-             (gdn_tc_chunk_bwd_kernel<<<dim3(p.n, p.B * p.H), 256, kChunkBwdSmem, st>>>(p)));
+  RowMaps maps;
+  std::memset(&maps, 0, sizeof maps);
+  const bool tma = !p.no_tma && make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, KD) &&
+                   make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, KD) &&
+                   make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, KD);
+  if (tma) {
+    if (bwd_set_smem(gdn_tc_chunk_bwd_kernel<true>, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
+               (gdn_tc_chunk_bwd_kernel<true><<<dim3(p.n, p.B * p.H), 256, kChunkBwdSmem, st>>>(p, maps)));
+  } else {
+    if (bwd_set_smem(gdn_tc_chunk_bwd_kernel<false>, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
+               (gdn_tc_chunk_bwd_kernel<false><<<dim3(p.n, p.B * p.H), 256, kChunkBwdSmem, st>>>(p, maps)));
+  }
   return check_launch("gdn_tc_chunk_bwd_kernel");
 }
 
