@@ -258,11 +258,12 @@ __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, c
 // copies; the second kernel loads those byte images back unchanged.
 //   phase 1: dO S0^T [0,128), (-dv_new) S0^T [128,256) -> dqp = d (dO S0^T), dw = -dv_new S0^T
 //   phase 2: v_new dS^T [0,128), dO v_new^T [128,192) -> dkp = r (v_new dS^T), dP*Gamma, L <dS, S0>
-constexpr int kChunkBwdStateSmem = 4 * 16384 + 32768 + 4 * C * 4 + 64 + 256;
+constexpr int kChunkBwdStateSmem = 4 * 16384 + 32768 + 4 * C * 4 + 64 + 1024;
 
-__global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
+template <bool TMA>
+__global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p, const __grid_constant__ RowMaps maps) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
+  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
   uint8_t* Xdo = sm;                // [64][128] dO            -> later the dkp image
   uint8_t* Xdvn = Xdo + 16384;      // [64][128] -dv_new       -> later the dqp image
   uint8_t* Xvn = Xdvn + 16384;      // [64][128] v_new         -> later the dP*Gamma image (first half)
@@ -272,8 +273,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   float* dd = gam + C;
   float* rr = dd + C;
   float* red = rr + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + C);
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + C);  // [0] MMA, [1] dO/dv_new/S0, [2] v_new, [3] dS
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
@@ -283,7 +284,20 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
   const bool own = lane < 16;
   const int i = 16 * (warp & 3) + (lane & 15), hc = warp >> 2;
 
-  {  // group 0: dO, dv_new, S0   group 1: v_new
+  if (tid == 0) {
+    for (int m = 0; m < 4; ++m) tc::mbar_init(mbar + m, 1);
+    tc::mbar_fence_init();
+    if (TMA) {  // dO by the copy engine (swizzled tile), the workspace images by bulk copies
+      tc::mbar_expect_tx(mbar + 1, 2 * 16384 + 32768);
+      tc::tma_load_4d(tc::smem_u32(Xdo), &maps.dO, 0, h, t0, b, mbar + 1);
+      tc::tma_load_4d(tc::smem_u32(Xdo) + 8192, &maps.dO, 64, h, t0, b, mbar + 1);
+      tc::bulk_load(tc::smem_u32(Xdvn), p.dvn + ci * C * KD, 16384, mbar + 1);
+      tc::bulk_load(tc::smem_u32(Xs), p.hs + ci * KD * KD, 32768, mbar + 1);
+      tc::mbar_expect_tx(mbar + 2, 16384);
+      tc::bulk_load(tc::smem_u32(Xvn), p.vn + ci * C * KD, 16384, mbar + 2);
+    }
+  }
+  if (!TMA) {  // group 0: dO, dv_new, S0   group 1: v_new
     const uint32_t sdo = tc::smem_u32(Xdo), sdvn = tc::smem_u32(Xdvn), svn = tc::smem_u32(Xvn), ss = tc::smem_u32(Xs);
     for (int u = tid; u < 64 * 16; u += 256) {
       const int r = urow16(u), c8 = ucol16(u);
@@ -300,10 +314,6 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
     tc::tmem_alloc(tslot, 256);
     tc::tmem_relinquish();
   }
-  if (tid == 0) {
-    tc::mbar_init(mbar, 1);
-    tc::mbar_fence_init();
-  }
   if (tid < C) gam[tid] = p.gam[ci * C + tid];
   __syncthreads();
   const float glast = gam[C - 1], L = exp_nonpos(glast);
@@ -311,24 +321,35 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
     dd[tid] = exp_nonpos(gam[tid]);
     rr[tid] = exp_nonpos(glast - gam[tid]);
   }
-  tc::cp_async_wait<1>();
+  bool ok = true;
+  if (TMA) ok = tc::mbar_wait(mbar + 1, 0);
+  else tc::cp_async_wait<1>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t taddr = *tslot;
-  bool ok = true;
   if (tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);     // dO S0^T
+    tc::issue_gemm(taddr + 0, in_kmajor<TMA>(Xdo), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);          // dO S0^T
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);  // -dv_new S0^T
     tc::mma_commit(mbar);
   }
   uint4 s0u[8];  // this thread's 8 units of S0, kept for <dS, S0> (the buffer is about to be reused)
 #pragma unroll
   for (int x = 0; x < 8; ++x) s0u[x] = *reinterpret_cast<const uint4*>(Xs + (tid + 256 * x) * 16);
-  ok = tc::mbar_wait(mbar, 0);
+  if (TMA) {  // every thread has taken its units before one thread lets the copy engine overwrite the buffer
+    tc::fence_async_smem();
+    __syncthreads();
+  }
+  if (ok) ok = tc::mbar_wait(mbar, 0);
   tc::fence_after_sync();
-  {  // S0 is dead in shared memory: fetch dS into the same buffer behind the epilogue
+  // S0 is dead in shared memory: fetch dS into the same buffer behind the epilogue
+  if (TMA) {
+    if (tid == 0) {
+      tc::mbar_expect_tx(mbar + 3, 32768);
+      tc::bulk_load(tc::smem_u32(Xs), p.dhs + ci * KD * KD, 32768, mbar + 3);
+    }
+  } else {
     const uint32_t ss = tc::smem_u32(Xs);
     for (int u = tid; u < 128 * 16; u += 256) tc::cp_async16(ss + 16 * u, p.dhs + ci * KD * KD + 8 * u);
     tc::cp_async_commit();
@@ -351,14 +372,19 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p) {
       }
     }
   }
-  tc::cp_async_wait<0>();  // v_new and dS
+  if (TMA) {  // v_new and dS
+    if (ok) ok = tc::mbar_wait(mbar + 2, 0);
+    if (ok) ok = tc::mbar_wait(mbar + 3, 0);
+  } else {
+    tc::cp_async_wait<0>();
+  }
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   if (ok && tid == 0) {
     tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);    // v_new dS^T
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdo, KD), tc::kmajor_tile(Xvn, KD), 64, 64, KD, false);  // dO v_new^T
+    tc::issue_gemm(taddr + 128, in_kmajor<TMA>(Xdo), tc::kmajor_tile(Xvn, KD), 64, 64, KD, false);     // dO v_new^T
     tc::mma_commit(mbar);
     tc::bulk_store(p.dqp + ci * C * KD, tc::smem_u32(Xdvn), 16384);
     tc::bulk_store(p.dw + ci * C * KD, tc::smem_u32(Xst), 16384);
@@ -836,16 +862,22 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
              (gdn_tc_state_bwd_kernel<<<dim3(p.B * p.H), 256, kStateBwdSmem, st>>>(p)));
   s = check_launch("gdn_tc_state_bwd_kernel");
   if (s != MXB_OK) return s;
-  if (bwd_set_smem(gdn_tc_chunk_bwd_state_kernel, kChunkBwdStateSmem) != MXB_OK) return MXB_ERR_CUDA;
-  MXB_LAUNCH("gdn_tc_chunk_bwd_state_kernel", st,
-             (gdn_tc_chunk_bwd_state_kernel<<<dim3(p.n, p.B * p.H), 256, kChunkBwdStateSmem, st>>>(p)));
-  s = check_launch("gdn_tc_chunk_bwd_state_kernel");
-  if (s != MXB_OK) return s;
   RowMaps maps;
   std::memset(&maps, 0, sizeof maps);
   const bool tma = !p.no_tma && make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, KD) &&
                    make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, KD) &&
                    make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, KD);
+  if (tma) {
+    if (bwd_set_smem(gdn_tc_chunk_bwd_state_kernel<true>, kChunkBwdStateSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_chunk_bwd_state_kernel", st,
+               (gdn_tc_chunk_bwd_state_kernel<true><<<dim3(p.n, p.B * p.H), 256, kChunkBwdStateSmem, st>>>(p, maps)));
+  } else {
+    if (bwd_set_smem(gdn_tc_chunk_bwd_state_kernel<false>, kChunkBwdStateSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_chunk_bwd_state_kernel", st,
+               (gdn_tc_chunk_bwd_state_kernel<false><<<dim3(p.n, p.B * p.H), 256, kChunkBwdStateSmem, st>>>(p, maps)));
+  }
+  s = check_launch("gdn_tc_chunk_bwd_state_kernel");
+  if (s != MXB_OK) return s;
   if (tma) {
     if (bwd_set_smem(gdn_tc_chunk_bwd_kernel<true>, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
