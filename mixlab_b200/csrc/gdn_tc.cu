@@ -136,23 +136,29 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   tc::fence_after_sync();
   if (ok) {
     const int i = tid & 63;
-    const float gi = gam[i];
+    const float gi = gam[i], bi = bet[i];
     for (int c0 = 0; c0 < 64; c0 += 32) {
       float f[32];
       ld_acc32(taddr, warp, c0, f);
       if (tid < 64) {  // A = -(k beta k^T) Gamma, strictly lower
+        // all 32 values first, then the stores: a store into A between the loads of gam would pin the order
+        // (the compiler must assume the two shared arrays overlap) and the exponentials would run one by one
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
           const int j = c0 + jj;
-          Am[i * LDA + j] = (j < i) ? -bet[i] * f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
+          const float val = -bi * f[jj] * exp_nonpos(gi - gam[j]);
+          f[jj] = (j < i) ? val : 0.f;
         }
+#pragma unroll
+        for (int x = 0; x < 8; ++x)
+          *reinterpret_cast<float4*>(Am + i * LDA + c0 + 4 * x) = make_float4(f[4 * x], f[4 * x + 1], f[4 * x + 2], f[4 * x + 3]);
       } else {         // P = (q k^T) Gamma, lower incl. diagonal -> workspace
         uint32_t pk[16];
 #pragma unroll
         for (int jj = 0; jj < 32; jj += 2) {
           const int j = c0 + jj;
-          const float x0 = (j <= i) ? f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
-          const float x1 = (j + 1 <= i) ? f[jj + 1] * exp_nonpos(gi - gam[j + 1]) : 0.f;
+          const float v0 = f[jj] * exp_nonpos(gi - gam[j]), v1 = f[jj + 1] * exp_nonpos(gi - gam[j + 1]);
+          const float x0 = (j <= i) ? v0 : 0.f, x1 = (j + 1 <= i) ? v1 : 0.f;
           pk[jj >> 1] = tc::pack_bf16(x0, x1);
         }
 #pragma unroll

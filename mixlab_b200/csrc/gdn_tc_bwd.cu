@@ -424,7 +424,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p, c
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) {
           const int j = c0 + jj;
-          f[jj] = (j <= i) ? f[jj] * exp_nonpos(gi - gam[j]) : 0.f;
+          const float val = f[jj] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
+          f[jj] = (j <= i) ? val : 0.f;
         }
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Xvn, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
@@ -704,7 +705,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
 #pragma unroll
     for (int jj = 0; jj < 32; ++jj) {
       const int j = cb + jj;
-      const float M = (own && j < i) ? -f[jj] * exp_nonpos(gi - gam[j]) : 0.f;  // -dA * Gamma
+      const float mv = -f[jj] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
+      const float M = (own && j < i) ? mv : 0.f;         // -dA * Gamma
       const float t = M * KKr[jj];
       rs += t;
       KKr[jj] = bi * t;
