@@ -211,18 +211,32 @@ __device__ __forceinline__ tc::Tile in_mnmajor(const void* ptr, int W) {
 template <bool SW>
 __device__ __forceinline__ void rotate_in_tile(uint8_t* tile, const float* sn, const float* cs) {
   if (!SW) { rotate_tile(tile, sn, cs); return; }
-  for (int w = threadIdx.x; w < Q * 16; w += blockDim.x) {  // unit w of a slab belongs to row w / 8
-    const int t = (w >> 3) & 63;
-    float e[8];
-    unpack8(*reinterpret_cast<const uint4*>(tile + 16 * w), e);
-    const float s_ = sn[t], c_ = cs[t];
+  // four units per pass, all loads before the first store (a store in between would pin the order of the
+  // loads that follow it); unit w of a slab belongs to row w / 8
+  const int nt = blockDim.x;
+  for (int w0 = threadIdx.x; w0 < Q * 16; w0 += 4 * nt) {
+    uint4 raw[4];
+    float sv[4], cv[4];
 #pragma unroll
-    for (int k = 0; k < 8; k += 2) {
-      const float ev = e[k], od = e[k + 1];
-      e[k] = c_ * ev + s_ * od;
-      e[k + 1] = -s_ * ev + c_ * od;
+    for (int q = 0; q < 4; ++q) {
+      const int w = w0 + q * nt, t = (w >> 3) & 63;
+      raw[q] = *reinterpret_cast<const uint4*>(tile + 16 * w);
+      sv[q] = sn[t]; cv[q] = cs[t];
     }
-    *reinterpret_cast<uint4*>(tile + 16 * w) = pack8(e);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float e[8];
+      unpack8(raw[q], e);
+#pragma unroll
+      for (int k = 0; k < 8; k += 2) {
+        const float ev = e[k], od = e[k + 1];
+        e[k] = cv[q] * ev + sv[q] * od;
+        e[k + 1] = -sv[q] * ev + cv[q] * od;
+      }
+      raw[q] = pack8(e);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(tile + 16 * (w0 + q * nt)) = raw[q];
   }
 }
 template <bool SW>
@@ -326,22 +340,14 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
     const ChunkScal& s = Sc(buf);
     const float* rowscale = mode == 0 ? s.re : s.dexp;
     if (TMA) {  // swizzled slabs of [64 rows][128 bytes]: unit w of a slab belongs to row w / 8
-      for (int w = tid; w < 1024; w += 256) {
-        const int t = (w >> 3) & 63;
-        float e[8];
-        unpack8(*reinterpret_cast<const uint4*>(Rt(buf) + 16 * w), e);
-        const float s_ = s.sn[t], c_ = s.cs[t];
-#pragma unroll
-        for (int k = 0; k < 8; k += 2) {
-          const float ev = e[k], od = e[k + 1];
-          e[k] = c_ * ev + s_ * od;
-          e[k + 1] = -s_ * ev + c_ * od;
-        }
-        *reinterpret_cast<uint4*>(Rt(buf) + 16 * w) = pack8(e);
+      rotate_in_tile<true>(Rt(buf), s.sn, s.cs);
+      {  // both units of this thread: loads first, then the stores
+        const uint4 a = *reinterpret_cast<const uint4*>(Xt(buf) + 16 * tid);
+        const uint4 c2 = *reinterpret_cast<const uint4*>(Xt(buf) + 16 * (tid + 256));
+        const float ra = rowscale[tid >> 3], rc = rowscale[(tid + 256) >> 3];
+        *reinterpret_cast<uint4*>(Xt(buf) + 16 * tid) = tc::scale_bf16x8(a, ra);
+        *reinterpret_cast<uint4*>(Xt(buf) + 16 * (tid + 256)) = tc::scale_bf16x8(c2, rc);
       }
-      for (int w = tid; w < 512; w += 256)
-        *reinterpret_cast<uint4*>(Xt(buf) + 16 * w) =
-            tc::scale_bf16x8(*reinterpret_cast<const uint4*>(Xt(buf) + 16 * w), rowscale[w >> 3]);
     } else {
       rotate_tile(Rt(buf), s.sn, s.cs);
       scale_x_tile(Xt(buf), Xt(buf), rowscale);
