@@ -40,7 +40,8 @@ GDN_FLOPS_PER_TOKEN_HEAD = 3 * 182955    # fwd + 2x for bwd
 M3_BYTES_PER_TOKEN = 23168
 M3_FLOPS_PER_TOKEN = 5.50e6
 # DRAM traffic per unit from the committed ncu captures (profiles/): dram__bytes_read.sum + dram__bytes_write.sum
-GDN_NCU_TRAFFIC_PER_CHUNK = 1051.4e6 / 2048    # B=2 capture: 1051.4 MB over 2048 (batch, head, chunk) units
+GDN_NCU_TRAFFIC_PER_CHUNK = 1286.2e6 / 2048    # B=2 capture: 1286.2 MB over 2048 (batch, head, chunk) units
+M3_NCU_TRAFFIC_PER_CHUNK = 746.4e6 / 4096      # B=2 capture: 746.4 MB over 2 x 32 x 64 (batch, head, chunk) units
 DECODE_NCU_TRAFFIC_PER_TILE = 482.8e6 / 4096   # full-size capture: 482.8 MB over 256 x 16 (sequence, head) tiles
 
 
@@ -261,7 +262,8 @@ def main():
         alg_bytes = units * M3_BYTES_PER_TOKEN
         alg_flops = units * M3_FLOPS_PER_TOKEN
         bound = "hbm"
-        traffic, traffic_note = None, "not captured"
+        traffic = B * NH * ((T + 63) // 64) * M3_NCU_TRAFFIC_PER_CHUNK if (P, N) == (64, 128) else None
+        traffic_note = "ncu capture at B=2 scaled by the number of (batch, head, chunk) units"
         margs = [d[k] for k in ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")]
 
         def step():
