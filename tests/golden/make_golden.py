@@ -175,9 +175,52 @@ def mamba3_torch_scan(ref: Path):
     print("mamba3_torch_scan.npz", sorted({k.split('_')[0] for k in out}))
 
 
+
+def gdn_block_stages(ref: Path):
+    """Pre- and post-scan stages of the gated_deltanet block (arch/blocks_gated_deltanet.go:207-343) through the
+    reference's own scalar helpers (short_conv_1d, rms_norm_rows, silu, softplus, sigmoid of
+    experiments/gated_deltanet_reference/generate_fixtures.py), on its fixture and on seeded inputs."""
+    mod = _load(ref / "experiments/gated_deltanet_reference/generate_fixtures.py", "ref_gdn_fix2")
+    rng = random.Random(4321)
+    cases = []
+    for (B, T, H, Dk, Dv) in [(1, 3, 1, 2, 3), (2, 7, 2, 8, 16), (1, 40, 3, 16, 8)]:
+        def vec(n, lo=-1.0, hi=1.0):
+            return [rng.uniform(lo, hi) for _ in range(n)]
+        Ck, Cv = H * Dk, H * Dv
+        qp, kp, vp = vec(B * T * Ck, -2, 2), vec(B * T * Ck, -2, 2), vec(B * T * Cv, -2, 2)
+        wq, wk, wv = vec(4 * Ck, -0.5, 0.5), vec(4 * Ck, -0.5, 0.5), vec(4 * Cv, -0.5, 0.5)
+        a_raw, b_raw = vec(B * T * H, -3, 3), vec(B * T * H, -3, 3)
+        a_log, dt_bias = vec(H, -1, 1), vec(H, -0.5, 0.5)
+        q_seq = mod.short_conv_1d(qp, wq, B, T, Ck)
+        k_seq = mod.short_conv_1d(kp, wk, B, T, Ck)
+        v_seq = mod.short_conv_1d(vp, wv, B, T, Cv)
+        q_unit = mod.rms_norm_rows(q_seq, B * T * H, Dk, [1.0] * Dk, 1e-6)
+        k_unit = mod.rms_norm_rows(k_seq, B * T * H, Dk, [1.0] * Dk, 1e-6)
+        inv = 1.0 / math.sqrt(Dk)
+        q = [x * inv * inv for x in q_unit]
+        k = [x * inv for x in k_unit]
+        gate, beta = [], []
+        for i, x in enumerate(a_raw):
+            h = i % H
+            dt = mod.softplus(x + dt_bias[h])
+            gate.append(math.exp(-dt * math.exp(a_log[h])))
+        beta = [mod.sigmoid(x) for x in b_raw]
+        # post stage
+        o, z, onw = vec(B * T * H * Dv, -2, 2), vec(B * T * H * Dv, -3, 3), vec(Dv, 0.5, 1.5)
+        y_norm = mod.rms_norm_rows(o, B * T * H, Dv, onw, 1e-5)
+        y = [a * mod.silu(b) for a, b in zip(y_norm, z)]
+        cases.append(dict(B=B, T=T, H=H, Dk=Dk, Dv=Dv, q_proj=qp, k_proj=kp, v_proj=vp, conv_q=wq, conv_k=wk, conv_v=wv,
+                          a_raw=a_raw, b_raw=b_raw, a_log=a_log, dt_bias=dt_bias, q=q, k=k, v=v_seq, beta=beta, gate=gate,
+                          o=o, z=z, o_norm=onw, y=y))
+    (HERE / "gdn_block_stages.json").write_text(json.dumps(dict(
+        cases=cases, source="helpers of experiments/gated_deltanet_reference/generate_fixtures.py composed as in "
+                            "fixture() / arch/blocks_gated_deltanet.go:207-343, python random.Random(4321) inputs")))
+    print("gdn_block_stages.json:", len(cases), "cases")
+
 def main():
     ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     gdn_block_fixture(ref)
+    gdn_block_stages(ref)
     gdn_torch_recurrence(ref)
     gdn_go_test_inputs()
     mamba3_block_fixture(ref)

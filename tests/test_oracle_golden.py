@@ -123,3 +123,21 @@ def test_mamba3_torch_scan_and_vjp(tag):
         err = torch.max(torch.abs(closed[name] - gr)).item()
         scale = max(1.0, torch.max(torch.abs(gr)).item())
         assert err / scale < 1e-10, (name, err)
+
+
+def test_gdn_block_stages_match_reference_helpers():
+    """oracle.gdn_block against vectors from the reference's own scalar block helpers."""
+    from oracle import gdn_block
+    data = json.load(open(os.path.join(G, "gdn_block_stages.json")))
+    for c in data["cases"]:
+        B, T, H, Dk, Dv = (c[k] for k in ("B", "T", "H", "Dk", "Dv"))
+        t = lambda name, *shape: torch.tensor(c[name], dtype=torch.float64).reshape(*shape)
+        q, k, v, beta, gate = gdn_block.block_pre(
+            t("q_proj", B, T, H * Dk), t("k_proj", B, T, H * Dk), t("v_proj", B, T, H * Dv), t("conv_q", 4, H * Dk),
+            t("conv_k", 4, H * Dk), t("conv_v", 4, H * Dv), t("a_raw", B, T, H), t("b_raw", B, T, H), t("a_log", H),
+            t("dt_bias", H), H, Dk, Dv)
+        for got, name, shape in ((q, "q", (B, T, H, Dk)), (k, "k", (B, T, H, Dk)), (v, "v", (B, T, H, Dv)),
+                                 (beta, "beta", (B, T, H)), (gate, "gate", (B, T, H))):
+            assert (got - t(name, *shape)).abs().max().item() < 1e-12, name
+        y = gdn_block.block_post(t("o", B, T, H, Dv), t("z", B, T, H * Dv), t("o_norm", Dv))
+        assert (y - t("y", B, T, H * Dv)).abs().max().item() < 1e-12
