@@ -155,6 +155,48 @@ MXB_API mxb_status mxb_gdn_decode_step(const mxb_gdn_desc* d, float* state, cons
                                const float* gate, void* out, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Element-wise stages of the gated_deltanet block on either side of the scan
+ * (emitGatedDeltaNetDeltaIR, arch/blocks_gated_deltanet.go:207-343; the 4-tap
+ * causal convolution is emitGatedDeltaNetShortConv1D, :345-368).  They replace
+ * the chain of MatMul-free IR ops between the projections and the scan (Full /
+ * Slice / Concat / Mul / Add / SiLU, RMSNorm, ScalarMul, Softplus, Exp, Sigmoid)
+ * and between the scan and the output projection (RMSNorm, SiLU, Mul).  The
+ * projections themselves are matrix products and stay with the caller.
+ *
+ * desc: B, T, H, Dk, Dv (multiples of 8, <= 128), io_dtype (q_proj .. v, o, z, y
+ * and their gradients), gate_is_log (gate is produced / its gradient taken as
+ * log gate, the form mxb_gdn_fwd accepts with the same bit).  chunk and flags are
+ * ignored.  Convolution weights [4, C] (tap j multiplies x[t-j]), a_raw, b_raw,
+ * beta, gate [B,T,H], A_log, dt_bias [H], o_norm [Dv] are float32.
+ *   pre   q = RMSNorm(SiLU(conv(q_proj)), 1, 1e-6) / Dk          [B,T,H,Dk]
+ *         k = RMSNorm(SiLU(conv(k_proj)), 1, 1e-6) / sqrt(Dk)    [B,T,H,Dk]
+ *         v = SiLU(conv(v_proj))                                 [B,T,H,Dv]
+ *         gate = exp(-softplus(a_raw + dt_bias) exp(A_log)), beta = sigmoid(b_raw)
+ *   post  y = RMSNorm(o, o_norm, 1e-5) SiLU(z)                   [B,T,H*Dv]
+ * The backward entry points return every gradient; sums over (batch, step) go
+ * through partial rows in the workspace in a fixed order.
+ * ---------------------------------------------------------------------- */
+MXB_API size_t mxb_gdn_block_workspace_bytes(const mxb_gdn_desc* d);
+MXB_API mxb_status mxb_gdn_block_pre_fwd(const mxb_gdn_desc* d, const void* q_proj, const void* k_proj,
+                                 const void* v_proj, const float* conv_q, const float* conv_k,
+                                 const float* conv_v, const float* a_raw, const float* b_raw,
+                                 const float* a_log, const float* dt_bias, void* q, void* k, void* v,
+                                 float* beta, float* gate, void* stream);
+MXB_API mxb_status mxb_gdn_block_pre_bwd(const mxb_gdn_desc* d, const void* q_proj, const void* k_proj,
+                                 const void* v_proj, const float* conv_q, const float* conv_k,
+                                 const float* conv_v, const float* a_raw, const float* b_raw,
+                                 const float* a_log, const float* dt_bias, const void* dq, const void* dk,
+                                 const void* dv, const float* dbeta, const float* dgate, void* dq_proj,
+                                 void* dk_proj, void* dv_proj, float* dconv_q, float* dconv_k,
+                                 float* dconv_v, float* da_raw, float* db_raw, float* da_log,
+                                 float* ddt_bias, void* workspace, size_t workspace_bytes, void* stream);
+MXB_API mxb_status mxb_gdn_block_post_fwd(const mxb_gdn_desc* d, const void* o, const void* z,
+                                  const float* o_norm, void* y, void* stream);
+MXB_API mxb_status mxb_gdn_block_post_bwd(const mxb_gdn_desc* d, const void* o, const void* z,
+                                  const float* o_norm, const void* dy, void* d_o, void* dz,
+                                  float* do_norm, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------
  * Mamba-3 exponential-trapezoidal selective scan.  IntParams of
  * OP_MAMBA3_SELECTIVE_SCAN are [B,T,D,N,G(,chunk)] (arch/ir.go:541-553).
  * ---------------------------------------------------------------------- */

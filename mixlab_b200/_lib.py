@@ -53,6 +53,11 @@ EXPORTS = {
     "mxb_gdn_fwd_static_scratch": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 9),
     "mxb_gdn_device_status": (C.c_int32, [_P, C.POINTER(C.c_int32)]),
     "mxb_gdn_decode_step": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 8),
+    "mxb_gdn_block_workspace_bytes": (C.c_size_t, [C.POINTER(GdnDesc)]),
+    "mxb_gdn_block_pre_fwd": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 16),
+    "mxb_gdn_block_pre_bwd": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 26 + [C.c_size_t, _P]),
+    "mxb_gdn_block_post_fwd": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 5),
+    "mxb_gdn_block_post_bwd": (C.c_int32, [C.POINTER(GdnDesc)] + [_P] * 8 + [C.c_size_t, _P]),
     "mxb_mamba3_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Mamba3Desc)]),
     "mxb_mamba3_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(Mamba3Desc)]),
     "mxb_mamba3_fwd": (C.c_int32, [C.POINTER(Mamba3Desc)] + [_P] * 9 + [C.c_size_t, _P]),

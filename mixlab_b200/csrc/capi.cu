@@ -79,6 +79,17 @@ mxb_status gdn_tc_bwd(const mxb_gdn_desc*, const void*, const void*, const void*
                       const float*, const float*, const void*, const float*, void*, void*, void*,
                       float*, float*, float*, void*, cudaStream_t);
 mxb_status umma_selftest(const void*, uint32_t, const void*, uint32_t, const uint32_t*, float*, int*, cudaStream_t);
+bool gdn_block_supported(const mxb_gdn_desc*);
+size_t gdn_block_workspace_bytes(const mxb_gdn_desc*);
+mxb_status gdn_block_pre_fwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*, const float*,
+                             const float*, const float*, const float*, const float*, const float*, void*, void*, void*,
+                             float*, float*, cudaStream_t);
+mxb_status gdn_block_pre_bwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*, const float*,
+                             const float*, const float*, const float*, const float*, const float*, const void*,
+                             const void*, const void*, const float*, const float*, void*, void*, void*, float*, float*,
+                             float*, float*, float*, float*, float*, void*, cudaStream_t);
+mxb_status gdn_block_post(const mxb_gdn_desc*, const void*, const void*, const float*, void*, const void*, void*, void*,
+                          float*, void*, cudaStream_t);
 bool mamba3_supported(const mxb_mamba3_desc*);
 size_t mamba3_workspace_bytes(const mxb_mamba3_desc*, bool bwd);
 mxb_status mamba3_fwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*,
@@ -221,6 +232,75 @@ mxb_status mxb_gdn_decode_step(const mxb_gdn_desc* d, float* state, const void* 
   if (!state || !q || !k || !v || !beta || !gate || !out) return MXB_ERR_INVALID_ARGUMENT;
   if (!aligned16(state)) return MXB_ERR_ALIGNMENT;
   return gdn_decode_dispatch(d, state, q, k, v, beta, gate, out, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------- gated_deltanet block stages
+static mxb_status check_block_desc(const mxb_gdn_desc* d) {
+  if (!d) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->B <= 0 || d->T <= 0 || d->H <= 0 || d->Dk <= 0 || d->Dv <= 0) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->io_dtype != MXB_F32 && d->io_dtype != MXB_BF16) return MXB_ERR_INVALID_ARGUMENT;
+  if (!gdn_block_supported(d)) return MXB_ERR_UNSUPPORTED;
+  return MXB_OK;
+}
+size_t mxb_gdn_block_workspace_bytes(const mxb_gdn_desc* d) {
+  return check_block_desc(d) == MXB_OK ? gdn_block_workspace_bytes(d) : 0;
+}
+mxb_status mxb_gdn_block_pre_fwd(const mxb_gdn_desc* d, const void* q_proj, const void* k_proj, const void* v_proj,
+                                 const float* conv_q, const float* conv_k, const float* conv_v, const float* a_raw,
+                                 const float* b_raw, const float* a_log, const float* dt_bias, void* q, void* k,
+                                 void* v, float* beta, float* gate, void* stream) {
+  mxb_status s = check_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (!q_proj || !k_proj || !v_proj || !conv_q || !conv_k || !conv_v || !a_raw || !b_raw || !a_log || !dt_bias || !q ||
+      !k || !v || !beta || !gate)
+    return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(q_proj) || !aligned16(k_proj) || !aligned16(v_proj) || !aligned16(q) || !aligned16(k) || !aligned16(v) ||
+      !aligned16(conv_q) || !aligned16(conv_k) || !aligned16(conv_v))
+    return MXB_ERR_ALIGNMENT;
+  return gdn_block_pre_fwd(d, q_proj, k_proj, v_proj, conv_q, conv_k, conv_v, a_raw, b_raw, a_log, dt_bias, q, k, v, beta,
+                           gate, static_cast<cudaStream_t>(stream));
+}
+mxb_status mxb_gdn_block_pre_bwd(const mxb_gdn_desc* d, const void* q_proj, const void* k_proj, const void* v_proj,
+                                 const float* conv_q, const float* conv_k, const float* conv_v, const float* a_raw,
+                                 const float* b_raw, const float* a_log, const float* dt_bias, const void* dq,
+                                 const void* dk, const void* dv, const float* dbeta, const float* dgate, void* dq_proj,
+                                 void* dk_proj, void* dv_proj, float* dconv_q, float* dconv_k, float* dconv_v,
+                                 float* da_raw, float* db_raw, float* da_log, float* ddt_bias, void* workspace,
+                                 size_t workspace_bytes, void* stream) {
+  mxb_status s = check_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (!q_proj || !k_proj || !v_proj || !conv_q || !conv_k || !conv_v || !a_raw || !b_raw || !a_log || !dt_bias || !dq ||
+      !dk || !dv || !dbeta || !dgate || !dq_proj || !dk_proj || !dv_proj || !dconv_q || !dconv_k || !dconv_v || !da_raw ||
+      !db_raw || !da_log || !ddt_bias || !workspace)
+    return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(q_proj) || !aligned16(k_proj) || !aligned16(v_proj) || !aligned16(dq) || !aligned16(dk) || !aligned16(dv) ||
+      !aligned16(dq_proj) || !aligned16(dk_proj) || !aligned16(dv_proj) || !aligned16(conv_q) || !aligned16(conv_k) ||
+      !aligned16(conv_v) || !aligned16(workspace))
+    return MXB_ERR_ALIGNMENT;
+  if (workspace_bytes < gdn_block_workspace_bytes(d)) return MXB_ERR_WORKSPACE;
+  return gdn_block_pre_bwd(d, q_proj, k_proj, v_proj, conv_q, conv_k, conv_v, a_raw, b_raw, a_log, dt_bias, dq, dk, dv, dbeta,
+                           dgate, dq_proj, dk_proj, dv_proj, dconv_q, dconv_k, dconv_v, da_raw, db_raw, da_log, ddt_bias,
+                           workspace, static_cast<cudaStream_t>(stream));
+}
+mxb_status mxb_gdn_block_post_fwd(const mxb_gdn_desc* d, const void* o, const void* z, const float* o_norm, void* y,
+                                  void* stream) {
+  mxb_status s = check_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (!o || !z || !o_norm || !y) return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(o) || !aligned16(z) || !aligned16(y) || !aligned16(o_norm)) return MXB_ERR_ALIGNMENT;
+  return gdn_block_post(d, o, z, o_norm, y, nullptr, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+mxb_status mxb_gdn_block_post_bwd(const mxb_gdn_desc* d, const void* o, const void* z, const float* o_norm,
+                                  const void* dy, void* d_o, void* dz, float* do_norm, void* workspace,
+                                  size_t workspace_bytes, void* stream) {
+  mxb_status s = check_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (!o || !z || !o_norm || !dy || !d_o || !dz || !do_norm || !workspace) return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(o) || !aligned16(z) || !aligned16(dy) || !aligned16(d_o) || !aligned16(dz) || !aligned16(o_norm) ||
+      !aligned16(workspace))
+    return MXB_ERR_ALIGNMENT;
+  if (workspace_bytes < gdn_block_workspace_bytes(d)) return MXB_ERR_WORKSPACE;
+  return gdn_block_post(d, o, z, o_norm, nullptr, dy, d_o, dz, do_norm, workspace, static_cast<cudaStream_t>(stream));
 }
 
 static mxb_status check_m3_desc(const mxb_mamba3_desc* d) {

@@ -132,6 +132,83 @@ def gated_delta_decode_step(state, q, k, v, beta, gate, *, gate_is_log=False, ou
     return out
 
 
+# ---------------------------------------------------------------- gated_deltanet block stages
+def _block_desc(q_proj, H, Dk, Dv, gate_is_log):
+    B, T, _ = q_proj.shape
+    return GdnDesc(B, T, H, Dk, Dv, 64, _io(q_proj), int(bool(gate_is_log)), 0)
+
+
+def gdn_block_pre(q_proj, k_proj, v_proj, conv_q, conv_k, conv_v, a_raw, b_raw, a_log, dt_bias, H, Dk, Dv, *,
+                  gate_is_log=False):
+    """Convolution + SiLU + L2-norm / gate / beta stage in front of the scan.  q_proj, k_proj [B,T,H*Dk],
+    v_proj [B,T,H*Dv]; returns q, k [B,T,H,Dk], v [B,T,H,Dv] (I/O dtype), beta, gate [B,T,H] fp32."""
+    _require_cuda(q_proj, k_proj, v_proj, conv_q, conv_k, conv_v, a_raw, b_raw, a_log, dt_bias)
+    l = _lib.lib()
+    d = _block_desc(q_proj, H, Dk, Dv, gate_is_log)
+    B, T = d.B, d.T
+    q = torch.empty(B, T, H, Dk, dtype=q_proj.dtype, device=q_proj.device)
+    k = torch.empty_like(q)
+    v = torch.empty(B, T, H, Dv, dtype=q_proj.dtype, device=q_proj.device)
+    beta = torch.empty(B, T, H, dtype=torch.float32, device=q_proj.device)
+    gate = torch.empty_like(beta)
+    _lib.check(l.mxb_gdn_block_pre_fwd(C.byref(d), _ptr(q_proj), _ptr(k_proj), _ptr(v_proj), _ptr(_f32(conv_q, "conv_q")),
+                                       _ptr(_f32(conv_k, "conv_k")), _ptr(_f32(conv_v, "conv_v")),
+                                       _ptr(_f32(a_raw, "a_raw")), _ptr(_f32(b_raw, "b_raw")), _ptr(_f32(a_log, "a_log")),
+                                       _ptr(_f32(dt_bias, "dt_bias")), _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(gate),
+                                       _stream()), "mxb_gdn_block_pre_fwd")
+    return q, k, v, beta, gate
+
+
+def gdn_block_pre_backward(q_proj, k_proj, v_proj, conv_q, conv_k, conv_v, a_raw, b_raw, a_log, dt_bias, H, Dk, Dv,
+                           dq, dk, dv, dbeta, dgate, *, gate_is_log=False):
+    """Gradients of gdn_block_pre: dict(dq_proj, dk_proj, dv_proj, dconv_q, dconv_k, dconv_v, da_raw, db_raw, da_log,
+    ddt_bias)."""
+    _require_cuda(q_proj, k_proj, v_proj, conv_q, conv_k, conv_v, a_raw, b_raw, a_log, dt_bias, dq, dk, dv, dbeta, dgate)
+    l = _lib.lib()
+    d = _block_desc(q_proj, H, Dk, Dv, gate_is_log)
+    dqp, dkp, dvp = torch.empty_like(q_proj), torch.empty_like(k_proj), torch.empty_like(v_proj)
+    f32 = dict(dtype=torch.float32, device=q_proj.device)
+    dcq, dck, dcv = torch.empty(4, H * Dk, **f32), torch.empty(4, H * Dk, **f32), torch.empty(4, H * Dv, **f32)
+    da, db = torch.empty(d.B, d.T, H, **f32), torch.empty(d.B, d.T, H, **f32)
+    dal, dbias = torch.empty(H, **f32), torch.empty(H, **f32)
+    ws = workspace(l.mxb_gdn_block_workspace_bytes(C.byref(d)), q_proj.device)
+    _lib.check(l.mxb_gdn_block_pre_bwd(C.byref(d), _ptr(q_proj), _ptr(k_proj), _ptr(v_proj), _ptr(_f32(conv_q, "conv_q")),
+                                       _ptr(_f32(conv_k, "conv_k")), _ptr(_f32(conv_v, "conv_v")),
+                                       _ptr(_f32(a_raw, "a_raw")), _ptr(_f32(b_raw, "b_raw")), _ptr(_f32(a_log, "a_log")),
+                                       _ptr(_f32(dt_bias, "dt_bias")), _ptr(dq), _ptr(dk), _ptr(dv),
+                                       _ptr(_f32(dbeta, "dbeta")), _ptr(_f32(dgate, "dgate")), _ptr(dqp), _ptr(dkp),
+                                       _ptr(dvp), _ptr(dcq), _ptr(dck), _ptr(dcv), _ptr(da), _ptr(db), _ptr(dal),
+                                       _ptr(dbias), _ptr(ws), ws.numel(), _stream()), "mxb_gdn_block_pre_bwd")
+    return dict(dq_proj=dqp, dk_proj=dkp, dv_proj=dvp, dconv_q=dcq, dconv_k=dck, dconv_v=dcv, da_raw=da, db_raw=db,
+                da_log=dal, ddt_bias=dbias)
+
+
+def gdn_block_post(o, z, o_norm):
+    """y = RMSNorm(o, o_norm, 1e-5) * SiLU(z).  o [B,T,H,Dv], z [B,T,H*Dv] -> y [B,T,H*Dv]."""
+    _require_cuda(o, z, o_norm)
+    l = _lib.lib()
+    B, T, H, Dv = o.shape
+    d = GdnDesc(B, T, H, 8, Dv, 64, _io(o), 0, 0)
+    y = torch.empty_like(z)
+    _lib.check(l.mxb_gdn_block_post_fwd(C.byref(d), _ptr(o), _ptr(z), _ptr(_f32(o_norm, "o_norm")), _ptr(y), _stream()),
+               "mxb_gdn_block_post_fwd")
+    return y
+
+
+def gdn_block_post_backward(o, z, o_norm, dy):
+    """Gradients of gdn_block_post: dict(do, dz, do_norm)."""
+    _require_cuda(o, z, o_norm, dy)
+    l = _lib.lib()
+    B, T, H, Dv = o.shape
+    d = GdnDesc(B, T, H, 8, Dv, 64, _io(o), 0, 0)
+    d_o, dz = torch.empty_like(o), torch.empty_like(z)
+    dw = torch.empty(Dv, dtype=torch.float32, device=o.device)
+    ws = workspace(l.mxb_gdn_block_workspace_bytes(C.byref(d)), o.device)
+    _lib.check(l.mxb_gdn_block_post_bwd(C.byref(d), _ptr(o), _ptr(z), _ptr(_f32(o_norm, "o_norm")), _ptr(dy), _ptr(d_o),
+                                        _ptr(dz), _ptr(dw), _ptr(ws), ws.numel(), _stream()), "mxb_gdn_block_post_bwd")
+    return dict(do=d_o, dz=dz, do_norm=dw)
+
+
 def mamba3_desc(x, b, nheads, flags=0) -> Mamba3Desc:
     B, T, D = x.shape
     G, N = b.shape[-2], b.shape[-1]
