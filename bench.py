@@ -33,12 +33,16 @@ WORKLOADS = {
     "gdn_train": dict(B=8, T=4096, H=16, Dk=128, Dv=128, chunk=64),
     "gdn_decode": dict(N=256, H=16, Dk=128, Dv=128, tokens_per_step=64),
     "mamba3_train": dict(B=8, T=4096, nheads=32, headdim=64, N=128, G=1),
+    "gdn_block": dict(B=8, T=4096, H=16, Dk=128, Dv=128),
 }
 # Algorithmic work per unit (stated in DESIGN.md).
 GDN_BYTES_PER_TOKEN_HEAD = 2840          # fwd 1032 + bwd read 1032 + bwd write 776
 GDN_FLOPS_PER_TOKEN_HEAD = 3 * 182955    # fwd + 2x for bwd
 M3_BYTES_PER_TOKEN = 23168
 M3_FLOPS_PER_TOKEN = 5.50e6
+# block stages around the scan, fwd+bwd, bf16: pre fwd 3 in + 3 out, pre bwd 6 in + 3 out, post fwd 2 in + 1 out,
+# post bwd 3 in + 2 out = 23 tensors of 128 channels x 2 bytes, plus the fp32 per-head scalars
+GDN_BLOCK_BYTES_PER_TOKEN_HEAD = 23 * 128 * 2 + 10 * 4
 # DRAM traffic per unit from the committed ncu captures (profiles/): dram__bytes_read.sum + dram__bytes_write.sum
 GDN_NCU_TRAFFIC_PER_CHUNK = 1286.2e6 / 2048    # B=2 capture: 1286.2 MB over 2048 (batch, head, chunk) units
 M3_NCU_TRAFFIC_PER_CHUNK = 746.4e6 / 4096      # B=2 capture: 746.4 MB over 2 x 32 x 64 (batch, head, chunk) units
@@ -247,6 +251,35 @@ def main():
 
         cfg = {"workload": "gdn_decode", **w, "io": "bf16", "state": "fp32 268 MB (exceeds L2)",
                "inputs": "ring of 16 pre-generated token inputs"}
+    elif args.workload == "gdn_block":
+        w = dict(WORKLOADS["gdn_block"])
+        if args.batch > 0:
+            w["B"] = args.batch
+        B, T, H, K, V = w["B"], w["T"], w["H"], w["Dk"], w["Dv"]
+        g = torch.Generator().manual_seed(4000 + rank)
+        rn = lambda *shape: torch.randn(*shape, generator=g)
+        io = torch.bfloat16
+        d = dict(qp=rn(B, T, H * K).to(io), kp=rn(B, T, H * K).to(io), vp=rn(B, T, H * V).to(io),
+                 cq=0.4 * rn(4, H * K), ck=0.4 * rn(4, H * K), cv=0.4 * rn(4, H * V), a=rn(B, T, H), b=rn(B, T, H),
+                 al=0.5 * rn(H), bias=0.3 * rn(H), o=rn(B, T, H, V).to(io), z=rn(B, T, H * V).to(io), wn=1 + 0.2 * rn(V),
+                 dq=rn(B, T, H, K).to(io), dk=rn(B, T, H, K).to(io), dv=rn(B, T, H, V).to(io), db=rn(B, T, H),
+                 dg=rn(B, T, H), dy=rn(B, T, H * V).to(io))
+        d = {k: v.to(dev) for k, v in d.items()}
+        units = B * T
+        metric, unit, dtype = "gdn_block_stages_fwd_bwd_tokens_per_s", "tokens/s", "f32"
+        alg_bytes = units * H * GDN_BLOCK_BYTES_PER_TOKEN_HEAD
+        alg_flops = 0.0
+        bound = "hbm"
+        traffic, traffic_note = None, "not captured"
+        pre = [d[k] for k in ("qp", "kp", "vp", "cq", "ck", "cv", "a", "b", "al", "bias")]
+
+        def step():
+            ops.gdn_block_pre(*pre, H, K, V, gate_is_log=True)
+            ops.gdn_block_post(d["o"], d["z"], d["wn"])
+            ops.gdn_block_post_backward(d["o"], d["z"], d["wn"], d["dy"])
+            ops.gdn_block_pre_backward(*pre, H, K, V, d["dq"], d["dk"], d["dv"], d["db"], d["dg"], gate_is_log=True)
+
+        cfg = {"workload": "gdn_block", **w, "io": "bf16", "what": "conv+SiLU+L2-norm/gate/beta and norm x gate, fwd+bwd"}
     else:
         w = dict(WORKLOADS["mamba3_train"])
         if args.batch > 0:

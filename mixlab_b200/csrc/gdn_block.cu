@@ -18,7 +18,7 @@ namespace mxb {
 namespace blk {
 
 using bf16 = __nv_bfloat16;
-constexpr int kRun = 8;       // steps per lane group
+constexpr int kRun = 16;      // steps per lane group (3 more are recomputed as halo in the backward)
 constexpr int kGroups = 8;    // lane groups per CTA (128 threads)
 constexpr int kTile = kRun * kGroups;
 
@@ -63,11 +63,18 @@ __device__ __forceinline__ float group_sum(float v) {
   for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o);
   return v;
 }
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
-__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
-__device__ __forceinline__ float dsilu_f(float x) {
-  const float s = sigmoid_f(x);
-  return s * (1.f + x * (1.f - s));
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// sigmoid for the streams: bf16 I/O takes tanh.approx (one MUFU op, relative error ~5e-4, far below the rounding
+// of the stored result); fp32 I/O takes exp + reciprocal (a few ulp)
+template <typename IO>
+__device__ __forceinline__ float sigmoid_io(float x) {
+  return sigmoid_f(x);
+}
+template <>
+__device__ __forceinline__ float sigmoid_io<__nv_bfloat16>(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
 }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 
@@ -95,7 +102,11 @@ __global__ void __launch_bounds__(128) gdn_block_pre_fwd_kernel(BlockP p, PreArg
   const int t0 = tile * kTile + grp * kRun;
   const IO* x = a.x[which] + (size_t)b * p.T * C + ch;
   IO* y = a.y[which] + (size_t)b * p.T * C + ch;
-  float w[4][8];
+  float w[4][8];  // zero for the lanes beyond D: their zero results take part in the row sums
+#pragma unroll
+  for (int tap = 0; tap < 4; ++tap)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) w[tap][c] = 0.f;
   if (act) {
 #pragma unroll
     for (int tap = 0; tap < 4; ++tap) load8<float>(a.w[which] + tap * C + ch, w[tap]);
@@ -121,7 +132,7 @@ __global__ void __launch_bounds__(128) gdn_block_pre_fwd_kernel(BlockP p, PreArg
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const float acc = w[0][c] * x0[c] + w[1][c] * x1[c] + w[2][c] * x2[c] + w[3][c] * x3[c];
-      s[c] = in ? silu_f(acc) : 0.f;
+      s[c] = acc * sigmoid_io<IO>(acc);  // rows past T are computed on zero-filled inputs and not stored
       ss = fmaf(s[c], s[c], ss);
     }
     if (which < 2) {
@@ -193,11 +204,14 @@ __global__ void __launch_bounds__(128) gdn_block_pre_bwd_kernel(BlockP p, PreArg
 #pragma unroll
     for (int c = 0; c < 8; ++c) { x0[c] = 0.f; g[c] = 0.f; }
     if (in) { load8<IO>(x + (size_t)t * C, x0); load8<IO>(dy + (size_t)t * C, g); }
-    float acc[8], sv[8], ss = 0.f, dot = 0.f;
+    // one sigmoid per element gives SiLU and its derivative; rows past T have zero dy, hence zero ds
+    float sv[8], dsl[8], ss = 0.f, dot = 0.f;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      acc[c] = w[0][c] * x0[c] + w[1][c] * x1[c] + w[2][c] * x2[c] + w[3][c] * x3[c];
-      sv[c] = in ? silu_f(acc[c]) : 0.f;
+      const float acc = w[0][c] * x0[c] + w[1][c] * x1[c] + w[2][c] * x2[c] + w[3][c] * x3[c];
+      const float sg = sigmoid_io<IO>(acc);
+      sv[c] = acc * sg;
+      dsl[c] = fmaf(sv[c], 1.f - sg, sg);  // sg (1 + acc (1 - sg))
       ss = fmaf(sv[c], sv[c], ss);
       dot = fmaf(sv[c], g[c], dot);
     }
@@ -210,7 +224,7 @@ __global__ void __launch_bounds__(128) gdn_block_pre_bwd_kernel(BlockP p, PreArg
       for (int c = 0; c < 8; ++c) g[c] = scale * rn * (g[c] - sv[c] * k2);
     }
 #pragma unroll
-    for (int c = 0; c < 8; ++c) ds[c] = in ? g[c] * dsilu_f(acc[c]) : 0.f;
+    for (int c = 0; c < 8; ++c) ds[c] = g[c] * dsl[c];
     if (r < kRun) {  // this step belongs to the run: its share of the weight gradient
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
@@ -251,14 +265,23 @@ __global__ void __launch_bounds__(128) gdn_block_pre_bwd_kernel(BlockP p, PreArg
   }
 }
 
-// out[j] = sum over rows of part[row][j], fixed order; grid ceil(n / 256)
+// out[j] = sum over rows of part[row][j] in a fixed order: a CTA owns 32 columns, its 8 warps take every 8th row
+// (coalesced 128-byte reads, 8 loads in flight per column), then the 8 slices are added in order.  grid ceil(n / 32)
 __global__ void __launch_bounds__(256) gdn_block_colsum_kernel(const float* __restrict__ part, int rows, int n,
                                                                float* __restrict__ out) {
-  const int j = blockIdx.x * 256 + threadIdx.x;
-  if (j >= n) return;
+  __shared__ float red[8][32];
+  const int j = blockIdx.x * 32 + (threadIdx.x & 31), slice = threadIdx.x >> 5;
   float s = 0.f;
-  for (int r = 0; r < rows; ++r) s += part[(size_t)r * n + j];
-  out[j] = s;
+  if (j < n)
+    for (int r = slice; r < rows; r += 8) s += part[(size_t)r * n + j];
+  red[slice][threadIdx.x & 31] = s;
+  __syncthreads();
+  if (threadIdx.x < 32 && j < n) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][threadIdx.x];
+    out[j] = t;
+  }
 }
 
 // gate / beta backward: one CTA per head walks all (b, t); the two per-head sums (A_log, dt_bias) in a fixed order
@@ -299,6 +322,46 @@ __global__ void __launch_bounds__(256) gdn_block_gate_bwd_kernel(BlockP p, const
   }
 }
 
+// The same with every (b, t, h) element on its own thread, coalesced, for head counts that divide 256: a thread's
+// head is then tid % H for every element it touches.  Per-CTA partial sums [2][G][H] -> fixed-order second pass.
+constexpr int kGatePerCta = 256 * 16;
+__global__ void __launch_bounds__(256) gdn_block_gate_bwd_flat_kernel(BlockP p, const float* __restrict__ a_raw,
+                                                                      const float* __restrict__ b_raw,
+                                                                      const float* __restrict__ a_log,
+                                                                      const float* __restrict__ dt_bias,
+                                                                      const float* __restrict__ dbeta,
+                                                                      const float* __restrict__ dgate,
+                                                                      float* __restrict__ da_raw,
+                                                                      float* __restrict__ db_raw,
+                                                                      float* __restrict__ part) {
+  __shared__ float red[2][256];
+  const int tid = threadIdx.x, h = tid % p.H;
+  const float A = expf(a_log[h]), bias = dt_bias[h];
+  const size_t n = (size_t)p.B * p.T * p.H, base = (size_t)blockIdx.x * kGatePerCta;
+  const size_t end = base + kGatePerCta < n ? base + kGatePerCta : n;
+  float s_alog = 0.f, s_bias = 0.f;
+  for (size_t idx = base + tid; idx < end; idx += 256) {
+    const float z = a_raw[idx] + bias;
+    const float lg = -softplus_f(z) * A;
+    const float dlg = p.gate_is_log ? dgate[idx] : dgate[idx] * expf(lg);
+    const float da = -A * dlg * sigmoid_f(z);
+    da_raw[idx] = da;
+    s_bias += da;
+    s_alog = fmaf(dlg, lg, s_alog);
+    const float bt = sigmoid_f(b_raw[idx]);
+    db_raw[idx] = dbeta[idx] * bt * (1.f - bt);
+  }
+  red[0][tid] = s_alog;
+  red[1][tid] = s_bias;
+  __syncthreads();
+  if (tid < p.H) {
+    float x = 0.f, y = 0.f;
+    for (int j = tid; j < 256; j += p.H) { x += red[0][j]; y += red[1][j]; }
+    part[(size_t)blockIdx.x * p.H + tid] = x;
+    part[((size_t)gridDim.x + blockIdx.x) * p.H + tid] = y;
+  }
+}
+
 // ------------------------------------------------------------------ post
 // y = o rsqrt(mean(o^2) + 1e-5) o_norm SiLU(z); rows = (b, t, h), D = Dv; 8 rows per CTA pass
 template <typename IO>
@@ -322,7 +385,7 @@ __global__ void __launch_bounds__(128) gdn_block_post_fwd_kernel(BlockP p, const
     ss = group_sum(ss);
     const float rn = rsqrtf(ss / (float)D + 1e-5f);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) ov[c] = ov[c] * rn * w[c] * silu_f(zv[c]);
+    for (int c = 0; c < 8; ++c) ov[c] = ov[c] * rn * w[c] * zv[c] * sigmoid_io<IO>(zv[c]);
     if (act) store8<IO>(y + off, ov);
   }
 }
@@ -345,10 +408,12 @@ __global__ void __launch_bounds__(128) gdn_block_post_bwd_kernel(BlockP p, const
 #pragma unroll
     for (int c = 0; c < 8; ++c) ov[c] = zv[c] = gv[c] = 0.f;
     if (act) { load8<IO>(o + off, ov); load8<IO>(z + off, zv); load8<IO>(dy + off, gv); }
-    float ss = 0.f, dot = 0.f, g[8], sz[8];
+    float ss = 0.f, dot = 0.f, g[8], sz[8], dsz[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      sz[c] = silu_f(zv[c]);
+      const float sg = sigmoid_io<IO>(zv[c]);
+      sz[c] = zv[c] * sg;
+      dsz[c] = fmaf(sz[c], 1.f - sg, sg);
       g[c] = gv[c] * sz[c] * w[c];  // gradient at o rn
       ss = fmaf(ov[c], ov[c], ss);
       dot = fmaf(ov[c], g[c], dot);
@@ -362,7 +427,7 @@ __global__ void __launch_bounds__(128) gdn_block_post_bwd_kernel(BlockP p, const
     for (int c = 0; c < 8; ++c) {
       const float on = ov[c] * rn;
       dw[c] = fmaf(gv[c] * sz[c], on, dw[c]);
-      dzv[c] = gv[c] * w[c] * on * dsilu_f(zv[c]);
+      dzv[c] = gv[c] * w[c] * on * dsz[c];
       g[c] = rn * (g[c] - ov[c] * k2);
     }
     if (act) { store8<IO>(d_o + off, g); store8<IO>(dz + off, dzv); }
@@ -397,12 +462,17 @@ static int blk_post_ctas(const mxb_gdn_desc* d) {
   const size_t want = (rows + blk::kGroups - 1) / blk::kGroups;
   return (int)(want < 148 * 16 ? want : 148 * 16);
 }
-// backward partial rows: conv weights of q, k, v, then the norm weight
+static int blk_gate_ctas(const mxb_gdn_desc* d) {
+  const size_t n = (size_t)d->B * d->T * d->H;
+  return (int)((n + blk::kGatePerCta - 1) / blk::kGatePerCta);
+}
+// backward partial rows: conv weights of q, k, v and the per-head gate sums; or the norm weight
 size_t gdn_block_workspace_bytes(const mxb_gdn_desc* d) {
   const size_t rows = (size_t)d->B * blk_tiles(d);
   const size_t pre = rows * 4 * ((size_t)2 * d->H * d->Dk + (size_t)d->H * d->Dv) * sizeof(float);
   const size_t post = (size_t)blk_post_ctas(d) * d->Dv * sizeof(float);
-  return (pre > post ? pre : post) + 256;
+  const size_t gate = 2 * (size_t)blk_gate_ctas(d) * d->H * sizeof(float);
+  return (pre + gate > post ? pre + gate : post) + 256;
 }
 
 template <typename IO>
@@ -456,11 +526,24 @@ static mxb_status blk_pre_bwd(const mxb_gdn_desc* d, const void* qp, const void*
   for (int w = 0; w < 3; ++w) {
     const int n = (int)(4 * (w == 2 ? Cv : Ck));
     MXB_LAUNCH("gdn_block_colsum_kernel", st,
-               (blk::gdn_block_colsum_kernel<<<(n + 255) / 256, 256, 0, st>>>(a.dwp[w], (int)rows, n, outs[w])));
+               (blk::gdn_block_colsum_kernel<<<(n + 31) / 32, 256, 0, st>>>(a.dwp[w], (int)rows, n, outs[w])));
   }
-  MXB_LAUNCH("gdn_block_gate_bwd_kernel", st,
-             (blk::gdn_block_gate_bwd_kernel<<<d->H, 256, 0, st>>>(p, a_raw, b_raw, a_log, dt_bias, dbeta, dgate, da_raw,
-                                                                    db_raw, da_log, ddt_bias)));
+  if (256 % d->H == 0) {
+    const int gc = blk_gate_ctas(d);
+    float* gpart = base + rows * 4 * (2 * Ck + Cv);
+    MXB_LAUNCH("gdn_block_gate_bwd_flat_kernel", st,
+               (blk::gdn_block_gate_bwd_flat_kernel<<<gc, 256, 0, st>>>(p, a_raw, b_raw, a_log, dt_bias, dbeta, dgate,
+                                                                       da_raw, db_raw, gpart)));
+    MXB_LAUNCH("gdn_block_colsum_kernel", st,
+               (blk::gdn_block_colsum_kernel<<<(d->H + 31) / 32, 256, 0, st>>>(gpart, gc, d->H, da_log)));
+    MXB_LAUNCH("gdn_block_colsum_kernel", st,
+               (blk::gdn_block_colsum_kernel<<<(d->H + 31) / 32, 256, 0, st>>>(gpart + (size_t)gc * d->H, gc, d->H,
+                                                                                 ddt_bias)));
+  } else {
+    MXB_LAUNCH("gdn_block_gate_bwd_kernel", st,
+               (blk::gdn_block_gate_bwd_kernel<<<d->H, 256, 0, st>>>(p, a_raw, b_raw, a_log, dt_bias, dbeta, dgate,
+                                                                      da_raw, db_raw, da_log, ddt_bias)));
+  }
   return check_launch("gdn_block_pre_bwd");
 }
 mxb_status gdn_block_pre_bwd(const mxb_gdn_desc* d, const void* qp, const void* kp, const void* vp, const float* cq,
@@ -495,7 +578,7 @@ static mxb_status blk_post(const mxb_gdn_desc* d, const void* o, const void* z, 
                                                                        static_cast<const IO*>(dy), static_cast<IO*>(d_o),
                                                                        static_cast<IO*>(dz), part)));
   MXB_LAUNCH("gdn_block_colsum_kernel", st,
-             (blk::gdn_block_colsum_kernel<<<(d->Dv + 255) / 256, 256, 0, st>>>(part, ctas, d->Dv, dwn)));
+             (blk::gdn_block_colsum_kernel<<<(d->Dv + 31) / 32, 256, 0, st>>>(part, ctas, d->Dv, dwn)));
   return check_launch("gdn_block_post_bwd");
 }
 mxb_status gdn_block_post(const mxb_gdn_desc* d, const void* o, const void* z, const float* wn, void* y, const void* dy,
