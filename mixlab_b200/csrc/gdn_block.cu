@@ -165,49 +165,82 @@ __global__ void __launch_bounds__(256) gdn_block_gate_fwd_kernel(BlockP p, const
 // ------------------------------------------------------------------ pre: backward
 // Same split as the forward.  A lane group recomputes the convolution of its run and of the three steps after it
 // (their ds feeds dx of the run), keeps the last four ds in registers and emits dx three steps behind.
+// The backward keeps 4 channels per thread (a warp covers a row): its per-thread state - weights, weight-gradient
+// accumulators, three previous inputs and three previous ds per channel - would otherwise take ~180 registers and
+// leave two CTAs per SM.
+constexpr int kBwdGroups = 4;                   // warps per CTA, one run each
+constexpr int kBwdTile = kRun * kBwdGroups;
+template <typename IO>
+__device__ __forceinline__ void load4(const IO* p, float (&e)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&e)[4]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  e[0] = a.x; e[1] = a.y; e[2] = a.z; e[3] = a.w;
+}
+template <>
+__device__ __forceinline__ void load4<bf16>(const bf16* p, float (&e)[4]) {
+  const uint2 v = __ldg(reinterpret_cast<const uint2*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+  e[0] = __low2float(h[0]); e[1] = __high2float(h[0]); e[2] = __low2float(h[1]); e[3] = __high2float(h[1]);
+}
+template <typename IO>
+__device__ __forceinline__ void store4(IO* p, const float (&e)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&e)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(e[0], e[1], e[2], e[3]);
+}
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* p, const float (&e)[4]) {
+  uint2 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+  h[0] = __floats2bfloat162_rn(e[0], e[1]);
+  h[1] = __floats2bfloat162_rn(e[2], e[3]);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
 template <typename IO>
 __global__ void __launch_bounds__(128) gdn_block_pre_bwd_kernel(BlockP p, PreArgs<IO> a, int ntiles) {
-  __shared__ float red[kGroups][4][128];
+  __shared__ float red[kBwdGroups][4][128];
   const int which = blockIdx.x / ntiles, tile = blockIdx.x % ntiles;
   const int h = blockIdx.y, b = blockIdx.z;
   const int D = which == 2 ? p.Dv : p.Dk, C = p.H * D;
-  const int lane16 = threadIdx.x & 15, grp = threadIdx.x >> 4;
-  const bool act = lane16 * 8 < D;
-  const int ch = h * D + lane16 * 8;
-  const int t0 = tile * kTile + grp * kRun;
+  const int lane32 = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const bool act = lane32 * 4 < D;
+  const int ch = h * D + lane32 * 4;
+  const int t0 = tile * kBwdTile + grp * kRun;
   const IO* x = a.x[which] + (size_t)b * p.T * C + ch;
   const IO* dy = a.dy[which] + (size_t)b * p.T * C + ch;
   IO* dx = a.dx[which] + (size_t)b * p.T * C + ch;
-  float w[4][8], dw[4][8];
+  float w[4][4], dw[4][4];
 #pragma unroll
   for (int tap = 0; tap < 4; ++tap)
 #pragma unroll
-    for (int c = 0; c < 8; ++c) { w[tap][c] = 0.f; dw[tap][c] = 0.f; }
+    for (int c = 0; c < 4; ++c) { w[tap][c] = 0.f; dw[tap][c] = 0.f; }
   if (act) {
 #pragma unroll
-    for (int tap = 0; tap < 4; ++tap) load8<float>(a.w[which] + tap * C + ch, w[tap]);
+    for (int tap = 0; tap < 4; ++tap) load4<float>(a.w[which] + tap * C + ch, w[tap]);
   }
   const float scale = which == 0 ? 1.f / (float)D : rsqrtf((float)D);
-  float x1[8], x2[8], x3[8], d1[8], d2[8], d3[8];  // previous inputs; previous three ds
+  float x1[4], x2[4], x3[4], d1[4], d2[4], d3[4];  // previous inputs; previous three ds
 #pragma unroll
-  for (int c = 0; c < 8; ++c) x1[c] = x2[c] = x3[c] = d1[c] = d2[c] = d3[c] = 0.f;
+  for (int c = 0; c < 4; ++c) x1[c] = x2[c] = x3[c] = d1[c] = d2[c] = d3[c] = 0.f;
   if (act) {
-    if (t0 - 1 >= 0 && t0 - 1 < p.T) load8<IO>(x + (size_t)(t0 - 1) * C, x1);
-    if (t0 - 2 >= 0 && t0 - 2 < p.T) load8<IO>(x + (size_t)(t0 - 2) * C, x2);
-    if (t0 - 3 >= 0 && t0 - 3 < p.T) load8<IO>(x + (size_t)(t0 - 3) * C, x3);
+    if (t0 - 1 >= 0 && t0 - 1 < p.T) load4<IO>(x + (size_t)(t0 - 1) * C, x1);
+    if (t0 - 2 >= 0 && t0 - 2 < p.T) load4<IO>(x + (size_t)(t0 - 2) * C, x2);
+    if (t0 - 3 >= 0 && t0 - 3 < p.T) load4<IO>(x + (size_t)(t0 - 3) * C, x3);
   }
 #pragma unroll
   for (int r = 0; r < kRun + 3; ++r) {
     const int t = t0 + r;
     const bool in = act && t < p.T;
-    float x0[8], g[8], ds[8];
+    float x0[4], g[4], ds[4];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) { x0[c] = 0.f; g[c] = 0.f; }
-    if (in) { load8<IO>(x + (size_t)t * C, x0); load8<IO>(dy + (size_t)t * C, g); }
+    for (int c = 0; c < 4; ++c) { x0[c] = 0.f; g[c] = 0.f; }
+    if (in) { load4<IO>(x + (size_t)t * C, x0); load4<IO>(dy + (size_t)t * C, g); }
     // one sigmoid per element gives SiLU and its derivative; rows past T have zero dy, hence zero ds
-    float sv[8], dsl[8], ss = 0.f, dot = 0.f;
+    float sv[4], dsl[4], ss = 0.f, dot = 0.f;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
       const float acc = w[0][c] * x0[c] + w[1][c] * x1[c] + w[2][c] * x2[c] + w[3][c] * x3[c];
       const float sg = sigmoid_io<IO>(acc);
       sv[c] = acc * sg;
@@ -216,18 +249,18 @@ __global__ void __launch_bounds__(128) gdn_block_pre_bwd_kernel(BlockP p, PreArg
       dot = fmaf(sv[c], g[c], dot);
     }
     if (which < 2) {  // y = s rn scale: ds_c = scale rn (g_c - s_c rn^2 dot / D)
-      ss = group_sum(ss);
-      dot = group_sum(dot);
+      ss = warp_sum(ss);
+      dot = warp_sum(dot);
       const float rn = rsqrtf(ss / (float)D + 1e-6f);
       const float k2 = rn * rn * dot / (float)D;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) g[c] = scale * rn * (g[c] - sv[c] * k2);
+      for (int c = 0; c < 4; ++c) g[c] = scale * rn * (g[c] - sv[c] * k2);
     }
 #pragma unroll
-    for (int c = 0; c < 8; ++c) ds[c] = g[c] * dsl[c];
+    for (int c = 0; c < 4; ++c) ds[c] = g[c] * dsl[c];
     if (r < kRun) {  // this step belongs to the run: its share of the weight gradient
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         dw[0][c] = fmaf(x0[c], ds[c], dw[0][c]);
         dw[1][c] = fmaf(x1[c], ds[c], dw[1][c]);
         dw[2][c] = fmaf(x2[c], ds[c], dw[2][c]);
@@ -237,14 +270,14 @@ __global__ void __launch_bounds__(128) gdn_block_pre_bwd_kernel(BlockP p, PreArg
     if (r >= 3) {  // dx of step t-3 is complete: w0 ds[t-3] + w1 ds[t-2] + w2 ds[t-1] + w3 ds[t]
       const int to = t - 3;
       if (act && to < p.T) {
-        float o[8];
+        float o[4];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) o[c] = w[0][c] * d3[c] + w[1][c] * d2[c] + w[2][c] * d1[c] + w[3][c] * ds[c];
-        store8<IO>(dx + (size_t)to * C, o);
+        for (int c = 0; c < 4; ++c) o[c] = w[0][c] * d3[c] + w[1][c] * d2[c] + w[2][c] * d1[c] + w[3][c] * ds[c];
+        store4<IO>(dx + (size_t)to * C, o);
       }
     }
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
       x3[c] = x2[c]; x2[c] = x1[c]; x1[c] = x0[c];
       d3[c] = d2[c]; d2[c] = d1[c]; d1[c] = ds[c];
     }
@@ -253,14 +286,14 @@ __global__ void __launch_bounds__(128) gdn_block_pre_bwd_kernel(BlockP p, PreArg
 #pragma unroll
   for (int tap = 0; tap < 4; ++tap)
 #pragma unroll
-    for (int c = 0; c < 8; ++c) red[grp][tap][lane16 * 8 + c] = dw[tap][c];
+    for (int c = 0; c < 4; ++c) red[grp][tap][lane32 * 4 + c] = dw[tap][c];
   __syncthreads();
   float* dst = a.dwp[which] + ((size_t)(b * ntiles + tile) * 4) * C + h * D;
   for (int i = threadIdx.x; i < 4 * D; i += 128) {
     const int tap = i / D, c = i % D;
     float s = 0.f;
 #pragma unroll
-    for (int g2 = 0; g2 < kGroups; ++g2) s += red[g2][tap][c];
+    for (int g2 = 0; g2 < kBwdGroups; ++g2) s += red[g2][tap][c];
     dst[(size_t)tap * C + c] = s;
   }
 }
@@ -457,6 +490,7 @@ bool gdn_block_supported(const mxb_gdn_desc* d) {
   return d->Dk % 8 == 0 && d->Dv % 8 == 0 && d->Dk <= 128 && d->Dv <= 128 && d->Dk > 0 && d->Dv > 0;
 }
 static int blk_tiles(const mxb_gdn_desc* d) { return (d->T + blk::kTile - 1) / blk::kTile; }
+static int blk_bwd_tiles(const mxb_gdn_desc* d) { return (d->T + blk::kBwdTile - 1) / blk::kBwdTile; }
 static int blk_post_ctas(const mxb_gdn_desc* d) {
   const size_t rows = (size_t)d->B * d->T * d->H;
   const size_t want = (rows + blk::kGroups - 1) / blk::kGroups;
@@ -468,7 +502,7 @@ static int blk_gate_ctas(const mxb_gdn_desc* d) {
 }
 // backward partial rows: conv weights of q, k, v and the per-head gate sums; or the norm weight
 size_t gdn_block_workspace_bytes(const mxb_gdn_desc* d) {
-  const size_t rows = (size_t)d->B * blk_tiles(d);
+  const size_t rows = (size_t)d->B * blk_bwd_tiles(d);
   const size_t pre = rows * 4 * ((size_t)2 * d->H * d->Dk + (size_t)d->H * d->Dv) * sizeof(float);
   const size_t post = (size_t)blk_post_ctas(d) * d->Dv * sizeof(float);
   const size_t gate = 2 * (size_t)blk_gate_ctas(d) * d->H * sizeof(float);
@@ -516,7 +550,7 @@ static mxb_status blk_pre_bwd(const mxb_gdn_desc* d, const void* qp, const void*
   a.w[0] = cq; a.w[1] = ck; a.w[2] = cv;
   a.dy[0] = static_cast<const IO*>(dq); a.dy[1] = static_cast<const IO*>(dk); a.dy[2] = static_cast<const IO*>(dv);
   a.dx[0] = static_cast<IO*>(dqp); a.dx[1] = static_cast<IO*>(dkp); a.dx[2] = static_cast<IO*>(dvp);
-  const int nt = blk_tiles(d);
+  const int nt = blk_bwd_tiles(d);
   const size_t rows = (size_t)d->B * nt, Ck = (size_t)d->H * d->Dk, Cv = (size_t)d->H * d->Dv;
   float* base = reinterpret_cast<float*>(static_cast<char*>(ws) + 256);
   a.dwp[0] = base; a.dwp[1] = base + rows * 4 * Ck; a.dwp[2] = base + rows * 8 * Ck;
