@@ -217,6 +217,34 @@ def gdn_block_stages(ref: Path):
                             "fixture() / arch/blocks_gated_deltanet.go:207-343, python random.Random(4321) inputs")))
     print("gdn_block_stages.json:", len(cases), "cases")
 
+
+def mamba3_block_stages(ref: Path):
+    """Element-wise stages of the canonical Mamba-3 block (gpu/ir.cpp:2034-2105) through the reference's own
+    scalar helpers (depthwise_conv_1d, rms_norm_rows, sigmoid of experiments/mamba3_reference/generate_fixtures.py)."""
+    mod = _load(ref / "experiments/mamba3_reference/generate_fixtures.py", "ref_m3_fix2")
+    rng = random.Random(8765)
+    cases = []
+    for (B, T, D, N, G, K) in [(1, 3, 4, 2, 1, 4), (2, 9, 16, 8, 2, 4), (1, 37, 24, 16, 1, 3)]:
+        def vec(n, lo=-1.0, hi=1.0):
+            return [rng.uniform(lo, hi) for _ in range(n)]
+        x, w = vec(B * T * D, -2, 2), vec(D * K, -0.6, 0.6)
+        conv = mod.depthwise_conv_1d(x, w, B, T, D, K)
+        bp, cp = vec(B * T * G * N, -2, 2), vec(B * T * G * N, -2, 2)
+        bs, cs, bb, cb = vec(N, 0.5, 1.5), vec(N, 0.5, 1.5), vec(G * N, -0.5, 0.5), vec(G * N, -0.5, 0.5)
+        bn = mod.rms_norm_rows(bp, B * T * G, N, bs)
+        cn = mod.rms_norm_rows(cp, B * T * G, N, cs)
+        b = [v + bb[i % (G * N)] for i, v in enumerate(bn)]
+        c = [v + cb[i % (G * N)] for i, v in enumerate(cn)]
+        y, z, pn = vec(B * T * D, -2, 2), vec(B * T * D, -3, 3), vec(D, 0.5, 1.5)
+        yn = mod.rms_norm_rows(y, B * T, D, pn)
+        out = [a * zz * mod.sigmoid(zz) for a, zz in zip(yn, z)]
+        cases.append(dict(B=B, T=T, D=D, N=N, G=G, K=K, x=x, conv_w=w, conv=conv, b_proj=bp, c_proj=cp, b_scale=bs,
+                          c_scale=cs, b_bias=bb, c_bias=cb, b=b, c=c, y=y, z=z, post_norm=pn, out=out))
+    (HERE / "mamba3_block_stages.json").write_text(json.dumps(dict(
+        cases=cases, source="helpers of experiments/mamba3_reference/generate_fixtures.py composed as in fixture() / "
+                            "gpu/ir.cpp:2034-2105 (eps 1e-5), python random.Random(8765) inputs")))
+    print("mamba3_block_stages.json:", len(cases), "cases")
+
 def main():
     ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     gdn_block_fixture(ref)
@@ -224,6 +252,7 @@ def main():
     gdn_torch_recurrence(ref)
     gdn_go_test_inputs()
     mamba3_block_fixture(ref)
+    mamba3_block_stages(ref)
     mamba3_torch_scan(ref)
 
 

@@ -141,3 +141,20 @@ def test_gdn_block_stages_match_reference_helpers():
             assert (got - t(name, *shape)).abs().max().item() < 1e-12, name
         y = gdn_block.block_post(t("o", B, T, H, Dv), t("z", B, T, H * Dv), t("o_norm", Dv))
         assert (y - t("y", B, T, H * Dv)).abs().max().item() < 1e-12
+
+
+def test_mamba3_block_stages_match_reference_helpers():
+    """oracle.mamba3_block against vectors from the reference's own scalar block helpers."""
+    from oracle import mamba3_block
+    data = json.load(open(os.path.join(G, "mamba3_block_stages.json")))
+    for c in data["cases"]:
+        B, T, D, N, Gr, K = (c[k] for k in ("B", "T", "D", "N", "G", "K"))
+        t = lambda name, *shape: torch.tensor(c[name], dtype=torch.float64).reshape(*shape)
+        conv = mamba3_block.depthwise_conv(t("x", B, T, D), t("conv_w", D, K))
+        assert (conv - t("conv", B, T, D)).abs().max().item() < 1e-12
+        b, cc = mamba3_block.bc_norm(t("b_proj", B, T, Gr * N), t("c_proj", B, T, Gr * N), t("b_scale", N), t("c_scale", N),
+                                     t("b_bias", Gr * N), t("c_bias", Gr * N), Gr, N)
+        assert (b - t("b", B, T, Gr, N)).abs().max().item() < 1e-12
+        assert (cc - t("c", B, T, Gr, N)).abs().max().item() < 1e-12
+        out = mamba3_block.post(t("y", B, T, D), t("z", B, T, D), t("post_norm", D))
+        assert (out - t("out", B, T, D)).abs().max().item() < 1e-12
