@@ -246,6 +246,42 @@ MXB_API mxb_status mxb_mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const
                           void* stream);
 
 /* ------------------------------------------------------------------------
+ * Element-wise stages of the canonical Mamba-3 block on either side of the scan
+ * (mamba3_canonical_block_impl / _vjp, gpu/ir.cpp:2034-2105, :2107-2288).  The
+ * projections are matrix products and stay with the caller.  desc: B, T, D (the
+ * inner width, multiple of 8, <= 2048), N (multiple of 8, <= 128), G, io_dtype;
+ * nheads and flags are ignored.  Weights, scales and biases are float32.
+ *   conv  y = causal depthwise convolution of x [B,T,D] with w [D,K], K <= 4; tap k
+ *         multiplies x[t-k] (causal_depthwise_conv1d, gpu/ir.cpp:1397-1425)
+ *   bc    b = RMSNorm(b_proj rows of N, b_scale [N], eps) + b_bias [G*N], same for c;
+ *         b_proj, c_proj, b, c are [B,T,G*N]
+ *   post  out = RMSNorm(y rows of D, post_norm [D], eps) z sigmoid(z); y, z [B,T,D]
+ * Each backward entry point returns every gradient; sums over (batch, step) go
+ * through partial rows in the workspace in a fixed order.
+ * ---------------------------------------------------------------------- */
+MXB_API size_t mxb_mamba3_block_workspace_bytes(const mxb_mamba3_desc* d);
+MXB_API mxb_status mxb_mamba3_block_conv_fwd(const mxb_mamba3_desc* d, int32_t K, const void* x, const float* w,
+                                     void* y, void* stream);
+MXB_API mxb_status mxb_mamba3_block_conv_bwd(const mxb_mamba3_desc* d, int32_t K, const void* x, const float* w,
+                                     const void* dy, void* dx, float* dw, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+MXB_API mxb_status mxb_mamba3_block_bc_fwd(const mxb_mamba3_desc* d, float eps, const void* b_proj,
+                                   const void* c_proj, const float* b_scale, const float* c_scale,
+                                   const float* b_bias, const float* c_bias, void* b, void* c,
+                                   void* stream);
+MXB_API mxb_status mxb_mamba3_block_bc_bwd(const mxb_mamba3_desc* d, float eps, const void* b_proj,
+                                   const void* c_proj, const float* b_scale, const float* c_scale,
+                                   const void* db, const void* dc, void* db_proj, void* dc_proj,
+                                   float* db_scale, float* dc_scale, float* db_bias, float* dc_bias,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+MXB_API mxb_status mxb_mamba3_block_post_fwd(const mxb_mamba3_desc* d, float eps, const void* y, const void* z,
+                                     const float* post_norm, void* out, void* stream);
+MXB_API mxb_status mxb_mamba3_block_post_bwd(const mxb_mamba3_desc* d, float eps, const void* y, const void* z,
+                                     const float* post_norm, const void* dout, void* dy, void* dz,
+                                     float* dpost_norm, void* workspace, size_t workspace_bytes,
+                                     void* stream);
+
+/* ------------------------------------------------------------------------
  * Diagnostics (no counterpart in the reference).  One tcgen05.mma tile
  * D[128 x ncols] = A * B^T from caller-built shared-memory images (device
  * pointers, multiples of 16 bytes) and raw descriptor fields:

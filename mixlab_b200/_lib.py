@@ -62,6 +62,13 @@ EXPORTS = {
     "mxb_mamba3_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(Mamba3Desc)]),
     "mxb_mamba3_fwd": (C.c_int32, [C.POINTER(Mamba3Desc)] + [_P] * 9 + [C.c_size_t, _P]),
     "mxb_mamba3_bwd": (C.c_int32, [C.POINTER(Mamba3Desc)] + [_P] * 16 + [C.c_size_t, _P]),
+    "mxb_mamba3_block_workspace_bytes": (C.c_size_t, [C.POINTER(Mamba3Desc)]),
+    "mxb_mamba3_block_conv_fwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_int32] + [_P] * 4),
+    "mxb_mamba3_block_conv_bwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_int32] + [_P] * 6 + [C.c_size_t, _P]),
+    "mxb_mamba3_block_bc_fwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 9),
+    "mxb_mamba3_block_bc_bwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 13 + [C.c_size_t, _P]),
+    "mxb_mamba3_block_post_fwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 5),
+    "mxb_mamba3_block_post_bwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 8 + [C.c_size_t, _P]),
     "mxb_selftest_umma": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint32, _P, _P, _P, _P]),
     "mxb_host_ctx_create": (C.c_int32, [C.c_int, C.c_size_t, C.POINTER(_P)]),
     "mxb_host_ctx_destroy": (None, [_P]),

@@ -90,6 +90,15 @@ mxb_status gdn_block_pre_bwd(const mxb_gdn_desc*, const void*, const void*, cons
                              float*, float*, float*, float*, float*, void*, cudaStream_t);
 mxb_status gdn_block_post(const mxb_gdn_desc*, const void*, const void*, const float*, void*, const void*, void*, void*,
                           float*, void*, cudaStream_t);
+bool mamba3_block_supported(const mxb_mamba3_desc*);
+size_t mamba3_block_workspace_bytes(const mxb_mamba3_desc*);
+mxb_status mamba3_block_conv(const mxb_mamba3_desc*, int, const void*, const float*, void*, const void*, void*, float*,
+                             void*, cudaStream_t);
+mxb_status mamba3_block_bc(const mxb_mamba3_desc*, float, const void*, const void*, const float*, const float*,
+                           const float*, const float*, void*, void*, const void*, const void*, void*, void*, float*,
+                           float*, float*, float*, void*, cudaStream_t);
+mxb_status mamba3_block_post(const mxb_mamba3_desc*, float, const void*, const void*, const float*, void*, const void*,
+                             void*, void*, float*, void*, cudaStream_t);
 bool mamba3_supported(const mxb_mamba3_desc*);
 size_t mamba3_workspace_bytes(const mxb_mamba3_desc*, bool bwd);
 mxb_status mamba3_fwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*,
@@ -349,6 +358,87 @@ mxb_status mxb_selftest_umma(const void* a_img, uint32_t a_bytes, const void* b_
                              const uint32_t* fields, float* d_out, int* status, void* stream) {
   if (!a_img || !b_img || !fields || !d_out || !status) return MXB_ERR_INVALID_ARGUMENT;
   return umma_selftest(a_img, a_bytes, b_img, b_bytes, fields, d_out, status, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------- Mamba-3 block stages
+static mxb_status check_m3_block_desc(const mxb_mamba3_desc* d) {
+  if (!d) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->B <= 0 || d->T <= 0 || d->D <= 0 || d->N <= 0 || d->G <= 0) return MXB_ERR_INVALID_ARGUMENT;
+  if (d->io_dtype != MXB_F32 && d->io_dtype != MXB_BF16) return MXB_ERR_INVALID_ARGUMENT;
+  if (!mamba3_block_supported(d)) return MXB_ERR_UNSUPPORTED;
+  return MXB_OK;
+}
+size_t mxb_mamba3_block_workspace_bytes(const mxb_mamba3_desc* d) {
+  return check_m3_block_desc(d) == MXB_OK ? mamba3_block_workspace_bytes(d) : 0;
+}
+mxb_status mxb_mamba3_block_conv_fwd(const mxb_mamba3_desc* d, int32_t K, const void* x, const float* w, void* y,
+                                     void* stream) {
+  mxb_status s = check_m3_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (K < 1 || K > 4) return MXB_ERR_UNSUPPORTED;
+  if (!x || !w || !y) return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(x) || !aligned16(y)) return MXB_ERR_ALIGNMENT;
+  return mamba3_block_conv(d, K, x, w, y, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+mxb_status mxb_mamba3_block_conv_bwd(const mxb_mamba3_desc* d, int32_t K, const void* x, const float* w, const void* dy,
+                                     void* dx, float* dw, void* workspace, size_t workspace_bytes, void* stream) {
+  mxb_status s = check_m3_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (K < 1 || K > 4) return MXB_ERR_UNSUPPORTED;
+  if (!x || !w || !dy || !dx || !dw || !workspace) return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(workspace)) return MXB_ERR_ALIGNMENT;
+  if (workspace_bytes < mamba3_block_workspace_bytes(d)) return MXB_ERR_WORKSPACE;
+  return mamba3_block_conv(d, K, x, w, nullptr, dy, dx, dw, workspace, static_cast<cudaStream_t>(stream));
+}
+mxb_status mxb_mamba3_block_bc_fwd(const mxb_mamba3_desc* d, float eps, const void* b_proj, const void* c_proj,
+                                   const float* b_scale, const float* c_scale, const float* b_bias, const float* c_bias,
+                                   void* b, void* c, void* stream) {
+  mxb_status s = check_m3_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (!b_proj || !c_proj || !b_scale || !c_scale || !b_bias || !c_bias || !b || !c) return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(b_proj) || !aligned16(c_proj) || !aligned16(b) || !aligned16(c) || !aligned16(b_scale) ||
+      !aligned16(c_scale) || !aligned16(b_bias) || !aligned16(c_bias))
+    return MXB_ERR_ALIGNMENT;
+  return mamba3_block_bc(d, eps, b_proj, c_proj, b_scale, c_scale, b_bias, c_bias, b, c, nullptr, nullptr, nullptr, nullptr,
+                         nullptr, nullptr, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+mxb_status mxb_mamba3_block_bc_bwd(const mxb_mamba3_desc* d, float eps, const void* b_proj, const void* c_proj,
+                                   const float* b_scale, const float* c_scale, const void* db, const void* dc,
+                                   void* db_proj, void* dc_proj, float* db_scale, float* dc_scale, float* db_bias,
+                                   float* dc_bias, void* workspace, size_t workspace_bytes, void* stream) {
+  mxb_status s = check_m3_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (!b_proj || !c_proj || !b_scale || !c_scale || !db || !dc || !db_proj || !dc_proj || !db_scale || !dc_scale ||
+      !db_bias || !dc_bias || !workspace)
+    return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(b_proj) || !aligned16(c_proj) || !aligned16(db) || !aligned16(dc) || !aligned16(db_proj) ||
+      !aligned16(dc_proj) || !aligned16(b_scale) || !aligned16(c_scale) || !aligned16(workspace))
+    return MXB_ERR_ALIGNMENT;
+  if (workspace_bytes < mamba3_block_workspace_bytes(d)) return MXB_ERR_WORKSPACE;
+  return mamba3_block_bc(d, eps, b_proj, c_proj, b_scale, c_scale, nullptr, nullptr, nullptr, nullptr, db, dc, db_proj,
+                         dc_proj, db_scale, dc_scale, db_bias, dc_bias, workspace, static_cast<cudaStream_t>(stream));
+}
+mxb_status mxb_mamba3_block_post_fwd(const mxb_mamba3_desc* d, float eps, const void* y, const void* z,
+                                     const float* post_norm, void* out, void* stream) {
+  mxb_status s = check_m3_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (!y || !z || !post_norm || !out) return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(y) || !aligned16(z) || !aligned16(out) || !aligned16(post_norm)) return MXB_ERR_ALIGNMENT;
+  return mamba3_block_post(d, eps, y, z, post_norm, out, nullptr, nullptr, nullptr, nullptr, nullptr,
+                           static_cast<cudaStream_t>(stream));
+}
+mxb_status mxb_mamba3_block_post_bwd(const mxb_mamba3_desc* d, float eps, const void* y, const void* z,
+                                     const float* post_norm, const void* dout, void* dy, void* dz, float* dpost_norm,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
+  mxb_status s = check_m3_block_desc(d);
+  if (s != MXB_OK) return s;
+  if (!y || !z || !post_norm || !dout || !dy || !dz || !dpost_norm || !workspace) return MXB_ERR_INVALID_ARGUMENT;
+  if (!aligned16(y) || !aligned16(z) || !aligned16(dout) || !aligned16(dy) || !aligned16(dz) || !aligned16(post_norm) ||
+      !aligned16(workspace))
+    return MXB_ERR_ALIGNMENT;
+  if (workspace_bytes < mamba3_block_workspace_bytes(d)) return MXB_ERR_WORKSPACE;
+  return mamba3_block_post(d, eps, y, z, post_norm, nullptr, dout, dy, dz, dpost_norm, workspace,
+                           static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------- host ctx

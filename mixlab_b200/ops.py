@@ -250,3 +250,86 @@ def mamba3_selective_scan_backward(x, dt, lam, theta, a_log, b, c, dy, *, nheads
                                 _ptr(dy), _ptr(dx), _ptr(ddt), _ptr(dlam), _ptr(dth), _ptr(dal), _ptr(db),
                                 _ptr(dc), _ptr(ws), ws.numel(), _stream()), "mxb_mamba3_bwd")
     return dict(dx=dx, ddt=ddt, dlambda=dlam, dtheta=dth, da_log=dal, db=db, dc=dc)
+
+
+# ---------------------------------------------------------------- Mamba-3 block stages
+def _m3_block_desc(x, N, G):
+    B, T, D = x.shape
+    return Mamba3Desc(B, T, D, int(N), int(G), 0, _io(x), 0)
+
+
+def mamba3_block_conv(x, w):
+    """Causal depthwise convolution: x [B,T,D], w [D,K] (K <= 4; tap k multiplies x[t-k])."""
+    _require_cuda(x, w)
+    l = _lib.lib()
+    d = _m3_block_desc(x, 8, 1)
+    y = torch.empty_like(x)
+    _lib.check(l.mxb_mamba3_block_conv_fwd(C.byref(d), int(w.shape[1]), _ptr(x), _ptr(_f32(w, "w")), _ptr(y), _stream()),
+               "mxb_mamba3_block_conv_fwd")
+    return y
+
+
+def mamba3_block_conv_backward(x, w, dy):
+    _require_cuda(x, w, dy)
+    l = _lib.lib()
+    d = _m3_block_desc(x, 8, 1)
+    dx = torch.empty_like(x)
+    dw = torch.empty(w.shape, dtype=torch.float32, device=x.device)
+    ws = workspace(l.mxb_mamba3_block_workspace_bytes(C.byref(d)), x.device)
+    _lib.check(l.mxb_mamba3_block_conv_bwd(C.byref(d), int(w.shape[1]), _ptr(x), _ptr(_f32(w, "w")), _ptr(dy), _ptr(dx),
+                                           _ptr(dw), _ptr(ws), ws.numel(), _stream()), "mxb_mamba3_block_conv_bwd")
+    return dict(dx=dx, dw=dw)
+
+
+def mamba3_block_bc(b_proj, c_proj, b_scale, c_scale, b_bias, c_bias, G, N, eps=1e-5):
+    """b = RMSNorm(b_proj rows of N, b_scale, eps) + b_bias, same for c.  [B,T,G*N] -> [B,T,G,N]."""
+    _require_cuda(b_proj, c_proj, b_scale, c_scale, b_bias, c_bias)
+    l = _lib.lib()
+    B, T, _ = b_proj.shape
+    d = Mamba3Desc(B, T, 8, int(N), int(G), 0, _io(b_proj), 0)
+    b = torch.empty(B, T, G, N, dtype=b_proj.dtype, device=b_proj.device)
+    c = torch.empty_like(b)
+    _lib.check(l.mxb_mamba3_block_bc_fwd(C.byref(d), float(eps), _ptr(b_proj), _ptr(c_proj), _ptr(_f32(b_scale, "b_scale")),
+                                         _ptr(_f32(c_scale, "c_scale")), _ptr(_f32(b_bias, "b_bias")),
+                                         _ptr(_f32(c_bias, "c_bias")), _ptr(b), _ptr(c), _stream()), "mxb_mamba3_block_bc_fwd")
+    return b, c
+
+
+def mamba3_block_bc_backward(b_proj, c_proj, b_scale, c_scale, db, dc, G, N, eps=1e-5):
+    _require_cuda(b_proj, c_proj, b_scale, c_scale, db, dc)
+    l = _lib.lib()
+    B, T, _ = b_proj.shape
+    d = Mamba3Desc(B, T, 8, int(N), int(G), 0, _io(b_proj), 0)
+    dbp, dcp = torch.empty_like(b_proj), torch.empty_like(c_proj)
+    f32 = dict(dtype=torch.float32, device=b_proj.device)
+    dbs, dcs, dbb, dcb = torch.empty(N, **f32), torch.empty(N, **f32), torch.empty(G * N, **f32), torch.empty(G * N, **f32)
+    ws = workspace(l.mxb_mamba3_block_workspace_bytes(C.byref(d)), b_proj.device)
+    _lib.check(l.mxb_mamba3_block_bc_bwd(C.byref(d), float(eps), _ptr(b_proj), _ptr(c_proj), _ptr(_f32(b_scale, "b_scale")),
+                                         _ptr(_f32(c_scale, "c_scale")), _ptr(db), _ptr(dc), _ptr(dbp), _ptr(dcp), _ptr(dbs),
+                                         _ptr(dcs), _ptr(dbb), _ptr(dcb), _ptr(ws), ws.numel(), _stream()),
+               "mxb_mamba3_block_bc_bwd")
+    return dict(db_proj=dbp, dc_proj=dcp, db_scale=dbs, dc_scale=dcs, db_bias=dbb, dc_bias=dcb)
+
+
+def mamba3_block_post(y, z, post_norm, eps=1e-5):
+    """RMSNorm(y rows of D, post_norm, eps) * z * sigmoid(z).  y, z [B,T,D]."""
+    _require_cuda(y, z, post_norm)
+    l = _lib.lib()
+    d = _m3_block_desc(y, 8, 1)
+    out = torch.empty_like(y)
+    _lib.check(l.mxb_mamba3_block_post_fwd(C.byref(d), float(eps), _ptr(y), _ptr(z), _ptr(_f32(post_norm, "post_norm")),
+                                           _ptr(out), _stream()), "mxb_mamba3_block_post_fwd")
+    return out
+
+
+def mamba3_block_post_backward(y, z, post_norm, dout, eps=1e-5):
+    _require_cuda(y, z, post_norm, dout)
+    l = _lib.lib()
+    d = _m3_block_desc(y, 8, 1)
+    dy, dz = torch.empty_like(y), torch.empty_like(z)
+    dw = torch.empty(y.shape[-1], dtype=torch.float32, device=y.device)
+    ws = workspace(l.mxb_mamba3_block_workspace_bytes(C.byref(d)), y.device)
+    _lib.check(l.mxb_mamba3_block_post_bwd(C.byref(d), float(eps), _ptr(y), _ptr(z), _ptr(_f32(post_norm, "post_norm")),
+                                           _ptr(dout), _ptr(dy), _ptr(dz), _ptr(dw), _ptr(ws), ws.numel(), _stream()),
+               "mxb_mamba3_block_post_bwd")
+    return dict(dy=dy, dz=dz, dpost_norm=dw)
