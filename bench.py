@@ -34,6 +34,7 @@ WORKLOADS = {
     "gdn_decode": dict(N=256, H=16, Dk=128, Dv=128, tokens_per_step=64),
     "mamba3_train": dict(B=8, T=4096, nheads=32, headdim=64, N=128, G=1),
     "gdn_block": dict(B=8, T=4096, H=16, Dk=128, Dv=128),
+    "mamba3_block": dict(B=8, T=4096, D=2048, N=128, G=1, K=4),
 }
 # Algorithmic work per unit (stated in DESIGN.md).
 GDN_BYTES_PER_TOKEN_HEAD = 2840          # fwd 1032 + bwd read 1032 + bwd write 776
@@ -43,6 +44,8 @@ M3_FLOPS_PER_TOKEN = 5.50e6
 # block stages around the scan, fwd+bwd, bf16: pre fwd 3 in + 3 out, pre bwd 6 in + 3 out, post fwd 2 in + 1 out,
 # post bwd 3 in + 2 out = 23 tensors of 128 channels x 2 bytes, plus the fp32 per-head scalars
 GDN_BLOCK_BYTES_PER_TOKEN_HEAD = 23 * 128 * 2 + 10 * 4
+# Mamba-3 block stages, fwd+bwd, bf16: conv 2 + 3, post 3 + 5 tensors of D channels; B/C norm 4 + 6 tensors of G*N
+M3_BLOCK_BYTES_PER_TOKEN = lambda D, GN: (13 * D + 10 * GN) * 2
 # DRAM traffic per unit from the committed ncu captures (profiles/): dram__bytes_read.sum + dram__bytes_write.sum
 GDN_NCU_TRAFFIC_PER_CHUNK = 1286.2e6 / 2048    # B=2 capture: 1286.2 MB over 2048 (batch, head, chunk) units
 M3_NCU_TRAFFIC_PER_CHUNK = 746.4e6 / 4096      # B=2 capture: 746.4 MB over 2 x 32 x 64 (batch, head, chunk) units
@@ -280,6 +283,35 @@ def main():
             ops.gdn_block_pre_backward(*pre, H, K, V, d["dq"], d["dk"], d["dv"], d["db"], d["dg"], gate_is_log=True)
 
         cfg = {"workload": "gdn_block", **w, "io": "bf16", "what": "conv+SiLU+L2-norm/gate/beta and norm x gate, fwd+bwd"}
+    elif args.workload == "mamba3_block":
+        w = dict(WORKLOADS["mamba3_block"])
+        if args.batch > 0:
+            w["B"] = args.batch
+        B, T, D, N, G, K = w["B"], w["T"], w["D"], w["N"], w["G"], w["K"]
+        g = torch.Generator().manual_seed(5000 + rank)
+        rn = lambda *shape: torch.randn(*shape, generator=g)
+        io = torch.bfloat16
+        d = dict(x=rn(B, T, D).to(io), cw=0.4 * rn(D, K), dyc=rn(B, T, D).to(io),
+                 bp=rn(B, T, G * N).to(io), cp=rn(B, T, G * N).to(io), bs=1 + 0.2 * rn(N), cs=1 + 0.2 * rn(N),
+                 bb=0.3 * rn(G * N), cb=0.3 * rn(G * N), db=rn(B, T, G, N).to(io), dc=rn(B, T, G, N).to(io),
+                 y=rn(B, T, D).to(io), z=rn(B, T, D).to(io), pn=1 + 0.2 * rn(D), dout=rn(B, T, D).to(io))
+        d = {k: v.to(dev) for k, v in d.items()}
+        units = B * T
+        metric, unit, dtype = "mamba3_block_stages_fwd_bwd_tokens_per_s", "tokens/s", "f32"
+        alg_bytes = units * M3_BLOCK_BYTES_PER_TOKEN(D, G * N)
+        alg_flops = 0.0
+        bound = "hbm"
+        traffic, traffic_note = None, "not captured"
+
+        def step():
+            ops.mamba3_block_conv(d["x"], d["cw"])
+            ops.mamba3_block_bc(d["bp"], d["cp"], d["bs"], d["cs"], d["bb"], d["cb"], G, N)
+            ops.mamba3_block_post(d["y"], d["z"], d["pn"])
+            ops.mamba3_block_post_backward(d["y"], d["z"], d["pn"], d["dout"])
+            ops.mamba3_block_bc_backward(d["bp"], d["cp"], d["bs"], d["cs"], d["db"], d["dc"], G, N)
+            ops.mamba3_block_conv_backward(d["x"], d["cw"], d["dyc"])
+
+        cfg = {"workload": "mamba3_block", **w, "io": "bf16", "what": "depthwise conv, B/C norm + bias, post-norm x gate, fwd+bwd"}
     else:
         w = dict(WORKLOADS["mamba3_train"])
         if args.batch > 0:

@@ -64,8 +64,8 @@ __global__ void __launch_bounds__(128) m3b_conv_fwd_kernel(BlkP p, const IO* __r
   for (int k = 0; k < kMaxK; ++k)
 #pragma unroll
     for (int c = 0; c < 8; ++c) wk[k][c] = k < p.K ? w[(size_t)(ch + c) * p.K + k] : 0.f;
-  const IO* xb = x + (size_t)b * p.T * p.D + ch;
-  IO* yb = y + (size_t)b * p.T * p.D + ch;
+  const IO* __restrict__ xb = x + (size_t)b * p.T * p.D + ch;
+  IO* __restrict__ yb = y + (size_t)b * p.T * p.D + ch;
   float x1[8], x2[8], x3[8];
 #pragma unroll
   for (int c = 0; c < 8; ++c) x1[c] = x2[c] = x3[c] = 0.f;
@@ -75,12 +75,12 @@ __global__ void __launch_bounds__(128) m3b_conv_fwd_kernel(BlkP p, const IO* __r
 #pragma unroll
   for (int r = 0; r < kRun; ++r) {
     const int t = t0 + r;
-    if (t >= p.T) break;
+    const bool in = t < p.T;
     float x0[8], o[8];
-    load8<IO>(xb + (size_t)t * p.D, x0);
+    load8<IO>(xb + (size_t)(in ? t : t0) * p.D, x0);  // clamped address: the loads of the run can all be in flight
 #pragma unroll
     for (int c = 0; c < 8; ++c) o[c] = wk[0][c] * x0[c] + wk[1][c] * x1[c] + wk[2][c] * x2[c] + wk[3][c] * x3[c];
-    store8<IO>(yb + (size_t)t * p.D, o);
+    if (in) store8<IO>(yb + (size_t)t * p.D, o);
 #pragma unroll
     for (int c = 0; c < 8; ++c) { x3[c] = x2[c]; x2[c] = x1[c]; x1[c] = x0[c]; }
   }
@@ -98,9 +98,9 @@ __global__ void __launch_bounds__(128) m3b_conv_bwd_kernel(BlkP p, const IO* __r
   for (int k = 0; k < kMaxK; ++k)
 #pragma unroll
     for (int c = 0; c < 8; ++c) { wk[k][c] = k < p.K ? w[(size_t)(ch + c) * p.K + k] : 0.f; dw[k][c] = 0.f; }
-  const IO* xb = x + (size_t)b * p.T * p.D + ch;
-  const IO* gb = dy + (size_t)b * p.T * p.D + ch;
-  IO* ob = dx + (size_t)b * p.T * p.D + ch;
+  const IO* __restrict__ xb = x + (size_t)b * p.T * p.D + ch;
+  const IO* __restrict__ gb = dy + (size_t)b * p.T * p.D + ch;
+  IO* __restrict__ ob = dx + (size_t)b * p.T * p.D + ch;
   float x1[8], x2[8], x3[8], g1[8], g2[8], g3[8];  // previous inputs; previous three dy
 #pragma unroll
   for (int c = 0; c < 8; ++c) x1[c] = x2[c] = x3[c] = g1[c] = g2[c] = g3[c] = 0.f;
@@ -110,12 +110,14 @@ __global__ void __launch_bounds__(128) m3b_conv_bwd_kernel(BlkP p, const IO* __r
 #pragma unroll
   for (int r = 0; r < kRun + 3; ++r) {
     const int t = t0 + r;
+    const bool in = t < p.T;
     float x0[8], g0[8];
+    load8<IO>(gb + (size_t)(in ? t : t0) * p.D, g0);  // clamped addresses, masked below
+    if (r < kRun) load8<IO>(xb + (size_t)(in ? t : t0) * p.D, x0);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) x0[c] = g0[c] = 0.f;
-    if (t < p.T) {
-      load8<IO>(gb + (size_t)t * p.D, g0);
-      if (r < kRun) load8<IO>(xb + (size_t)t * p.D, x0);
+    for (int c = 0; c < 8; ++c) {
+      g0[c] = in ? g0[c] : 0.f;
+      x0[c] = (in && r < kRun) ? x0[c] : 0.f;
     }
     if (r < kRun) {
 #pragma unroll
@@ -263,21 +265,17 @@ __global__ void __launch_bounds__(128) m3b_bc_bwd_kernel(BlkP p, BcArgs<IO> a) {
     dst[(size_t)kind * p.N + c] = s;
   }
 }
-// dscale[c] = sum over (cta, g) of part[cta][g][0][c];  dbias[g][c] = sum over cta of part[cta][g][1][c]
-__global__ void __launch_bounds__(128) m3b_bc_final_kernel(BlkP p, const float* __restrict__ part, int ctas,
+// from the column sums tab[g][kind][c] over the CTAs: dbias[g][c] = tab[g][1][c], dscale[c] = sum over g of tab[g][0][c]
+__global__ void __launch_bounds__(128) m3b_bc_final_kernel(BlkP p, const float* __restrict__ tab,
                                                            float* __restrict__ dscale, float* __restrict__ dbias) {
-  const int c = threadIdx.x, g = blockIdx.x;  // grid G + 1: block G computes dscale
+  const int c = threadIdx.x;
   if (c >= p.N) return;
-  if (g < p.G) {
-    float s = 0.f;
-    for (int k = 0; k < ctas; ++k) s += part[(((size_t)k * p.G + g) * 2 + 1) * p.N + c];
-    dbias[g * p.N + c] = s;
-  } else {
-    float s = 0.f;
-    for (int k = 0; k < ctas; ++k)
-      for (int gg = 0; gg < p.G; ++gg) s += part[(((size_t)k * p.G + gg) * 2 + 0) * p.N + c];
-    dscale[c] = s;
+  float s = 0.f;
+  for (int g = 0; g < p.G; ++g) {
+    s += tab[((size_t)g * 2 + 0) * p.N + c];
+    dbias[g * p.N + c] = tab[((size_t)g * 2 + 1) * p.N + c];
   }
+  dscale[c] = s;
 }
 
 // ------------------------------------------------------------------ post: RMSNorm over D x SiLU gate
@@ -382,7 +380,7 @@ static int m3b_post_ctas(const mxb_mamba3_desc* d) {
 }
 size_t mamba3_block_workspace_bytes(const mxb_mamba3_desc* d) {
   const size_t conv = (size_t)d->B * m3b_runs(d) * m3b::kMaxK * d->D * sizeof(float);
-  const size_t bc = 2 * (size_t)m3b_bc_ctas(d) * d->G * 2 * d->N * sizeof(float);
+  const size_t bc = 2 * ((size_t)m3b_bc_ctas(d) + 1) * d->G * 2 * d->N * sizeof(float);
   const size_t post = (size_t)m3b_post_ctas(d) * d->D * sizeof(float);
   size_t m = conv > bc ? conv : bc;
   m = m > post ? m : post;
@@ -434,8 +432,15 @@ static mxb_status m3b_bc(const mxb_mamba3_desc* d, float eps, const void* bp, co
   const size_t per = (size_t)ctas * d->G * 2 * d->N;
   a.part[0] = base; a.part[1] = base + per;
   MXB_LAUNCH("m3b_bc_bwd_kernel", st, (m3b::m3b_bc_bwd_kernel<IO><<<dim3(ctas, d->G, 2), 128, 0, st>>>(p, a)));
-  MXB_LAUNCH("m3b_bc_final_kernel", st, (m3b::m3b_bc_final_kernel<<<d->G + 1, 128, 0, st>>>(p, a.part[0], ctas, dbs, dbb)));
-  MXB_LAUNCH("m3b_bc_final_kernel", st, (m3b::m3b_bc_final_kernel<<<d->G + 1, 128, 0, st>>>(p, a.part[1], ctas, dcs, dcb)));
+  const int n = d->G * 2 * d->N;
+  float* tab = base + 2 * per;  // [2][G][2][N]
+  float* outs[2][2] = {{dbs, dbb}, {dcs, dcb}};
+  for (int w = 0; w < 2; ++w) {
+    MXB_LAUNCH("m3b_colsum_kernel", st,
+               (m3b::m3b_colsum_kernel<<<(n + 31) / 32, 256, 0, st>>>(a.part[w], ctas, n, tab + (size_t)w * n, n, 0)));
+    MXB_LAUNCH("m3b_bc_final_kernel", st,
+               (m3b::m3b_bc_final_kernel<<<1, 128, 0, st>>>(p, tab + (size_t)w * n, outs[w][0], outs[w][1])));
+  }
   return check_launch("m3b_bc_bwd");
 }
 mxb_status mamba3_block_bc(const mxb_mamba3_desc* d, float eps, const void* bp, const void* cp, const float* bs,
