@@ -240,15 +240,20 @@ __device__ __forceinline__ uint4 pack8(const float* e) {
 // sum_k tile[row][c0 + k] * f[k], k < 32, for a blocked [.][128] bf16 tile in shared memory
 template <bool SW>
 __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
-  float s = 0.f;
+  // the four units are fetched first and summed in four independent chains (one chain of 32 dependent FMAs
+  // would cost ~130 cycles of latency on its own)
+  uint4 raw[4];
+#pragma unroll
+  for (int x = 0; x < 4; ++x) raw[x] = *reinterpret_cast<const uint4*>(tile + in_unit<SW>(r, (c0 >> 3) + x));
+  float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int x = 0; x < 4; ++x) {
     float e[8];
-    unpack8(*reinterpret_cast<const uint4*>(tile + in_unit<SW>(r, (c0 >> 3) + x)), e);
+    unpack8(raw[x], e);
 #pragma unroll
-    for (int y = 0; y < 8; ++y) s = fmaf(e[y], f[8 * x + y], s);
+    for (int y = 0; y < 8; ++y) s[x] = fmaf(e[y], f[8 * x + y], s[x]);
   }
-  return s;
+  return (s[0] + s[1]) + (s[2] + s[3]);
 }
 
 // ------------------------------------------------- chunk backward, part 1: state contractions

@@ -557,15 +557,19 @@ constexpr int kGradSmem = 16384 * 4 + 8192 * 5 + sizeof(ChunkScal) + (4 * Q + 4 
 
 template <bool SW>
 __device__ __forceinline__ float row_dot32_64(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
-  float acc = 0.f;  // sum_k tile[r][c0 + k] f[k] for a blocked [.][64] tile
+  // sum_k tile[r][c0 + k] f[k] for a [.][64] tile: four independent chains
+  uint4 raw[4];
+#pragma unroll
+  for (int x = 0; x < 4; ++x) raw[x] = *reinterpret_cast<const uint4*>(tile + in_unit<SW>(r, (c0 >> 3) + x, P));
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int x = 0; x < 4; ++x) {
     float e[8];
-    unpack8(*reinterpret_cast<const uint4*>(tile + in_unit<SW>(r, (c0 >> 3) + x, P)), e);
+    unpack8(raw[x], e);
 #pragma unroll
-    for (int y = 0; y < 8; ++y) acc = fmaf(e[y], f[8 * x + y], acc);
+    for (int y = 0; y < 8; ++y) acc[x] = fmaf(e[y], f[8 * x + y], acc[x]);
   }
-  return acc;
+  return (acc[0] + acc[1]) + (acc[2] + acc[3]);
 }
 
 template <bool TMA>
