@@ -36,7 +36,7 @@ WORKLOADS = {
     "gdn_block": dict(B=8, T=4096, H=16, Dk=128, Dv=128),
     "mamba3_block": dict(B=8, T=4096, D=2048, N=128, G=1, K=4),
 }
-# Algorithmic work per unit (stated in DESIGN.md).
+# Algorithmic work per unit: the bytes that must cross HBM if every intermediate stayed on chip.
 GDN_BYTES_PER_TOKEN_HEAD = 2840          # fwd 1032 + bwd read 1032 + bwd write 776
 GDN_FLOPS_PER_TOKEN_HEAD = 3 * 182955    # fwd + 2x for bwd
 M3_BYTES_PER_TOKEN = 23168

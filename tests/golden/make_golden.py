@@ -246,7 +246,9 @@ def mamba3_block_stages(ref: Path):
     print("mamba3_block_stages.json:", len(cases), "cases")
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference-checkout")
+    ref = Path(sys.argv[1])
     gdn_block_fixture(ref)
     gdn_block_stages(ref)
     gdn_torch_recurrence(ref)

@@ -94,9 +94,6 @@ def test_umma_operand_layouts():
     results = {}
     for c in cases:
         results["M%d_N%d_K%d_A:%s_B:%s" % c] = run_case(lib, *c)
-    os.makedirs("gpurun_out", exist_ok=True)
-    with open("gpurun_out/umma_selftest.json", "w") as f:
-        json.dump(results, f, indent=1)
     bad = {k: v for k, v in results.items() if not v["ok"]}
     print(json.dumps(results, indent=1))
     assert not bad, bad
