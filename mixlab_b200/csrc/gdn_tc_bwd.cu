@@ -289,7 +289,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p, c
   const bool own = lane < 16;
   const int i = 16 * (warp & 3) + (lane & 15), hc = warp >> 2;
 
-  if (tid == 0) {
+  // prologue latencies side by side: warp 0 allocates TMEM, one thread of warp 1 issues the copies, warp 2-3 fetch gam
+  if (tid == 32) {
     for (int m = 0; m < 4; ++m) tc::mbar_init(mbar + m, 1);
     tc::mbar_fence_init();
     if (TMA) {  // dO by the copy engine (swizzled tile), the workspace images by bulk copies
@@ -319,7 +320,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p, c
     tc::tmem_alloc(tslot, 256);
     tc::tmem_relinquish();
   }
-  if (tid < C) gam[tid] = p.gam[ci * C + tid];
+  if (tid >= 64 && tid < 64 + C) gam[tid - 64] = p.gam[ci * C + tid - 64];
   __syncthreads();
   const float glast = gam[C - 1], L = exp_nonpos(glast);
   if (tid < C) {
@@ -491,14 +492,25 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   const int i = 16 * (warp & 3) + (lane & 15);  // the row this thread owns in every epilogue
   const int hc = warp >> 2;  // warps 0-3 take the first half of an accumulator's columns, warps 4-7 the second
 
-  if (tid == 0) {
-    for (int m = 0; m < 4; ++m) tc::mbar_init(mbar + m, 1);
+  // The serial latencies of the prologue run side by side on different warps: warp 0 allocates TMEM, one thread
+  // each of warps 1 and 4 initialises two barriers and issues the copies that complete on them, warps 2-3 fetch
+  // the per-row scalars.
+  if (tid == 32) {
+    tc::mbar_init(mbar + 0, 1);
+    tc::mbar_init(mbar + 1, 1);
     tc::mbar_fence_init();
     if (TMA) {
       tc::mbar_expect_tx(mbar + 1, 2 * 16384 + 8192);
       tc::bulk_load(tc::smem_u32(Xdvn), p.dvn + ci * C * KD, 16384, mbar + 1);  // byte images of the operand tiles
       tc::bulk_load(tc::smem_u32(Xdw), p.dw + ci * C * KD, 16384, mbar + 1);
       tc::bulk_load(tc::smem_u32(Xt), p.Tm + ci * C * C, 8192, mbar + 1);
+    }
+  }
+  if (tid == 128) {
+    tc::mbar_init(mbar + 2, 1);
+    tc::mbar_init(mbar + 3, 1);
+    tc::mbar_fence_init();
+    if (TMA) {
       tc::mbar_expect_tx(mbar + 2, 3 * 16384 + 8192);
       for (int sl = 0; sl < 2; ++sl) {
         tc::tma_load_4d(tc::smem_u32(Xk) + 8192 * sl, &maps.k, 64 * sl, h, t0, b, mbar + 2);
@@ -543,9 +555,10 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     tc::tmem_alloc(tslot, 256);
     tc::tmem_relinquish();
   }
-  if (tid < C) {
-    gam[tid] = p.gam[ci * C + tid];
-    bet[tid] = tid < imax ? p.beta[row(tid)] : 0.f;
+  if (tid >= 64 && tid < 64 + C) {
+    const int r = tid - 64;
+    gam[r] = p.gam[ci * C + r];
+    bet[r] = r < imax ? p.beta[row(r)] : 0.f;
   }
   for (int u = tid; u < 4 * C; u += 256) csw[u] = 0.f;
   __syncthreads();
