@@ -441,11 +441,11 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p, const __grid
   const size_t ci = ((size_t)b * p.NH + head) * p.n + c;
 
   if (warp == 0) { tc::tmem_alloc(tslot, 128); tc::tmem_relinquish(); }
-  if (tid == 0) { tc::mbar_init(mbar, 1); tc::mbar_init(mbar + 1, 1); tc::mbar_fence_init(); }
+  // the thread that initialises the barriers also issues the copies, on another warp than the TMEM allocation
+  if (tid == 32) { tc::mbar_init(mbar, 1); tc::mbar_init(mbar + 1, 1); tc::mbar_fence_init(); }
   bool ok = true;
   if (TMA) {  // every operand by the copy engine, one barrier
-    __syncthreads();
-    if (tid == 0) {
+    if (tid == 32) {
       tc::mbar_expect_tx(mbar + 1, 3 * 16384 + 8192 + (uint32_t)sizeof(ChunkScal));
       for (int sl = 0; sl < 2; ++sl) {
         tc::tma_load_4d(tc::smem_u32(Bt) + 8192 * sl, &maps.b, 64 * sl, g, t0, b, mbar + 1);
@@ -455,6 +455,7 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p, const __grid
       tc::bulk_load(tc::smem_u32(Ht), p.H0 + ci * (N * P), 16384, mbar + 1);
       tc::bulk_load(tc::smem_u32(&s), p.cs + ci * (sizeof(ChunkScal) / 4), (uint32_t)sizeof(ChunkScal), mbar + 1);
     }
+    __syncthreads();  // barriers initialised before anyone waits on them
     ok = tc::mbar_wait(mbar + 1, 0);
   } else {
     issue_rows_tile(Bt, p.b, p, b, g, t0);
@@ -602,14 +603,14 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p, const __gri
   const int t = 16 * (warp & 3) + (lane & 15), hc = warp >> 2;
 
   if (warp == 0) { tc::tmem_alloc(tslot, 256); tc::tmem_relinquish(); }
-  if (tid == 0) {
+  // the thread that initialises the barriers also issues the copies, on another warp than the TMEM allocation
+  if (tid == 32) {
     for (int m = 0; m < 3; ++m) tc::mbar_init(mbar + m, 1);
     tc::mbar_fence_init();
   }
   bool ok = true;
   if (TMA) {  // every operand by the copy engine: token tiles on one barrier, the state images on another
-    __syncthreads();
-    if (tid == 0) {
+    if (tid == 32) {
       tc::mbar_expect_tx(mbar + 1, 2 * 16384 + 2 * 8192 + (uint32_t)sizeof(ChunkScal));
       for (int sl = 0; sl < 2; ++sl) {
         tc::tma_load_4d(tc::smem_u32(Bt) + 8192 * sl, &maps.b, 64 * sl, g, t0, b, mbar + 1);
@@ -634,6 +635,7 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p, const __gri
     tc::cp_async_commit();
   }
   for (int u = tid; u < 8 * Q; u += 256) { csw_e[u] = 0.f; }  // csw_e and csw_l are contiguous
+  if (TMA) __syncthreads();  // barriers initialised before anyone waits on them
   if (TMA) ok = tc::mbar_wait(mbar + 1, 0);
   else tc::cp_async_wait<1>();
   __syncthreads();
