@@ -62,15 +62,16 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
   const int imax = min(C, p.T - t0);
 
-  if (tid == 0) {
+  // prologue latencies side by side: warp 0 allocates TMEM, warp 1 reads the gates, one thread of warp 2
+  // initialises the barriers and issues the copies that complete on them
+  if (tid == 64) {
     tc::mbar_init(&mbar[0], 1);
     tc::mbar_init(&mbar[1], 1);
     tc::mbar_init(&mbar[2], 1);
     tc::mbar_fence_init();
   }
   if (TMA) {
-    __syncthreads();  // barriers initialised before the copies can complete on them
-    if (tid == 0) {
+    if (tid == 64) {
       // slab s (columns 64 s ..) of [k;q]: k box then q box; v: one box per slab
       tc::mbar_expect_tx(&mbar[1], 32768);
       for (int sl = 0; sl < 2; ++sl) {
@@ -119,8 +120,12 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
     p.gam[ci * C + 2 * lane + 1] = c1;
   }
   bool ok = true;
-  if (TMA) ok = tc::mbar_wait(&mbar[1], 0);  // [k;q]
-  else tc::cp_async_wait<1>();
+  if (TMA) {
+    __syncthreads();  // barriers initialised before anyone waits on them
+    ok = tc::mbar_wait(&mbar[1], 0);  // [k;q]
+  } else {
+    tc::cp_async_wait<1>();
+  }
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
