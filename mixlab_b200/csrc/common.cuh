@@ -72,6 +72,19 @@ __device__ __forceinline__ void colsum16(float (&v)[16], int lane) {
   colsum16_step<1, 1, 16>(v, lane);
 }
 
+// Reverse inclusive cumulative sum over 64 values by one warp, two per lane: call with a = x[63 - 2 lane],
+// b = x[62 - 2 lane]; returns in a, b the sums x[63] + ... + x[63 - 2 lane] and ... + x[62 - 2 lane].  A fixed order.
+__device__ __forceinline__ void warp_rcumsum64(float& a, float& b, int lane) {
+  float v = a + b;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += t;
+  }
+  a = v - b;
+  b = v;
+}
+
 // ---- host side ----------------------------------------------------------
 void note_launch(int n = 1);           // bumps mxb_launch_count()
 mxb_status check_launch(const char* what);  // cudaGetLastError -> status

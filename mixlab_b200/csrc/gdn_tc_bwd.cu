@@ -828,14 +828,17 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
       }
     }
   }
-  if (tid == 0) {  // dg = reverse cumulative sum of dgam within the chunk
+  if (tid < 32) {  // dg = reverse cumulative sum of dgam within the chunk: one warp, two rows per lane
     // d/dgam_last: E(gam_last) <dS, S0> (from the first kernel) and the sum of rho over the rows
-    float acc = p.ls[ci];
-    for (int wv = 0; wv < 8; ++wv) acc += red[8 + wv];
-    for (int r = C - 1; r >= 0; --r) {
-      acc += dgo[r] + dgo[C + r] + csw[r] + csw[C + r] + csw[2 * C + r] + csw[3 * C + r];
-      dgo[r] = acc;
-    }
+    float base = p.ls[ci];
+    for (int wv = 0; wv < 8; ++wv) base += red[8 + wv];
+    const int ra = C - 1 - 2 * tid, rb = ra - 1;
+    float a = dgo[ra] + dgo[C + ra] + csw[ra] + csw[C + ra] + csw[2 * C + ra] + csw[3 * C + ra];
+    float bq = dgo[rb] + dgo[C + rb] + csw[rb] + csw[C + rb] + csw[2 * C + rb] + csw[3 * C + rb];
+    warp_rcumsum64(a, bq, tid);
+    __syncwarp();  // every lane has read its rows before any lane overwrites them
+    dgo[ra] = base + a;
+    dgo[rb] = base + bq;
   }
   __syncthreads();
   if (!ok && tid == 0) atomicExch(p.status, 4);

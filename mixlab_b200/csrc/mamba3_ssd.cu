@@ -842,14 +842,16 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p, const __gri
   }
   tc::fence_before_sync();
   __syncthreads();
-  if (tid == 0) {  // dLam -> da: reverse in-chunk cumulative sum (fixed order)
+  if (tid < 32) {  // dLam -> da: reverse in-chunk cumulative sum (one warp, two rows per lane, fixed order)
     float zs = 0.f, hh = 0.f;
     for (int wv = 0; wv < 8; ++wv) { zs += red[8 + wv]; hh += red[wv]; }
-    float acc = zs + s.L * hh;  // d/dLam_end
-    for (int r = Q - 1; r >= 0; --r) {
-      acc += part[0 * Q + r] + part[4 * Q + r] + csw_l[r] + csw_l[Q + r] + csw_l[2 * Q + r] + csw_l[3 * Q + r];
-      s.Lam[r] = acc;  // Lam is dead by now: reuse for da
-    }
+    const float base = zs + s.L * hh;  // d/dLam_end
+    const int ra = Q - 1 - 2 * tid, rb = ra - 1;
+    float a = part[0 * Q + ra] + part[4 * Q + ra] + csw_l[ra] + csw_l[Q + ra] + csw_l[2 * Q + ra] + csw_l[3 * Q + ra];
+    float bq = part[0 * Q + rb] + part[4 * Q + rb] + csw_l[rb] + csw_l[Q + rb] + csw_l[2 * Q + rb] + csw_l[3 * Q + rb];
+    warp_rcumsum64(a, bq, tid);
+    s.Lam[ra] = base + a;  // Lam is dead by now: reuse for da
+    s.Lam[rb] = base + bq;
   }
   __syncthreads();
   if (!ok && tid == 0) atomicExch(p.status, 13);
