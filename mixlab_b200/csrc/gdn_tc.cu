@@ -274,15 +274,20 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   if (ok) ok = tc::mbar_wait(mbar, 1);
   tc::fence_after_sync();
   if (ok) {
-    // u and w are assembled as operand-layout images over v and [k;q] (dead once the MMA has completed)
+    // u and w are assembled as operand-layout images over v and [k;q] (dead once the MMA has completed): u in the
+    // un-swizzled K-major layout, w in the 128-byte-swizzled layout of a TMA tile (two 8 KB slabs of 64 columns), so
+    // that the state kernels can put it beside TMA-loaded q rows in one operand
     const int i = 16 * warp + (lane & 15);  // M=64: row m sits in TMEM lane (m%16) + 32*(m/16)
     for (int c0 = 0; c0 < 256; c0 += 32) {
       float f[32];
       ld_acc32(taddr, warp, c0, f);
       if (lane < 16) {
-        uint8_t* tile = (c0 < 128) ? Vt : Akq;
 #pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(tile, tc::kmajor_unit(i, ((c0 & 127) >> 3) + x, KD), pack8f(&f[8 * x]));
+        for (int x = 0; x < 4; ++x) {
+          const int c8 = ((c0 & 127) >> 3) + x;
+          if (c0 < 128) sts16(Vt, tc::kmajor_unit(i, c8, KD), pack8f(&f[8 * x]));
+          else sts16(Akq, tc::sw128_unit(i, c8), pack8f(&f[8 * x]));
+        }
       }
     }
   } else if (tid == 0) {
@@ -313,17 +318,23 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
 //   group U  u          free after epilogue 1       needed before epilogue 1
 //   group PK P and k    free after MMA2/MMA3        needed before MMA2/MMA3
 // Exactly three groups are outstanding at the top of every chunk, in the order A, U, PK.
-constexpr int kStateFwdSmem = 32768 + 32768 + 16384 + 16384 + 16384 + 16384 + 16384 + 2 * C * 4 + 64 + 128;
+//
+// TMA = true: q and k rows arrive as tensor-map boxes (128-byte swizzle) issued by ONE thread and complete on the
+// barrier of their group, like the images: no thread spends issue slots on copies (four cp.async per thread and
+// group cost every thread ~1.6 k and ~1.1 k cycles per chunk, on the critical path between an MMA and its epilogue).
+// TMA = false: the same rows by cp.async into the same swizzled positions.
+constexpr int kStateFwdSmem = 32768 + 32768 + 16384 + 16384 + 16384 + 16384 + 16384 + 2 * C * 4 + 64 + 1024;
 
-__global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
+template <bool TMA>
+__global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __grid_constant__ RowMaps maps) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
-  uint8_t* A1 = sm;                 // [128: w rows 0-63, q rows 64-127][128 kk]
+  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
+  uint8_t* A1 = sm;                 // [128: w rows 0-63, q rows 64-127][128 kk], two swizzled slabs of 64 columns
   uint8_t* Sop = A1 + 32768;        // [128 kk][128 j]   bf16 copy of the state
   uint8_t* A2 = Sop + 32768;        // [128: zero rows 0-63, P rows 64-127][64 m]
   uint8_t* Vn = A2 + 16384;         // [64 i][128 j]     v_new
   uint8_t* Vr = Vn + 16384;         // [64 i][128 j]     E(gam_last-gam_i) v_new
-  uint8_t* A3 = Vr + 16384;         // [64 i][128 kk]    k  (A = k^T)
+  uint8_t* A3 = Vr + 16384;         // [64 i][128 kk]    k  (A = k^T), two swizzled slabs of 64 columns
   uint8_t* Ut = A3 + 16384;         // [64 i][128 j]     u
   float* dd = reinterpret_cast<float*>(Ut + 16384);
   float* rr = dd + C;
@@ -338,43 +349,55 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
   auto grow = [&](int c, int i) { return ((size_t)(b * p.T + c * C + i) * p.H + h); };
   // The workspace tiles (w, u, P) are byte images of the operand layout: one bulk copy each, issued by one
   // thread, completing on an mbarrier.  The raw q and k rows come by cp.async.
+  // Slab s of A1 (columns 64 s ..): the w slab (rows 0-63), then the q box (rows 64-127).  The issuing threads sit
+  // in warps whose epilogue after the issue point is the short one (tid 64: q rows; tid 32: state update).
   auto issue_A = [&](int c) {  // [w;q] of chunk c
     if (c < p.n) {
       const size_t ci = (size_t)bh * p.n + c;
-      const int imax = min(C, p.T - c * C);
-      if (tid == 0) {
-        tc::mbar_expect_tx(&mbar[1], 16384);
-        tc::bulk_load(sA1, p.w + ci * C * KD, 16384, &mbar[1]);
+      if (tid == 64) {
+        tc::mbar_expect_tx(&mbar[1], TMA ? 32768 : 16384);
+        for (int sl = 0; sl < 2; ++sl) {
+          tc::bulk_load(sA1 + sl * 16384, p.w + ci * C * KD + sl * 4096, 8192, &mbar[1]);
+          if (TMA) tc::tma_load_4d(sA1 + sl * 16384 + 8192, &maps.q, 64 * sl, h, c * C, b, &mbar[1]);
+        }
       }
-      for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = urow16(u), c8 = ucol16(u);
-        tc::cp_async16(sA1 + 16384 + 16 * u, i < imax ? p.q + grow(c, i) * KD + c8 * 8 : p.q, i < imax);
+      if (!TMA) {
+        const int imax = min(C, p.T - c * C);
+        for (int u = tid; u < 64 * 16; u += 256) {
+          const int i = urow16(u), c8 = ucol16(u);
+          const uint32_t off = (uint32_t)(c8 >> 3) * 16384u + 8192u + (uint32_t)i * 128u + (uint32_t)(((c8 & 7) ^ (i & 7)) << 4);
+          tc::cp_async16(sA1 + off, i < imax ? p.q + grow(c, i) * KD + c8 * 8 : p.q, i < imax);
+        }
       }
     }
-    tc::cp_async_commit();
+    if (!TMA) tc::cp_async_commit();
   };
   auto issue_U = [&](int c) {
-    if (c < p.n && tid == 0) {
+    if (c < p.n && tid == 64) {
       const size_t ci = (size_t)bh * p.n + c;
       tc::mbar_expect_tx(&mbar[2], 16384);
       tc::bulk_load(sU, p.u + ci * C * KD, 16384, &mbar[2]);
     }
-    tc::cp_async_commit();  // (empty: keeps the group count of the schedule below)
+    if (!TMA) tc::cp_async_commit();  // (empty: keeps the group count of the schedule below)
   };
   auto issue_PK = [&](int c) {
     if (c < p.n) {
       const size_t ci = (size_t)bh * p.n + c;
-      const int imax = min(C, p.T - c * C);
-      if (tid == 0) {
-        tc::mbar_expect_tx(&mbar[3], 8192);
+      if (tid == 32) {
+        tc::mbar_expect_tx(&mbar[3], TMA ? 8192 + 16384 : 8192);
         tc::bulk_load(sA2 + 8192, p.P + ci * C * C, 8192, &mbar[3]);  // rows 64..127 of the [128][64] tile
+        if (TMA)
+          for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(sA3 + sl * 8192, &maps.k, 64 * sl, h, c * C, b, &mbar[3]);
       }
-      for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = urow16(u), c8 = ucol16(u);
-        tc::cp_async16(sA3 + 16 * u, i < imax ? p.k + grow(c, i) * KD + c8 * 8 : p.k, i < imax);
+      if (!TMA) {
+        const int imax = min(C, p.T - c * C);
+        for (int u = tid; u < 64 * 16; u += 256) {
+          const int i = urow16(u), c8 = ucol16(u);
+          tc::cp_async16(sA3 + tc::sw128_unit(i, c8), i < imax ? p.k + grow(c, i) * KD + c8 * 8 : p.k, i < imax);
+        }
       }
     }
-    tc::cp_async_commit();
+    if (!TMA) tc::cp_async_commit();
   };
 
   if (warp == 0) {
@@ -433,14 +456,14 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       sts16(Sop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's v_new image has left its tile
-    tc::cp_async_wait<2>();  // group A of this chunk has landed (q rows; the w image on its barrier)
+    if (!TMA) tc::cp_async_wait<2>();  // group A of this chunk has landed (q rows; the images on the barrier)
     ok = tc::mbar_wait(&mbar[1], lph);
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     if (tid == 0) {  // D1 = [w;q] S
-      tc::issue_gemm(taddr, tc::kmajor_tile(A1, KD), tc::mnmajor_tile(Sop, KD), 128, KD, KD, false);
+      tc::issue_gemm(taddr, tc::kmajor_sw128_tile(A1, 16384), tc::mnmajor_tile(Sop, KD), 128, KD, KD, false);
       tc::mma_commit(mbar);
       if (p.save) {  // the state at chunk start, saved for the backward as the byte image of the operand tile
         tc::bulk_store(p.hs + ci * KD * KD, tc::smem_u32(Sop), 32768);
@@ -483,7 +506,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
       }
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the state image has left its tile
-    tc::cp_async_wait<1>();  // group PK of this chunk (group A of the next one may still fly)
+    if (!TMA) tc::cp_async_wait<1>();  // group PK of this chunk (group A of the next one may still fly)
     if (ok) ok = tc::mbar_wait(&mbar[3], lph);
     tc::fence_async_smem();
     tc::fence_before_sync();
@@ -493,7 +516,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
     if (ok && tid == 0) {
       // D2 = [0;P] v_new          D3 = k^T (r v_new)
       tc::issue_gemm(taddr + 128, tc::kmajor_tile(A2, C), tc::mnmajor_tile(Vn, KD), 128, KD, C, false);
-      tc::issue_gemm(taddr + 256, tc::mnmajor_tile(A3, KD), tc::mnmajor_tile(Vr, KD), 128, KD, C, false);
+      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(A3, 8192), tc::mnmajor_tile(Vr, KD), 128, KD, C, false);
       tc::mma_commit(mbar);
       if (p.save) {
         tc::bulk_store(p.vn + ci * C * KD, tc::smem_u32(Vn), 16384);
@@ -529,7 +552,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p) {
     }
     tc::fence_before_sync();
   }
-  tc::cp_async_wait<0>();
+  if (!TMA) tc::cp_async_wait<0>();
   if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 2);
   if (ok && p.hT) {
@@ -652,9 +675,15 @@ mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
   }
   mxb_status s = check_launch("gdn_tc_prep_kernel");
   if (s != MXB_OK) return s;
-  if (tc_set_smem(gdn_tc_state_fwd_kernel, kStateFwdSmem) != MXB_OK) return MXB_ERR_CUDA;
-  MXB_LAUNCH("gdn_tc_state_fwd_kernel", st,
-             (gdn_tc_state_fwd_kernel<<<dim3(p.B * p.H), 256, kStateFwdSmem, st>>>(p)));
+  if (tma) {
+    if (tc_set_smem(gdn_tc_state_fwd_kernel<true>, kStateFwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_state_fwd_kernel", st,
+               (gdn_tc_state_fwd_kernel<true><<<dim3(p.B * p.H), 256, kStateFwdSmem, st>>>(p, maps)));
+  } else {
+    if (tc_set_smem(gdn_tc_state_fwd_kernel<false>, kStateFwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_state_fwd_kernel", st,
+               (gdn_tc_state_fwd_kernel<false><<<dim3(p.B * p.H), 256, kStateFwdSmem, st>>>(p, maps)));
+  }
   return check_launch("gdn_tc_state_fwd_kernel");
 }
 

@@ -30,16 +30,22 @@ namespace mxb {
 //   group A  k, P, dO, q   buffers free after the first MMA batch
 //   group B  w             free after the second MMA batch
 // Two groups are outstanding at the top of every chunk, in the order A, B.
-constexpr int kStateBwdSmem = 16384 + 32768 + 8192 + 16384 + 32768 + 32768 + 2 * C * 4 + 64 + 128;
+//
+// TMA = true: the k, dO and q rows arrive as tensor-map boxes (128-byte swizzle, two 8 KB slabs of 64 columns per
+// tile) issued by one thread on the barrier of group A; TMA = false: by cp.async into the same swizzled positions
+// (twelve copies per thread and chunk, on the critical path between the MMA and its epilogue).  The w image is
+// stored in the same swizzled layout by the prep kernel.
+constexpr int kStateBwdSmem = 16384 + 32768 + 8192 + 16384 + 32768 + 32768 + 2 * C * 4 + 64 + 1024;
 
-__global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
+template <bool TMA>
+__global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __grid_constant__ RowMaps maps) {
   extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((128u - (tc::smem_u32(raw) & 127u)) & 127u);
-  uint8_t* Ak = sm;                 // [64 i][128 kk]      k
+  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
+  uint8_t* Ak = sm;                 // [64 i][128 kk]      k  (swizzled slabs)
   uint8_t* dSop = Ak + 16384;       // [128 kk][128 j]     bf16 copy of dS
   uint8_t* Pt = dSop + 32768;       // [64 m][64 i]        P   (A = P^T: contraction over rows)
-  uint8_t* dOop = Pt + 8192;        // [64 m][128 j]       dO
-  uint8_t* Aqw = dOop + 16384;      // [128: q rows, w rows][128 kk]   (A = [q^T | w^T])
+  uint8_t* dOop = Pt + 8192;        // [64 m][128 j]       dO (swizzled slabs)
+  uint8_t* Aqw = dOop + 16384;      // [q rows | w rows][128 kk], each half in swizzled slabs   (A = [q^T | w^T])
   uint8_t* Bdd = Aqw + 32768;       // [128: d dO rows, -dv_new rows][128 j]
   float* dd = reinterpret_cast<float*>(Bdd + 32768);
   float* rr = dd + C;
@@ -55,29 +61,39 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
   auto issue_A = [&](int c) {
     if (c >= 0) {
       const size_t ci = (size_t)bh * p.n + c;
-      const int imax = min(C, p.T - c * C);
-      for (int u = tid; u < 64 * 16; u += 256) {
-        const int i = urow16(u), c8 = ucol16(u);
-        const bool v = i < imax;
-        const size_t g = v ? grow(c, i) * KD + c8 * 8 : 0;
-        tc::cp_async16(sAk + 16 * u, p.k + g, v);
-        tc::cp_async16(sdO + 16 * u, p.dO + g, v);
-        tc::cp_async16(sAqw + 16 * u, p.q + g, v);
+      if (!TMA) {
+        const int imax = min(C, p.T - c * C);
+        for (int u = tid; u < 64 * 16; u += 256) {
+          const int i = urow16(u), c8 = ucol16(u);
+          const bool v = i < imax;
+          const size_t g = v ? grow(c, i) * KD + c8 * 8 : 0;
+          const uint32_t off = tc::sw128_unit(i, c8);
+          tc::cp_async16(sAk + off, p.k + g, v);
+          tc::cp_async16(sdO + off, p.dO + g, v);
+          tc::cp_async16(sAqw + off, p.q + g, v);
+        }
       }
-      if (tid == 0) {  // P is a byte image of its operand tile: one bulk copy, completing on its barrier
-        tc::mbar_expect_tx(&mbar[1], 8192);
+      if (tid == 32) {  // P is a byte image of its operand tile: one bulk copy, completing on the group's barrier
+        tc::mbar_expect_tx(&mbar[1], TMA ? 8192 + 3 * 16384 : 8192);
         tc::bulk_load(sPt, p.P + ci * C * C, 8192, &mbar[1]);
+        if (TMA) {
+          for (int sl = 0; sl < 2; ++sl) {
+            tc::tma_load_4d(sAk + sl * 8192, &maps.k, 64 * sl, h, c * C, b, &mbar[1]);
+            tc::tma_load_4d(sdO + sl * 8192, &maps.dO, 64 * sl, h, c * C, b, &mbar[1]);
+            tc::tma_load_4d(sAqw + sl * 8192, &maps.q, 64 * sl, h, c * C, b, &mbar[1]);
+          }
+        }
       }
     }
-    tc::cp_async_commit();
+    if (!TMA) tc::cp_async_commit();
   };
   auto issue_B = [&](int c) {
-    if (c >= 0 && tid == 0) {
+    if (c >= 0 && tid == 32) {
       const size_t ci = (size_t)bh * p.n + c;
       tc::mbar_expect_tx(&mbar[2], 16384);
-      tc::bulk_load(sAqw + 16384, p.w + ci * C * KD, 16384, &mbar[2]);  // rows 64..127 of the [128][128] tile
+      tc::bulk_load(sAqw + 16384, p.w + ci * C * KD, 16384, &mbar[2]);  // the second half of the tile
     }
-    tc::cp_async_commit();  // (empty: keeps the group count of the schedule)
+    if (!TMA) tc::cp_async_commit();  // (empty: keeps the group count of the schedule)
   };
 
   if (warp == 0) {
@@ -132,22 +148,22 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
       sts16(dSop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's -dv_new image has left its tile
-    tc::cp_async_wait<1>();  // group A of this chunk (k, dO, q rows; the P image on its barrier)
+    if (!TMA) tc::cp_async_wait<1>();  // group A of this chunk (k, dO, q rows; the images on the barrier)
     ok = tc::mbar_wait(&mbar[1], lph);
     __syncthreads();         // dO tile and dd visible to every thread
     for (int u = tid; u < 64 * 16; u += 256) {  // d dO
       const int i = urow16(u), c8 = ucol16(u);
-      const uint32_t off = tc::kmajor_unit(i, c8, KD);
-      sts16(Bdd, off, tc::scale_bf16x8(*reinterpret_cast<const uint4*>(dOop + off), dd[i]));
+      sts16(Bdd, tc::kmajor_unit(i, c8, KD),
+            tc::scale_bf16x8(*reinterpret_cast<const uint4*>(dOop + tc::sw128_unit(i, c8)), dd[i]));
     }
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     if (tid == 0) {
-      tc::issue_gemm(taddr, tc::kmajor_tile(Ak, KD), tc::mnmajor_tile(dSop, KD), 64, KD, KD, false);          // k dS
-      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Pt, C), tc::mnmajor_tile(dOop, KD), 64, KD, C, false);     // P^T dO
-      tc::issue_gemm(taddr + 256, tc::mnmajor_tile(Aqw, KD), tc::mnmajor_tile(Bdd, KD), 128, KD, C, false);   // q^T (d dO)
+      tc::issue_gemm(taddr, tc::kmajor_sw128_tile(Ak, 8192), tc::mnmajor_tile(dSop, KD), 64, KD, KD, false);         // k dS
+      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Pt, C), tc::mnmajor_sw128_tile(dOop, 8192), 64, KD, C, false);    // P^T dO
+      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(Aqw, 8192), tc::mnmajor_tile(Bdd, KD), 128, KD, C, false);  // q^T (d dO)
       tc::mma_commit(mbar);
       tc::bulk_store(p.dhs + ci * KD * KD, tc::smem_u32(dSop), 32768);  // dS at chunk end, as the operand-tile image
       tc::bulk_commit();
@@ -184,7 +200,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
     __syncthreads();
     tc::fence_after_sync();
     if (ok && tid == 0) {  // ... - w^T dv_new
-      tc::issue_gemm(taddr + 256, tc::skip_k(tc::mnmajor_tile(Aqw, KD), 64), tc::skip_k(tc::mnmajor_tile(Bdd, KD), 64),
+      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(Aqw + 16384, 8192), tc::skip_k(tc::mnmajor_tile(Bdd, KD), 64),
                      128, KD, C, true);
       tc::mma_commit(mbar);
       tc::bulk_store(p.dvn + ci * C * KD, tc::smem_u32(Bdd) + 16384, 16384);  // -dv_new: rows 64..127 of the operand tile
@@ -206,7 +222,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p) {
     }
     tc::fence_before_sync();
   }
-  tc::cp_async_wait<0>();
+  if (!TMA) tc::cp_async_wait<0>();
   if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 3);
   if (ok && p.dh0) {
@@ -880,16 +896,22 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
     p.hT = keep_hT;
     if (s != MXB_OK) return s;
   }
-  if (bwd_set_smem(gdn_tc_state_bwd_kernel, kStateBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
-  MXB_LAUNCH("gdn_tc_state_bwd_kernel", st,
-             (gdn_tc_state_bwd_kernel<<<dim3(p.B * p.H), 256, kStateBwdSmem, st>>>(p)));
-  s = check_launch("gdn_tc_state_bwd_kernel");
-  if (s != MXB_OK) return s;
   RowMaps maps;
   std::memset(&maps, 0, sizeof maps);
   const bool tma = !p.no_tma && make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, KD) &&
                    make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, KD) &&
                    make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, KD);
+  if (tma) {
+    if (bwd_set_smem(gdn_tc_state_bwd_kernel<true>, kStateBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_state_bwd_kernel", st,
+               (gdn_tc_state_bwd_kernel<true><<<dim3(p.B * p.H), 256, kStateBwdSmem, st>>>(p, maps)));
+  } else {
+    if (bwd_set_smem(gdn_tc_state_bwd_kernel<false>, kStateBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+    MXB_LAUNCH("gdn_tc_state_bwd_kernel", st,
+               (gdn_tc_state_bwd_kernel<false><<<dim3(p.B * p.H), 256, kStateBwdSmem, st>>>(p, maps)));
+  }
+  s = check_launch("gdn_tc_state_bwd_kernel");
+  if (s != MXB_OK) return s;
   if (tma) {
     if (bwd_set_smem(gdn_tc_chunk_bwd_state_kernel<true>, kChunkBwdStateSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("gdn_tc_chunk_bwd_state_kernel", st,

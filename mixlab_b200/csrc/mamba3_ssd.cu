@@ -47,6 +47,7 @@ struct SsdP {
   float *dt, *lam, *phi;        // [B,NH,T]
   bf16 *H0, *dH1;               // [B,NH,n,N,P] state at chunk start / state gradient at chunk end
   float *dphi, *da, *de, *dgam; // [B,NH,T] per-token scalar gradients
+  float* dal_part;              // [B,NH] per-batch shares of da_log
   float* cs;                    // [B,NH,n] ChunkScal records
   bf16 *pb, *pc;                // [B,NH,T,N] per-head partial dB, dC (summed in fp32 by the reduce kernel)
 };
@@ -251,33 +252,76 @@ struct ChunkMaps {
   CUtensorMap x, dy;  // [B,T,heads,64] viewed as (P, heads, T, B)
 };
 
+// Inclusive prefix sum of one double per thread over a 256-thread CTA (warp scans + the eight warp totals, a fixed
+// order); wtot is 8 doubles of shared memory.  Also returns the CTA total.
+__device__ __forceinline__ double cta_scan256(double v, double* wtot, double& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const double t = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += t;
+  }
+  if (lane == 31) wtot[warp] = v;
+  __syncthreads();
+  double off = 0.0, tot = 0.0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    const double x = wtot[w];
+    if (w < warp) off += x;
+    tot += x;
+  }
+  total = tot;
+  return v + off;
+}
+
 // ------------------------------------------------------------ per-(b,head) scalars
+constexpr int kScalBatch = 8;
 __global__ void __launch_bounds__(256) m3s_scalars_kernel(SsdP p) {
-  __shared__ double part[256];
+  __shared__ double wtot[8];
   const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   const size_t base = ((size_t)b * p.NH + head) * p.T;
   const int per = (p.T + 255) / 256, lo = tid * per, hi = min(p.T, lo + per);
+  // Batches of kScalBatch steps: all loads of a batch are issued before its first store (a store in between would
+  // pin the order, since the compiler cannot prove the arrays distinct, and every step would pay a full memory latency).
   double acc = 0.0;
-  for (int t = lo; t < hi; ++t) {
-    const size_t r = ((size_t)b * p.T + t) * p.NH + head;
-    const float dt = softplus_f(p.dt_raw[r]);
-    p.dt[base + t] = dt;
-    p.lam[base + t] = sigmoid_f(p.lam_raw[r]);
-    acc += (double)dt * (double)p.theta[r];
+  for (int t0 = lo; t0 < hi; t0 += kScalBatch) {
+    float draw[kScalBatch], lraw[kScalBatch], th[kScalBatch];
+#pragma unroll
+    for (int x = 0; x < kScalBatch; ++x) {
+      const int t = min(t0 + x, hi - 1);
+      const size_t r = ((size_t)b * p.T + t) * p.NH + head;
+      draw[x] = __ldg(p.dt_raw + r);
+      lraw[x] = __ldg(p.lam_raw + r);
+      th[x] = __ldg(p.theta + r);
+    }
+#pragma unroll
+    for (int x = 0; x < kScalBatch; ++x) {
+      if (t0 + x < hi) {
+        const float dt = softplus_f(draw[x]);
+        p.dt[base + t0 + x] = dt;
+        p.lam[base + t0 + x] = sigmoid_f(lraw[x]);
+        acc += (double)dt * (double)th[x];
+      }
+    }
   }
-  part[tid] = acc;
-  __syncthreads();
-  if (tid == 0) {
-    double run = 0.0;
-    for (int i = 0; i < 256; ++i) { const double v = part[i]; part[i] = run; run += v; }
-  }
-  __syncthreads();
-  double phi = part[tid];
-  const double two_pi = 6.283185307179586476925;
-  for (int t = lo; t < hi; ++t) {
-    const size_t r = ((size_t)b * p.T + t) * p.NH + head;
-    phi += (double)p.dt[base + t] * (double)p.theta[r];
-    p.phi[base + t] = (float)(phi - two_pi * rint(phi / two_pi));
+  double total;
+  double phi = cta_scan256(acc, wtot, total) - acc;  // angle at the start of this thread's steps
+  const double two_pi = 6.283185307179586476925, inv_two_pi = 1.0 / two_pi;
+  for (int t0 = lo; t0 < hi; t0 += kScalBatch) {
+    float dtv[kScalBatch], th[kScalBatch];
+#pragma unroll
+    for (int x = 0; x < kScalBatch; ++x) {
+      const int t = min(t0 + x, hi - 1);
+      dtv[x] = p.dt[base + t];
+      th[x] = __ldg(p.theta + ((size_t)b * p.T + t) * p.NH + head);
+    }
+#pragma unroll
+    for (int x = 0; x < kScalBatch; ++x) {
+      if (t0 + x < hi) {
+        phi += (double)dtv[x] * (double)th[x];
+        p.phi[base + t0 + x] = (float)(phi - two_pi * rint(phi * inv_two_pi));  // wrapped to [-pi, pi]
+      }
+    }
   }
 }
 
@@ -868,36 +912,59 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p, const __gri
 
 // ------------------------------------------------------------ final per-token scalars
 __global__ void __launch_bounds__(256) m3s_final_kernel(SsdP p) {
-  __shared__ double part[256];
+  __shared__ double wtot[8];
   __shared__ float wsum[8];
   const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   const size_t base = ((size_t)b * p.NH + head) * p.T;
   const float A = -expf(p.a_log[head]);
   const int per = (p.T + 255) / 256, lo = tid * per, hi = min(p.T, lo + per);
   double acc = 0.0;
-  for (int t = lo; t < hi; ++t) acc += (double)p.dphi[base + t];
-  part[tid] = acc;
-  __syncthreads();
-  if (tid == 0) {  // exclusive suffix sums of the per-thread totals
-    double run = 0.0;
-    for (int i = 255; i >= 0; --i) { const double v = part[i]; part[i] = run; run += v; }
+  for (int t0 = lo; t0 < hi; t0 += kScalBatch) {
+    float v[kScalBatch];
+#pragma unroll
+    for (int x = 0; x < kScalBatch; ++x) v[x] = t0 + x < hi ? p.dphi[base + t0 + x] : 0.f;
+#pragma unroll
+    for (int x = 0; x < kScalBatch; ++x) acc += (double)v[x];
   }
-  __syncthreads();
-  double suf = part[tid];
+  double total;
+  const double incl = cta_scan256(acc, wtot, total);
+  double suf = total - incl;  // sum over the threads after this one (exclusive suffix; exact enough in fp64)
   float dal = 0.f;
-  for (int t = hi - 1; t >= lo; --t) {
-    suf += (double)p.dphi[base + t];
-    const float dinc = (float)suf;
-    const size_t r = ((size_t)b * p.T + t) * p.NH + head;
-    const float dt = p.dt[base + t], lam = p.lam[base + t], th = p.theta[r];
-    const float dgam = p.dgam[base + t] + p.de[base + t];
-    const float dnxt = t > 0 ? p.de[base + t - 1] : 0.f;
-    const float da = p.da[base + t];
-    const float ddelta = A * da + lam * dgam + (1.f - lam) * dnxt + th * dinc;
-    p.ddt[r] = ddelta * sigmoid_f(p.dt_raw[r]);
-    p.dlam[r] = dt * (dgam - dnxt) * lam * (1.f - lam);
-    p.dtheta[r] = dt * dinc;
-    dal = fmaf(dt, da, dal);
+  // backwards over this thread's steps, kFinalBatch at a time with the loads of a batch ahead of its stores
+  constexpr int kFinalBatch = 4;
+  for (int t1 = hi - 1; t1 >= lo; t1 -= kFinalBatch) {
+    float dph[kFinalBatch], dtv[kFinalBatch], lamv[kFinalBatch], thv[kFinalBatch], dgv[kFinalBatch], dev[kFinalBatch],
+        dnv[kFinalBatch], dav[kFinalBatch], drw[kFinalBatch];
+#pragma unroll
+    for (int x = 0; x < kFinalBatch; ++x) {
+      const int t = max(t1 - x, lo);
+      const size_t r = ((size_t)b * p.T + t) * p.NH + head;
+      dph[x] = p.dphi[base + t];
+      dtv[x] = p.dt[base + t];
+      lamv[x] = p.lam[base + t];
+      thv[x] = __ldg(p.theta + r);
+      drw[x] = __ldg(p.dt_raw + r);
+      dgv[x] = p.dgam[base + t];
+      dev[x] = p.de[base + t];
+      dnv[x] = t > 0 ? p.de[base + t - 1] : 0.f;
+      dav[x] = p.da[base + t];
+    }
+#pragma unroll
+    for (int x = 0; x < kFinalBatch; ++x) {
+      const int t = t1 - x;
+      if (t >= lo) {
+        suf += (double)dph[x];
+        const float dinc = (float)suf;
+        const size_t r = ((size_t)b * p.T + t) * p.NH + head;
+        const float dt = dtv[x], lam = lamv[x];
+        const float dgam = dgv[x] + dev[x], dnxt = dnv[x], da = dav[x];
+        const float ddelta = A * da + lam * dgam + (1.f - lam) * dnxt + thv[x] * dinc;
+        p.ddt[r] = ddelta * sigmoid_f(drw[x]);
+        p.dlam[r] = dt * (dgam - dnxt) * lam * (1.f - lam);
+        p.dtheta[r] = dt * dinc;
+        dal = fmaf(dt, da, dal);
+      }
+    }
   }
   dal = warp_sum(dal);
   if ((tid & 31) == 0) wsum[tid >> 5] = dal;
@@ -905,8 +972,15 @@ __global__ void __launch_bounds__(256) m3s_final_kernel(SsdP p) {
   if (tid == 0) {
     float tot = 0.f;
     for (int i = 0; i < 8; ++i) tot += wsum[i];
-    atomicAdd(&p.da_log[head], A * tot);  // sum over the batch
+    p.dal_part[b * p.NH + head] = A * tot;  // summed over the batch in a fixed order by m3s_dalog_kernel
   }
+}
+__global__ void m3s_dalog_kernel(SsdP p) {
+  const int head = blockIdx.x * blockDim.x + threadIdx.x;
+  if (head >= p.NH) return;
+  float s = 0.f;
+  for (int b = 0; b < p.B; ++b) s += p.dal_part[b * p.NH + head];
+  p.da_log[head] = s;
 }
 
 // dB[b,t,g,:] = sum over the heads of group g of the per-head partial rows (fp32, fixed order).
@@ -959,6 +1033,7 @@ static size_t carve_ssd(SsdP& p, void* ws, bool bwd) {
     p.da = cv.take<float>(bh * p.T);
     p.de = cv.take<float>(bh * p.T);
     p.dgam = cv.take<float>(bh * p.T);
+    p.dal_part = cv.take<float>(bh);
     p.pb = cv.take<m3s::bf16>(bh * p.T * m3s::N);
     p.pc = cv.take<m3s::bf16>(bh * p.T * m3s::N);
   }
@@ -1064,7 +1139,6 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
     mxb_status s = ssd_forward(p, st);
     if (s != MXB_OK) return s;
   }
-  if (cudaMemsetAsync(da_log, 0, (size_t)p.NH * sizeof(float), st) != cudaSuccess) return MXB_ERR_CUDA;
   const dim3 gc(p.n, p.NH, p.B);
   mxb_status ps = ssd_state_pass(p, 1, st);
   if (ps != MXB_OK) return ps;
@@ -1077,6 +1151,7 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
     MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<false><<<gc, 256, m3s::kGradSmem, st>>>(p, maps)));
   }
   MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
+  MXB_LAUNCH("m3s_dalog_kernel", st, (m3s::m3s_dalog_kernel<<<(p.NH + 127) / 128, 128, 0, st>>>(p)));
   MXB_LAUNCH("m3s_reduce_kernel", st,
              (m3s::m3s_reduce_kernel<<<dim3((p.T + 3) / 4, p.G, p.B), 128, 0, st>>>(p.pb, p.pc, static_cast<m3s::bf16*>(db),
                                                                             static_cast<m3s::bf16*>(dc), p.T, p.G, p.NH)));
