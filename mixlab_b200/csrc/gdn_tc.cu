@@ -311,40 +311,43 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
 
 // ------------------------------------------------------------ state forward
 // One CTA (256 threads) per (batch, head).  Thread t owns state row kk = t & 127 and the
-// 64 columns of half t >> 7.  The operands of chunk c+1 are fetched with cp.async as soon
-// as the MMA that last read the buffer for chunk c has completed, so their latency hides
-// behind the epilogues and MMAs of chunk c:
-//   group A  [w;q]      buffer free after MMA1      needed before MMA1 of the next chunk
+// 64 columns of half t >> 7.  The operand tiles are double-buffered (buffer c & 1 for chunk c): the operands of
+// chunk c+2 are requested as soon as the MMA (or epilogue) that last read the buffer for chunk c has finished, so
+// a copy has more than a whole chunk period to land (a chunk takes ~2.5 us, a copy from HBM up to ~1.5 us):
+//   group A  [w;q]      buffer free after MMA1      needed before MMA1
 //   group U  u          free after epilogue 1       needed before epilogue 1
-//   group PK P and k    free after MMA2/MMA3        needed before MMA2/MMA3
-// Exactly three groups are outstanding at the top of every chunk, in the order A, U, PK.
+//   group PK P and k    free after MMA2/MMA3        needed in the shadow of MMA1 (k is scaled in place there)
+// Six groups are outstanding at the top of every chunk, in the order A, U, PK (chunk c), A, U, PK (chunk c+1).
 //
 // TMA = true: q and k rows arrive as tensor-map boxes (128-byte swizzle) issued by ONE thread and complete on the
 // barrier of their group, like the images: no thread spends issue slots on copies (four cp.async per thread and
 // group cost every thread ~1.6 k and ~1.1 k cycles per chunk, on the critical path between an MMA and its epilogue).
 // TMA = false: the same rows by cp.async into the same swizzled positions.
-constexpr int kStateFwdSmem = 32768 + 32768 + 16384 + 16384 + 16384 + 16384 + 16384 + 2 * C * 4 + 64 + 1024;
+constexpr int kStateFwdSmem = 2 * 32768 + 32768 + 2 * 16384 + 16384 + 16384 + 2 * 16384 + 2 * 16384 + 2 * C * 4 + 128 + 1024;
 
 template <bool TMA>
 __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __grid_constant__ RowMaps maps) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
-  uint8_t* A1 = sm;                 // [128: w rows 0-63, q rows 64-127][128 kk], two swizzled slabs of 64 columns
-  uint8_t* Sop = A1 + 32768;        // [128 kk][128 j]   bf16 copy of the state
-  uint8_t* A2 = Sop + 32768;        // [128: zero rows 0-63, P rows 64-127][64 m]
-  uint8_t* Vn = A2 + 16384;         // [64 i][128 j]     v_new
-  uint8_t* Vr = Vn + 16384;         // [64 i][128 j]     E(gam_last-gam_i) v_new
-  uint8_t* A3 = Vr + 16384;         // [64 i][128 kk]    k  (A = k^T), two swizzled slabs of 64 columns
-  uint8_t* Ut = A3 + 16384;         // [64 i][128 j]     u
-  float* dd = reinterpret_cast<float*>(Ut + 16384);
+  uint8_t* A1 = sm;                 // x2 [128: w rows 0-63, q rows 64-127][128 kk], two swizzled slabs of 64 columns
+  uint8_t* Sop = A1 + 2 * 32768;    // [128 kk][128 j]   bf16 copy of the state
+  uint8_t* A2 = Sop + 32768;        // x2 [128: zero rows 0-63, P rows 64-127][64 m]
+  uint8_t* Vn = A2 + 2 * 16384;     // [64 i][128 j]     v_new
+  uint8_t* Ot = Vn + 16384;         // [64 i][128 j]     output tile on its way out (two swizzled slabs)
+  uint8_t* A3 = Ot + 16384;         // x2 [64 i][128 kk] k, then diag(E(gam_last-gam_i)) k  (A = k^T), swizzled slabs
+  uint8_t* Ut = A3 + 2 * 16384;     // x2 [64 i][128 j]  u
+  float* dd = reinterpret_cast<float*>(Ut + 2 * 16384);
   float* rr = dd + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);  // [0] MMA completion, [1] w, [2] u, [3] P images landed
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
+  // [0] MMA completion; per buffer: [1 + buf] w image and q rows, [3 + buf] u image, [5 + buf] P image and k rows landed
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int kk = tid & 127, half = tid >> 7, j0 = 64 * half;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-  const uint32_t sA1 = tc::smem_u32(A1), sA2 = tc::smem_u32(A2), sA3 = tc::smem_u32(A3), sU = tc::smem_u32(Ut);
+  const uint32_t sA1b = tc::smem_u32(A1), sA2b = tc::smem_u32(A2), sA3b = tc::smem_u32(A3), sUb = tc::smem_u32(Ut);
+  const uint32_t sOt = tc::smem_u32(Ot);
+  constexpr int kOutThread = 96;  // hands the output tiles to the copy engine (its own bulk-group queue)
 
   auto grow = [&](int c, int i) { return ((size_t)(b * p.T + c * C + i) * p.H + h); };
   // The workspace tiles (w, u, P) are byte images of the operand layout: one bulk copy each, issued by one
@@ -354,11 +357,13 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
   auto issue_A = [&](int c) {  // [w;q] of chunk c
     if (c < p.n) {
       const size_t ci = (size_t)bh * p.n + c;
+      const uint32_t sA1 = sA1b + (c & 1) * 32768;
+      uint64_t* mb = &mbar[1 + (c & 1)];
       if (tid == 64) {
-        tc::mbar_expect_tx(&mbar[1], TMA ? 32768 : 16384);
+        tc::mbar_expect_tx(mb, TMA ? 32768 : 16384);
         for (int sl = 0; sl < 2; ++sl) {
-          tc::bulk_load(sA1 + sl * 16384, p.w + ci * C * KD + sl * 4096, 8192, &mbar[1]);
-          if (TMA) tc::tma_load_4d(sA1 + sl * 16384 + 8192, &maps.q, 64 * sl, h, c * C, b, &mbar[1]);
+          tc::bulk_load(sA1 + sl * 16384, p.w + ci * C * KD + sl * 4096, 8192, mb);
+          if (TMA) tc::tma_load_4d(sA1 + sl * 16384 + 8192, &maps.q, 64 * sl, h, c * C, b, mb);
         }
       }
       if (!TMA) {
@@ -375,19 +380,21 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
   auto issue_U = [&](int c) {
     if (c < p.n && tid == 64) {
       const size_t ci = (size_t)bh * p.n + c;
-      tc::mbar_expect_tx(&mbar[2], 16384);
-      tc::bulk_load(sU, p.u + ci * C * KD, 16384, &mbar[2]);
+      tc::mbar_expect_tx(&mbar[3 + (c & 1)], 16384);
+      tc::bulk_load(sUb + (c & 1) * 16384, p.u + ci * C * KD, 16384, &mbar[3 + (c & 1)]);
     }
     if (!TMA) tc::cp_async_commit();  // (empty: keeps the group count of the schedule below)
   };
   auto issue_PK = [&](int c) {
     if (c < p.n) {
       const size_t ci = (size_t)bh * p.n + c;
+      const uint32_t sA2 = sA2b + (c & 1) * 16384, sA3 = sA3b + (c & 1) * 16384;
+      uint64_t* mb = &mbar[5 + (c & 1)];
       if (tid == 32) {
-        tc::mbar_expect_tx(&mbar[3], TMA ? 8192 + 16384 : 8192);
-        tc::bulk_load(sA2 + 8192, p.P + ci * C * C, 8192, &mbar[3]);  // rows 64..127 of the [128][64] tile
+        tc::mbar_expect_tx(mb, TMA ? 8192 + 16384 : 8192);
+        tc::bulk_load(sA2 + 8192, p.P + ci * C * C, 8192, mb);  // rows 64..127 of the [128][64] tile
         if (TMA)
-          for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(sA3 + sl * 8192, &maps.k, 64 * sl, h, c * C, b, &mbar[3]);
+          for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(sA3 + sl * 8192, &maps.k, 64 * sl, h, c * C, b, mb);
       }
       if (!TMA) {
         const int imax = min(C, p.T - c * C);
@@ -405,13 +412,15 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
     tc::tmem_relinquish();
   }
   if (tid == 0) {
-    for (int m = 0; m < 4; ++m) tc::mbar_init(&mbar[m], 1);
+    for (int m = 0; m < 7; ++m) tc::mbar_init(&mbar[m], 1);
     tc::mbar_fence_init();
   }
   __syncthreads();  // barriers initialised before the copies can complete on them
-  issue_A(0);
-  issue_U(0);
-  issue_PK(0);
+  for (int c = 0; c < 2; ++c) {
+    issue_A(c);
+    issue_U(c);
+    issue_PK(c);
+  }
   float S[64];  // state row kk, columns j0 .. j0+63
   if (p.h0) {
     const float4* src = reinterpret_cast<const float4*>(p.h0 + ((size_t)bh * KD + kk) * KD + j0);
@@ -424,7 +433,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
 #pragma unroll
     for (int x = 0; x < 64; ++x) S[x] = 0.f;
   }
-  for (int u = tid; u < 64 * 8; u += 256) sts16(A2, tc::kmajor_unit(u >> 3, u & 7, C), zero16());
+  for (int u = tid; u < 2 * 64 * 8; u += 256)  // the zero rows of both [0;P] tiles
+    sts16(A2 + (u >> 9) * 16384, tc::kmajor_unit((u >> 3) & 63, u & 7, C), zero16());
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -438,7 +448,12 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
   for (int c = 0; c < p.n && ok; ++c) {
     const size_t ci = (size_t)bh * p.n + c;
     const int t0 = c * C, imax = min(C, p.T - t0);
-    const uint32_t lph = c & 1;  // phase of the image barriers
+    const int buf = c & 1;
+    const uint32_t lph = (c >> 1) & 1;  // phase of the image barriers of this buffer
+    uint8_t* A1c = A1 + buf * 32768;
+    uint8_t* A2c = A2 + buf * 16384;
+    uint8_t* A3c = A3 + buf * 16384;
+    uint8_t* Utc = Ut + buf * 16384;
     const float glast = gl_nxt, g = g_nxt;
     if (c + 1 < p.n) {
       g_nxt = p.gam[(ci + 1) * C + (tid & 63)];
@@ -456,67 +471,73 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
       sts16(Sop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's v_new image has left its tile
-    if (!TMA) tc::cp_async_wait<2>();  // group A of this chunk has landed (q rows; the images on the barrier)
-    ok = tc::mbar_wait(&mbar[1], lph);
+    if (!TMA) tc::cp_async_wait<5>();  // group A of this chunk has landed (q rows; the images on the barrier)
+    ok = tc::mbar_wait(&mbar[1 + buf], lph);
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     if (tid == 0) {  // D1 = [w;q] S
-      tc::issue_gemm(taddr, tc::kmajor_sw128_tile(A1, 16384), tc::mnmajor_tile(Sop, KD), 128, KD, KD, false);
+      tc::issue_gemm(taddr, tc::kmajor_sw128_tile(A1c, 16384), tc::mnmajor_tile(Sop, KD), 128, KD, KD, false);
       tc::mma_commit(mbar);
       if (p.save) {  // the state at chunk start, saved for the backward as the byte image of the operand tile
         tc::bulk_store(p.hs + ci * KD * KD, tc::smem_u32(Sop), 32768);
         tc::bulk_commit();
       }
     }
+    if (TMA && tid == kOutThread && c > 0) {  // the previous chunk's output tile (complete since the barrier above)
+      for (int sl = 0; sl < 2; ++sl) tc::tma_store_4d(&maps.o, sOt + sl * 8192, 64 * sl, h, t0 - C, b);
+      tc::bulk_commit();
+    }
+    // In the shadow of the MMA: k <- diag(r) k in place, so that the state update contracts it with v_new itself
+    // (every thread scales the 16-byte units it would copy in the cp.async variant: no barrier needed for those)
+    if (!TMA) tc::cp_async_wait<3>();
+    if (ok) ok = tc::mbar_wait(&mbar[5 + buf], lph);  // P image and k rows of this chunk
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int u = tid + 256 * m, i = urow16(u);
+      uint4* unit = reinterpret_cast<uint4*>(A3c + tc::sw128_unit(i, ucol16(u)));
+      *unit = tc::scale_bf16x8(*unit, rr[i]);
+    }
     if (ok) ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
-    issue_A(c + 1);
-    if (ok) ok = tc::mbar_wait(&mbar[2], lph);  // u image of this chunk
-    __syncthreads();
-    float qs[64];
+    issue_A(c + 2);
+    if (ok) ok = tc::mbar_wait(&mbar[3 + buf], lph);  // u image of this chunk
+    float f[64];  // accumulator row; rows 64-127 keep E(gam_i) (q S) here until P v_new arrives
     if (ok) {
       const int i = kk & 63;
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        float f[32];
-        ld_acc32(taddr + j0, warp, c0, f);
-        if (kk < 64) {  // v_new = u - w S
-          const float ri = rr[i];
+      ld_acc64(taddr + j0, warp, f);
+      if (kk < 64) {  // v_new = u - w S
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const int c8 = 8 * half + (c0 >> 3) + x;
-            const uint4 uu = *reinterpret_cast<const uint4*>(Ut + tc::kmajor_unit(i, c8, KD));
-            float e[8];
-            tc::unpack_bf16(uu.x, e[0], e[1]); tc::unpack_bf16(uu.y, e[2], e[3]);
-            tc::unpack_bf16(uu.z, e[4], e[5]); tc::unpack_bf16(uu.w, e[6], e[7]);
+        for (int x = 0; x < 8; ++x) {
+          const int c8 = 8 * half + x;
+          const uint4 uu = *reinterpret_cast<const uint4*>(Utc + tc::kmajor_unit(i, c8, KD));
+          float e[8];
+          tc::unpack_bf16(uu.x, e[0], e[1]); tc::unpack_bf16(uu.y, e[2], e[3]);
+          tc::unpack_bf16(uu.z, e[4], e[5]); tc::unpack_bf16(uu.w, e[6], e[7]);
 #pragma unroll
-            for (int y = 0; y < 8; ++y) e[y] -= f[8 * x + y];
-            const uint4 vv = make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
-                                        tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7]));
-            sts16(Vn, tc::mnmajor_unit(i, c8, KD), vv);
-            sts16(Vr, tc::mnmajor_unit(i, c8, KD), tc::scale_bf16x8(vv, ri));
-          }
-        } else {        // E(gam_i) (q S), kept until P v_new arrives
-          const float di = dd[i];
-#pragma unroll
-          for (int jj = 0; jj < 32; ++jj) qs[c0 + jj] = di * f[jj];
+          for (int y = 0; y < 8; ++y) e[y] -= f[8 * x + y];
+          sts16(Vn, tc::mnmajor_unit(i, c8, KD), make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
+                                                            tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7])));
         }
+      } else {
+        const float di = dd[i];
+#pragma unroll
+        for (int jj = 0; jj < 64; ++jj) f[jj] *= di;
       }
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the state image has left its tile
-    if (!TMA) tc::cp_async_wait<1>();  // group PK of this chunk (group A of the next one may still fly)
-    if (ok) ok = tc::mbar_wait(&mbar[3], lph);
+    if (TMA && tid == kOutThread) tc::bulk_wait_read<0>();  // the previous output tile has left its tile
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
-    issue_U(c + 1);  // u has been consumed by every thread
+    issue_U(c + 2);  // u has been consumed by every thread
     if (ok && tid == 0) {
-      // D2 = [0;P] v_new          D3 = k^T (r v_new)
-      tc::issue_gemm(taddr + 128, tc::kmajor_tile(A2, C), tc::mnmajor_tile(Vn, KD), 128, KD, C, false);
-      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(A3, 8192), tc::mnmajor_tile(Vr, KD), 128, KD, C, false);
+      // D2 = [0;P] v_new          D3 = (r k)^T v_new
+      tc::issue_gemm(taddr + 128, tc::kmajor_tile(A2c, C), tc::mnmajor_tile(Vn, KD), 128, KD, C, false);
+      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(A3c, 8192), tc::mnmajor_tile(Vn, KD), 128, KD, C, false);
       tc::mma_commit(mbar);
       if (p.save) {
         tc::bulk_store(p.vn + ci * C * KD, tc::smem_u32(Vn), 16384);
@@ -528,31 +549,46 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
       ph ^= 1;
     }
     tc::fence_after_sync();
-    issue_PK(c + 1);
+    issue_PK(c + 2);
     if (ok) {
       const int i = kk & 63;
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        float f[32];
-        if (kk >= 64) {  // out = E(gam)(q S) + P v_new      (warp-uniform branch)
-          ld_acc32(taddr + 128 + j0, warp, c0, f);
-          if (i < imax) {
-            uint4* dst = reinterpret_cast<uint4*>(p.out + grow(c, i) * KD + j0 + c0);
+      float a[64];
+      if (kk >= 64) {  // out = E(gam)(q S) + P v_new      (warp-uniform branch)
+        ld_acc64(taddr + 128 + j0, warp, a);
+        if (TMA) {     // into the swizzled output tile; one thread hands it to the copy engine after the next barrier
 #pragma unroll
-            for (int x = 0; x < 4; ++x)
-              dst[x] = make_uint4(tc::pack_bf16(qs[c0 + 8 * x] + f[8 * x], qs[c0 + 8 * x + 1] + f[8 * x + 1]),
-                                  tc::pack_bf16(qs[c0 + 8 * x + 2] + f[8 * x + 2], qs[c0 + 8 * x + 3] + f[8 * x + 3]),
-                                  tc::pack_bf16(qs[c0 + 8 * x + 4] + f[8 * x + 4], qs[c0 + 8 * x + 5] + f[8 * x + 5]),
-                                  tc::pack_bf16(qs[c0 + 8 * x + 6] + f[8 * x + 6], qs[c0 + 8 * x + 7] + f[8 * x + 7]));
-          }
+          for (int x = 0; x < 8; ++x)
+            sts16(Ot, tc::sw128_unit(i, 8 * half + x),
+                  make_uint4(tc::pack_bf16(f[8 * x] + a[8 * x], f[8 * x + 1] + a[8 * x + 1]),
+                             tc::pack_bf16(f[8 * x + 2] + a[8 * x + 2], f[8 * x + 3] + a[8 * x + 3]),
+                             tc::pack_bf16(f[8 * x + 4] + a[8 * x + 4], f[8 * x + 5] + a[8 * x + 5]),
+                             tc::pack_bf16(f[8 * x + 6] + a[8 * x + 6], f[8 * x + 7] + a[8 * x + 7])));
+        } else if (i < imax) {
+          uint4* dst = reinterpret_cast<uint4*>(p.out + grow(c, i) * KD + j0);
+#pragma unroll
+          for (int x = 0; x < 8; ++x)
+            dst[x] = make_uint4(tc::pack_bf16(f[8 * x] + a[8 * x], f[8 * x + 1] + a[8 * x + 1]),
+                                tc::pack_bf16(f[8 * x + 2] + a[8 * x + 2], f[8 * x + 3] + a[8 * x + 3]),
+                                tc::pack_bf16(f[8 * x + 4] + a[8 * x + 4], f[8 * x + 5] + a[8 * x + 5]),
+                                tc::pack_bf16(f[8 * x + 6] + a[8 * x + 6], f[8 * x + 7] + a[8 * x + 7]));
         }
-        ld_acc32(taddr + 256 + j0, warp, c0, f);  // S <- E(gam_last) S + k^T (r v_new)
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) S[c0 + jj] = fmaf(L, S[c0 + jj], f[jj]);
       }
+      ld_acc64(taddr + 256 + j0, warp, a);  // S <- E(gam_last) S + (r k)^T v_new
+#pragma unroll
+      for (int jj = 0; jj < 64; ++jj) S[jj] = fmaf(L, S[jj], a[jj]);
     }
     tc::fence_before_sync();
   }
   if (!TMA) tc::cp_async_wait<0>();
+  if (TMA) {  // the last chunk's output tile
+    tc::fence_async_smem();
+    __syncthreads();
+    if (ok && tid == kOutThread) {
+      for (int sl = 0; sl < 2; ++sl) tc::tma_store_4d(&maps.o, sOt + sl * 8192, 64 * sl, h, (p.n - 1) * C, b);
+      tc::bulk_commit();
+    }
+    if (tid == kOutThread) tc::bulk_wait_read<0>();
+  }
   if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 2);
   if (ok && p.hT) {
@@ -663,7 +699,8 @@ mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
   PrepMaps maps;
   std::memset(&maps, 0, sizeof maps);
   const bool tma = g_tc_use_tma && !p.no_tma && make_map_bthd(&maps.k, p.k, p.B, p.T, p.H) &&
-                   make_map_bthd(&maps.q, p.q, p.B, p.T, p.H) && make_map_bthd(&maps.v, p.v, p.B, p.T, p.H);
+                   make_map_bthd(&maps.q, p.q, p.B, p.T, p.H) && make_map_bthd(&maps.v, p.v, p.B, p.T, p.H) &&
+                   make_map_bthd(&maps.o, p.out, p.B, p.T, p.H);
   if (tma) {
     if (tc_set_smem(gdn_tc_prep_kernel<true>, kPrepSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("gdn_tc_prep_kernel", st,

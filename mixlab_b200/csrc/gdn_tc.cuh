@@ -50,8 +50,9 @@ struct TcP {
 
 // Tensor maps of the token-indexed operands: [B,T,H,128] bf16 viewed as (D, H, T, B), boxes of 64 columns x
 // 64 time steps with 128-byte swizzle; rows past the end of the sequence are zero-filled by the copy engine.
+// o: the forward output, written back by tiled stores (rows past the end of the sequence are clipped).
 struct alignas(64) RowMaps {
-  CUtensorMap k, q, v, dO;
+  CUtensorMap k, q, v, dO, o;
 };
 
 // Views of a [64][128] tile for tcgen05 and for 16-byte unit access: written by the copy engine with 128-byte
@@ -92,6 +93,19 @@ __device__ __forceinline__ void ld_acc32(uint32_t taddr, int warp, int c0, float
   tc::tmem_ld_wait();
 #pragma unroll
   for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+}
+// Loads 64 fp32 accumulator columns [0, 64) at taddr of this thread's TMEM lane: both loads in flight, one wait.
+__device__ __forceinline__ void ld_acc64(uint32_t taddr, int warp, float (&f)[64]) {
+  uint32_t r0[32], r1[32];
+  const uint32_t base = taddr + ((uint32_t)(32 * (warp & 3)) << 16);
+  tc::tmem_ld_32x32b_x32(base, r0);
+  tc::tmem_ld_32x32b_x32(base + 32u, r1);
+  tc::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    f[i] = __uint_as_float(r0[i]);
+    f[32 + i] = __uint_as_float(r1[i]);
+  }
 }
 }  // namespace tcg
 using namespace tcg;

@@ -141,6 +141,14 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap,
       : "memory");
 }
 
+// Tiled tensor copy shared -> global (bulk async-group completion); elements outside the tensor are not written.
+__device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(src_smem), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+
 // ---- asynchronous 16-byte global -> shared copies (cp.async) ----------------------
 // valid == false writes 16 zero bytes (source size 0); gptr must still be a mapped address.
 __device__ __forceinline__ void cp_async16(uint32_t saddr, const void* gptr, bool valid = true) {
