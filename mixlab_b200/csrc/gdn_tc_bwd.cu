@@ -26,61 +26,68 @@
 namespace mxb {
 
 // One CTA (256 threads) per (batch, head); thread t owns row kk = t & 127 of dS and the 64
-// columns of half t >> 7.  cp.async prefetch of the next (earlier) chunk:
-//   group A  k, P, dO, q   buffers free after the first MMA batch
-//   group B  w             free after the second MMA batch
-// Two groups are outstanding at the top of every chunk, in the order A, B.
+// columns of half t >> 7.  Chunks run in reverse.  The operand tiles are double-buffered (buffer c & 1 for
+// chunk c) and requested two chunks ahead, as soon as the MMA batch that last read the buffer has completed:
+//   group A  k, dO, q rows and the P image   free after the first MMA batch
+//   group B  the w image                     free after the second MMA batch
+// q is scaled in place to diag(E(gam)) q one chunk early, in the shadow of the second MMA batch, so that the
+// first batch contracts it with the raw dO tile:  dS <- E(gam_last) dS + (d q)^T dO - w^T dv_new.
 //
 // TMA = true: the k, dO and q rows arrive as tensor-map boxes (128-byte swizzle, two 8 KB slabs of 64 columns per
 // tile) issued by one thread on the barrier of group A; TMA = false: by cp.async into the same swizzled positions
-// (twelve copies per thread and chunk, on the critical path between the MMA and its epilogue).  The w image is
-// stored in the same swizzled layout by the prep kernel.
-constexpr int kStateBwdSmem = 16384 + 32768 + 8192 + 16384 + 32768 + 32768 + 2 * C * 4 + 64 + 1024;
+// (twelve copies per thread and chunk).  The w image is stored in the same swizzled layout by the prep kernel.
+constexpr int kStateBwdSmem =
+    2 * 16384 + 32768 + 2 * 8192 + 2 * 16384 + 2 * 16384 + 2 * 16384 + 16384 + 3 * C * 4 + 128 + 1024;
 
 template <bool TMA>
 __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __grid_constant__ RowMaps maps) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
-  uint8_t* Ak = sm;                 // [64 i][128 kk]      k  (swizzled slabs)
-  uint8_t* dSop = Ak + 16384;       // [128 kk][128 j]     bf16 copy of dS
-  uint8_t* Pt = dSop + 32768;       // [64 m][64 i]        P   (A = P^T: contraction over rows)
-  uint8_t* dOop = Pt + 8192;        // [64 m][128 j]       dO (swizzled slabs)
-  uint8_t* Aqw = dOop + 16384;      // [q rows | w rows][128 kk], each half in swizzled slabs   (A = [q^T | w^T])
-  uint8_t* Bdd = Aqw + 32768;       // [128: d dO rows, -dv_new rows][128 j]
-  float* dd = reinterpret_cast<float*>(Bdd + 32768);
-  float* rr = dd + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(rr + C);  // [0] MMA completion, [1] P image, [2] w image landed
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
+  uint8_t* Ak = sm;                  // x2 [64 i][128 kk]   k  (swizzled slabs)
+  uint8_t* dSop = Ak + 2 * 16384;    // [128 kk][128 j]     bf16 copy of dS
+  uint8_t* Pt = dSop + 32768;        // x2 [64 m][64 i]     P   (A = P^T: contraction over rows)
+  uint8_t* dOop = Pt + 2 * 8192;     // x2 [64 m][128 j]    dO (swizzled slabs)
+  uint8_t* Aq = dOop + 2 * 16384;    // x2 [64 i][128 kk]   q, then diag(E(gam)) q (swizzled slabs)   (A = q^T)
+  uint8_t* Aw = Aq + 2 * 16384;      // x2 [64 i][128 kk]   w image (swizzled slabs)                  (A = w^T)
+  uint8_t* Bd = Aw + 2 * 16384;      // [64 i][128 j]       -dv_new
+  float* rr = reinterpret_cast<float*>(Bd + 16384);
+  float* ddn = rr + C;               // x2 E(gam) of the chunk whose q is scaled next (buffer = chunk & 1)
+  // [0] MMA completion; per buffer: [1 + buf] group A landed, [3 + buf] w image landed
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(ddn + 2 * C);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kk = tid & 127, half = tid >> 7, j0 = 64 * half;
   const int bh = blockIdx.x, b = bh / p.H, h = bh % p.H;
-  const uint32_t sAk = tc::smem_u32(Ak), sPt = tc::smem_u32(Pt), sdO = tc::smem_u32(dOop), sAqw = tc::smem_u32(Aqw);
+  const uint32_t sAk = tc::smem_u32(Ak), sPt = tc::smem_u32(Pt), sdO = tc::smem_u32(dOop), sAq = tc::smem_u32(Aq);
+  const uint32_t sAw = tc::smem_u32(Aw);
 
   auto grow = [&](int c, int i) { return ((size_t)(b * p.T + c * C + i) * p.H + h); };
   auto issue_A = [&](int c) {
     if (c >= 0) {
       const size_t ci = (size_t)bh * p.n + c;
+      const uint32_t o16 = (c & 1) * 16384;
       if (!TMA) {
         const int imax = min(C, p.T - c * C);
         for (int u = tid; u < 64 * 16; u += 256) {
           const int i = urow16(u), c8 = ucol16(u);
           const bool v = i < imax;
           const size_t g = v ? grow(c, i) * KD + c8 * 8 : 0;
-          const uint32_t off = tc::sw128_unit(i, c8);
+          const uint32_t off = o16 + tc::sw128_unit(i, c8);
           tc::cp_async16(sAk + off, p.k + g, v);
           tc::cp_async16(sdO + off, p.dO + g, v);
-          tc::cp_async16(sAqw + off, p.q + g, v);
+          tc::cp_async16(sAq + off, p.q + g, v);
         }
       }
       if (tid == 32) {  // P is a byte image of its operand tile: one bulk copy, completing on the group's barrier
-        tc::mbar_expect_tx(&mbar[1], TMA ? 8192 + 3 * 16384 : 8192);
-        tc::bulk_load(sPt, p.P + ci * C * C, 8192, &mbar[1]);
+        uint64_t* mb = &mbar[1 + (c & 1)];
+        tc::mbar_expect_tx(mb, TMA ? 8192 + 3 * 16384 : 8192);
+        tc::bulk_load(sPt + (c & 1) * 8192, p.P + ci * C * C, 8192, mb);
         if (TMA) {
           for (int sl = 0; sl < 2; ++sl) {
-            tc::tma_load_4d(sAk + sl * 8192, &maps.k, 64 * sl, h, c * C, b, &mbar[1]);
-            tc::tma_load_4d(sdO + sl * 8192, &maps.dO, 64 * sl, h, c * C, b, &mbar[1]);
-            tc::tma_load_4d(sAqw + sl * 8192, &maps.q, 64 * sl, h, c * C, b, &mbar[1]);
+            tc::tma_load_4d(sAk + o16 + sl * 8192, &maps.k, 64 * sl, h, c * C, b, mb);
+            tc::tma_load_4d(sdO + o16 + sl * 8192, &maps.dO, 64 * sl, h, c * C, b, mb);
+            tc::tma_load_4d(sAq + o16 + sl * 8192, &maps.q, 64 * sl, h, c * C, b, mb);
           }
         }
       }
@@ -90,10 +97,19 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
   auto issue_B = [&](int c) {
     if (c >= 0 && tid == 32) {
       const size_t ci = (size_t)bh * p.n + c;
-      tc::mbar_expect_tx(&mbar[2], 16384);
-      tc::bulk_load(sAqw + 16384, p.w + ci * C * KD, 16384, &mbar[2]);  // the second half of the tile
+      tc::mbar_expect_tx(&mbar[3 + (c & 1)], 16384);
+      tc::bulk_load(sAw + (c & 1) * 16384, p.w + ci * C * KD, 16384, &mbar[3 + (c & 1)]);
     }
     if (!TMA) tc::cp_async_commit();  // (empty: keeps the group count of the schedule)
+  };
+  // q of chunk c <- diag(E(gam)) q in place; every thread scales the 16-byte units it would copy itself
+  auto scale_q = [&](int c) {
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int u = tid + 256 * m, i = urow16(u);
+      uint4* unit = reinterpret_cast<uint4*>(Aq + (c & 1) * 16384 + tc::sw128_unit(i, ucol16(u)));
+      *unit = tc::scale_bf16x8(*unit, ddn[(c & 1) * C + i]);
+    }
   };
 
   if (warp == 0) {
@@ -101,12 +117,14 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
     tc::tmem_relinquish();
   }
   if (tid == 0) {
-    for (int m = 0; m < 3; ++m) tc::mbar_init(&mbar[m], 1);
+    for (int m = 0; m < 5; ++m) tc::mbar_init(&mbar[m], 1);
     tc::mbar_fence_init();
   }
   __syncthreads();  // barriers initialised before the copies can complete on them
-  issue_A(p.n - 1);
-  issue_B(p.n - 1);
+  for (int c = p.n - 1; c > p.n - 3; --c) {
+    issue_A(c);
+    issue_B(c);
+  }
   float dS[64];  // row kk of dS, columns j0 .. j0+63
   if (p.dhT_in) {
     const float4* src = reinterpret_cast<const float4*>(p.dhT_in + ((size_t)bh * KD + kk) * KD + j0);
@@ -119,27 +137,42 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
 #pragma unroll
     for (int x = 0; x < 64; ++x) dS[x] = 0.f;
   }
+  // in-chunk cumulative log decay: this chunk's, and the next (earlier) one's fetched a chunk early
+  const size_t gbase = (size_t)bh * p.n * C;
+  float g_cur = p.gam[gbase + (size_t)(p.n - 1) * C + (tid & 63)], gl_cur = p.gam[gbase + (size_t)(p.n - 1) * C + C - 1];
+  float g_nxt = 0.f, gl_nxt = 0.f;
+  if (p.n > 1) {
+    g_nxt = p.gam[gbase + (size_t)(p.n - 2) * C + (tid & 63)];
+    gl_nxt = p.gam[gbase + (size_t)(p.n - 2) * C + C - 1];
+  }
+  if (tid < C) ddn[((p.n - 1) & 1) * C + tid] = exp_nonpos(g_cur);
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   const uint32_t taddr = *tslot;
   uint32_t ph = 0;
   bool ok = true;
+  {  // the last chunk's q is scaled here; every later one in the shadow of the previous iteration's second batch
+    const int c = p.n - 1;
+    if (!TMA) tc::cp_async_wait<2>();
+    ok = tc::mbar_wait(&mbar[1 + (c & 1)], 0);
+    scale_q(c);
+  }
 
-  // in-chunk cumulative log decay of the chunk ahead, fetched one chunk early
-  float g_nxt = p.gam[((size_t)bh * p.n + p.n - 1) * C + (tid & 63)], gl_nxt = p.gam[((size_t)bh * p.n + p.n - 1) * C + C - 1];
   for (int c = p.n - 1; c >= 0 && ok; --c) {
     const size_t ci = (size_t)bh * p.n + c;
-    const uint32_t lph = (p.n - 1 - c) & 1;  // phase of the image barriers
-    const float glast = gl_nxt, g = g_nxt;
-    if (c > 0) {
-      g_nxt = p.gam[(ci - 1) * C + (tid & 63)];
-      gl_nxt = p.gam[(ci - 1) * C + C - 1];
+    const int buf = c & 1;
+    const uint32_t lph = ((p.n - 1 - c) >> 1) & 1;  // phase of this buffer's barriers
+    const float glast = gl_cur, g = g_cur;
+    g_cur = g_nxt; gl_cur = gl_nxt;
+    if (c > 1) {
+      g_nxt = p.gam[(ci - 2) * C + (tid & 63)];
+      gl_nxt = p.gam[(ci - 2) * C + C - 1];
     }
     const float L = exp_nonpos(glast);
     if (tid < C) {
-      dd[tid] = exp_nonpos(g);
       rr[tid] = exp_nonpos(glast - g);
+      if (c > 0) ddn[(buf ^ 1) * C + tid] = exp_nonpos(g_cur);  // for the next chunk's q
     }
 #pragma unroll
     for (int c8 = 0; c8 < 8; ++c8) {  // dS at chunk end: MMA operand + saved for the chunk kernel
@@ -148,22 +181,17 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
       sts16(dSop, tc::mnmajor_unit(kk, 8 * half + c8, KD), val);
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's -dv_new image has left its tile
-    if (!TMA) tc::cp_async_wait<1>();  // group A of this chunk (k, dO, q rows; the images on the barrier)
-    ok = tc::mbar_wait(&mbar[1], lph);
-    __syncthreads();         // dO tile and dd visible to every thread
-    for (int u = tid; u < 64 * 16; u += 256) {  // d dO
-      const int i = urow16(u), c8 = ucol16(u);
-      sts16(Bdd, tc::kmajor_unit(i, c8, KD),
-            tc::scale_bf16x8(*reinterpret_cast<const uint4*>(dOop + tc::sw128_unit(i, c8)), dd[i]));
-    }
+    // group A of this chunk was waited for when its q was scaled (previous iteration / prologue)
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     if (tid == 0) {
-      tc::issue_gemm(taddr, tc::kmajor_sw128_tile(Ak, 8192), tc::mnmajor_tile(dSop, KD), 64, KD, KD, false);         // k dS
-      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Pt, C), tc::mnmajor_sw128_tile(dOop, 8192), 64, KD, C, false);    // P^T dO
-      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(Aqw, 8192), tc::mnmajor_tile(Bdd, KD), 128, KD, C, false);  // q^T (d dO)
+      tc::issue_gemm(taddr, tc::kmajor_sw128_tile(Ak + buf * 16384, 8192), tc::mnmajor_tile(dSop, KD), 64, KD, KD, false);  // k dS
+      tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Pt + buf * 8192, C), tc::mnmajor_sw128_tile(dOop + buf * 16384, 8192), 64, KD,
+                     C, false);                                                                                           // P^T dO
+      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(Aq + buf * 16384, 8192), tc::mnmajor_sw128_tile(dOop + buf * 16384, 8192),
+                     128, KD, C, false);                                                                                  // (d q)^T dO
       tc::mma_commit(mbar);
       tc::bulk_store(p.dhs + ci * KD * KD, tc::smem_u32(dSop), 32768);  // dS at chunk end, as the operand-tile image
       tc::bulk_commit();
@@ -171,7 +199,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
     if (ok) ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
-    issue_A(c - 1);
+    issue_A(c - 2);
     if (ok) {
       const int i = 16 * (warp & 3) + (lane & 15);  // M=64 accumulators: row i in TMEM lane (i%16) + 32*(i/16)
       const float ri = rr[i];
@@ -184,41 +212,42 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
           for (int x = 0; x < 4; ++x) {
             float e[8];
 #pragma unroll
-            for (int y = 0; y < 8; ++y) e[y] = fmaf(ri, fa[8 * x + y], fb[8 * x + y]);
-            const uint4 vv = make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
-                                        tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7]));
+            for (int y = 0; y < 8; ++y) e[y] = -fmaf(ri, fa[8 * x + y], fb[8 * x + y]);
             const int c8 = 8 * half + (c0 >> 3) + x;
-            sts16(Bdd, tc::kmajor_unit(64 + i, c8, KD), tc::scale_bf16x8(vv, -1.f));
+            sts16(Bd, tc::kmajor_unit(i, c8, KD), make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]),
+                                                             tc::pack_bf16(e[4], e[5]), tc::pack_bf16(e[6], e[7])));
           }
         }
       }
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the dS image has left its tile
-    if (ok) ok = tc::mbar_wait(&mbar[2], lph);  // w image of this chunk
+    if (ok) ok = tc::mbar_wait(&mbar[3 + buf], lph);  // w image of this chunk
     tc::fence_async_smem();
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     if (ok && tid == 0) {  // ... - w^T dv_new
-      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(Aqw + 16384, 8192), tc::skip_k(tc::mnmajor_tile(Bdd, KD), 64),
-                     128, KD, C, true);
+      tc::issue_gemm(taddr + 256, tc::mnmajor_sw128_tile(Aw + buf * 16384, 8192), tc::mnmajor_tile(Bd, KD), 128, KD, C, true);
       tc::mma_commit(mbar);
-      tc::bulk_store(p.dvn + ci * C * KD, tc::smem_u32(Bdd) + 16384, 16384);  // -dv_new: rows 64..127 of the operand tile
+      tc::bulk_store(p.dvn + ci * C * KD, tc::smem_u32(Bd), 16384);  // -dv_new as the operand-tile image
       tc::bulk_commit();
+    }
+    if (c > 0) {  // in the shadow of the MMA: the next chunk's q (its group landed a chunk ago)
+      if (!TMA) tc::cp_async_wait<2>();
+      if (ok) ok = tc::mbar_wait(&mbar[1 + (buf ^ 1)], ((p.n - c) >> 1) & 1);
+      scale_q(c - 1);
     }
     if (ok) {
       ok = tc::mbar_wait(mbar, ph);
       ph ^= 1;
     }
     tc::fence_after_sync();
-    issue_B(c - 1);
+    issue_B(c - 2);
     if (ok) {
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        float f[32];
-        ld_acc32(taddr + 256 + j0, warp, c0, f);
+      float a[64];
+      ld_acc64(taddr + 256 + j0, warp, a);
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) dS[c0 + jj] = fmaf(L, dS[c0 + jj], f[jj]);
-      }
+      for (int jj = 0; jj < 64; ++jj) dS[jj] = fmaf(L, dS[jj], a[jj]);
     }
     tc::fence_before_sync();
   }
