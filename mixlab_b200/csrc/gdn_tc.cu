@@ -24,13 +24,20 @@ namespace mxb {
 // ------------------------------------------------------------------ prep
 // u = T (v beta) and w = T (k beta E(gam)) are evaluated as (T diag(beta)) v and
 // (T diag(beta E(gam))) k: the scaling goes into two column-scaled bf16 copies of T written
-// straight from the solve's registers, so k, q and v are staged raw with cp.async.
+// straight from the solve's registers, so k, q and v are staged raw.
 //
+// A CTA is a chain of dependent steps (copy -> MMA -> epilogue -> solve -> MMA -> epilogue -> stores) that leaves
+// the SM idle most of the time, so the kernel is sized for THREE CTAs per SM: 128 TMEM columns (u and w go through
+// the same columns one after the other) and 67 KB of shared memory, every region reused as soon as it is dead:
+//   [k;q] (32 KB, two slabs of 64 columns: k box then q box)  ->  v lands in the q boxes once q k^T is done
+//                                                              ->  u image over v, w image over k
+//   Tb region: the P image on its way out, then T diag(beta)
+//   A / T fp32 matrix: then the bf16 T image on its way out
 // TMA = true: k, q, v arrive as cp.async.bulk.tensor tiles (boxes of 64 rows x 64 columns, 128-byte
-// swizzle; rows past the end of the sequence are zero-filled by the copy engine) and the MMAs read
-// them through swizzled descriptors.  TMA = false: the same tiles staged with cp.async in the
-// un-swizzled layout (kept as a cross-check and for drivers without the tensor-map entry point).
-constexpr int kPrepSmem = 32768 + 16384 + 4 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 1024;
+// swizzle; rows past the end of the sequence are zero-filled by the copy engine).  TMA = false: the same
+// tiles staged with cp.async into the same swizzled positions (kept as a cross-check and for drivers
+// without the tensor-map entry point).
+constexpr int kPrepSmem = 32768 + 2 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 64 + 1024;
 
 using PrepMaps = RowMaps;
 
@@ -40,16 +47,14 @@ __device__ __forceinline__ uint4 pack8f(const float* e) {
 }
 
 template <bool TMA>
-__global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_constant__ PrepMaps maps) {
+__global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid_constant__ PrepMaps maps) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
-  uint8_t* Akq = sm;                    // [128: k rows 0-63, q rows 64-127][128]
-  uint8_t* Vt = Akq + 32768;            // [64 m][128]  v
-  uint8_t* Tt = Vt + 16384;             // [64 i][64 m] T
-  uint8_t* Tb = Tt + 8192;              // [64 i][64 m] T diag(beta)
+  uint8_t* Akq = sm;                    // slab s at 16384 s: k box [64][64], then q box [64][64] (later v, u / w images)
+  uint8_t* Tb = Akq + 32768;            // [64 i][64 m] P image, then T diag(beta)
   uint8_t* Tbd = Tb + 8192;             // [64 i][64 m] T diag(beta E(gam))
-  uint8_t* Pt = Tbd + 8192;             // [64 i][64 m] P image on its way to the workspace
-  float* Am = reinterpret_cast<float*>(Pt + 8192);   // [64][LDA]  A, then T in place
+  float* Am = reinterpret_cast<float*>(Tbd + 8192);   // [64][LDA]  A, then T in place
+  uint8_t* Tt = reinterpret_cast<uint8_t*>(Am);       // [64 i][64 m] T image, over the fp32 matrix once it is dead
   float* gam = Am + C * LDA;
   float* bet = gam + C;
   float* bd = bet + C;
@@ -61,6 +66,11 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   const size_t ci = (size_t)bh * p.n + c;
   auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
   const int imax = min(C, p.T - t0);
+  const uint32_t sAkq = tc::smem_u32(Akq);
+  // byte offset in Akq of unit (i, c8) of the k tile; the q (later v) tile sits 8192 bytes further
+  auto kq_unit = [](int i, int c8) {
+    return (uint32_t)(c8 >> 3) * 16384u + (uint32_t)i * 128u + (uint32_t)(((c8 & 7) ^ (i & 7)) << 4);
+  };
 
   // prologue latencies side by side: warp 0 allocates TMEM, warp 1 reads the gates, one thread of warp 2
   // initialises the barriers and issues the copies that complete on them
@@ -72,33 +82,24 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   }
   if (TMA) {
     if (tid == 64) {
-      // slab s (columns 64 s ..) of [k;q]: k box then q box; v: one box per slab
       tc::mbar_expect_tx(&mbar[1], 32768);
       for (int sl = 0; sl < 2; ++sl) {
-        tc::tma_load_4d(tc::smem_u32(Akq + sl * 16384), &maps.k, 64 * sl, h, t0, b, &mbar[1]);
-        tc::tma_load_4d(tc::smem_u32(Akq + sl * 16384 + 8192), &maps.q, 64 * sl, h, t0, b, &mbar[1]);
+        tc::tma_load_4d(sAkq + sl * 16384, &maps.k, 64 * sl, h, t0, b, &mbar[1]);
+        tc::tma_load_4d(sAkq + sl * 16384 + 8192, &maps.q, 64 * sl, h, t0, b, &mbar[1]);
       }
-      tc::mbar_expect_tx(&mbar[2], 16384);
-      for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(tc::smem_u32(Vt + sl * 8192), &maps.v, 64 * sl, h, t0, b, &mbar[2]);
     }
-  } else {  // group 0: [k;q]   group 1: v
-    const uint32_t sa = tc::smem_u32(Akq), sv = tc::smem_u32(Vt);
-    for (int u = tid; u < 128 * 16; u += 128) {
-      const int r = urow16(u), c8 = ucol16(u), i = r & 63;
-      const bool ok = i < imax;
-      const bf16* src = r < 64 ? p.k : p.q;
-      tc::cp_async16(sa + tc::kmajor_unit(r, c8, KD), ok ? src + row(i) * KD + c8 * 8 : src, ok);
-    }
-    tc::cp_async_commit();
+  } else {
     for (int u = tid; u < 64 * 16; u += 128) {
       const int i = urow16(u), c8 = ucol16(u);
       const bool ok = i < imax;
-      tc::cp_async16(sv + tc::kmajor_unit(i, c8, KD), ok ? p.v + row(i) * KD + c8 * 8 : p.v, ok);
+      const size_t g = ok ? row(i) * KD + c8 * 8 : 0;
+      tc::cp_async16(sAkq + kq_unit(i, c8), p.k + g, ok);
+      tc::cp_async16(sAkq + 8192 + kq_unit(i, c8), p.q + g, ok);
     }
     tc::cp_async_commit();
   }
   if (warp == 0) {
-    tc::tmem_alloc(tslot, 256);
+    tc::tmem_alloc(tslot, 128);
     tc::tmem_relinquish();
   }
   if (warp == 1) {  // in-chunk inclusive cumulative sum of the log gate: two elements per lane
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
     __syncthreads();  // barriers initialised before anyone waits on them
     ok = tc::mbar_wait(&mbar[1], 0);  // [k;q]
   } else {
-    tc::cp_async_wait<1>();
+    tc::cp_async_wait<0>();
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
@@ -133,12 +134,26 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   const uint32_t taddr = *tslot;
   // D0[128 x 64] = [k;q] k^T
   if (tid == 0) {
-    const tc::Tile a = TMA ? tc::kmajor_sw128_tile(Akq, 16384) : tc::kmajor_tile(Akq, KD);
+    const tc::Tile a = tc::kmajor_sw128_tile(Akq, 16384);
     tc::issue_gemm(taddr, a, a, 128, 64, KD, false);  // B = first 64 rows of the same tile
     tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar, 0);
   tc::fence_after_sync();
+  // q is dead: v takes its place (needed only for the second MMA, long after the solve)
+  if (TMA) {
+    if (tid == 64) {
+      tc::mbar_expect_tx(&mbar[2], 16384);
+      for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(sAkq + sl * 16384 + 8192, &maps.v, 64 * sl, h, t0, b, &mbar[2]);
+    }
+  } else {
+    for (int u = tid; u < 64 * 16; u += 128) {
+      const int i = urow16(u), c8 = ucol16(u);
+      const bool okv = i < imax;
+      tc::cp_async16(sAkq + 8192 + kq_unit(i, c8), okv ? p.v + row(i) * KD + c8 * 8 : p.v, okv);
+    }
+    tc::cp_async_commit();
+  }
   if (ok) {
     const int i = tid & 63;
     const float gi = gam[i], bi = bet[i];
@@ -157,7 +172,7 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
 #pragma unroll
         for (int x = 0; x < 8; ++x)
           *reinterpret_cast<float4*>(Am + i * LDA + c0 + 4 * x) = make_float4(f[4 * x], f[4 * x + 1], f[4 * x + 2], f[4 * x + 3]);
-      } else {         // P = (q k^T) Gamma, lower incl. diagonal -> workspace
+      } else {         // P = (q k^T) Gamma, lower incl. diagonal -> workspace (staged in the Tb region)
         uint32_t pk[16];
 #pragma unroll
         for (int jj = 0; jj < 32; jj += 2) {
@@ -168,7 +183,7 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
         }
 #pragma unroll
         for (int x = 0; x < 4; ++x)
-          sts16(Pt, tc::kmajor_unit(i, (c0 >> 3) + x, C), make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]));
+          sts16(Tb, tc::kmajor_unit(i, (c0 >> 3) + x, C), make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]));
       }
     }
   }
@@ -177,7 +192,7 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   __syncthreads();
   tc::fence_after_sync();
   if (ok && tid == 0) {  // P leaves as the byte image of its operand tile
-    tc::bulk_store(p.P + ci * C * C, tc::smem_u32(Pt), 8192);
+    tc::bulk_store(p.P + ci * C * C, tc::smem_u32(Tb), 8192);
     tc::bulk_commit();
   }
   // T = (I - A)^-1 in fp32, in place over A.  The two 32 x 32 diagonal blocks by forward substitution
@@ -220,6 +235,7 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
       *reinterpret_cast<float4*>(Am + i2 * LDA + 32 + jb) = make_float4(x[0], x[1], x[2], x[3]);
       *reinterpret_cast<float4*>(Am + i2 * LDA + 32 + jb + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
+    if (tid == 0) tc::bulk_wait_read<0>();  // the P image has left the Tb region (it is rewritten after the next barriers)
     __syncthreads();
     {  // T21 = T22 X -> over A21 (nothing reads A21 any more)
       float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -235,23 +251,29 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
       *reinterpret_cast<float4*>(Am + (32 + i2) * LDA + jb + 4) = make_float4(y[4], y[5], y[6], y[7]);
     }
     __syncthreads();
-    // bf16 operand tiles T, T diag(beta), T diag(beta E(gam)); the upper triangle (it holds X) reads as zero
-    for (int u = tid; u < 64 * 8; u += 128) {
-      const int i = urow8(u), c8 = ucol8(u);
+    // bf16 operand tiles T diag(beta), T diag(beta E(gam)) and the T image; the upper triangle (it holds X) reads as
+    // zero.  The T image goes over the fp32 matrix: every thread first reads all its rows, then a barrier, then writes.
+    uint4 timg[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int u = tid + 128 * m, i = urow8(u), c8 = ucol8(u);
       const float4 a0 = *reinterpret_cast<const float4*>(Am + i * LDA + 8 * c8);
       const float4 a1 = *reinterpret_cast<const float4*>(Am + i * LDA + 8 * c8 + 4);
       float e[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, eb[8], ed[8];
 #pragma unroll
       for (int y = 0; y < 8; ++y) {
-        const int m = 8 * c8 + y;
-        e[y] = (m <= i) ? e[y] : 0.f;
-        eb[y] = e[y] * bet[m];
-        ed[y] = e[y] * bd[m];
+        const int mm = 8 * c8 + y;
+        e[y] = (mm <= i) ? e[y] : 0.f;
+        eb[y] = e[y] * bet[mm];
+        ed[y] = e[y] * bd[mm];
       }
-      sts16(Tt, 16 * u, pack8f(e));
+      timg[m] = pack8f(e);
       sts16(Tb, 16 * u, pack8f(eb));
       sts16(Tbd, 16 * u, pack8f(ed));
     }
+    __syncthreads();
+#pragma unroll
+    for (int m = 0; m < 4; ++m) sts16(Tt, 16 * (tid + 128 * m), timg[m]);
   }
   if (TMA) { if (ok) ok = tc::mbar_wait(&mbar[2], 0); }  // v
   else tc::cp_async_wait<0>();
@@ -259,35 +281,52 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  // D1[64 x 256] = [ (T beta) v | (T beta d) k ]  -> u | w     (v, k contracted over their rows)
+  // D1[64 x 128] = (T beta) v -> u     (v contracted over its rows)
   if (ok && tid == 0) {
-    const tc::Tile bv = TMA ? tc::mnmajor_sw128_tile(Vt, 8192) : tc::mnmajor_tile(Vt, KD);
-    const tc::Tile bk = TMA ? tc::mnmajor_sw128_tile(Akq, 16384) : tc::mnmajor_tile(Akq, KD);
-    tc::issue_gemm(taddr, tc::kmajor_tile(Tb, C), bv, 64, KD, C, false);
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Tbd, C), bk, 64, KD, C, false);
+    tc::issue_gemm(taddr, tc::kmajor_tile(Tb, C), tc::mnmajor_sw128_tile(Akq + 8192, 16384), 64, KD, C, false);
     tc::mma_commit(mbar);
-  }
-  if (ok && tid == 0) {  // T leaves as the byte image of its operand tile while the MMA runs
-    tc::bulk_store(p.Tm + ci * C * C, tc::smem_u32(Tt), 8192);
+    tc::bulk_store(p.Tm + ci * C * C, tc::smem_u32(Tt), 8192);  // T leaves as the byte image of its operand tile
     tc::bulk_commit();
   }
   if (ok) ok = tc::mbar_wait(mbar, 1);
   tc::fence_after_sync();
+  const int ir = 16 * warp + (lane & 15);  // M=64: row m sits in TMEM lane (m%16) + 32*(m/16)
   if (ok) {
-    // u and w are assembled as operand-layout images over v and [k;q] (dead once the MMA has completed): u in the
-    // un-swizzled K-major layout, w in the 128-byte-swizzled layout of a TMA tile (two 8 KB slabs of 64 columns), so
-    // that the state kernels can put it beside TMA-loaded q rows in one operand
-    const int i = 16 * warp + (lane & 15);  // M=64: row m sits in TMEM lane (m%16) + 32*(m/16)
-    for (int c0 = 0; c0 < 256; c0 += 32) {
+    // the u image (un-swizzled K-major layout; rows 0-31 and 32-63 are its two contiguous halves) over the v boxes
+    for (int c0 = 0; c0 < 128; c0 += 32) {
       float f[32];
       ld_acc32(taddr, warp, c0, f);
       if (lane < 16) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-          const int c8 = ((c0 & 127) >> 3) + x;
-          if (c0 < 128) sts16(Vt, tc::kmajor_unit(i, c8, KD), pack8f(&f[8 * x]));
-          else sts16(Akq, tc::sw128_unit(i, c8), pack8f(&f[8 * x]));
+          const uint32_t off = tc::kmajor_unit(ir, (c0 >> 3) + x, KD);
+          sts16(Akq, 8192u + (off >> 13) * 16384u + (off & 8191u), pack8f(&f[8 * x]));
         }
+      }
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();  // the accumulator columns have been read: the second product may overwrite them
+  tc::fence_after_sync();
+  // D1[64 x 128] = (T beta d) k -> w
+  if (ok && tid == 0) {
+    tc::issue_gemm(taddr, tc::kmajor_tile(Tbd, C), tc::mnmajor_sw128_tile(Akq, 16384), 64, KD, C, false);
+    tc::mma_commit(mbar);
+    for (int hf = 0; hf < 2; ++hf) tc::bulk_store(p.u + ci * C * KD + hf * 4096, sAkq + 8192 + hf * 16384, 8192);
+    tc::bulk_commit();
+  }
+  if (ok) ok = tc::mbar_wait(mbar, 0);
+  tc::fence_after_sync();
+  if (ok) {
+    // the w image in the 128-byte-swizzled layout of a TMA tile (two 8 KB slabs of 64 columns), over the k boxes, so
+    // that the state kernels can put it beside TMA-loaded q rows in one operand
+    for (int c0 = 0; c0 < 128; c0 += 32) {
+      float f[32];
+      ld_acc32(taddr, warp, c0, f);
+      if (lane < 16) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Akq, kq_unit(ir, (c0 >> 3) + x), pack8f(&f[8 * x]));
       }
     }
   } else if (tid == 0) {
@@ -298,15 +337,14 @@ __global__ void __launch_bounds__(128) gdn_tc_prep_kernel(TcP p, const __grid_co
   __syncthreads();
   if (tid == 0) {
     if (ok) {
-      tc::bulk_store(p.u + ci * C * KD, tc::smem_u32(Vt), 16384);
-      tc::bulk_store(p.w + ci * C * KD, tc::smem_u32(Akq), 16384);
+      for (int sl = 0; sl < 2; ++sl) tc::bulk_store(p.w + ci * C * KD + sl * 4096, sAkq + sl * 16384, 8192);
       tc::bulk_commit();
     }
     tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   }
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+  if (warp == 0) tc::tmem_dealloc(taddr, 128);
 }
 
 // ------------------------------------------------------------ state forward
