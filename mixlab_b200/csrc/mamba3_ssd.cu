@@ -465,20 +465,23 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
 }
 
 // ------------------------------------------------------------ chunk output
-constexpr int kOutSmem = 16384 * 3 + 8192 * 2 + sizeof(ChunkScal) + 64 + 1024;
+// A CTA is a chain of dependent steps, so the kernel is sized for FOUR CTAs per SM: 128 TMEM columns and 51 KB of
+// shared memory.  The chunk state H0 lands in the Brot tile once G = Crot Brot^T has been formed (its copy hides
+// behind the mask epilogue), and Crot H0 joins the second MMA batch.
+constexpr int kOutSmem = 16384 * 2 + 8192 * 2 + sizeof(ChunkScal) + 64 + 1024;
 
 template <bool TMA>
-__global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p, const __grid_constant__ ChunkMaps maps) {
+__global__ void __launch_bounds__(128, 4) m3s_chunk_out_kernel(SsdP p, const __grid_constant__ ChunkMaps maps) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
-  uint8_t* Bt = sm;               // [64][128] Brot
+  uint8_t* Bt = sm;               // [64][128] Brot, then [128][64] H0
   uint8_t* Ct = Bt + 16384;       // [64][128] Crot
-  uint8_t* Ht = Ct + 16384;       // [128][64] H0
-  uint8_t* Xt = Ht + 16384;       // [64][64]  x
+  uint8_t* Ht = Bt;
+  uint8_t* Xt = Ct + 16384;       // [64][64]  x
   uint8_t* Gm = Xt + 8192;        // [64][64]  (Crot Brot^T) * M
   ChunkScal& s = *reinterpret_cast<ChunkScal*>(Gm + 8192);
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(&s + 1);
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 2);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(&s + 1);  // [0] MMA completion, [1] token tiles landed, [2] H0 landed
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 3);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, head = blockIdx.y, b = blockIdx.z, t0 = c * Q;
   const int d0 = head * P, g = d0 / (p.D / p.G);
@@ -486,17 +489,19 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p, const __grid
 
   if (warp == 0) { tc::tmem_alloc(tslot, 128); tc::tmem_relinquish(); }
   // the thread that initialises the barriers also issues the copies, on another warp than the TMEM allocation
-  if (tid == 32) { tc::mbar_init(mbar, 1); tc::mbar_init(mbar + 1, 1); tc::mbar_fence_init(); }
+  if (tid == 32) {
+    for (int m = 0; m < 3; ++m) tc::mbar_init(mbar + m, 1);
+    tc::mbar_fence_init();
+  }
   bool ok = true;
-  if (TMA) {  // every operand by the copy engine, one barrier
+  if (TMA) {  // every operand by the copy engine
     if (tid == 32) {
-      tc::mbar_expect_tx(mbar + 1, 3 * 16384 + 8192 + (uint32_t)sizeof(ChunkScal));
+      tc::mbar_expect_tx(mbar + 1, 2 * 16384 + 8192 + (uint32_t)sizeof(ChunkScal));
       for (int sl = 0; sl < 2; ++sl) {
         tc::tma_load_4d(tc::smem_u32(Bt) + 8192 * sl, &maps.b, 64 * sl, g, t0, b, mbar + 1);
         tc::tma_load_4d(tc::smem_u32(Ct) + 8192 * sl, &maps.c, 64 * sl, g, t0, b, mbar + 1);
       }
       tc::tma_load_4d(tc::smem_u32(Xt), &maps.x, 0, head, t0, b, mbar + 1);
-      tc::bulk_load(tc::smem_u32(Ht), p.H0 + ci * (N * P), 16384, mbar + 1);
       tc::bulk_load(tc::smem_u32(&s), p.cs + ci * (sizeof(ChunkScal) / 4), (uint32_t)sizeof(ChunkScal), mbar + 1);
     }
     __syncthreads();  // barriers initialised before anyone waits on them
@@ -505,7 +510,6 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p, const __grid
     issue_rows_tile(Bt, p.b, p, b, g, t0);
     issue_rows_tile(Ct, p.c, p, b, g, t0);
     issue_x_tile(Xt, p.x, p, b, d0, t0);
-    issue_state_tile(Ht, p.H0 + ci * (N * P));
     issue_chunk_scalars(p, ci, s);
     tc::cp_async_commit();
     tc::cp_async_wait<0>();
@@ -520,11 +524,20 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p, const __grid
   const uint32_t taddr = *tslot;
   if (tid == 0) {
     tc::issue_gemm(taddr, in_kmajor<TMA>(Ct, N), in_kmajor<TMA>(Bt, N), 64, Q, N, false);           // G = Crot Brot^T
-    tc::issue_gemm(taddr + 64, in_kmajor<TMA>(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);    // Crot H0
     tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar, 0);
   tc::fence_after_sync();
+  // Brot is dead: the chunk state takes its place while the mask is applied
+  if (TMA) {
+    if (tid == 32) {
+      tc::mbar_expect_tx(mbar + 2, 16384);
+      tc::bulk_load(tc::smem_u32(Ht), p.H0 + ci * (N * P), 16384, mbar + 2);
+    }
+  } else {
+    issue_state_tile(Ht, p.H0 + ci * (N * P));
+    tc::cp_async_commit();
+  }
   const int t = 16 * warp + (lane & 15);
   const bool own = lane < 16;
   if (ok) {
@@ -552,12 +565,15 @@ __global__ void __launch_bounds__(128) m3s_chunk_out_kernel(SsdP p, const __grid
 #pragma unroll
     for (int x = 0; x < 4; ++x) sts16(Gm, tc::kmajor_unit(t, 4 * hx + x, Q), pack8(&f[8 * x]));
   }
+  if (TMA) { if (ok) ok = tc::mbar_wait(mbar + 2, 0); }  // H0
+  else tc::cp_async_wait<0>();
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
   if (ok && tid == 0) {
     tc::issue_gemm(taddr, tc::kmajor_tile(Gm, Q), in_mnmajor<TMA>(Xt, P), 64, P, Q, false);  // (G*M) X, over the consumed G
+    tc::issue_gemm(taddr + 64, in_kmajor<TMA>(Ct, N), tc::mnmajor_tile(Ht, P), 64, P, N, false);    // Crot H0
     tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar, 1);
