@@ -252,9 +252,12 @@ struct ChunkMaps {
   CUtensorMap x, dy;  // [B,T,heads,64] viewed as (P, heads, T, B)
 };
 
-// Inclusive prefix sum of one double per thread over a 256-thread CTA (warp scans + the eight warp totals, a fixed
-// order); wtot is 8 doubles of shared memory.  Also returns the CTA total.
-__device__ __forceinline__ double cta_scan256(double v, double* wtot, double& total) {
+// Threads of the two per-(batch, head) scalar kernels: they are chains of dependent fp64 operations behind strided
+// loads, so many short chains (4 steps per thread at T = 4096) hide the latencies that few long ones expose.
+constexpr int kScalThreads = 1024;
+// Inclusive prefix sum of one double per thread over a kScalThreads-thread CTA (warp scans + the warp totals, a fixed
+// order); wtot is kScalThreads / 32 doubles of shared memory.  Also returns the CTA total.
+__device__ __forceinline__ double cta_scan(double v, double* wtot, double& total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -265,7 +268,7 @@ __device__ __forceinline__ double cta_scan256(double v, double* wtot, double& to
   __syncthreads();
   double off = 0.0, tot = 0.0;
 #pragma unroll
-  for (int w = 0; w < 8; ++w) {
+  for (int w = 0; w < kScalThreads / 32; ++w) {
     const double x = wtot[w];
     if (w < warp) off += x;
     tot += x;
@@ -275,12 +278,12 @@ __device__ __forceinline__ double cta_scan256(double v, double* wtot, double& to
 }
 
 // ------------------------------------------------------------ per-(b,head) scalars
-constexpr int kScalBatch = 8;
-__global__ void __launch_bounds__(256) m3s_scalars_kernel(SsdP p) {
-  __shared__ double wtot[8];
+constexpr int kScalBatch = 4;
+__global__ void __launch_bounds__(kScalThreads) m3s_scalars_kernel(SsdP p) {
+  __shared__ double wtot[kScalThreads / 32];
   const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   const size_t base = ((size_t)b * p.NH + head) * p.T;
-  const int per = (p.T + 255) / 256, lo = tid * per, hi = min(p.T, lo + per);
+  const int per = (p.T + kScalThreads - 1) / kScalThreads, lo = tid * per, hi = min(p.T, lo + per);
   // Batches of kScalBatch steps: all loads of a batch are issued before its first store (a store in between would
   // pin the order, since the compiler cannot prove the arrays distinct, and every step would pay a full memory latency).
   double acc = 0.0;
@@ -305,7 +308,7 @@ __global__ void __launch_bounds__(256) m3s_scalars_kernel(SsdP p) {
     }
   }
   double total;
-  double phi = cta_scan256(acc, wtot, total) - acc;  // angle at the start of this thread's steps
+  double phi = cta_scan(acc, wtot, total) - acc;  // angle at the start of this thread's steps
   const double two_pi = 6.283185307179586476925, inv_two_pi = 1.0 / two_pi;
   for (int t0 = lo; t0 < hi; t0 += kScalBatch) {
     float dtv[kScalBatch], th[kScalBatch];
@@ -927,13 +930,13 @@ __global__ void __launch_bounds__(256) m3s_chunk_grad_kernel(SsdP p, const __gri
 
 
 // ------------------------------------------------------------ final per-token scalars
-__global__ void __launch_bounds__(256) m3s_final_kernel(SsdP p) {
-  __shared__ double wtot[8];
-  __shared__ float wsum[8];
+__global__ void __launch_bounds__(kScalThreads) m3s_final_kernel(SsdP p) {
+  __shared__ double wtot[kScalThreads / 32];
+  __shared__ float wsum[kScalThreads / 32];
   const int head = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   const size_t base = ((size_t)b * p.NH + head) * p.T;
   const float A = -expf(p.a_log[head]);
-  const int per = (p.T + 255) / 256, lo = tid * per, hi = min(p.T, lo + per);
+  const int per = (p.T + kScalThreads - 1) / kScalThreads, lo = tid * per, hi = min(p.T, lo + per);
   double acc = 0.0;
   for (int t0 = lo; t0 < hi; t0 += kScalBatch) {
     float v[kScalBatch];
@@ -943,7 +946,7 @@ __global__ void __launch_bounds__(256) m3s_final_kernel(SsdP p) {
     for (int x = 0; x < kScalBatch; ++x) acc += (double)v[x];
   }
   double total;
-  const double incl = cta_scan256(acc, wtot, total);
+  const double incl = cta_scan(acc, wtot, total);
   double suf = total - incl;  // sum over the threads after this one (exclusive suffix; exact enough in fp64)
   float dal = 0.f;
   // backwards over this thread's steps, kFinalBatch at a time with the loads of a batch ahead of its stores
@@ -987,7 +990,7 @@ __global__ void __launch_bounds__(256) m3s_final_kernel(SsdP p) {
   __syncthreads();
   if (tid == 0) {
     float tot = 0.f;
-    for (int i = 0; i < 8; ++i) tot += wsum[i];
+    for (int i = 0; i < kScalThreads / 32; ++i) tot += wsum[i];
     p.dal_part[b * p.NH + head] = A * tot;  // summed over the batch in a fixed order by m3s_dalog_kernel
   }
 }
@@ -1111,7 +1114,7 @@ static mxb_status ssd_state_pass(SsdP& p, int mode, cudaStream_t st) {
 static mxb_status ssd_forward(SsdP& p, cudaStream_t st) {
   const dim3 gc(p.n, p.NH, p.B);
   if (cudaMemsetAsync(p.status, 0, 256, st) != cudaSuccess) return MXB_ERR_CUDA;
-  MXB_LAUNCH("m3s_scalars_kernel", st, (m3s::m3s_scalars_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
+  MXB_LAUNCH("m3s_scalars_kernel", st, (m3s::m3s_scalars_kernel<<<dim3(p.NH, p.B), m3s::kScalThreads, 0, st>>>(p)));
   MXB_LAUNCH("m3s_chunk_scalars_kernel", st, (m3s::m3s_chunk_scalars_kernel<<<gc, 64, 0, st>>>(p)));
   mxb_status ps = ssd_state_pass(p, 0, st);
   if (ps != MXB_OK) return ps;
@@ -1166,7 +1169,7 @@ mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
     if (ssd_smem(m3s::m3s_chunk_grad_kernel<false>, m3s::kGradSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("m3s_chunk_grad_kernel", st, (m3s::m3s_chunk_grad_kernel<false><<<gc, 256, m3s::kGradSmem, st>>>(p, maps)));
   }
-  MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), 256, 0, st>>>(p)));
+  MXB_LAUNCH("m3s_final_kernel", st, (m3s::m3s_final_kernel<<<dim3(p.NH, p.B), m3s::kScalThreads, 0, st>>>(p)));
   MXB_LAUNCH("m3s_dalog_kernel", st, (m3s::m3s_dalog_kernel<<<(p.NH + 127) / 128, 128, 0, st>>>(p)));
   MXB_LAUNCH("m3s_reduce_kernel", st,
              (m3s::m3s_reduce_kernel<<<dim3((p.T + 3) / 4, p.G, p.B), 128, 0, st>>>(p.pb, p.pc, static_cast<m3s::bf16*>(db),
