@@ -3,16 +3,17 @@
 //
 // Same mathematics as the fp32 path (gdn_simt.cu; reference
 // gated_delta_scan_chunked, gpu/ir.cpp:2352-2550).  Every contraction runs as
-// tcgen05.mma.kind::f16 on bf16 operands staged in shared memory in the
-// un-swizzled canonical layouts (umma_tiles.cuh) with fp32 accumulation in
-// tensor memory; the triangular inverse, all decay factors, the recurrent state
-// and every reduction stay in fp32.
+// tcgen05.mma.kind::f16 on bf16 operands staged in shared memory (token rows by
+// TMA in the 128-byte-swizzled layout, workspace tiles as byte images of the
+// canonical layouts of umma_tiles.cuh) with fp32 accumulation in tensor memory;
+// the triangular inverse, all decay factors, the recurrent state and every
+// reduction stay in fp32.
 //
-//   gdn_tc_prep_kernel       one CTA per chunk: [k;q] k^T (M=128), fp32 solve,
-//                            T [v beta | k beta E(gam)] (M=64, N=256) -> u, w, P, T
-//   gdn_tc_state_fwd_kernel  one CTA per (64-column slab of Dv, b*H+h), sequential over
-//                            chunks, fp32 state in registers (thread = state row):
-//                            [w;q] S (M=128) -> v_new, then [0;P] v_new and k^T (r v_new)
+//   gdn_tc_prep_kernel       one CTA per chunk (three per SM): [k;q] k^T (M=128), fp32 solve,
+//                            (T beta) v and (T beta E(gam)) k (M=64, N=128 each) -> u, w, P, T
+//   gdn_tc_state_fwd_kernel  one CTA per (batch, head), sequential over chunks, fp32 state in
+//                            registers (thread = state row, 64 columns), operands two chunks ahead:
+//                            [w;q] S (M=128) -> v_new, then [0;P] v_new and (r k)^T v_new
 #include <cuda.h>
 
 #include <cstring>

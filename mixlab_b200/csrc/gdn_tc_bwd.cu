@@ -7,9 +7,10 @@
 // With d = E(gam), r = E(gam_last-gam), L = E(gam_last), S0 the state at chunk start
 // and dS the state gradient at chunk end:
 //
-//   gdn_tc_state_bwd_kernel  reverse over chunks, one CTA per (64-column slab, b*H+h):
+//   gdn_tc_state_bwd_kernel  reverse over chunks, one CTA per (batch, head), operands two chunks ahead:
 //       dv_new = P^T dO + r (k dS)
-//       dS    <- L dS + q^T (d dO) - w^T dv_new
+//       dS    <- L dS + (d q)^T dO - w^T dv_new
+//   gdn_tc_chunk_bwd_state_kernel  one CTA per chunk: the contractions with the saved states S0 and dS
 //   gdn_tc_chunk_bwd_kernel  one CTA per chunk, everything else:
 //       dq = d (dO S0^T) + (dP*Gamma) k                      dP = tril(dO v_new^T)
 //       dw = -dv_new S0^T ; dT = dv_new (v beta)^T + dw (k beta d)^T ; dA = tril(T^T dT T^T,-1)
