@@ -90,7 +90,7 @@ gdn_decode_bulk_kernel(float* __restrict__ state, const IO* __restrict__ q, cons
   prefetch(0);
   bool ok = true;
 
-  for (int it = 0; it < my_tiles && ok; ++it) {
+  for (int it = 0; it < my_tiles; ++it) {
     const int s = it % kStages, par = (it / kStages) & 1, buf = it & 1;
     const size_t t = (size_t)first + (size_t)it * stride;
     float* S = tiles + s * (kMaxTileBytes / 4);
@@ -100,8 +100,10 @@ gdn_decode_bulk_kernel(float* __restrict__ state, const IO* __restrict__ q, cons
     const float bt = pre_beta;
     const float a = gate_is_log ? expf(pre_gate) : pre_gate;
     prefetch(it + 1);
-    ok = tc::mbar_wait(&full[s], par);
-    __syncthreads();  // k, q visible; tile landed for everybody
+    if (ok) ok = tc::mbar_wait(&full[s], par);
+    // k, q visible; tile landed for everybody
+    ok = __syncthreads_and(ok);  // the barrier also makes the verdict of the bounded waits uniform, so that all
+    if (!ok) break;              // threads leave the loop together
     const float* sk = s_k + buf * 128;
     const float* sq = s_q + buf * 128;
     float4 pk = make_float4(0.f, 0.f, 0.f, 0.f), pq = pk;

@@ -484,7 +484,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
   // in-chunk cumulative log decay of the chunk ahead, fetched one chunk early (its latency would otherwise sit
   // at the top of every link of the chain)
   float g_nxt = p.gam[(size_t)bh * p.n * C + (tid & 63)], gl_nxt = p.gam[(size_t)bh * p.n * C + C - 1];
-  for (int c = 0; c < p.n && ok; ++c) {
+  for (int c = 0; c < p.n; ++c) {
     const size_t ci = (size_t)bh * p.n + c;
     const int t0 = c * C, imax = min(C, p.T - t0);
     const int buf = c & 1;
@@ -511,10 +511,11 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
     }
     if (tid == 0) tc::bulk_wait_read<0>();  // the previous chunk's v_new image has left its tile
     if (!TMA) tc::cp_async_wait<5>();  // group A of this chunk has landed (q rows; the images on the barrier)
-    ok = tc::mbar_wait(&mbar[1 + buf], lph);
+    if (ok) ok = tc::mbar_wait(&mbar[1 + buf], lph);
     tc::fence_async_smem();
     tc::fence_before_sync();
-    __syncthreads();
+    ok = __syncthreads_and(ok);  // the barrier also makes the verdict of the bounded waits uniform, so that all
+    if (!ok) break;              // threads leave the loop together
     tc::fence_after_sync();
     if (tid == 0) {  // D1 = [w;q] S
       tc::issue_gemm(taddr, tc::kmajor_sw128_tile(A1c, 16384), tc::mnmajor_tile(Sop, KD), 128, KD, KD, false);

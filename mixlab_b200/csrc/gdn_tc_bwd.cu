@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
     scale_q(c);
   }
 
-  for (int c = p.n - 1; c >= 0 && ok; --c) {
+  for (int c = p.n - 1; c >= 0; --c) {
     const size_t ci = (size_t)bh * p.n + c;
     const int buf = c & 1;
     const uint32_t lph = ((p.n - 1 - c) >> 1) & 1;  // phase of this buffer's barriers
@@ -185,7 +185,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
     // group A of this chunk was waited for when its q was scaled (previous iteration / prologue)
     tc::fence_async_smem();
     tc::fence_before_sync();
-    __syncthreads();
+    ok = __syncthreads_and(ok);  // the barrier also makes the verdict of the bounded waits uniform, so that all
+    if (!ok) break;              // threads leave the loop together
     tc::fence_after_sync();
     if (tid == 0) {
       tc::issue_gemm(taddr, tc::kmajor_sw128_tile(Ak + buf * 16384, 8192), tc::mnmajor_tile(dSop, KD), 64, KD, KD, false);  // k dS

@@ -421,7 +421,7 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
   bf16* out = mode == 0 ? p.H0 : p.dH1;
   uint32_t ph = 0;
   fix_tiles(0);
-  for (int it = 0; it < p.n && ok; ++it) {
+  for (int it = 0; it < p.n; ++it) {
     const int c = chunk_at(it), buf = it & 1;
     const float L = Sc(buf).L;
     uint8_t* Hi = Himg + buf * 16384;  // the image written two chunks ago has left this tile (checked below)
@@ -429,7 +429,9 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
     for (int x = 0; x < 4; ++x) sts16(Hi, tc::kmajor_unit(nrow, 4 * half + x, P), pack8(&H[8 * x]));
     tc::fence_async_smem();
     tc::fence_before_sync();
-    __syncthreads();  // tiles of this chunk rotated and scaled (during the previous chunk's MMA), image staged
+    // tiles of this chunk rotated and scaled (during the previous chunk's MMA), image staged
+    ok = __syncthreads_and(ok);  // the barrier also makes the verdict of the bounded waits uniform, so that all
+    if (!ok) break;              // threads leave the loop together
     tc::fence_after_sync();
     if (tid == 0) {  // [128 n x 64 p] = R^T X, both contracted over their rows
       if (TMA)
@@ -442,7 +444,7 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
       tc::bulk_wait_read<1>();  // all but the copy just issued have been read out of shared memory
     }
     if (it + 1 < p.n) {  // while the tensor core works: the next chunk's tiles
-      if (TMA) ok = tc::mbar_wait(&mbar[1 + (buf ^ 1)], ((it + 1) >> 1) & 1);
+      if (TMA) { if (ok) ok = tc::mbar_wait(&mbar[1 + (buf ^ 1)], ((it + 1) >> 1) & 1); }
       else tc::cp_async_wait<0>();
       __syncthreads();
       fix_tiles(buf ^ 1);
