@@ -48,7 +48,7 @@ GDN_BLOCK_BYTES_PER_TOKEN_HEAD = 23 * 128 * 2 + 10 * 4
 M3_BLOCK_BYTES_PER_TOKEN = lambda D, GN: (13 * D + 10 * GN) * 2
 # DRAM traffic per unit from the committed ncu captures (profiles/): dram__bytes_read.sum + dram__bytes_write.sum
 GDN_NCU_TRAFFIC_PER_CHUNK = 1280.5e6 / 2048    # B=2 capture: 1280.5 MB over 2048 (batch, head, chunk) units
-M3_NCU_TRAFFIC_PER_CHUNK = 746.4e6 / 4096      # B=2 capture: 746.4 MB over 2 x 32 x 64 (batch, head, chunk) units
+M3_NCU_TRAFFIC_PER_CHUNK = 747.8e6 / 4096      # B=2 capture: 747.8 MB over 2 x 32 x 64 (batch, head, chunk) units
 DECODE_NCU_TRAFFIC_PER_TILE = 482.8e6 / 4096   # full-size capture: 482.8 MB over 256 x 16 (sequence, head) tiles
 
 
