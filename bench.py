@@ -47,8 +47,8 @@ GDN_BLOCK_BYTES_PER_TOKEN_HEAD = 23 * 128 * 2 + 10 * 4
 # Mamba-3 block stages, fwd+bwd, bf16: conv 2 + 3, post 3 + 5 tensors of D channels; B/C norm 4 + 6 tensors of G*N
 M3_BLOCK_BYTES_PER_TOKEN = lambda D, GN: (13 * D + 10 * GN) * 2
 # DRAM traffic per unit from the committed ncu captures (profiles/): dram__bytes_read.sum + dram__bytes_write.sum
-GDN_NCU_TRAFFIC_PER_CHUNK = 1280.5e6 / 2048    # B=2 capture: 1280.5 MB over 2048 (batch, head, chunk) units
-M3_NCU_TRAFFIC_PER_CHUNK = 747.8e6 / 4096      # B=2 capture: 747.8 MB over 2 x 32 x 64 (batch, head, chunk) units
+GDN_NCU_TRAFFIC_PER_CHUNK = 5648.3e6 / 8192    # one-pass DRAM-byte capture of a full-size step: 5648.3 MB over 8 x 16 x 64 (batch, head, chunk) units
+M3_NCU_TRAFFIC_PER_CHUNK = 3447.8e6 / 16384    # one-pass DRAM-byte capture of a full-size step: 3447.8 MB over 8 x 32 x 64 units
 DECODE_NCU_TRAFFIC_PER_TILE = 482.8e6 / 4096   # full-size capture: 482.8 MB over 256 x 16 (sequence, head) tiles
 
 
@@ -218,7 +218,7 @@ def main():
         alg_flops = units * H * GDN_FLOPS_PER_TOKEN_HEAD
         bound = "hbm"
         traffic = B * H * ((T + Cc - 1) // Cc) * GDN_NCU_TRAFFIC_PER_CHUNK if not args.fp32_path else None
-        traffic_note = "ncu capture at B=2 scaled by the number of (batch, head, chunk) units"
+        traffic_note = "one-pass ncu capture (dram bytes read + written) of a full-size step, per (batch, head, chunk) unit x units"
 
         def step():
             ops.gated_delta_scan(d["q"], d["k"], d["v"], d["beta"], d["g"], Cc, gate_is_log=True, flags=flags,
@@ -328,7 +328,7 @@ def main():
         alg_flops = units * M3_FLOPS_PER_TOKEN
         bound = "hbm"
         traffic = B * NH * ((T + 63) // 64) * M3_NCU_TRAFFIC_PER_CHUNK if (P, N) == (64, 128) else None
-        traffic_note = "ncu capture at B=2 scaled by the number of (batch, head, chunk) units"
+        traffic_note = "one-pass ncu capture (dram bytes read + written) of a full-size step, per (batch, head, chunk) unit x units"
         margs = [d[k] for k in ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")]
 
         def step():
