@@ -333,10 +333,12 @@ __global__ void __launch_bounds__(kScalThreads) m3s_scalars_kernel(SsdP p) {
 // state in registers (thread = state row n and 32 of its 64 fp32 columns):
 //   mode 0: H0_c = H;  H = L_c H + Brot_c^T diag(r e) X_c          (states at chunk start, for y and the backward)
 //   mode 1: dH1_c = dH; dH = L_c dH + Crot_c^T diag(exp(Lam)) dY_c  (state gradients at chunk end)
-// The chunk contribution is one M=128 tcgen05 tile that never leaves the SM; the operands of the next two
-// chunks are in flight (cp.async, two buffers) while the current one is rotated, multiplied and folded in.
-// The saved state leaves as the byte image of the [128][64] operand tile (one bulk copy per chunk).
-constexpr int kPassSmem = 2 * (16384 + 8192) + 2 * sizeof(ChunkScal) + 2 * 16384 + 64 + 1024;
+// The chunk contribution is one M=128 tcgen05 tile that never leaves the SM; the operands of the next chunks are
+// in flight in a ring of kPassStages buffers (a chunk takes ~1.5 us here and a copy up to ~2 us, so with two
+// buffers every chunk waited ~0.9 k cycles for its tiles) while the current one is rotated, multiplied and folded
+// in.  The saved state leaves as the byte image of the [128][64] operand tile (one bulk copy per chunk).
+constexpr int kPassStages = 3;
+constexpr int kPassSmem = kPassStages * (16384 + 8192) + kPassStages * sizeof(ChunkScal) + 2 * 16384 + 64 + 1024;
 
 struct PassMaps {
   CUtensorMap r;  // b or c: [B,T,G,128] viewed as (N, G, T, B), boxes of 64 columns x 64 steps, 128-byte swizzle
@@ -349,24 +351,24 @@ template <bool TMA>
 __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, const __grid_constant__ PassMaps maps) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
-  uint8_t* Himg = sm + 2 * (16384 + 8192);  // 2 x [128 n][64 p] bf16 images of the state on their way out
+  uint8_t* Himg = sm + kPassStages * (16384 + 8192);  // 2 x [128 n][64 p] bf16 images of the state on their way out
   uint8_t* scal = Himg + 2 * 16384;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(scal + 2 * sizeof(ChunkScal));  // [0] MMA, [1], [2] buffers full
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(scal + kPassStages * sizeof(ChunkScal));  // [0] MMA, [1 + stage] stage full
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 1 + kPassStages);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int nrow = tid & 127, half = tid >> 7;  // thread = state row n, 32 of its 64 columns
   const int head = blockIdx.x, b = blockIdx.y;
   const int d0 = head * P, g = d0 / (p.D / p.G);
   const size_t cbase = ((size_t)b * p.NH + head) * p.n;
   auto Rt = [&](int buf) { return sm + buf * 16384; };             // [64 s][128 n] B or C rows, rotated in place
-  auto Xt = [&](int buf) { return sm + 32768 + buf * 8192; };      // [64 s][64 p]  x or dy, scaled in place
+  auto Xt = [&](int buf) { return sm + kPassStages * 16384 + buf * 8192; };  // [64 s][64 p]  x or dy, scaled in place
   auto Sc = [&](int buf) -> ChunkScal& { return *reinterpret_cast<ChunkScal*>(scal + buf * sizeof(ChunkScal)); };
   auto chunk_at = [&](int it) { return mode == 0 ? it : p.n - 1 - it; };
   auto issue = [&](int it) {
     if (it < p.n) {
-      const int c = chunk_at(it), buf = it & 1;
+      const int c = chunk_at(it), buf = it % kPassStages;
       if (TMA) {
-        if (tid == 0) {
+        if (tid == 32) {  // not the thread that issues the MMAs and the stores
           tc::mbar_expect_tx(&mbar[1 + buf], 16384 + 8192 + (uint32_t)sizeof(ChunkScal));
           tc::tma_load_4d(tc::smem_u32(Rt(buf)), &maps.r, 0, g, c * Q, b, &mbar[1 + buf]);
           tc::tma_load_4d(tc::smem_u32(Rt(buf)) + 8192, &maps.r, 64, g, c * Q, b, &mbar[1 + buf]);
@@ -402,18 +404,17 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
   };
   if (warp == 0) { tc::tmem_alloc(tslot, 64); tc::tmem_relinquish(); }
   if (tid == 0) {
-    for (int m = 0; m < 3; ++m) tc::mbar_init(&mbar[m], 1);
+    for (int m = 0; m < 1 + kPassStages; ++m) tc::mbar_init(&mbar[m], 1);
     tc::mbar_fence_init();
   }
   __syncthreads();  // barriers initialised before the copies can complete on them
-  issue(0);
-  issue(1);
+  for (int it = 0; it < kPassStages; ++it) issue(it);
   float H[32];
 #pragma unroll
   for (int x = 0; x < 32; ++x) H[x] = 0.f;
   bool ok = true;
   if (TMA) ok = tc::mbar_wait(&mbar[1], 0);
-  else tc::cp_async_wait<1>();  // operands of the first chunk
+  else tc::cp_async_wait<kPassStages - 1>();  // operands of the first chunk
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
@@ -422,9 +423,9 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
   uint32_t ph = 0;
   fix_tiles(0);
   for (int it = 0; it < p.n; ++it) {
-    const int c = chunk_at(it), buf = it & 1;
+    const int c = chunk_at(it), buf = it % kPassStages, nbuf = (it + 1) % kPassStages;
     const float L = Sc(buf).L;
-    uint8_t* Hi = Himg + buf * 16384;  // the image written two chunks ago has left this tile (checked below)
+    uint8_t* Hi = Himg + (it & 1) * 16384;  // the image written two chunks ago has left this tile (checked below)
 #pragma unroll
     for (int x = 0; x < 4; ++x) sts16(Hi, tc::kmajor_unit(nrow, 4 * half + x, P), pack8(&H[8 * x]));
     tc::fence_async_smem();
@@ -444,15 +445,15 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
       tc::bulk_wait_read<1>();  // all but the copy just issued have been read out of shared memory
     }
     if (it + 1 < p.n) {  // while the tensor core works: the next chunk's tiles
-      if (TMA) { if (ok) ok = tc::mbar_wait(&mbar[1 + (buf ^ 1)], ((it + 1) >> 1) & 1); }
-      else tc::cp_async_wait<0>();
+      if (TMA) { if (ok) ok = tc::mbar_wait(&mbar[1 + nbuf], ((it + 1) / kPassStages) & 1); }
+      else tc::cp_async_wait<kPassStages - 2>();
       __syncthreads();
-      fix_tiles(buf ^ 1);
+      fix_tiles(nbuf);
     }
     if (ok) ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
     tc::fence_after_sync();
-    issue(it + 2);  // this buffer is free: the MMA has read the tiles, every thread has read L
+    issue(it + kPassStages);  // this buffer is free: the MMA has read the tiles, every thread has read L
     if (ok) {
       float f[32];
       ld_acc32(taddr, warp, 32 * half, f);
