@@ -338,6 +338,7 @@ __global__ void __launch_bounds__(kScalThreads) m3s_scalars_kernel(SsdP p) {
 // buffers every chunk waited ~0.9 k cycles for its tiles) while the current one is rotated, multiplied and folded
 // in.  The saved state leaves as the byte image of the [128][64] operand tile (one bulk copy per chunk).
 constexpr int kPassStages = 3;
+constexpr int kPassStoreThread = 64;   // issues the state-image stores (its own bulk-group queue)
 constexpr int kPassSmem = kPassStages * (16384 + 8192) + kPassStages * sizeof(ChunkScal) + 2 * 16384 + 64 + 1024;
 
 struct PassMaps {
@@ -368,10 +369,14 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
     if (it < p.n) {
       const int c = chunk_at(it), buf = it % kPassStages;
       if (TMA) {
-        if (tid == 32) {  // not the thread that issues the MMAs and the stores
+        // two threads of two other warps than the one that issues the MMAs share the copies; the barrier's single
+        // arrival is the expect_tx, so the phase cannot complete before every byte announced there has landed
+        if (tid == 32) {
           tc::mbar_expect_tx(&mbar[1 + buf], 16384 + 8192 + (uint32_t)sizeof(ChunkScal));
           tc::tma_load_4d(tc::smem_u32(Rt(buf)), &maps.r, 0, g, c * Q, b, &mbar[1 + buf]);
           tc::tma_load_4d(tc::smem_u32(Rt(buf)) + 8192, &maps.r, 64, g, c * Q, b, &mbar[1 + buf]);
+        }
+        if (tid == 96) {
           tc::tma_load_4d(tc::smem_u32(Xt(buf)), &maps.x, 0, head, c * Q, b, &mbar[1 + buf]);
           tc::bulk_load(tc::smem_u32(&Sc(buf)), p.cs + (cbase + c) * (sizeof(ChunkScal) / 4), (uint32_t)sizeof(ChunkScal),
                         &mbar[1 + buf]);
@@ -440,6 +445,8 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
       else
         tc::issue_gemm(taddr, tc::mnmajor_tile(Rt(buf), N), tc::mnmajor_tile(Xt(buf), P), 128, P, Q, false);
       tc::mma_commit(mbar);
+    }
+    if (tid == kPassStoreThread) {  // the state image leaves from another warp than the one issuing the MMAs
       tc::bulk_store(out + (cbase + c) * (N * P), tc::smem_u32(Hi), 16384);
       tc::bulk_commit();
       tc::bulk_wait_read<1>();  // all but the copy just issued have been read out of shared memory
@@ -463,7 +470,7 @@ __global__ void __launch_bounds__(256) m3s_state_pass_kernel(SsdP p, int mode, c
     tc::fence_before_sync();
   }
   if (!TMA) tc::cp_async_wait<0>();
-  if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
+  if (tid == kPassStoreThread) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 11);
   tc::fence_before_sync();
   __syncthreads();
