@@ -544,6 +544,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   // the per-row scalars.
   if (tid == 32) {
     tc::mbar_init(mbar + 0, 1);
+    tc::mbar_init(mbar + 5, 1);  // second MMA barrier: a phase with two commits never puts both on one barrier (a waiter
+                                 // that falls two phases behind a single barrier would wait for a third)
     tc::mbar_init(mbar + 1, 1);
     tc::mbar_fence_init();
     if (TMA) {
@@ -672,18 +674,33 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   __syncthreads();
   tc::fence_after_sync();
   // ---- phase 2: Y = T^T dT = (T^T dv_new)(v beta)^T + z (k beta d)^T, with the column scales applied in the
-  //      epilogue; k k^T and q k^T ride along ----
+  //      epilogue; k k^T and q k^T ride along.  Two commits: the Y epilogue (all the next MMA needs) runs while
+  //      the tensor core still works on k k^T and q k^T ----
   if (ok && tid == 0) {
     tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdvn, KD), in_kmajor<TMA>(Xv), 64, 64, KD, false);
     tc::issue_gemm(taddr + 64, tc::kmajor_tile(Xdw, KD), in_kmajor<TMA>(Xk), 64, 64, KD, false);
+    tc::mma_commit(mbar);
     tc::issue_gemm(taddr + 128, in_kmajor<TMA>(Xk), in_kmajor<TMA>(Xk), 64, 64, KD, false);  // k k^T
     tc::issue_gemm(taddr + 192, in_kmajor<TMA>(Xq), in_kmajor<TMA>(Xk), 64, 64, KD, false);  // q k^T
-    tc::mma_commit(mbar);
+    tc::mma_commit(mbar + 5);
   }
   if (ok) {
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
   }
+  tc::fence_after_sync();
+  if (ok) {  // Y[i][m] = beta_m ((T^T dv_new)_i . v_m) + beta_m d_m (z_i . k_m)   -> X2 (v is dead)
+    float f[32], f2[32];
+    ld_acc32(taddr + 0, warp, cb, f);
+    ld_acc32(taddr + 64, warp, cb, f2);
+    if (own) {
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) f[jj] = bet[cb + jj] * fmaf(dd[cb + jj], f2[jj], f[jj]);
+#pragma unroll
+      for (int x = 0; x < 4; ++x) sts16(X2, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
+    }
+  }
+  if (ok) ok = tc::mbar_wait(mbar + 5, 0);
   tc::fence_after_sync();
   float KKr[32];  // (k_i . k_j) for j in [cb, cb+32)
   if (ok) {
@@ -712,17 +729,6 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
       }
     }
     ld_acc32(taddr + 128, warp, cb, KKr);  // k k^T
-    {  // Y[i][m] = beta_m ((T^T dv_new)_i . v_m) + beta_m d_m (z_i . k_m)   -> X2 (v is dead)
-      float f2[32];
-      ld_acc32(taddr + 0, warp, cb, f);
-      ld_acc32(taddr + 64, warp, cb, f2);
-      if (own) {
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) f[jj] = bet[cb + jj] * fmaf(dd[cb + jj], f2[jj], f[jj]);
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(X2, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
-      }
-    }
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
@@ -799,19 +805,20 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   // ---- phase 4: (dP*Gamma) k  and  (dP*Gamma)^T q + (Mb + Mb^T) k ----
   if (ok && tid == 0) {
     tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xpg, C), in_mnmajor<TMA>(Xk), 64, 128, C, false);
+    tc::mma_commit(mbar);  // the dq epilogue runs while the three products of dk are still on the tensor core
     tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xpg, C), in_mnmajor<TMA>(Xq), 64, 128, C, false);
     tc::issue_gemm(taddr + 128, tc::kmajor_tile(X1, C), in_mnmajor<TMA>(Xk), 64, 128, C, true);
     tc::issue_gemm(taddr + 128, tc::mnmajor_tile(X1, C), in_mnmajor<TMA>(Xk), 64, 128, C, true);
-    tc::mma_commit(mbar);
+    tc::mma_commit(mbar + 5);
   }
   if (ok) {
     ok = tc::mbar_wait(mbar, ph);
     ph ^= 1;
   }
   tc::fence_after_sync();
+  // dq and dk are assembled over the dqp / dkp images (each thread rewrites the units it read)
+  float qdot = 0.f, kdot = 0.f;
   if (ok) {
-    // dq and dk are assembled over the dqp / dkp images (each thread rewrites the units it read)
-    float qdot = 0.f, kdot = 0.f;
     for (int s = 0; s < 2; ++s) {
       const int c0 = cw + 32 * s;
       float f[32], g2[32];
@@ -830,6 +837,14 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Xv, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&g2[8 * x]));
       }
+    }
+  }
+  if (ok) ok = tc::mbar_wait(mbar + 5, 1);
+  tc::fence_after_sync();
+  if (ok) {
+    for (int s = 0; s < 2; ++s) {
+      const int c0 = cw + 32 * s;
+      float f[32], g2[32];
       ld_acc32(taddr + 128, warp, c0, g2);  // (dP*Gamma)^T q + (Mb+Mb^T) k
       if (own) {
 #pragma unroll
