@@ -139,6 +139,23 @@ def test_decode_steps():
             assert_close(st, st_ref, 1e-4, f"state@{t + 1}")
 
 
+def test_decode_1024_steps():
+    """Recurrent decode: the state and the output after 1024 steps on 4 sequences (config 2 dims) still match the
+    float64 recurrence (fp32 state, bf16 tokens)."""
+    N, H, K, V, steps = 4, 16, 128, 128, 1024
+    a = inputs.gdn_decode_inputs(N, H, K, V, steps, seed=22, io_dtype=torch.bfloat16)
+    st_ref = a["state"].double()
+    st = _dev(a["state"].clone())
+    q, k, v, beta, g = (_dev(a[n]) for n in ("q", "k", "v", "beta", "g"))
+    for t in range(steps):
+        o_ref, st_ref = gdn.decode_step(st_ref, a["q"][t].double(), a["k"][t].double(), a["v"][t].double(),
+                                        a["beta"][t].double(), torch.exp(a["g"][t].double()))
+        o = ops.gated_delta_decode_step(st, q[t], k[t], v[t], beta[t], g[t], gate_is_log=True)
+        if t + 1 in (256, 1024):
+            assert_close(o, o_ref, TOL_BF16, f"out@{t + 1}")
+            assert_close(st, st_ref, 1e-4, f"state@{t + 1}")
+
+
 @pytest.mark.parametrize("dims", [(3, 2, 64, 64), (2, 3, 8, 12), (1, 1, 200, 256), (2, 2, 40, 132)])
 def test_decode_fp32_shapes(dims):
     N, H, K, V = dims
