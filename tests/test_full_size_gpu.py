@@ -2,7 +2,8 @@
 minutes): splitting a sequence in two with the state handed over, independence of the (batch, head) problems,
 backward from saved intermediates against the recomputing backward, tensor-copy staging against per-thread staging.
 Every property compares two runs of the same kernels on the same data, so the bar is bit-exact equality
-(fp32 hand-over of the state and fixed-order reductions make the two sides the same arithmetic).
+(fp32 hand-over of the state and fixed-order reductions make the two sides the same arithmetic).  One sequence of the
+benchmark configuration is also checked against the float64 oracle itself (about 12 s of CPU time).
 
 Sizes: gated delta rule B=8, T=4096, H=16, d_k=d_v=128, chunk 64, bf16 I/O; recurrent decode 256 sequences x 16
 heads; Mamba-3 B=8, T=4096, 32 heads x 64, d_state 128, bf16 I/O."""
@@ -12,6 +13,8 @@ import pytest
 import torch
 
 from mixlab_b200 import _lib, ops
+from oracle import gdn, inputs
+from tests.util import assert_close
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -122,6 +125,26 @@ def test_gdn_decode_kernels_agree_and_match_one_step_scan():
 
     assert close(o1, o2, 1e-5) and close(s1, s2, 1e-5)
     assert close(o1, o3[:, 0], 1e-4) and close(s1, s3, 1e-4)
+
+
+def test_gdn_config1_sub_batch_against_oracle():
+    """One sequence of the benchmark configuration (T=4096, H=16, d=128, chunk 64, bf16 I/O) against the float64 oracle
+    in its chunked form (itself checked against the naive recurrence on the small shapes): outputs, final state and
+    every gradient within 2e-2."""
+    a = inputs.gdn_inputs(1, 4096, 16, 128, 128, seed=1, io_dtype=torch.bfloat16, with_grad_out=True)
+    f = {k: v.double() for k, v in a.items()}
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], f["g"], f["d_out"], gate_is_log=True, chunk_size=64)
+    dev = {k: v.to(DEV).contiguous() for k, v in a.items()}
+    o, s = ops.gated_delta_scan(dev["q"], dev["k"], dev["v"], dev["beta"], dev["g"], 64, gate_is_log=True,
+                                return_final_state=True)
+    got = ops.gated_delta_scan_backward(dev["q"], dev["k"], dev["v"], dev["beta"], dev["g"], dev["d_out"], 64,
+                                        gate_is_log=True)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert_close(o, want["out"], 2e-2, "out")
+    assert_close(s, want["state"], 2e-2, "final_state")
+    for name in ("dq", "dk", "dv", "dbeta", "dgate"):
+        assert_close(got[name], want[name], 2e-2, name)
 
 
 def _m3_full(B=8, T=4096, NH=32, P=64, N=128, seed=31):
