@@ -190,3 +190,43 @@ def test_mamba3_saved_forward_staging_variants_and_batch_rows():
     for name in M3_GRADS:
         if name != "da_log":
             assert torch.equal(g[name][bsel:bsel + 1], g1[name]), name
+
+
+def test_mamba3_full_length_two_heads_against_oracle():
+    """T=4096 (64 chunks: the state chain and the wrapped angle at the benchmark length), two heads of 64 channels,
+    d_state 128, bf16 I/O, against the float64 oracle on the bf16-rounded inputs: output and every gradient within 2e-2."""
+    from oracle import mamba3
+    B, T, H, P, N = 1, 4096, 2, 64, 128
+    args = ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")
+    a = inputs.mamba3_inputs(B, T, H, P, N, G=1, seed=6, io_dtype=torch.bfloat16, per_head=True)
+    full = inputs.mamba3_expand_per_head(a)
+    y_ref, want = mamba3.scan_vjp(*(full[k].double() for k in args), a["dy"].double())
+    want = dict(want)
+    want["ddt"] = want["ddt"].reshape(B, T, H, P).sum(-1)
+    want["dlambda"] = want["dlambda"].reshape(B, T, H, P).sum(-1)
+    want["dtheta"] = want["dtheta"].reshape(B, T, H, P, N // 2).sum((-1, -2))
+    want["da_log"] = want["da_log"].reshape(H, P, N).sum((-1, -2))
+    dev = [a[k].to(DEV).contiguous() for k in args]
+    y = ops.mamba3_selective_scan(*dev, nheads=H)
+    got = ops.mamba3_selective_scan_backward(*dev, a["dy"].to(DEV).contiguous(), nheads=H)
+    torch.cuda.synchronize()
+    assert_close(y, y_ref, 2e-2, "y")
+    for name in M3_GRADS:
+        assert_close(got[name], want[name], 2e-2, name)
+
+
+def test_mamba3_full_size_chunked_against_recurrent_kernels():
+    """Config-3 size: the chunked tensor-core kernels against the recurrent CTA-per-head kernels (a different
+    algorithm for the same mathematics, itself checked against the oracle on small shapes), 2e-2."""
+    args, dy = _m3_full(seed=32)
+    NH = 32
+    y = ops.mamba3_selective_scan(*args, nheads=NH)
+    g = ops.mamba3_selective_scan_backward(*args, dy, nheads=NH)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0  # (the status word leads the chunked kernels' workspace only)
+    y_r = ops.mamba3_selective_scan(*args, nheads=NH, flags=_lib.MXB_MAMBA3_RECURRENT_KERNELS)
+    g_r = ops.mamba3_selective_scan_backward(*args, dy, nheads=NH, flags=_lib.MXB_MAMBA3_RECURRENT_KERNELS)
+    torch.cuda.synchronize()
+    assert_close(y, y_r.double(), 2e-2, "y")
+    for name in M3_GRADS:
+        assert_close(g[name], g_r[name].double(), 2e-2, name)
