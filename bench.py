@@ -46,10 +46,29 @@ M3_FLOPS_PER_TOKEN = 5.50e6
 GDN_BLOCK_BYTES_PER_TOKEN_HEAD = 23 * 128 * 2 + 10 * 4
 # Mamba-3 block stages, fwd+bwd, bf16: conv 2 + 3, post 3 + 5 tensors of D channels; B/C norm 4 + 6 tensors of G*N
 M3_BLOCK_BYTES_PER_TOKEN = lambda D, GN: (13 * D + 10 * GN) * 2
-# DRAM traffic per unit from the committed ncu captures (profiles/): dram__bytes_read.sum + dram__bytes_write.sum
-GDN_NCU_TRAFFIC_PER_CHUNK = 5648.3e6 / 8192    # one-pass DRAM-byte capture of a full-size step: 5648.3 MB over 8 x 16 x 64 (batch, head, chunk) units
-M3_NCU_TRAFFIC_PER_CHUNK = 3447.8e6 / 16384    # one-pass DRAM-byte capture of a full-size step: 3447.8 MB over 8 x 32 x 64 units
-DECODE_NCU_TRAFFIC_PER_TILE = 482.8e6 / 4096   # full-size capture: 482.8 MB over 256 x 16 (sequence, head) tiles
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, MB per launch at the full workload size) per kernel, from
+# one ncu byte capture of a step.  Keyed by kernel name: when the kernels a step launches are not exactly these, the
+# capture no longer describes the step and roofline.traffic is reported as null instead of a stale number.
+GDN_NCU_TRAFFIC_MB = {
+    "gdn_tc_prep_kernel": 763.0, "gdn_tc_state_fwd_kernel": 1090.2, "gdn_tc_state_bwd_kernel": 963.7,
+    "gdn_tc_chunk_bwd_state_kernel": 1373.9, "gdn_tc_chunk_bwd_kernel": 1457.5,
+}
+GDN_NCU_TRAFFIC_UNITS = 8192     # (batch, head, chunk) units of the captured step
+M3_NCU_TRAFFIC_MB = {
+    "m3s_scalars_kernel": 12.6, "m3s_chunk_scalars_kernel": 12.6, "m3s_state_pass_kernel": 390.3 + 390.4,
+    "m3s_chunk_out_kernel": 566.2, "m3s_chunk_grad_kernel": 1494.2, "m3s_final_kernel": 33.6, "m3s_dalog_kernel": 0.0,
+    "m3s_reduce_kernel": 548.0,
+}
+M3_NCU_TRAFFIC_UNITS = 16384
+DECODE_NCU_TRAFFIC_MB = {"gdn_decode_bulk_kernel": 482.8}
+DECODE_NCU_TRAFFIC_UNITS = 4096  # (sequence, head) tiles of the captured launch
+
+
+def traffic_from_table(table, table_units, units, kernels, launches_per_step=1):
+    """Bytes per step from the per-kernel capture, or None when the step's kernel list differs from the capture's."""
+    if not kernels or set(kernels) != set(table):
+        return None
+    return sum(table.values()) * 1e6 * launches_per_step * units / table_units
 
 
 def peaks():
@@ -137,6 +156,13 @@ def cpu_gdn_sample(threads: int, passes: int):
     return w["T"], times
 
 
+def gdn_train_cfg(w, world):
+    """The config object of the headline workload (the same for both arms)."""
+    return {"workload": "gdn_train", **w, "io": "bf16", "state": "fp32", "per_gpu_batch": w["B"],
+            "parallelism": f"batch-sharded x{world}, no collective",
+            "l2": "inputs (q,k,v,dO = 4 x 134 MB at B=8) exceed the 126 MB L2"}
+
+
 def run_reference_arm(args):
     rank, world, _ = dist_env()
     if rank != 0:
@@ -152,7 +178,7 @@ def run_reference_arm(args):
         "impl": "reference", "metric": "gdn_fwd_bwd_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": len(times), "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "gdn_train B=8/GPU T=4096 H=16 dk=dv=128 chunk=64 (CPU arm: bounded sample)", **w},
+        "config": gdn_train_cfg(w, max(1, args.gpus)),
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -160,200 +186,201 @@ def run_reference_arm(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gdn_train", choices=sorted(WORKLOADS))
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--fp32-path", action="store_true", help="force the CUDA-core fp32 kernels")
-    ap.add_argument("--batch", type=int, default=0,
-                    help="override the per-GPU batch (sequences) - small cases for profiler captures only")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
-        return run_reference_arm(args)
+class Ctx:
+    """What the workload builders and the timing loop share."""
 
-    rank, world, local = dist_env()
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU fallback")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
-        # NCCL prints its version banner on stdout at VERSION level; stdout carries only the JSON line
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"
-        dist.init_process_group("nccl", device_id=dev)
+    def __init__(self, args):
+        self.args = args
+        self.rank, self.world, self.local = dist_env()
+        self.dev = torch.device("cuda", self.local)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            self.dist = dist
+        import mixlab_b200
+        from mixlab_b200 import ops, _lib, sharding
+        from oracle import inputs  # seeded input generators only (no compute)
+        self.mx, self.ops, self._lib, self.sharding, self.inputs = mixlab_b200, ops, _lib, sharding, inputs
+        self.lib = mixlab_b200.lib()
+        self.pk = peaks()
 
-    import mixlab_b200
-    from mixlab_b200 import ops, _lib, sharding
-    from oracle import inputs  # seeded input generators only (no compute)
-    lib = mixlab_b200.lib()
-    pk = peaks()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
-    flags = _lib.MXB_GDN_FORCE_FP32_PATH if args.fp32_path else 0
-    e2e = None
-    if args.workload == "gdn_train":
-        w = dict(WORKLOADS["gdn_train"])
-        if args.batch > 0:
-            w["B"] = args.batch
-        B, T, H, K, V, Cc = w["B"], w["T"], w["H"], w["Dk"], w["Dv"], w["chunk"]
-        # seeded inputs, generated one sequence at a time to bound host memory
-        parts = [inputs.gdn_inputs(1, T, H, K, V, seed=1000 * (rank + 1) + b, io_dtype=torch.bfloat16,
-                                   with_grad_out=True) for b in range(B)]
-        host = {k: torch.cat([p[k] for p in parts]).contiguous().pin_memory() for k in parts[0]}
-        d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
-        units = B * T  # tokens per step per GPU
-        metric, unit, dtype = "gdn_fwd_bwd_tokens_per_s", "tokens/s", "bf16"
-        alg_bytes = units * H * GDN_BYTES_PER_TOKEN_HEAD
-        alg_flops = units * H * GDN_FLOPS_PER_TOKEN_HEAD
-        bound = "hbm"
-        traffic = B * H * ((T + Cc - 1) // Cc) * GDN_NCU_TRAFFIC_PER_CHUNK if not args.fp32_path else None
-        traffic_note = "one-pass ncu capture (dram bytes read + written) of a full-size step, per (batch, head, chunk) unit x units"
 
-        def step():
-            ops.gated_delta_scan(d["q"], d["k"], d["v"], d["beta"], d["g"], Cc, gate_is_log=True, flags=flags,
-                                 save_for_backward=True)
-            ops.gated_delta_scan_backward(d["q"], d["k"], d["v"], d["beta"], d["g"], d["d_out"], Cc,
-                                          gate_is_log=True, flags=flags, use_saved=True)
+def build_gdn_train(cx, batch):
+    w = dict(WORKLOADS["gdn_train"])
+    if batch > 0:
+        w["B"] = batch
+    B, T, H, K, V, Cc = w["B"], w["T"], w["H"], w["Dk"], w["Dv"], w["chunk"]
+    flags = cx._lib.MXB_GDN_FORCE_FP32_PATH if cx.args.fp32_path else 0
+    # seeded inputs, generated one sequence at a time to bound host memory
+    parts = [cx.inputs.gdn_inputs(1, T, H, K, V, seed=1000 * (cx.rank + 1) + b, io_dtype=torch.bfloat16,
+                                  with_grad_out=True) for b in range(B)]
+    host = {k: torch.cat([p[k] for p in parts]).contiguous().pin_memory() for k in parts[0]}
+    d = {k: v.to(cx.dev, non_blocking=True) for k, v in host.items()}
+    units = B * T  # tokens per step per GPU
+    ops = cx.ops
 
-        cfg = {"workload": "gdn_train", **w, "io": "bf16", "state": "fp32", "per_gpu_batch": B,
-               "parallelism": f"batch-sharded x{world}, no collective",
-               "l2": "inputs (q,k,v,dO = 4 x 134 MB) exceed the 126 MB L2"}
-    elif args.workload == "gdn_decode":
-        w = dict(WORKLOADS["gdn_decode"])
-        if args.batch > 0:
-            w["N"] = args.batch
-        N, H, K, V, tps = w["N"], w["H"], w["Dk"], w["Dv"], w["tokens_per_step"]
-        a = inputs.gdn_decode_inputs(N, H, K, V, 16, seed=2 + rank, io_dtype=torch.bfloat16)
-        d = {k: v.to(dev) for k, v in a.items()}
-        out = torch.empty(N, H, V, dtype=torch.bfloat16, device=dev)
-        units = N * tps
-        metric, unit, dtype = "gdn_decode_tokens_per_s", "tokens/s", "f32"
-        per_tok_bytes = 2 * K * V * 4 * H + (2 * K + 2 * V) * 2 * H + 8 * H
-        alg_bytes = units * per_tok_bytes
-        alg_flops = units * H * 7 * K * V
-        bound = "hbm"
-        traffic = tps * N * H * DECODE_NCU_TRAFFIC_PER_TILE if (K, V) == (128, 128) else None
-        traffic_note = "ncu capture of one launch at config 2, per launch x launches per step"
+    def step():
+        ops.gated_delta_scan(d["q"], d["k"], d["v"], d["beta"], d["g"], Cc, gate_is_log=True, flags=flags,
+                             save_for_backward=True)
+        ops.gated_delta_scan_backward(d["q"], d["k"], d["v"], d["beta"], d["g"], d["d_out"], Cc,
+                                      gate_is_log=True, flags=flags, use_saved=True)
 
-        def step():
-            for t in range(tps):
-                i = t % 16
-                ops.gated_delta_decode_step(d["state"], d["q"][i], d["k"][i], d["v"][i], d["beta"][i], d["g"][i],
-                                            gate_is_log=True, out=out)
+    nchunks = B * H * ((T + Cc - 1) // Cc)
+    return dict(step=step, units=units, metric="gdn_fwd_bwd_tokens_per_s", unit="tokens/s", dtype="bf16",
+                alg_bytes=units * H * GDN_BYTES_PER_TOKEN_HEAD, alg_flops=units * H * GDN_FLOPS_PER_TOKEN_HEAD,
+                traffic=lambda kernels: traffic_from_table(GDN_NCU_TRAFFIC_MB, GDN_NCU_TRAFFIC_UNITS, nchunks, kernels),
+                traffic_note="per-kernel ncu byte capture (dram bytes read + written) of a full-size step, scaled by the "
+                             "number of (batch, head, chunk) units; null when the step's kernel list differs from the capture's",
+                cfg=gdn_train_cfg(w, cx.world), host=host, dev_tensors=d, w=w, flags=flags)
 
-        cfg = {"workload": "gdn_decode", **w, "io": "bf16", "state": "fp32 268 MB (exceeds L2)",
-               "inputs": "ring of 16 pre-generated token inputs"}
-    elif args.workload == "gdn_block":
-        w = dict(WORKLOADS["gdn_block"])
-        if args.batch > 0:
-            w["B"] = args.batch
-        B, T, H, K, V = w["B"], w["T"], w["H"], w["Dk"], w["Dv"]
-        g = torch.Generator().manual_seed(4000 + rank)
-        rn = lambda *shape: torch.randn(*shape, generator=g)
-        io = torch.bfloat16
-        d = dict(qp=rn(B, T, H * K).to(io), kp=rn(B, T, H * K).to(io), vp=rn(B, T, H * V).to(io),
-                 cq=0.4 * rn(4, H * K), ck=0.4 * rn(4, H * K), cv=0.4 * rn(4, H * V), a=rn(B, T, H), b=rn(B, T, H),
-                 al=0.5 * rn(H), bias=0.3 * rn(H), o=rn(B, T, H, V).to(io), z=rn(B, T, H * V).to(io), wn=1 + 0.2 * rn(V),
-                 dq=rn(B, T, H, K).to(io), dk=rn(B, T, H, K).to(io), dv=rn(B, T, H, V).to(io), db=rn(B, T, H),
-                 dg=rn(B, T, H), dy=rn(B, T, H * V).to(io))
-        d = {k: v.to(dev) for k, v in d.items()}
-        units = B * T
-        metric, unit, dtype = "gdn_block_stages_fwd_bwd_tokens_per_s", "tokens/s", "f32"
-        alg_bytes = units * H * GDN_BLOCK_BYTES_PER_TOKEN_HEAD
-        alg_flops = 0.0
-        bound = "hbm"
-        traffic, traffic_note = None, "not captured"
-        pre = [d[k] for k in ("qp", "kp", "vp", "cq", "ck", "cv", "a", "b", "al", "bias")]
 
-        def step():
-            ops.gdn_block_pre(*pre, H, K, V, gate_is_log=True)
-            ops.gdn_block_post(d["o"], d["z"], d["wn"])
-            ops.gdn_block_post_backward(d["o"], d["z"], d["wn"], d["dy"])
-            ops.gdn_block_pre_backward(*pre, H, K, V, d["dq"], d["dk"], d["dv"], d["db"], d["dg"], gate_is_log=True)
+def build_gdn_decode(cx, batch):
+    w = dict(WORKLOADS["gdn_decode"])
+    if batch > 0:
+        w["N"] = batch
+    N, H, K, V, tps = w["N"], w["H"], w["Dk"], w["Dv"], w["tokens_per_step"]
+    a = cx.inputs.gdn_decode_inputs(N, H, K, V, 16, seed=2 + cx.rank, io_dtype=torch.bfloat16)
+    d = {k: v.to(cx.dev) for k, v in a.items()}
+    out = torch.empty(N, H, V, dtype=torch.bfloat16, device=cx.dev)
+    units = N * tps
+    per_tok_bytes = 2 * K * V * 4 * H + (2 * K + 2 * V) * 2 * H + 8 * H
+    ops = cx.ops
 
-        cfg = {"workload": "gdn_block", **w, "io": "bf16", "what": "conv+SiLU+L2-norm/gate/beta and norm x gate, fwd+bwd"}
-    elif args.workload == "mamba3_block":
-        w = dict(WORKLOADS["mamba3_block"])
-        if args.batch > 0:
-            w["B"] = args.batch
-        B, T, D, N, G, K = w["B"], w["T"], w["D"], w["N"], w["G"], w["K"]
-        g = torch.Generator().manual_seed(5000 + rank)
-        rn = lambda *shape: torch.randn(*shape, generator=g)
-        io = torch.bfloat16
-        d = dict(x=rn(B, T, D).to(io), cw=0.4 * rn(D, K), dyc=rn(B, T, D).to(io),
-                 bp=rn(B, T, G * N).to(io), cp=rn(B, T, G * N).to(io), bs=1 + 0.2 * rn(N), cs=1 + 0.2 * rn(N),
-                 bb=0.3 * rn(G * N), cb=0.3 * rn(G * N), db=rn(B, T, G, N).to(io), dc=rn(B, T, G, N).to(io),
-                 y=rn(B, T, D).to(io), z=rn(B, T, D).to(io), pn=1 + 0.2 * rn(D), dout=rn(B, T, D).to(io))
-        d = {k: v.to(dev) for k, v in d.items()}
-        units = B * T
-        metric, unit, dtype = "mamba3_block_stages_fwd_bwd_tokens_per_s", "tokens/s", "f32"
-        alg_bytes = units * M3_BLOCK_BYTES_PER_TOKEN(D, G * N)
-        alg_flops = 0.0
-        bound = "hbm"
-        traffic, traffic_note = None, "not captured"
+    def step():
+        for t in range(tps):
+            i = t % 16
+            ops.gated_delta_decode_step(d["state"], d["q"][i], d["k"][i], d["v"][i], d["beta"][i], d["g"][i],
+                                        gate_is_log=True, out=out)
 
-        def step():
-            ops.mamba3_block_conv(d["x"], d["cw"])
-            ops.mamba3_block_bc(d["bp"], d["cp"], d["bs"], d["cs"], d["bb"], d["cb"], G, N)
-            ops.mamba3_block_post(d["y"], d["z"], d["pn"])
-            ops.mamba3_block_post_backward(d["y"], d["z"], d["pn"], d["dout"])
-            ops.mamba3_block_bc_backward(d["bp"], d["cp"], d["bs"], d["cs"], d["db"], d["dc"], G, N)
-            ops.mamba3_block_conv_backward(d["x"], d["cw"], d["dyc"])
+    return dict(step=step, units=units, metric="gdn_decode_tokens_per_s", unit="tokens/s", dtype="f32",
+                alg_bytes=units * per_tok_bytes, alg_flops=units * H * 7 * K * V,
+                traffic=lambda kernels: traffic_from_table(DECODE_NCU_TRAFFIC_MB, DECODE_NCU_TRAFFIC_UNITS, N * H, kernels,
+                                                           launches_per_step=tps) if (K, V) == (128, 128) else None,
+                traffic_note="ncu byte capture of one launch at config 2, scaled by the (sequence, head) tiles and the "
+                             "launches per step",
+                cfg={"workload": "gdn_decode", **w, "io": "bf16", "state": "fp32 268 MB at N=256 (exceeds L2)",
+                     "inputs": "ring of 16 pre-generated token inputs"})
 
-        cfg = {"workload": "mamba3_block", **w, "io": "bf16", "what": "depthwise conv, B/C norm + bias, post-norm x gate, fwd+bwd"}
-    else:
-        w = dict(WORKLOADS["mamba3_train"])
-        if args.batch > 0:
-            w["B"] = args.batch
-        B, T, NH, P, N, G = w["B"], w["T"], w["nheads"], w["headdim"], w["N"], w["G"]
-        parts = [inputs.mamba3_inputs(1, T, NH, P, N, G=G, seed=3000 * (rank + 1) + b, io_dtype=torch.bfloat16)
-                 for b in range(B)]
-        keys = ("x", "dt_raw", "lambda_raw", "theta", "b", "c", "dy")
-        d = {k: torch.cat([p[k] for p in parts]).to(dev) for k in keys}
-        d["a_log"] = parts[0]["a_log"].to(dev)
-        units = B * T
-        metric, unit, dtype = "mamba3_fwd_bwd_tokens_per_s", "tokens/s", "bf16"
-        alg_bytes = units * M3_BYTES_PER_TOKEN
-        alg_flops = units * M3_FLOPS_PER_TOKEN
-        bound = "hbm"
-        traffic = B * NH * ((T + 63) // 64) * M3_NCU_TRAFFIC_PER_CHUNK if (P, N) == (64, 128) else None
-        traffic_note = "one-pass ncu capture (dram bytes read + written) of a full-size step, per (batch, head, chunk) unit x units"
-        margs = [d[k] for k in ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")]
 
-        def step():
-            ops.mamba3_selective_scan(*margs, nheads=NH, save_for_backward=True)
-            ops.mamba3_selective_scan_backward(*margs, d["dy"], nheads=NH, use_saved=True)
+def build_gdn_block(cx, batch):
+    w = dict(WORKLOADS["gdn_block"])
+    if batch > 0:
+        w["B"] = batch
+    B, T, H, K, V = w["B"], w["T"], w["H"], w["Dk"], w["Dv"]
+    g = torch.Generator().manual_seed(4000 + cx.rank)
+    rn = lambda *shape: torch.randn(*shape, generator=g)
+    io = torch.bfloat16
+    d = dict(qp=rn(B, T, H * K).to(io), kp=rn(B, T, H * K).to(io), vp=rn(B, T, H * V).to(io),
+             cq=0.4 * rn(4, H * K), ck=0.4 * rn(4, H * K), cv=0.4 * rn(4, H * V), a=rn(B, T, H), b=rn(B, T, H),
+             al=0.5 * rn(H), bias=0.3 * rn(H), o=rn(B, T, H, V).to(io), z=rn(B, T, H * V).to(io), wn=1 + 0.2 * rn(V),
+             dq=rn(B, T, H, K).to(io), dk=rn(B, T, H, K).to(io), dv=rn(B, T, H, V).to(io), db=rn(B, T, H),
+             dg=rn(B, T, H), dy=rn(B, T, H * V).to(io))
+    d = {k: v.to(cx.dev) for k, v in d.items()}
+    units = B * T
+    pre = [d[k] for k in ("qp", "kp", "vp", "cq", "ck", "cv", "a", "b", "al", "bias")]
+    ops = cx.ops
 
-        cfg = {"workload": "mamba3_train", **w, "io": "bf16", "layout": "head-broadcast dt/lambda/theta/a_log"}
+    def step():
+        ops.gdn_block_pre(*pre, H, K, V, gate_is_log=True)
+        ops.gdn_block_post(d["o"], d["z"], d["wn"])
+        ops.gdn_block_post_backward(d["o"], d["z"], d["wn"], d["dy"])
+        ops.gdn_block_pre_backward(*pre, H, K, V, d["dq"], d["dk"], d["dv"], d["db"], d["dg"], gate_is_log=True)
 
-    # ---- warm-up, then the timed region --------------------------------------
-    for _ in range(args.warmup):
+    return dict(step=step, units=units, metric="gdn_block_stages_fwd_bwd_tokens_per_s", unit="tokens/s", dtype="f32",
+                alg_bytes=units * H * GDN_BLOCK_BYTES_PER_TOKEN_HEAD, alg_flops=0.0, traffic=lambda kernels: None,
+                traffic_note="not captured",
+                cfg={"workload": "gdn_block", **w, "io": "bf16",
+                     "what": "conv+SiLU+L2-norm/gate/beta and norm x gate, fwd+bwd"})
+
+
+def build_mamba3_block(cx, batch):
+    w = dict(WORKLOADS["mamba3_block"])
+    if batch > 0:
+        w["B"] = batch
+    B, T, D, N, G, K = w["B"], w["T"], w["D"], w["N"], w["G"], w["K"]
+    g = torch.Generator().manual_seed(5000 + cx.rank)
+    rn = lambda *shape: torch.randn(*shape, generator=g)
+    io = torch.bfloat16
+    d = dict(x=rn(B, T, D).to(io), cw=0.4 * rn(D, K), dyc=rn(B, T, D).to(io),
+             bp=rn(B, T, G * N).to(io), cp=rn(B, T, G * N).to(io), bs=1 + 0.2 * rn(N), cs=1 + 0.2 * rn(N),
+             bb=0.3 * rn(G * N), cb=0.3 * rn(G * N), db=rn(B, T, G, N).to(io), dc=rn(B, T, G, N).to(io),
+             y=rn(B, T, D).to(io), z=rn(B, T, D).to(io), pn=1 + 0.2 * rn(D), dout=rn(B, T, D).to(io))
+    d = {k: v.to(cx.dev) for k, v in d.items()}
+    units = B * T
+    ops = cx.ops
+
+    def step():
+        ops.mamba3_block_conv(d["x"], d["cw"])
+        ops.mamba3_block_bc(d["bp"], d["cp"], d["bs"], d["cs"], d["bb"], d["cb"], G, N)
+        ops.mamba3_block_post(d["y"], d["z"], d["pn"])
+        ops.mamba3_block_post_backward(d["y"], d["z"], d["pn"], d["dout"])
+        ops.mamba3_block_bc_backward(d["bp"], d["cp"], d["bs"], d["cs"], d["db"], d["dc"], G, N)
+        ops.mamba3_block_conv_backward(d["x"], d["cw"], d["dyc"])
+
+    return dict(step=step, units=units, metric="mamba3_block_stages_fwd_bwd_tokens_per_s", unit="tokens/s", dtype="f32",
+                alg_bytes=units * M3_BLOCK_BYTES_PER_TOKEN(D, G * N), alg_flops=0.0, traffic=lambda kernels: None,
+                traffic_note="not captured",
+                cfg={"workload": "mamba3_block", **w, "io": "bf16",
+                     "what": "depthwise conv, B/C norm + bias, post-norm x gate, fwd+bwd"})
+
+
+def build_mamba3_train(cx, batch):
+    w = dict(WORKLOADS["mamba3_train"])
+    if batch > 0:
+        w["B"] = batch
+    B, T, NH, P, N, G = w["B"], w["T"], w["nheads"], w["headdim"], w["N"], w["G"]
+    parts = [cx.inputs.mamba3_inputs(1, T, NH, P, N, G=G, seed=3000 * (cx.rank + 1) + b, io_dtype=torch.bfloat16)
+             for b in range(B)]
+    keys = ("x", "dt_raw", "lambda_raw", "theta", "b", "c", "dy")
+    d = {k: torch.cat([p[k] for p in parts]).to(cx.dev) for k in keys}
+    d["a_log"] = parts[0]["a_log"].to(cx.dev)
+    units = B * T
+    margs = [d[k] for k in ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")]
+    ops = cx.ops
+
+    def step():
+        ops.mamba3_selective_scan(*margs, nheads=NH, save_for_backward=True)
+        ops.mamba3_selective_scan_backward(*margs, d["dy"], nheads=NH, use_saved=True)
+
+    nchunks = B * NH * ((T + 63) // 64)
+    return dict(step=step, units=units, metric="mamba3_fwd_bwd_tokens_per_s", unit="tokens/s", dtype="bf16",
+                alg_bytes=units * M3_BYTES_PER_TOKEN, alg_flops=units * M3_FLOPS_PER_TOKEN,
+                traffic=lambda kernels: traffic_from_table(M3_NCU_TRAFFIC_MB, M3_NCU_TRAFFIC_UNITS, nchunks, kernels)
+                if (P, N) == (64, 128) else None,
+                traffic_note="per-kernel ncu byte capture (dram bytes read + written) of a full-size step, scaled by the "
+                             "number of (batch, head, chunk) units; null when the step's kernel list differs from the capture's",
+                cfg={"workload": "mamba3_train", **w, "io": "bf16", "layout": "head-broadcast dt/lambda/theta/a_log"})
+
+
+BUILDERS = {"gdn_train": build_gdn_train, "gdn_decode": build_gdn_decode, "gdn_block": build_gdn_block,
+            "mamba3_block": build_mamba3_block, "mamba3_train": build_mamba3_train}
+
+
+def time_workload(cx, wl, steps, warmup):
+    """W warm-up steps, then exactly K steps between two barriers; device time by CUDA events (max over ranks), every
+    kernel of the library timed by its own event pair on the launching stream, clocks sampled during the region."""
+    lib, step = cx.lib, wl["step"]
+    for _ in range(warmup):
         step()
-    barrier()
-    sampler = ClockSampler(local)
+    cx.barrier()
+    sampler = ClockSampler(cx.local)
     sampler.start()
     time.sleep(0.25)
     lib.mxb_trace_enable(1)
     n0 = lib.mxb_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    cx.barrier()
     t_wall0 = time.time()
     ev0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     ev1.record()
-    barrier()
+    cx.barrier()
     t_wall1 = time.time()
     ms = ev0.elapsed_time(ev1)
     launches = int(lib.mxb_launch_count() - n0)
@@ -361,7 +388,7 @@ def main():
     lib.mxb_trace_summary(buf, len(buf))
     lib.mxb_trace_enable(0)
     clocks = sampler.stop(t_wall0, t_wall1)
-    ms = sharding.max_over_ranks(ms, dev)
+    ms = cx.sharding.max_over_ranks(ms, cx.dev)
     kernels = {}
     for line in buf.value.decode().splitlines():
         name, cnt, tot = line.split()
@@ -371,56 +398,150 @@ def main():
         k["share"] = k["total_ms"] / ksum
         k["avg_ms"] = k["total_ms"] / max(k["launches"], 1)
     top = max(kernels, key=lambda n: kernels[n]["total_ms"]) if kernels else None
-
-    ms_step = ms / args.steps
-    value = sharding.whole_job_rate(units, world, ms_step * 1e-3)
+    ms_step = ms / steps
+    value = cx.sharding.whole_job_rate(wl["units"], cx.world, ms_step * 1e-3)
     # roofline of the step, taken as one launch: algorithmic bytes / summed kernel time
-    kern_ms_step = ksum / args.steps
-    achieved = alg_bytes / (kern_ms_step * 1e-3) / 1e9
-    roofline = {"bound": bound, "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                "frac": achieved / pk["hbm"], "traffic": traffic, "traffic_note": traffic_note, "peak_source": pk["src"],
+    kern_ms_step = ksum / steps
+    achieved = wl["alg_bytes"] / (kern_ms_step * 1e-3) / 1e9
+    pk = cx.pk
+    tfl = wl["alg_flops"] / (kern_ms_step * 1e-3) / 1e12
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s", "frac": achieved / pk["hbm"],
+                "traffic": wl["traffic"](kernels), "traffic_note": wl["traffic_note"], "peak_source": pk["src"],
                 "scope": "all kernels of one step (algorithmic bytes of the step / summed kernel time)",
-                "top_kernel": top, "kernels": kernels,
-                "tensor_tflops": alg_flops / (kern_ms_step * 1e-3) / 1e12,
-                "tensor_frac_of_sustained": alg_flops / (kern_ms_step * 1e-3) / 1e12 / pk["tf_sus"]}
+                "top_kernel": top, "kernels": kernels, "tensor_tflops": tfl,
+                "tensor_frac_of_sustained": tfl / pk["tf_sus"]}
+    return dict(ms_step=ms_step, value=value, launches=launches, clocks=clocks, roofline=roofline)
 
-    # ---- end to end through the host-buffer C ABI (gdn_train only) -----------
+
+def copy_floor(cx, host, res, steps):
+    """The host<->device traffic of one end-to-end step and nothing else: every input tensor uploaded by one
+    cudaMemcpyAsync each on one stream while every result tensor is downloaded on a second stream (pinned host
+    memory, no kernels), all ranks at once between the same barriers.  The end-to-end call cannot be faster."""
+    up, down = torch.cuda.Stream(cx.dev), torch.cuda.Stream(cx.dev)
+    names_in = ("q", "k", "v", "beta", "g", "d_out")
+    dev_in = {k: torch.empty_like(host[k], device=cx.dev) for k in names_in}
+    dev_out = {k: torch.empty_like(v, device=cx.dev) for k, v in res.items()}
+
+    def once():
+        with torch.cuda.stream(up):
+            for k in names_in:
+                dev_in[k].copy_(host[k], non_blocking=True)
+        with torch.cuda.stream(down):
+            for k, v in res.items():
+                v.copy_(dev_out[k], non_blocking=True)
+        up.synchronize()
+        down.synchronize()
+
+    once()
+    cx.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        once()
+    cx.barrier()
+    dt = (time.perf_counter() - t0) / steps
+    return cx.sharding.max_over_ranks(dt, cx.dev) * 1e3
+
+
+def end_to_end_gdn(cx, wl):
+    """The same step through the host-buffer C ABI (mxb_host_gdn): pinned host tensors in and out, blocking."""
+    lib, mx, host, w = cx.lib, cx.mx, wl["host"], wl["w"]
+    B, T, H, K, V, Cc = w["B"], w["T"], w["H"], w["Dk"], w["Dv"], w["chunk"]
+    ctx = C.c_void_p()
+    desc = mx.GdnDesc(B, T, H, K, V, Cc, mx.MXB_BF16, 1, wl["flags"])
+    need = lib.mxb_gdn_bwd_workspace_bytes(C.byref(desc)) + 12 * B * T * H * max(K, V) * 2 + (64 << 20)
+    wl["dev_tensors"].clear()
+    torch.cuda.empty_cache()
+    st = lib.mxb_host_ctx_create(cx.local, need, C.byref(ctx))
+    if st != 0:
+        return {"value": None, "unit": wl["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "error": f"mxb_host_ctx_create status {st}"}
+    res = {n: torch.empty_like(host[s]).pin_memory() for n, s in
+           (("out", "v"), ("dq", "q"), ("dk", "k"), ("dv", "v"), ("dbeta", "beta"), ("dgate", "g"))}
+    p = lambda t: C.c_void_p(t.data_ptr())
+
+    def host_step():
+        s = lib.mxb_host_gdn(ctx, C.byref(desc), p(host["q"]), p(host["k"]), p(host["v"]), p(host["beta"]),
+                             p(host["g"]), p(res["out"]), p(host["d_out"]), p(res["dq"]), p(res["dk"]),
+                             p(res["dv"]), p(res["dbeta"]), p(res["dgate"]))
+        if s != 0:
+            raise RuntimeError(f"mxb_host_gdn status {s}")
+
+    host_step()
+    nst = max(2, min(cx.args.steps, 5))
+    cx.barrier()
+    t0 = time.perf_counter()
+    for _ in range(nst):
+        host_step()  # blocking: H2D + kernels + D2H + stream sync
+    cx.barrier()
+    dt = (time.perf_counter() - t0) / nst
+    dt = cx.sharding.max_over_ranks(dt, cx.dev)
+    lib.mxb_host_ctx_destroy(ctx)
+    floor_ms = copy_floor(cx, host, res, nst)
+    h2d = sum(host[k].numel() * host[k].element_size() for k in ("q", "k", "v", "beta", "g", "d_out"))
+    d2h = sum(t.numel() * t.element_size() for t in res.values())
+    return {"value": cx.world * wl["units"] / dt, "unit": wl["unit"], "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "ms_per_step": dt * 1e3, "copy_floor_ms": floor_ms, "frac_of_copy_floor": floor_ms / (dt * 1e3),
+            "copy_floor_note": "the same bytes by bare cudaMemcpyAsync on two streams, no kernels, all ranks at once",
+            "api": "mxb_host_gdn (pinned host buffers, blocking)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gdn_train", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the short gdn_decode and mamba3_train legs")
+    ap.add_argument("--fp32-path", action="store_true", help="force the CUDA-core fp32 kernels")
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the per-GPU batch (sequences) - small cases for profiler captures only")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operators have no CPU fallback")
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        # NCCL prints its version banner on stdout at VERSION level; stdout carries only the JSON line
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cx = Ctx(args)
+
+    wl = BUILDERS[args.workload](cx, args.batch)
+    main_res = time_workload(cx, wl, args.steps, args.warmup)
+
+    # ---- short legs of the other two primitives the headline metric names (default workload only) ----
+    extra = None
+    if args.workload == "gdn_train" and not args.no_extra and args.batch == 0:
+        extra = {}
+        for name, nsteps in (("gdn_decode", 3), ("mamba3_train", 5)):
+            w2 = BUILDERS[name](cx, 0)
+            r = time_workload(cx, w2, nsteps, 3)
+            rf = r["roofline"]
+            extra[name] = {"metric": w2["metric"], "value": r["value"], "unit": w2["unit"], "ms_per_step": r["ms_step"],
+                           "steps": nsteps, "warmup": 3, "config": w2["cfg"], "clocks": r["clocks"],
+                           "gpu_launches": r["launches"],
+                           "roofline": {k: rf[k] for k in ("bound", "achieved", "peak", "unit", "frac", "traffic",
+                                                           "top_kernel", "peak_source")},
+                           "kernels": {n: {"launches": k["launches"], "avg_ms": k["avg_ms"], "share": k["share"]}
+                                       for n, k in rf["kernels"].items()}}
+            if name == "gdn_decode":  # one launch per token: the per-launch figure is the decode roofline
+                tps = w2["cfg"]["tokens_per_step"]
+                extra[name]["hbm_gbs_per_launch"] = w2["alg_bytes"] / tps / (rf["kernels"][rf["top_kernel"]]["avg_ms"] * 1e-3) / 1e9
+            del w2
+            torch.cuda.empty_cache()
+
+    e2e = None
     if args.workload == "gdn_train" and not args.no_e2e:
-        ctx = C.c_void_p()
-        desc = mixlab_b200.GdnDesc(B, T, H, K, V, Cc, mixlab_b200.MXB_BF16, 1, flags)
-        need = lib.mxb_gdn_bwd_workspace_bytes(C.byref(desc)) + 12 * B * T * H * max(K, V) * 2 + (64 << 20)
-        del d
-        torch.cuda.empty_cache()
-        st = lib.mxb_host_ctx_create(local, need, C.byref(ctx))
-        if st == 0:
-            res = {n: torch.empty_like(host[s]).pin_memory() for n, s in
-                   (("out", "v"), ("dq", "q"), ("dk", "k"), ("dv", "v"), ("dbeta", "beta"), ("dgate", "g"))}
-            p = lambda t: C.c_void_p(t.data_ptr())
-
-            def host_step():
-                s = lib.mxb_host_gdn(ctx, C.byref(desc), p(host["q"]), p(host["k"]), p(host["v"]), p(host["beta"]),
-                                     p(host["g"]), p(res["out"]), p(host["d_out"]), p(res["dq"]), p(res["dk"]),
-                                     p(res["dv"]), p(res["dbeta"]), p(res["dgate"]))
-                if s != 0:
-                    raise RuntimeError(f"mxb_host_gdn status {s}")
-
-            host_step()
-            nst = max(2, min(args.steps, 5))
-            barrier()
-            t0 = time.perf_counter()
-            for _ in range(nst):
-                host_step()  # blocking: H2D + kernels + D2H + stream sync
-            barrier()
-            dt = (time.perf_counter() - t0) / nst
-            dt = sharding.max_over_ranks(dt, dev)
-            lib.mxb_host_ctx_destroy(ctx)
-            h2d = sum(host[k].numel() * host[k].element_size() for k in ("q", "k", "v", "beta", "g", "d_out"))
-            d2h = sum(t.numel() * t.element_size() for t in res.values())
-            e2e = {"value": world * units / dt, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                   "ms_per_step": dt * 1e3, "api": "mxb_host_gdn (pinned host buffers, blocking)"}
-        else:
-            e2e = {"value": None, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                   "error": f"mxb_host_ctx_create status {st}"}
+        e2e = end_to_end_gdn(cx, wl)
 
     cpu = None
     if rank == 0 and world == 1 and args.workload == "gdn_train" and not args.no_cpu_baseline:
@@ -431,14 +552,18 @@ def main():
                          "oracle.gdn.scan_chunked + torch autograd"}
 
     if rank == 0:
-        print(json.dumps({
-            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": dtype, "data": "synthetic", "config": cfg,
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu,
-        }))
+        line = {
+            "metric": wl["metric"], "value": main_res["value"], "unit": wl["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": main_res["ms_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic", "config": wl["cfg"],
+            "clocks": main_res["clocks"], "e2e": e2e, "gpu_launches": main_res["launches"],
+            "roofline": main_res["roofline"], "cpu_baseline": cpu,
+        }
+        if extra is not None:
+            line["extra"] = extra
+        print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        cx.dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -74,7 +74,16 @@ MXB_API size_t mxb_trace_summary(char* buf, size_t capacity);
 /* ------------------------------------------------------------------------
  * Gated delta rule.  IntParams of OP_GATED_DELTA_SCAN are [B,T,H,Dk,Dv,chunk]
  * (arch/ir.go:600-602); chunk <= 1 selects the token-by-token recurrence
- * (gpu/ir.cpp:4648-4652), chunk in [2,64] the chunked WY/UT form.
+ * (gpu/ir.cpp:4648-4652), chunk >= 2 the chunked WY/UT form.  The result does not
+ * depend on the chunk size; sizes above 64 (which the reference accepts,
+ * arch/blocks_gated_deltanet.go:11-17) are computed with chunks of 64.
+ *
+ * Numeric guards: the chunked form floors the gate at 1e-30 and clamps every decay
+ * exponent to [-80, 0] (gpu/ir.cpp:35-37, :2396, :893-905); the recurrence applies
+ * neither (gpu/ir.cpp:2334).  mxb_gdn_fwd follows the reference in both forms.
+ * mxb_gdn_bwd always differentiates the chunked form (chunks of 64), also for
+ * chunk <= 1: the gradient with respect to a gate below the floor is then zero,
+ * where differentiating the unguarded recurrence would give a (tiny) nonzero value.
  * ---------------------------------------------------------------------- */
 typedef struct {
   int32_t B, T, H, Dk, Dv, chunk;
@@ -129,11 +138,17 @@ MXB_API mxb_status mxb_gdn_bwd(const mxb_gdn_desc* d, const void* q, const void*
  * is not acceptable.  No counterpart in the reference.  The scratch is a fixed array
  * of MXB_GDN_STATIC_SCRATCH_BYTES inside the library (present once per GPU while the
  * library is loaded); problems whose workspace (mxb_gdn_fwd_workspace_bytes with
- * MXB_GDN_FORCE_FP32_PATH) is larger return MXB_ERR_WORKSPACE.  Always runs the
- * full-fp32 CUDA-core kernels; same arguments and results as mxb_gdn_fwd with that
- * flag.  Calls no cudaMalloc/cudaFree.  All calls on a GPU share the one array: do
- * not let two of them overlap on the device.  The first call on each device looks up
- * the array's address; make that call before any stream capture begins. */
+ * flags = MXB_GDN_FORCE_FP32_PATH) is larger return MXB_ERR_WORKSPACE before anything
+ * is launched.  Always runs the full-fp32 CUDA-core kernels; same arguments and
+ * results as mxb_gdn_fwd with that flag.  desc.flags is ignored: in particular
+ * MXB_GDN_SAVE_FOR_BWD saves nothing (the array is private to this entry point).
+ * Calls no cudaMalloc/cudaFree.  All calls on a GPU share the one array: do not let
+ * two of them overlap on the device.  The first call on each device looks up the
+ * array's address; make that call before any stream capture begins.  The array's
+ * memory is reserved when the CUDA runtime loads this library's device code on that
+ * GPU (at the latest during that first call), so on a device without 16 MiB free the
+ * first call returns MXB_ERR_CUDA.  The stream must belong to the device that is
+ * current during the call, and the cached address does not survive cudaDeviceReset. */
 #define MXB_GDN_STATIC_SCRATCH_BYTES (16u << 20)
 MXB_API size_t mxb_gdn_static_scratch_bytes(void);
 MXB_API mxb_status mxb_gdn_fwd_static_scratch(const mxb_gdn_desc* d, const void* q, const void* k,
@@ -219,8 +234,9 @@ enum {
   MXB_MAMBA3_SAVE_FOR_BWD = 4,     /* forward: mxb_mamba3_fwd_workspace_bytes returns the backward size and
                                       the chunk states and per-token scalars stay in the workspace */
   MXB_MAMBA3_NO_TMA = 16,          /* chunked kernels: stage the operand tiles with cp.async instead of
-                                      the copy engine (the path taken anyway when a tensor map cannot be
-                                      made, e.g. a base pointer that is not 16-byte aligned) */
+                                      the copy engine (the path taken anyway when the driver offers no
+                                      tensor-map entry point).  Both stagings need x, b, c, y, dy, dx, db,
+                                      dc 16-byte aligned: other pointers return MXB_ERR_ALIGNMENT */
   MXB_MAMBA3_BWD_USE_SAVED = 8     /* backward: the workspace is the one a forward call with
                                       MXB_MAMBA3_SAVE_FOR_BWD just filled for the same inputs; the forward
                                       recompute is skipped.  Honoured by the chunked tensor-core kernels;
@@ -296,6 +312,14 @@ MXB_API mxb_status mxb_mamba3_block_post_bwd(const mxb_mamba3_desc* d, float eps
 MXB_API mxb_status mxb_selftest_umma(const void* a_img, uint32_t a_bytes, const void* b_img,
                              uint32_t b_bytes, const uint32_t* fields, float* d_out,
                              int* status, void* stream);
+
+/* Runs the give-up path of the bounded device-side waits on purpose, without a
+ * fault: a small kernel polls a barrier that nothing arrives on poll_limit times
+ * (1 .. 65536), leaves normally and writes code 9 into the status word that leads
+ * `workspace` (>= 256 bytes, cleared first), where mxb_gdn_device_status reads it
+ * like the status of a production kernel whose copy or MMA never completed. */
+MXB_API mxb_status mxb_selftest_wait_timeout(void* workspace, size_t workspace_bytes,
+                                     uint32_t poll_limit, void* stream);
 
 /* ------------------------------------------------------------------------
  * Host-buffer evaluation, the shape of the reference bridge's

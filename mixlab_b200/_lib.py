@@ -70,6 +70,7 @@ EXPORTS = {
     "mxb_mamba3_block_post_fwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 5),
     "mxb_mamba3_block_post_bwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 8 + [C.c_size_t, _P]),
     "mxb_selftest_umma": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint32, _P, _P, _P, _P]),
+    "mxb_selftest_wait_timeout": (C.c_int32, [_P, C.c_size_t, C.c_uint32, _P]),
     "mxb_host_ctx_create": (C.c_int32, [C.c_int, C.c_size_t, C.POINTER(_P)]),
     "mxb_host_ctx_destroy": (None, [_P]),
     "mxb_host_gdn": (C.c_int32, [_P, C.POINTER(GdnDesc)] + [_P] * 12),

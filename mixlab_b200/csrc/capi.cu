@@ -79,6 +79,7 @@ mxb_status gdn_tc_bwd(const mxb_gdn_desc*, const void*, const void*, const void*
                       const float*, const float*, const void*, const float*, void*, void*, void*,
                       float*, float*, float*, void*, cudaStream_t);
 mxb_status umma_selftest(const void*, uint32_t, const void*, uint32_t, const uint32_t*, float*, int*, cudaStream_t);
+mxb_status wait_timeout_selftest(void*, uint32_t, cudaStream_t);
 bool gdn_block_supported(const mxb_gdn_desc*);
 size_t gdn_block_workspace_bytes(const mxb_gdn_desc*);
 mxb_status gdn_block_pre_fwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*, const float*,
@@ -203,7 +204,11 @@ mxb_status mxb_gdn_fwd(const mxb_gdn_desc* d, const void* q, const void* k, cons
   if (need > 0 && (!workspace || workspace_bytes < need)) return MXB_ERR_WORKSPACE;
   if (need > 0 && !aligned16(workspace)) return MXB_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (use_tc(d)) return gdn_tc_fwd(d, q, k, v, beta, gate, h0, out, hT, workspace, st);
+  if (use_tc(d)) {  // the tensor-core kernels move whole 16-byte units (TMA tiles, bulk copies, 128-bit loads)
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(h0) || !aligned16(hT))
+      return MXB_ERR_ALIGNMENT;
+    return gdn_tc_fwd(d, q, k, v, beta, gate, h0, out, hT, workspace, st);
+  }
   if (!gdn_simt_supported(d)) return MXB_ERR_UNSUPPORTED;
   return gdn_simt_fwd(d, q, k, v, beta, gate, h0, out, hT, workspace, st);
 }
@@ -220,8 +225,12 @@ mxb_status mxb_gdn_bwd(const mxb_gdn_desc* d, const void* q, const void* k, cons
   if (!workspace || workspace_bytes < need) return MXB_ERR_WORKSPACE;
   if (!aligned16(workspace)) return MXB_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (use_tc(d))
+  if (use_tc(d)) {
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_out) || !aligned16(dq) || !aligned16(dk) ||
+        !aligned16(dv) || !aligned16(h0) || !aligned16(d_hT) || !aligned16(dh0))
+      return MXB_ERR_ALIGNMENT;
     return gdn_tc_bwd(d, q, k, v, beta, gate, h0, d_out, d_hT, dq, dk, dv, dbeta, dgate, dh0, workspace, st);
+  }
   if (!gdn_simt_supported(d)) return MXB_ERR_UNSUPPORTED;
   return gdn_simt_bwd(d, q, k, v, beta, gate, h0, d_out, d_hT, dq, dk, dv, dbeta, dgate, dh0, workspace, st);
 }
@@ -358,6 +367,12 @@ mxb_status mxb_selftest_umma(const void* a_img, uint32_t a_bytes, const void* b_
                              const uint32_t* fields, float* d_out, int* status, void* stream) {
   if (!a_img || !b_img || !fields || !d_out || !status) return MXB_ERR_INVALID_ARGUMENT;
   return umma_selftest(a_img, a_bytes, b_img, b_bytes, fields, d_out, status, static_cast<cudaStream_t>(stream));
+}
+
+mxb_status mxb_selftest_wait_timeout(void* workspace, size_t workspace_bytes, uint32_t poll_limit, void* stream) {
+  if (!workspace || workspace_bytes < 256) return MXB_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return MXB_ERR_ALIGNMENT;
+  return wait_timeout_selftest(workspace, poll_limit, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------- Mamba-3 block stages
@@ -513,9 +528,9 @@ void mxb_host_ctx_destroy(mxb_host_ctx* c) {
 
 // The batch is cut into single sequences; sequence b+1 is uploaded and sequence b-1 downloaded
 // while sequence b computes (two device slots per tensor, three streams, events between them).
-mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, const void* k,
-                        const void* v, const float* beta, const float* gate, void* out,
-                        const void* d_out, void* dq, void* dk, void* dv, float* dbeta, float* dgate) {
+static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, const void* k,
+                                    const void* v, const float* beta, const float* gate, void* out,
+                                    const void* d_out, void* dq, void* dk, void* dv, float* dbeta, float* dgate) {
   if (!c) return MXB_ERR_INVALID_ARGUMENT;
   mxb_status s = check_gdn_desc(d, true);
   if (s != MXB_OK) return s;
@@ -535,9 +550,8 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
   mxb_gdn_desc d1 = *d;
   d1.B = per;
   mxb_gdn_desc df = d1, db = d1;
-  // The slices' kernels stage their operands with per-thread copies: this call is bound by the two PCIe copy streams,
-  // and with the kernels fed by the tensor-copy engine (TMA / bulk copies) those streams ran slower (14.0 ms per call
-  // at B=8, T=4096, H=16, d=128 against 13.0 ms with per-thread staging, although the kernels alone are 20 % slower).
+  // The slices' kernels stage their operands with per-thread copies where they have such a variant: this call is
+  // bound by the two PCIe copy streams, which ran slower beside kernels fed by the tensor-copy engine.
   df.flags |= MXB_GDN_NO_TMA;
   db.flags |= MXB_GDN_NO_TMA;
   if (bwd) {  // keep the forward intermediates in the arena for the backward that follows
@@ -614,6 +628,23 @@ mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, c
   MXB_CUDA_TRY(cudaStreamSynchronize(c->stream));
   MXB_CUDA_TRY(cudaStreamSynchronize(c->stream2));
   return MXB_OK;
+}
+
+mxb_status mxb_host_gdn(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, const void* k,
+                        const void* v, const float* beta, const float* gate, void* out,
+                        const void* d_out, void* dq, void* dk, void* dv, float* dbeta, float* dgate) {
+  const mxb_status s = host_gdn_pipeline(c, d, q, k, v, beta, gate, out, d_out, dq, dk, dv, dbeta, dgate);
+  if (s != MXB_OK && c) {
+    // The call is blocking also when it fails: copies of earlier slices may still be reading or writing the
+    // caller's host buffers and the arena slots, so all four streams are drained (errors ignored) before returning.
+    const int keep = g_last_cuda_error;
+    cudaStreamSynchronize(c->s_h2d);
+    cudaStreamSynchronize(c->s_d2h);
+    cudaStreamSynchronize(c->stream);
+    cudaStreamSynchronize(c->stream2);
+    g_last_cuda_error = keep;
+  }
+  return s;
 }
 
 }  // extern "C"

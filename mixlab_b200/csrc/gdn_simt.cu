@@ -670,8 +670,11 @@ size_t gdn_simt_workspace_bytes(const mxb_gdn_desc* d, bool bwd) {
   return carve(p, nullptr, bwd);
 }
 
+// Any chunk size is accepted: the result does not depend on it, and sizes above 64 are computed
+// with chunks of 64 (make_params), as the reference allows larger scan_chunk_size overrides
+// (arch/blocks_gated_deltanet.go:11-17).  Dv up to 256 covers the reference default Dv = 2 Dk.
 bool gdn_simt_supported(const mxb_gdn_desc* d) {
-  return d->Dk >= 1 && d->Dv >= 1 && d->Dk <= 128 && d->Dv <= 128 && d->chunk <= 64;
+  return d->Dk >= 1 && d->Dv >= 1 && d->Dk <= 128 && d->Dv <= 256;
 }
 
 template <typename KernelT>

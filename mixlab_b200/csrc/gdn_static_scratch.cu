@@ -22,6 +22,11 @@
 // is obtained with cudaGetSymbolAddress the first time the entry point runs on a
 // device (with that device current) and cached per device.  That first call therefore
 // does a little one-off set-up work; make it before starting any stream capture.
+// The array's memory is reserved by the CUDA runtime when this library's device code is
+// loaded on a GPU, which with lazy loading is that same first call: on a device with
+// less than the array's size free it fails with MXB_ERR_CUDA.  The cached address
+// belongs to the context it was looked up in: it does not survive cudaDeviceReset, and
+// the caller's stream must belong to the device that is current during the call.
 #include <cstdio>
 #include <mutex>
 
@@ -79,6 +84,12 @@ mxb_status mxb_gdn_fwd_static_scratch(const mxb_gdn_desc* d, const void* q, cons
   if (d->io_dtype != MXB_F32 && d->io_dtype != MXB_BF16) return MXB_ERR_INVALID_ARGUMENT;
   if (d->gate_is_log != 0 && d->gate_is_log != 1) return MXB_ERR_INVALID_ARGUMENT;
   if (!gdn_simt_supported(d)) return MXB_ERR_UNSUPPORTED;
+  // Only the forward-sized scratch is checked against the array, so the flags that would make the kernels keep
+  // more in it (MXB_GDN_SAVE_FOR_BWD: the saved tiles could not be handed to a backward anyway, the array's
+  // address is private) or pick other kernels are dropped from a private copy of the descriptor.
+  mxb_gdn_desc own = *d;
+  own.flags = MXB_GDN_FORCE_FP32_PATH;
+  d = &own;
   const size_t need = gdn_simt_workspace_bytes(d, false);
   if (need > kStaticScratchBytes) {
     std::fprintf(stderr,

@@ -647,8 +647,9 @@ mxb_status gdn_simt_bwd(const mxb_gdn_desc*, const void*, const void*, const voi
                         const float*, const float*, const void*, const float*, void*, void*, void*,
                         float*, float*, float*, void*, cudaStream_t);
 
+// chunk > 64 is computed with chunks of 64 (the result does not depend on the chunk size).
 bool gdn_tc_supported(const mxb_gdn_desc* d) {
-  return d->io_dtype == MXB_BF16 && d->Dk == KD && d->Dv == KD && d->chunk == C;
+  return d->io_dtype == MXB_BF16 && d->Dk == KD && d->Dv == KD && d->chunk >= C;
 }
 
 static size_t carve_tc(TcP& p, void* ws, bool bwd) {

@@ -335,6 +335,7 @@ mxb_status mamba3_ssd_fwd(const mxb_mamba3_desc*, const void*, const float*, con
 mxb_status mamba3_ssd_bwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
                           const void*, const void*, const void*, void*, float*, float*, float*, float*, void*, void*,
                           void*, cudaStream_t);
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static bool use_ssd(const mxb_mamba3_desc* d) {
   return !(d->flags & (MXB_MAMBA3_CHANNEL_KERNELS | MXB_MAMBA3_RECURRENT_KERNELS)) && mamba3_ssd_supported(d);
 }
@@ -420,7 +421,10 @@ mxb_status mamba3_head_fwd(const mxb_mamba3_desc*, const void*, const float*, co
 mxb_status mamba3_fwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
                       const float* theta, const float* a_log, const void* b, const void* c, void* y, void* ws,
                       cudaStream_t st) {
-  if (use_ssd(d)) return mamba3_ssd_fwd(d, x, dt, lam, theta, a_log, b, c, y, ws, st);
+  if (use_ssd(d)) {  // the chunked kernels move whole 16-byte units, by TMA or by cp.async
+    if (!aligned16(x) || !aligned16(b) || !aligned16(c) || !aligned16(y) || !aligned16(ws)) return MXB_ERR_ALIGNMENT;
+    return mamba3_ssd_fwd(d, x, dt, lam, theta, a_log, b, c, y, ws, st);
+  }
   if (!(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_supported(d))
     return mamba3_head_fwd(d, x, dt, lam, theta, a_log, b, c, y, nullptr, nullptr, st);
   M3P p = make_m3(d);
@@ -432,8 +436,12 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
                       const float* theta, const float* a_log, const void* b, const void* c,
                       const void* dy, void* dx, float* ddt, float* dlam, float* dtheta, float* da_log,
                       void* db, void* dc, void* ws, cudaStream_t st) {
-  if (use_ssd(d))
+  if (use_ssd(d)) {
+    if (!aligned16(x) || !aligned16(b) || !aligned16(c) || !aligned16(dy) || !aligned16(dx) || !aligned16(db) ||
+        !aligned16(dc) || !aligned16(ws))
+      return MXB_ERR_ALIGNMENT;
     return mamba3_ssd_bwd(d, x, dt, lam, theta, a_log, b, c, dy, dx, ddt, dlam, dtheta, da_log, db, dc, ws, st);
+  }
   M3P p = make_m3(d);
   const bool f32 = d->io_dtype == MXB_F32;
   p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c;

@@ -1092,7 +1092,8 @@ static mxb_status ssd_smem(KernelT k, size_t bytes) {
 bool make_tma_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, int D);
 
 // Tensor maps for the token-indexed operands of the chunk kernels (dy only in the backward); false when one
-// cannot be made (a base that is not 16-byte aligned): the kernels then stage with cp.async.
+// cannot be made (no tensor-map entry point in the driver): the kernels then stage with cp.async.  Either way
+// the operand bases are 16-byte aligned: the dispatcher refuses other pointers.
 static bool ssd_chunk_maps(const SsdP& p, m3s::ChunkMaps& maps) {
   std::memset(&maps, 0, sizeof maps);
   if (p.no_tma) return false;
@@ -1103,7 +1104,7 @@ static bool ssd_chunk_maps(const SsdP& p, m3s::ChunkMaps& maps) {
 }
 
 // Sequential pass over the chunks (mode 0: forward states, mode 1: reverse state gradients); the copy engine
-// feeds it when tensor maps can be made for the operands (16-byte aligned bases), cp.async otherwise.
+// feeds it when tensor maps can be made for the operands, cp.async otherwise.
 static mxb_status ssd_state_pass(SsdP& p, int mode, cudaStream_t st) {
   m3s::PassMaps maps;
   std::memset(&maps, 0, sizeof maps);

@@ -91,4 +91,27 @@ mxb_status umma_selftest(const void* a_img, uint32_t a_bytes, const void* b_img,
   return check_launch("umma_selftest_kernel");
 }
 
+// A wait that runs out on purpose: one barrier that nothing ever arrives on, polled `limit` times by every
+// thread through the same bounded wait the production kernels use.  The kernel then leaves normally and
+// records code 9 in the status word, exactly like a production kernel whose copy or MMA never completed.
+__global__ void __launch_bounds__(64) wait_timeout_selftest_kernel(int* status, uint32_t limit) {
+  __shared__ uint64_t mbar;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&mbar, 1);
+    tc::mbar_fence_init();
+  }
+  __syncthreads();
+  const bool ok = tc::mbar_wait(&mbar, 0, limit);
+  if (!__syncthreads_and(ok) && threadIdx.x == 0) atomicExch(status, 9);
+}
+
+mxb_status wait_timeout_selftest(void* workspace, uint32_t limit, cudaStream_t st) {
+  if (limit == 0 || limit > (1u << 16)) return MXB_ERR_INVALID_ARGUMENT;  // keeps the polling short
+  cudaError_t e = cudaMemsetAsync(workspace, 0, 256, st);
+  if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
+  MXB_LAUNCH("wait_timeout_selftest_kernel", st,
+             (wait_timeout_selftest_kernel<<<1, 64, 0, st>>>(static_cast<int*>(workspace), limit)));
+  return check_launch("wait_timeout_selftest_kernel");
+}
+
 }  // namespace mxb

@@ -87,3 +87,66 @@ def test_ops_refuse_cpu_tensors():
 def test_missing_library_fails_loudly(tmp_path):
     with pytest.raises(ImportError):
         mixlab_b200.load_library(str(tmp_path / "nope.so"))
+
+
+def test_tensor_core_paths_reject_unaligned_pointers():
+    """The tensor-core kernels move whole 16-byte units: a q/k/v/out (x/b/c/y) base that is not 16-byte aligned is
+    refused at the C ABI, before any launch (fake pointers: nothing is dereferenced)."""
+    lib = mixlab_b200.lib()
+    ok, odd = C.c_void_p(1 << 20), C.c_void_p((1 << 20) + 8)
+    d = mixlab_b200.GdnDesc(1, 128, 2, 128, 128, 64, _lib.MXB_BF16, 1, 0)        # tensor-core shape
+    n = lib.mxb_gdn_bwd_workspace_bytes(C.byref(d))
+    for bad in range(3):
+        a = [ok, ok, ok]
+        a[bad] = odd
+        assert lib.mxb_gdn_fwd(C.byref(d), *a, ok, ok, None, ok, None, ok, n, None) == -5
+        assert lib.mxb_gdn_bwd(C.byref(d), *a, ok, ok, None, ok, None, ok, ok, ok, ok, ok, None, ok, n, None) == -5
+    assert lib.mxb_gdn_fwd(C.byref(d), ok, ok, ok, ok, ok, None, odd, None, ok, n, None) == -5
+    assert lib.mxb_gdn_bwd(C.byref(d), ok, ok, ok, ok, ok, None, odd, None, ok, ok, ok, ok, ok, None, ok, n, None) == -5
+    assert lib.mxb_gdn_bwd(C.byref(d), ok, ok, ok, ok, ok, None, ok, None, ok, odd, ok, ok, ok, None, ok, n, None) == -5
+    m = mixlab_b200.Mamba3Desc(1, 128, 128, 128, 1, 2, _lib.MXB_BF16, 0)         # chunked tensor-core shape
+    nm = lib.mxb_mamba3_bwd_workspace_bytes(C.byref(m))
+    assert nm > 0
+    assert lib.mxb_mamba3_fwd(C.byref(m), odd, ok, ok, ok, ok, ok, ok, ok, ok, nm, None) == -5
+    assert lib.mxb_mamba3_fwd(C.byref(m), ok, ok, ok, ok, ok, odd, ok, ok, ok, nm, None) == -5
+    assert lib.mxb_mamba3_bwd(C.byref(m), ok, ok, ok, ok, ok, ok, ok, odd, *([ok] * 7), ok, nm, None) == -5
+
+
+def test_chunk_above_64_is_accepted():
+    lib = mixlab_b200.lib()
+    d64 = mixlab_b200.GdnDesc(1, 256, 2, 32, 32, 64, _lib.MXB_F32, 0, 0)
+    d128 = mixlab_b200.GdnDesc(1, 256, 2, 32, 32, 128, _lib.MXB_F32, 0, 0)
+    assert lib.mxb_gdn_fwd_workspace_bytes(C.byref(d128)) == lib.mxb_gdn_fwd_workspace_bytes(C.byref(d64)) > 0
+    wide = mixlab_b200.GdnDesc(1, 64, 1, 128, 256, 64, _lib.MXB_F32, 0, 0)     # the reference default Dv = 2 Dk
+    assert lib.mxb_gdn_bwd_workspace_bytes(C.byref(wide)) > 0
+
+
+def test_ops_check_every_operand():
+    """Shape, dtype and device of every operand are checked in Python before the C ABI sees a pointer.  The checks
+    run before the CUDA requirement is looked at only for CUDA tensors, so this uses the helper directly."""
+    import torch
+    from mixlab_b200 import ops
+    dev = torch.device("cpu")
+    t = torch.zeros(2, 3)
+
+    class FakeCuda:
+        """Stands in for a CUDA tensor: only the attributes the checker reads."""
+        def __init__(self, shape, dtype, device="cuda:0", contiguous=True):
+            self.shape, self.dtype, self.device, self._c, self.is_cuda = shape, dtype, device, contiguous, True
+
+        def is_contiguous(self):
+            return self._c
+
+    good = FakeCuda((2, 3), torch.float32)
+    ops._check_like(good, (2, 3), torch.float32, "cuda:0", "x")
+    ops._check_like(None, (2, 3), torch.float32, "cuda:0", "x")
+    with pytest.raises(ValueError):
+        ops._check_like(t, (2, 3), torch.float32, dev, "x")                              # not a CUDA tensor
+    with pytest.raises(ValueError):
+        ops._check_like(FakeCuda((2, 4), torch.float32), (2, 3), torch.float32, "cuda:0", "x")
+    with pytest.raises(TypeError):
+        ops._check_like(FakeCuda((2, 3), torch.bfloat16), (2, 3), torch.float32, "cuda:0", "x")
+    with pytest.raises(ValueError):
+        ops._check_like(FakeCuda((2, 3), torch.float32, "cuda:1"), (2, 3), torch.float32, "cuda:0", "x")
+    with pytest.raises(ValueError):
+        ops._check_like(FakeCuda((2, 3), torch.float32, contiguous=False), (2, 3), torch.float32, "cuda:0", "x")

@@ -345,3 +345,150 @@ def test_tensor_core_tma_matches_cp_async_staging(T):
     g2 = ops.gated_delta_scan_backward(*args, _dev(a["d_out"]), 64, gate_is_log=True, flags=_lib.MXB_GDN_NO_TMA)
     for name in ("dq", "dk", "dv", "dbeta", "dgate"):
         assert torch.equal(g1[name], g2[name]), name
+
+
+# ---------------------------------------------------------------- numeric guards, chunk sizes, wide values
+def _guard_case(kind, B, T, H, K, V, io, seed=51):
+    """Inputs on which the reference's guards change the result (gpu/ir.cpp:35-37): gates at and below the floor of
+    1e-30 (multiplicative form) or log decays whose in-chunk cumulative sum passes -80 / falls below log(1e-30)."""
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=seed, io_dtype=io, with_grad_out=True, with_h0=True)
+    g = a["g"].clone()
+    if kind == "tiny_gates":      # multiplicative gate with exact zeros and values around the floor
+        gate = torch.exp(g)
+        flat = gate.view(-1)
+        for off, val in ((5, 0.0), (17, 1e-38), (29, 1e-31), (43, 1e-29)):
+            flat[off::97] = val
+        return a, gate, False
+    if kind == "steep":           # -3 per token: the in-chunk cumulative sum passes -80 after 27 tokens
+        return a, torch.full_like(g, -3.0), True
+    if kind == "abyss":           # single log decays below log(1e-30) = -69.08
+        flat = g.view(-1)
+        flat[7::53] = -200.0
+        return a, g, True
+    raise ValueError(kind)
+
+
+def _check_guard_case(kind, shape, io, tol, flags=0, chunk=64):
+    B, T, H, K, V = shape
+    a, gate, is_log = _guard_case(kind, B, T, H, K, V, io)
+    f = {k: v.double() for k, v in a.items()}
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], gate.double(), f["d_out"], f["d_state"], f["h0"],
+                          gate_is_log=is_log, chunk_size=64)
+    args = (_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(gate))
+    o, s = ops.gated_delta_scan(*args, chunk, gate_is_log=is_log, h0=_dev(a["h0"]), return_final_state=True, flags=flags)
+    got = ops.gated_delta_scan_backward(*args, _dev(a["d_out"]), chunk, gate_is_log=is_log, h0=_dev(a["h0"]),
+                                        d_final_state=_dev(a["d_state"]), flags=flags)
+    torch.cuda.synchronize()
+    assert_close(o, want["out"], tol, f"{kind}: out")
+    assert_close(s, want["state"], tol, f"{kind}: final_state")
+    for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
+        assert_close(got[name], want[name], tol, f"{kind}: {name}")
+    return a, gate, is_log, got
+
+
+@pytest.mark.parametrize("kind", ["tiny_gates", "steep", "abyss"])
+@pytest.mark.parametrize("shape", [(2, 130, 2, 16, 24), (1, 200, 2, 64, 64)])
+def test_numeric_guards_fp32(kind, shape):
+    """fp32 kernels on the inputs the gate floor and the exponent clamp exist for, against the float64 oracle of the
+    chunked form (which carries the same guards): outputs, final state, every gradient, all finite."""
+    a, gate, is_log, got = _check_guard_case(kind, shape, torch.float32, TOL_F32)
+    if kind == "tiny_gates":  # the gradient with respect to a gate below the floor is exactly zero (clamp)
+        below = _dev(gate) < 1e-30
+        assert below.any() and (got["dgate"][below] == 0).all()
+
+
+@pytest.mark.parametrize("kind", ["tiny_gates", "steep", "abyss"])
+def test_numeric_guards_tensor_core(kind):
+    """The same inputs through the tcgen05 kernels (bf16 I/O, d = 128, chunk 64) at 2e-2."""
+    _check_guard_case(kind, (1, 200, 2, 128, 128), torch.bfloat16, TOL_BF16)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["tiny_gates", "abyss"])
+def test_recurrence_has_no_gate_floor(kind):
+    """chunk <= 1 and the decode step follow gated_delta_scan_naive (gpu/ir.cpp:2334), which applies no floor: a zero
+    gate empties the state exactly.  The backward of chunk <= 1 differentiates the chunked form (its gate gradient is
+    zero below the floor); all other gradients agree with the recurrence's to fp32 accuracy."""
+    B, T, H, K, V = 2, 60, 2, 16, 24
+    a, gate, is_log = _guard_case(kind, B, T, H, K, V, torch.float32)
+    f = {k: v.double() for k, v in a.items()}
+    g64 = torch.exp(gate.double()) if is_log else gate.double()
+    want_o, want_s = gdn.scan_naive(f["q"], f["k"], f["v"], f["beta"], g64, f["h0"])
+    args = (_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(gate))
+    o, s = ops.gated_delta_scan(*args, 0, gate_is_log=is_log, h0=_dev(a["h0"]), return_final_state=True)
+    assert_close(o, want_o, TOL_F32, "out")
+    assert_close(s, want_s, TOL_F32, "final_state")
+    st = _dev(a["h0"].clone())
+    for t in range(T):
+        od = ops.gated_delta_decode_step(st, *(x[:, t].contiguous() for x in args), gate_is_log=is_log)
+        assert_close(od, want_o[:, t], TOL_F32, f"decode out[{t}]")
+    assert_close(st, want_s, TOL_F32, "decode state")
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], gate.double(), f["d_out"], f["d_state"], f["h0"],
+                          gate_is_log=is_log, chunk_size=64)
+    got = ops.gated_delta_scan_backward(*args, _dev(a["d_out"]), 0, gate_is_log=is_log, h0=_dev(a["h0"]),
+                                        d_final_state=_dev(a["d_state"]))
+    for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
+        assert_close(got[name], want[name], TOL_F32, name)
+
+
+@pytest.mark.parametrize("case", [(2, 300, 2, 32, 20, torch.float32, 0), (1, 300, 2, 128, 128, torch.bfloat16, 0),
+                                  (1, 300, 2, 128, 128, torch.bfloat16, 1)])
+def test_chunk_above_64_equals_chunk_64(case):
+    """The reference accepts scan_chunk_size overrides above 64 (arch/blocks_gated_deltanet.go:11-17); the result does
+    not depend on the chunk size and is computed with chunks of 64: same bits."""
+    from mixlab_b200 import _lib
+    B, T, H, K, V, io, fp32_path = case
+    flags = _lib.MXB_GDN_FORCE_FP32_PATH if fp32_path else 0
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=61, io_dtype=io, with_grad_out=True)
+    args = (_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]))
+    res = {}
+    for chunk in (64, 128, 256):
+        o, s = ops.gated_delta_scan(*args, chunk, gate_is_log=True, return_final_state=True, flags=flags)
+        g = ops.gated_delta_scan_backward(*args, _dev(a["d_out"]), chunk, gate_is_log=True, flags=flags)
+        res[chunk] = (o, s, g)
+    for chunk in (128, 256):
+        assert torch.equal(res[chunk][0], res[64][0]) and torch.equal(res[chunk][1], res[64][1])
+        for name in ("dq", "dk", "dv", "dbeta", "dgate"):
+            assert torch.equal(res[chunk][2][name], res[64][2][name]), name
+    want_o, _ = _oracle_fwd(a, 128)
+    assert_close(res[128][0], want_o, TOL_F32 if io == torch.float32 else TOL_BF16, "out vs oracle at chunk 128")
+
+
+@pytest.mark.parametrize("shape", [(1, 100, 2, 16, 256, 64), (1, 70, 1, 128, 256, 64), (1, 40, 1, 64, 160, 0)])
+def test_wide_values_fp32(shape):
+    """Dv = 2 Dk is the reference default (effectiveGatedDeltaNetDV): values up to 256 wide on the fp32 kernels."""
+    B, T, H, K, V, C = shape
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=71, with_grad_out=True, with_h0=True)
+    f = {k: v.double() for k, v in a.items()}
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], f["g"], f["d_out"], f["d_state"], f["h0"], gate_is_log=True)
+    args = (_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]))
+    o, s = ops.gated_delta_scan(*args, C, gate_is_log=True, h0=_dev(a["h0"]), return_final_state=True)
+    assert_close(o, want["out"], TOL_F32, "out")
+    assert_close(s, want["state"], TOL_F32, "final_state")
+    got = ops.gated_delta_scan_backward(*args, _dev(a["d_out"]), C, gate_is_log=True, h0=_dev(a["h0"]),
+                                        d_final_state=_dev(a["d_state"]))
+    for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
+        assert_close(got[name], want[name], TOL_F32, name)
+
+
+def test_front_end_rejects_mismatched_operands():
+    """A k with fewer heads, a float32 k beside a bf16 q, an h0 of the wrong width: Python errors, no launch."""
+    lib = mixlab_b200.lib()
+    a = inputs.gdn_inputs(1, 32, 2, 16, 16, seed=0, with_grad_out=True, with_h0=True)
+    d = {k: _dev(v) for k, v in a.items()}
+    n0 = lib.mxb_launch_count()
+    with pytest.raises(ValueError):
+        ops.gated_delta_scan(d["q"], d["k"][:, :, :1].contiguous(), d["v"], d["beta"], d["g"], 64, gate_is_log=True)
+    with pytest.raises(TypeError):
+        ops.gated_delta_scan(d["q"].bfloat16(), d["k"], d["v"].bfloat16(), d["beta"], d["g"], 64, gate_is_log=True)
+    with pytest.raises(ValueError):
+        ops.gated_delta_scan(d["q"], d["k"], d["v"], d["beta"], d["g"], 64, gate_is_log=True, h0=d["h0"][..., :8].contiguous())
+    with pytest.raises(ValueError):
+        ops.gated_delta_scan_backward(d["q"], d["k"], d["v"], d["beta"], d["g"], d["d_out"][:, :16].contiguous(), 64,
+                                      gate_is_log=True)
+    with pytest.raises(RuntimeError):  # use_saved without a saving forward just before
+        ops.gated_delta_scan(d["q"], d["k"], d["v"], d["beta"], d["g"], 64, gate_is_log=True)
+        ops.gated_delta_scan_backward(d["q"], d["k"], d["v"], d["beta"], d["g"], d["d_out"], 64, gate_is_log=True,
+                                      use_saved=True)
+    torch.cuda.synchronize()
+    assert lib.mxb_launch_count() - n0 <= 2  # only the one plain forward above launched anything

@@ -97,3 +97,21 @@ def test_umma_operand_layouts():
     bad = {k: v for k, v in results.items() if not v["ok"]}
     print(json.dumps(results, indent=1))
     assert not bad, bad
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A device-side wait that runs out: the kernel returns, the status word carries the code, the context stays
+    usable (a following launch works) and a later clean launch reads status 0 again."""
+    lib = mixlab_b200.lib()
+    ws = torch.empty(4096, dtype=torch.uint8, device="cuda")
+    out = C.c_int32(-1)
+    assert lib.mxb_selftest_wait_timeout(C.c_void_p(ws.data_ptr()), ws.numel(), 0, None) == -1   # limit out of range
+    assert lib.mxb_selftest_wait_timeout(C.c_void_p(ws.data_ptr()), 16, 100, None) == -3          # no room for the header
+    assert lib.mxb_selftest_wait_timeout(C.c_void_p(ws.data_ptr()), ws.numel(), 2000, None) == 0
+    assert lib.mxb_gdn_device_status(C.c_void_p(ws.data_ptr()), C.byref(out)) == 0
+    assert out.value == 9
+    torch.cuda.synchronize()
+    # the context is intact: an ordinary tile still runs and a fresh status header reads clean
+    assert run_case(lib, 128, 64, 64, "k_none", "k_none")["ok"]
+    ws.zero_()
+    assert lib.mxb_gdn_device_status(C.c_void_p(ws.data_ptr()), C.byref(out)) == 0 and out.value == 0
