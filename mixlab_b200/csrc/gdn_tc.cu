@@ -666,11 +666,6 @@ static size_t carve_tc(TcP& p, void* ws, bool bwd) {
     p.vn = cv.take<bf16>(nc * C * KD);
     p.dhs = cv.take<bf16>(nc * KD * KD);
     p.dvn = cv.take<bf16>(nc * C * KD);
-    p.dqp = cv.take<bf16>(nc * C * KD);
-    p.dkp = cv.take<bf16>(nc * C * KD);
-    p.dw = cv.take<bf16>(nc * C * KD);
-    p.dpg = cv.take<bf16>(nc * C * C);
-    p.ls = cv.take<float>(nc);
   }
   return cv.bytes();
 }

@@ -41,18 +41,13 @@ struct TcP {
   bf16* vn;      // [C][KD]
   bf16* dhs;     // [KD][KD]  dS at chunk end
   bf16* dvn;     // [C][KD]   -dv_new (the sign the state pass needs as an operand)
-  bf16* dqp;     // [C][KD]   d (dO S0^T)        } state contractions of the chunk backward,
-  bf16* dkp;     // [C][KD]   r (v_new dS^T)     } handed from its first kernel to its second
-  bf16* dw;      // [C][KD]   -dv_new S0^T       }
-  bf16* dpg;     // [C][C]    (dO v_new^T) * Gamma, lower triangle incl. diagonal
-  float* ls;     // [1]       E(gam_last) <dS, S0>
 };
 
 // Tensor maps of the token-indexed operands: [B,T,H,128] bf16 viewed as (D, H, T, B), boxes of 64 columns x
 // 64 time steps with 128-byte swizzle; rows past the end of the sequence are zero-filled by the copy engine.
-// o: the forward output, written back by tiled stores (rows past the end of the sequence are clipped).
+// o, dq, dk: results written back by tiled stores (rows past the end of the sequence are clipped).
 struct alignas(64) RowMaps {
-  CUtensorMap k, q, v, dO, o;
+  CUtensorMap k, q, v, dO, o, dq, dk;
 };
 
 // Views of a [64][128] tile for tcgen05 and for 16-byte unit access: written by the copy engine with 128-byte

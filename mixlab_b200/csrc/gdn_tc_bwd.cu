@@ -10,8 +10,8 @@
 //   gdn_tc_state_bwd_kernel  reverse over chunks, one CTA per (batch, head), operands two chunks ahead:
 //       dv_new = P^T dO + r (k dS)
 //       dS    <- L dS + (d q)^T dO - w^T dv_new
-//   gdn_tc_chunk_bwd_state_kernel  one CTA per chunk: the contractions with the saved states S0 and dS
-//   gdn_tc_chunk_bwd_kernel  one CTA per chunk, everything else:
+//   gdn_tc_chunk_bwd_kernel  one CTA per chunk, everything else (the contractions with the saved states S0 and dS
+//       included):
 //       dq = d (dO S0^T) + (dP*Gamma) k                      dP = tril(dO v_new^T)
 //       dw = -dv_new S0^T ; dT = dv_new (v beta)^T + dw (k beta d)^T ; dA = tril(T^T dT T^T,-1)
 //       dk = (dP*Gamma)^T q + r (v_new dS^T) + beta d (T^T dw) + (Mb + Mb^T) k,  Mb = -beta dA*Gamma
@@ -266,15 +266,29 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
   if (warp == 0) tc::tmem_dealloc(taddr, 512);
 }
 
-// ------------------------------------------------- chunk backward, part 2: everything else
-// 256 TMEM columns and 108 KB of shared memory: two CTAs share an SM.  TMEM column map (fp32 columns; all
-// accumulators are M=64, so row i of every result sits in TMEM lane (i%16) + 32*(i/16) and is handled by
-// thread (warp i/16, lane i%16); warps 4-7 take the second half of the columns):
-//   1: T^T dv_new [0,128)             z = T^T dw [128,256)      (both rewritten to shared memory as bf16)
-//   2: (T^T dv_new) v^T [0,64)        z k^T [64,128)            k k^T [128,192)   q k^T [192,256)
-//   3: Y T^T [0,64)   with Y = T^T dT assembled from phase 2
-//   4: (dP*Gamma) k [0,128)           (dP*Gamma)^T q + (Mb + Mb^T) k [128,256)
-constexpr int kChunkBwdSmem = 5 * 16384 + 3 * 8192 + 13 * C * 4 + 64 + 1024;
+// ------------------------------------------------- chunk backward
+// One CTA per chunk does everything that is not the sequential state pass.  With e = T^T dv_new, z = T^T dw = -e S0^T
+// (dw = -dv_new S0^T never needs to be formed), Gamma_ij = E(gam_i - gam_j):
+//   batch 1   -e = T^T (-dv_new)                    dP = dO v_new^T                -> dPG = dP*Gamma (lower incl. diagonal)
+//   batch 2   DQ = (d dO) S0^T   (stays in TMEM)    z = (-e) S0^T                  (dO is scaled by d in place first)
+//   batch 3   r (v_new dS^T) -> dkp                                                 <dS, S0> on the side
+//   batch 4   (-e) v^T, z k^T   -> Y = T^T dT = beta_m (e.v_m + d_m z.k_m)
+//   batch 5   dA = tril(Y T^T, -1), k k^T           -> M = -dA*Gamma, Mb = beta_i M
+//   batch 6   DQ += dPG k                            dPG^T q + Mb k + Mb^T k
+//   dq = DQ      dk = dkp + batch 6 + beta d z      dv = beta e      dbeta = e.v + d (k.z) + sum_j M_ij (k_i.k_j)
+//   dgam_i = q_i.dq_i - k_i.dk_i + 2 beta_i (d_i (k_i.z_i) + sum_j M_ij (k_i.k_j)),  dgam_last += L <dS,S0> + sum_i k_i.dkp_i
+// (the row and column sums over Gamma of the P and A terms are exactly the parts of q.dq and k.dk that come from
+// dPG and Mb, so they need no products of their own).
+//
+// 256 TMEM columns and 107 KB of shared memory: two CTAs share an SM.  Every buffer is reused as soon as it is dead:
+//   XdO   dO (TMA tile) -> d dO -> z                      Xe   -dv_new image -> -e -> ... -> the dq tile on its way out
+//   Xvn   v_new image -> v (TMA) -> q (TMA)               R1   S0 image -> dS image -> k (TMA) | dkp -> the dk tile
+// TMEM: [0,128) -e, then DQ until the end; [128,256) the other products one after the other.  All accumulators are
+// M=64: row i sits in TMEM lane (i%16) + 32*(i/16) and is handled by thread (warp i/16, lane i%16); warps 4-7 take
+// the second half of the columns.  Grid = (batch*head, chunk) with batch*head fastest: neighbouring CTAs read
+// neighbouring heads of the same time steps (one contiguous row of the token tensors between them), and the chunks
+// the reverse state pass wrote last are read first.
+constexpr int kChunkBwdSmem = 3 * 16384 + 32768 + 3 * 8192 + 8 * C * 4 + 16 * 4 + 64 + 64 + 1024;
 
 __device__ __forceinline__ void unpack8(uint4 v, float (&e)[8]) {
   tc::unpack_bf16(v.x, e[0], e[1]); tc::unpack_bf16(v.y, e[2], e[3]);
@@ -284,11 +298,10 @@ __device__ __forceinline__ uint4 pack8(const float* e) {
   return make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]), tc::pack_bf16(e[4], e[5]),
                     tc::pack_bf16(e[6], e[7]));
 }
-// sum_k tile[row][c0 + k] * f[k], k < 32, for a blocked [.][128] bf16 tile in shared memory
+// sum_k tile[row][c0 + k] * f[k], k < 32, for a [64][128] bf16 tile in shared memory (SW: 128-byte-swizzled TMA
+// tile, else the blocked layout): the four units are fetched first and summed in four independent chains
 template <bool SW>
 __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
-  // the four units are fetched first and summed in four independent chains (one chain of 32 dependent FMAs
-  // would cost ~130 cycles of latency on its own)
   uint4 raw[4];
 #pragma unroll
   for (int x = 0; x < 4; ++x) raw[x] = *reinterpret_cast<const uint4*>(tile + in_unit<SW>(r, (c0 >> 3) + x));
@@ -302,303 +315,67 @@ __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, c
   }
   return (s[0] + s[1]) + (s[2] + s[3]);
 }
-
-// ------------------------------------------------- chunk backward, part 1: state contractions
-// Per chunk: everything that needs the saved states.  256 TMEM columns and 97 KB of shared memory, so two
-// CTAs share an SM.  S0 and dS use the same shared-memory buffer one after the other.  The four results are
-// assembled in shared memory in the blocked operand layout and leave as contiguous 16 KB / 8 KB bulk
-// copies; the second kernel loads those byte images back unchanged.
-//   phase 1: dO S0^T [0,128), (-dv_new) S0^T [128,256) -> dqp = d (dO S0^T), dw = -dv_new S0^T
-//   phase 2: v_new dS^T [0,128), dO v_new^T [128,192) -> dkp = r (v_new dS^T), dP*Gamma, L <dS, S0>
-constexpr int kChunkBwdStateSmem = 4 * 16384 + 32768 + 4 * C * 4 + 64 + 1024;
-
-template <bool TMA>
-__global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_state_kernel(TcP p, const __grid_constant__ RowMaps maps) {
-  extern __shared__ uint8_t raw[];
-  uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
-  uint8_t* Xdo = sm;                // [64][128] dO            -> later the dkp image
-  uint8_t* Xdvn = Xdo + 16384;      // [64][128] -dv_new       -> later the dqp image
-  uint8_t* Xvn = Xdvn + 16384;      // [64][128] v_new         -> later the dP*Gamma image (first half)
-  uint8_t* Xst = Xvn + 16384;       // the dw image
-  uint8_t* Xs = Xst + 16384;        // [128][128] S0, then dS
-  float* gam = reinterpret_cast<float*>(Xs + 32768);
-  float* dd = gam + C;
-  float* rr = dd + C;
-  float* red = rr + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + C);  // [0] MMA, [1] dO/dv_new/S0, [2] v_new, [3] dS
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
-  const size_t ci = (size_t)bh * p.n + c;
-  const int imax = min(C, p.T - t0);
-  auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
-  const bool own = lane < 16;
-  const int i = 16 * (warp & 3) + (lane & 15), hc = warp >> 2;
-
-  // prologue latencies side by side: warp 0 allocates TMEM, one thread of warp 1 issues the copies, warp 2-3 fetch gam
-  if (tid == 32) {
-    for (int m = 0; m < 4; ++m) tc::mbar_init(mbar + m, 1);
-    tc::mbar_fence_init();
-    if (TMA) {  // dO by the copy engine (swizzled tile), the workspace images by bulk copies
-      tc::mbar_expect_tx(mbar + 1, 2 * 16384 + 32768);
-      tc::tma_load_4d(tc::smem_u32(Xdo), &maps.dO, 0, h, t0, b, mbar + 1);
-      tc::tma_load_4d(tc::smem_u32(Xdo) + 8192, &maps.dO, 64, h, t0, b, mbar + 1);
-      tc::bulk_load(tc::smem_u32(Xdvn), p.dvn + ci * C * KD, 16384, mbar + 1);
-      tc::bulk_load(tc::smem_u32(Xs), p.hs + ci * KD * KD, 32768, mbar + 1);
-      tc::mbar_expect_tx(mbar + 2, 16384);
-      tc::bulk_load(tc::smem_u32(Xvn), p.vn + ci * C * KD, 16384, mbar + 2);
-    }
-  }
-  if (!TMA) {  // group 0: dO, dv_new, S0   group 1: v_new
-    const uint32_t sdo = tc::smem_u32(Xdo), sdvn = tc::smem_u32(Xdvn), svn = tc::smem_u32(Xvn), ss = tc::smem_u32(Xs);
-    for (int u = tid; u < 64 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
-      const uint32_t off = tc::kmajor_unit(r, c8, KD);
-      tc::cp_async16(sdo + off, r < imax ? p.dO + row(r) * KD + c8 * 8 : p.dO, r < imax);
-      tc::cp_async16(sdvn + 16 * u, p.dvn + ci * C * KD + 8 * u);  // byte images of the operand tiles from here on
-    }
-    for (int u = tid; u < 128 * 16; u += 256) tc::cp_async16(ss + 16 * u, p.hs + ci * KD * KD + 8 * u);
-    tc::cp_async_commit();
-    for (int u = tid; u < 64 * 16; u += 256) tc::cp_async16(svn + 16 * u, p.vn + ci * C * KD + 8 * u);
-    tc::cp_async_commit();
-  }
-  if (warp == 0) {
-    tc::tmem_alloc(tslot, 256);
-    tc::tmem_relinquish();
-  }
-  if (tid >= 64 && tid < 64 + C) gam[tid - 64] = p.gam[ci * C + tid - 64];
-  __syncthreads();
-  const float glast = gam[C - 1], L = exp_nonpos(glast);
-  if (tid < C) {
-    dd[tid] = exp_nonpos(gam[tid]);
-    rr[tid] = exp_nonpos(glast - gam[tid]);
-  }
-  bool ok = true;
-  if (TMA) ok = tc::mbar_wait(mbar + 1, 0);
-  else tc::cp_async_wait<1>();
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  const uint32_t taddr = *tslot;
-  if (tid == 0) {
-    tc::issue_gemm(taddr + 0, in_kmajor<TMA>(Xdo), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);          // dO S0^T
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(Xdvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);  // -dv_new S0^T
-    tc::mma_commit(mbar);
-  }
-  uint4 s0u[8];  // this thread's 8 units of S0, kept for <dS, S0> (the buffer is about to be reused)
+// sum over 64 columns [c0, c0+64) of a[row][.] * b[row][.] for two [64][128] bf16 tiles in shared memory
+template <bool SWA, bool SWB>
+__device__ __forceinline__ float row_dot_tiles64(const uint8_t* a, const uint8_t* b, int r, int c0) {
+  float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int x = 0; x < 8; ++x) s0u[x] = *reinterpret_cast<const uint4*>(Xs + (tid + 256 * x) * 16);
-  if (TMA) {  // every thread has taken its units before one thread lets the copy engine overwrite the buffer
-    tc::fence_async_smem();
-    __syncthreads();
+  for (int x = 0; x < 8; ++x) {
+    float ea[8], eb[8];
+    unpack8(*reinterpret_cast<const uint4*>(a + in_unit<SWA>(r, (c0 >> 3) + x)), ea);
+    unpack8(*reinterpret_cast<const uint4*>(b + in_unit<SWB>(r, (c0 >> 3) + x)), eb);
+#pragma unroll
+    for (int y = 0; y < 8; ++y) s[x & 3] = fmaf(ea[y], eb[y], s[x & 3]);
   }
-  if (ok) ok = tc::mbar_wait(mbar, 0);
-  tc::fence_after_sync();
-  // S0 is dead in shared memory: fetch dS into the same buffer behind the epilogue
-  if (TMA) {
-    if (tid == 0) {
-      tc::mbar_expect_tx(mbar + 3, 32768);
-      tc::bulk_load(tc::smem_u32(Xs), p.dhs + ci * KD * KD, 32768, mbar + 3);
-    }
-  } else {
-    const uint32_t ss = tc::smem_u32(Xs);
-    for (int u = tid; u < 128 * 16; u += 256) tc::cp_async16(ss + 16 * u, p.dhs + ci * KD * KD + 8 * u);
-    tc::cp_async_commit();
-  }
-  const float di = dd[i], ri = rr[i], gi = gam[i];
-  if (ok) {
-    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {
-      float f[32];
-      ld_acc32(taddr + 0, warp, c0, f);
-      if (own) {
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) f[jj] *= di;
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
-      }
-      ld_acc32(taddr + 128, warp, c0, f);
-      if (own) {  // the workspace holds -dv_new, so this is dw = -dv_new S0^T already
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xst, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
-      }
-    }
-  }
-  if (TMA) {  // v_new and dS
-    if (ok) ok = tc::mbar_wait(mbar + 2, 0);
-    if (ok) ok = tc::mbar_wait(mbar + 3, 0);
-  } else {
-    tc::cp_async_wait<0>();
-  }
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xvn, KD), tc::kmajor_tile(Xs, KD), 64, 128, KD, false);    // v_new dS^T
-    tc::issue_gemm(taddr + 128, in_kmajor<TMA>(Xdo), tc::kmajor_tile(Xvn, KD), 64, 64, KD, false);     // dO v_new^T
-    tc::mma_commit(mbar);
-    tc::bulk_store(p.dqp + ci * C * KD, tc::smem_u32(Xdvn), 16384);
-    tc::bulk_store(p.dw + ci * C * KD, tc::smem_u32(Xst), 16384);
-    tc::bulk_commit();
-  }
-  {  // <dS, S0>
-    float part = 0.f;
-#pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      float a[8], bq[8];
-      unpack8(*reinterpret_cast<const uint4*>(Xs + (tid + 256 * x) * 16), a);
-      unpack8(s0u[x], bq);
-#pragma unroll
-      for (int y = 0; y < 8; ++y) part = fmaf(a[y], bq[y], part);
-    }
-    part = warp_sum(part);
-    if (lane == 0) red[warp] = part;
-  }
-  if (ok) ok = tc::mbar_wait(mbar, 1);
-  tc::fence_after_sync();
-  if (ok) {
-    for (int c0 = 64 * hc; c0 < 64 * hc + 64; c0 += 32) {  // dkp = r (v_new dS^T)   (dO is dead: reuse its tile)
-      float f[32];
-      ld_acc32(taddr + 0, warp, c0, f);
-      if (own) {
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) f[jj] *= ri;
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xdo, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
-      }
-    }
-    {  // dP * Gamma, lower incl. diagonal (32 columns per half)   (v_new is dead: reuse its tile)
-      const int c0 = 32 * hc;
-      float f[32];
-      ld_acc32(taddr + 128, warp, c0, f);
-      if (own) {
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          const int j = c0 + jj;
-          const float val = f[jj] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
-          f[jj] = (j <= i) ? val : 0.f;
-        }
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xvn, tc::kmajor_unit(i, (c0 >> 3) + x, C), pack8(&f[8 * x]));
-      }
-    }
-  } else if (tid == 0) {
-    atomicExch(p.status, 5);
-  }
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  if (tid == 0) {
-    if (ok) {
-      tc::bulk_store(p.dkp + ci * C * KD, tc::smem_u32(Xdo), 16384);
-      tc::bulk_store(p.dpg + ci * C * C, tc::smem_u32(Xvn), 8192);
-      tc::bulk_commit();
-    }
-    float s = 0.f;
-    for (int wv = 0; wv < 8; ++wv) s += red[wv];
-    p.ls[ci] = L * s;  // d/dgam_last of E(gam_last) <dS, S0>
-    tc::bulk_wait_read<0>();  // shared memory must outlive the copies
-  }
-  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+  return (s[0] + s[1]) + (s[2] + s[3]);
 }
 
-// TMA = true: k, q, v by the copy engine (128-byte-swizzled tiles) and every workspace image by bulk copies, all
-// completing on mbarriers; TMA = false: cp.async staging in the un-swizzled layout.
-template <bool TMA>
 __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const __grid_constant__ RowMaps maps) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
-  uint8_t* Xk = sm;                 // [64][128] k
-  uint8_t* Xq = Xk + 16384;         // [64][128] q
-  uint8_t* Xv = Xq + 16384;         // [64][128] v; then Y = T^T dT (first half); then the dqp image -> dq
-  uint8_t* X2 = Xv;
-  uint8_t* Xdvn = Xv + 16384;       // [64][128] -dv_new, then T^T dv_new in place; then the dkp image -> dk
-  uint8_t* Xdw = Xdvn + 16384;      // [64][128] dw, then z = T^T dw in place
-  uint8_t* Xt = Xdw + 16384;        // [64][64]  T
+  uint8_t* XdO = sm;                // [64][128] dO (swizzled TMA tile), d dO in place, then z (blocked layout)
+  uint8_t* Xe = XdO + 16384;        // [64][128] -dv_new image, then -e in place (blocked), at the end the dq tile (swizzled)
+  uint8_t* Xvn = Xe + 16384;        // [64][128] v_new image, then v, then q (swizzled TMA tiles)
+  uint8_t* R1 = Xvn + 16384;        // [128][128] S0 image, then dS image, then k (swizzled TMA tile) | dkp -> dk (swizzled)
+  uint8_t* Xk = R1;
+  uint8_t* Xdk = R1 + 16384;
+  uint8_t* Xt = R1 + 32768;         // [64][64]  T
   uint8_t* Xpg = Xt + 8192;         // [64][64]  dP*Gamma
-  uint8_t* X1 = Xpg + 8192;         // [64][64]  Mb + Mb^T
-  float* gam = reinterpret_cast<float*>(X1 + 8192);
+  uint8_t* Xy = Xpg + 8192;         // [64][64]  Y, then Mb
+  float* gam = reinterpret_cast<float*>(Xy + 8192);
   float* bet = gam + C;
   float* dd = bet + C;
   float* rr = dd + C;
   float* dgo = rr + C;              // [2][C] per-row dgam / dbeta partials of the two column halves
   float* dbo = dgo + 2 * C;
-  float* red = dbo + 2 * C;
-  float* csw = red + C;             // [4 warps][C] per-warp column sums (no atomics)
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(csw + 4 * C);  // [0] MMA, [1] dv_new/dw/T, [2] k/q/v/dP*Gamma, [3] dqp/dkp
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
+  float* red = dbo + 2 * C;         // [0,8) <dS,S0> per warp, [8,16) sum of k.dkp per warp
+  // [0] MMA, [6] second MMA barrier of the last batch; loads: [1] -dv_new/T/dO/v_new, [2] S0, [3] dS, [4] k/v, [5] q
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + 16);
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, bh = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
+  const int bh = blockIdx.x, c = blockIdx.y, b = bh / p.H, h = bh % p.H, t0 = c * C;
   const size_t ci = (size_t)bh * p.n + c;
   const int imax = min(C, p.T - t0);
   auto row = [&](int i) { return ((size_t)(b * p.T + t0 + i) * p.H + h); };
   const bool own = lane < 16;
   const int i = 16 * (warp & 3) + (lane & 15);  // the row this thread owns in every epilogue
-  const int hc = warp >> 2;  // warps 0-3 take the first half of an accumulator's columns, warps 4-7 the second
+  const int hc = warp >> 2;   // warps 0-3 take the first half of an accumulator's columns, warps 4-7 the second
+  const int cb = 32 * hc;     // this thread's 32 columns of every [64][64] accumulator
+  const int cw = 64 * hc;     // this thread's 64 columns of every [64][128] accumulator
 
-  // The serial latencies of the prologue run side by side on different warps: warp 0 allocates TMEM, one thread
-  // each of warps 1 and 4 initialises two barriers and issues the copies that complete on them, warps 2-3 fetch
-  // the per-row scalars.
+  // prologue latencies side by side: warp 0 allocates TMEM, one thread of warp 1 initialises the barriers and issues
+  // the first copies, warps 2-3 fetch the per-row scalars
   if (tid == 32) {
-    tc::mbar_init(mbar + 0, 1);
-    tc::mbar_init(mbar + 5, 1);  // second MMA barrier: a phase with two commits never puts both on one barrier (a waiter
-                                 // that falls two phases behind a single barrier would wait for a third)
-    tc::mbar_init(mbar + 1, 1);
+    for (int m = 0; m < 7; ++m) tc::mbar_init(mbar + m, 1);
     tc::mbar_fence_init();
-    if (TMA) {
-      tc::mbar_expect_tx(mbar + 1, 2 * 16384 + 8192);
-      tc::bulk_load(tc::smem_u32(Xdvn), p.dvn + ci * C * KD, 16384, mbar + 1);  // byte images of the operand tiles
-      tc::bulk_load(tc::smem_u32(Xdw), p.dw + ci * C * KD, 16384, mbar + 1);
-      tc::bulk_load(tc::smem_u32(Xt), p.Tm + ci * C * C, 8192, mbar + 1);
-    }
-  }
-  if (tid == 128) {
-    tc::mbar_init(mbar + 2, 1);
-    tc::mbar_init(mbar + 3, 1);
-    tc::mbar_fence_init();
-    if (TMA) {
-      tc::mbar_expect_tx(mbar + 2, 3 * 16384 + 8192);
-      for (int sl = 0; sl < 2; ++sl) {
-        tc::tma_load_4d(tc::smem_u32(Xk) + 8192 * sl, &maps.k, 64 * sl, h, t0, b, mbar + 2);
-        tc::tma_load_4d(tc::smem_u32(Xq) + 8192 * sl, &maps.q, 64 * sl, h, t0, b, mbar + 2);
-        tc::tma_load_4d(tc::smem_u32(Xv) + 8192 * sl, &maps.v, 64 * sl, h, t0, b, mbar + 2);
-      }
-      tc::bulk_load(tc::smem_u32(Xpg), p.dpg + ci * C * C, 8192, mbar + 2);
-    }
-  }
-  if (!TMA) {  // group 0: dv_new, dw, T   group 1: k, q, v, dP*Gamma
-    const uint32_t sk = tc::smem_u32(Xk), sq = tc::smem_u32(Xq), sv = tc::smem_u32(Xv);
-    const uint32_t sdvn = tc::smem_u32(Xdvn), sdw = tc::smem_u32(Xdw);
-    const uint32_t st = tc::smem_u32(Xt), spg = tc::smem_u32(Xpg);
-    for (int u = tid; u < 64 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
-      const uint32_t off = tc::kmajor_unit(r, c8, KD);
-      tc::cp_async16(sdvn + 16 * u, p.dvn + ci * C * KD + 8 * u);  // byte images of the operand tiles (-dv_new, dw)
-      tc::cp_async16(sdw + 16 * u, p.dw + ci * C * KD + 8 * u);
-    }
-    for (int u = tid; u < 64 * 8; u += 256) {
-      const int r = urow8(u), c8 = ucol8(u);
-      tc::cp_async16(st + 16 * u, p.Tm + ci * C * C + 8 * u);
-    }
-    tc::cp_async_commit();
-    for (int u = tid; u < 64 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
-      const uint32_t off = tc::kmajor_unit(r, c8, KD);
-      const bool v = r < imax;
-      const size_t g = v ? row(r) * KD + c8 * 8 : 0;
-      tc::cp_async16(sk + off, p.k + g, v);
-      tc::cp_async16(sq + off, p.q + g, v);
-      tc::cp_async16(sv + off, p.v + g, v);
-    }
-    for (int u = tid; u < 64 * 8; u += 256) {
-      const int r = urow8(u), c8 = ucol8(u);
-      tc::cp_async16(spg + 16 * u, p.dpg + ci * C * C + 8 * u);
-      (void)r; (void)c8;
-    }
-    tc::cp_async_commit();
+    tc::mbar_expect_tx(mbar + 1, 3 * 16384 + 8192);
+    tc::bulk_load(tc::smem_u32(Xe), p.dvn + ci * C * KD, 16384, mbar + 1);  // byte images of the operand tiles
+    tc::bulk_load(tc::smem_u32(Xt), p.Tm + ci * C * C, 8192, mbar + 1);
+    tc::bulk_load(tc::smem_u32(Xvn), p.vn + ci * C * KD, 16384, mbar + 1);
+    for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(tc::smem_u32(XdO) + 8192 * sl, &maps.dO, 64 * sl, h, t0, b, mbar + 1);
+    tc::mbar_expect_tx(mbar + 2, 32768);
+    tc::bulk_load(tc::smem_u32(R1), p.hs + ci * KD * KD, 32768, mbar + 2);
   }
   if (warp == 0) {
     tc::tmem_alloc(tslot, 256);
@@ -609,294 +386,307 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     gam[r] = p.gam[ci * C + r];
     bet[r] = r < imax ? p.beta[row(r)] : 0.f;
   }
-  for (int u = tid; u < 4 * C; u += 256) csw[u] = 0.f;
+  tc::fence_before_sync();
   __syncthreads();
-  const float glast = gam[C - 1];
+  tc::fence_after_sync();
+  const float glast = gam[C - 1], L = exp_nonpos(glast);
   if (tid < C) {
     dd[tid] = exp_nonpos(gam[tid]);
     rr[tid] = exp_nonpos(glast - gam[tid]);
   }
-  bool ok = true;
-  if (TMA) ok = tc::mbar_wait(mbar + 1, 0);
-  else tc::cp_async_wait<1>();
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  const uint32_t taddr = *tslot;
+  const uint32_t tA = *tslot, tB = tA + 128;
+  bool ok = tc::mbar_wait(mbar + 1, 0);
   uint32_t ph = 0;
-  // ---- phase 1: T^T dv_new and z = T^T dw (both operands contracted over their rows) ----
-  if (tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdvn, KD), 64, 128, C, false);
-    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xdw, KD), 64, 128, C, false);
+  // ---- batch 1: -e = T^T (-dv_new) (both operands contracted over their rows), dP = dO v_new^T ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(tA, tc::mnmajor_tile(Xt, C), tc::mnmajor_tile(Xe, KD), 64, 128, C, false);
+    tc::issue_gemm(tB, tc::kmajor_sw128_tile(XdO, 8192), tc::kmajor_tile(Xvn, KD), 64, 64, KD, false);
     tc::mma_commit(mbar);
   }
-  if (TMA) { if (ok) ok = tc::mbar_wait(mbar + 2, 0); }  // k, q, v, dP*Gamma
-  else tc::cp_async_wait<0>();
-  __syncthreads();
+  __syncthreads();  // dd, rr visible
+  const float gi = gam[i], bi = bet[i], di = dd[i], ri = rr[i];
+  const float bd_i = bi * di;
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
-  float dg_own = 0.f, db_own = 0.f;
-  const float gi = gam[i], bi = bet[i], di = dd[i], ri = rr[i];
-  const float bd_i = bi * di;
-  const int cb = 32 * hc;  // this thread's 32 columns of every [64][64] accumulator
-  const int cw = 64 * hc;  // this thread's 64 columns of every [64][128] accumulator
   if (ok) {
-    // Both products go back to shared memory as bf16 operands of phase 2, over the operands they were
-    // computed from (their MMAs are complete); dv = beta (T^T dv_new) leaves from there after phase 2.
-    float vdot = 0.f, kz = 0.f;
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 2; ++s) {  // -e goes back over the operand it was computed from (its MMA is complete)
       const int c0 = cw + 32 * s;
       float f[32];
-      ld_acc32(taddr + 0, warp, c0, f);
+      ld_acc32(tA, warp, c0, f);
       if (own) {
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) f[jj] = -f[jj];  // the workspace holds -dv_new
-        vdot += row_dot32<TMA>(Xv, i, c0, f);
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
+        for (int x = 0; x < 4; ++x) sts16(Xe, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
-      ld_acc32(taddr + 128, warp, c0, f);
+    }
+    {  // dP * Gamma, lower triangle incl. diagonal
+      float f[32];
+      ld_acc32(tB, warp, cb, f);
       if (own) {
-        kz += row_dot32<TMA>(Xk, i, c0, f);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xdw, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
-      }
-    }
-    if (own) {
-      db_own += vdot + di * kz;
-      dg_own += bd_i * kz;
-    }
-  }
-  tc::fence_async_smem();
-  tc::fence_before_sync();
-  __syncthreads();
-  tc::fence_after_sync();
-  // ---- phase 2: Y = T^T dT = (T^T dv_new)(v beta)^T + z (k beta d)^T, with the column scales applied in the
-  //      epilogue; k k^T and q k^T ride along.  Two commits: the Y epilogue (all the next MMA needs) runs while
-  //      the tensor core still works on k k^T and q k^T ----
-  if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xdvn, KD), in_kmajor<TMA>(Xv), 64, 64, KD, false);
-    tc::issue_gemm(taddr + 64, tc::kmajor_tile(Xdw, KD), in_kmajor<TMA>(Xk), 64, 64, KD, false);
-    tc::mma_commit(mbar);
-    tc::issue_gemm(taddr + 128, in_kmajor<TMA>(Xk), in_kmajor<TMA>(Xk), 64, 64, KD, false);  // k k^T
-    tc::issue_gemm(taddr + 192, in_kmajor<TMA>(Xq), in_kmajor<TMA>(Xk), 64, 64, KD, false);  // q k^T
-    tc::mma_commit(mbar + 5);
-  }
-  if (ok) {
-    ok = tc::mbar_wait(mbar, ph);
-    ph ^= 1;
-  }
-  tc::fence_after_sync();
-  if (ok) {  // Y[i][m] = beta_m ((T^T dv_new)_i . v_m) + beta_m d_m (z_i . k_m)   -> X2 (v is dead)
-    float f[32], f2[32];
-    ld_acc32(taddr + 0, warp, cb, f);
-    ld_acc32(taddr + 64, warp, cb, f2);
-    if (own) {
-#pragma unroll
-      for (int jj = 0; jj < 32; ++jj) f[jj] = bet[cb + jj] * fmaf(dd[cb + jj], f2[jj], f[jj]);
-#pragma unroll
-      for (int x = 0; x < 4; ++x) sts16(X2, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
-    }
-  }
-  if (ok) ok = tc::mbar_wait(mbar + 5, 0);
-  tc::fence_after_sync();
-  float KKr[32];  // (k_i . k_j) for j in [cb, cb+32)
-  if (ok) {
-    float f[32];
-    ld_acc32(taddr + 192, warp, cb, f);  // q k^T: dgam from P
-    {
-      float rs = 0.f;
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        float e[8];
-        unpack8(*reinterpret_cast<const uint4*>(Xpg + tc::kmajor_unit(i, (cb >> 3) + x, C)), e);
-#pragma unroll
-        for (int y = 0; y < 8; ++y) {
-          const int j = cb + 8 * x + y;
-          const float X = (own && j <= i) ? e[y] * f[8 * x + y] : 0.f;
-          rs += X;
-          f[8 * x + y] = X;
+        for (int jj = 0; jj < 32; ++jj) {
+          const int j = cb + jj;
+          const float val = f[jj] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
+          f[jj] = (j <= i) ? val : 0.f;
         }
-      }
-      dg_own += rs;
-      colsum16(f, lane);  // over the 16 rows this warp owns
-      if (own) {
-        float* dst = csw + (warp & 3) * C + cb + colsum16_col(lane);
-        dst[0] -= f[0];
-        dst[1] -= f[1];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Xpg, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
       }
     }
-    ld_acc32(taddr + 128, warp, cb, KKr);  // k k^T
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {  // dO <- diag(d) dO in place, so that DQ can take dPG k on top later
+      const int u = tid + 256 * m, r = urow16(u);
+      uint4* unit = reinterpret_cast<uint4*>(XdO + tc::sw128_unit(r, ucol16(u)));
+      *unit = tc::scale_bf16x8(*unit, dd[r]);
+    }
   }
+  if (ok) ok = tc::mbar_wait(mbar + 2, 0);  // S0
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  // ---- phase 3: dA = tril(Y T^T, -1) ----
+  // ---- batch 2: DQ = (d dO) S0^T, z = (-e) S0^T ----
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(X2, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
+    tc::issue_gemm(tA, tc::kmajor_sw128_tile(XdO, 8192), tc::kmajor_tile(R1, KD), 64, 128, KD, false);
+    tc::issue_gemm(tB, tc::kmajor_tile(Xe, KD), tc::kmajor_tile(R1, KD), 64, 128, KD, false);
     tc::mma_commit(mbar);
   }
-  if (ok) {  // dv = beta (T^T dv_new), from the bf16 tile, in 64-byte row pieces
+  uint4 s0u[8];  // this thread's 8 units of S0, kept for <dS, S0> (the buffer is about to be reused)
+#pragma unroll
+  for (int x = 0; x < 8; ++x) s0u[x] = *reinterpret_cast<const uint4*>(R1 + (tid + 256 * x) * 16);
+  if (ok) {  // dv = beta e, from the bf16 tile, in 64-byte row pieces
     for (int u = tid; u < 64 * 16; u += 256) {
       const int r = urow16(u), c8 = ucol16(u);
       if (r < imax)
         *reinterpret_cast<uint4*>(p.dv + row(r) * KD + c8 * 8) =
-            tc::scale_bf16x8(*reinterpret_cast<const uint4*>(Xdvn + tc::kmajor_unit(r, c8, KD)), bet[r]);
+            tc::scale_bf16x8(*reinterpret_cast<const uint4*>(Xe + tc::kmajor_unit(r, c8, KD)), -bet[r]);
+    }
+  }
+  tc::fence_async_smem();
+  __syncthreads();  // every thread has taken its units of S0 before the copy engine overwrites the buffer
+  if (ok) ok = tc::mbar_wait(mbar, ph);
+  ph ^= 1;
+  tc::fence_after_sync();
+  if (ok && tid == 0) {  // S0 is dead in shared memory: dS comes into the same buffer behind the epilogue
+    tc::mbar_expect_tx(mbar + 3, 32768);
+    tc::bulk_load(tc::smem_u32(R1), p.dhs + ci * KD * KD, 32768, mbar + 3);
+  }
+  if (ok) {
+    for (int s = 0; s < 2; ++s) {  // z -> bf16 operand over the dead dO tile (blocked layout)
+      const int c0 = cw + 32 * s;
+      float f[32];
+      ld_acc32(tB, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(XdO, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
+      }
+    }
+  }
+  if (ok) ok = tc::mbar_wait(mbar + 3, 0);  // dS
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  // ---- batch 3: v_new dS^T ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(tB, tc::kmajor_tile(Xvn, KD), tc::kmajor_tile(R1, KD), 64, 128, KD, false);
+    tc::mma_commit(mbar);
+  }
+  {  // <dS, S0>
+    float part = 0.f;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+      float a[8], bq[8];
+      unpack8(*reinterpret_cast<const uint4*>(R1 + (tid + 256 * x) * 16), a);
+      unpack8(s0u[x], bq);
+#pragma unroll
+      for (int y = 0; y < 8; ++y) part = fmaf(a[y], bq[y], part);
+    }
+    part = warp_sum(part);
+    if (lane == 0) red[warp] = part;
+  }
+  tc::fence_async_smem();
+  __syncthreads();  // every thread is done with dS before the copy engine overwrites the buffer
+  if (ok) ok = tc::mbar_wait(mbar, ph);
+  ph ^= 1;
+  tc::fence_after_sync();
+  if (ok && tid == 128) {  // v_new and dS are dead: k and v take their places
+    tc::mbar_expect_tx(mbar + 4, 2 * 16384);
+    for (int sl = 0; sl < 2; ++sl) {
+      tc::tma_load_4d(tc::smem_u32(Xk) + 8192 * sl, &maps.k, 64 * sl, h, t0, b, mbar + 4);
+      tc::tma_load_4d(tc::smem_u32(Xvn) + 8192 * sl, &maps.v, 64 * sl, h, t0, b, mbar + 4);
     }
   }
   if (ok) {
-    ok = tc::mbar_wait(mbar, ph);
-    ph ^= 1;
+    for (int s = 0; s < 2; ++s) {  // dkp = r (v_new dS^T), kept as bf16 where dk will be assembled
+      const int c0 = cw + 32 * s;
+      float f[32];
+      ld_acc32(tB, warp, c0, f);
+      if (own) {
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) f[jj] *= ri;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Xdk, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&f[8 * x]));
+      }
+    }
   }
+  if (ok) ok = tc::mbar_wait(mbar + 4, 0);  // k, v
+  tc::fence_before_sync();
+  __syncthreads();
   tc::fence_after_sync();
-  tc::fence_async_smem();
-  __syncthreads();  // every thread is done with the T^T dv_new tile; Y (over v) has been consumed by the MMA
-  // the state contractions from the first kernel land over v and T^T dv_new while phase 3's epilogue runs
-  if (TMA) {
-    if (tid == 0) {
-      tc::mbar_expect_tx(mbar + 3, 2 * 16384);
-      tc::bulk_load(tc::smem_u32(Xv), p.dqp + ci * C * KD, 16384, mbar + 3);
-      tc::bulk_load(tc::smem_u32(Xdvn), p.dkp + ci * C * KD, 16384, mbar + 3);
-    }
-  } else {
-    const uint32_t sqp = tc::smem_u32(Xv), skp = tc::smem_u32(Xdvn);
-    for (int u = tid; u < 64 * 16; u += 256) {
-      tc::cp_async16(sqp + 16 * u, p.dqp + ci * C * KD + 8 * u);
-      tc::cp_async16(skp + 16 * u, p.dkp + ci * C * KD + 8 * u);
-    }
-    tc::cp_async_commit();
+  // ---- batch 4: (-e) v^T and z k^T; their column-scaled sum is Y = T^T dT (dT is never formed) ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(tB, tc::kmajor_tile(Xe, KD), tc::kmajor_sw128_tile(Xvn, 8192), 64, 64, KD, false);
+    tc::issue_gemm(tB + 64, tc::kmajor_tile(XdO, KD), tc::kmajor_sw128_tile(Xk, 8192), 64, 64, KD, false);
+    tc::mma_commit(mbar);
   }
-  if (ok) {  // X1 <- Mb = beta_i M, strictly lower triangle, zeros elsewhere
-    float f[32];
-    ld_acc32(taddr + 0, warp, cb, f);
+  float vdot = 0.f, kz = 0.f;  // e_i . v_i and k_i . z_i over this thread's half of the columns
+  if (ok && own) {
+    vdot = -row_dot_tiles64<false, true>(Xe, Xvn, i, cw);
+    kz = row_dot_tiles64<false, true>(XdO, Xk, i, cw);
+  }
+  if (ok) ok = tc::mbar_wait(mbar, ph);
+  ph ^= 1;
+  tc::fence_after_sync();
+  if (ok) {  // Y[i][m] = beta_m ((e_i . v_m) + d_m (z_i . k_m))
+    float f[32], f2[32];
+    ld_acc32(tB, warp, cb, f);
+    ld_acc32(tB + 64, warp, cb, f2);
+    if (own) {
+#pragma unroll
+      for (int jj = 0; jj < 32; ++jj) f[jj] = bet[cb + jj] * fmaf(dd[cb + jj], f2[jj], -f[jj]);
+#pragma unroll
+      for (int x = 0; x < 4; ++x) sts16(Xy, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
+    }
+  }
+  tc::fence_async_smem();
+  tc::fence_before_sync();
+  __syncthreads();  // also: every thread is done with v
+  tc::fence_after_sync();
+  if (ok && tid == 128) {  // q takes the place of v
+    tc::mbar_expect_tx(mbar + 5, 16384);
+    for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(tc::smem_u32(Xvn) + 8192 * sl, &maps.q, 64 * sl, h, t0, b, mbar + 5);
+  }
+  // ---- batch 5: dA = tril(Y T^T, -1) and k k^T ----
+  if (ok && tid == 0) {
+    tc::issue_gemm(tB, tc::kmajor_tile(Xy, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
+    tc::issue_gemm(tB + 64, tc::kmajor_sw128_tile(Xk, 8192), tc::kmajor_sw128_tile(Xk, 8192), 64, 64, KD, false);
+    tc::mma_commit(mbar);
+  }
+  if (ok) ok = tc::mbar_wait(mbar, ph);
+  ph ^= 1;
+  tc::fence_after_sync();
+  float db_own = 0.f, dg_own = 0.f;
+  if (ok) {  // Xy <- Mb = beta_i M, M = -dA*Gamma strictly lower, zeros elsewhere
+    float f[32], kk[32];
+    ld_acc32(tB, warp, cb, f);
+    ld_acc32(tB + 64, warp, cb, kk);
     float rs = 0.f;
 #pragma unroll
     for (int jj = 0; jj < 32; ++jj) {
       const int j = cb + jj;
       const float mv = -f[jj] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
-      const float M = (own && j < i) ? mv : 0.f;         // -dA * Gamma
-      const float t = M * KKr[jj];
-      rs += t;
-      KKr[jj] = bi * t;
+      const float M = (j < i) ? mv : 0.f;
+      rs = fmaf(M, kk[jj], rs);
       f[jj] = bi * M;
     }
     if (own) {
 #pragma unroll
-      for (int x = 0; x < 4; ++x) sts16(X1, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
-    }
-    db_own += rs;
-    dg_own += bi * rs;
-    colsum16(KKr, lane);
-    if (own) {
-      float* dst = csw + (warp & 3) * C + cb + colsum16_col(lane);
-      dst[0] -= KKr[0];
-      dst[1] -= KKr[1];
+      for (int x = 0; x < 4; ++x) sts16(Xy, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
+      db_own = vdot + di * kz + rs;
+      dg_own = 2.f * bi * (di * kz + rs);
     }
   }
-  if (TMA) { if (ok) ok = tc::mbar_wait(mbar + 3, 0); }
-  else tc::cp_async_wait<0>();
+  if (ok) ok = tc::mbar_wait(mbar + 5, 0);  // q
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  // ---- phase 4: (dP*Gamma) k  and  (dP*Gamma)^T q + (Mb + Mb^T) k ----
+  // ---- batch 6: DQ += dPG k (first commit: the dq epilogue runs while the three products of dk are still on the
+  //      tensor core), then dPG^T q + Mb k + Mb^T k (one tile read K-major and MN-major) ----
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr + 0, tc::kmajor_tile(Xpg, C), in_mnmajor<TMA>(Xk), 64, 128, C, false);
-    tc::mma_commit(mbar);  // the dq epilogue runs while the three products of dk are still on the tensor core
-    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(Xpg, C), in_mnmajor<TMA>(Xq), 64, 128, C, false);
-    tc::issue_gemm(taddr + 128, tc::kmajor_tile(X1, C), in_mnmajor<TMA>(Xk), 64, 128, C, true);
-    tc::issue_gemm(taddr + 128, tc::mnmajor_tile(X1, C), in_mnmajor<TMA>(Xk), 64, 128, C, true);
-    tc::mma_commit(mbar + 5);
+    tc::issue_gemm(tA, tc::kmajor_tile(Xpg, C), tc::mnmajor_sw128_tile(Xk, 8192), 64, 128, C, true);
+    tc::mma_commit(mbar);
+    tc::issue_gemm(tB, tc::mnmajor_tile(Xpg, C), tc::mnmajor_sw128_tile(Xvn, 8192), 64, 128, C, false);
+    tc::issue_gemm(tB, tc::kmajor_tile(Xy, C), tc::mnmajor_sw128_tile(Xk, 8192), 64, 128, C, true);
+    tc::issue_gemm(tB, tc::mnmajor_tile(Xy, C), tc::mnmajor_sw128_tile(Xk, 8192), 64, 128, C, true);
+    tc::mma_commit(mbar + 6);
   }
-  if (ok) {
-    ok = tc::mbar_wait(mbar, ph);
-    ph ^= 1;
-  }
+  if (ok) ok = tc::mbar_wait(mbar, ph);
+  ph ^= 1;
   tc::fence_after_sync();
-  // dq and dk are assembled over the dqp / dkp images (each thread rewrites the units it read)
-  float qdot = 0.f, kdot = 0.f;
-  if (ok) {
+  if (ok) {  // dq: into the swizzled tile the copy engine stores from (the -e tile is dead)
+    float qd = 0.f;
     for (int s = 0; s < 2; ++s) {
       const int c0 = cw + 32 * s;
-      float f[32], g2[32];
-      ld_acc32(taddr + 0, warp, c0, g2);  // (dP*Gamma) k
+      float f[32];
+      ld_acc32(tA, warp, c0, f);
       if (own) {
+        qd += row_dot32<true>(Xvn, i, c0, f);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          float e[8];
-          unpack8(*reinterpret_cast<const uint4*>(Xv + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), e);
-#pragma unroll
-          for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
-        }
-        qdot += row_dot32<TMA>(Xq, i, c0, f);  // q_i . d_i dqi_i
-#pragma unroll
-        for (int jj = 0; jj < 32; ++jj) g2[jj] += f[jj];
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xv, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&g2[8 * x]));
+        for (int x = 0; x < 4; ++x) sts16(Xe, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&f[8 * x]));
       }
     }
+    dg_own += qd;
   }
-  if (ok) ok = tc::mbar_wait(mbar + 5, 1);
+  if (ok) ok = tc::mbar_wait(mbar + 6, 0);
   tc::fence_after_sync();
-  if (ok) {
+  float rho = 0.f;
+  if (ok) {  // dk = dkp + (dPG^T q + (Mb + Mb^T) k) + beta d z, assembled over dkp (each thread rewrites the units it read)
+    float kd = 0.f;
     for (int s = 0; s < 2; ++s) {
       const int c0 = cw + 32 * s;
       float f[32], g2[32];
-      ld_acc32(taddr + 128, warp, c0, g2);  // (dP*Gamma)^T q + (Mb+Mb^T) k
+      ld_acc32(tB, warp, c0, g2);
       if (own) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float e[8];
-          unpack8(*reinterpret_cast<const uint4*>(Xdvn + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), e);
+          unpack8(*reinterpret_cast<const uint4*>(Xdk + tc::sw128_unit(i, (c0 >> 3) + x)), e);
 #pragma unroll
           for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
         }
-        kdot += row_dot32<TMA>(Xk, i, c0, f);  // k_i . r_i dkt_i
+        rho += row_dot32<true>(Xk, i, c0, f);  // k_i . dkp_i
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
           float z[8];
-          unpack8(*reinterpret_cast<const uint4*>(Xdw + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), z);
+          unpack8(*reinterpret_cast<const uint4*>(XdO + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), z);
 #pragma unroll
           for (int y = 0; y < 8; ++y) g2[8 * x + y] += f[8 * x + y] + bd_i * z[y];
         }
+        kd += row_dot32<true>(Xk, i, c0, g2);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xdvn, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&g2[8 * x]));
+        for (int x = 0; x < 4; ++x) sts16(Xdk, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&g2[8 * x]));
       }
     }
-    {
-      const float rho = own ? kdot : 0.f;
-      if (own) dg_own += qdot - rho;
-      const float tot = warp_sum(rho);
-      if (lane == 0) red[8 + warp] = tot;  // summed in a fixed order at the end (deterministic)
-    }
+    dg_own -= kd;
   }
-  (void)ri;
+  {
+    const float tot = warp_sum(own ? rho : 0.f);
+    if (lane == 0) red[8 + warp] = tot;  // summed in a fixed order below (deterministic)
+  }
   if (own) {  // the two column halves hold partial sums of the same row
     dgo[hc * C + i] = dg_own;
     dbo[hc * C + i] = db_own;
   }
+  tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
-  if (ok) {  // dq, dk leave in 64-byte row pieces
-    for (int u = tid; u < 64 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
-      if (r < imax) {
-        const uint32_t off = tc::kmajor_unit(r, c8, KD);
-        *reinterpret_cast<uint4*>(p.dq + row(r) * KD + c8 * 8) = *reinterpret_cast<const uint4*>(Xv + off);
-        *reinterpret_cast<uint4*>(p.dk + row(r) * KD + c8 * 8) = *reinterpret_cast<const uint4*>(Xdvn + off);
-      }
+  if (ok && tid == 64) {  // dq and dk leave by tiled stores (rows past the end of the sequence are clipped)
+    for (int sl = 0; sl < 2; ++sl) {
+      tc::tma_store_4d(&maps.dq, tc::smem_u32(Xe) + 8192 * sl, 64 * sl, h, t0, b);
+      tc::tma_store_4d(&maps.dk, tc::smem_u32(Xdk) + 8192 * sl, 64 * sl, h, t0, b);
     }
+    tc::bulk_commit();
   }
   if (tid < 32) {  // dg = reverse cumulative sum of dgam within the chunk: one warp, two rows per lane
-    // d/dgam_last: E(gam_last) <dS, S0> (from the first kernel) and the sum of rho over the rows
-    float base = p.ls[ci];
-    for (int wv = 0; wv < 8; ++wv) base += red[8 + wv];
+    // d/dgam_last: E(gam_last) <dS, S0> and the sum over the rows of k_i . dkp_i
+    float base = 0.f, kp = 0.f;
+    for (int wv = 0; wv < 8; ++wv) { base += red[wv]; kp += red[8 + wv]; }
+    base = L * base + kp;
     const int ra = C - 1 - 2 * tid, rb = ra - 1;
-    float a = dgo[ra] + dgo[C + ra] + csw[ra] + csw[C + ra] + csw[2 * C + ra] + csw[3 * C + ra];
-    float bq = dgo[rb] + dgo[C + rb] + csw[rb] + csw[C + rb] + csw[2 * C + rb] + csw[3 * C + rb];
+    float a = dgo[ra] + dgo[C + ra];
+    float bq = dgo[rb] + dgo[C + rb];
     warp_rcumsum64(a, bq, tid);
     __syncwarp();  // every lane has read its rows before any lane overwrites them
     dgo[ra] = base + a;
@@ -915,7 +705,10 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     }
     p.dgate[row(tid)] = dg;
   }
-  if (warp == 0) tc::tmem_dealloc(taddr, 256);
+  if (tid == 64) tc::bulk_wait_read<0>();  // shared memory must outlive the stores
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(tA, 256);
 }
 
 // ------------------------------------------------------------------ host
@@ -958,26 +751,19 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
   }
   s = check_launch("gdn_tc_state_bwd_kernel");
   if (s != MXB_OK) return s;
-  if (tma) {
-    if (bwd_set_smem(gdn_tc_chunk_bwd_state_kernel<true>, kChunkBwdStateSmem) != MXB_OK) return MXB_ERR_CUDA;
-    MXB_LAUNCH("gdn_tc_chunk_bwd_state_kernel", st,
-               (gdn_tc_chunk_bwd_state_kernel<true><<<dim3(p.n, p.B * p.H), 256, kChunkBwdStateSmem, st>>>(p, maps)));
-  } else {
-    if (bwd_set_smem(gdn_tc_chunk_bwd_state_kernel<false>, kChunkBwdStateSmem) != MXB_OK) return MXB_ERR_CUDA;
-    MXB_LAUNCH("gdn_tc_chunk_bwd_state_kernel", st,
-               (gdn_tc_chunk_bwd_state_kernel<false><<<dim3(p.n, p.B * p.H), 256, kChunkBwdStateSmem, st>>>(p, maps)));
+  // The chunk kernel is fed and drained by the copy engine only (also under MXB_GDN_NO_TMA, which selects the
+  // per-thread staging of the kernels that have one): it needs the tensor maps.
+  if (!tma) {
+    std::memset(&maps, 0, sizeof maps);
+    if (!(make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, KD) &&
+          make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, KD)))
+      return MXB_ERR_UNSUPPORTED;
   }
-  s = check_launch("gdn_tc_chunk_bwd_state_kernel");
-  if (s != MXB_OK) return s;
-  if (tma) {
-    if (bwd_set_smem(gdn_tc_chunk_bwd_kernel<true>, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
-    MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
-               (gdn_tc_chunk_bwd_kernel<true><<<dim3(p.n, p.B * p.H), 256, kChunkBwdSmem, st>>>(p, maps)));
-  } else {
-    if (bwd_set_smem(gdn_tc_chunk_bwd_kernel<false>, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
-    MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
-               (gdn_tc_chunk_bwd_kernel<false><<<dim3(p.n, p.B * p.H), 256, kChunkBwdSmem, st>>>(p, maps)));
-  }
+  if (!(make_tma_map_bthd(&maps.dq, p.dq, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.dk, p.dk, p.B, p.T, p.H, KD)))
+    return MXB_ERR_UNSUPPORTED;
+  if (bwd_set_smem(gdn_tc_chunk_bwd_kernel, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
+  MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,
+             (gdn_tc_chunk_bwd_kernel<<<dim3(p.B * p.H, p.n), 256, kChunkBwdSmem, st>>>(p, maps)));
   return check_launch("gdn_tc_chunk_bwd_kernel");
 }
 
