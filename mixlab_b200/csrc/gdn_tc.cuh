@@ -45,9 +45,9 @@ struct TcP {
 
 // Tensor maps of the token-indexed operands: [B,T,H,128] bf16 viewed as (D, H, T, B), boxes of 64 columns x
 // 64 time steps with 128-byte swizzle; rows past the end of the sequence are zero-filled by the copy engine.
-// o, dq, dk: results written back by tiled stores (rows past the end of the sequence are clipped).
+// o, dq, dk, dv: results written back by tiled stores (rows past the end of the sequence are clipped).
 struct alignas(64) RowMaps {
-  CUtensorMap k, q, v, dO, o, dq, dk;
+  CUtensorMap k, q, v, dO, o, dq, dk, dv;
 };
 
 // Views of a [64][128] tile for tcgen05 and for 16-byte unit access: written by the copy engine with 128-byte
@@ -88,6 +88,24 @@ __device__ __forceinline__ void ld_acc32(uint32_t taddr, int warp, int c0, float
   tc::tmem_ld_wait();
 #pragma unroll
   for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+}
+// Two blocks of 32 accumulator columns [c0, c0+32), [c0+32, c0+64) of this thread's TMEM lane, the second load in
+// flight while the first block is processed: process(column of the block, values).
+template <typename F>
+__device__ __forceinline__ void for_acc2x32(uint32_t taddr, int warp, int c0, F&& process) {
+  uint32_t r0[32], r1[32];
+  const uint32_t base = taddr + ((uint32_t)(32 * (warp & 3)) << 16) + (uint32_t)c0;
+  tc::tmem_ld_32x32b_x32(base, r0);
+  tc::tmem_ld_wait();
+  tc::tmem_ld_32x32b_x32(base + 32u, r1);
+  float f[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r0[i]);
+  process(c0, f);
+  tc::tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r1[i]);
+  process(c0 + 32, f);
 }
 // Loads 64 fp32 accumulator columns [0, 64) at taddr of this thread's TMEM lane: both loads in flight, one wait.
 __device__ __forceinline__ void ld_acc64(uint32_t taddr, int warp, float (&f)[64]) {

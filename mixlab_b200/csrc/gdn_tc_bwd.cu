@@ -281,8 +281,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
 // dPG and Mb, so they need no products of their own).
 //
 // 256 TMEM columns and 107 KB of shared memory: two CTAs share an SM.  Every buffer is reused as soon as it is dead:
-//   XdO   dO (TMA tile) -> d dO -> z                      Xe   -dv_new image -> -e -> ... -> the dq tile on its way out
-//   Xvn   v_new image -> v (TMA) -> q (TMA)               R1   S0 image -> dS image -> k (TMA) | dkp -> the dk tile
+//   XdO   dO (TMA tile) -> d dO -> z                      Xe   -dv_new image -> -e -> dv = beta e on its way out
+//   Xvn   v_new image -> v (TMA) -> q (TMA) -> dq         R1   S0 image -> dS image -> k (TMA) | dkp -> dk
 // TMEM: [0,128) -e, then DQ until the end; [128,256) the other products one after the other.  All accumulators are
 // M=64: row i sits in TMEM lane (i%16) + 32*(i/16) and is handled by thread (warp i/16, lane i%16); warps 4-7 take
 // the second half of the columns.  Grid = (batch*head, chunk) with batch*head fastest: neighbouring CTAs read
@@ -315,12 +315,12 @@ __device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, c
   }
   return (s[0] + s[1]) + (s[2] + s[3]);
 }
-// sum over 64 columns [c0, c0+64) of a[row][.] * b[row][.] for two [64][128] bf16 tiles in shared memory
+// sum over 32 columns [c0, c0+32) of a[row][.] * b[row][.] for two [64][128] bf16 tiles in shared memory
 template <bool SWA, bool SWB>
-__device__ __forceinline__ float row_dot_tiles64(const uint8_t* a, const uint8_t* b, int r, int c0) {
+__device__ __forceinline__ float row_dot_tiles32(const uint8_t* a, const uint8_t* b, int r, int c0) {
   float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-  for (int x = 0; x < 8; ++x) {
+  for (int x = 0; x < 4; ++x) {
     float ea[8], eb[8];
     unpack8(*reinterpret_cast<const uint4*>(a + in_unit<SWA>(r, (c0 >> 3) + x)), ea);
     unpack8(*reinterpret_cast<const uint4*>(b + in_unit<SWB>(r, (c0 >> 3) + x)), eb);
@@ -334,8 +334,8 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
   uint8_t* XdO = sm;                // [64][128] dO (swizzled TMA tile), d dO in place, then z (blocked layout)
-  uint8_t* Xe = XdO + 16384;        // [64][128] -dv_new image, then -e in place (blocked), at the end the dq tile (swizzled)
-  uint8_t* Xvn = Xe + 16384;        // [64][128] v_new image, then v, then q (swizzled TMA tiles)
+  uint8_t* Xe = XdO + 16384;        // [64][128] -dv_new image (blocked), then -e and finally dv (swizzled like a TMA tile)
+  uint8_t* Xvn = Xe + 16384;        // [64][128] v_new image, then v, then q (swizzled TMA tiles), then dq in place
   uint8_t* R1 = Xvn + 16384;        // [128][128] S0 image, then dS image, then k (swizzled TMA tile) | dkp -> dk (swizzled)
   uint8_t* Xk = R1;
   uint8_t* Xdk = R1 + 16384;
@@ -376,6 +376,13 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     for (int sl = 0; sl < 2; ++sl) tc::tma_load_4d(tc::smem_u32(XdO) + 8192 * sl, &maps.dO, 64 * sl, h, t0, b, mbar + 1);
     tc::mbar_expect_tx(mbar + 2, 32768);
     tc::bulk_load(tc::smem_u32(R1), p.hs + ci * KD * KD, 32768, mbar + 2);
+    // the operands whose buffers are still occupied are pulled into L2 now, so that their copies find them on chip
+    tc::bulk_prefetch_l2(p.dhs + ci * KD * KD, 32768);
+    for (int sl = 0; sl < 2; ++sl) {
+      tc::tma_prefetch_4d(&maps.k, 64 * sl, h, t0, b);
+      tc::tma_prefetch_4d(&maps.v, 64 * sl, h, t0, b);
+      tc::tma_prefetch_4d(&maps.q, 64 * sl, h, t0, b);
+    }
   }
   if (warp == 0) {
     tc::tmem_alloc(tslot, 256);
@@ -410,15 +417,14 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   ph ^= 1;
   tc::fence_after_sync();
   if (ok) {
-    for (int s = 0; s < 2; ++s) {  // -e goes back over the operand it was computed from (its MMA is complete)
-      const int c0 = cw + 32 * s;
-      float f[32];
-      ld_acc32(tA, warp, c0, f);
+    // -e goes back over the operand it was computed from (its MMA is complete), in the swizzled layout of a TMA
+    // tile: scaled by -beta in place later, the same bytes leave as dv through a tiled store
+    for_acc2x32(tA, warp, cw, [&](int c0, const float (&f)[32]) {
       if (own) {
 #pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xe, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
+        for (int x = 0; x < 4; ++x) sts16(Xe, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&f[8 * x]));
       }
-    }
+    });
     {  // dP * Gamma, lower triangle incl. diagonal
       float f[32];
       ld_acc32(tB, warp, cb, f);
@@ -448,20 +454,12 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   // ---- batch 2: DQ = (d dO) S0^T, z = (-e) S0^T ----
   if (ok && tid == 0) {
     tc::issue_gemm(tA, tc::kmajor_sw128_tile(XdO, 8192), tc::kmajor_tile(R1, KD), 64, 128, KD, false);
-    tc::issue_gemm(tB, tc::kmajor_tile(Xe, KD), tc::kmajor_tile(R1, KD), 64, 128, KD, false);
-    tc::mma_commit(mbar);
+    tc::issue_gemm(tB, tc::kmajor_sw128_tile(Xe, 8192), tc::kmajor_tile(R1, KD), 64, 128, KD, false);
+    tc::mma_commit(mbar);  // one commit: z overwrites d dO and dS overwrites S0, which DQ reads as well
   }
   uint4 s0u[8];  // this thread's 8 units of S0, kept for <dS, S0> (the buffer is about to be reused)
 #pragma unroll
   for (int x = 0; x < 8; ++x) s0u[x] = *reinterpret_cast<const uint4*>(R1 + (tid + 256 * x) * 16);
-  if (ok) {  // dv = beta e, from the bf16 tile, in 64-byte row pieces
-    for (int u = tid; u < 64 * 16; u += 256) {
-      const int r = urow16(u), c8 = ucol16(u);
-      if (r < imax)
-        *reinterpret_cast<uint4*>(p.dv + row(r) * KD + c8 * 8) =
-            tc::scale_bf16x8(*reinterpret_cast<const uint4*>(Xe + tc::kmajor_unit(r, c8, KD)), -bet[r]);
-    }
-  }
   tc::fence_async_smem();
   __syncthreads();  // every thread has taken its units of S0 before the copy engine overwrites the buffer
   if (ok) ok = tc::mbar_wait(mbar, ph);
@@ -472,15 +470,12 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     tc::bulk_load(tc::smem_u32(R1), p.dhs + ci * KD * KD, 32768, mbar + 3);
   }
   if (ok) {
-    for (int s = 0; s < 2; ++s) {  // z -> bf16 operand over the dead dO tile (blocked layout)
-      const int c0 = cw + 32 * s;
-      float f[32];
-      ld_acc32(tB, warp, c0, f);
+    for_acc2x32(tB, warp, cw, [&](int c0, const float (&f)[32]) {  // z -> bf16 operand over the dead dO tile (blocked layout)
       if (own) {
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(XdO, tc::kmajor_unit(i, (c0 >> 3) + x, KD), pack8(&f[8 * x]));
       }
-    }
+    });
   }
   if (ok) ok = tc::mbar_wait(mbar + 3, 0);  // dS
   tc::fence_async_smem();
@@ -518,17 +513,14 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     }
   }
   if (ok) {
-    for (int s = 0; s < 2; ++s) {  // dkp = r (v_new dS^T), kept as bf16 where dk will be assembled
-      const int c0 = cw + 32 * s;
-      float f[32];
-      ld_acc32(tB, warp, c0, f);
+    for_acc2x32(tB, warp, cw, [&](int c0, float (&f)[32]) {  // dkp = r (v_new dS^T), kept as bf16 where dk will be assembled
       if (own) {
 #pragma unroll
         for (int jj = 0; jj < 32; ++jj) f[jj] *= ri;
 #pragma unroll
         for (int x = 0; x < 4; ++x) sts16(Xdk, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&f[8 * x]));
       }
-    }
+    });
   }
   if (ok) ok = tc::mbar_wait(mbar + 4, 0);  // k, v
   tc::fence_before_sync();
@@ -536,14 +528,19 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   tc::fence_after_sync();
   // ---- batch 4: (-e) v^T and z k^T; their column-scaled sum is Y = T^T dT (dT is never formed) ----
   if (ok && tid == 0) {
-    tc::issue_gemm(tB, tc::kmajor_tile(Xe, KD), tc::kmajor_sw128_tile(Xvn, 8192), 64, 64, KD, false);
+    tc::issue_gemm(tB, tc::kmajor_sw128_tile(Xe, 8192), tc::kmajor_sw128_tile(Xvn, 8192), 64, 64, KD, false);
     tc::issue_gemm(tB + 64, tc::kmajor_tile(XdO, KD), tc::kmajor_sw128_tile(Xk, 8192), 64, 64, KD, false);
     tc::mma_commit(mbar);
   }
-  float vdot = 0.f, kz = 0.f;  // e_i . v_i and k_i . z_i over this thread's half of the columns
-  if (ok && own) {
-    vdot = -row_dot_tiles64<false, true>(Xe, Xvn, i, cw);
-    kz = row_dot_tiles64<false, true>(XdO, Xk, i, cw);
+  // e_i . v_i and k_i . z_i over this thread's half of the columns: both operands are in shared memory, so all 32
+  // lanes work (lane l and lane l + 16 take 32 columns each of row i)
+  float vdot = 0.f, kz = 0.f;
+  if (ok) {
+    const int cq = cw + 32 * (lane >> 4);
+    vdot = -row_dot_tiles32<true, true>(Xe, Xvn, i, cq);
+    kz = row_dot_tiles32<false, true>(XdO, Xk, i, cq);
+    vdot += __shfl_xor_sync(0xffffffffu, vdot, 16);
+    kz += __shfl_xor_sync(0xffffffffu, kz, 16);
   }
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
@@ -572,6 +569,14 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     tc::issue_gemm(tB, tc::kmajor_tile(Xy, C), tc::kmajor_tile(Xt, C), 64, 64, C, false);
     tc::issue_gemm(tB + 64, tc::kmajor_sw128_tile(Xk, 8192), tc::kmajor_sw128_tile(Xk, 8192), 64, 64, KD, false);
     tc::mma_commit(mbar);
+  }
+  if (ok) {  // -e has served as an operand and in the row dots for the last time (barrier above): dv = beta e in place
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int u = tid + 256 * m, r = urow16(u);
+      uint4* unit = reinterpret_cast<uint4*>(Xe + tc::sw128_unit(r, ucol16(u)));
+      *unit = tc::scale_bf16x8(*unit, -bet[r]);
+    }
   }
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
@@ -602,32 +607,15 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  // ---- batch 6: DQ += dPG k (first commit: the dq epilogue runs while the three products of dk are still on the
-  //      tensor core), then dPG^T q + Mb k + Mb^T k (one tile read K-major and MN-major) ----
+  // ---- batch 6: dPG^T q + Mb k + Mb^T k (one tile read K-major and MN-major), committed first: the dk epilogue
+  //      runs while DQ += dPG k is still on the tensor core ----
   if (ok && tid == 0) {
-    tc::issue_gemm(tA, tc::kmajor_tile(Xpg, C), tc::mnmajor_sw128_tile(Xk, 8192), 64, 128, C, true);
-    tc::mma_commit(mbar);
     tc::issue_gemm(tB, tc::mnmajor_tile(Xpg, C), tc::mnmajor_sw128_tile(Xvn, 8192), 64, 128, C, false);
     tc::issue_gemm(tB, tc::kmajor_tile(Xy, C), tc::mnmajor_sw128_tile(Xk, 8192), 64, 128, C, true);
     tc::issue_gemm(tB, tc::mnmajor_tile(Xy, C), tc::mnmajor_sw128_tile(Xk, 8192), 64, 128, C, true);
     tc::mma_commit(mbar + 6);
-  }
-  if (ok) ok = tc::mbar_wait(mbar, ph);
-  ph ^= 1;
-  tc::fence_after_sync();
-  if (ok) {  // dq: into the swizzled tile the copy engine stores from (the -e tile is dead)
-    float qd = 0.f;
-    for (int s = 0; s < 2; ++s) {
-      const int c0 = cw + 32 * s;
-      float f[32];
-      ld_acc32(tA, warp, c0, f);
-      if (own) {
-        qd += row_dot32<true>(Xvn, i, c0, f);
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xe, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&f[8 * x]));
-      }
-    }
-    dg_own += qd;
+    tc::issue_gemm(tA, tc::kmajor_tile(Xpg, C), tc::mnmajor_sw128_tile(Xk, 8192), 64, 128, C, true);
+    tc::mma_commit(mbar);
   }
   if (ok) ok = tc::mbar_wait(mbar + 6, 0);
   tc::fence_after_sync();
@@ -636,30 +624,48 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     float kd = 0.f;
     for (int s = 0; s < 2; ++s) {
       const int c0 = cw + 32 * s;
-      float f[32], g2[32];
+      float g2[32];
       ld_acc32(tB, warp, c0, g2);
       if (own) {
+        float r4[4] = {0.f, 0.f, 0.f, 0.f}, k4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-          float e[8];
-          unpack8(*reinterpret_cast<const uint4*>(Xdk + tc::sw128_unit(i, (c0 >> 3) + x)), e);
+          const int c8 = (c0 >> 3) + x;
+          float e[8], z[8], kr[8];
+          unpack8(*reinterpret_cast<const uint4*>(Xdk + tc::sw128_unit(i, c8)), e);
+          unpack8(*reinterpret_cast<const uint4*>(XdO + tc::kmajor_unit(i, c8, KD)), z);
+          unpack8(*reinterpret_cast<const uint4*>(Xk + tc::sw128_unit(i, c8)), kr);
 #pragma unroll
-          for (int y = 0; y < 8; ++y) f[8 * x + y] = e[y];
+          for (int y = 0; y < 8; ++y) {
+            r4[x] = fmaf(kr[y], e[y], r4[x]);              // k_i . dkp_i
+            const float val = g2[8 * x + y] + e[y] + bd_i * z[y];
+            k4[x] = fmaf(kr[y], val, k4[x]);               // k_i . dk_i
+            g2[8 * x + y] = val;
+          }
+          sts16(Xdk, tc::sw128_unit(i, c8), pack8(&g2[8 * x]));
         }
-        rho += row_dot32<true>(Xk, i, c0, f);  // k_i . dkp_i
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          float z[8];
-          unpack8(*reinterpret_cast<const uint4*>(XdO + tc::kmajor_unit(i, (c0 >> 3) + x, KD)), z);
-#pragma unroll
-          for (int y = 0; y < 8; ++y) g2[8 * x + y] += f[8 * x + y] + bd_i * z[y];
-        }
-        kd += row_dot32<true>(Xk, i, c0, g2);
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xdk, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&g2[8 * x]));
+        rho += (r4[0] + r4[1]) + (r4[2] + r4[3]);
+        kd += (k4[0] + k4[1]) + (k4[2] + k4[3]);
       }
     }
     dg_own -= kd;
+  }
+  if (ok) ok = tc::mbar_wait(mbar, ph);  // every product has completed
+  ph ^= 1;
+  tc::fence_after_sync();
+  if (ok) {  // dq, assembled over q (each thread rewrites the units it read)
+    float qd = 0.f;
+    for (int s = 0; s < 2; ++s) {
+      const int c0 = cw + 32 * s;
+      float f[32];
+      ld_acc32(tA, warp, c0, f);
+      if (own) {
+        qd += row_dot32<true>(Xvn, i, c0, f);
+#pragma unroll
+        for (int x = 0; x < 4; ++x) sts16(Xvn, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&f[8 * x]));
+      }
+    }
+    dg_own += qd;
   }
   {
     const float tot = warp_sum(own ? rho : 0.f);
@@ -672,10 +678,11 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
-  if (ok && tid == 64) {  // dq and dk leave by tiled stores (rows past the end of the sequence are clipped)
+  if (ok && tid == 64) {  // dq, dk and dv leave by tiled stores (rows past the end of the sequence are clipped)
     for (int sl = 0; sl < 2; ++sl) {
-      tc::tma_store_4d(&maps.dq, tc::smem_u32(Xe) + 8192 * sl, 64 * sl, h, t0, b);
+      tc::tma_store_4d(&maps.dq, tc::smem_u32(Xvn) + 8192 * sl, 64 * sl, h, t0, b);
       tc::tma_store_4d(&maps.dk, tc::smem_u32(Xdk) + 8192 * sl, 64 * sl, h, t0, b);
+      tc::tma_store_4d(&maps.dv, tc::smem_u32(Xe) + 8192 * sl, 64 * sl, h, t0, b);
     }
     tc::bulk_commit();
   }
@@ -759,7 +766,8 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
           make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, KD)))
       return MXB_ERR_UNSUPPORTED;
   }
-  if (!(make_tma_map_bthd(&maps.dq, p.dq, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.dk, p.dk, p.B, p.T, p.H, KD)))
+  if (!(make_tma_map_bthd(&maps.dq, p.dq, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.dk, p.dk, p.B, p.T, p.H, KD) &&
+        make_tma_map_bthd(&maps.dv, p.dv, p.B, p.T, p.H, KD)))
     return MXB_ERR_UNSUPPORTED;
   if (bwd_set_smem(gdn_tc_chunk_bwd_kernel, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,

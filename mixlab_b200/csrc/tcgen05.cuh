@@ -141,6 +141,17 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap,
       : "memory");
 }
 
+// Prefetches of a tile / a contiguous range into L2 (no completion to wait for): issued early for operands whose
+// shared-memory buffer is still occupied, so that the later copy finds its bytes on chip.
+__device__ __forceinline__ void tma_prefetch_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(reinterpret_cast<uint64_t>(tmap)),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
 // Tiled tensor copy shared -> global (bulk async-group completion); elements outside the tensor are not written.
 __device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
