@@ -6,7 +6,8 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libmixlab_b200.so")
+# MIXLAB_B200_LIB selects another build of the same library (same exports), e.g. to compare two builds
+LIB_PATH = os.environ.get("MIXLAB_B200_LIB") or os.path.join(_PKG, "libmixlab_b200.so")
 
 MXB_F32, MXB_BF16 = 1, 2
 MXB_GDN_FORCE_FP32_PATH = 1

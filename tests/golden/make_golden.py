@@ -14,7 +14,8 @@ Sources used (paths inside the reference checkout):
   experiments/gated_deltanet_reference/generate_fixtures.py   scalar GDN block + scan
   experiments/mamba3_reference/generate_fixtures.py           scalar Mamba-3 block + scan
   experiments/gated_deltanet_test/dump_fla_reference_pure.py  torch GDN recurrence
-  train/hf_templates/mamba3_mixlab.py                         torch Mamba-3 scan
+  train/hf_templates/mamba3_mixlab.py                         torch Mamba-3 scan and full canonical block
+  experiments/gated_deltanet_test/dump_fla_grad_reference.py  torch GDN full block, forward + every weight gradient
   train/testdata/gated_deltanet_full_block_reference.json     checked-in expected output
   train/testdata/mamba3_full_block_reference.json             checked-in expected output
   gpu/gated_delta_scan_test.go:44-83                          closed-form test inputs (restated below)
@@ -245,6 +246,49 @@ def mamba3_block_stages(ref: Path):
                             "gpu/ir.cpp:2034-2105 (eps 1e-5), python random.Random(8765) inputs")))
     print("mamba3_block_stages.json:", len(cases), "cases")
 
+def gdn_fla_grad_fixtures(ref: Path):
+    """The reference's own gradient fixture of one full gated_deltanet block (ReferenceStack of
+    dump_fla_reference_pure.py:94-155 driven by dump_fla_grad_reference.py, the generator behind
+    train/gated_deltanet_fla_grad_parity_test.go): input, every weight, the block output and the gradient of
+    mean(y^2) with respect to every weight, with and without kv_share, at the generator's default sizes."""
+    sys.path.insert(0, str(ref / "experiments/gated_deltanet_test"))
+    mod = _load(ref / "experiments/gated_deltanet_test/dump_fla_grad_reference.py", "ref_gdn_grad")
+    for share in (True, False):
+        cfg = mod.Config(model_dim=64, heads=4, d_k=8, d_v=16, seq_len=16, layers=1, kv_share=share, seed=7)
+        name = "gdn_fla_grad_kvshare.npz" if share else "gdn_fla_grad_nokvshare.npz"
+        mod.save_grad_fixture(str(HERE / name), cfg)
+
+
+def mamba3_full_block_torch(ref: Path):
+    """One canonical Mamba-3 block through the reference's own torch module (MixlabMamba3CanonicalBlock of
+    train/hf_templates/mamba3_mixlab.py: pre-norm, projections, causal depthwise conv, B/C norm + bias, scan,
+    post-norm x gate, output projection, residual) in float64: input, every parameter, the output and the gradient of
+    mean(y^2) with respect to every parameter (torch autograd through the module's own code)."""
+    mod = _load(ref / "train/hf_templates/mamba3_mixlab.py", "ref_m3_hf2")
+    torch.manual_seed(21)
+    cfg = types.SimpleNamespace(model_dim=32)
+    blk = mod.MixlabMamba3CanonicalBlock(cfg, dict(inner_dim=32, state_size=16, n_groups=2, dt_rank=2, conv_kernel=4)).double()
+    with torch.no_grad():  # the module's A_log is left uninitialised (torch.empty): give it the documented range
+        blk.A_log.copy_(math.log(16.0) * torch.rand(32, 16, dtype=torch.float64))
+        blk.dt_bias.copy_(-1.0 + 0.5 * torch.randn(32, dtype=torch.float64))
+        for nrm in (blk.pre_norm, blk.B_norm, blk.C_norm, blk.post_norm):
+            nrm.weight.copy_(1.0 + 0.2 * torch.randn_like(nrm.weight))
+        blk.B_bias.copy_(1.0 + 0.3 * torch.randn_like(blk.B_bias))
+        blk.C_bias.copy_(1.0 + 0.3 * torch.randn_like(blk.C_bias))
+    B, T = 2, 24
+    x = torch.randn(B, T, 32, dtype=torch.float64)
+    y = blk(x)
+    loss = y.pow(2).mean()
+    loss.backward()
+    out = dict(input=x.numpy(), output=y.detach().numpy(), loss=np.array([loss.item()]),
+               dims=np.array([B, T, 32, 32, 16, 2, 2, 4], dtype=np.int64))  # B, T, model, inner, state, groups, rank, K
+    for name, prm in blk.named_parameters():
+        out["w:" + name] = prm.detach().numpy()
+        out["g:" + name] = prm.grad.detach().numpy()
+    np.savez_compressed(HERE / "mamba3_full_block_torch.npz", **out)
+    print("mamba3_full_block_torch.npz", sorted(k for k in out if k.startswith("w:")))
+
+
 def main():
     if len(sys.argv) < 2:
         sys.exit("usage: make_golden.py /path/to/reference-checkout")
@@ -256,6 +300,8 @@ def main():
     mamba3_block_fixture(ref)
     mamba3_block_stages(ref)
     mamba3_torch_scan(ref)
+    gdn_fla_grad_fixtures(ref)
+    mamba3_full_block_torch(ref)
 
 
 if __name__ == "__main__":
