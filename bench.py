@@ -413,6 +413,55 @@ def time_workload(cx, wl, steps, warmup):
     return dict(ms_step=ms_step, value=value, launches=launches, clocks=clocks, roofline=roofline)
 
 
+def dp_allreduce_leg(cx, steps=5, warmup=2):
+    """The gradient exchange of the end-to-end training configuration (12 layers, d_model 1024, vocab 32768: about
+    1.07 GB of fp32 gradients) on this job's ranks: bucket plan of 32 MiB buckets, staged all-reduce (bad flag and
+    denominator packed into the last bucket), NCCL on a communication stream.  Reports the whole staged step and
+    the all-reduces alone; bus bandwidth = 2 (N-1)/N x bytes / time."""
+    import torch.distributed as dist
+    from mixlab_b200 import dp
+    plan = dp.build_gradient_bucket_plan(dp.hybrid_lm_weight_shapes())
+    store = dp.BucketStorage(plan, cx.dev)
+    g = torch.Generator(device=cx.dev).manual_seed(7 + cx.rank)
+    for buf in store.flat:
+        buf.normal_(generator=g)
+    comm = torch.cuda.Stream(cx.dev)
+    loss = torch.ones((), device=cx.dev)
+
+    def staged():
+        grads = list(store.views)
+        return dp.staged_gradient_allreduce(grads, loss, 1.0, True, 1.0, plan, storage=store, comm_stream=comm)
+
+    def bare():
+        works = [dist.all_reduce(buf, async_op=True) for buf in store.flat]
+        for w in works:
+            w.wait()
+
+    out = {}
+    for name, fn in (("staged_step", staged), ("allreduce_only", bare)):
+        for _ in range(warmup):
+            fn()
+            for buf in store.flat:   # keep the values bounded across repeated sums
+                buf.mul_(1.0 / cx.world)
+        cx.barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        cx.barrier()
+        ms = cx.sharding.max_over_ranks(ev0.elapsed_time(ev1) / steps, cx.dev)
+        nbytes = sum(b.numel() * 4 for b in store.flat)
+        out[name] = {"ms": ms, "bus_gbs": 2.0 * (cx.world - 1) / cx.world * nbytes / (ms * 1e-3) / 1e9,
+                     "alg_gbs": nbytes / (ms * 1e-3) / 1e9}
+    out.update(bytes=plan.total_bytes, buckets=len(plan.buckets), bucket_target_bytes=plan.target_bytes,
+               plan_digest=f"{plan.digest:016x}", n_ranks=cx.world,
+               reference_points="measured on this pool: 8-rank all-reduce bus bandwidth 725 GB/s at 1 GiB, peer copy 770 GB/s")
+    del store
+    torch.cuda.empty_cache()
+    return out
+
+
 def copy_floor(cx, host, res, steps):
     """The host<->device traffic of one end-to-end step and nothing else: every input tensor uploaded by one
     cudaMemcpyAsync each on one stream while every result tensor is downloaded on a second stream (pinned host
@@ -538,6 +587,9 @@ def main():
                 extra[name]["hbm_gbs_per_launch"] = w2["alg_bytes"] / tps / (rf["kernels"][rf["top_kernel"]]["avg_ms"] * 1e-3) / 1e9
             del w2
             torch.cuda.empty_cache()
+
+    if extra is not None and world > 1:
+        extra["dp_allreduce"] = dp_allreduce_leg(cx)
 
     e2e = None
     if args.workload == "gdn_train" and not args.no_e2e:

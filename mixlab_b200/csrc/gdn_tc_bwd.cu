@@ -298,23 +298,6 @@ __device__ __forceinline__ uint4 pack8(const float* e) {
   return make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]), tc::pack_bf16(e[4], e[5]),
                     tc::pack_bf16(e[6], e[7]));
 }
-// sum_k tile[row][c0 + k] * f[k], k < 32, for a [64][128] bf16 tile in shared memory (SW: 128-byte-swizzled TMA
-// tile, else the blocked layout): the four units are fetched first and summed in four independent chains
-template <bool SW>
-__device__ __forceinline__ float row_dot32(const uint8_t* tile, int r, int c0, const float (&f)[32]) {
-  uint4 raw[4];
-#pragma unroll
-  for (int x = 0; x < 4; ++x) raw[x] = *reinterpret_cast<const uint4*>(tile + in_unit<SW>(r, (c0 >> 3) + x));
-  float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int x = 0; x < 4; ++x) {
-    float e[8];
-    unpack8(raw[x], e);
-#pragma unroll
-    for (int y = 0; y < 8; ++y) s[x] = fmaf(e[y], f[8 * x + y], s[x]);
-  }
-  return (s[0] + s[1]) + (s[2] + s[3]);
-}
 // sum over 32 columns [c0, c0+32) of a[row][.] * b[row][.] for two [64][128] bf16 tiles in shared memory
 template <bool SWA, bool SWB>
 __device__ __forceinline__ float row_dot_tiles32(const uint8_t* a, const uint8_t* b, int r, int c0) {
@@ -328,6 +311,18 @@ __device__ __forceinline__ float row_dot_tiles32(const uint8_t* a, const uint8_t
     for (int y = 0; y < 8; ++y) s[x & 3] = fmaf(ea[y], eb[y], s[x & 3]);
   }
   return (s[0] + s[1]) + (s[2] + s[3]);
+}
+
+// M=64 accumulators leave lanes 16-31 of every warp without a row.  Where an epilogue does real arithmetic per
+// element, the owning lane l hands columns 16..31 of its 32-column block to lane l + 16: both then work on 16
+// columns of the same row (16 shuffles buy half of the arithmetic).  h[q] = column c0 + 16 (lane >> 4) + q.
+__device__ __forceinline__ void split_block32(const float (&f)[32], int lane, float (&h)[16]) {
+  const bool upper = (lane >> 4) != 0;
+#pragma unroll
+  for (int q = 0; q < 16; ++q) {
+    const float up = __shfl_sync(0xffffffffu, f[16 + q], lane & 15);
+    h[q] = upper ? up : f[q];
+  }
 }
 
 __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const __grid_constant__ RowMaps maps) {
@@ -363,6 +358,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   const int hc = warp >> 2;   // warps 0-3 take the first half of an accumulator's columns, warps 4-7 the second
   const int cb = 32 * hc;     // this thread's 32 columns of every [64][64] accumulator
   const int cw = 64 * hc;     // this thread's 64 columns of every [64][128] accumulator
+  const int hx = lane >> 4;   // which 16 columns of a shared 32-column block this lane works on (split_block32)
 
   // prologue latencies side by side: warp 0 allocates TMEM, one thread of warp 1 initialises the barriers and issues
   // the first copies, warps 2-3 fetch the per-row scalars
@@ -416,6 +412,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
+  ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogues below shuffle with a full mask
   if (ok) {
     // -e goes back over the operand it was computed from (its MMA is complete), in the swizzled layout of a TMA
     // tile: scaled by -beta in place later, the same bytes leave as dv through a tiled store
@@ -426,18 +423,18 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
       }
     });
     {  // dP * Gamma, lower triangle incl. diagonal
-      float f[32];
+      float f[32], hq[16];
       ld_acc32(tB, warp, cb, f);
-      if (own) {
+      split_block32(f, lane, hq);
+      const int j0 = cb + 16 * hx;
 #pragma unroll
-        for (int jj = 0; jj < 32; ++jj) {
-          const int j = cb + jj;
-          const float val = f[jj] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
-          f[jj] = (j <= i) ? val : 0.f;
-        }
-#pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xpg, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
+      for (int q = 0; q < 16; ++q) {
+        const int j = j0 + q;
+        const float val = hq[q] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
+        hq[q] = (j <= i) ? val : 0.f;
       }
+#pragma unroll
+      for (int x = 0; x < 2; ++x) sts16(Xpg, tc::kmajor_unit(i, (j0 >> 3) + x, C), pack8(&hq[8 * x]));
     }
 #pragma unroll
     for (int m = 0; m < 4; ++m) {  // dO <- diag(d) dO in place, so that DQ can take dPG k on top later
@@ -465,6 +462,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
+  ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogues below shuffle with a full mask
   if (ok && tid == 0) {  // S0 is dead in shared memory: dS comes into the same buffer behind the epilogue
     tc::mbar_expect_tx(mbar + 3, 32768);
     tc::bulk_load(tc::smem_u32(R1), p.dhs + ci * KD * KD, 32768, mbar + 3);
@@ -505,6 +503,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
+  ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogues below shuffle with a full mask
   if (ok && tid == 128) {  // v_new and dS are dead: k and v take their places
     tc::mbar_expect_tx(mbar + 4, 2 * 16384);
     for (int sl = 0; sl < 2; ++sl) {
@@ -545,16 +544,18 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
+  ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogues below shuffle with a full mask
   if (ok) {  // Y[i][m] = beta_m ((e_i . v_m) + d_m (z_i . k_m))
-    float f[32], f2[32];
+    float f[32], ha[16], hb[16];
     ld_acc32(tB, warp, cb, f);
-    ld_acc32(tB + 64, warp, cb, f2);
-    if (own) {
+    split_block32(f, lane, ha);
+    ld_acc32(tB + 64, warp, cb, f);
+    split_block32(f, lane, hb);
+    const int j0 = cb + 16 * hx;
 #pragma unroll
-      for (int jj = 0; jj < 32; ++jj) f[jj] = bet[cb + jj] * fmaf(dd[cb + jj], f2[jj], -f[jj]);
+    for (int q = 0; q < 16; ++q) ha[q] = bet[j0 + q] * fmaf(dd[j0 + q], hb[q], -ha[q]);
 #pragma unroll
-      for (int x = 0; x < 4; ++x) sts16(Xy, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
-    }
+    for (int x = 0; x < 2; ++x) sts16(Xy, tc::kmajor_unit(i, (j0 >> 3) + x, C), pack8(&ha[8 * x]));
   }
   tc::fence_async_smem();
   tc::fence_before_sync();
@@ -581,23 +582,28 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
+  ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogues below shuffle with a full mask
   float db_own = 0.f, dg_own = 0.f;
   if (ok) {  // Xy <- Mb = beta_i M, M = -dA*Gamma strictly lower, zeros elsewhere
-    float f[32], kk[32];
+    float f[32], ha[16], hk[16];
     ld_acc32(tB, warp, cb, f);
-    ld_acc32(tB + 64, warp, cb, kk);
+    split_block32(f, lane, ha);
+    ld_acc32(tB + 64, warp, cb, f);
+    split_block32(f, lane, hk);
+    const int j0 = cb + 16 * hx;
     float rs = 0.f;
 #pragma unroll
-    for (int jj = 0; jj < 32; ++jj) {
-      const int j = cb + jj;
-      const float mv = -f[jj] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
+    for (int q = 0; q < 16; ++q) {
+      const int j = j0 + q;
+      const float mv = -ha[q] * exp_nonpos(gi - gam[j]);  // unconditional: the exponentials overlap
       const float M = (j < i) ? mv : 0.f;
-      rs = fmaf(M, kk[jj], rs);
-      f[jj] = bi * M;
+      rs = fmaf(M, hk[q], rs);
+      ha[q] = bi * M;
     }
-    if (own) {
 #pragma unroll
-      for (int x = 0; x < 4; ++x) sts16(Xy, tc::kmajor_unit(i, (cb >> 3) + x, C), pack8(&f[8 * x]));
+    for (int x = 0; x < 2; ++x) sts16(Xy, tc::kmajor_unit(i, (j0 >> 3) + x, C), pack8(&ha[8 * x]));
+    rs += __shfl_xor_sync(0xffffffffu, rs, 16);
+    if (own) {
       db_own = vdot + di * kz + rs;
       dg_own = 2.f * bi * (di * kz + rs);
     }
@@ -619,52 +625,61 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   }
   if (ok) ok = tc::mbar_wait(mbar + 6, 0);
   tc::fence_after_sync();
+  ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogues below shuffle with a full mask
   float rho = 0.f;
   if (ok) {  // dk = dkp + (dPG^T q + (Mb + Mb^T) k) + beta d z, assembled over dkp (each thread rewrites the units it read)
     float kd = 0.f;
     for (int s = 0; s < 2; ++s) {
       const int c0 = cw + 32 * s;
-      float g2[32];
-      ld_acc32(tB, warp, c0, g2);
-      if (own) {
-        float r4[4] = {0.f, 0.f, 0.f, 0.f}, k4[4] = {0.f, 0.f, 0.f, 0.f};
+      float f[32], g2[16];
+      ld_acc32(tB, warp, c0, f);
+      split_block32(f, lane, g2);
+      float r2[2] = {0.f, 0.f}, k2[2] = {0.f, 0.f};
 #pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const int c8 = (c0 >> 3) + x;
-          float e[8], z[8], kr[8];
-          unpack8(*reinterpret_cast<const uint4*>(Xdk + tc::sw128_unit(i, c8)), e);
-          unpack8(*reinterpret_cast<const uint4*>(XdO + tc::kmajor_unit(i, c8, KD)), z);
-          unpack8(*reinterpret_cast<const uint4*>(Xk + tc::sw128_unit(i, c8)), kr);
+      for (int x = 0; x < 2; ++x) {
+        const int c8 = (c0 >> 3) + 2 * hx + x;
+        float e[8], z[8], kr[8];
+        unpack8(*reinterpret_cast<const uint4*>(Xdk + tc::sw128_unit(i, c8)), e);
+        unpack8(*reinterpret_cast<const uint4*>(XdO + tc::kmajor_unit(i, c8, KD)), z);
+        unpack8(*reinterpret_cast<const uint4*>(Xk + tc::sw128_unit(i, c8)), kr);
 #pragma unroll
-          for (int y = 0; y < 8; ++y) {
-            r4[x] = fmaf(kr[y], e[y], r4[x]);              // k_i . dkp_i
-            const float val = g2[8 * x + y] + e[y] + bd_i * z[y];
-            k4[x] = fmaf(kr[y], val, k4[x]);               // k_i . dk_i
-            g2[8 * x + y] = val;
-          }
-          sts16(Xdk, tc::sw128_unit(i, c8), pack8(&g2[8 * x]));
+        for (int y = 0; y < 8; ++y) {
+          r2[x] = fmaf(kr[y], e[y], r2[x]);              // k_i . dkp_i
+          const float val = g2[8 * x + y] + e[y] + bd_i * z[y];
+          k2[x] = fmaf(kr[y], val, k2[x]);               // k_i . dk_i
+          g2[8 * x + y] = val;
         }
-        rho += (r4[0] + r4[1]) + (r4[2] + r4[3]);
-        kd += (k4[0] + k4[1]) + (k4[2] + k4[3]);
+        sts16(Xdk, tc::sw128_unit(i, c8), pack8(&g2[8 * x]));
       }
+      rho += r2[0] + r2[1];
+      kd += k2[0] + k2[1];
     }
+    rho += __shfl_xor_sync(0xffffffffu, rho, 16);
+    kd += __shfl_xor_sync(0xffffffffu, kd, 16);
     dg_own -= kd;
   }
   if (ok) ok = tc::mbar_wait(mbar, ph);  // every product has completed
   ph ^= 1;
   tc::fence_after_sync();
+  ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogues below shuffle with a full mask
   if (ok) {  // dq, assembled over q (each thread rewrites the units it read)
     float qd = 0.f;
     for (int s = 0; s < 2; ++s) {
       const int c0 = cw + 32 * s;
-      float f[32];
+      float f[32], hq[16];
       ld_acc32(tA, warp, c0, f);
-      if (own) {
-        qd += row_dot32<true>(Xvn, i, c0, f);
+      split_block32(f, lane, hq);
 #pragma unroll
-        for (int x = 0; x < 4; ++x) sts16(Xvn, tc::sw128_unit(i, (c0 >> 3) + x), pack8(&f[8 * x]));
+      for (int x = 0; x < 2; ++x) {
+        const int c8 = (c0 >> 3) + 2 * hx + x;
+        float qr[8];
+        unpack8(*reinterpret_cast<const uint4*>(Xvn + tc::sw128_unit(i, c8)), qr);
+#pragma unroll
+        for (int y = 0; y < 8; ++y) qd = fmaf(qr[y], hq[8 * x + y], qd);
+        sts16(Xvn, tc::sw128_unit(i, c8), pack8(&hq[8 * x]));
       }
     }
+    qd += __shfl_xor_sync(0xffffffffu, qd, 16);
     dg_own += qd;
   }
   {
