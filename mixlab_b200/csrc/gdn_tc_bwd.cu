@@ -298,21 +298,6 @@ __device__ __forceinline__ uint4 pack8(const float* e) {
   return make_uint4(tc::pack_bf16(e[0], e[1]), tc::pack_bf16(e[2], e[3]), tc::pack_bf16(e[4], e[5]),
                     tc::pack_bf16(e[6], e[7]));
 }
-// sum over 32 columns [c0, c0+32) of a[row][.] * b[row][.] for two [64][128] bf16 tiles in shared memory
-template <bool SWA, bool SWB>
-__device__ __forceinline__ float row_dot_tiles32(const uint8_t* a, const uint8_t* b, int r, int c0) {
-  float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int x = 0; x < 4; ++x) {
-    float ea[8], eb[8];
-    unpack8(*reinterpret_cast<const uint4*>(a + in_unit<SWA>(r, (c0 >> 3) + x)), ea);
-    unpack8(*reinterpret_cast<const uint4*>(b + in_unit<SWB>(r, (c0 >> 3) + x)), eb);
-#pragma unroll
-    for (int y = 0; y < 8; ++y) s[x & 3] = fmaf(ea[y], eb[y], s[x & 3]);
-  }
-  return (s[0] + s[1]) + (s[2] + s[3]);
-}
-
 // M=64 accumulators leave lanes 16-31 of every warp without a row.  Where an epilogue does real arithmetic per
 // element, the owning lane l hands columns 16..31 of its 32-column block to lane l + 16: both then work on 16
 // columns of the same row (16 shuffles buy half of the arithmetic).  h[q] = column c0 + 16 (lane >> 4) + q.
@@ -531,16 +516,7 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     tc::issue_gemm(tB + 64, tc::kmajor_tile(XdO, KD), tc::kmajor_sw128_tile(Xk, 8192), 64, 64, KD, false);
     tc::mma_commit(mbar);
   }
-  // e_i . v_i and k_i . z_i over this thread's half of the columns: both operands are in shared memory, so all 32
-  // lanes work (lane l and lane l + 16 take 32 columns each of row i)
-  float vdot = 0.f, kz = 0.f;
-  if (ok) {
-    const int cq = cw + 32 * (lane >> 4);
-    vdot = -row_dot_tiles32<true, true>(Xe, Xvn, i, cq);
-    kz = row_dot_tiles32<false, true>(XdO, Xk, i, cq);
-    vdot += __shfl_xor_sync(0xffffffffu, vdot, 16);
-    kz += __shfl_xor_sync(0xffffffffu, kz, 16);
-  }
+  float vdot = 0.f, kz = 0.f;  // e_i . v_i and k_i . z_i: the diagonals of the two products of this batch
   if (ok) ok = tc::mbar_wait(mbar, ph);
   ph ^= 1;
   tc::fence_after_sync();
@@ -552,6 +528,13 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
     ld_acc32(tB + 64, warp, cb, f);
     split_block32(f, lane, hb);
     const int j0 = cb + 16 * hx;
+#pragma unroll
+    for (int q = 0; q < 16; ++q) {  // the lane whose 16 columns contain column i picks the two row dots off the diagonal
+      vdot = (j0 + q == i) ? -ha[q] : vdot;
+      kz = (j0 + q == i) ? hb[q] : kz;
+    }
+    vdot += __shfl_xor_sync(0xffffffffu, vdot, 16);  // one of the two lanes of a row found it (the other holds 0);
+    kz += __shfl_xor_sync(0xffffffffu, kz, 16);      // rows whose diagonal lies in the other column half keep 0
 #pragma unroll
     for (int q = 0; q < 16; ++q) ha[q] = bet[j0 + q] * fmaf(dd[j0 + q], hb[q], -ha[q]);
 #pragma unroll
