@@ -1,5 +1,6 @@
 // Gated delta rule, chunked WY/UT form - tensor-core path (tcgen05.mma, TMEM
-// accumulators) for bf16 I/O with fp32 state, chunk 64, Dk = Dv = 128.
+// accumulators) for bf16 I/O with fp32 state, chunk 64, Dk and Dv up to 128 (tiles are 128 wide; narrower heads ride
+// on the copy engine's zero fill and clipping).
 //
 // Same mathematics as the fp32 path (gdn_simt.cu; reference
 // gated_delta_scan_chunked, gpu/ir.cpp:2352-2550).  Every contraction runs as
@@ -460,12 +461,12 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
     issue_U(c);
     issue_PK(c);
   }
-  float S[64];  // state row kk, columns j0 .. j0+63
+  float S[64];  // state row kk, columns j0 .. j0+63 (zero outside the true Dk x Dv state)
   if (p.h0) {
-    const float4* src = reinterpret_cast<const float4*>(p.h0 + ((size_t)bh * KD + kk) * KD + j0);
+    const float4* src = reinterpret_cast<const float4*>(p.h0 + ((size_t)bh * p.Dk + kk) * p.Dv + j0);
 #pragma unroll
     for (int x = 0; x < 16; ++x) {
-      const float4 t4 = __ldg(src + x);
+      const float4 t4 = (kk < p.Dk && j0 + 4 * x < p.Dv) ? __ldg(src + x) : make_float4(0.f, 0.f, 0.f, 0.f);
       S[4 * x] = t4.x; S[4 * x + 1] = t4.y; S[4 * x + 2] = t4.z; S[4 * x + 3] = t4.w;
     }
   } else {
@@ -526,7 +527,8 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
       }
     }
     if (TMA && tid == kOutThread && c > 0) {  // the previous chunk's output tile (complete since the barrier above)
-      for (int sl = 0; sl < 2; ++sl) tc::tma_store_4d(&maps.o, sOt + sl * 8192, 64 * sl, h, t0 - C, b);
+      for (int sl = 0; sl < 2; ++sl)  // a slab that lies wholly past the true width is not stored at all
+        if (64 * sl < p.Dv) tc::tma_store_4d(&maps.o, sOt + sl * 8192, 64 * sl, h, t0 - C, b);
       tc::bulk_commit();
     }
     // In the shadow of the MMA: k <- diag(r) k in place, so that the state update contracts it with v_new itself
@@ -624,17 +626,19 @@ __global__ void __launch_bounds__(256) gdn_tc_state_fwd_kernel(TcP p, const __gr
     tc::fence_async_smem();
     __syncthreads();
     if (ok && tid == kOutThread) {
-      for (int sl = 0; sl < 2; ++sl) tc::tma_store_4d(&maps.o, sOt + sl * 8192, 64 * sl, h, (p.n - 1) * C, b);
+      for (int sl = 0; sl < 2; ++sl)
+        if (64 * sl < p.Dv) tc::tma_store_4d(&maps.o, sOt + sl * 8192, 64 * sl, h, (p.n - 1) * C, b);
       tc::bulk_commit();
     }
     if (tid == kOutThread) tc::bulk_wait_read<0>();
   }
   if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 2);
-  if (ok && p.hT) {
-    float4* dst = reinterpret_cast<float4*>(p.hT + ((size_t)bh * KD + kk) * KD + j0);
+  if (ok && p.hT && kk < p.Dk) {
+    float4* dst = reinterpret_cast<float4*>(p.hT + ((size_t)bh * p.Dk + kk) * p.Dv + j0);
 #pragma unroll
-    for (int x = 0; x < 16; ++x) dst[x] = make_float4(S[4 * x], S[4 * x + 1], S[4 * x + 2], S[4 * x + 3]);
+    for (int x = 0; x < 16; ++x)
+      if (j0 + 4 * x < p.Dv) dst[x] = make_float4(S[4 * x], S[4 * x + 1], S[4 * x + 2], S[4 * x + 3]);
   }
   tc::fence_before_sync();
   __syncthreads();
@@ -647,9 +651,12 @@ mxb_status gdn_simt_bwd(const mxb_gdn_desc*, const void*, const void*, const voi
                         const float*, const float*, const void*, const float*, void*, void*, void*,
                         float*, float*, float*, void*, cudaStream_t);
 
-// chunk > 64 is computed with chunks of 64 (the result does not depend on the chunk size).
+// chunk > 64 is computed with chunks of 64 (the result does not depend on the chunk size).  Heads narrower than the
+// 128-wide tiles (64 <= Dk, Dv < 128, multiples of 8 so that rows stay 16-byte aligned) use the same kernels: their
+// tensor maps carry the true width, loads of the missing columns return zeros and stores of them are clipped.
 bool gdn_tc_supported(const mxb_gdn_desc* d) {
-  return d->io_dtype == MXB_BF16 && d->Dk == KD && d->Dv == KD && d->chunk >= C;
+  auto width_ok = [](int w) { return w >= 64 && w <= KD && w % 8 == 0; };
+  return d->io_dtype == MXB_BF16 && width_ok(d->Dk) && width_ok(d->Dv) && d->chunk >= C;
 }
 
 static size_t carve_tc(TcP& p, void* ws, bool bwd) {
@@ -673,6 +680,7 @@ static size_t carve_tc(TcP& p, void* ws, bool bwd) {
 static TcP make_tc(const mxb_gdn_desc* d) {
   TcP p{};
   p.B = d->B; p.T = d->T; p.H = d->H;
+  p.Dk = d->Dk; p.Dv = d->Dv;
   p.n = (d->T + C - 1) / C;
   p.gate_is_log = d->gate_is_log;
   return p;
@@ -711,19 +719,17 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 // [B,T,H,D] bf16 as a 4-d tensor (D, H, T, B) with boxes of 64 columns x 64 time steps, 128-byte swizzle
-// (D a multiple of 64; rows past T are zero-filled by the copy engine).  Shared with the Mamba-3 kernels.
+// (D a multiple of 8: rows are 16-byte multiples; columns past D and rows past T are zero-filled by the copy engine
+// on loads and clipped on stores).  Shared with the Mamba-3 kernels.
 bool make_tma_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H, int D) {
   EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || D % 64) return false;
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || D % 8 || D <= 0) return false;
   const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
   const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2, (cuuint64_t)T * H * D * 2};
   const cuuint32_t box[4] = {64, 1, 64, 1}, estr[4] = {1, 1, 1, 1};
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-static bool make_map_bthd(CUtensorMap* m, const void* base, int B, int T, int H) {
-  return make_tma_map_bthd(m, base, B, T, H, KD);
 }
 
 static bool g_tc_use_tma = true;
@@ -734,9 +740,12 @@ mxb_status tc_run_fwd(TcP& p, cudaStream_t st) {
   if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
   PrepMaps maps;
   std::memset(&maps, 0, sizeof maps);
-  const bool tma = g_tc_use_tma && !p.no_tma && make_map_bthd(&maps.k, p.k, p.B, p.T, p.H) &&
-                   make_map_bthd(&maps.q, p.q, p.B, p.T, p.H) && make_map_bthd(&maps.v, p.v, p.B, p.T, p.H) &&
-                   make_map_bthd(&maps.o, p.out, p.B, p.T, p.H);
+  // heads narrower than the tiles exist only through the copy engine (the per-thread staging addresses full rows)
+  const bool narrow = p.Dk != KD || p.Dv != KD;
+  const bool tma = g_tc_use_tma && (!p.no_tma || narrow) && make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, p.Dk) &&
+                   make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, p.Dk) && make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, p.Dv) &&
+                   make_tma_map_bthd(&maps.o, p.out, p.B, p.T, p.H, p.Dv);
+  if (narrow && !tma) return MXB_ERR_UNSUPPORTED;
   if (tma) {
     if (tc_set_smem(gdn_tc_prep_kernel<true>, kPrepSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("gdn_tc_prep_kernel", st,

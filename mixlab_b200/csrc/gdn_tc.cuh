@@ -21,6 +21,9 @@ using bf16 = __nv_bfloat16;
 
 struct TcP {
   int B, T, H, n, gate_is_log, save, no_tma;
+  int Dk, Dv;    // true widths of q,k and of v,out (multiples of 8 up to KD).  The tiles are always KD wide: the copy
+                 // engine zero-fills the columns a narrower tensor does not have and clips them on the way out, so
+                 // only the kernels' direct accesses to the fp32 states index with these
   const bf16 *q, *k, *v;
   const float *beta, *gate, *h0;
   bf16* out;

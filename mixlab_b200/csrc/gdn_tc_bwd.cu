@@ -128,10 +128,10 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
   }
   float dS[64];  // row kk of dS, columns j0 .. j0+63
   if (p.dhT_in) {
-    const float4* src = reinterpret_cast<const float4*>(p.dhT_in + ((size_t)bh * KD + kk) * KD + j0);
+    const float4* src = reinterpret_cast<const float4*>(p.dhT_in + ((size_t)bh * p.Dk + kk) * p.Dv + j0);
 #pragma unroll
     for (int x = 0; x < 16; ++x) {
-      const float4 t4 = __ldg(src + x);
+      const float4 t4 = (kk < p.Dk && j0 + 4 * x < p.Dv) ? __ldg(src + x) : make_float4(0.f, 0.f, 0.f, 0.f);
       dS[4 * x] = t4.x; dS[4 * x + 1] = t4.y; dS[4 * x + 2] = t4.z; dS[4 * x + 3] = t4.w;
     }
   } else {
@@ -256,10 +256,11 @@ __global__ void __launch_bounds__(256) gdn_tc_state_bwd_kernel(TcP p, const __gr
   if (!TMA) tc::cp_async_wait<0>();
   if (tid == 0) tc::bulk_wait_read<0>();  // shared memory must outlive the copies
   if (!ok && tid == 0) atomicExch(p.status, 3);
-  if (ok && p.dh0) {
-    float4* dst = reinterpret_cast<float4*>(p.dh0 + ((size_t)bh * KD + kk) * KD + j0);
+  if (ok && p.dh0 && kk < p.Dk) {
+    float4* dst = reinterpret_cast<float4*>(p.dh0 + ((size_t)bh * p.Dk + kk) * p.Dv + j0);
 #pragma unroll
-    for (int x = 0; x < 16; ++x) dst[x] = make_float4(dS[4 * x], dS[4 * x + 1], dS[4 * x + 2], dS[4 * x + 3]);
+    for (int x = 0; x < 16; ++x)
+      if (j0 + 4 * x < p.Dv) dst[x] = make_float4(dS[4 * x], dS[4 * x + 1], dS[4 * x + 2], dS[4 * x + 3]);
   }
   tc::fence_before_sync();
   __syncthreads();
@@ -677,10 +678,12 @@ __global__ void __launch_bounds__(256, 2) gdn_tc_chunk_bwd_kernel(TcP p, const _
   tc::fence_before_sync();
   __syncthreads();
   if (ok && tid == 64) {  // dq, dk and dv leave by tiled stores (rows past the end of the sequence are clipped)
-    for (int sl = 0; sl < 2; ++sl) {
-      tc::tma_store_4d(&maps.dq, tc::smem_u32(Xvn) + 8192 * sl, 64 * sl, h, t0, b);
-      tc::tma_store_4d(&maps.dk, tc::smem_u32(Xdk) + 8192 * sl, 64 * sl, h, t0, b);
-      tc::tma_store_4d(&maps.dv, tc::smem_u32(Xe) + 8192 * sl, 64 * sl, h, t0, b);
+    for (int sl = 0; sl < 2; ++sl) {  // a slab that lies wholly past the true width is not stored at all
+      if (64 * sl < p.Dk) {
+        tc::tma_store_4d(&maps.dq, tc::smem_u32(Xvn) + 8192 * sl, 64 * sl, h, t0, b);
+        tc::tma_store_4d(&maps.dk, tc::smem_u32(Xdk) + 8192 * sl, 64 * sl, h, t0, b);
+      }
+      if (64 * sl < p.Dv) tc::tma_store_4d(&maps.dv, tc::smem_u32(Xe) + 8192 * sl, 64 * sl, h, t0, b);
     }
     tc::bulk_commit();
   }
@@ -742,9 +745,11 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
   }
   RowMaps maps;
   std::memset(&maps, 0, sizeof maps);
-  const bool tma = !p.no_tma && make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, KD) &&
-                   make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, KD) &&
-                   make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, KD);
+  const bool narrow = p.Dk != KD || p.Dv != KD;  // narrower heads exist only through the copy engine
+  const bool tma = (!p.no_tma || narrow) && make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, p.Dk) &&
+                   make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, p.Dk) && make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, p.Dv) &&
+                   make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, p.Dv);
+  if (narrow && !tma) return MXB_ERR_UNSUPPORTED;
   if (tma) {
     if (bwd_set_smem(gdn_tc_state_bwd_kernel<true>, kStateBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
     MXB_LAUNCH("gdn_tc_state_bwd_kernel", st,
@@ -760,12 +765,12 @@ mxb_status tc_run_bwd(TcP& p, bool recompute, cudaStream_t st) {
   // per-thread staging of the kernels that have one): it needs the tensor maps.
   if (!tma) {
     std::memset(&maps, 0, sizeof maps);
-    if (!(make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, KD) &&
-          make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, KD)))
+    if (!(make_tma_map_bthd(&maps.k, p.k, p.B, p.T, p.H, p.Dk) && make_tma_map_bthd(&maps.q, p.q, p.B, p.T, p.H, p.Dk) &&
+          make_tma_map_bthd(&maps.v, p.v, p.B, p.T, p.H, p.Dv) && make_tma_map_bthd(&maps.dO, p.dO, p.B, p.T, p.H, p.Dv)))
       return MXB_ERR_UNSUPPORTED;
   }
-  if (!(make_tma_map_bthd(&maps.dq, p.dq, p.B, p.T, p.H, KD) && make_tma_map_bthd(&maps.dk, p.dk, p.B, p.T, p.H, KD) &&
-        make_tma_map_bthd(&maps.dv, p.dv, p.B, p.T, p.H, KD)))
+  if (!(make_tma_map_bthd(&maps.dq, p.dq, p.B, p.T, p.H, p.Dk) && make_tma_map_bthd(&maps.dk, p.dk, p.B, p.T, p.H, p.Dk) &&
+        make_tma_map_bthd(&maps.dv, p.dv, p.B, p.T, p.H, p.Dv)))
     return MXB_ERR_UNSUPPORTED;
   if (bwd_set_smem(gdn_tc_chunk_bwd_kernel, kChunkBwdSmem) != MXB_OK) return MXB_ERR_CUDA;
   MXB_LAUNCH("gdn_tc_chunk_bwd_kernel", st,

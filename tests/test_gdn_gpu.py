@@ -502,3 +502,33 @@ def test_front_end_rejects_mismatched_operands():
                                       use_saved=True)
     torch.cuda.synchronize()
     assert lib.mxb_launch_count() - n0 <= 2  # only the one plain forward above launched anything
+
+
+@pytest.mark.parametrize("dims", [(64, 64), (64, 128), (128, 64), (96, 72)])
+@pytest.mark.parametrize("T", [200, 64])
+def test_tensor_core_narrow_heads(dims, T):
+    """Heads narrower than the 128-wide tiles run the same tcgen05 kernels (the copy engine zero-fills the missing
+    columns and clips them on stores): forward and every gradient at 2e-2 against the float64 oracle, with initial
+    state and final-state gradient; (64, 64) is the head size of the end-to-end training configuration, (64, 128) the
+    reference's own benchmark shape (gpu/gated_delta_scan_test.go:265-277)."""
+    K, V = dims
+    lib = mixlab_b200.lib()
+    a = inputs.gdn_inputs(2, T, 3, K, V, seed=81, io_dtype=torch.bfloat16, with_grad_out=True, with_h0=True)
+    f = {k: v.double() for k, v in a.items()}
+    want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], f["g"], f["d_out"], f["d_state"], f["h0"], gate_is_log=True)
+    args = (_dev(a["q"]), _dev(a["k"]), _dev(a["v"]), _dev(a["beta"]), _dev(a["g"]))
+    lib.mxb_trace_enable(1)
+    o, s = ops.gated_delta_scan(*args, 64, gate_is_log=True, h0=_dev(a["h0"]), return_final_state=True)
+    got = ops.gated_delta_scan_backward(*args, _dev(a["d_out"]), 64, gate_is_log=True, h0=_dev(a["h0"]),
+                                        d_final_state=_dev(a["d_state"]))
+    torch.cuda.synchronize()
+    import ctypes as C
+    buf = C.create_string_buffer(4096)
+    lib.mxb_trace_summary(buf, len(buf))
+    lib.mxb_trace_enable(0)
+    assert b"gdn_tc_prep_kernel" in buf.value and b"gdn_tc_chunk_bwd_kernel" in buf.value, buf.value  # the tensor-core path ran
+    assert ops.device_status() == 0
+    assert_close(o, want["out"], TOL_BF16, "out")
+    assert_close(s, want["state"], TOL_BF16, "final_state")
+    for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
+        assert_close(got[name], want[name], TOL_BF16, name)
