@@ -39,6 +39,11 @@ WORKLOADS = {
 # Algorithmic work per unit: the bytes that must cross HBM if every intermediate stayed on chip.
 GDN_BYTES_PER_TOKEN_HEAD = 2840          # fwd 1032 + bwd read 1032 + bwd write 776
 GDN_FLOPS_PER_TOKEN_HEAD = 3 * 182955    # fwd + 2x for bwd
+
+
+def gdn_bytes_per_token_head(dk, dv):
+    """fwd: q,k,v,o bf16 + beta,g fp32; bwd: q,k,v,dO,beta,g in, dq,dk,dv bf16 + dbeta,dg fp32 out."""
+    return 2 * (2 * dk + 2 * dv) + 8 + 2 * (2 * dk + 2 * dv) + 8 + 2 * (2 * dk + dv) + 8
 M3_BYTES_PER_TOKEN = 23168
 M3_FLOPS_PER_TOKEN = 5.50e6
 # block stages around the scan, fwd+bwd, bf16: pre fwd 3 in + 3 out, pre bwd 6 in + 3 out, post fwd 2 in + 1 out,
@@ -214,6 +219,8 @@ def build_gdn_train(cx, batch):
     w = dict(WORKLOADS["gdn_train"])
     if batch > 0:
         w["B"] = batch
+    if cx.args.dims:
+        w["B"], w["T"], w["H"], w["Dk"], w["Dv"] = (int(x) for x in cx.args.dims.split(","))
     B, T, H, K, V, Cc = w["B"], w["T"], w["H"], w["Dk"], w["Dv"], w["chunk"]
     flags = cx._lib.MXB_GDN_FORCE_FP32_PATH if cx.args.fp32_path else 0
     # seeded inputs, generated one sequence at a time to bound host memory
@@ -232,8 +239,10 @@ def build_gdn_train(cx, batch):
 
     nchunks = B * H * ((T + Cc - 1) // Cc)
     return dict(step=step, units=units, metric="gdn_fwd_bwd_tokens_per_s", unit="tokens/s", dtype="bf16",
-                alg_bytes=units * H * GDN_BYTES_PER_TOKEN_HEAD, alg_flops=units * H * GDN_FLOPS_PER_TOKEN_HEAD,
-                traffic=lambda kernels: traffic_from_table(GDN_NCU_TRAFFIC_MB, GDN_NCU_TRAFFIC_UNITS, nchunks, kernels),
+                alg_bytes=units * H * gdn_bytes_per_token_head(K, V),
+                alg_flops=units * H * GDN_FLOPS_PER_TOKEN_HEAD * (K * V) / (128.0 * 128.0),
+                traffic=(lambda kernels: traffic_from_table(GDN_NCU_TRAFFIC_MB, GDN_NCU_TRAFFIC_UNITS, nchunks, kernels))
+                if (K, V) == (128, 128) else (lambda kernels: None),
                 traffic_note="per-kernel ncu byte capture (dram bytes read + written) of a full-size step, scaled by the "
                              "number of (batch, head, chunk) units; null when the step's kernel list differs from the capture's",
                 cfg=gdn_train_cfg(w, cx.world), host=host, dev_tensors=d, w=w, flags=flags)
@@ -547,6 +556,8 @@ def main():
     ap.add_argument("--fp32-path", action="store_true", help="force the CUDA-core fp32 kernels")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the per-GPU batch (sequences) - small cases for profiler captures only")
+    ap.add_argument("--dims", default="", help="gdn_train only: B,T,H,Dk,Dv of another shape (side measurements; the "
+                                               "headline workload is the default)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -569,7 +580,7 @@ def main():
 
     # ---- short legs of the other two primitives the headline metric names (default workload only) ----
     extra = None
-    if args.workload == "gdn_train" and not args.no_extra and args.batch == 0:
+    if args.workload == "gdn_train" and not args.no_extra and args.batch == 0 and not args.dims:
         extra = {}
         for name, nsteps in (("gdn_decode", 3), ("mamba3_train", 5)):
             w2 = BUILDERS[name](cx, 0)
@@ -592,11 +603,11 @@ def main():
         extra["dp_allreduce"] = dp_allreduce_leg(cx)
 
     e2e = None
-    if args.workload == "gdn_train" and not args.no_e2e:
+    if args.workload == "gdn_train" and not args.no_e2e and not args.dims:
         e2e = end_to_end_gdn(cx, wl)
 
     cpu = None
-    if rank == 0 and world == 1 and args.workload == "gdn_train" and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and args.workload == "gdn_train" and not args.no_cpu_baseline and not args.dims:
         threads = os.cpu_count() or 1
         tok, times = cpu_gdn_sample(threads, 2)
         cpu = {"value": tok / (sum(times) / len(times)), "unit": "tokens/s", "cores": threads, "kind": "port",

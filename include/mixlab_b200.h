@@ -298,6 +298,39 @@ MXB_API mxb_status mxb_mamba3_block_post_bwd(const mxb_mamba3_desc* d, float eps
                                      void* stream);
 
 /* ------------------------------------------------------------------------
+ * IR op records.  The reference's Go side hands every op to the interpreter as
+ * one record (mlx_ir_program_add_op, gpu/mlx_bridge.h:83-89): op type, input and
+ * output names, float params, int params; the interpreter resolves the names to
+ * arrays and switches on the op type (gpu/ir.cpp:4633-4654 for op 60,
+ * :4837-4853 for op 63).  mxb_ir_op is that record after name resolution:
+ * device pointers instead of names, everything else unchanged, so a cgo shim
+ * can forward the records of these two ops as they are.  Rules taken over from
+ * the interpreter: op 60 needs 5 inputs (q, k, v, beta, gate), 1 output and
+ * IntParams [B,T,H,Dk,Dv(,chunk)] with a missing or non-positive chunk meaning
+ * the token recurrence; op 63 needs 7 inputs (x, dt, lambda, theta, a_log,
+ * B_proj, C_proj), 1 output and IntParams [B,T,D,N,G(,chunk)] (the chunk size
+ * does not change the result and is ignored).  Anything else is
+ * MXB_ERR_INVALID_ARGUMENT, other op types MXB_ERR_UNSUPPORTED.  The gate of op
+ * 60 is the multiplicative decay (reference convention).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int32_t op_type;              /* MXB_OP_GATED_DELTA_SCAN | MXB_OP_MAMBA3_SELECTIVE_SCAN */
+  const void* const* inputs;    /* device pointers, in the order of the record's input names */
+  int32_t n_inputs;
+  void* const* outputs;
+  int32_t n_outputs;
+  const float* float_params;    /* unused by these two ops */
+  int32_t n_float_params;
+  const int32_t* int_params;
+  int32_t n_int_params;
+  int32_t io_dtype;             /* MXB_F32 (the reference's only dtype) | MXB_BF16 */
+} mxb_ir_op;
+
+MXB_API size_t mxb_ir_op_workspace_bytes(const mxb_ir_op* op);
+MXB_API mxb_status mxb_ir_op_forward(const mxb_ir_op* op, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
+/* ------------------------------------------------------------------------
  * Diagnostics (no counterpart in the reference).  One tcgen05.mma tile
  * D[128 x ncols] = A * B^T from caller-built shared-memory images (device
  * pointers, multiples of 16 bytes) and raw descriptor fields:

@@ -37,6 +37,14 @@ class Mamba3Desc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("B", "T", "D", "N", "G", "nheads", "io_dtype", "flags")]
 
 
+class IrOp(C.Structure):
+    """mxb_ir_op: an IR op record (mlx_ir_program_add_op) after name resolution."""
+    _fields_ = [("op_type", C.c_int32), ("inputs", C.POINTER(C.c_void_p)), ("n_inputs", C.c_int32),
+                ("outputs", C.POINTER(C.c_void_p)), ("n_outputs", C.c_int32), ("float_params", C.POINTER(C.c_float)),
+                ("n_float_params", C.c_int32), ("int_params", C.POINTER(C.c_int32)), ("n_int_params", C.c_int32),
+                ("io_dtype", C.c_int32)]
+
+
 # name -> (restype, argtypes); the complete export list of include/mixlab_b200.h
 _P = C.c_void_p
 EXPORTS = {
@@ -70,6 +78,8 @@ EXPORTS = {
     "mxb_mamba3_block_bc_bwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 13 + [C.c_size_t, _P]),
     "mxb_mamba3_block_post_fwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 5),
     "mxb_mamba3_block_post_bwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 8 + [C.c_size_t, _P]),
+    "mxb_ir_op_workspace_bytes": (C.c_size_t, [C.POINTER(IrOp)]),
+    "mxb_ir_op_forward": (C.c_int32, [C.POINTER(IrOp), _P, C.c_size_t, _P]),
     "mxb_selftest_umma": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint32, _P, _P, _P, _P]),
     "mxb_selftest_wait_timeout": (C.c_int32, [_P, C.c_size_t, C.c_uint32, _P]),
     "mxb_host_ctx_create": (C.c_int32, [C.c_int, C.c_size_t, C.POINTER(_P)]),

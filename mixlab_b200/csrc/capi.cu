@@ -363,6 +363,58 @@ mxb_status mxb_mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* 
                     workspace, static_cast<cudaStream_t>(stream));
 }
 
+// ---------------------------------------------------------------- IR op records
+static mxb_status ir_op_to_gdn(const mxb_ir_op* op, mxb_gdn_desc* d) {
+  if (op->n_inputs < 5 || op->n_outputs < 1 || op->n_int_params < 5 || !op->inputs || !op->outputs || !op->int_params)
+    return MXB_ERR_INVALID_ARGUMENT;  // "OP_GATED_DELTA_SCAN requires B,T,H,Dk,Dv"
+  const int32_t* ip = op->int_params;
+  *d = mxb_gdn_desc{ip[0], ip[1], ip[2], ip[3], ip[4], op->n_int_params >= 6 ? ip[5] : 0, op->io_dtype, 0, 0};
+  if (d->chunk < 0) d->chunk = 0;
+  return MXB_OK;
+}
+static mxb_status ir_op_to_m3(const mxb_ir_op* op, mxb_mamba3_desc* d) {
+  if (op->n_inputs < 7 || op->n_outputs < 1 || op->n_int_params < 5 || !op->inputs || !op->outputs || !op->int_params)
+    return MXB_ERR_INVALID_ARGUMENT;  // "OP_MAMBA3_SELECTIVE_SCAN requires 7 inputs and B,T,D,N,G params"
+  const int32_t* ip = op->int_params;
+  *d = mxb_mamba3_desc{ip[0], ip[1], ip[2], ip[3], ip[4], 0, op->io_dtype, 0};
+  return MXB_OK;
+}
+
+size_t mxb_ir_op_workspace_bytes(const mxb_ir_op* op) {
+  if (!op) return 0;
+  if (op->op_type == MXB_OP_GATED_DELTA_SCAN) {
+    mxb_gdn_desc d;
+    return ir_op_to_gdn(op, &d) == MXB_OK ? mxb_gdn_fwd_workspace_bytes(&d) : 0;
+  }
+  if (op->op_type == MXB_OP_MAMBA3_SELECTIVE_SCAN) {
+    mxb_mamba3_desc d;
+    return ir_op_to_m3(op, &d) == MXB_OK ? mxb_mamba3_fwd_workspace_bytes(&d) : 0;
+  }
+  return 0;
+}
+
+mxb_status mxb_ir_op_forward(const mxb_ir_op* op, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!op) return MXB_ERR_INVALID_ARGUMENT;
+  if (op->op_type == MXB_OP_GATED_DELTA_SCAN) {
+    mxb_gdn_desc d;
+    mxb_status s = ir_op_to_gdn(op, &d);
+    if (s != MXB_OK) return s;
+    const void* const* in = op->inputs;
+    return mxb_gdn_fwd(&d, in[0], in[1], in[2], static_cast<const float*>(in[3]), static_cast<const float*>(in[4]), nullptr,
+                       op->outputs[0], nullptr, workspace, workspace_bytes, stream);
+  }
+  if (op->op_type == MXB_OP_MAMBA3_SELECTIVE_SCAN) {
+    mxb_mamba3_desc d;
+    mxb_status s = ir_op_to_m3(op, &d);
+    if (s != MXB_OK) return s;
+    const void* const* in = op->inputs;
+    return mxb_mamba3_fwd(&d, in[0], static_cast<const float*>(in[1]), static_cast<const float*>(in[2]),
+                          static_cast<const float*>(in[3]), static_cast<const float*>(in[4]), in[5], in[6], op->outputs[0],
+                          workspace, workspace_bytes, stream);
+  }
+  return MXB_ERR_UNSUPPORTED;
+}
+
 mxb_status mxb_selftest_umma(const void* a_img, uint32_t a_bytes, const void* b_img, uint32_t b_bytes,
                              const uint32_t* fields, float* d_out, int* status, void* stream) {
   if (!a_img || !b_img || !fields || !d_out || !status) return MXB_ERR_INVALID_ARGUMENT;

@@ -197,6 +197,28 @@ def gated_delta_scan_backward(q, k, v, beta, gate, d_out, chunk=64, *, gate_is_l
     return dict(dq=dq, dk=dk, dv=dv, dbeta=dbeta, dgate=dgate, dh0=dh0)
 
 
+def ir_op_forward(op_type: int, inputs, int_params, *, out_shape, float_params=()):
+    """Runs one IR op record the way the reference's interpreter does after resolving its names
+    (gpu/ir.cpp:4633-4654, :4837-4853): ``inputs`` in the record's order, IntParams as the Go side emits them
+    (arch/ir.go:550-555, :600-602).  Returns the output tensor of ``out_shape`` in the dtype of the first input."""
+    _require_cuda(*inputs)
+    for i, t in enumerate(inputs):
+        if not t.is_contiguous() or t.device != inputs[0].device:
+            raise ValueError(f"input {i}: contiguous tensors on one device expected")
+    l = _lib.lib()
+    with torch.cuda.device(inputs[0].device):
+        out = torch.empty(out_shape, dtype=inputs[0].dtype, device=inputs[0].device)
+        ins = (C.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
+        outs = (C.c_void_p * 1)(out.data_ptr())
+        ip = (C.c_int32 * len(int_params))(*[int(v) for v in int_params])
+        fp = (C.c_float * max(len(float_params), 1))(*[float(v) for v in float_params])
+        rec = _lib.IrOp(int(op_type), ins, len(inputs), outs, 1, fp, len(float_params), ip, len(int_params), _io(inputs[0]))
+        nws = l.mxb_ir_op_workspace_bytes(C.byref(rec))
+        ws = workspace(nws, inputs[0].device)
+        _lib.check(l.mxb_ir_op_forward(C.byref(rec), _ptr(ws), ws.numel(), _stream()), "mxb_ir_op_forward")
+    return out
+
+
 def device_status(device=None) -> int:
     """Blocking read of the device-side error word of the cached workspace (0 = ok)."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device

@@ -150,3 +150,32 @@ def test_ops_check_every_operand():
         ops._check_like(FakeCuda((2, 3), torch.float32, "cuda:1"), (2, 3), torch.float32, "cuda:0", "x")
     with pytest.raises(ValueError):
         ops._check_like(FakeCuda((2, 3), torch.float32, contiguous=False), (2, 3), torch.float32, "cuda:0", "x")
+
+
+def test_ir_op_records_are_validated_like_the_interpreter():
+    """mxb_ir_op mirrors mlx_ir_program_add_op records (gpu/mlx_bridge.h:83-89); the argument rules are the
+    interpreter's (gpu/ir.cpp:4633-4654, :4837-4853).  Fake pointers: every case returns before a launch."""
+    lib = mixlab_b200.lib()
+    fake = 1 << 20
+
+    def rec(op_type, n_in, ints, n_out=1):
+        ins = (C.c_void_p * max(n_in, 1))(*([fake] * max(n_in, 1)))
+        outs = (C.c_void_p * 1)(fake)
+        ip = (C.c_int32 * max(len(ints), 1))(*ints) if ints else (C.c_int32 * 1)(0)
+        r = _lib.IrOp(op_type, ins, n_in, outs, n_out, None, 0, ip, len(ints), _lib.MXB_F32)
+        r._keep = (ins, outs, ip)
+        return r
+
+    ok60 = rec(60, 5, [2, 16, 2, 8, 8, 64])
+    assert lib.mxb_ir_op_workspace_bytes(C.byref(ok60)) > 0
+    assert lib.mxb_ir_op_forward(C.byref(ok60), None, 0, None) == -3                 # valid record, no workspace given
+    assert lib.mxb_ir_op_workspace_bytes(C.byref(rec(60, 5, [2, 16, 2, 8, 8]))) == 0  # no chunk = recurrence: no workspace
+    assert lib.mxb_ir_op_forward(C.byref(rec(60, 5, [2, 16, 2, 8])), None, 0, None) == -1     # "requires B,T,H,Dk,Dv"
+    assert lib.mxb_ir_op_forward(C.byref(rec(60, 4, [2, 16, 2, 8, 8, 64])), None, 0, None) == -1
+    assert lib.mxb_ir_op_forward(C.byref(rec(60, 5, [2, 16, 2, 8, 8, 64], n_out=0)), None, 0, None) == -1
+    ok63 = rec(63, 7, [1, 8, 4, 8, 2])
+    assert lib.mxb_ir_op_workspace_bytes(C.byref(ok63)) == 0 or lib.mxb_ir_op_workspace_bytes(C.byref(ok63)) > 0
+    assert lib.mxb_ir_op_forward(C.byref(rec(63, 6, [1, 8, 4, 8, 2])), None, 0, None) == -1   # "requires 7 inputs"
+    assert lib.mxb_ir_op_forward(C.byref(rec(63, 7, [1, 8, 4, 8])), None, 0, None) == -1
+    assert lib.mxb_ir_op_forward(C.byref(rec(61, 5, [2, 16, 2, 8, 8])), None, 0, None) == -2   # another op of the IR
+    assert lib.mxb_ir_op_forward(None, None, 0, None) == -1

@@ -532,3 +532,26 @@ def test_tensor_core_narrow_heads(dims, T):
     assert_close(s, want["state"], TOL_BF16, "final_state")
     for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
         assert_close(got[name], want[name], TOL_BF16, name)
+
+
+def test_ir_op_records_replay():
+    """The records the reference's Go side emits for ops 60 and 63 (arch/ir.go:550-555, :600-602), replayed through
+    mxb_ir_op_forward with device pointers in place of the names: same results as the reference-generated vectors."""
+    with open(os.path.join(G, "gdn_scalar_reference.json")) as f:
+        c = json.load(f)["cases"][2]
+    B, T, H, K, V = (c[x] for x in ("B", "T", "H", "Dk", "Dv"))
+    t = lambda key, *s: _dev(torch.tensor(c[key], dtype=torch.float32).reshape(*s))
+    ins = [t("q", B, T, H, K), t("k", B, T, H, K), t("v", B, T, H, V), t("beta", B, T, H), t("gate", B, T, H)]
+    want = torch.tensor(c["out"], dtype=torch.float64).reshape(B * T * H, V)
+    for int_params in ([B, T, H, K, V, 64], [B, T, H, K, V, 0], [B, T, H, K, V]):   # chunked, recurrence, legacy record
+        out = ops.ir_op_forward(60, ins, int_params, out_shape=(B * T * H, V))     # "out: [B*T*H, Dv]"
+        assert_close(out, want, TOL_F32, f"op 60 {int_params}")
+    z = np.load(os.path.join(G, "mamba3_torch_scan.npz"))
+    Bm, Tm, D = z["b_x"].shape
+    Gm, N = z["b_b"].shape[-2:]
+    m = lambda key, *s: _dev(torch.from_numpy(z["b_" + key]).float().reshape(*s))
+    ins = [m("x", Bm * Tm, D), m("dt_raw", Bm * Tm, D), m("lambda_raw", Bm * Tm, D), m("theta", Bm * Tm, D * N // 2),
+           m("a_log", D, N), m("b", Bm * Tm, Gm * N), m("c", Bm * Tm, Gm * N)]
+    for int_params in ([Bm, Tm, D, N, Gm], [Bm, Tm, D, N, Gm, 16]):
+        y = ops.ir_op_forward(63, ins, int_params, out_shape=(Bm * Tm, D))
+        assert_close(y, torch.from_numpy(z["b_y"]).reshape(Bm * Tm, D), TOL_F32, f"op 63 {int_params}")
