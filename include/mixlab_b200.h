@@ -298,6 +298,31 @@ MXB_API mxb_status mxb_mamba3_block_post_bwd(const mxb_mamba3_desc* d, float eps
                                      void* stream);
 
 /* ------------------------------------------------------------------------
+ * Data-parallel gradient exchange: the element-wise passes on either side of the
+ * per-bucket all-reduce, over flat float32 buckets on the device (the collective
+ * itself is the caller's: NCCL).  They fuse what the reference does op by op per
+ * weight: non-finite entries zeroed and gradients turned into numerators before
+ * the sums (gpu/distributed_step.cpp:140-152); division by the global
+ * denominator, non-finite count, global norm and clipping after them
+ * (gpu/distributed_step.cpp:231-240, gpu/optimizer_step_guard.cpp:76-104).
+ *   sanitize  x <- finite(x) ? x * scale : 0; *flag = 1 if anything was non-finite
+ *             (flag is only ever set, clear it before the first bucket)
+ *   finalize  x <- x * inv_denominator with non-finite results zeroed and counted;
+ *             totals[0] += sum of squares, totals[1] += count (zero totals before the
+ *             first bucket), totals[2] = clip scale so far: min(1, max_norm /
+ *             (sqrt(totals[0]) + 1e-6)), 0 if totals[1] != 0, 1 if max_norm <= 0.
+ *             partial: scratch of mxb_dp_partial_floats() floats.  Sums run in a fixed
+ *             order (no floating-point atomics): same inputs, same bits.
+ *   scale     x <- x * *scale_dev (a device scalar, e.g. totals + 2 after the last
+ *             finalize: no host round trip between norm and clipping)
+ * ---------------------------------------------------------------------- */
+MXB_API size_t mxb_dp_partial_floats(void);
+MXB_API mxb_status mxb_dp_sanitize(float* x, size_t n, float scale, float* flag, void* stream);
+MXB_API mxb_status mxb_dp_finalize(float* x, size_t n, float inv_denominator, float max_norm,
+                           float* partial, float* totals, void* stream);
+MXB_API mxb_status mxb_dp_scale(float* x, size_t n, const float* scale_dev, void* stream);
+
+/* ------------------------------------------------------------------------
  * IR op records.  The reference's Go side hands every op to the interpreter as
  * one record (mlx_ir_program_add_op, gpu/mlx_bridge.h:83-89): op type, input and
  * output names, float params, int params; the interpreter resolves the names to

@@ -78,6 +78,10 @@ EXPORTS = {
     "mxb_mamba3_block_bc_bwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 13 + [C.c_size_t, _P]),
     "mxb_mamba3_block_post_fwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 5),
     "mxb_mamba3_block_post_bwd": (C.c_int32, [C.POINTER(Mamba3Desc), C.c_float] + [_P] * 8 + [C.c_size_t, _P]),
+    "mxb_dp_partial_floats": (C.c_size_t, []),
+    "mxb_dp_sanitize": (C.c_int32, [_P, C.c_size_t, C.c_float, _P, _P]),
+    "mxb_dp_finalize": (C.c_int32, [_P, C.c_size_t, C.c_float, C.c_float, _P, _P, _P]),
+    "mxb_dp_scale": (C.c_int32, [_P, C.c_size_t, _P, _P]),
     "mxb_ir_op_workspace_bytes": (C.c_size_t, [C.POINTER(IrOp)]),
     "mxb_ir_op_forward": (C.c_int32, [C.POINTER(IrOp), _P, C.c_size_t, _P]),
     "mxb_selftest_umma": (C.c_int32, [_P, C.c_uint32, _P, C.c_uint32, _P, _P, _P, _P]),

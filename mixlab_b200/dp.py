@@ -155,15 +155,35 @@ def sanitize_and_clip_(grads: Sequence[torch.Tensor], max_grad_norm: float) -> t
     return nonfinite
 
 
+def _all_reduce_buckets(flat, group, comm_stream, dev):
+    """One SUM all-reduce per bucket, in plan order, asynchronously; on CUDA on the communication stream."""
+    cuda = dev.type == "cuda"
+    works = []
+    if cuda and comm_stream is not None:
+        comm_stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(comm_stream):
+            for buf in flat:
+                works.append(dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True))
+    else:
+        for buf in flat:
+            works.append(dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True))
+    for w in works:
+        w.wait()
+    if cuda and comm_stream is not None:
+        torch.cuda.current_stream(dev).wait_stream(comm_stream)
+
+
 def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, loss_normalizer: float,
                               gradients_are_numerators: bool, max_grad_norm: float, plan: GradientBucketPlan,
                               storage: Optional[BucketStorage] = None, group=None,
                               comm_stream: Optional["torch.cuda.Stream"] = None) -> StagedGradientResult:
     """Replaces ``grads[i]`` by the globally averaged, clipped gradient (views into ``storage``).
 
-    ``grads`` may already be the views of ``storage`` (no packing copy then).  On CUDA the bucket all-reduces are
-    enqueued on ``comm_stream`` (default: the current stream) one after the other in plan order and the host waits
-    once, for the last of them."""
+    ``grads`` may already be the views of ``storage`` (no packing copy then).  On CUDA every element-wise stage is
+    one fused pass per bucket of the library's kernels (mxb_dp_sanitize / _finalize / _scale), the bucket
+    all-reduces are enqueued on ``comm_stream`` (default: the current stream) one after the other in plan order,
+    and the host reads the device twice: the packed scalars after the sums and the non-finite count at the end.
+    CPU tensors (the gloo tests of the host logic) take the same stages through torch ops."""
     if not grads or not plan.buckets:
         raise ValueError("distributed gradient bucket plan is empty")
     dev = grads[0].device
@@ -171,51 +191,65 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
         storage = BucketStorage(plan, dev)
     denominator_valid = math.isfinite(loss_normalizer) and loss_normalizer >= 0.0
     safe = float(loss_normalizer) if denominator_valid else 0.0
-    # -- numerator conversion (+ pack into the flat buckets when the gradients live elsewhere)
-    raw_bad = torch.zeros((), dtype=torch.float32, device=dev)
-    for i, g in enumerate(grads):
+    for i, g in enumerate(grads):  # pack into the flat buckets when the gradients live elsewhere
         view = storage.views[i]
         if g.data_ptr() != view.data_ptr():
             view.copy_(g.to(torch.float32).reshape(view.shape))
-        fin = torch.isfinite(view)
-        raw_bad = torch.maximum(raw_bad, (~fin).any().float())
-        view.masked_fill_(~fin, 0.0)
-        if not gradients_are_numerators:
-            view.mul_(safe)
-    local_bad = torch.maximum((~torch.isfinite(loss.float())).any().float(), raw_bad) if safe > 0.0 else torch.zeros_like(raw_bad)
-    if not denominator_valid:
-        local_bad = torch.ones_like(raw_bad)
-    storage.scalars[0] = local_bad
-    storage.scalars[1] = safe
-    # -- one sum per bucket, in plan order, asynchronously
-    cuda = dev.type == "cuda"
-    works = []
-    if cuda and comm_stream is not None:
-        comm_stream.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(comm_stream):
-            for buf in storage.flat:
-                works.append(dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True))
-    else:
-        for buf in storage.flat:
-            works.append(dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True))
-    for w in works:
-        w.wait()
-    if cuda and comm_stream is not None:
-        torch.cuda.current_stream(dev).wait_stream(comm_stream)
-    bad_count, denominator = (float(x) for x in storage.scalars.tolist())  # the one host read
-    nbytes = sum(b.numel() * 4 for b in storage.flat)
     for i in range(len(grads)):
         grads[i] = storage.views[i]
+    cuda = dev.type == "cuda"
+    scale = 1.0 if gradients_are_numerators else safe
+    nbytes = sum(b.numel() * 4 for b in storage.flat)
+    # -- numerator conversion: non-finite -> 0 (and flagged), x scale
+    if cuda:
+        from . import _lib
+        import ctypes as C
+        l = _lib.lib()
+        st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        aux = torch.zeros(4 + l.mxb_dp_partial_floats(), dtype=torch.float32, device=dev)  # flag, totals[3], partials
+        P = lambda t, off=0: C.c_void_p(t.data_ptr() + 4 * off)
+        with torch.cuda.device(dev):
+            for b, buf in zip(plan.buckets, storage.flat):
+                _lib.check(l.mxb_dp_sanitize(P(buf), b.elements, scale, P(aux), st), "mxb_dp_sanitize")
+        raw_bad = aux[0]
+    else:
+        raw_bad = torch.zeros((), dtype=torch.float32, device=dev)
+        for b, buf in zip(plan.buckets, storage.flat):
+            body = buf[:b.elements]
+            fin = torch.isfinite(body)
+            raw_bad = torch.maximum(raw_bad, (~fin).any().float())
+            body.masked_fill_(~fin, 0.0)
+            if scale != 1.0:
+                body.mul_(scale)
+    local_bad = torch.maximum((~torch.isfinite(loss.float())).any().float().to(dev), raw_bad) if safe > 0.0 \
+        else torch.zeros((), dtype=torch.float32, device=dev)
+    if not denominator_valid:
+        local_bad = torch.ones((), dtype=torch.float32, device=dev)
+    storage.scalars[0] = local_bad
+    storage.scalars[1] = safe
+    _all_reduce_buckets(storage.flat, group, comm_stream, dev)
+    bad_count, denominator = (float(x) for x in storage.scalars.tolist())  # host read of the two packed scalars
     if bad_count > 0.0:
         return StagedGradientResult(bad_count, False, True, denominator, len(storage.flat), nbytes)
     if not math.isfinite(denominator) or denominator < 0.0:
         raise RuntimeError("distributed global loss denominator is invalid")
     if denominator == 0.0:
         return StagedGradientResult(0.0, True, False, 0.0, len(storage.flat), nbytes)
-    for b, buf in zip(plan.buckets, storage.flat):
-        buf[:b.elements].div_(denominator)
-    nonfinite = sanitize_and_clip_(grads, max_grad_norm)
-    return StagedGradientResult(float(nonfinite), False, False, denominator, len(storage.flat), nbytes)
+    # -- divide by the global denominator, sanitize, global norm, clip
+    if cuda:
+        with torch.cuda.device(dev):
+            for b, buf in zip(plan.buckets, storage.flat):
+                _lib.check(l.mxb_dp_finalize(P(buf), b.elements, 1.0 / denominator, float(max_grad_norm), P(aux, 4), P(aux, 1),
+                                             st), "mxb_dp_finalize")
+            if max_grad_norm > 0.0:
+                for b, buf in zip(plan.buckets, storage.flat):
+                    _lib.check(l.mxb_dp_scale(P(buf), b.elements, P(aux, 3), st), "mxb_dp_scale")
+        nonfinite = float(aux[2])
+    else:
+        for b, buf in zip(plan.buckets, storage.flat):
+            buf[:b.elements].div_(denominator)
+        nonfinite = float(sanitize_and_clip_(grads, max_grad_norm))
+    return StagedGradientResult(nonfinite, False, False, denominator, len(storage.flat), nbytes)
 
 
 def hybrid_lm_weight_shapes(layers=12, d_model=1024, heads=16, d_k=64, d_v=64, ffn=4096, vocab=32768) -> List[tuple]:
