@@ -45,8 +45,10 @@ def test_dp_passes_match_torch(n, offset):
     assert aux[2].item() == float((~finy).sum())
     assert abs(aux[1].item() - wanty.double().pow(2).sum().item()) <= 1e-4 * max(1.0, wanty.double().pow(2).sum().item())
     assert aux[3].item() == (0.0 if (~finy).any() else min(1.0, 2.0 / (math.sqrt(aux[1].item()) + 1e-6)))
-    # same inputs, same bits: the reductions run in a fixed order
-    x2, aux2 = y.clone(), torch.zeros_like(aux)
+    # same inputs (at the same alignment), same bits: the reductions run in a fixed order
+    base2 = torch.empty_like(base)
+    x2, aux2 = base2[offset:offset + n], torch.zeros_like(aux)
+    x2.copy_(y)
     lib.mxb_dp_finalize(_p(x2), n, 1.0 / 3.0, 2.0, _p(aux2, 4), _p(aux2, 1), None)
     assert torch.equal(aux2[1:4], aux[1:4])
     aux[3] = 0.25
