@@ -54,11 +54,11 @@ M3_BLOCK_BYTES_PER_TOKEN = lambda D, GN: (13 * D + 10 * GN) * 2
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, MB per launch at the full workload size) per kernel, from
 # one ncu byte capture of a step.  Keyed by kernel name: when the kernels a step launches are not exactly these, the
 # capture no longer describes the step and roofline.traffic is reported as null instead of a stale number.
-GDN_NCU_TRAFFIC_MB = {
-    "gdn_tc_prep_kernel": 763.0, "gdn_tc_state_fwd_kernel": 1090.2, "gdn_tc_state_bwd_kernel": 963.7,
-    "gdn_tc_chunk_bwd_state_kernel": 1373.9, "gdn_tc_chunk_bwd_kernel": 1457.5,
+GDN_NCU_TRAFFIC_MB = {   # captured at B=4 (4096 units); at B=8 a little less of the producer -> consumer tiles stays in L2
+    "gdn_tc_prep_kernel": 356.3, "gdn_tc_state_fwd_kernel": 525.1, "gdn_tc_state_bwd_kernel": 464.1,
+    "gdn_tc_chunk_bwd_kernel": 886.6,
 }
-GDN_NCU_TRAFFIC_UNITS = 8192     # (batch, head, chunk) units of the captured step
+GDN_NCU_TRAFFIC_UNITS = 4096     # (batch, head, chunk) units of the captured step
 M3_NCU_TRAFFIC_MB = {
     "m3s_scalars_kernel": 12.6, "m3s_chunk_scalars_kernel": 12.6, "m3s_state_pass_kernel": 390.3 + 390.4,
     "m3s_chunk_out_kernel": 566.2, "m3s_chunk_grad_kernel": 1494.2, "m3s_final_kernel": 33.6, "m3s_dalog_kernel": 0.0,
