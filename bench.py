@@ -41,9 +41,10 @@ GDN_BYTES_PER_TOKEN_HEAD = 2840          # fwd 1032 + bwd read 1032 + bwd write 
 GDN_FLOPS_PER_TOKEN_HEAD = 3 * 182955    # fwd + 2x for bwd
 
 
-def gdn_bytes_per_token_head(dk, dv):
-    """fwd: q,k,v,o bf16 + beta,g fp32; bwd: q,k,v,dO,beta,g in, dq,dk,dv bf16 + dbeta,dg fp32 out."""
-    return 2 * (2 * dk + 2 * dv) + 8 + 2 * (2 * dk + 2 * dv) + 8 + 2 * (2 * dk + dv) + 8
+def gdn_bytes_per_token_head(dk, dv, io_bytes=2):
+    """fwd: q,k,v,o + beta,g fp32; bwd: q,k,v,dO,beta,g in, dq,dk,dv + dbeta,dg fp32 out (bf16 tensors unless io_bytes=4)."""
+    e = io_bytes
+    return e * (2 * dk + 2 * dv) + 8 + e * (2 * dk + 2 * dv) + 8 + e * (2 * dk + dv) + 8
 M3_BYTES_PER_TOKEN = 23168
 M3_FLOPS_PER_TOKEN = 5.50e6
 # block stages around the scan, fwd+bwd, bf16: pre fwd 3 in + 3 out, pre bwd 6 in + 3 out, post fwd 2 in + 1 out,
@@ -223,9 +224,12 @@ def build_gdn_train(cx, batch):
         w["B"], w["T"], w["H"], w["Dk"], w["Dv"] = (int(x) for x in cx.args.dims.split(","))
     B, T, H, K, V, Cc = w["B"], w["T"], w["H"], w["Dk"], w["Dv"], w["chunk"]
     flags = cx._lib.MXB_GDN_FORCE_FP32_PATH if cx.args.fp32_path else 0
+    f32 = cx.args.io == "f32"
+    if f32 and not cx.args.fp32_path:  # float32 tensors, bf16 operands inside (the flag is off by default)
+        flags |= cx._lib.MXB_GDN_F32_IO_BF16_OPERANDS
     # seeded inputs, generated one sequence at a time to bound host memory
-    parts = [cx.inputs.gdn_inputs(1, T, H, K, V, seed=1000 * (cx.rank + 1) + b, io_dtype=torch.bfloat16,
-                                  with_grad_out=True) for b in range(B)]
+    parts = [cx.inputs.gdn_inputs(1, T, H, K, V, seed=1000 * (cx.rank + 1) + b,
+                                  io_dtype=torch.float32 if f32 else torch.bfloat16, with_grad_out=True) for b in range(B)]
     host = {k: torch.cat([p[k] for p in parts]).contiguous().pin_memory() for k in parts[0]}
     d = {k: v.to(cx.dev, non_blocking=True) for k, v in host.items()}
     units = B * T  # tokens per step per GPU
@@ -238,14 +242,18 @@ def build_gdn_train(cx, batch):
                                       gate_is_log=True, flags=flags, use_saved=True)
 
     nchunks = B * H * ((T + Cc - 1) // Cc)
-    return dict(step=step, units=units, metric="gdn_fwd_bwd_tokens_per_s", unit="tokens/s", dtype="bf16",
-                alg_bytes=units * H * gdn_bytes_per_token_head(K, V),
+    cfg = gdn_train_cfg(w, cx.world)
+    if f32:
+        cfg["io"] = "f32 tensors" + (", fp32 kernels" if cx.args.fp32_path else ", bf16 operands inside (MXB_GDN_F32_IO_BF16_OPERANDS)")
+    return dict(step=step, units=units, metric="gdn_fwd_bwd_tokens_per_s", unit="tokens/s",
+                dtype="f32" if (f32 and cx.args.fp32_path) else "bf16",
+                alg_bytes=units * H * gdn_bytes_per_token_head(K, V, 4 if f32 else 2),
                 alg_flops=units * H * GDN_FLOPS_PER_TOKEN_HEAD * (K * V) / (128.0 * 128.0),
                 traffic=(lambda kernels: traffic_from_table(GDN_NCU_TRAFFIC_MB, GDN_NCU_TRAFFIC_UNITS, nchunks, kernels))
-                if (K, V) == (128, 128) else (lambda kernels: None),
+                if (K, V) == (128, 128) and not f32 else (lambda kernels: None),
                 traffic_note="per-kernel ncu byte capture (dram bytes read + written) of a full-size step, scaled by the "
                              "number of (batch, head, chunk) units; null when the step's kernel list differs from the capture's",
-                cfg=gdn_train_cfg(w, cx.world), host=host, dev_tensors=d, w=w, flags=flags)
+                cfg=cfg, host=host, dev_tensors=d, w=w, flags=flags)
 
 
 def build_gdn_decode(cx, batch):
@@ -554,6 +562,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the short gdn_decode and mamba3_train legs")
     ap.add_argument("--fp32-path", action="store_true", help="force the CUDA-core fp32 kernels")
+    ap.add_argument("--io", default="bf16", choices=["bf16", "f32"],
+                    help="gdn_train only: float32 tensors (side measurement; the headline is bf16)")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the per-GPU batch (sequences) - small cases for profiler captures only")
     ap.add_argument("--dims", default="", help="gdn_train only: B,T,H,Dk,Dv of another shape (side measurements; the "

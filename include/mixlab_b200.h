@@ -106,6 +106,13 @@ enum {
                                           the bulk-copy pipelined kernel covers the shape */
   MXB_GDN_NO_TMA = 32,          /* tensor-core path: stage k, q, v of the prep kernel with cp.async instead
                                    of TMA tensor copies (a cross-check of the two staging paths) */
+  MXB_GDN_F32_IO_BF16_OPERANDS = 64, /* io_dtype MXB_F32 only: round q, k, v (and d_out) to bf16, run the
+                                        tensor-core kernels on the copies and widen the results back to
+                                        float32.  Results then carry bf16 rounding (relative 2^-9), which the
+                                        reference's float32 evaluation does not; without the flag float32
+                                        tensors take the full-fp32 kernels.  Needs the larger workspace the
+                                        size queries report for this flag; ignored where the tensor-core
+                                        kernels do not cover the shape or MXB_GDN_FORCE_FP32_PATH is set. */
   MXB_GDN_BWD_USE_SAVED = 8     /* backward: the workspace still holds what a forward with
                                    MXB_GDN_SAVE_FOR_BWD on the same inputs left there, so the
                                    forward recompute is skipped (the reference keeps its forward

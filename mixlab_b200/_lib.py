@@ -16,6 +16,7 @@ MXB_GDN_SAVE_FOR_BWD = 4
 MXB_GDN_BWD_USE_SAVED = 8
 MXB_GDN_DECODE_REGISTER_KERNEL = 16
 MXB_GDN_NO_TMA = 32
+MXB_GDN_F32_IO_BF16_OPERANDS = 64
 MXB_MAMBA3_CHANNEL_KERNELS = 1
 MXB_MAMBA3_RECURRENT_KERNELS = 2
 MXB_MAMBA3_SAVE_FOR_BWD = 4

@@ -15,7 +15,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libmixlab_b200.so")
-SOURCES = ["capi.cu", "dp_grad.cu", "gdn_block.cu", "gdn_decode.cu", "gdn_decode_bulk.cu", "gdn_simt.cu", "gdn_static_scratch.cu", "gdn_tc.cu", "gdn_tc_bwd.cu", "mamba3.cu", "mamba3_block.cu", "mamba3_head.cu", "mamba3_ssd.cu", "umma_selftest.cu"]
+SOURCES = ["capi.cu", "dp_grad.cu", "gdn_block.cu", "gdn_decode.cu", "gdn_decode_bulk.cu", "gdn_f32io.cu", "gdn_simt.cu", "gdn_static_scratch.cu", "gdn_tc.cu", "gdn_tc_bwd.cu", "mamba3.cu", "mamba3_block.cu", "mamba3_head.cu", "mamba3_ssd.cu", "umma_selftest.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "--std=c++17",
     "--extended-lambda", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

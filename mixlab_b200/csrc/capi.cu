@@ -72,6 +72,13 @@ mxb_status gdn_simt_bwd(const mxb_gdn_desc*, const void*, const void*, const voi
                         const float*, const float*, const void*, const float*, void*, void*, void*,
                         float*, float*, float*, void*, cudaStream_t);
 bool gdn_tc_supported(const mxb_gdn_desc*);
+bool gdn_f32io_wanted(const mxb_gdn_desc*);
+size_t gdn_f32io_workspace_bytes(const mxb_gdn_desc*, bool bwd);
+mxb_status gdn_f32io_fwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*, const float*,
+                         const float*, void*, float*, void*, cudaStream_t);
+mxb_status gdn_f32io_bwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*, const float*,
+                         const float*, const void*, const float*, void*, void*, void*, float*, float*, float*, void*,
+                         cudaStream_t);
 size_t gdn_tc_workspace_bytes(const mxb_gdn_desc*, bool bwd);
 mxb_status gdn_tc_fwd(const mxb_gdn_desc*, const void*, const void*, const void*, const float*,
                       const float*, const float*, void*, float*, void*, cudaStream_t);
@@ -184,12 +191,14 @@ size_t mxb_trace_summary(char* buf, size_t cap) {
 size_t mxb_gdn_fwd_workspace_bytes(const mxb_gdn_desc* d) {
   if (check_gdn_desc(d, true) != MXB_OK) return 0;
   const bool save = (d->flags & MXB_GDN_SAVE_FOR_BWD) != 0;
+  if (gdn_f32io_wanted(d)) return gdn_f32io_workspace_bytes(d, false);
   if (use_tc(d)) return gdn_tc_workspace_bytes(d, save);
   return gdn_simt_workspace_bytes(d, save);
 }
 
 size_t mxb_gdn_bwd_workspace_bytes(const mxb_gdn_desc* d) {
   if (check_gdn_desc(d, true) != MXB_OK) return 0;
+  if (gdn_f32io_wanted(d)) return gdn_f32io_workspace_bytes(d, true);
   if (use_tc(d)) return gdn_tc_workspace_bytes(d, true);
   return gdn_simt_workspace_bytes(d, true);
 }
@@ -204,9 +213,11 @@ mxb_status mxb_gdn_fwd(const mxb_gdn_desc* d, const void* q, const void* k, cons
   if (need > 0 && (!workspace || workspace_bytes < need)) return MXB_ERR_WORKSPACE;
   if (need > 0 && !aligned16(workspace)) return MXB_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (use_tc(d)) {  // the tensor-core kernels move whole 16-byte units (TMA tiles, bulk copies, 128-bit loads)
+  const bool f32io = gdn_f32io_wanted(d);
+  if (f32io || use_tc(d)) {  // these kernels move whole 16-byte units (TMA tiles, bulk copies, 128-bit loads)
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || !aligned16(h0) || !aligned16(hT))
       return MXB_ERR_ALIGNMENT;
+    if (f32io) return gdn_f32io_fwd(d, q, k, v, beta, gate, h0, out, hT, workspace, st);
     return gdn_tc_fwd(d, q, k, v, beta, gate, h0, out, hT, workspace, st);
   }
   if (!gdn_simt_supported(d)) return MXB_ERR_UNSUPPORTED;
@@ -225,10 +236,13 @@ mxb_status mxb_gdn_bwd(const mxb_gdn_desc* d, const void* q, const void* k, cons
   if (!workspace || workspace_bytes < need) return MXB_ERR_WORKSPACE;
   if (!aligned16(workspace)) return MXB_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (use_tc(d)) {
+  const bool f32io = gdn_f32io_wanted(d);
+  if (f32io || use_tc(d)) {
     if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(d_out) || !aligned16(dq) || !aligned16(dk) ||
         !aligned16(dv) || !aligned16(h0) || !aligned16(d_hT) || !aligned16(dh0))
       return MXB_ERR_ALIGNMENT;
+    if (f32io)
+      return gdn_f32io_bwd(d, q, k, v, beta, gate, h0, d_out, d_hT, dq, dk, dv, dbeta, dgate, dh0, workspace, st);
     return gdn_tc_bwd(d, q, k, v, beta, gate, h0, d_out, d_hT, dq, dk, dv, dbeta, dgate, dh0, workspace, st);
   }
   if (!gdn_simt_supported(d)) return MXB_ERR_UNSUPPORTED;

@@ -132,6 +132,11 @@ def _keep_saved(device, rec, ws, what):
     _ws_saved[_dev_key(device)] = rec
 
 
+def _path_flags(flags):
+    """The flag bits that choose a kernel family (and with it the layout of what a forward saves)."""
+    return int(flags) & ~(_lib.MXB_GDN_SAVE_FOR_BWD | _lib.MXB_GDN_BWD_USE_SAVED)
+
+
 def gdn_desc(q, v, chunk, gate_is_log, flags=0) -> GdnDesc:
     B, T, H, Dk = q.shape
     return GdnDesc(B, T, H, Dk, v.shape[-1], int(chunk), _io(q), int(bool(gate_is_log)), int(flags))
@@ -166,7 +171,7 @@ def gated_delta_scan(q, k, v, beta, gate, chunk=64, *, gate_is_log=False, h0=Non
         _lib.check(l.mxb_gdn_fwd(C.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(gate), _ptr(h0), _ptr(out),
                                  _ptr(hT), _ptr(ws), ws.numel(), _stream()), "mxb_gdn_fwd")
         if save_for_backward:
-            _mark_saved(q.device, _saved_token("gdn", (q, k, v, beta, gate), (int(chunk), bool(gate_is_log))), ws)
+            _mark_saved(q.device, _saved_token("gdn", (q, k, v, beta, gate), (int(chunk), bool(gate_is_log), _path_flags(flags))), ws)
     return (out, hT) if return_final_state else out
 
 
@@ -182,7 +187,7 @@ def gated_delta_scan_backward(q, k, v, beta, gate, d_out, chunk=64, *, gate_is_l
     with torch.cuda.device(q.device):
         saved = None
         if use_saved:
-            saved = _require_saved(q.device, _saved_token("gdn", (q, k, v, beta, gate), (int(chunk), bool(gate_is_log))),
+            saved = _require_saved(q.device, _saved_token("gdn", (q, k, v, beta, gate), (int(chunk), bool(gate_is_log), _path_flags(flags))),
                                    "gated_delta_scan_backward")
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dbeta, dgate = torch.empty_like(beta), torch.empty_like(gate)

@@ -555,3 +555,39 @@ def test_ir_op_records_replay():
     for int_params in ([Bm, Tm, D, N, Gm], [Bm, Tm, D, N, Gm, 16]):
         y = ops.ir_op_forward(63, ins, int_params, out_shape=(Bm * Tm, D))
         assert_close(y, torch.from_numpy(z["b_y"]).reshape(Bm * Tm, D), TOL_F32, f"op 63 {int_params}")
+
+
+@pytest.mark.parametrize("dims", [(2, 200, 2, 128, 128), (1, 130, 3, 64, 96)])
+def test_float32_tensors_through_tensor_core_kernels(dims):
+    """MXB_GDN_F32_IO_BF16_OPERANDS: float32 tensors in and out, bf16 operands inside.  The results must be
+    exactly those of the bf16 entry on the rounded inputs (widened), stay within the bf16 tolerance of the oracle
+    on the float32 inputs, and the saved-forward backward must agree with the recomputing one."""
+    from mixlab_b200 import _lib
+    B, T, H, K, V = dims
+    flag = _lib.MXB_GDN_F32_IO_BF16_OPERANDS
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=77, io_dtype=torch.float32, with_grad_out=True, with_h0=True)
+    q, k, v, beta, g, do = (_dev(a[n]) for n in ("q", "k", "v", "beta", "g", "d_out"))
+    kw = dict(gate_is_log=True, h0=_dev(a["h0"]))
+    out, hT = ops.gated_delta_scan(q, k, v, beta, g, 64, return_final_state=True, flags=flag, **kw)
+    assert out.dtype == torch.float32
+    q16, k16, v16, do16 = (t.to(torch.bfloat16) for t in (q, k, v, do))
+    out16, hT16 = ops.gated_delta_scan(q16, k16, v16, beta, g, 64, return_final_state=True, **kw)
+    assert torch.equal(out, out16.float()) and torch.equal(hT, hT16)
+    ref_out, ref_state = _oracle_fwd(a, 64, h0=a["h0"])
+    assert_close(out, ref_out, TOL_BF16, "out")
+    assert_close(hT, ref_state, TOL_BF16, "hT")
+
+    dst = _dev(a["d_state"])
+    got = ops.gated_delta_scan_backward(q, k, v, beta, g, do, 64, d_final_state=dst, flags=flag, **kw)
+    want = ops.gated_delta_scan_backward(q16, k16, v16, beta, g, do16, 64, d_final_state=dst, **kw)
+    for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
+        assert got[name].dtype == torch.float32
+        assert torch.equal(got[name], want[name].float()), name
+    ops.gated_delta_scan(q, k, v, beta, g, 64, save_for_backward=True, flags=flag, **kw)
+    again = ops.gated_delta_scan_backward(q, k, v, beta, g, do, 64, d_final_state=dst, flags=flag, use_saved=True, **kw)
+    for name in ("dq", "dk", "dv", "dbeta", "dgate", "dh0"):
+        assert torch.equal(again[name], got[name]), name
+    # without the flag float32 tensors keep the full-fp32 kernels: the results differ from the rounded ones
+    exact = ops.gated_delta_scan(q, k, v, beta, g, 64, **kw)
+    assert not torch.equal(exact, out)
+    assert_close(exact, ref_out, TOL_F32, "out (fp32 kernels)")
