@@ -35,6 +35,8 @@ WORKLOADS = {
     "mamba3_train": dict(B=8, T=4096, nheads=32, headdim=64, N=128, G=1),
     "gdn_block": dict(B=8, T=4096, H=16, Dk=128, Dv=128),
     "mamba3_block": dict(B=8, T=4096, D=2048, N=128, G=1, K=4),
+    # the shape the reference's own scan benchmark is quoted on, in its per-channel float32 layout
+    "mamba3_ref_shape": dict(B=2, T=1024, D=128, N=16, G=4),
 }
 # Algorithmic work per unit: the bytes that must cross HBM if every intermediate stayed on chip.
 GDN_BYTES_PER_TOKEN_HEAD = 2840          # fwd 1032 + bwd read 1032 + bwd write 776
@@ -374,7 +376,31 @@ def build_mamba3_train(cx, batch):
                 cfg={"workload": "mamba3_train", **w, "io": "bf16", "layout": "head-broadcast dt/lambda/theta/a_log"})
 
 
-BUILDERS = {"gdn_train": build_gdn_train, "gdn_decode": build_gdn_decode, "gdn_block": build_gdn_block,
+def build_mamba3_ref_shape(cx, batch):
+    w = dict(WORKLOADS["mamba3_ref_shape"])
+    if batch > 0:
+        w["B"] = batch
+    B, T, D, N, G = w["B"], w["T"], w["D"], w["N"], w["G"]
+    a = cx.inputs.mamba3_inputs(B, T, D, 1, N, G=G, seed=4000 + cx.rank, per_head=False)
+    d = {k: a[k].to(cx.dev) for k in ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c", "dy")}
+    margs = [d[k] for k in ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")]
+    ops = cx.ops
+
+    def step():
+        ops.mamba3_selective_scan(*margs)
+        ops.mamba3_selective_scan_backward(*margs, d["dy"])
+
+    # fp32: forward reads x, dt, lambda [D], theta [D N/2], B, C [G N] and writes y; the backward reads those and
+    # dy and writes dx, ddt, dlambda, dtheta, dB, dC
+    per_token = 4 * ((D * (4 + N // 2) + 2 * G * N) + (D * (4 + N // 2) + 2 * G * N) + (D * (3 + N // 2) + 2 * G * N))
+    return dict(step=step, units=B * T, metric="mamba3_fwd_bwd_tokens_per_s", unit="tokens/s", dtype="f32",
+                alg_bytes=B * T * per_token, alg_flops=0.0, traffic=lambda kernels: None,
+                traffic_note="no byte capture for this workload (7 MB of tensors: it lives in L2)",
+                cfg={"workload": "mamba3_ref_shape", **w, "io": "f32", "layout": "per-channel dt/lambda/theta/a_log (the reference's)",
+                     "l2": "the whole problem fits L2; the step is bound by the T-long serial walk, not by HBM"})
+
+
+BUILDERS = {"mamba3_ref_shape": build_mamba3_ref_shape, "gdn_train": build_gdn_train, "gdn_decode": build_gdn_decode, "gdn_block": build_gdn_block,
             "mamba3_block": build_mamba3_block, "mamba3_train": build_mamba3_train}
 
 

@@ -22,9 +22,14 @@
 //
 // Backward: a checkpointing forward pass stores (h, phi) every W steps; the
 // reverse pass walks the windows backwards, replays each window into shared
-// memory and applies the closed-form adjoint step by step.  Sums over the
-// channels of a group (dB, dC) or of a head (head-broadcast gradients) and over
-// the batch (da_log) are accumulated with fp32 atomics into zeroed buffers.
+// memory and applies the closed-form adjoint step by step.  Every sum over
+// channels or over the batch has a fixed order, so the same inputs give the same
+// bits: the warps of a CTA are channels of one group and add their dB, dC rows
+// through shared memory once per step; CTAs that share a group write partial
+// rows that a second kernel adds in slice order; head-broadcast gradients and
+// da_log go through per-channel / per-batch partials in the same way.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace mxb {
@@ -40,7 +45,12 @@ struct M3P {
   const void* dy;
   void* dx;
   float *ddt, *dlam, *dtheta, *da_log;
-  float *db32, *dc32;  // fp32 accumulators [B,T,G,N]
+  float *db32, *dc32;  // head-broadcast kernels only: fp32 rows [B,T,G,N]
+  // channel kernels: CW channels (warps) per CTA, S = channels per group / CW slices per group
+  int CW, S;
+  float *pb32, *pc32;  // [B,T,G,S,N] rows summed over the CW channels of a CTA
+  float* hd;           // head-broadcast layout only: per-channel ddt, dlam, dtheta, 3 x [B,T,D]
+  float* dal_part;     // per-batch da_log: [B,D,N], or [B,D] in the head-broadcast layout
 };
 
 __device__ __forceinline__ float m3_softplus(float x) {
@@ -139,13 +149,17 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
 
 // ----------------------------------------------------------------- backward
 template <typename IO, int PR>
-__global__ void __launch_bounds__(128) mamba3_bwd_kernel(M3P p) {
+__global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int d = blockIdx.x * 4 + warp, b = blockIdx.y;
-  if (d >= p.D) return;
+  const int CW = p.CW;  // = blockDim.x / 32; divides the channels of a group, so every warp has a channel
+  const int d = blockIdx.x * CW + warp, b = blockIdx.y;
+  const int cpg = p.D / p.G, g = d / cpg, sl = (d % cpg) / CW;
   // per warp: [W][PR][3][32]  (h0_after, h1_after, phi)
   float* buf = smem + (size_t)warp * kM3Window * PR * 3 * 32;
+  // [2 (step parity)][2 (dB, dC)][CW][N]: the rows of one step, added over the warps by the first 2N threads
+  // while the warps already fill the other half with the next step (one barrier per step)
+  float* red = smem + (size_t)CW * kM3Window * PR * 3 * 32;
   auto slot = [&](int s, int r, int which) -> float& { return buf[((s * PR + r) * 3 + which) * 32 + lane]; };
   const M3Idx ix(p);
   const IO* X = static_cast<const IO*>(p.x);
@@ -270,10 +284,10 @@ __global__ void __launch_bounds__(128) mamba3_bwd_kernel(M3P p) {
           dh0[r] = al0 * up0;
           dh1[r] = al1 * up1;
           // rotation adjoint
-          atomicAdd(&p.db32[gi], c * gb0 - s * gb1);
-          atomicAdd(&p.db32[gi + 1], s * gb0 + c * gb1);
-          atomicAdd(&p.dc32[gi], c * gc0 - s * gc1);
-          atomicAdd(&p.dc32[gi + 1], s * gc0 + c * gc1);
+          float* rb = red + (size_t)(((t & 1) * 2 + 0) * CW + warp) * p.N + 2 * kp;
+          float* rc = red + (size_t)(((t & 1) * 2 + 1) * CW + warp) * p.N + 2 * kp;
+          *reinterpret_cast<float2*>(rb) = make_float2(c * gb0 - s * gb1, s * gb0 + c * gb1);
+          *reinterpret_cast<float2*>(rc) = make_float2(c * gc0 - s * gc1, s * gc0 + c * gc1);
           carry[r] += b1 * gb0 - b0 * gb1 + c1 * gc0 - c0 * gc1;
           const float th = p.theta[ix.theta(row, d, kp)];
           s_ddelta += carry[r] * th;
@@ -288,14 +302,23 @@ __global__ void __launch_bounds__(128) mamba3_bwd_kernel(M3P p) {
       pend_dx = s_pdx;
       if (lane == 0) {
         DX[row * p.D + d] = from_f32<IO>(s_dx);
-        if (per_head) {
-          atomicAdd(&p.ddt[ix.chan(row, d)], s_ddelta);
-          atomicAdd(&p.dlam[ix.chan(row, d)], s_dlam);
-          atomicAdd(&p.dtheta[ix.chan(row, d)], s_dtheta);
+        if (per_head) {  // per channel; m3_head_sum_kernel adds the channels of a head
+          const size_t btd = (size_t)p.B * p.T * p.D;
+          p.hd[row * p.D + d] = s_ddelta;
+          p.hd[btd + row * p.D + d] = s_dlam;
+          p.hd[2 * btd + row * p.D + d] = s_dtheta;
         } else {
           p.ddt[row * p.D + d] = s_ddelta;
           p.dlam[row * p.D + d] = s_dlam;
         }
+      }
+      __syncthreads();
+      for (int i = threadIdx.x; i < 2 * p.N; i += blockDim.x) {
+        const int which = i >= p.N, n = i - which * p.N;
+        const float* src = red + (size_t)(((t & 1) * 2 + which) * CW) * p.N + n;
+        float acc = 0.f;
+        for (int w2 = 0; w2 < CW; ++w2) acc += src[(size_t)w2 * p.N];
+        (which ? p.pc32 : p.pb32)[((row * p.G + g) * p.S + sl) * p.N + n] = acc;
       }
     }
   }
@@ -305,23 +328,75 @@ __global__ void __launch_bounds__(128) mamba3_bwd_kernel(M3P p) {
 #pragma unroll
     for (int r = 0; r < PR; ++r) s += dal0[r] + dal1[r];
     s = warp_sum(s);
-    if (lane == 0) atomicAdd(&p.da_log[ix.alog(d, 0)], s);
+    if (lane == 0) p.dal_part[(size_t)b * p.D + d] = s;
   } else {
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
       const int kp = lane + 32 * r;
       if (kp < p.Kp) {
-        atomicAdd(&p.da_log[(size_t)d * p.N + 2 * kp], dal0[r]);
-        atomicAdd(&p.da_log[(size_t)d * p.N + 2 * kp + 1], dal1[r]);
+        p.dal_part[((size_t)b * p.D + d) * p.N + 2 * kp] = dal0[r];
+        p.dal_part[((size_t)b * p.D + d) * p.N + 2 * kp + 1] = dal1[r];
       }
     }
   }
 }
 
+// dB[b,t,g,:] = the S slice rows of the group added in slice order, in the tensors' dtype.
 template <typename IO>
-__global__ void m3_cast_kernel(const float* __restrict__ src, IO* __restrict__ dst, size_t n) {
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
-    dst[i] = from_f32<IO>(src[i]);
+__global__ void __launch_bounds__(256) m3_bc_sum_kernel(const float* __restrict__ pb, const float* __restrict__ pc,
+                                                        IO* __restrict__ db, IO* __restrict__ dc, size_t rows, int S, int N) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows * N; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / N;
+    const int n = (int)(i - r * N);
+    float sb = 0.f, sc = 0.f;
+    for (int s = 0; s < S; ++s) {
+      sb += pb[(r * S + s) * N + n];
+      sc += pc[(r * S + s) * N + n];
+    }
+    db[i] = from_f32<IO>(sb);
+    dc[i] = from_f32<IO>(sc);
+  }
+}
+
+// Head-broadcast layout: ddt, dlam, dtheta [B,T,NH] = the per-channel values of a head added in channel order.
+__global__ void __launch_bounds__(256) m3_head_sum_kernel(const float* __restrict__ hd, float* __restrict__ ddt,
+                                                          float* __restrict__ dlam, float* __restrict__ dtheta,
+                                                          size_t rows, int D, int NH) {
+  const int cph = D / NH;
+  const size_t btd = rows * D;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows * NH; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / NH;
+    const int h = (int)(i - r * NH);
+    float a = 0.f, l = 0.f, th = 0.f;
+    for (int c = 0; c < cph; ++c) {
+      const size_t j = r * D + (size_t)h * cph + c;
+      a += hd[j];
+      l += hd[btd + j];
+      th += hd[2 * btd + j];
+    }
+    ddt[i] = a;
+    dlam[i] = l;
+    dtheta[i] = th;
+  }
+}
+
+// da_log = the per-batch partials added in batch order ([D,N]), and over the channels of a head ([NH]).
+__global__ void __launch_bounds__(256) m3_dalog_sum_kernel(const float* __restrict__ part, float* __restrict__ out, int B,
+                                                           int D, int N, int NH) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (NH > 0) {
+    if (i >= NH) return;
+    const int cph = D / NH;
+    float s = 0.f;
+    for (int b = 0; b < B; ++b)
+      for (int c = 0; c < cph; ++c) s += part[(size_t)b * D + i * cph + c];
+    out[i] = s;
+  } else {
+    if (i >= D * N) return;
+    float s = 0.f;
+    for (int b = 0; b < B; ++b) s += part[(size_t)b * D * N + i];
+    out[i] = s;
+  }
 }
 
 // --------------------------------------------------------------------- host
@@ -358,10 +433,20 @@ bool mamba3_supported(const mxb_mamba3_desc* d) {
   return true;
 }
 
+// Channels (warps) per CTA of the channel backward: the largest divisor of the channels of a group that fits the
+// CTA (8 warps; 4 where a lane owns four state pairs and the replay buffers are that much larger).
+static int m3_channel_warps(const M3P& p) {
+  const int cpg = p.D / p.G, cap = p.Kp > 64 ? 4 : 8;
+  int cw = 1;
+  for (int c = 1; c <= cap; ++c)
+    if (cpg % c == 0) cw = c;
+  return cw;
+}
+
 static size_t carve_m3(M3P& p, void* ws, bool io_f32, size_t partial_floats = 0, float** pb = nullptr,
                        float** pc = nullptr) {
   Carver cv(ws);
-  if (partial_floats) {
+  if (partial_floats) {  // head-broadcast kernels
     float* a = cv.take<float>(partial_floats);
     float* b2 = cv.take<float>(partial_floats);
     if (pb) *pb = a;
@@ -369,10 +454,20 @@ static size_t carve_m3(M3P& p, void* ws, bool io_f32, size_t partial_floats = 0,
   }
   p.ck_h = cv.take<float>((size_t)p.B * p.nW * p.D * p.N);
   p.ck_phi = cv.take<float>((size_t)p.B * p.nW * p.D * p.Kp);
-  if (!io_f32) {
-    p.db32 = cv.take<float>((size_t)p.B * p.T * p.G * p.N);
-    p.dc32 = cv.take<float>((size_t)p.B * p.T * p.G * p.N);
+  if (partial_floats) {
+    if (!io_f32) {
+      p.db32 = cv.take<float>((size_t)p.B * p.T * p.G * p.N);
+      p.dc32 = cv.take<float>((size_t)p.B * p.T * p.G * p.N);
+    }
+    return cv.bytes();
   }
+  p.CW = m3_channel_warps(p);
+  p.S = p.D / p.G / p.CW;
+  const size_t rows = (size_t)p.B * p.T * p.G * p.S * p.N;
+  p.pb32 = cv.take<float>(rows);
+  p.pc32 = cv.take<float>(rows);
+  if (p.NH > 0) p.hd = cv.take<float>(3 * (size_t)p.B * p.T * p.D);
+  p.dal_part = cv.take<float>(p.NH > 0 ? (size_t)p.B * p.D : (size_t)p.B * p.D * p.N);
   return cv.bytes();
 }
 
@@ -399,12 +494,12 @@ static mxb_status m3_fwd_pr(const M3P& p, cudaStream_t st) {
 
 template <typename IO, int PR>
 static mxb_status m3_bwd_launch(const M3P& p, cudaStream_t st) {
-  const size_t sm = sizeof(float) * 4 * kM3Window * PR * 3 * 32;
+  const size_t sm = sizeof(float) * ((size_t)p.CW * kM3Window * PR * 3 * 32 + 4 * (size_t)p.CW * p.N);
   if (sm > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(mamba3_bwd_kernel<IO, PR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
   }
-  MXB_LAUNCH("mamba3_bwd_kernel", st, (mamba3_bwd_kernel<IO, PR><<<dim3((p.D + 3) / 4, p.B), 128, sm, st>>>(p)));
+  MXB_LAUNCH("mamba3_bwd_kernel", st, (mamba3_bwd_kernel<IO, PR><<<dim3(p.D / p.CW, p.B), 32 * p.CW, sm, st>>>(p)));
   return check_launch("mamba3_bwd_kernel");
 }
 template <typename IO>
@@ -450,38 +545,46 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
   float *pb = nullptr, *pc = nullptr;
   if (head_bwd) p.nW = (d->T + mamba3_head_window() - 1) / mamba3_head_window();
   carve_m3(p, ws, f32, head_bwd ? mamba3_head_partial_floats(d) : 0, &pb, &pc);
-  const size_t nbc = (size_t)p.B * p.T * p.G * p.N;
-  if (f32) { p.db32 = static_cast<float*>(db); p.dc32 = static_cast<float*>(dc); }
-  cudaError_t e = cudaMemsetAsync(p.db32, 0, nbc * sizeof(float), st);
-  if (e == cudaSuccess) e = cudaMemsetAsync(p.dc32, 0, nbc * sizeof(float), st);
-  const size_t nal = p.NH > 0 ? (size_t)p.NH : (size_t)p.D * p.N;
-  if (e == cudaSuccess) e = cudaMemsetAsync(da_log, 0, nal * sizeof(float), st);
-  if (p.NH > 0) {
+  mxb_status s;
+  if (head_bwd) {
+    const size_t nbc = (size_t)p.B * p.T * p.G * p.N;
+    if (f32) { p.db32 = static_cast<float*>(db); p.dc32 = static_cast<float*>(dc); }
+    // the CTA-per-head kernels add their head-broadcast gradients with atomics into zeroed buffers
+    cudaError_t e = cudaMemsetAsync(p.db32, 0, nbc * sizeof(float), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(p.dc32, 0, nbc * sizeof(float), st);
+    if (e == cudaSuccess) e = cudaMemsetAsync(da_log, 0, (size_t)p.NH * sizeof(float), st);
     const size_t nh = (size_t)p.B * p.T * p.NH * sizeof(float);
     if (e == cudaSuccess) e = cudaMemsetAsync(ddt, 0, nh, st);
     if (e == cudaSuccess) e = cudaMemsetAsync(dlam, 0, nh, st);
     if (e == cudaSuccess) e = cudaMemsetAsync(dtheta, 0, nh, st);
-  }
-  if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
-  mxb_status s;
-  if (head_bwd) {
-    // CTA-per-head kernels: checkpoint pass (y == nullptr), reverse pass, reduction of the dB/dC partials
+    if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
+    // checkpoint pass (y == nullptr), reverse pass, reduction of the dB/dC partials
     s = mamba3_head_fwd(d, x, dt, lam, theta, a_log, b, c, nullptr, p.ck_h, p.ck_phi, st);
     if (s != MXB_OK) return s;
     return mamba3_head_bwd(d, x, dt, lam, theta, a_log, b, c, dy, dx, ddt, dlam, dtheta, da_log, db, dc, pb, pc,
                            p.ck_h, p.ck_phi, st);
-  } else {
-    s = f32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);  // checkpoint pass (y == nullptr)
-    if (s != MXB_OK) return s;
-    s = f32 ? m3_bwd_pr<float>(p, st) : m3_bwd_pr<__nv_bfloat16>(p, st);
   }
+  // warp-per-channel kernels: checkpoint pass (y == nullptr), reverse pass, fixed-order sums of the partials
+  s = f32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);
   if (s != MXB_OK) return s;
-  if (!f32) {
-    MXB_LAUNCH("m3_cast_kernel", st, (m3_cast_kernel<__nv_bfloat16><<<592, 256, 0, st>>>(p.db32, static_cast<__nv_bfloat16*>(db), nbc)));
-    MXB_LAUNCH("m3_cast_kernel", st, (m3_cast_kernel<__nv_bfloat16><<<592, 256, 0, st>>>(p.dc32, static_cast<__nv_bfloat16*>(dc), nbc)));
-    s = check_launch("m3_cast_kernel");
+  s = f32 ? m3_bwd_pr<float>(p, st) : m3_bwd_pr<__nv_bfloat16>(p, st);
+  if (s != MXB_OK) return s;
+  const size_t rows = (size_t)p.B * p.T * p.G;
+  const int grid = (int)std::min<size_t>((rows * p.N + 255) / 256, 148 * 8);
+  if (f32)
+    MXB_LAUNCH("m3_bc_sum_kernel", st, (m3_bc_sum_kernel<float><<<grid, 256, 0, st>>>(
+        p.pb32, p.pc32, static_cast<float*>(db), static_cast<float*>(dc), rows, p.S, p.N)));
+  else
+    MXB_LAUNCH("m3_bc_sum_kernel", st, (m3_bc_sum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        p.pb32, p.pc32, static_cast<__nv_bfloat16*>(db), static_cast<__nv_bfloat16*>(dc), rows, p.S, p.N)));
+  if (p.NH > 0) {
+    const size_t bt = (size_t)p.B * p.T;
+    const int gh = (int)std::min<size_t>((bt * p.NH + 255) / 256, 148 * 8);
+    MXB_LAUNCH("m3_head_sum_kernel", st, (m3_head_sum_kernel<<<gh, 256, 0, st>>>(p.hd, ddt, dlam, dtheta, bt, p.D, p.NH)));
   }
-  return s;
+  const int nal = p.NH > 0 ? p.NH : p.D * p.N;
+  MXB_LAUNCH("m3_dalog_sum_kernel", st, (m3_dalog_sum_kernel<<<(nal + 255) / 256, 256, 0, st>>>(p.dal_part, da_log, p.B, p.D, p.N, p.NH)));
+  return check_launch("mamba3 channel backward sums");
 }
 
 }  // namespace mxb

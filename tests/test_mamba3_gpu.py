@@ -31,6 +31,7 @@ def _check_grads(got, want, tol):
 @pytest.mark.parametrize("shape", [
     (2, 8, 4, 8, 1), (2, 8, 4, 8, 2),            # the reference test's shapes
     (2, 130, 8, 8, 2), (2, 130, 8, 64, 1), (1, 130, 8, 128, 2), (1, 33, 4, 256, 1),
+    (1, 70, 24, 16, 1), (2, 50, 40, 8, 2),        # several CTAs per group: partial rows added in slice order
 ])
 def test_per_channel_fp32(shape):
     B, T, D, N, Gr = shape
@@ -189,3 +190,35 @@ def test_chunked_kernels_without_tma_match():
     g2 = ops.mamba3_selective_scan_backward(*dev, dy, nheads=H, flags=_lib.MXB_MAMBA3_NO_TMA)
     for name in GRADS:
         assert torch.equal(g1[name], g2[name]), name
+
+
+@pytest.mark.parametrize("case", [(2, 1024, 128, 16, 4, False, torch.float32),   # the shape the reference publishes
+                                  (2, 100, 48, 8, 1, False, torch.bfloat16),
+                                  (2, 100, 32, 16, 2, True, torch.float32)])
+def test_channel_kernels_repeat_bit_for_bit(case):
+    """The warp-per-channel backward adds over channels and over the batch in a fixed order (no floating-point
+    atomics): two runs on the same inputs agree in every bit, and the result matches the oracle."""
+    from mixlab_b200 import _lib
+    B, T, D, N, Gr, per_head, io = case
+    nheads = D // 8 if per_head else 1
+    a = inputs.mamba3_inputs(B, T, nheads if per_head else D, 8 if per_head else 1, N, G=Gr, seed=9,
+                             io_dtype=io, per_head=per_head)
+    dev = [_dev(a[k]) for k in ARGS]
+    kw = dict(nheads=nheads, flags=_lib.MXB_MAMBA3_CHANNEL_KERNELS) if per_head else {}
+    first = ops.mamba3_selective_scan_backward(*dev, _dev(a["dy"]), **kw)
+    first = {k: v.clone() for k, v in first.items()}
+    ops.mamba3_selective_scan(*dev, **kw)  # something else through the workspace in between
+    second = ops.mamba3_selective_scan_backward(*dev, _dev(a["dy"]), **kw)
+    for name in GRADS:
+        assert torch.equal(first[name], second[name]), name
+    e = inputs.mamba3_expand_per_head(a) if per_head else a
+    f = [e[k].double() for k in ARGS]
+    _, want = mamba3.scan_vjp(*f, a["dy"].double())
+    if per_head:  # gradients of broadcast parameters are the sums over what they were broadcast to
+        P = 8
+        want = dict(want)
+        want["ddt"] = want["ddt"].reshape(B, T, nheads, P).sum(-1)
+        want["dlambda"] = want["dlambda"].reshape(B, T, nheads, P).sum(-1)
+        want["dtheta"] = want["dtheta"].reshape(B, T, nheads, P, N // 2).sum((-1, -2))
+        want["da_log"] = want["da_log"].reshape(nheads, P, N).sum((-1, -2))
+    _check_grads(second, want, 1e-4 if io == torch.float32 else 2e-2)
