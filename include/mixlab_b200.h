@@ -244,6 +244,13 @@ enum {
                                       the copy engine (the path taken anyway when the driver offers no
                                       tensor-map entry point).  Both stagings need x, b, c, y, dy, dx, db,
                                       dc 16-byte aligned: other pointers return MXB_ERR_ALIGNMENT */
+  MXB_MAMBA3_SERIAL_WALK = 32,     /* warp-per-channel kernels: one warp walks the whole sequence of its
+                                      (batch, channel) pair, also where there are too few pairs to fill the GPU */
+  MXB_MAMBA3_WINDOW_PARALLEL = 64, /* warp-per-channel kernels: one warp per (batch, channel, window of 16
+                                      steps) with scans over the windows in between, also where the pairs alone
+                                      would fill the GPU (the window form does about twice the arithmetic; by
+                                      default it is taken when 2 B D <= 148 x 64 warps).  The forward then needs
+                                      the workspace mxb_mamba3_fwd_workspace_bytes reports. */
   MXB_MAMBA3_BWD_USE_SAVED = 8     /* backward: the workspace is the one a forward call with
                                       MXB_MAMBA3_SAVE_FOR_BWD just filled for the same inputs; the forward
                                       recompute is skipped.  Honoured by the chunked tensor-core kernels;

@@ -22,6 +22,8 @@ MXB_MAMBA3_RECURRENT_KERNELS = 2
 MXB_MAMBA3_SAVE_FOR_BWD = 4
 MXB_MAMBA3_BWD_USE_SAVED = 8
 MXB_MAMBA3_NO_TMA = 16
+MXB_MAMBA3_SERIAL_WALK = 32
+MXB_MAMBA3_WINDOW_PARALLEL = 64
 
 
 class MxbError(RuntimeError):

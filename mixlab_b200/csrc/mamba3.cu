@@ -16,6 +16,20 @@
 // at 64, gpu/mamba3_cuda_primitive.cpp:22).  The cumulative angle is kept wrapped
 // to [-pi, pi] so fp32 keeps its resolution over thousands of steps.
 //
+// Short problems (few batch x channel pairs) would leave most of the GPU idle behind T-long walks, so the
+// kernels also run window-parallel: one warp per (batch, channel, window of kM3Window steps).  Every carried
+// quantity is linear in what crosses a window boundary, which turns the walk into local walks plus short scans
+// over the windows:
+//   forward   window sums of dt theta -> scan: angle at each window start
+//             local walks from a zero state -> scan with exp(A sum dt): state at each window start
+//             walks from the true start states write y
+//   backward  (after the same two scans) local reverse walks of dh from zero -> reverse scan: dh entering each
+//             window and the `up` value of its first step, from which the window before takes the trapezoid's
+//             look-back terms; true reverse walks with window-local angle-gradient sums; reverse scan of those
+//             sums; one pass adds the later windows' sums to ddt and dtheta.
+// The walks cost about twice the serial arithmetic, so the serial kernels stay for shapes whose (batch, channel)
+// pairs fill the GPU by themselves.
+//
 // Two parameter layouts share the kernels through index helpers: the
 // reference's per-channel one, and a head-broadcast one where dt, lambda, theta
 // and a_log carry one value per (b,t,head) / per head.
@@ -50,7 +64,11 @@ struct M3P {
   int CW, S;
   float *pb32, *pc32;  // [B,T,G,S,N] rows summed over the CW channels of a CTA
   float* hd;           // head-broadcast layout only: per-channel ddt, dlam, dtheta, 3 x [B,T,D]
-  float* dal_part;     // per-batch da_log: [B,D,N], or [B,D] in the head-broadcast layout
+  float* dal_part;     // per-batch (window-parallel: per batch and window) da_log: [.,D,N], or [.,D] head-broadcast
+  // window-parallel kernels
+  float* dtsum;        // [B,nW,D] sum of dt over the window
+  float *dhk, *upk;    // [B,nW,D,N]: dh entering the window from later steps; `up` of the window's first step
+  float* ang;          // [B,nW,D,Kp]: angle-gradient sum of the window, then of all later windows
 };
 
 __device__ __forceinline__ float m3_softplus(float x) {
@@ -80,10 +98,13 @@ struct M3Idx {
 
 // ------------------------------------------------------------------ forward
 // Also the checkpoint pass of the backward (y == nullptr, ck_h != nullptr).
-template <typename IO, int PR>
+// MODE 0: the whole sequence (also the checkpoint pass of the serial backward: y == nullptr, ck_h != nullptr).
+// MODE 1: one window from a zero state and the window's start angle; leaves the local end state in ck_h.
+// MODE 2: one window from the true start state in ck_h; writes y.
+template <typename IO, int PR, int MODE>
 __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int d = blockIdx.x * 8 + warp, b = blockIdx.y;
+  const int d = blockIdx.x * 8 + warp, b = MODE == 0 ? blockIdx.y : blockIdx.z;
   if (d >= p.D) return;
   const M3Idx ix(p);
   const IO* X = static_cast<const IO*>(p.x);
@@ -99,10 +120,35 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
     A1[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp + 1)]) : 0.f;
     h0[r] = h1[r] = phi[r] = pb0[r] = pb1[r] = 0.f;
   }
+  const int ts = MODE == 0 ? 0 : (int)blockIdx.y * kM3Window;
+  const int te = MODE == 0 ? p.T : min(p.T, ts + kM3Window);
+  const size_t wrow_w = MODE == 0 ? 0 : ((size_t)b * p.nW + blockIdx.y) * p.D + d;
   float px = 0.f;
-  for (int t = 0; t < p.T; ++t) {
+  if (MODE != 0) {
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) {
+        phi[r] = p.ck_phi[wrow_w * p.Kp + kp];
+        if (MODE == 2) {
+          h0[r] = p.ck_h[wrow_w * p.N + 2 * kp];
+          h1[r] = p.ck_h[wrow_w * p.N + 2 * kp + 1];
+        }
+        if (ts > 0) {  // rotated B of the step before the window, at the window's start angle
+          float s, c;
+          sincosf(phi[r], &s, &c);
+          const size_t gi = ix.grp((size_t)b * p.T + ts - 1, d, 2 * kp);
+          const float be = to_f32(Bp[gi]), bo = to_f32(Bp[gi + 1]);
+          pb0[r] = c * be + s * bo;
+          pb1[r] = -s * be + c * bo;
+        }
+      }
+    }
+    if (ts > 0) px = to_f32(X[((size_t)b * p.T + ts - 1) * p.D + d]);
+  }
+  for (int t = ts; t < te; ++t) {
     const size_t row = (size_t)b * p.T + t;
-    if (p.ck_h && (t % kM3Window) == 0) {
+    if (MODE == 0 && p.ck_h && (t % kM3Window) == 0) {
       const size_t wrow = ((size_t)b * p.nW + t / kM3Window) * p.D + d;
 #pragma unroll
       for (int r = 0; r < PR; ++r) {
@@ -128,32 +174,242 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
         sincosf(phi[r], &s, &c);
         const size_t gi = ix.grp(row, d, 2 * kp);
         const float be = to_f32(Bp[gi]), bo = to_f32(Bp[gi + 1]);
-        const float ce = to_f32(Cp[gi]), co = to_f32(Cp[gi + 1]);
         const float b0 = c * be + s * bo, b1 = -s * be + c * bo;
-        const float c0 = c * ce + s * co, c1 = -s * ce + c * co;
         const float al0 = expf(dt * A0[r]), al1 = expf(dt * A1[r]);
         h0[r] = al0 * h0[r] + gamma * b0 * x + bfac * al0 * pb0[r] * px;
         h1[r] = al1 * h1[r] + gamma * b1 * x + bfac * al1 * pb1[r] * px;
-        part += h0[r] * c0 + h1[r] * c1;
+        if (MODE != 1) {
+          const float ce = to_f32(Cp[gi]), co = to_f32(Cp[gi + 1]);
+          const float c0 = c * ce + s * co, c1 = -s * ce + c * co;
+          part += h0[r] * c0 + h1[r] * c1;
+        }
         pb0[r] = b0;
         pb1[r] = b1;
       }
     }
     px = x;  // t = 0 uses px = 0, which realises the [t>0] factor
-    if (Y) {
+    if (MODE != 1 && Y) {
       part = warp_sum(part);
       if (lane == 0) Y[row * p.D + d] = from_f32<IO>(part);
+    }
+  }
+  if (MODE == 1) {
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) {
+        p.ck_h[wrow_w * p.N + 2 * kp] = h0[r];
+        p.ck_h[wrow_w * p.N + 2 * kp + 1] = h1[r];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------- window-parallel: sums and scans
+// Sum of dt theta (per state pair) and of dt over each window.
+template <int PR>
+__global__ void __launch_bounds__(256) m3w_phase_kernel(M3P p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int d = blockIdx.x * 8 + warp, w = blockIdx.y, b = blockIdx.z;
+  if (d >= p.D) return;
+  const M3Idx ix(p);
+  const int ts = w * kM3Window, te = min(p.T, ts + kM3Window);
+  float ph[PR], dts = 0.f;
+#pragma unroll
+  for (int r = 0; r < PR; ++r) ph[r] = 0.f;
+  for (int t = ts; t < te; ++t) {
+    const size_t row = (size_t)b * p.T + t;
+    const float dt = m3_softplus(p.dt[ix.chan(row, d)]);
+    dts += dt;
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) ph[r] = fmaf(dt, p.theta[ix.theta(row, d, kp)], ph[r]);
+    }
+  }
+  const size_t wrow = ((size_t)b * p.nW + w) * p.D + d;
+#pragma unroll
+  for (int r = 0; r < PR; ++r) {
+    const int kp = lane + 32 * r;
+    if (kp < p.Kp) p.ck_phi[wrow * p.Kp + kp] = ph[r];
+  }
+  if (lane == 0) p.dtsum[wrow] = dts;
+}
+
+// ck_phi: window sums -> wrapped angle at each window start (exclusive scan over the windows).
+__global__ void __launch_bounds__(256) m3w_phase_scan_kernel(M3P p) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)p.B * p.D * p.Kp) return;
+  const size_t per = (size_t)p.D * p.Kp, b = i / per, rem = i - b * per;
+  float run = 0.f;
+  for (int w = 0; w < p.nW; ++w) {
+    const size_t idx = (b * p.nW + w) * per + rem;
+    const float loc = p.ck_phi[idx];
+    p.ck_phi[idx] = run;
+    run = m3_wrap(run + loc);
+  }
+}
+
+// ck_h: local end states -> true state at each window start:  H <- exp(A sum dt) H + local.
+__global__ void __launch_bounds__(256) m3w_state_scan_kernel(M3P p) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)p.B * p.D * p.N) return;
+  const M3Idx ix(p);
+  const size_t per = (size_t)p.D * p.N, b = i / per, rem = i - b * per;
+  const int d = (int)(rem / p.N), n = (int)(rem - (size_t)d * p.N);
+  const float A = -expf(p.a_log[ix.alog(d, n)]);
+  float H = 0.f;
+  for (int w = 0; w < p.nW; ++w) {
+    const size_t idx = (b * p.nW + w) * per + rem;
+    const float loc = p.ck_h[idx];
+    p.ck_h[idx] = H;
+    H = fmaf(expf(A * p.dtsum[(b * p.nW + w) * p.D + d]), H, loc);
+  }
+}
+
+// Reverse walk of dh alone through one window, from zero:  up_t = dh_t + dy_t Crot_t,  dh_{t-1} = alpha_t up_t.
+// Leaves the local dh that leaves the window at its start (dhk) and the local up of its first step (upk).
+template <typename IO, int PR>
+__global__ void __launch_bounds__(256) m3w_dh_local_kernel(M3P p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int d = blockIdx.x * 8 + warp, w = blockIdx.y, b = blockIdx.z;
+  if (d >= p.D) return;
+  const M3Idx ix(p);
+  const IO* Cp = static_cast<const IO*>(p.c);
+  const IO* DY = static_cast<const IO*>(p.dy);
+  const int ts = w * kM3Window, te = min(p.T, ts + kM3Window);
+  const size_t wrow = ((size_t)b * p.nW + w) * p.D + d;
+  float A0[PR], A1[PR], phi[PR], dh0[PR], dh1[PR], u0[PR], u1[PR];
+#pragma unroll
+  for (int r = 0; r < PR; ++r) {
+    const int kp = lane + 32 * r;
+    const bool act = kp < p.Kp;
+    A0[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp)]) : 0.f;
+    A1[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp + 1)]) : 0.f;
+    phi[r] = act ? p.ck_phi[wrow * p.Kp + kp] : 0.f;
+    dh0[r] = dh1[r] = u0[r] = u1[r] = 0.f;
+  }
+  for (int t = ts; t < te; ++t) {  // the angle of the window's last step
+    const size_t row = (size_t)b * p.T + t;
+    const float dt = m3_softplus(p.dt[ix.chan(row, d)]);
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) phi[r] = m3_wrap(fmaf(dt, p.theta[ix.theta(row, d, kp)], phi[r]));
+    }
+  }
+  for (int t = te - 1; t >= ts; --t) {
+    const size_t row = (size_t)b * p.T + t;
+    const float dt = m3_softplus(p.dt[ix.chan(row, d)]);
+    const float dy = to_f32(DY[row * p.D + d]);
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) {
+        float s, c;
+        sincosf(phi[r], &s, &c);
+        const size_t gi = ix.grp(row, d, 2 * kp);
+        const float ce = to_f32(Cp[gi]), co = to_f32(Cp[gi + 1]);
+        u0[r] = fmaf(dy, c * ce + s * co, dh0[r]);
+        u1[r] = fmaf(dy, -s * ce + c * co, dh1[r]);
+        dh0[r] = expf(dt * A0[r]) * u0[r];
+        dh1[r] = expf(dt * A1[r]) * u1[r];
+        phi[r] = m3_wrap(fmaf(-dt, p.theta[ix.theta(row, d, kp)], phi[r]));  // back to the step before
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < PR; ++r) {
+    const int kp = lane + 32 * r;
+    if (kp < p.Kp) {
+      p.dhk[wrow * p.N + 2 * kp] = dh0[r];
+      p.dhk[wrow * p.N + 2 * kp + 1] = dh1[r];
+      p.upk[wrow * p.N + 2 * kp] = u0[r];
+      p.upk[wrow * p.N + 2 * kp + 1] = u1[r];
+    }
+  }
+}
+
+// Reverse scan over the windows: dhk <- dh entering the window from later steps (DH); upk <- true up of the
+// window's first step = (decay over the window's other steps) DH + local;  DH <- (decay over the window) DH + local.
+__global__ void __launch_bounds__(256) m3w_dh_scan_kernel(M3P p) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)p.B * p.D * p.N) return;
+  const M3Idx ix(p);
+  const size_t per = (size_t)p.D * p.N, b = i / per, rem = i - b * per;
+  const int d = (int)(rem / p.N), n = (int)(rem - (size_t)d * p.N);
+  const float A = -expf(p.a_log[ix.alog(d, n)]);
+  float DH = 0.f;
+  for (int w = p.nW - 1; w >= 0; --w) {
+    const size_t idx = (b * p.nW + w) * per + rem;
+    const float loc_dh = p.dhk[idx], loc_up = p.upk[idx];
+    const float dts = p.dtsum[(b * p.nW + w) * p.D + d];
+    const float dt0 = m3_softplus(p.dt[ix.chan(b * p.T + (size_t)w * kM3Window, d)]);
+    p.dhk[idx] = DH;
+    p.upk[idx] = fmaf(expf(A * (dts - dt0)), DH, loc_up);
+    DH = fmaf(expf(A * dts), DH, loc_dh);
+  }
+}
+
+// ang: per-window sums -> sum over all later windows (exclusive reverse scan).
+__global__ void __launch_bounds__(256) m3w_ang_scan_kernel(M3P p) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)p.B * p.D * p.Kp) return;
+  const size_t per = (size_t)p.D * p.Kp, b = i / per, rem = i - b * per;
+  float run = 0.f;
+  for (int w = p.nW - 1; w >= 0; --w) {
+    const size_t idx = (b * p.nW + w) * per + rem;
+    const float tot = p.ang[idx];
+    p.ang[idx] = run;
+    run += tot;
+  }
+}
+
+// The angle gradient reaches every earlier step: add the later windows' sums to ddt and dtheta of each step
+// (the walks used only the sums inside their own window).  One warp per (batch, step, channel).
+__global__ void __launch_bounds__(256) m3w_fix_kernel(M3P p) {
+  const int lane = threadIdx.x & 31;
+  const size_t wi = blockIdx.x * (size_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wi >= (size_t)p.B * p.T * p.D) return;
+  const M3Idx ix(p);
+  const size_t row = wi / p.D;
+  const int d = (int)(wi - row * p.D);
+  const size_t b = row / p.T;
+  const int w = (int)(row - b * p.T) / kM3Window;
+  if (w == p.nW - 1) return;  // nothing comes after the last window
+  const float dt_raw = p.dt[ix.chan(row, d)], dt = m3_softplus(dt_raw);
+  const float* off = p.ang + ((b * p.nW + w) * p.D + d) * p.Kp;
+  const bool per_head = p.NH > 0;
+  float s_th = 0.f, s_off = 0.f;
+  for (int kp = lane; kp < p.Kp; kp += 32) {
+    const float o = off[kp];
+    s_th = fmaf(o, p.theta[ix.theta(row, d, kp)], s_th);
+    if (per_head) s_off += o;
+    else p.dtheta[ix.theta(row, d, kp)] += o * dt;
+  }
+  s_th = warp_sum(s_th);
+  if (per_head) s_off = warp_sum(s_off);
+  if (lane == 0) {
+    if (per_head) {
+      const size_t btd = (size_t)p.B * p.T * p.D;
+      p.hd[row * p.D + d] += s_th * m3_sigmoid(dt_raw);
+      p.hd[2 * btd + row * p.D + d] += s_off * dt;
+    } else {
+      p.ddt[row * p.D + d] += s_th * m3_sigmoid(dt_raw);
     }
   }
 }
 
 // ----------------------------------------------------------------- backward
-template <typename IO, int PR>
+// WIN false: a warp walks all windows of its channel in reverse, carrying dh, the trapezoid's look-back terms and
+// the angle-gradient sum.  WIN true: a warp has one window (blockIdx.y); what enters it from later steps comes from
+// dhk / upk, and its angle-gradient sum and da_log share leave as per-window partials.
+template <typename IO, int PR, bool WIN>
 __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int CW = p.CW;  // = blockDim.x / 32; divides the channels of a group, so every warp has a channel
-  const int d = blockIdx.x * CW + warp, b = blockIdx.y;
+  const int d = blockIdx.x * CW + warp, b = WIN ? blockIdx.z : blockIdx.y;
   const int cpg = p.D / p.G, g = d / cpg, sl = (d % cpg) / CW;
   // per warp: [W][PR][3][32]  (h0_after, h1_after, phi)
   float* buf = smem + (size_t)warp * kM3Window * PR * 3 * 32;
@@ -179,8 +435,20 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
     dh0[r] = dh1[r] = carry[r] = pgb0[r] = pgb1[r] = dal0[r] = dal1[r] = 0.f;
   }
   float pend_dx = 0.f;  // contribution of step t+1 to dx_t (lane partial)
+  const int w_hi = WIN ? (int)blockIdx.y : p.nW - 1, w_lo = WIN ? (int)blockIdx.y : 0;
+  if (WIN) {
+    const size_t wrow = ((size_t)b * p.nW + w_hi) * p.D + d;
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) {
+        dh0[r] = p.dhk[wrow * p.N + 2 * kp];
+        dh1[r] = p.dhk[wrow * p.N + 2 * kp + 1];
+      }
+    }
+  }
 
-  for (int w = p.nW - 1; w >= 0; --w) {
+  for (int w = w_hi; w >= w_lo; --w) {
     const int ts = w * kM3Window, te = min(p.T, ts + kM3Window);
     const size_t wrow = ((size_t)b * p.nW + w) * p.D + d;
     // ---- replay the window forward, keeping h_after and phi per step ----
@@ -230,6 +498,27 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
         }
       }
       px = x;
+    }
+    if (WIN && te < p.T) {
+      // what the first step of the next window sends back to this window's last step: px and pb are x and the
+      // rotated B of step te-1 now, upk holds that step's `up`
+      const size_t row_e = (size_t)b * p.T + te;
+      const float dt_e = m3_softplus(p.dt[ix.chan(row_e, d)]);
+      const float bf_e = (1.f - m3_sigmoid(p.lam[ix.chan(row_e, d)])) * dt_e;
+      const size_t wnext = wrow + p.D;
+      float acc = 0.f;
+#pragma unroll
+      for (int r = 0; r < PR; ++r) {
+        const int kp = lane + 32 * r;
+        if (kp < p.Kp) {
+          const float bni0 = bf_e * expf(dt_e * A0[r]), bni1 = bf_e * expf(dt_e * A1[r]);
+          const float up0 = p.upk[wnext * p.N + 2 * kp], up1 = p.upk[wnext * p.N + 2 * kp + 1];
+          pgb0[r] = bni0 * px * up0;
+          pgb1[r] = bni1 * px * up1;
+          acc += bni0 * pb0[r] * up0 + bni1 * pb1[r] * up1;
+        }
+      }
+      pend_dx = acc;
     }
     // ---- reverse over the window ----
     for (int t = te - 1; t >= ts; --t) {
@@ -323,19 +612,27 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
     }
   }
   // da_log: d/d a_log = d/dA * A  (A = -exp(a_log)); the closed form above already carries A.
+  const size_t bw = WIN ? (size_t)b * p.nW + w_hi : (size_t)b;  // which partial of da_log this warp fills
+  if (WIN) {
+#pragma unroll
+    for (int r = 0; r < PR; ++r) {
+      const int kp = lane + 32 * r;
+      if (kp < p.Kp) p.ang[(bw * p.D + d) * p.Kp + kp] = carry[r];
+    }
+  }
   if (per_head) {
     float s = 0.f;
 #pragma unroll
     for (int r = 0; r < PR; ++r) s += dal0[r] + dal1[r];
     s = warp_sum(s);
-    if (lane == 0) p.dal_part[(size_t)b * p.D + d] = s;
+    if (lane == 0) p.dal_part[bw * p.D + d] = s;
   } else {
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
       const int kp = lane + 32 * r;
       if (kp < p.Kp) {
-        p.dal_part[((size_t)b * p.D + d) * p.N + 2 * kp] = dal0[r];
-        p.dal_part[((size_t)b * p.D + d) * p.N + 2 * kp + 1] = dal1[r];
+        p.dal_part[(bw * p.D + d) * p.N + 2 * kp] = dal0[r];
+        p.dal_part[(bw * p.D + d) * p.N + 2 * kp + 1] = dal1[r];
       }
     }
   }
@@ -443,8 +740,16 @@ static int m3_channel_warps(const M3P& p) {
   return cw;
 }
 
+// Window-parallel channel kernels: where the (batch, channel) pairs alone leave half of the GPU's warp slots empty,
+// unless a flag asks for one of the two forms.
+static bool m3_use_windows(const mxb_mamba3_desc* d) {
+  if (d->flags & MXB_MAMBA3_SERIAL_WALK) return false;
+  if (d->flags & MXB_MAMBA3_WINDOW_PARALLEL) return true;
+  return (size_t)d->B * d->D * 2 <= (size_t)148 * 64 && d->T > kM3Window;
+}
+
 static size_t carve_m3(M3P& p, void* ws, bool io_f32, size_t partial_floats = 0, float** pb = nullptr,
-                       float** pc = nullptr) {
+                       float** pc = nullptr, bool windows = false, bool bwd = true) {
   Carver cv(ws);
   if (partial_floats) {  // head-broadcast kernels
     float* a = cv.take<float>(partial_floats);
@@ -461,52 +766,102 @@ static size_t carve_m3(M3P& p, void* ws, bool io_f32, size_t partial_floats = 0,
     }
     return cv.bytes();
   }
+  if (windows) p.dtsum = cv.take<float>((size_t)p.B * p.nW * p.D);
+  if (!bwd) return cv.bytes();
   p.CW = m3_channel_warps(p);
   p.S = p.D / p.G / p.CW;
   const size_t rows = (size_t)p.B * p.T * p.G * p.S * p.N;
   p.pb32 = cv.take<float>(rows);
   p.pc32 = cv.take<float>(rows);
   if (p.NH > 0) p.hd = cv.take<float>(3 * (size_t)p.B * p.T * p.D);
-  p.dal_part = cv.take<float>(p.NH > 0 ? (size_t)p.B * p.D : (size_t)p.B * p.D * p.N);
+  const size_t parts = windows ? (size_t)p.B * p.nW : (size_t)p.B;
+  p.dal_part = cv.take<float>(p.NH > 0 ? parts * p.D : parts * p.D * p.N);
+  if (windows) {
+    p.dhk = cv.take<float>((size_t)p.B * p.nW * p.D * p.N);
+    p.upk = cv.take<float>((size_t)p.B * p.nW * p.D * p.N);
+    p.ang = cv.take<float>((size_t)p.B * p.nW * p.D * p.Kp);
+  }
   return cv.bytes();
 }
 
 size_t mamba3_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
   if (use_ssd(d)) return mamba3_ssd_workspace_bytes(d, bwd || (d->flags & MXB_MAMBA3_SAVE_FOR_BWD));
-  if (!bwd) return 0;
   M3P p = make_m3(d);
+  if (!bwd) {  // only the window-parallel channel kernels need scratch in the forward
+    const bool head = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_supported(d);
+    if (head || !m3_use_windows(d)) return 0;
+    return carve_m3(p, nullptr, d->io_dtype == MXB_F32, 0, nullptr, nullptr, true, false);
+  }
   const bool head = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
   if (head) p.nW = (d->T + mamba3_head_window() - 1) / mamba3_head_window();  // checkpoint spacing of the head kernels
-  return carve_m3(p, nullptr, d->io_dtype == MXB_F32, head ? mamba3_head_partial_floats(d) : 0);
+  return carve_m3(p, nullptr, d->io_dtype == MXB_F32, head ? mamba3_head_partial_floats(d) : 0, nullptr, nullptr,
+                  !head && m3_use_windows(d));
 }
 
-template <typename IO, int PR>
-static mxb_status m3_fwd_launch(const M3P& p, cudaStream_t st) {
-  MXB_LAUNCH("mamba3_fwd_kernel", st, (mamba3_fwd_kernel<IO, PR><<<dim3((p.D + 7) / 8, p.B), 256, 0, st>>>(p)));
+#define M3_PR_DISPATCH(p, call)                    \
+  do {                                            \
+    if ((p).Kp <= 32) { constexpr int PRV = 1; call; } \
+    else if ((p).Kp <= 64) { constexpr int PRV = 2; call; } \
+    else { constexpr int PRV = 4; call; }              \
+  } while (0)
+
+static int m3_blocks(size_t n) { return (int)((n + 255) / 256); }
+
+// Serial walk: y, or the checkpoints of the serial backward (p.y == nullptr).
+template <typename IO>
+static mxb_status m3_fwd_serial(const M3P& p, cudaStream_t st) {
+  M3_PR_DISPATCH(p, MXB_LAUNCH("mamba3_fwd_kernel", st,
+                               (mamba3_fwd_kernel<IO, PRV, 0><<<dim3((p.D + 7) / 8, p.B), 256, 0, st>>>(p))));
   return check_launch("mamba3_fwd_kernel");
 }
+
+// Window-parallel: angle and state at every window start (ck_phi, ck_h), then y if asked for.
 template <typename IO>
-static mxb_status m3_fwd_pr(const M3P& p, cudaStream_t st) {
-  if (p.Kp <= 32) return m3_fwd_launch<IO, 1>(p, st);
-  if (p.Kp <= 64) return m3_fwd_launch<IO, 2>(p, st);
-  return m3_fwd_launch<IO, 4>(p, st);
+static mxb_status m3_fwd_windows(const M3P& p, bool write_y, cudaStream_t st) {
+  const dim3 grid((p.D + 7) / 8, p.nW, p.B);
+  M3_PR_DISPATCH(p, MXB_LAUNCH("m3w_phase_kernel", st, (m3w_phase_kernel<PRV><<<grid, 256, 0, st>>>(p))));
+  MXB_LAUNCH("m3w_phase_scan_kernel", st,
+             (m3w_phase_scan_kernel<<<m3_blocks((size_t)p.B * p.D * p.Kp), 256, 0, st>>>(p)));
+  M3_PR_DISPATCH(p, MXB_LAUNCH("mamba3_fwd_kernel", st, (mamba3_fwd_kernel<IO, PRV, 1><<<grid, 256, 0, st>>>(p))));
+  MXB_LAUNCH("m3w_state_scan_kernel", st,
+             (m3w_state_scan_kernel<<<m3_blocks((size_t)p.B * p.D * p.N), 256, 0, st>>>(p)));
+  if (write_y)
+    M3_PR_DISPATCH(p, MXB_LAUNCH("mamba3_fwd_kernel", st, (mamba3_fwd_kernel<IO, PRV, 2><<<grid, 256, 0, st>>>(p))));
+  return check_launch("mamba3 window-parallel forward");
 }
 
-template <typename IO, int PR>
+template <typename IO, int PR, bool WIN>
 static mxb_status m3_bwd_launch(const M3P& p, cudaStream_t st) {
   const size_t sm = sizeof(float) * ((size_t)p.CW * kM3Window * PR * 3 * 32 + 4 * (size_t)p.CW * p.N);
   if (sm > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(mamba3_bwd_kernel<IO, PR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+    cudaError_t e =
+        cudaFuncSetAttribute(mamba3_bwd_kernel<IO, PR, WIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
   }
-  MXB_LAUNCH("mamba3_bwd_kernel", st, (mamba3_bwd_kernel<IO, PR><<<dim3(p.D / p.CW, p.B), 32 * p.CW, sm, st>>>(p)));
+  const dim3 grid = WIN ? dim3(p.D / p.CW, p.nW, p.B) : dim3(p.D / p.CW, p.B);
+  MXB_LAUNCH("mamba3_bwd_kernel", st, (mamba3_bwd_kernel<IO, PR, WIN><<<grid, 32 * p.CW, sm, st>>>(p)));
   return check_launch("mamba3_bwd_kernel");
 }
-template <typename IO>
+template <typename IO, bool WIN>
 static mxb_status m3_bwd_pr(const M3P& p, cudaStream_t st) {
-  if (p.Kp <= 32) return m3_bwd_launch<IO, 1>(p, st);
-  if (p.Kp <= 64) return m3_bwd_launch<IO, 2>(p, st);
-  return m3_bwd_launch<IO, 4>(p, st);
+  if (p.Kp <= 32) return m3_bwd_launch<IO, 1, WIN>(p, st);
+  if (p.Kp <= 64) return m3_bwd_launch<IO, 2, WIN>(p, st);
+  return m3_bwd_launch<IO, 4, WIN>(p, st);
+}
+
+// Window-parallel backward after m3_fwd_windows: dh at the window boundaries, the true walks, the angle fix-up.
+template <typename IO>
+static mxb_status m3_bwd_windows(const M3P& p, cudaStream_t st) {
+  const dim3 grid((p.D + 7) / 8, p.nW, p.B);
+  M3_PR_DISPATCH(p, MXB_LAUNCH("m3w_dh_local_kernel", st, (m3w_dh_local_kernel<IO, PRV><<<grid, 256, 0, st>>>(p))));
+  MXB_LAUNCH("m3w_dh_scan_kernel", st, (m3w_dh_scan_kernel<<<m3_blocks((size_t)p.B * p.D * p.N), 256, 0, st>>>(p)));
+  mxb_status s = check_launch("mamba3 window-parallel dh");
+  if (s != MXB_OK) return s;
+  s = m3_bwd_pr<IO, true>(p, st);
+  if (s != MXB_OK) return s;
+  MXB_LAUNCH("m3w_ang_scan_kernel", st, (m3w_ang_scan_kernel<<<m3_blocks((size_t)p.B * p.D * p.Kp), 256, 0, st>>>(p)));
+  MXB_LAUNCH("m3w_fix_kernel", st, (m3w_fix_kernel<<<m3_blocks((size_t)p.B * p.T * p.D * 32), 256, 0, st>>>(p)));
+  return check_launch("mamba3 window-parallel angle fix-up");
 }
 
 
@@ -524,7 +879,12 @@ mxb_status mamba3_fwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
     return mamba3_head_fwd(d, x, dt, lam, theta, a_log, b, c, y, nullptr, nullptr, st);
   M3P p = make_m3(d);
   p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c; p.y = y;
-  return d->io_dtype == MXB_F32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);
+  const bool f32 = d->io_dtype == MXB_F32;
+  if (m3_use_windows(d)) {
+    carve_m3(p, ws, f32, 0, nullptr, nullptr, true, false);
+    return f32 ? m3_fwd_windows<float>(p, true, st) : m3_fwd_windows<__nv_bfloat16>(p, true, st);
+  }
+  return f32 ? m3_fwd_serial<float>(p, st) : m3_fwd_serial<__nv_bfloat16>(p, st);
 }
 
 mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
@@ -544,7 +904,8 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
   const bool head_bwd = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
   float *pb = nullptr, *pc = nullptr;
   if (head_bwd) p.nW = (d->T + mamba3_head_window() - 1) / mamba3_head_window();
-  carve_m3(p, ws, f32, head_bwd ? mamba3_head_partial_floats(d) : 0, &pb, &pc);
+  const bool windows = !head_bwd && m3_use_windows(d);
+  carve_m3(p, ws, f32, head_bwd ? mamba3_head_partial_floats(d) : 0, &pb, &pc, windows);
   mxb_status s;
   if (head_bwd) {
     const size_t nbc = (size_t)p.B * p.T * p.G * p.N;
@@ -564,10 +925,16 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
     return mamba3_head_bwd(d, x, dt, lam, theta, a_log, b, c, dy, dx, ddt, dlam, dtheta, da_log, db, dc, pb, pc,
                            p.ck_h, p.ck_phi, st);
   }
-  // warp-per-channel kernels: checkpoint pass (y == nullptr), reverse pass, fixed-order sums of the partials
-  s = f32 ? m3_fwd_pr<float>(p, st) : m3_fwd_pr<__nv_bfloat16>(p, st);
-  if (s != MXB_OK) return s;
-  s = f32 ? m3_bwd_pr<float>(p, st) : m3_bwd_pr<__nv_bfloat16>(p, st);
+  // warp-per-channel kernels: checkpoints (no y), reverse pass, fixed-order sums of the partials
+  if (windows) {
+    s = f32 ? m3_fwd_windows<float>(p, false, st) : m3_fwd_windows<__nv_bfloat16>(p, false, st);
+    if (s != MXB_OK) return s;
+    s = f32 ? m3_bwd_windows<float>(p, st) : m3_bwd_windows<__nv_bfloat16>(p, st);
+  } else {
+    s = f32 ? m3_fwd_serial<float>(p, st) : m3_fwd_serial<__nv_bfloat16>(p, st);
+    if (s != MXB_OK) return s;
+    s = f32 ? m3_bwd_pr<float, false>(p, st) : m3_bwd_pr<__nv_bfloat16, false>(p, st);
+  }
   if (s != MXB_OK) return s;
   const size_t rows = (size_t)p.B * p.T * p.G;
   const int grid = (int)std::min<size_t>((rows * p.N + 255) / 256, 148 * 8);
@@ -583,7 +950,7 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
     MXB_LAUNCH("m3_head_sum_kernel", st, (m3_head_sum_kernel<<<gh, 256, 0, st>>>(p.hd, ddt, dlam, dtheta, bt, p.D, p.NH)));
   }
   const int nal = p.NH > 0 ? p.NH : p.D * p.N;
-  MXB_LAUNCH("m3_dalog_sum_kernel", st, (m3_dalog_sum_kernel<<<(nal + 255) / 256, 256, 0, st>>>(p.dal_part, da_log, p.B, p.D, p.N, p.NH)));
+  MXB_LAUNCH("m3_dalog_sum_kernel", st, (m3_dalog_sum_kernel<<<(nal + 255) / 256, 256, 0, st>>>(p.dal_part, da_log, windows ? p.B * p.nW : p.B, p.D, p.N, p.NH)));
   return check_launch("mamba3 channel backward sums");
 }
 

@@ -192,28 +192,34 @@ def test_chunked_kernels_without_tma_match():
         assert torch.equal(g1[name], g2[name]), name
 
 
+@pytest.mark.parametrize("form", ["serial", "windows"])
 @pytest.mark.parametrize("case", [(2, 1024, 128, 16, 4, False, torch.float32),   # the shape the reference publishes
                                   (2, 100, 48, 8, 1, False, torch.bfloat16),
+                                  (1, 70, 8, 256, 1, False, torch.float32),     # four state pairs per lane
                                   (2, 100, 32, 16, 2, True, torch.float32)])
-def test_channel_kernels_repeat_bit_for_bit(case):
-    """The warp-per-channel backward adds over channels and over the batch in a fixed order (no floating-point
-    atomics): two runs on the same inputs agree in every bit, and the result matches the oracle."""
+def test_channel_kernels_repeat_bit_for_bit(case, form):
+    """The warp-per-channel kernels, as one walk per (batch, channel) and window-parallel, add over channels, windows
+    and the batch in a fixed order (no floating-point atomics): two runs on the same inputs agree in every bit, and
+    the result matches the oracle."""
     from mixlab_b200 import _lib
     B, T, D, N, Gr, per_head, io = case
     nheads = D // 8 if per_head else 1
     a = inputs.mamba3_inputs(B, T, nheads if per_head else D, 8 if per_head else 1, N, G=Gr, seed=9,
                              io_dtype=io, per_head=per_head)
     dev = [_dev(a[k]) for k in ARGS]
-    kw = dict(nheads=nheads, flags=_lib.MXB_MAMBA3_CHANNEL_KERNELS) if per_head else {}
+    flags = _lib.MXB_MAMBA3_SERIAL_WALK if form == "serial" else _lib.MXB_MAMBA3_WINDOW_PARALLEL
+    kw = dict(flags=flags)
+    if per_head:
+        kw = dict(nheads=nheads, flags=flags | _lib.MXB_MAMBA3_CHANNEL_KERNELS)
     first = ops.mamba3_selective_scan_backward(*dev, _dev(a["dy"]), **kw)
     first = {k: v.clone() for k, v in first.items()}
-    ops.mamba3_selective_scan(*dev, **kw)  # something else through the workspace in between
+    y = ops.mamba3_selective_scan(*dev, **kw)  # something else through the workspace in between
     second = ops.mamba3_selective_scan_backward(*dev, _dev(a["dy"]), **kw)
     for name in GRADS:
         assert torch.equal(first[name], second[name]), name
     e = inputs.mamba3_expand_per_head(a) if per_head else a
     f = [e[k].double() for k in ARGS]
-    _, want = mamba3.scan_vjp(*f, a["dy"].double())
+    y_ref, want = mamba3.scan_vjp(*f, a["dy"].double())
     if per_head:  # gradients of broadcast parameters are the sums over what they were broadcast to
         P = 8
         want = dict(want)
@@ -221,4 +227,23 @@ def test_channel_kernels_repeat_bit_for_bit(case):
         want["dlambda"] = want["dlambda"].reshape(B, T, nheads, P).sum(-1)
         want["dtheta"] = want["dtheta"].reshape(B, T, nheads, P, N // 2).sum((-1, -2))
         want["da_log"] = want["da_log"].reshape(nheads, P, N).sum((-1, -2))
-    _check_grads(second, want, 1e-4 if io == torch.float32 else 2e-2)
+    tol = 1e-4 if io == torch.float32 else 2e-2
+    assert_close(y, y_ref, tol, "y")
+    _check_grads(second, want, tol)
+
+
+@pytest.mark.parametrize("shape", [(2, 130, 8, 8, 2), (1, 17, 4, 64, 1), (1, 16, 4, 8, 1), (2, 5, 4, 8, 2)])
+def test_window_parallel_matches_serial_walk(shape):
+    """Both forms of the channel kernels compute the same recurrence: windows that end inside the sequence, a last
+    window of one step, a single window."""
+    from mixlab_b200 import _lib
+    B, T, D, N, Gr = shape
+    a = inputs.mamba3_inputs(B, T, D, 1, N, G=Gr, seed=21, per_head=False)
+    dev = [_dev(a[k]) for k in ARGS]
+    ys = ops.mamba3_selective_scan(*dev, flags=_lib.MXB_MAMBA3_SERIAL_WALK)
+    yw = ops.mamba3_selective_scan(*dev, flags=_lib.MXB_MAMBA3_WINDOW_PARALLEL)
+    assert_close(yw, ys.double(), 1e-5, "y")
+    gs = ops.mamba3_selective_scan_backward(*dev, _dev(a["dy"]), flags=_lib.MXB_MAMBA3_SERIAL_WALK)
+    gw = ops.mamba3_selective_scan_backward(*dev, _dev(a["dy"]), flags=_lib.MXB_MAMBA3_WINDOW_PARALLEL)
+    for name in GRADS:
+        assert_close(gw[name], gs[name].double(), 1e-5, name)
