@@ -365,6 +365,9 @@ typedef struct {
   int32_t io_dtype;             /* MXB_F32 (the reference's only dtype) | MXB_BF16 */
 } mxb_ir_op;
 
+/* Kernel-selection bits for gated-delta records come from the environment variable MXB_IR_GDN_FLAGS (read once per
+ * process; only MXB_GDN_F32_IO_BF16_OPERANDS, MXB_GDN_FORCE_FP32_PATH and MXB_GDN_NO_TMA are honoured): the record
+ * itself is the reference's and has no field for them. */
 MXB_API size_t mxb_ir_op_workspace_bytes(const mxb_ir_op* op);
 MXB_API mxb_status mxb_ir_op_forward(const mxb_ir_op* op, void* workspace, size_t workspace_bytes,
                              void* stream);

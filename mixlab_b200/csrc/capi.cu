@@ -384,6 +384,14 @@ static mxb_status ir_op_to_gdn(const mxb_ir_op* op, mxb_gdn_desc* d) {
   const int32_t* ip = op->int_params;
   *d = mxb_gdn_desc{ip[0], ip[1], ip[2], ip[3], ip[4], op->n_int_params >= 6 ? ip[5] : 0, op->io_dtype, 0, 0};
   if (d->chunk < 0) d->chunk = 0;
+  // The record has no room for kernel-selection bits: a deployment that accepts bf16 operand rounding for its float32
+  // tensors says so once per process (MXB_IR_GDN_FLAGS=64 is MXB_GDN_F32_IO_BF16_OPERANDS), and its unchanged op
+  // records then reach the tensor-core kernels.
+  static const int32_t env_flags = [] {
+    const char* e = std::getenv("MXB_IR_GDN_FLAGS");
+    return e ? (int32_t)std::atoi(e) : 0;
+  }();
+  d->flags = env_flags & (MXB_GDN_F32_IO_BF16_OPERANDS | MXB_GDN_FORCE_FP32_PATH | MXB_GDN_NO_TMA);
   return MXB_OK;
 }
 static mxb_status ir_op_to_m3(const mxb_ir_op* op, mxb_mamba3_desc* d) {

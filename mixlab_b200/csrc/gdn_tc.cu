@@ -29,17 +29,21 @@ namespace mxb {
 // straight from the solve's registers, so k, q and v are staged raw.
 //
 // A CTA is a chain of dependent steps (copy -> MMA -> epilogue -> solve -> MMA -> epilogue -> stores) that leaves
-// the SM idle most of the time, so the kernel is sized for THREE CTAs per SM: 128 TMEM columns (u and w go through
-// the same columns one after the other) and 67 KB of shared memory, every region reused as soon as it is dead:
+// the SM idle most of the time, so the kernel is sized for FOUR CTAs per SM: 128 TMEM columns (u and w go through
+// the same columns one after the other) and 51 KB of shared memory, every region reused as soon as it is dead:
 //   [k;q] (32 KB, two slabs of 64 columns: k box then q box)  ->  v lands in the q boxes once q k^T is done
+//                                                              ->  k scaled to diag(d) k in place during the solve
 //                                                              ->  u image over v, w image over k
-//   Tb region: the P image on its way out, then T diag(beta)
-//   A / T fp32 matrix: then the bf16 T image on its way out
+//   A / T fp32 matrix (17 KB): then the bf16 T image on its way out and T diag(beta), the one operand of both
+//   products (w = (T diag beta)(diag(d) k)), over it
+//   P goes from the accumulator straight to the workspace (a warp's stores fill whole 128-byte lines of the image)
 // TMA = true: k, q, v arrive as cp.async.bulk.tensor tiles (boxes of 64 rows x 64 columns, 128-byte
 // swizzle; rows past the end of the sequence are zero-filled by the copy engine).  TMA = false: the same
 // tiles staged with cp.async into the same swizzled positions (kept as a cross-check and for drivers
 // without the tensor-map entry point).
-constexpr int kPrepSmem = 32768 + 2 * 8192 + C * LDA * 4 + 3 * C * 4 + 64 + 64 + 1024;
+constexpr int kPrepSmem = 32768 + C * LDA * 4 + 3 * C * 4 + 64 + 64 + 1024;
+static_assert(C * LDA * 4 >= 2 * 8192, "the T image and T diag(beta) go over the fp32 matrix");
+static_assert(4 * (kPrepSmem + 1024) <= 228 * 1024, "four CTAs per SM");
 
 using PrepMaps = RowMaps;
 
@@ -49,18 +53,17 @@ __device__ __forceinline__ uint4 pack8f(const float* e) {
 }
 
 template <bool TMA>
-__global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid_constant__ PrepMaps maps) {
+__global__ void __launch_bounds__(128, 4) gdn_tc_prep_kernel(TcP p, const __grid_constant__ PrepMaps maps) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = raw + ((1024u - (tc::smem_u32(raw) & 1023u)) & 1023u);
   uint8_t* Akq = sm;                    // slab s at 16384 s: k box [64][64], then q box [64][64] (later v, u / w images)
-  uint8_t* Tb = Akq + 32768;            // [64 i][64 m] P image, then T diag(beta)
-  uint8_t* Tbd = Tb + 8192;             // [64 i][64 m] T diag(beta E(gam))
-  float* Am = reinterpret_cast<float*>(Tbd + 8192);   // [64][LDA]  A, then T in place
+  float* Am = reinterpret_cast<float*>(Akq + 32768);  // [64][LDA]  A, then T in place
   uint8_t* Tt = reinterpret_cast<uint8_t*>(Am);       // [64 i][64 m] T image, over the fp32 matrix once it is dead
+  uint8_t* Tb = Tt + 8192;              // [64 i][64 m] T diag(beta), behind it
   float* gam = Am + C * LDA;
   float* bet = gam + C;
-  float* bd = bet + C;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(bd + C);  // [0] MMA completion, [1] k,q landed, [2] v landed
+  float* dd = bet + C;                  // E(gam)
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(dd + C);  // [0] MMA completion, [1] k,q landed, [2] v landed
   uint32_t* tslot = reinterpret_cast<uint32_t*>(mbar + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -118,7 +121,7 @@ __global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid
     const float b0 = ok0 ? p.beta[row(2 * lane)] : 0.f, b1 = ok1 ? p.beta[row(2 * lane + 1)] : 0.f;
     gam[2 * lane] = c0; gam[2 * lane + 1] = c1;
     bet[2 * lane] = b0; bet[2 * lane + 1] = b1;
-    bd[2 * lane] = b0 * exp_nonpos(c0); bd[2 * lane + 1] = b1 * exp_nonpos(c1);
+    dd[2 * lane] = exp_nonpos(c0); dd[2 * lane + 1] = exp_nonpos(c1);
     p.gam[ci * C + 2 * lane] = c0;
     p.gam[ci * C + 2 * lane + 1] = c1;
   }
@@ -174,7 +177,7 @@ __global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid
 #pragma unroll
         for (int x = 0; x < 8; ++x)
           *reinterpret_cast<float4*>(Am + i * LDA + c0 + 4 * x) = make_float4(f[4 * x], f[4 * x + 1], f[4 * x + 2], f[4 * x + 3]);
-      } else {         // P = (q k^T) Gamma, lower incl. diagonal -> workspace (staged in the Tb region)
+      } else {         // P = (q k^T) Gamma, lower incl. diagonal -> straight into its operand-tile image in the workspace
         uint32_t pk[16];
 #pragma unroll
         for (int jj = 0; jj < 32; jj += 2) {
@@ -183,20 +186,17 @@ __global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid
           const float x0 = (j <= i) ? v0 : 0.f, x1 = (j + 1 <= i) ? v1 : 0.f;
           pk[jj >> 1] = tc::pack_bf16(x0, x1);
         }
+        uint8_t* pimg = reinterpret_cast<uint8_t*>(p.P + ci * C * C);
 #pragma unroll
-        for (int x = 0; x < 4; ++x)
-          sts16(Tb, tc::kmajor_unit(i, (c0 >> 3) + x, C), make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]));
+        for (int x = 0; x < 4; ++x)  // eight consecutive rows of a unit column are one 128-byte line of the image
+          *reinterpret_cast<uint4*>(pimg + tc::kmajor_unit(i, (c0 >> 3) + x, C)) =
+              make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
       }
     }
   }
-  tc::fence_async_smem();
   tc::fence_before_sync();
   __syncthreads();
   tc::fence_after_sync();
-  if (ok && tid == 0) {  // P leaves as the byte image of its operand tile
-    tc::bulk_store(p.P + ci * C * C, tc::smem_u32(Tb), 8192);
-    tc::bulk_commit();
-  }
   // T = (I - A)^-1 in fp32, in place over A.  The two 32 x 32 diagonal blocks by forward substitution
   // (thread = block and column, the column in registers), then the off-diagonal block
   // T21 = T22 (A21 T11) as two small fp32 products over all 128 threads.
@@ -215,6 +215,16 @@ __global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid
         }
         if (i & 1) s0 = fmaf(arow[i - 1], Tc[i - 1], s0);
         Tc[i] = (i < cc) ? 0.f : s0 + s1;
+      }
+    } else if (ok) {
+      // the other half of the CTA meanwhile turns k into diag(d) k in place (its product with itself is done), so
+      // that w = (T diag beta)(diag(d) k) needs no second scaled copy of T
+      const int i = tid - C;
+      const float di = dd[i];
+#pragma unroll
+      for (int c8 = 0; c8 < 16; ++c8) {
+        uint4* unit = reinterpret_cast<uint4*>(Akq + kq_unit(i, c8));
+        *unit = tc::scale_bf16x8(*unit, di);
       }
     }
     __syncthreads();  // every thread has read its block of A
@@ -237,7 +247,6 @@ __global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid
       *reinterpret_cast<float4*>(Am + i2 * LDA + 32 + jb) = make_float4(x[0], x[1], x[2], x[3]);
       *reinterpret_cast<float4*>(Am + i2 * LDA + 32 + jb + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
-    if (tid == 0) tc::bulk_wait_read<0>();  // the P image has left the Tb region (it is rewritten after the next barriers)
     __syncthreads();
     {  // T21 = T22 X -> over A21 (nothing reads A21 any more)
       float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -253,29 +262,30 @@ __global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid
       *reinterpret_cast<float4*>(Am + (32 + i2) * LDA + jb + 4) = make_float4(y[4], y[5], y[6], y[7]);
     }
     __syncthreads();
-    // bf16 operand tiles T diag(beta), T diag(beta E(gam)) and the T image; the upper triangle (it holds X) reads as
-    // zero.  The T image goes over the fp32 matrix: every thread first reads all its rows, then a barrier, then writes.
-    uint4 timg[4];
+    // the T image and the bf16 operand tile T diag(beta); the upper triangle (it holds X) reads as zero.  Both go
+    // over the fp32 matrix: every thread first reads all its rows, then a barrier, then writes.
+    uint4 timg[4], tbimg[4];
 #pragma unroll
     for (int m = 0; m < 4; ++m) {
       const int u = tid + 128 * m, i = urow8(u), c8 = ucol8(u);
       const float4 a0 = *reinterpret_cast<const float4*>(Am + i * LDA + 8 * c8);
       const float4 a1 = *reinterpret_cast<const float4*>(Am + i * LDA + 8 * c8 + 4);
-      float e[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, eb[8], ed[8];
+      float e[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w}, eb[8];
 #pragma unroll
       for (int y = 0; y < 8; ++y) {
         const int mm = 8 * c8 + y;
         e[y] = (mm <= i) ? e[y] : 0.f;
         eb[y] = e[y] * bet[mm];
-        ed[y] = e[y] * bd[mm];
       }
       timg[m] = pack8f(e);
-      sts16(Tb, 16 * u, pack8f(eb));
-      sts16(Tbd, 16 * u, pack8f(ed));
+      tbimg[m] = pack8f(eb);
     }
     __syncthreads();
 #pragma unroll
-    for (int m = 0; m < 4; ++m) sts16(Tt, 16 * (tid + 128 * m), timg[m]);
+    for (int m = 0; m < 4; ++m) {
+      sts16(Tt, 16 * (tid + 128 * m), timg[m]);
+      sts16(Tb, 16 * (tid + 128 * m), tbimg[m]);
+    }
   }
   if (TMA) { if (ok) ok = tc::mbar_wait(&mbar[2], 0); }  // v
   else tc::cp_async_wait<0>();
@@ -311,9 +321,9 @@ __global__ void __launch_bounds__(128, 3) gdn_tc_prep_kernel(TcP p, const __grid
   tc::fence_before_sync();
   __syncthreads();  // the accumulator columns have been read: the second product may overwrite them
   tc::fence_after_sync();
-  // D1[64 x 128] = (T beta d) k -> w
+  // D1[64 x 128] = (T beta)(d k) -> w
   if (ok && tid == 0) {
-    tc::issue_gemm(taddr, tc::kmajor_tile(Tbd, C), tc::mnmajor_sw128_tile(Akq, 16384), 64, KD, C, false);
+    tc::issue_gemm(taddr, tc::kmajor_tile(Tb, C), tc::mnmajor_sw128_tile(Akq, 16384), 64, KD, C, false);
     tc::mma_commit(mbar);
     for (int hf = 0; hf < 2; ++hf) tc::bulk_store(p.u + ci * C * KD + hf * 4096, sAkq + 8192 + hf * 16384, 8192);
     tc::bulk_commit();

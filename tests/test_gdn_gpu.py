@@ -591,3 +591,29 @@ def test_float32_tensors_through_tensor_core_kernels(dims):
     exact = ops.gated_delta_scan(q, k, v, beta, g, 64, **kw)
     assert not torch.equal(exact, out)
     assert_close(exact, ref_out, TOL_F32, "out (fp32 kernels)")
+
+
+def test_ir_op_records_take_flags_from_the_environment():
+    """An unchanged op-60 record with float32 tensors reaches the tensor-core kernels when the process sets
+    MXB_IR_GDN_FLAGS=64 (the variable is read once per process, hence the child process)."""
+    import subprocess
+    import sys
+    code = r'''
+import torch
+from mixlab_b200 import ops
+from oracle import inputs
+B, T, H, K, V = 2, 200, 2, 128, 128
+a = inputs.gdn_inputs(B, T, H, K, V, seed=5, io_dtype=torch.float32)
+q, k, v, beta = (a[n].cuda() for n in ("q", "k", "v", "beta"))
+gate = torch.exp(a["g"]).cuda()
+out = ops.ir_op_forward(60, [q, k, v, beta, gate], [B, T, H, K, V, 64], out_shape=(B * T * H, V))
+ref = ops.gated_delta_scan(q.bfloat16(), k.bfloat16(), v.bfloat16(), beta, gate, 64).float().reshape(B * T * H, V)
+exact = ops.gated_delta_scan(q, k, v, beta, gate, 64).reshape(B * T * H, V)
+assert torch.equal(out, ref), "record did not take the tensor-core kernels"
+assert not torch.equal(out, exact)
+print("IR_FLAGS_OK")
+'''
+    env = dict(os.environ, MXB_IR_GDN_FLAGS="64")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    assert "IR_FLAGS_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
