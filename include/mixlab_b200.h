@@ -334,6 +334,12 @@ MXB_API size_t mxb_dp_partial_floats(void);
 MXB_API mxb_status mxb_dp_sanitize(float* x, size_t n, float scale, float* flag, void* stream);
 MXB_API mxb_status mxb_dp_finalize(float* x, size_t n, float inv_denominator, float max_norm,
                            float* partial, float* totals, void* stream);
+/* finalize with the divisor read from device memory (the all-reduced loss denominator where the sums left it), so
+ * that a bucket can be finalized as soon as its own sum has arrived, while later buckets are still in flight and
+ * without a host read in between.  A zero, negative or non-finite divisor leaves the values undivided; the host
+ * checks it after the step. */
+MXB_API mxb_status mxb_dp_finalize_dev(float* x, size_t n, const float* denominator_dev, float max_norm,
+                               float* partial, float* totals, void* stream);
 MXB_API mxb_status mxb_dp_scale(float* x, size_t n, const float* scale_dev, void* stream);
 
 /* ------------------------------------------------------------------------

@@ -84,6 +84,7 @@ EXPORTS = {
     "mxb_dp_partial_floats": (C.c_size_t, []),
     "mxb_dp_sanitize": (C.c_int32, [_P, C.c_size_t, C.c_float, _P, _P]),
     "mxb_dp_finalize": (C.c_int32, [_P, C.c_size_t, C.c_float, C.c_float, _P, _P, _P]),
+    "mxb_dp_finalize_dev": (C.c_int32, [_P, C.c_size_t, _P, C.c_float, _P, _P, _P]),
     "mxb_dp_scale": (C.c_int32, [_P, C.c_size_t, _P, _P]),
     "mxb_ir_op_workspace_bytes": (C.c_size_t, [C.POINTER(IrOp)]),
     "mxb_ir_op_forward": (C.c_int32, [C.POINTER(IrOp), _P, C.c_size_t, _P]),

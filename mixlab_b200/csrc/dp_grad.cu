@@ -59,9 +59,17 @@ __global__ void __launch_bounds__(kDpThreads) dp_sanitize_kernel(float* x, size_
   if (__syncthreads_or(bad) && threadIdx.x == 0) *flag = 1.0f;  // every writer stores the same value: no race to resolve
 }
 
-// partial[2 * blockIdx.x] = sum of squares, partial[2 * blockIdx.x + 1] = number of non-finite entries
-__global__ void __launch_bounds__(kDpThreads) dp_finalize_kernel(float* x, size_t n, float inv_denominator, float* partial) {
+// partial[2 * blockIdx.x] = sum of squares, partial[2 * blockIdx.x + 1] = number of non-finite entries.
+// With den_dev the divisor is read from device memory (the all-reduced loss denominator, which then never has to
+// visit the host between the sums and this pass); a zero, negative or non-finite one leaves the values as they are
+// (the host reads it afterwards and skips or rejects the step).
+__global__ void __launch_bounds__(kDpThreads) dp_finalize_kernel(float* x, size_t n, float inv_denominator,
+                                                                 const float* den_dev, float* partial) {
   __shared__ float red[2][kDpThreads / 32];
+  if (den_dev) {
+    const float den = *den_dev;
+    inv_denominator = (den > 0.f && finite_f(den)) ? 1.f / den : 1.f;
+  }
   const Span sp = make_span(x, n);
   float sq = 0.f, cnt = 0.f;
   float4* v = reinterpret_cast<float4*>(x + sp.head);
@@ -163,18 +171,30 @@ mxb_status mxb_dp_sanitize(float* x, size_t n, float scale, float* flag, void* s
   return check_launch("dp_sanitize_kernel");
 }
 
-mxb_status mxb_dp_finalize(float* x, size_t n, float inv_denominator, float max_norm, float* partial, float* totals,
-                           void* stream) {
+static mxb_status dp_finalize_run(float* x, size_t n, float inv_denominator, const float* den_dev, float max_norm,
+                                  float* partial, float* totals, void* stream) {
   if (!x || !partial || !totals) return MXB_ERR_INVALID_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int grid = dp_grid(n);
   if (n > 0) {
-    MXB_LAUNCH("dp_finalize_kernel", st, (dp_finalize_kernel<<<grid, kDpThreads, 0, st>>>(x, n, inv_denominator, partial)));
+    MXB_LAUNCH("dp_finalize_kernel", st,
+               (dp_finalize_kernel<<<grid, kDpThreads, 0, st>>>(x, n, inv_denominator, den_dev, partial)));
     mxb_status s = check_launch("dp_finalize_kernel");
     if (s != MXB_OK) return s;
   }
   MXB_LAUNCH("dp_reduce_kernel", st, (dp_reduce_kernel<<<1, 32, 0, st>>>(partial, n > 0 ? grid : 0, max_norm, totals)));
   return check_launch("dp_reduce_kernel");
+}
+
+mxb_status mxb_dp_finalize(float* x, size_t n, float inv_denominator, float max_norm, float* partial, float* totals,
+                           void* stream) {
+  return dp_finalize_run(x, n, inv_denominator, nullptr, max_norm, partial, totals, stream);
+}
+
+mxb_status mxb_dp_finalize_dev(float* x, size_t n, const float* denominator_dev, float max_norm, float* partial,
+                               float* totals, void* stream) {
+  if (!denominator_dev) return MXB_ERR_INVALID_ARGUMENT;
+  return dp_finalize_run(x, n, 1.f, denominator_dev, max_norm, partial, totals, stream);
 }
 
 mxb_status mxb_dp_scale(float* x, size_t n, const float* scale_dev, void* stream) {

@@ -105,23 +105,32 @@ def build_gradient_bucket_plan(shapes: Sequence[Sequence[int]], target_bytes: in
 
 class BucketStorage:
     """Flat fp32 buffers of a plan on one device, with one view per weight.  A trainer that writes its gradients
-    straight into ``views`` needs no packing copy; the last buffer carries two extra slots for the packed scalars."""
+    straight into ``views`` needs no packing copy.  Two extra slots carry the packed scalars through the sums: the
+    loss denominator rides behind the FIRST bucket (every later bucket can then be finalized as soon as its own sum
+    has arrived), the bad flag behind the LAST one (it is only complete once every bucket has been looked at)."""
 
     def __init__(self, plan: GradientBucketPlan, device):
         self.plan = plan
         self.flat: List[torch.Tensor] = []
         self.views: List[Optional[torch.Tensor]] = [None] * sum(len(b.entries) for b in plan.buckets)
+        last = len(plan.buckets) - 1
         for bi, b in enumerate(plan.buckets):
-            extra = 2 if bi == len(plan.buckets) - 1 else 0
+            extra = (1 if bi == 0 else 0) + (1 if bi == last else 0)
             buf = torch.zeros(b.elements + extra, dtype=torch.float32, device=device)
             self.flat.append(buf)
             for e in b.entries:
                 self.views[e.weight_index] = buf[e.offset:e.offset + e.elements].view(e.shape)
 
     @property
-    def scalars(self) -> torch.Tensor:
-        """[bad flag, loss denominator] at the tail of the last bucket."""
-        return self.flat[-1][self.plan.buckets[-1].elements:]
+    def denominator(self) -> torch.Tensor:
+        """The loss-denominator slot (one element) behind the first bucket."""
+        n = self.plan.buckets[0].elements
+        return self.flat[0][n:n + 1]
+
+    @property
+    def bad(self) -> torch.Tensor:
+        """The bad-flag slot (one element): the last element of the last bucket."""
+        return self.flat[-1][-1:]
 
 
 @dataclass
@@ -182,7 +191,8 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
     ``grads`` may already be the views of ``storage`` (no packing copy then).  On CUDA every element-wise stage is
     one fused pass per bucket of the library's kernels (mxb_dp_sanitize / _finalize / _scale), the bucket
     all-reduces are enqueued on ``comm_stream`` (default: the current stream) one after the other in plan order,
-    and the host reads the device twice: the packed scalars after the sums and the non-finite count at the end.
+    each bucket is finalized behind its own sum while the later sums are in flight, and the host reads the device
+    once, at the end.
     CPU tensors (the gloo tests of the host logic) take the same stages through torch ops."""
     if not grads or not plan.buckets:
         raise ValueError("distributed gradient bucket plan is empty")
@@ -200,6 +210,7 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
     cuda = dev.type == "cuda"
     scale = 1.0 if gradients_are_numerators else safe
     nbytes = sum(b.numel() * 4 for b in storage.flat)
+    storage.denominator.fill_(safe)  # behind the first bucket, so that its sum can leave right after its own pass
     # -- numerator conversion: non-finite -> 0 (and flagged), x scale
     if cuda:
         from . import _lib
@@ -208,9 +219,13 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
         st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         aux = torch.zeros(4 + l.mxb_dp_partial_floats(), dtype=torch.float32, device=dev)  # flag, totals[3], partials
         P = lambda t, off=0: C.c_void_p(t.data_ptr() + 4 * off)
+        sanitized = []
         with torch.cuda.device(dev):
             for b, buf in zip(plan.buckets, storage.flat):
                 _lib.check(l.mxb_dp_sanitize(P(buf), b.elements, scale, P(aux), st), "mxb_dp_sanitize")
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(dev))
+                sanitized.append(ev)
         raw_bad = aux[0]
     else:
         raw_bad = torch.zeros((), dtype=torch.float32, device=dev)
@@ -225,10 +240,11 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
         else torch.zeros((), dtype=torch.float32, device=dev)
     if not denominator_valid:
         local_bad = torch.ones((), dtype=torch.float32, device=dev)
-    storage.scalars[0] = local_bad
-    storage.scalars[1] = safe
+    storage.bad.copy_(local_bad.reshape(1))
+    if cuda:
+        return _finish_pipelined(storage, plan, group, comm_stream, dev, max_grad_norm, l, st, aux, P, sanitized, nbytes)
     _all_reduce_buckets(storage.flat, group, comm_stream, dev)
-    bad_count, denominator = (float(x) for x in storage.scalars.tolist())  # host read of the two packed scalars
+    bad_count, denominator = float(storage.bad), float(storage.denominator)  # host read of the two packed scalars
     if bad_count > 0.0:
         return StagedGradientResult(bad_count, False, True, denominator, len(storage.flat), nbytes)
     if not math.isfinite(denominator) or denominator < 0.0:
@@ -236,19 +252,43 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
     if denominator == 0.0:
         return StagedGradientResult(0.0, True, False, 0.0, len(storage.flat), nbytes)
     # -- divide by the global denominator, sanitize, global norm, clip
-    if cuda:
-        with torch.cuda.device(dev):
+    for b, buf in zip(plan.buckets, storage.flat):
+        buf[:b.elements].div_(denominator)
+    nonfinite = float(sanitize_and_clip_([v for v in storage.views], max_grad_norm))
+    return StagedGradientResult(nonfinite, False, False, denominator, len(storage.flat), nbytes)
+
+
+def _finish_pipelined(storage, plan, group, comm_stream, dev, max_grad_norm, l, st, aux, P, sanitized, nbytes):
+    """CUDA: the bucket sums go out on the communication stream as soon as the bucket is sanitized (the last one
+    after the bad flag is in place); on the compute stream every bucket is divided, sanitized and measured right
+    behind its own sum, with the divisor taken from the device slot behind the first bucket, while the later sums
+    are still in flight.  The host reads the device once, at the end: bad flag, denominator, non-finite count."""
+    from . import _lib
+    cur = torch.cuda.current_stream(dev)
+    comm = comm_stream if comm_stream is not None else cur
+    ready = torch.cuda.Event()
+    ready.record(cur)  # every bucket sanitized and the bad flag in its slot
+    works = []
+    with torch.cuda.stream(comm):
+        for i, buf in enumerate(storage.flat):
+            # a bucket's sum may leave as soon as its own pass is done; the last one also carries the bad flag
+            comm.wait_event(sanitized[i] if i < len(storage.flat) - 1 else ready)
+            works.append(dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True))
+    with torch.cuda.device(dev):
+        for i, (b, buf) in enumerate(zip(plan.buckets, storage.flat)):
+            works[i].wait()  # the compute stream waits for this bucket's sum only
+            _lib.check(l.mxb_dp_finalize_dev(P(buf), b.elements, P(storage.denominator), float(max_grad_norm), P(aux, 4),
+                                             P(aux, 1), st), "mxb_dp_finalize_dev")
+        if max_grad_norm > 0.0:
             for b, buf in zip(plan.buckets, storage.flat):
-                _lib.check(l.mxb_dp_finalize(P(buf), b.elements, 1.0 / denominator, float(max_grad_norm), P(aux, 4), P(aux, 1),
-                                             st), "mxb_dp_finalize")
-            if max_grad_norm > 0.0:
-                for b, buf in zip(plan.buckets, storage.flat):
-                    _lib.check(l.mxb_dp_scale(P(buf), b.elements, P(aux, 3), st), "mxb_dp_scale")
-        nonfinite = float(aux[2])
-    else:
-        for b, buf in zip(plan.buckets, storage.flat):
-            buf[:b.elements].div_(denominator)
-        nonfinite = float(sanitize_and_clip_(grads, max_grad_norm))
+                _lib.check(l.mxb_dp_scale(P(buf), b.elements, P(aux, 3), st), "mxb_dp_scale")
+    bad_count, denominator, nonfinite = torch.stack([storage.bad[0], storage.denominator[0], aux[2]]).tolist()
+    if bad_count > 0.0:
+        return StagedGradientResult(bad_count, False, True, denominator, len(storage.flat), nbytes)
+    if not math.isfinite(denominator) or denominator < 0.0:
+        raise RuntimeError("distributed global loss denominator is invalid")
+    if denominator == 0.0:
+        return StagedGradientResult(0.0, True, False, 0.0, len(storage.flat), nbytes)
     return StagedGradientResult(nonfinite, False, False, denominator, len(storage.flat), nbytes)
 
 

@@ -56,6 +56,26 @@ def test_dp_passes_match_torch(n, offset):
     assert torch.equal(x, wanty * 0.25)
 
 
+@pytest.mark.parametrize("den", [3.0, 0.0, float("nan")])
+def test_finalize_with_device_denominator(den):
+    """mxb_dp_finalize_dev reads the divisor from device memory: same bits as the host-argument form for a valid
+    denominator; a zero or non-finite one leaves the values undivided (the host decides about the step)."""
+    lib = mixlab_b200.lib()
+    n = 100_003
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(n, device="cuda", generator=g)
+    y = x.clone()
+    d = torch.tensor([den], device="cuda")
+    a1 = torch.zeros(4 + lib.mxb_dp_partial_floats(), device="cuda")
+    a2 = torch.zeros_like(a1)
+    assert lib.mxb_dp_finalize_dev(_p(x), n, _p(d), 2.0, _p(a1, 4), _p(a1, 1), None) == 0
+    inv = 1.0 / den if den > 0 else 1.0
+    inv32 = (torch.ones(1) / torch.tensor([den])).item() if den > 0 else 1.0   # the float32 reciprocal the kernel forms
+    assert lib.mxb_dp_finalize(_p(y), n, inv32, 2.0, _p(a2, 4), _p(a2, 1), None) == 0
+    assert torch.equal(x, y) and torch.equal(a1[1:4], a2[1:4])
+    assert lib.mxb_dp_finalize_dev(_p(x), n, None, 2.0, _p(a1, 4), _p(a1, 1), None) != 0
+
+
 def test_staged_step_on_one_rank_nccl_group():
     import torch.distributed as dist
     from mixlab_b200 import dp
