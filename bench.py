@@ -458,8 +458,9 @@ def time_workload(cx, wl, steps, warmup):
 
 def dp_allreduce_leg(cx, steps=5, warmup=2):
     """The gradient exchange of the end-to-end training configuration (12 layers, d_model 1024, vocab 32768: about
-    1.07 GB of fp32 gradients) on this job's ranks: bucket plan of 32 MiB buckets, staged all-reduce (bad flag and
-    denominator packed into the last bucket), NCCL on a communication stream.  Reports the whole staged step and
+    1.07 GB of fp32 gradients) on this job's ranks: bucket plan of 32 MiB buckets, staged all-reduce (the loss
+    denominator rides behind the first bucket, the bad flag behind the last; every bucket is finalized behind its own
+    sum), NCCL on a communication stream.  Reports the whole staged step and
     the all-reduces alone; bus bandwidth = 2 (N-1)/N x bytes / time."""
     import torch.distributed as dist
     from mixlab_b200 import dp
