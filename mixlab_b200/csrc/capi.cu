@@ -540,6 +540,7 @@ struct mxb_host_ctx {
   cudaStream_t s_h2d, s_d2h;     // copy engines, one per direction
   cudaEvent_t h2d_done[2], comp_done[2], d2h_done[2];
   cudaEvent_t do_done[2], fwd_done[2];  // dO uploaded / forward finished: the forward need not wait for dO, nor out for the backward
+  cudaEvent_t bg_up;                    // beta and gate of the whole batch uploaded
 };
 
 #define MXB_CUDA_TRY(expr)                          \
@@ -572,6 +573,7 @@ mxb_status mxb_host_ctx_create(int device, size_t arena_bytes, mxb_host_ctx** ou
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->do_done[i], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->fwd_done[i], cudaEventDisableTiming);
   }
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->bg_up, cudaEventDisableTiming);
   if (e != cudaSuccess) {
     g_last_cuda_error = (int)e;
     mxb_host_ctx_destroy(c);
@@ -592,6 +594,7 @@ void mxb_host_ctx_destroy(mxb_host_ctx* c) {
     if (c->do_done[i]) cudaEventDestroy(c->do_done[i]);
     if (c->fwd_done[i]) cudaEventDestroy(c->fwd_done[i]);
   }
+  if (c->bg_up) cudaEventDestroy(c->bg_up);
   if (c->stream) cudaStreamDestroy(c->stream);
   if (c->stream2) cudaStreamDestroy(c->stream2);
   if (c->s_h2d) cudaStreamDestroy(c->s_h2d);
@@ -600,8 +603,23 @@ void mxb_host_ctx_destroy(mxb_host_ctx* c) {
   delete c;
 }
 
-// The batch is cut into single sequences; sequence b+1 is uploaded and sequence b-1 downloaded
-// while sequence b computes (two device slots per tensor, three streams, events between them).
+// Per-head scalars of a head group: compact[r][j] = full[r][h0 + j] (gather) and back (scatter).
+__global__ void __launch_bounds__(256) head_gather_kernel(const float* __restrict__ full, float* __restrict__ compact,
+                                                          size_t rows, int H, int h0, int Hs) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows * Hs; i += (size_t)gridDim.x * blockDim.x)
+    compact[i] = full[(i / Hs) * H + h0 + (i % Hs)];
+}
+__global__ void __launch_bounds__(256) head_scatter_kernel(const float* __restrict__ compact, float* __restrict__ full,
+                                                           size_t rows, int H, int h0, int Hs) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows * Hs; i += (size_t)gridDim.x * blockDim.x)
+    full[(i / Hs) * H + h0 + (i % Hs)] = compact[i];
+}
+
+// The batch is cut into slices; slice i+1 is uploaded and slice i-1 downloaded while slice i computes (two device
+// slots per tensor, two copy streams, two kernel streams, events between them).  A slice is one sequence, or - when
+// the batch has few sequences - a group of heads of one sequence, moved by strided copies: the first upload and the
+// last download are the part of the traffic nothing overlaps, so slices are kept to about a sixteenth of the batch.
+// beta and gate (and their gradients) are small: they cross once for the whole batch.
 static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, const void* q, const void* k,
                                     const void* v, const float* beta, const float* gate, void* out,
                                     const void* d_out, void* dq, void* dk, void* dv, float* dbeta, float* dgate) {
@@ -613,21 +631,35 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
   if (bwd && (!dq || !dk || !dv || !dbeta || !dgate)) return MXB_ERR_INVALID_ARGUMENT;
   MXB_CUDA_TRY(cudaSetDevice(c->device));
   const size_t es = d->io_dtype == MXB_F32 ? 4 : 2;
-  // per-sequence element counts
-  const size_t sk = (size_t)d->T * d->H * d->Dk, sv = (size_t)d->T * d->H * d->Dv, ss = (size_t)d->T * d->H;
-  // sequences per pipeline slice (MXB_HOST_SLICE_SEQS overrides the default of 1)
-  int per = 1;
-  if (const char* ev = std::getenv("MXB_HOST_SLICE_SEQS")) per = std::atoi(ev);
+  // sequences per slice (MXB_HOST_SLICE_SEQS overrides the default of 1) and head groups per sequence
+  // (MXB_HOST_HEAD_SPLIT overrides; by default doubled until there are 16 slices, while a group's rows stay >= 1 KB)
+  int per = 1, nsplit = 1;
+  bool per_set = false;
+  if (const char* ev = std::getenv("MXB_HOST_SLICE_SEQS")) { per = std::atoi(ev); per_set = true; }
   if (per < 1) per = 1;
   if (per > d->B) per = d->B;
-  const int nslices = (d->B + per - 1) / per;
+  if (const char* ev = std::getenv("MXB_HOST_HEAD_SPLIT")) {
+    nsplit = std::atoi(ev);
+    if (nsplit < 1 || d->H % nsplit) nsplit = 1;
+  } else if (!per_set) {
+    const size_t dmin = (size_t)(d->Dk < d->Dv ? d->Dk : d->Dv) * es;
+    while (d->B * nsplit < 16 && d->H % (2 * nsplit) == 0 && (size_t)(d->H / (2 * nsplit)) * dmin >= 1024) nsplit *= 2;
+  }
+  if (nsplit > 1) per = 1;
+  const int Hs = d->H / nsplit;
+  const int nslices = nsplit > 1 ? d->B * nsplit : (d->B + per - 1) / per;
+  // per-sequence element counts of a slice's tensors
+  const size_t sk = (size_t)d->T * Hs * d->Dk, sv = (size_t)d->T * Hs * d->Dv, ss = (size_t)d->T * Hs;
   mxb_gdn_desc d1 = *d;
   d1.B = per;
+  d1.H = Hs;
   mxb_gdn_desc df = d1, db = d1;
   // The slices' kernels stage their operands with per-thread copies where they have such a variant: this call is
   // bound by the two PCIe copy streams, which ran slower beside kernels fed by the tensor-copy engine.
-  df.flags |= MXB_GDN_NO_TMA;
-  db.flags |= MXB_GDN_NO_TMA;
+  if (!std::getenv("MXB_HOST_TMA")) {
+    df.flags |= MXB_GDN_NO_TMA;
+    db.flags |= MXB_GDN_NO_TMA;
+  }
   if (bwd) {  // keep the forward intermediates in the arena for the backward that follows
     df.flags |= MXB_GDN_SAVE_FOR_BWD;
     db.flags |= MXB_GDN_BWD_USE_SAVED;
@@ -635,19 +667,24 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
   const size_t ws_f = mxb_gdn_fwd_workspace_bytes(&df), ws_b = bwd ? mxb_gdn_bwd_workspace_bytes(&db) : 0;
   const size_t ws_bytes = ws_f > ws_b ? ws_f : ws_b;
   const size_t nk = sk * per, nv = sv * per, ns = ss * per;  // slot capacities
+  const size_t nfull = (size_t)d->B * d->T * d->H;           // beta, gate and their gradients, whole batch
   Carver cv(c->arena);
   char *i_q[2], *i_k[2], *i_v[2], *i_do[2], *o_out[2], *o_q[2], *o_k[2], *o_v[2];
   float *i_b[2], *i_g[2], *o_b[2], *o_g[2];
+  float* f_beta = cv.take<float>(nfull);
+  float* f_gate = cv.take<float>(nfull);
+  float* f_dbeta = bwd ? cv.take<float>(nfull) : nullptr;
+  float* f_dgate = bwd ? cv.take<float>(nfull) : nullptr;
   for (int sl = 0; sl < 2; ++sl) {
     i_q[sl] = cv.take<char>(nk * es); i_k[sl] = cv.take<char>(nk * es); i_v[sl] = cv.take<char>(nv * es);
-    i_b[sl] = cv.take<float>(ns); i_g[sl] = cv.take<float>(ns);
     o_out[sl] = cv.take<char>(nv * es);
+    i_b[sl] = i_g[sl] = o_b[sl] = o_g[sl] = nullptr;
+    if (nsplit > 1) { i_b[sl] = cv.take<float>(ns); i_g[sl] = cv.take<float>(ns); }
     i_do[sl] = o_q[sl] = o_k[sl] = o_v[sl] = nullptr;
-    o_b[sl] = o_g[sl] = nullptr;
     if (bwd) {
       i_do[sl] = cv.take<char>(nv * es);
       o_q[sl] = cv.take<char>(nk * es); o_k[sl] = cv.take<char>(nk * es); o_v[sl] = cv.take<char>(nv * es);
-      o_b[sl] = cv.take<float>(ns); o_g[sl] = cv.take<float>(ns);
+      if (nsplit > 1) { o_b[sl] = cv.take<float>(ns); o_g[sl] = cv.take<float>(ns); }
     }
   }
   char* wss[2] = {cv.take<char>(ws_bytes), cv.take<char>(ws_bytes)};  // one workspace per slot
@@ -655,48 +692,84 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
   auto hp = [](const void* base, size_t off) { return static_cast<const char*>(base) + off; };
   auto hpw = [](void* base, size_t off) { return static_cast<char*>(base) + off; };
   const cudaMemcpyKind H2D = cudaMemcpyHostToDevice, D2H = cudaMemcpyDeviceToHost;
+  // a [rows][Hs][D] slice of a [.][H][D] tensor: one contiguous block, or rows of Hs*D elements at a pitch of H*D
+  auto up = [&](char* dst, const void* src, size_t off_bytes, size_t bytes, int D) -> cudaError_t {
+    if (nsplit == 1) return cudaMemcpyAsync(dst, hp(src, off_bytes), bytes, H2D, c->s_h2d);
+    const size_t w = (size_t)Hs * D * es;
+    return cudaMemcpy2DAsync(dst, w, hp(src, off_bytes), (size_t)d->H * D * es, w, (size_t)d->T, H2D, c->s_h2d);
+  };
+  auto down = [&](void* dst, size_t off_bytes, const char* src, size_t bytes, int D) -> cudaError_t {
+    if (nsplit == 1) return cudaMemcpyAsync(hpw(dst, off_bytes), src, bytes, D2H, c->s_d2h);
+    const size_t w = (size_t)Hs * D * es;
+    return cudaMemcpy2DAsync(hpw(dst, off_bytes), (size_t)d->H * D * es, src, w, w, (size_t)d->T, D2H, c->s_d2h);
+  };
+  MXB_CUDA_TRY(cudaMemcpyAsync(f_beta, beta, nfull * 4, H2D, c->s_h2d));
+  MXB_CUDA_TRY(cudaMemcpyAsync(f_gate, gate, nfull * 4, H2D, c->s_h2d));
+  MXB_CUDA_TRY(cudaEventRecord(c->bg_up, c->s_h2d));
   for (int bi = 0; bi < nslices; ++bi) {
     const int sl = bi & 1;
-    const int b0 = bi * per, nb = (b0 + per <= d->B) ? per : d->B - b0;
-    const size_t ck = sk * nb * es, cvb = sv * nb * es, cs = ss * nb * 4;   // bytes of this slice
-    const size_t ok_ = (size_t)b0 * sk * es, ov_ = (size_t)b0 * sv * es, os_ = (size_t)b0 * ss * 4;
+    const int b0 = nsplit > 1 ? bi / nsplit : bi * per, h0 = nsplit > 1 ? (bi % nsplit) * Hs : 0;
+    const int nb = nsplit > 1 ? 1 : ((b0 + per <= d->B) ? per : d->B - b0);
+    const size_t ck = sk * nb * es, cvb = sv * nb * es;   // bytes of this slice
+    // element offsets of the slice's first row in the full tensors
+    const size_t ok_ = ((size_t)b0 * d->T * d->H + h0) * d->Dk * es, ov_ = ((size_t)b0 * d->T * d->H + h0) * d->Dv * es;
+    const size_t os_ = (size_t)b0 * d->T * d->H;
     df.B = db.B = nb;
     if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_h2d, c->comp_done[sl], 0));  // slot inputs consumed
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_q[sl], hp(q, ok_), ck, H2D, c->s_h2d));
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_k[sl], hp(k, ok_), ck, H2D, c->s_h2d));
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_v[sl], hp(v, ov_), cvb, H2D, c->s_h2d));
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_b[sl], hp(beta, os_), cs, H2D, c->s_h2d));
-    MXB_CUDA_TRY(cudaMemcpyAsync(i_g[sl], hp(gate, os_), cs, H2D, c->s_h2d));
+    MXB_CUDA_TRY(up(i_q[sl], q, ok_, ck, d->Dk));
+    MXB_CUDA_TRY(up(i_k[sl], k, ok_, ck, d->Dk));
+    MXB_CUDA_TRY(up(i_v[sl], v, ov_, cvb, d->Dv));
     MXB_CUDA_TRY(cudaEventRecord(c->h2d_done[sl], c->s_h2d));
     if (bwd) {
-      MXB_CUDA_TRY(cudaMemcpyAsync(i_do[sl], hp(d_out, ov_), cvb, H2D, c->s_h2d));
+      MXB_CUDA_TRY(up(i_do[sl], d_out, ov_, cvb, d->Dv));
       MXB_CUDA_TRY(cudaEventRecord(c->do_done[sl], c->s_h2d));
     }
     cudaStream_t kst = sl ? c->stream2 : c->stream;
     char* ws = wss[sl];
     MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->h2d_done[sl], 0));
+    if (bi < 2) MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->bg_up, 0));
     if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->d2h_done[sl], 0));  // slot outputs drained
-    s = mxb_gdn_fwd(&df, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, o_out[sl], nullptr, ws, ws_bytes, kst);
+    const float *sb = f_beta + os_, *sg = f_gate + os_;
+    float *sdb = bwd ? f_dbeta + os_ : nullptr, *sdg = bwd ? f_dgate + os_ : nullptr;
+    const size_t rows = (size_t)nb * d->T;
+    const int gblocks = (int)((rows * Hs + 255) / 256 < 592 ? (rows * Hs + 255) / 256 : 592);
+    if (nsplit > 1) {
+      MXB_LAUNCH("head_gather_kernel", kst, (head_gather_kernel<<<gblocks, 256, 0, kst>>>(sb, i_b[sl], rows, d->H, h0, Hs)));
+      MXB_LAUNCH("head_gather_kernel", kst, (head_gather_kernel<<<gblocks, 256, 0, kst>>>(sg, i_g[sl], rows, d->H, h0, Hs)));
+      sb = i_b[sl]; sg = i_g[sl];
+      sdb = o_b[sl]; sdg = o_g[sl];
+    }
+    s = mxb_gdn_fwd(&df, i_q[sl], i_k[sl], i_v[sl], sb, sg, nullptr, o_out[sl], nullptr, ws, ws_bytes, kst);
     if (s != MXB_OK) return s;
     MXB_CUDA_TRY(cudaEventRecord(c->fwd_done[sl], kst));
     if (bwd) {
       MXB_CUDA_TRY(cudaStreamWaitEvent(kst, c->do_done[sl], 0));
-      s = mxb_gdn_bwd(&db, i_q[sl], i_k[sl], i_v[sl], i_b[sl], i_g[sl], nullptr, i_do[sl], nullptr, o_q[sl], o_k[sl],
-                      o_v[sl], o_b[sl], o_g[sl], nullptr, ws, ws_bytes, kst);
+      s = mxb_gdn_bwd(&db, i_q[sl], i_k[sl], i_v[sl], sb, sg, nullptr, i_do[sl], nullptr, o_q[sl], o_k[sl], o_v[sl], sdb,
+                      sdg, nullptr, ws, ws_bytes, kst);
       if (s != MXB_OK) return s;
+      if (nsplit > 1) {
+        MXB_LAUNCH("head_scatter_kernel", kst,
+                   (head_scatter_kernel<<<gblocks, 256, 0, kst>>>(o_b[sl], f_dbeta + os_, rows, d->H, h0, Hs)));
+        MXB_LAUNCH("head_scatter_kernel", kst,
+                   (head_scatter_kernel<<<gblocks, 256, 0, kst>>>(o_g[sl], f_dgate + os_, rows, d->H, h0, Hs)));
+      }
     }
     MXB_CUDA_TRY(cudaEventRecord(c->comp_done[sl], kst));
     MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->fwd_done[sl], 0));
-    MXB_CUDA_TRY(cudaMemcpyAsync(hpw(out, ov_), o_out[sl], cvb, D2H, c->s_d2h));
+    MXB_CUDA_TRY(down(out, ov_, o_out[sl], cvb, d->Dv));
     if (bwd) {
       MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[sl], 0));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dq, ok_), o_q[sl], ck, D2H, c->s_d2h));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dk, ok_), o_k[sl], ck, D2H, c->s_d2h));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dv, ov_), o_v[sl], cvb, D2H, c->s_d2h));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dbeta, os_), o_b[sl], cs, D2H, c->s_d2h));
-      MXB_CUDA_TRY(cudaMemcpyAsync(hpw(dgate, os_), o_g[sl], cs, D2H, c->s_d2h));
+      MXB_CUDA_TRY(down(dq, ok_, o_q[sl], ck, d->Dk));
+      MXB_CUDA_TRY(down(dk, ok_, o_k[sl], ck, d->Dk));
+      MXB_CUDA_TRY(down(dv, ov_, o_v[sl], cvb, d->Dv));
     }
     MXB_CUDA_TRY(cudaEventRecord(c->d2h_done[sl], c->s_d2h));
+  }
+  if (bwd) {  // the per-head gradients of the whole batch, once every slice has computed
+    MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[0], 0));
+    if (nslices > 1) MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[1], 0));
+    MXB_CUDA_TRY(cudaMemcpyAsync(dbeta, f_dbeta, nfull * 4, D2H, c->s_d2h));
+    MXB_CUDA_TRY(cudaMemcpyAsync(dgate, f_dgate, nfull * 4, D2H, c->s_d2h));
   }
   MXB_CUDA_TRY(cudaStreamSynchronize(c->s_d2h));
   MXB_CUDA_TRY(cudaStreamSynchronize(c->stream));

@@ -185,13 +185,16 @@ def test_decode_equals_scan():
     assert_close(st, s_scan, TOL_F32, "state")
 
 
-@pytest.mark.parametrize("B", [1, 3, 4])
-def test_host_buffer_entry_point(B):
-    """mxb_host_gdn: host tensors in, host tensors out, forward + backward (sequences are
-    pipelined through two device slots, so B > 2 exercises slot reuse)."""
+@pytest.mark.parametrize("B,H,split", [(1, 2, None), (3, 2, None), (4, 2, None), (3, 4, "2"), (1, 4, "4"), (2, 6, "3")])
+def test_host_buffer_entry_point(B, H, split, monkeypatch):
+    """mxb_host_gdn: host tensors in, host tensors out, forward + backward (slices are pipelined through two device
+    slots, so more than two slices exercise slot reuse; with a head split a slice is a group of heads of one sequence,
+    moved by strided copies)."""
     import ctypes as C
     lib = mixlab_b200.lib()
-    T, H, K, V = 100, 2, 32, 32
+    if split is not None:
+        monkeypatch.setenv("MXB_HOST_HEAD_SPLIT", split)
+    T, K, V = 100, 32, 32
     a = inputs.gdn_inputs(B, T, H, K, V, seed=6, with_grad_out=True)
     f = {k: v.double() for k, v in a.items()}
     want = gdn.scan_grads(f["q"], f["k"], f["v"], f["beta"], f["g"], f["d_out"], gate_is_log=True)
@@ -617,3 +620,36 @@ print("IR_FLAGS_OK")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=600)
     assert "IR_FLAGS_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_host_buffer_entry_point_head_groups_on_tensor_core_kernels(monkeypatch):
+    """Two sequences of four 128-wide bf16 heads: by default the call cuts every sequence into head groups (rows of a
+    group stay >= 1 KB) and must return what the device entry points return on the whole tensors."""
+    import ctypes as C
+    lib = mixlab_b200.lib()
+    B, T, H, K, V = 2, 200, 4, 128, 128
+    a = inputs.gdn_inputs(B, T, H, K, V, seed=8, io_dtype=torch.bfloat16, with_grad_out=True)
+    dev = {n: _dev(a[n]) for n in ("q", "k", "v", "beta", "g", "d_out")}
+    want_out = ops.gated_delta_scan(dev["q"], dev["k"], dev["v"], dev["beta"], dev["g"], 64, gate_is_log=True)
+    want = ops.gated_delta_scan_backward(dev["q"], dev["k"], dev["v"], dev["beta"], dev["g"], dev["d_out"], 64, gate_is_log=True)
+    host = {n: a[n].contiguous().pin_memory() for n in ("q", "k", "v", "beta", "g", "d_out")}
+    res = {n: torch.empty_like(host[m]).pin_memory() for n, m in
+           (("out", "v"), ("dq", "q"), ("dk", "k"), ("dv", "v"), ("dbeta", "beta"), ("dgate", "g"))}
+    p = lambda t: C.c_void_p(t.data_ptr())
+    for split in (None, "1"):
+        if split is not None:
+            monkeypatch.setenv("MXB_HOST_HEAD_SPLIT", split)
+        ctx = C.c_void_p()
+        assert lib.mxb_host_ctx_create(0, 256 << 20, C.byref(ctx)) == 0
+        try:
+            d = mixlab_b200.GdnDesc(B, T, H, K, V, 64, mixlab_b200.MXB_BF16, 1, 0)
+            st = lib.mxb_host_gdn(ctx, C.byref(d), p(host["q"]), p(host["k"]), p(host["v"]), p(host["beta"]), p(host["g"]),
+                                  p(res["out"]), p(host["d_out"]), p(res["dq"]), p(res["dk"]), p(res["dv"]), p(res["dbeta"]),
+                                  p(res["dgate"]))
+            assert st == 0
+        finally:
+            lib.mxb_host_ctx_destroy(ctx)
+        # a head group is computed by the same kernels on the same numbers: bit-identical to the whole-tensor call
+        assert torch.equal(res["out"], want_out.cpu()), split
+        for n in ("dq", "dk", "dv", "dbeta", "dgate"):
+            assert torch.equal(res[n], want[n].cpu()), (split, n)
