@@ -11,9 +11,10 @@
 //     h_t = alpha h_{t-1} + gamma Brot_t x_t + [t>0] beta Brot_{t-1} x_{t-1}
 //     y_t = sum_n h_t[n] Crot_t[n]
 //
-// Mapping: one warp per (batch, channel); a lane owns state pairs lane, lane+32,
-// ... (PR of them), so d_state up to 256 is covered (the reference's kernels stop
-// at 64, gpu/mamba3_cuda_primitive.cpp:22).  The cumulative angle is kept wrapped
+// Mapping: LPC lanes per (batch, channel): a whole warp, whose lanes own state pairs lane, lane+32, ... (PR of
+// them), so d_state up to 256 is covered (the reference's kernels stop at 64, gpu/mamba3_cuda_primitive.cpp:22);
+// for d_state <= 32 / <= 16 a half / a quarter of a warp, so that two / four channels share a warp and no lane is
+// without a state pair at the sizes the reference runs (d_state 16).  The cumulative angle is kept wrapped
 // to [-pi, pi] so fp32 keeps its resolution over thousands of steps.
 //
 // Short problems (few batch x channel pairs) would leave most of the GPU idle behind T-long walks, so the
@@ -52,6 +53,7 @@ constexpr int kM3Window = 16;
 
 struct M3P {
   int B, T, D, N, G, NH, Kp, nW;
+  int LPC;  // lanes per channel: 32, or 16 / 8 where d_state <= 32 / 16 would leave most lanes of a warp without a state pair
   const void *x, *b, *c;
   const float *dt, *lam, *theta, *a_log;
   void* y;
@@ -84,6 +86,14 @@ __device__ __forceinline__ float m3_wrap(float phi) {
   return fmaf(-k, 1.9353071795864769e-3f, phi);
 }
 
+// Sum over the LPC lanes that share a channel (LPC = 32: the whole warp); every lane of the group gets the sum.
+template <int LPC>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPC / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 struct M3Idx {
   int D, N, G, NH, Kp, cpg, cph;
   __device__ M3Idx(const M3P& p)
@@ -101,11 +111,15 @@ struct M3Idx {
 // MODE 0: the whole sequence (also the checkpoint pass of the serial backward: y == nullptr, ck_h != nullptr).
 // MODE 1: one window from a zero state and the window's start angle; leaves the local end state in ck_h.
 // MODE 2: one window from the true start state in ck_h; writes y.
-template <typename IO, int PR, int MODE>
+template <typename IO, int PR, int LPC, int MODE>
 __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int d = blockIdx.x * 8 + warp, b = MODE == 0 ? blockIdx.y : blockIdx.z;
-  if (d >= p.D) return;
+  constexpr int CPW = 32 / LPC;  // channels per warp
+  const int sl = lane % LPC, d_raw = (blockIdx.x * 8 + warp) * CPW + lane / LPC;
+  const int b = MODE == 0 ? blockIdx.y : blockIdx.z;
+  if ((blockIdx.x * 8 + warp) * CPW >= p.D) return;
+  const bool live = d_raw < p.D;       // lanes past the last channel walk a copy of it and store nothing
+  const int d = live ? d_raw : p.D - 1;
   const M3Idx ix(p);
   const IO* X = static_cast<const IO*>(p.x);
   const IO* Bp = static_cast<const IO*>(p.b);
@@ -114,7 +128,7 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
   float A0[PR], A1[PR], h0[PR], h1[PR], phi[PR], pb0[PR], pb1[PR];
 #pragma unroll
   for (int r = 0; r < PR; ++r) {
-    const int kp = lane + 32 * r;
+    const int kp = sl + LPC * r;
     const bool act = kp < p.Kp;
     A0[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp)]) : 0.f;
     A1[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp + 1)]) : 0.f;
@@ -127,7 +141,7 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
   if (MODE != 0) {
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       if (kp < p.Kp) {
         phi[r] = p.ck_phi[wrow_w * p.Kp + kp];
         if (MODE == 2) {
@@ -152,8 +166,8 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
       const size_t wrow = ((size_t)b * p.nW + t / kM3Window) * p.D + d;
 #pragma unroll
       for (int r = 0; r < PR; ++r) {
-        const int kp = lane + 32 * r;
-        if (kp < p.Kp) {
+        const int kp = sl + LPC * r;
+        if (kp < p.Kp && live) {
           p.ck_h[wrow * p.N + 2 * kp] = h0[r];
           p.ck_h[wrow * p.N + 2 * kp + 1] = h1[r];
           p.ck_phi[wrow * p.Kp + kp] = phi[r];
@@ -167,7 +181,7 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
     float part = 0.f;
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       if (kp < p.Kp) {
         phi[r] = m3_wrap(fmaf(dt, p.theta[ix.theta(row, d, kp)], phi[r]));
         float s, c;
@@ -189,15 +203,15 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
     }
     px = x;  // t = 0 uses px = 0, which realises the [t>0] factor
     if (MODE != 1 && Y) {
-      part = warp_sum(part);
-      if (lane == 0) Y[row * p.D + d] = from_f32<IO>(part);
+      part = group_sum<LPC>(part);
+      if (sl == 0 && live) Y[row * p.D + d] = from_f32<IO>(part);
     }
   }
   if (MODE == 1) {
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
-      if (kp < p.Kp) {
+      const int kp = sl + LPC * r;
+      if (kp < p.Kp && live) {
         p.ck_h[wrow_w * p.N + 2 * kp] = h0[r];
         p.ck_h[wrow_w * p.N + 2 * kp + 1] = h1[r];
       }
@@ -207,11 +221,14 @@ __global__ void __launch_bounds__(256) mamba3_fwd_kernel(M3P p) {
 
 // ------------------------------------------------- window-parallel: sums and scans
 // Sum of dt theta (per state pair) and of dt over each window.
-template <int PR>
+template <int PR, int LPC>
 __global__ void __launch_bounds__(256) m3w_phase_kernel(M3P p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int d = blockIdx.x * 8 + warp, w = blockIdx.y, b = blockIdx.z;
-  if (d >= p.D) return;
+  constexpr int CPW = 32 / LPC;
+  const int sl = lane % LPC, d_raw = (blockIdx.x * 8 + warp) * CPW + lane / LPC, w = blockIdx.y, b = blockIdx.z;
+  if ((blockIdx.x * 8 + warp) * CPW >= p.D) return;
+  const bool live = d_raw < p.D;
+  const int d = live ? d_raw : p.D - 1;
   const M3Idx ix(p);
   const int ts = w * kM3Window, te = min(p.T, ts + kM3Window);
   float ph[PR], dts = 0.f;
@@ -223,18 +240,20 @@ __global__ void __launch_bounds__(256) m3w_phase_kernel(M3P p) {
     dts += dt;
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       if (kp < p.Kp) ph[r] = fmaf(dt, p.theta[ix.theta(row, d, kp)], ph[r]);
     }
   }
   const size_t wrow = ((size_t)b * p.nW + w) * p.D + d;
 #pragma unroll
   for (int r = 0; r < PR; ++r) {
-    const int kp = lane + 32 * r;
-    if (kp < p.Kp) p.ck_phi[wrow * p.Kp + kp] = ph[r];
+    const int kp = sl + LPC * r;
+    if (kp < p.Kp && live) p.ck_phi[wrow * p.Kp + kp] = ph[r];
   }
-  if (lane == 0) p.dtsum[wrow] = dts;
+  if (sl == 0 && live) p.dtsum[wrow] = dts;
 }
+
+constexpr int kScanBatch = 8;
 
 // ck_phi: window sums -> wrapped angle at each window start (exclusive scan over the windows).
 __global__ void __launch_bounds__(256) m3w_phase_scan_kernel(M3P p) {
@@ -242,11 +261,19 @@ __global__ void __launch_bounds__(256) m3w_phase_scan_kernel(M3P p) {
   if (i >= (size_t)p.B * p.D * p.Kp) return;
   const size_t per = (size_t)p.D * p.Kp, b = i / per, rem = i - b * per;
   float run = 0.f;
-  for (int w = 0; w < p.nW; ++w) {
-    const size_t idx = (b * p.nW + w) * per + rem;
-    const float loc = p.ck_phi[idx];
-    p.ck_phi[idx] = run;
-    run = m3_wrap(run + loc);
+  // kScanBatch windows at a time, every load of a batch before its first store: a store in between would pin the
+  // order (the compiler must assume the arrays overlap) and each window would pay a full memory latency
+  for (int w0 = 0; w0 < p.nW; w0 += kScanBatch) {
+    float loc[kScanBatch];
+#pragma unroll
+    for (int x = 0; x < kScanBatch; ++x) loc[x] = w0 + x < p.nW ? p.ck_phi[(b * p.nW + w0 + x) * per + rem] : 0.f;
+#pragma unroll
+    for (int x = 0; x < kScanBatch; ++x) {
+      if (w0 + x < p.nW) {
+        p.ck_phi[(b * p.nW + w0 + x) * per + rem] = run;
+        run = m3_wrap(run + loc[x]);
+      }
+    }
   }
 }
 
@@ -259,21 +286,34 @@ __global__ void __launch_bounds__(256) m3w_state_scan_kernel(M3P p) {
   const int d = (int)(rem / p.N), n = (int)(rem - (size_t)d * p.N);
   const float A = -expf(p.a_log[ix.alog(d, n)]);
   float H = 0.f;
-  for (int w = 0; w < p.nW; ++w) {
-    const size_t idx = (b * p.nW + w) * per + rem;
-    const float loc = p.ck_h[idx];
-    p.ck_h[idx] = H;
-    H = fmaf(expf(A * p.dtsum[(b * p.nW + w) * p.D + d]), H, loc);
+  for (int w0 = 0; w0 < p.nW; w0 += kScanBatch) {
+    float loc[kScanBatch], dec[kScanBatch];
+#pragma unroll
+    for (int x = 0; x < kScanBatch; ++x) {
+      const bool in = w0 + x < p.nW;
+      loc[x] = in ? p.ck_h[(b * p.nW + w0 + x) * per + rem] : 0.f;
+      dec[x] = in ? p.dtsum[(b * p.nW + w0 + x) * p.D + d] : 0.f;
+    }
+#pragma unroll
+    for (int x = 0; x < kScanBatch; ++x) {
+      if (w0 + x < p.nW) {
+        p.ck_h[(b * p.nW + w0 + x) * per + rem] = H;
+        H = fmaf(expf(A * dec[x]), H, loc[x]);
+      }
+    }
   }
 }
 
 // Reverse walk of dh alone through one window, from zero:  up_t = dh_t + dy_t Crot_t,  dh_{t-1} = alpha_t up_t.
 // Leaves the local dh that leaves the window at its start (dhk) and the local up of its first step (upk).
-template <typename IO, int PR>
+template <typename IO, int PR, int LPC>
 __global__ void __launch_bounds__(256) m3w_dh_local_kernel(M3P p) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int d = blockIdx.x * 8 + warp, w = blockIdx.y, b = blockIdx.z;
-  if (d >= p.D) return;
+  constexpr int CPW = 32 / LPC;
+  const int sl = lane % LPC, d_raw = (blockIdx.x * 8 + warp) * CPW + lane / LPC, w = blockIdx.y, b = blockIdx.z;
+  if ((blockIdx.x * 8 + warp) * CPW >= p.D) return;
+  const bool live = d_raw < p.D;
+  const int d = live ? d_raw : p.D - 1;
   const M3Idx ix(p);
   const IO* Cp = static_cast<const IO*>(p.c);
   const IO* DY = static_cast<const IO*>(p.dy);
@@ -282,7 +322,7 @@ __global__ void __launch_bounds__(256) m3w_dh_local_kernel(M3P p) {
   float A0[PR], A1[PR], phi[PR], dh0[PR], dh1[PR], u0[PR], u1[PR];
 #pragma unroll
   for (int r = 0; r < PR; ++r) {
-    const int kp = lane + 32 * r;
+    const int kp = sl + LPC * r;
     const bool act = kp < p.Kp;
     A0[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp)]) : 0.f;
     A1[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp + 1)]) : 0.f;
@@ -294,7 +334,7 @@ __global__ void __launch_bounds__(256) m3w_dh_local_kernel(M3P p) {
     const float dt = m3_softplus(p.dt[ix.chan(row, d)]);
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       if (kp < p.Kp) phi[r] = m3_wrap(fmaf(dt, p.theta[ix.theta(row, d, kp)], phi[r]));
     }
   }
@@ -304,7 +344,7 @@ __global__ void __launch_bounds__(256) m3w_dh_local_kernel(M3P p) {
     const float dy = to_f32(DY[row * p.D + d]);
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       if (kp < p.Kp) {
         float s, c;
         sincosf(phi[r], &s, &c);
@@ -320,8 +360,8 @@ __global__ void __launch_bounds__(256) m3w_dh_local_kernel(M3P p) {
   }
 #pragma unroll
   for (int r = 0; r < PR; ++r) {
-    const int kp = lane + 32 * r;
-    if (kp < p.Kp) {
+    const int kp = sl + LPC * r;
+    if (kp < p.Kp && live) {
       p.dhk[wrow * p.N + 2 * kp] = dh0[r];
       p.dhk[wrow * p.N + 2 * kp + 1] = dh1[r];
       p.upk[wrow * p.N + 2 * kp] = u0[r];
@@ -340,14 +380,28 @@ __global__ void __launch_bounds__(256) m3w_dh_scan_kernel(M3P p) {
   const int d = (int)(rem / p.N), n = (int)(rem - (size_t)d * p.N);
   const float A = -expf(p.a_log[ix.alog(d, n)]);
   float DH = 0.f;
-  for (int w = p.nW - 1; w >= 0; --w) {
-    const size_t idx = (b * p.nW + w) * per + rem;
-    const float loc_dh = p.dhk[idx], loc_up = p.upk[idx];
-    const float dts = p.dtsum[(b * p.nW + w) * p.D + d];
-    const float dt0 = m3_softplus(p.dt[ix.chan(b * p.T + (size_t)w * kM3Window, d)]);
-    p.dhk[idx] = DH;
-    p.upk[idx] = fmaf(expf(A * (dts - dt0)), DH, loc_up);
-    DH = fmaf(expf(A * dts), DH, loc_dh);
+  for (int w0 = p.nW - 1; w0 >= 0; w0 -= kScanBatch) {
+    float ldh[kScanBatch], lup[kScanBatch], dts[kScanBatch], dt0[kScanBatch];
+#pragma unroll
+    for (int x = 0; x < kScanBatch; ++x) {
+      const int w = w0 - x;
+      const bool in = w >= 0;
+      const size_t idx = (b * p.nW + (in ? w : 0)) * per + rem;
+      ldh[x] = in ? p.dhk[idx] : 0.f;
+      lup[x] = in ? p.upk[idx] : 0.f;
+      dts[x] = in ? p.dtsum[(b * p.nW + w) * p.D + d] : 0.f;
+      dt0[x] = in ? p.dt[ix.chan(b * p.T + (size_t)w * kM3Window, d)] : 0.f;
+    }
+#pragma unroll
+    for (int x = 0; x < kScanBatch; ++x) {
+      const int w = w0 - x;
+      if (w >= 0) {
+        const size_t idx = (b * p.nW + w) * per + rem;
+        p.dhk[idx] = DH;
+        p.upk[idx] = fmaf(expf(A * (dts[x] - m3_softplus(dt0[x]))), DH, lup[x]);
+        DH = fmaf(expf(A * dts[x]), DH, ldh[x]);
+      }
+    }
   }
 }
 
@@ -357,11 +411,17 @@ __global__ void __launch_bounds__(256) m3w_ang_scan_kernel(M3P p) {
   if (i >= (size_t)p.B * p.D * p.Kp) return;
   const size_t per = (size_t)p.D * p.Kp, b = i / per, rem = i - b * per;
   float run = 0.f;
-  for (int w = p.nW - 1; w >= 0; --w) {
-    const size_t idx = (b * p.nW + w) * per + rem;
-    const float tot = p.ang[idx];
-    p.ang[idx] = run;
-    run += tot;
+  for (int w0 = p.nW - 1; w0 >= 0; w0 -= kScanBatch) {
+    float tot[kScanBatch];
+#pragma unroll
+    for (int x = 0; x < kScanBatch; ++x) tot[x] = w0 - x >= 0 ? p.ang[(b * p.nW + w0 - x) * per + rem] : 0.f;
+#pragma unroll
+    for (int x = 0; x < kScanBatch; ++x) {
+      if (w0 - x >= 0) {
+        p.ang[(b * p.nW + w0 - x) * per + rem] = run;
+        run += tot[x];
+      }
+    }
   }
 }
 
@@ -400,22 +460,54 @@ __global__ void __launch_bounds__(256) m3w_fix_kernel(M3P p) {
   }
 }
 
+// The same for few state pairs per channel (Kp <= 16), where a warp per channel would leave most lanes idle: one
+// thread per (batch, step, channel) walks its pairs.
+__global__ void __launch_bounds__(256) m3w_fix_small_kernel(M3P p) {
+  const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  if (i >= (size_t)p.B * p.T * p.D) return;
+  const M3Idx ix(p);
+  const size_t row = i / p.D;
+  const int d = (int)(i - row * p.D);
+  const size_t b = row / p.T;
+  const int w = (int)(row - b * p.T) / kM3Window;
+  if (w == p.nW - 1) return;  // nothing comes after the last window
+  const float dt_raw = p.dt[ix.chan(row, d)], dt = m3_softplus(dt_raw);
+  const float* off = p.ang + ((b * p.nW + w) * p.D + d) * p.Kp;
+  const bool per_head = p.NH > 0;
+  float s_th = 0.f, s_off = 0.f;
+  for (int kp = 0; kp < p.Kp; ++kp) {
+    const float o = off[kp];
+    s_th = fmaf(o, p.theta[ix.theta(row, d, kp)], s_th);
+    if (per_head) s_off += o;
+    else p.dtheta[ix.theta(row, d, kp)] += o * dt;
+  }
+  if (per_head) {
+    const size_t btd = (size_t)p.B * p.T * p.D;
+    p.hd[row * p.D + d] += s_th * m3_sigmoid(dt_raw);
+    p.hd[2 * btd + row * p.D + d] += s_off * dt;
+  } else {
+    p.ddt[row * p.D + d] += s_th * m3_sigmoid(dt_raw);
+  }
+}
+
 // ----------------------------------------------------------------- backward
 // WIN false: a warp walks all windows of its channel in reverse, carrying dh, the trapezoid's look-back terms and
 // the angle-gradient sum.  WIN true: a warp has one window (blockIdx.y); what enters it from later steps comes from
 // dhk / upk, and its angle-gradient sum and da_log share leave as per-window partials.
-template <typename IO, int PR, bool WIN>
+template <typename IO, int PR, int LPC, bool WIN>
 __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
   extern __shared__ float smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int CW = p.CW;  // = blockDim.x / 32; divides the channels of a group, so every warp has a channel
-  const int d = blockIdx.x * CW + warp, b = WIN ? blockIdx.z : blockIdx.y;
-  const int cpg = p.D / p.G, g = d / cpg, sl = (d % cpg) / CW;
+  constexpr int CPW = 32 / LPC;  // channels per warp
+  const int CW = p.CW;  // channels per CTA = CPW * warps; divides the channels of a group, so every lane has a channel
+  const int sl = lane % LPC, wc = warp * CPW + lane / LPC;  // lane within its channel, channel within the CTA
+  const int d = blockIdx.x * CW + wc, b = WIN ? blockIdx.z : blockIdx.y;
+  const int cpg = p.D / p.G, g = d / cpg, slice = (d % cpg) / CW;
   // per warp: [W][PR][3][32]  (h0_after, h1_after, phi)
   float* buf = smem + (size_t)warp * kM3Window * PR * 3 * 32;
   // [2 (step parity)][2 (dB, dC)][CW][N]: the rows of one step, added over the warps by the first 2N threads
   // while the warps already fill the other half with the next step (one barrier per step)
-  float* red = smem + (size_t)CW * kM3Window * PR * 3 * 32;
+  float* red = smem + (size_t)(blockDim.x >> 5) * kM3Window * PR * 3 * 32;
   auto slot = [&](int s, int r, int which) -> float& { return buf[((s * PR + r) * 3 + which) * 32 + lane]; };
   const M3Idx ix(p);
   const IO* X = static_cast<const IO*>(p.x);
@@ -428,7 +520,7 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
   float A0[PR], A1[PR], dh0[PR], dh1[PR], carry[PR], pgb0[PR], pgb1[PR], dal0[PR], dal1[PR];
 #pragma unroll
   for (int r = 0; r < PR; ++r) {
-    const int kp = lane + 32 * r;
+    const int kp = sl + LPC * r;
     const bool act = kp < p.Kp;
     A0[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp)]) : 0.f;
     A1[r] = act ? -expf(p.a_log[ix.alog(d, 2 * kp + 1)]) : 0.f;
@@ -440,7 +532,7 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
     const size_t wrow = ((size_t)b * p.nW + w_hi) * p.D + d;
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       if (kp < p.Kp) {
         dh0[r] = p.dhk[wrow * p.N + 2 * kp];
         dh1[r] = p.dhk[wrow * p.N + 2 * kp + 1];
@@ -456,7 +548,7 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
     float px = ts > 0 ? to_f32(X[((size_t)b * p.T + ts - 1) * p.D + d]) : 0.f;
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       const bool act = kp < p.Kp;
       ck0[r] = h0[r] = act ? p.ck_h[wrow * p.N + 2 * kp] : 0.f;
       ck1[r] = h1[r] = act ? p.ck_h[wrow * p.N + 2 * kp + 1] : 0.f;
@@ -479,7 +571,7 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
       const float gamma = lam * dt, bfac = (1.f - lam) * dt;
 #pragma unroll
       for (int r = 0; r < PR; ++r) {
-        const int kp = lane + 32 * r;
+        const int kp = sl + LPC * r;
         if (kp < p.Kp) {
           phi[r] = m3_wrap(fmaf(dt, p.theta[ix.theta(row, d, kp)], phi[r]));
           float s, c;
@@ -509,7 +601,7 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
       float acc = 0.f;
 #pragma unroll
       for (int r = 0; r < PR; ++r) {
-        const int kp = lane + 32 * r;
+        const int kp = sl + LPC * r;
         if (kp < p.Kp) {
           const float bni0 = bf_e * expf(dt_e * A0[r]), bni1 = bf_e * expf(dt_e * A1[r]);
           const float up0 = p.upk[wnext * p.N + 2 * kp], up1 = p.upk[wnext * p.N + 2 * kp + 1];
@@ -532,7 +624,7 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
       float s_dx = pend_dx, s_pdx = 0.f, s_dlam = 0.f, s_ddelta = 0.f, s_dtheta = 0.f;
 #pragma unroll
       for (int r = 0; r < PR; ++r) {
-        const int kp = lane + 32 * r;
+        const int kp = sl + LPC * r;
         if (kp < p.Kp) {
           const float ha0 = slot(t - ts, r, 0), ha1 = slot(t - ts, r, 1), ph = slot(t - ts, r, 2);
           const float hb0 = (t == ts) ? ck0[r] : slot(t - ts - 1, r, 0);
@@ -573,8 +665,8 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
           dh0[r] = al0 * up0;
           dh1[r] = al1 * up1;
           // rotation adjoint
-          float* rb = red + (size_t)(((t & 1) * 2 + 0) * CW + warp) * p.N + 2 * kp;
-          float* rc = red + (size_t)(((t & 1) * 2 + 1) * CW + warp) * p.N + 2 * kp;
+          float* rb = red + (size_t)(((t & 1) * 2 + 0) * CW + wc) * p.N + 2 * kp;
+          float* rc = red + (size_t)(((t & 1) * 2 + 1) * CW + wc) * p.N + 2 * kp;
           *reinterpret_cast<float2*>(rb) = make_float2(c * gb0 - s * gb1, s * gb0 + c * gb1);
           *reinterpret_cast<float2*>(rc) = make_float2(c * gc0 - s * gc1, s * gc0 + c * gc1);
           carry[r] += b1 * gb0 - b0 * gb1 + c1 * gc0 - c0 * gc1;
@@ -584,12 +676,12 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
           else p.dtheta[ix.theta(row, d, kp)] = carry[r] * dt;
         }
       }
-      s_dx = warp_sum(s_dx);
-      s_dlam = warp_sum(s_dlam) * lam * (1.f - lam);
-      s_ddelta = warp_sum(s_ddelta) * m3_sigmoid(dt_raw);
-      if (per_head) s_dtheta = warp_sum(s_dtheta);
+      s_dx = group_sum<LPC>(s_dx);
+      s_dlam = group_sum<LPC>(s_dlam) * lam * (1.f - lam);
+      s_ddelta = group_sum<LPC>(s_ddelta) * m3_sigmoid(dt_raw);
+      if (per_head) s_dtheta = group_sum<LPC>(s_dtheta);
       pend_dx = s_pdx;
-      if (lane == 0) {
+      if (sl == 0) {
         DX[row * p.D + d] = from_f32<IO>(s_dx);
         if (per_head) {  // per channel; m3_head_sum_kernel adds the channels of a head
           const size_t btd = (size_t)p.B * p.T * p.D;
@@ -607,7 +699,7 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
         const float* src = red + (size_t)(((t & 1) * 2 + which) * CW) * p.N + n;
         float acc = 0.f;
         for (int w2 = 0; w2 < CW; ++w2) acc += src[(size_t)w2 * p.N];
-        (which ? p.pc32 : p.pb32)[((row * p.G + g) * p.S + sl) * p.N + n] = acc;
+        (which ? p.pc32 : p.pb32)[((row * p.G + g) * p.S + slice) * p.N + n] = acc;
       }
     }
   }
@@ -616,7 +708,7 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
   if (WIN) {
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       if (kp < p.Kp) p.ang[(bw * p.D + d) * p.Kp + kp] = carry[r];
     }
   }
@@ -624,12 +716,12 @@ __global__ void __launch_bounds__(256) mamba3_bwd_kernel(M3P p) {
     float s = 0.f;
 #pragma unroll
     for (int r = 0; r < PR; ++r) s += dal0[r] + dal1[r];
-    s = warp_sum(s);
-    if (lane == 0) p.dal_part[bw * p.D + d] = s;
+    s = group_sum<LPC>(s);
+    if (sl == 0) p.dal_part[bw * p.D + d] = s;
   } else {
 #pragma unroll
     for (int r = 0; r < PR; ++r) {
-      const int kp = lane + 32 * r;
+      const int kp = sl + LPC * r;
       if (kp < p.Kp) {
         p.dal_part[(bw * p.D + d) * p.N + 2 * kp] = dal0[r];
         p.dal_part[(bw * p.D + d) * p.N + 2 * kp + 1] = dal1[r];
@@ -720,6 +812,9 @@ static M3P make_m3(const mxb_mamba3_desc* d) {
   p.B = d->B; p.T = d->T; p.D = d->D; p.N = d->N; p.G = d->G; p.NH = d->nheads;
   p.Kp = d->N / 2;
   p.nW = (d->T + kM3Window - 1) / kM3Window;
+  // channels that share a warp must share a group (the backward adds their dB, dC rows inside the CTA)
+  p.LPC = p.Kp <= 8 ? 8 : p.Kp <= 16 ? 16 : 32;
+  if (d->G >= 1 && d->D % d->G == 0 && (d->D / d->G) % (32 / p.LPC) != 0) p.LPC = 32;
   return p;
 }
 
@@ -730,14 +825,14 @@ bool mamba3_supported(const mxb_mamba3_desc* d) {
   return true;
 }
 
-// Channels (warps) per CTA of the channel backward: the largest divisor of the channels of a group that fits the
-// CTA (8 warps; 4 where a lane owns four state pairs and the replay buffers are that much larger).
+// Channels per CTA of the channel backward: 32 / LPC per warp times the largest number of warps (up to 8; 4 where a
+// lane owns four state pairs and the replay buffers are that much larger) that divides the warps of a group.
 static int m3_channel_warps(const M3P& p) {
-  const int cpg = p.D / p.G, cap = p.Kp > 64 ? 4 : 8;
-  int cw = 1;
+  const int cpw = 32 / p.LPC, wpg = p.D / p.G / cpw, cap = p.Kp > 64 ? 4 : 8;
+  int w = 1;
   for (int c = 1; c <= cap; ++c)
-    if (cpg % c == 0) cw = c;
-  return cw;
+    if (wpg % c == 0) w = c;
+  return w * cpw;
 }
 
 // Window-parallel channel kernels: where the (batch, channel) pairs alone leave half of the GPU's warp slots empty,
@@ -798,12 +893,20 @@ size_t mamba3_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
                   !head && m3_use_windows(d));
 }
 
-#define M3_PR_DISPATCH(p, call)                    \
-  do {                                            \
-    if ((p).Kp <= 32) { constexpr int PRV = 1; call; } \
-    else if ((p).Kp <= 64) { constexpr int PRV = 2; call; } \
-    else { constexpr int PRV = 4; call; }              \
+// PRV state pairs per lane, LPCV lanes per channel
+#define M3_PR_DISPATCH(p, call)                                                   \
+  do {                                                                           \
+    if ((p).LPC == 8) { constexpr int PRV = 1, LPCV = 8; call; }                 \
+    else if ((p).LPC == 16) { constexpr int PRV = 1, LPCV = 16; call; }          \
+    else if ((p).Kp <= 32) { constexpr int PRV = 1, LPCV = 32; call; }           \
+    else if ((p).Kp <= 64) { constexpr int PRV = 2, LPCV = 32; call; }           \
+    else { constexpr int PRV = 4, LPCV = 32; call; }                             \
   } while (0)
+
+static dim3 m3_walk_grid(const M3P& p, int ny, int nz) {
+  const int per_cta = 8 * (32 / p.LPC);  // channels per 256-thread CTA
+  return dim3((p.D + per_cta - 1) / per_cta, ny, nz);
+}
 
 static int m3_blocks(size_t n) { return (int)((n + 255) / 256); }
 
@@ -811,56 +914,60 @@ static int m3_blocks(size_t n) { return (int)((n + 255) / 256); }
 template <typename IO>
 static mxb_status m3_fwd_serial(const M3P& p, cudaStream_t st) {
   M3_PR_DISPATCH(p, MXB_LAUNCH("mamba3_fwd_kernel", st,
-                               (mamba3_fwd_kernel<IO, PRV, 0><<<dim3((p.D + 7) / 8, p.B), 256, 0, st>>>(p))));
+                               (mamba3_fwd_kernel<IO, PRV, LPCV, 0><<<m3_walk_grid(p, p.B, 1), 256, 0, st>>>(p))));
   return check_launch("mamba3_fwd_kernel");
 }
 
 // Window-parallel: angle and state at every window start (ck_phi, ck_h), then y if asked for.
 template <typename IO>
 static mxb_status m3_fwd_windows(const M3P& p, bool write_y, cudaStream_t st) {
-  const dim3 grid((p.D + 7) / 8, p.nW, p.B);
-  M3_PR_DISPATCH(p, MXB_LAUNCH("m3w_phase_kernel", st, (m3w_phase_kernel<PRV><<<grid, 256, 0, st>>>(p))));
+  const dim3 grid = m3_walk_grid(p, p.nW, p.B);
+  M3_PR_DISPATCH(p, MXB_LAUNCH("m3w_phase_kernel", st, (m3w_phase_kernel<PRV, LPCV><<<grid, 256, 0, st>>>(p))));
   MXB_LAUNCH("m3w_phase_scan_kernel", st,
              (m3w_phase_scan_kernel<<<m3_blocks((size_t)p.B * p.D * p.Kp), 256, 0, st>>>(p)));
-  M3_PR_DISPATCH(p, MXB_LAUNCH("mamba3_fwd_kernel", st, (mamba3_fwd_kernel<IO, PRV, 1><<<grid, 256, 0, st>>>(p))));
+  M3_PR_DISPATCH(p, MXB_LAUNCH("mamba3_fwd_kernel", st, (mamba3_fwd_kernel<IO, PRV, LPCV, 1><<<grid, 256, 0, st>>>(p))));
   MXB_LAUNCH("m3w_state_scan_kernel", st,
              (m3w_state_scan_kernel<<<m3_blocks((size_t)p.B * p.D * p.N), 256, 0, st>>>(p)));
   if (write_y)
-    M3_PR_DISPATCH(p, MXB_LAUNCH("mamba3_fwd_kernel", st, (mamba3_fwd_kernel<IO, PRV, 2><<<grid, 256, 0, st>>>(p))));
+    M3_PR_DISPATCH(p, MXB_LAUNCH("mamba3_fwd_kernel", st, (mamba3_fwd_kernel<IO, PRV, LPCV, 2><<<grid, 256, 0, st>>>(p))));
   return check_launch("mamba3 window-parallel forward");
 }
 
-template <typename IO, int PR, bool WIN>
+template <typename IO, int PR, int LPC, bool WIN>
 static mxb_status m3_bwd_launch(const M3P& p, cudaStream_t st) {
-  const size_t sm = sizeof(float) * ((size_t)p.CW * kM3Window * PR * 3 * 32 + 4 * (size_t)p.CW * p.N);
+  const int warps = p.CW / (32 / LPC);
+  const size_t sm = sizeof(float) * ((size_t)warps * kM3Window * PR * 3 * 32 + 4 * (size_t)p.CW * p.N);
   if (sm > 48 * 1024) {
     cudaError_t e =
-        cudaFuncSetAttribute(mamba3_bwd_kernel<IO, PR, WIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        cudaFuncSetAttribute(mamba3_bwd_kernel<IO, PR, LPC, WIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
     if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
   }
   const dim3 grid = WIN ? dim3(p.D / p.CW, p.nW, p.B) : dim3(p.D / p.CW, p.B);
-  MXB_LAUNCH("mamba3_bwd_kernel", st, (mamba3_bwd_kernel<IO, PR, WIN><<<grid, 32 * p.CW, sm, st>>>(p)));
+  MXB_LAUNCH("mamba3_bwd_kernel", st, (mamba3_bwd_kernel<IO, PR, LPC, WIN><<<grid, 32 * warps, sm, st>>>(p)));
   return check_launch("mamba3_bwd_kernel");
 }
 template <typename IO, bool WIN>
 static mxb_status m3_bwd_pr(const M3P& p, cudaStream_t st) {
-  if (p.Kp <= 32) return m3_bwd_launch<IO, 1, WIN>(p, st);
-  if (p.Kp <= 64) return m3_bwd_launch<IO, 2, WIN>(p, st);
-  return m3_bwd_launch<IO, 4, WIN>(p, st);
+  mxb_status s = MXB_OK;
+  M3_PR_DISPATCH(p, (s = m3_bwd_launch<IO, PRV, LPCV, WIN>(p, st)));
+  return s;
 }
 
 // Window-parallel backward after m3_fwd_windows: dh at the window boundaries, the true walks, the angle fix-up.
 template <typename IO>
 static mxb_status m3_bwd_windows(const M3P& p, cudaStream_t st) {
-  const dim3 grid((p.D + 7) / 8, p.nW, p.B);
-  M3_PR_DISPATCH(p, MXB_LAUNCH("m3w_dh_local_kernel", st, (m3w_dh_local_kernel<IO, PRV><<<grid, 256, 0, st>>>(p))));
+  const dim3 grid = m3_walk_grid(p, p.nW, p.B);
+  M3_PR_DISPATCH(p, MXB_LAUNCH("m3w_dh_local_kernel", st, (m3w_dh_local_kernel<IO, PRV, LPCV><<<grid, 256, 0, st>>>(p))));
   MXB_LAUNCH("m3w_dh_scan_kernel", st, (m3w_dh_scan_kernel<<<m3_blocks((size_t)p.B * p.D * p.N), 256, 0, st>>>(p)));
   mxb_status s = check_launch("mamba3 window-parallel dh");
   if (s != MXB_OK) return s;
   s = m3_bwd_pr<IO, true>(p, st);
   if (s != MXB_OK) return s;
   MXB_LAUNCH("m3w_ang_scan_kernel", st, (m3w_ang_scan_kernel<<<m3_blocks((size_t)p.B * p.D * p.Kp), 256, 0, st>>>(p)));
-  MXB_LAUNCH("m3w_fix_kernel", st, (m3w_fix_kernel<<<m3_blocks((size_t)p.B * p.T * p.D * 32), 256, 0, st>>>(p)));
+  if (p.Kp <= 16)
+    MXB_LAUNCH("m3w_fix_small_kernel", st, (m3w_fix_small_kernel<<<m3_blocks((size_t)p.B * p.T * p.D), 256, 0, st>>>(p)));
+  else
+    MXB_LAUNCH("m3w_fix_kernel", st, (m3w_fix_kernel<<<m3_blocks((size_t)p.B * p.T * p.D * 32), 256, 0, st>>>(p)));
   return check_launch("mamba3 window-parallel angle fix-up");
 }
 

@@ -32,6 +32,8 @@ def _check_grads(got, want, tol):
     (2, 8, 4, 8, 1), (2, 8, 4, 8, 2),            # the reference test's shapes
     (2, 130, 8, 8, 2), (2, 130, 8, 64, 1), (1, 130, 8, 128, 2), (1, 33, 4, 256, 1),
     (1, 70, 24, 16, 1), (2, 50, 40, 8, 2),        # several CTAs per group: partial rows added in slice order
+    (2, 50, 24, 32, 2), (1, 40, 8, 8, 1),         # two / four channels per warp (d_state <= 32 / <= 16)
+    (1, 40, 6, 8, 1),                             # channels of a group do not fill whole warps: one channel per warp
 ])
 def test_per_channel_fp32(shape):
     B, T, D, N, Gr = shape
