@@ -58,8 +58,8 @@ M3_BLOCK_BYTES_PER_TOKEN = lambda D, GN: (13 * D + 10 * GN) * 2
 # one ncu byte capture of a step.  Keyed by kernel name: when the kernels a step launches are not exactly these, the
 # capture no longer describes the step and roofline.traffic is reported as null instead of a stale number.
 GDN_NCU_TRAFFIC_MB = {   # captured at B=4 (4096 units); at B=8 a little less of the producer -> consumer tiles stays in L2
-    "gdn_tc_prep_kernel": 356.3, "gdn_tc_state_fwd_kernel": 525.1, "gdn_tc_state_bwd_kernel": 464.1,
-    "gdn_tc_chunk_bwd_kernel": 886.6,
+    "gdn_tc_prep_kernel": 353.9, "gdn_tc_state_fwd_kernel": 524.6, "gdn_tc_state_bwd_kernel": 464.9,
+    "gdn_tc_chunk_bwd_kernel": 886.5,
 }
 GDN_NCU_TRAFFIC_UNITS = 4096     # (batch, head, chunk) units of the captured step
 M3_NCU_TRAFFIC_MB = {
