@@ -219,13 +219,20 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
         st = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         aux = torch.zeros(4 + l.mxb_dp_partial_floats(), dtype=torch.float32, device=dev)  # flag, totals[3], partials
         P = lambda t, off=0: C.c_void_p(t.data_ptr() + 4 * off)
-        sanitized = []
+        # every bucket but the last leaves for its sum right behind its own pass (the last one carries the bad flag,
+        # which is complete only after all passes)
+        cur = torch.cuda.current_stream(dev)
+        comm = comm_stream if comm_stream is not None else cur
+        works = []
         with torch.cuda.device(dev):
-            for b, buf in zip(plan.buckets, storage.flat):
+            for i, (b, buf) in enumerate(zip(plan.buckets, storage.flat)):
                 _lib.check(l.mxb_dp_sanitize(P(buf), b.elements, scale, P(aux), st), "mxb_dp_sanitize")
-                ev = torch.cuda.Event()
-                ev.record(torch.cuda.current_stream(dev))
-                sanitized.append(ev)
+                if i < len(storage.flat) - 1:
+                    ev = torch.cuda.Event()
+                    ev.record(cur)
+                    with torch.cuda.stream(comm):
+                        comm.wait_event(ev)
+                        works.append(dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True))
         raw_bad = aux[0]
     else:
         raw_bad = torch.zeros((), dtype=torch.float32, device=dev)
@@ -242,7 +249,7 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
         local_bad = torch.ones((), dtype=torch.float32, device=dev)
     storage.bad.copy_(local_bad.reshape(1))
     if cuda:
-        return _finish_pipelined(storage, plan, group, comm_stream, dev, max_grad_norm, l, st, aux, P, sanitized, nbytes)
+        return _finish_pipelined(storage, plan, group, comm, dev, max_grad_norm, l, st, aux, P, works, nbytes)
     _all_reduce_buckets(storage.flat, group, comm_stream, dev)
     bad_count, denominator = float(storage.bad), float(storage.denominator)  # host read of the two packed scalars
     if bad_count > 0.0:
@@ -258,22 +265,19 @@ def staged_gradient_allreduce(grads: List[torch.Tensor], loss: torch.Tensor, los
     return StagedGradientResult(nonfinite, False, False, denominator, len(storage.flat), nbytes)
 
 
-def _finish_pipelined(storage, plan, group, comm_stream, dev, max_grad_norm, l, st, aux, P, sanitized, nbytes):
-    """CUDA: the bucket sums go out on the communication stream as soon as the bucket is sanitized (the last one
-    after the bad flag is in place); on the compute stream every bucket is divided, sanitized and measured right
-    behind its own sum, with the divisor taken from the device slot behind the first bucket, while the later sums
-    are still in flight.  The host reads the device once, at the end: bad flag, denominator, non-finite count."""
+def _finish_pipelined(storage, plan, group, comm, dev, max_grad_norm, l, st, aux, P, works, nbytes):
+    """CUDA: the sums of all buckets but the last are already on the communication stream (each went out behind its own
+    sanitize pass); the last one follows now that the bad flag is in place.  On the compute stream every bucket is
+    divided, sanitized and measured right behind its own sum, with the divisor taken from the device slot behind the
+    first bucket, while the later sums are still in flight.  The host reads the device once, at the end: bad flag,
+    denominator, non-finite count."""
     from . import _lib
     cur = torch.cuda.current_stream(dev)
-    comm = comm_stream if comm_stream is not None else cur
     ready = torch.cuda.Event()
     ready.record(cur)  # every bucket sanitized and the bad flag in its slot
-    works = []
     with torch.cuda.stream(comm):
-        for i, buf in enumerate(storage.flat):
-            # a bucket's sum may leave as soon as its own pass is done; the last one also carries the bad flag
-            comm.wait_event(sanitized[i] if i < len(storage.flat) - 1 else ready)
-            works.append(dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=True))
+        comm.wait_event(ready)
+        works.append(dist.all_reduce(storage.flat[-1], op=dist.ReduceOp.SUM, group=group, async_op=True))
     with torch.cuda.device(dev):
         for i, (b, buf) in enumerate(zip(plan.buckets, storage.flat)):
             works[i].wait()  # the compute stream waits for this bucket's sum only
