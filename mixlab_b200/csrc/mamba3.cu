@@ -61,7 +61,6 @@ struct M3P {
   const void* dy;
   void* dx;
   float *ddt, *dlam, *dtheta, *da_log;
-  float *db32, *dc32;  // head-broadcast kernels only: fp32 rows [B,T,G,N]
   // channel kernels: CW channels (warps) per CTA, S = channels per group / CW slices per group
   int CW, S;
   float *pb32, *pc32;  // [B,T,G,S,N] rows summed over the CW channels of a CTA
@@ -792,6 +791,7 @@ __global__ void __launch_bounds__(256) m3_dalog_sum_kernel(const float* __restri
 bool mamba3_head_supported(const mxb_mamba3_desc* d);
 bool mamba3_head_bwd_supported(const mxb_mamba3_desc* d);
 size_t mamba3_head_partial_floats(const mxb_mamba3_desc* d);
+size_t mamba3_head_scalar_floats(const mxb_mamba3_desc* d);
 bool mamba3_ssd_supported(const mxb_mamba3_desc* d);
 size_t mamba3_ssd_workspace_bytes(const mxb_mamba3_desc* d, bool bwd);
 mxb_status mamba3_ssd_fwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
@@ -806,7 +806,7 @@ static bool use_ssd(const mxb_mamba3_desc* d) {
 int mamba3_head_window();
 mxb_status mamba3_head_bwd(const mxb_mamba3_desc*, const void*, const float*, const float*, const float*, const float*,
                            const void*, const void*, const void*, void*, float*, float*, float*, float*, void*, void*,
-                           float*, float*, float*, float*, cudaStream_t);
+                           float*, float*, float*, float*, float*, cudaStream_t);
 static M3P make_m3(const mxb_mamba3_desc* d) {
   M3P p{};
   p.B = d->B; p.T = d->T; p.D = d->D; p.N = d->N; p.G = d->G; p.NH = d->nheads;
@@ -844,23 +844,20 @@ static bool m3_use_windows(const mxb_mamba3_desc* d) {
 }
 
 static size_t carve_m3(M3P& p, void* ws, bool io_f32, size_t partial_floats = 0, float** pb = nullptr,
-                       float** pc = nullptr, bool windows = false, bool bwd = true) {
+                       float** pc = nullptr, bool windows = false, bool bwd = true, size_t head_scalar_floats = 0,
+                       float** hscal = nullptr) {
   Carver cv(ws);
   if (partial_floats) {  // head-broadcast kernels
     float* a = cv.take<float>(partial_floats);
     float* b2 = cv.take<float>(partial_floats);
+    float* h3 = cv.take<float>(head_scalar_floats);
     if (pb) *pb = a;
     if (pc) *pc = b2;
+    if (hscal) *hscal = h3;
   }
   p.ck_h = cv.take<float>((size_t)p.B * p.nW * p.D * p.N);
   p.ck_phi = cv.take<float>((size_t)p.B * p.nW * p.D * p.Kp);
-  if (partial_floats) {
-    if (!io_f32) {
-      p.db32 = cv.take<float>((size_t)p.B * p.T * p.G * p.N);
-      p.dc32 = cv.take<float>((size_t)p.B * p.T * p.G * p.N);
-    }
-    return cv.bytes();
-  }
+  if (partial_floats) return cv.bytes();
   if (windows) p.dtsum = cv.take<float>((size_t)p.B * p.nW * p.D);
   if (!bwd) return cv.bytes();
   p.CW = m3_channel_warps(p);
@@ -890,7 +887,7 @@ size_t mamba3_workspace_bytes(const mxb_mamba3_desc* d, bool bwd) {
   const bool head = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
   if (head) p.nW = (d->T + mamba3_head_window() - 1) / mamba3_head_window();  // checkpoint spacing of the head kernels
   return carve_m3(p, nullptr, d->io_dtype == MXB_F32, head ? mamba3_head_partial_floats(d) : 0, nullptr, nullptr,
-                  !head && m3_use_windows(d));
+                  !head && m3_use_windows(d), true, head ? mamba3_head_scalar_floats(d) : 0);
 }
 
 // PRV state pairs per lane, LPCV lanes per channel
@@ -1009,27 +1006,17 @@ mxb_status mamba3_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, 
   p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c;
   p.dy = dy; p.dx = dx; p.ddt = ddt; p.dlam = dlam; p.dtheta = dtheta; p.da_log = da_log;
   const bool head_bwd = !(d->flags & MXB_MAMBA3_CHANNEL_KERNELS) && mamba3_head_bwd_supported(d);
-  float *pb = nullptr, *pc = nullptr;
+  float *pb = nullptr, *pc = nullptr, *hscal = nullptr;
   if (head_bwd) p.nW = (d->T + mamba3_head_window() - 1) / mamba3_head_window();
   const bool windows = !head_bwd && m3_use_windows(d);
-  carve_m3(p, ws, f32, head_bwd ? mamba3_head_partial_floats(d) : 0, &pb, &pc, windows);
+  carve_m3(p, ws, f32, head_bwd ? mamba3_head_partial_floats(d) : 0, &pb, &pc, windows, true,
+           head_bwd ? mamba3_head_scalar_floats(d) : 0, &hscal);
   mxb_status s;
   if (head_bwd) {
-    const size_t nbc = (size_t)p.B * p.T * p.G * p.N;
-    if (f32) { p.db32 = static_cast<float*>(db); p.dc32 = static_cast<float*>(dc); }
-    // the CTA-per-head kernels add their head-broadcast gradients with atomics into zeroed buffers
-    cudaError_t e = cudaMemsetAsync(p.db32, 0, nbc * sizeof(float), st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(p.dc32, 0, nbc * sizeof(float), st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(da_log, 0, (size_t)p.NH * sizeof(float), st);
-    const size_t nh = (size_t)p.B * p.T * p.NH * sizeof(float);
-    if (e == cudaSuccess) e = cudaMemsetAsync(ddt, 0, nh, st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(dlam, 0, nh, st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(dtheta, 0, nh, st);
-    if (e != cudaSuccess) { set_last_cuda_error((int)e); return MXB_ERR_CUDA; }
-    // checkpoint pass (y == nullptr), reverse pass, reduction of the dB/dC partials
+    // CTA-per-head kernels: checkpoint pass (y == nullptr), reverse pass, fixed-order sums of the per-CTA shares
     s = mamba3_head_fwd(d, x, dt, lam, theta, a_log, b, c, nullptr, p.ck_h, p.ck_phi, st);
     if (s != MXB_OK) return s;
-    return mamba3_head_bwd(d, x, dt, lam, theta, a_log, b, c, dy, dx, ddt, dlam, dtheta, da_log, db, dc, pb, pc,
+    return mamba3_head_bwd(d, x, dt, lam, theta, a_log, b, c, dy, dx, ddt, dlam, dtheta, da_log, db, dc, pb, pc, hscal,
                            p.ck_h, p.ck_phi, st);
   }
   // warp-per-channel kernels: checkpoints (no y), reverse pass, fixed-order sums of the partials

@@ -209,6 +209,8 @@ struct M3HB {
   void* dx;
   float *ddt, *dlam, *dtheta, *da_log;
   float *pb, *pc;  // per-CTA partial gradients of B and C: [B][D/16][T][N]
+  float* hpart;    // per-CTA shares of the head-broadcast gradients: 3 x [B][T][D/16] (dtheta, ddt, dlambda)
+  float* dalpart;  // per-warp shares of da_log: [B][D/16][8]
   void *db, *dc;   // final gradients (io dtype), written by the reduction kernel
 };
 
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(256) mamba3_head_bwd_kernel(M3HB q) {
   __shared__ float s_x[(W + 1) * CH], s_dy[W * CH];
   __shared__ float s_pdx[8 * W * CH], s_psc[8 * W * 2];  // per-warp partials of dx and of (dlam, ddelta)
   __shared__ float s_al[W], s_ga[W], s_be[W], s_lam[W], s_dt[W], s_dtraw[W], s_th[W], s_sin[W + 1], s_cos[W + 1];
-  __shared__ float s_gphi[W];
+  __shared__ float s_gphi[W], s_gphi_p[W * 4];  // angle gradient per step; its per-warp shares (N / 64 of them)
   __shared__ float s_phicarry;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -256,7 +258,6 @@ __global__ void __launch_bounds__(256) mamba3_head_bwd_kernel(M3HB q) {
       s_dtraw[tid] = raw; s_dt[tid] = dt; s_lam[tid] = lam; s_al[tid] = al; s_th[tid] = th;
       s_ga[tid] = lam * dt;
       s_be[tid] = (1.f - lam) * dt * al;
-      s_gphi[tid] = 0.f;
     }
     __syncthreads();
     if (tid == 0) {
@@ -391,7 +392,7 @@ __global__ void __launch_bounds__(256) mamba3_head_bwd_kernel(M3HB q) {
       float gph = b1 * gb0 - b0 * gb1 + cc1 * gc0 - cc0 * gc1;
       // N/2 >= 32 pairs per step and 32 | N/2: a warp's items all belong to one step
       gph = warp_sum(gph);
-      if (lane == 0) atomicAdd(&s_gphi[s_], gph);
+      if (lane == 0) s_gphi_p[s_ * 4 + (kp >> 5)] = gph;  // added in a fixed order below
     }
     for (int u = tid; u < nt * CH; u += 256) {
       const int s_ = u / CH, ch = u - s_ * CH;
@@ -404,7 +405,7 @@ __global__ void __launch_bounds__(256) mamba3_head_bwd_kernel(M3HB q) {
     if (tid == 0) {
       float carry = s_phicarry;
       for (int s_ = nt - 1; s_ >= 0; --s_) {
-        carry += s_gphi[s_];
+        for (int j = 0; j < N / 64; ++j) carry += s_gphi_p[s_ * 4 + j];
         s_gphi[s_] = carry;  // suffix sum of the angle gradient
       }
       s_phicarry = carry;
@@ -417,14 +418,52 @@ __global__ void __launch_bounds__(256) mamba3_head_bwd_kernel(M3HB q) {
       float sdl = 0.f, sdd = 0.f;
 #pragma unroll
       for (int wv = 0; wv < 8; ++wv) { sdl += s_psc[(wv * W + tid) * 2]; sdd += s_psc[(wv * W + tid) * 2 + 1]; }
-      atomicAdd(&q.dtheta[r], carry * s_dt[tid]);
-      atomicAdd(&q.ddt[r], (sdd + carry * s_th[tid]) * m3h_sigmoid(s_dtraw[tid]));
-      atomicAdd(&q.dlam[r], sdl * lam * (1.f - lam));
+      // this CTA's share; the CTAs of a head are added in slice order by m3h_head_sum_kernel
+      const size_t plane = (size_t)p.B * p.T * gridDim.x;
+      const size_t hp = ((size_t)b * p.T + ts + tid) * gridDim.x + blockIdx.x;
+      q.hpart[hp] = carry * s_dt[tid];
+      q.hpart[plane + hp] = (sdd + carry * s_th[tid]) * m3h_sigmoid(s_dtraw[tid]);
+      q.hpart[2 * plane + hp] = sdl * lam * (1.f - lam);
     }
     __syncthreads();
   }
   dal = warp_sum(dal);
-  if (lane == 0) atomicAdd(&q.da_log[head], dal);
+  if (lane == 0) q.dalpart[((size_t)b * gridDim.x + blockIdx.x) * 8 + warp] = dal;
+}
+
+// dtheta, ddt, dlambda [B,T,NH] = the shares of the CTAs of each head, added in slice order.
+__global__ void __launch_bounds__(256) m3h_head_sum_kernel(const float* __restrict__ hpart, float* __restrict__ dtheta,
+                                                           float* __restrict__ ddt, float* __restrict__ dlam, size_t rows,
+                                                           int nslice, int NH) {
+  const int per = nslice / NH;
+  const size_t plane = rows * nslice;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < rows * NH; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / NH;
+    const int h = (int)(i - r * NH);
+    float a = 0.f, d = 0.f, l = 0.f;
+    for (int s = 0; s < per; ++s) {
+      const size_t j = r * nslice + (size_t)h * per + s;
+      a += hpart[j];
+      d += hpart[plane + j];
+      l += hpart[2 * plane + j];
+    }
+    dtheta[i] = a;
+    ddt[i] = d;
+    dlam[i] = l;
+  }
+}
+
+// da_log [NH] = the per-warp shares over the batch, the CTAs of the head and their warps, in that order.
+__global__ void __launch_bounds__(128) m3h_dalog_sum_kernel(const float* __restrict__ part, float* __restrict__ da_log, int B,
+                                                            int nslice, int NH) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= NH) return;
+  const int per = nslice / NH;
+  float s = 0.f;
+  for (int b = 0; b < B; ++b)
+    for (int c = 0; c < per; ++c)
+      for (int w = 0; w < 8; ++w) s += part[((size_t)b * nslice + h * per + c) * 8 + w];
+  da_log[h] = s;
 }
 
 bool mamba3_head_supported(const mxb_mamba3_desc* d) {
@@ -498,6 +537,12 @@ static mxb_status m3hb_launch(const M3HB& q, cudaStream_t st) {
              (m3h_reduce_kernel<IO><<<dim3(q.f.T, q.f.G, q.f.B), 128, 0, st>>>(q.pb, q.pc, static_cast<IO*>(q.db),
                                                                             static_cast<IO*>(q.dc), q.f.T, q.f.N,
                                                                             q.f.G, nchunks)));
+  const size_t rows = (size_t)q.f.B * q.f.T;
+  const int hb = (int)((rows * q.f.NH + 255) / 256 < 1184 ? (rows * q.f.NH + 255) / 256 : 1184);
+  MXB_LAUNCH("m3h_head_sum_kernel", st,
+             (m3h_head_sum_kernel<<<hb, 256, 0, st>>>(q.hpart, q.dtheta, q.ddt, q.dlam, rows, nchunks, q.f.NH)));
+  MXB_LAUNCH("m3h_dalog_sum_kernel", st,
+             (m3h_dalog_sum_kernel<<<(q.f.NH + 127) / 128, 128, 0, st>>>(q.dalpart, q.da_log, q.f.B, nchunks, q.f.NH)));
   return check_launch("m3h_reduce_kernel");
 }
 
@@ -511,11 +556,15 @@ bool mamba3_head_bwd_supported(const mxb_mamba3_desc* d) {
   return mamba3_head_supported(d) && (d->D / d->nheads) % 16 == 0;
 }
 
-// Reverse pass; the caller has zeroed the accumulation buffers and run the checkpoint pass.
+size_t mamba3_head_scalar_floats(const mxb_mamba3_desc* d) {  // hpart + dalpart
+  return 3 * (size_t)d->B * d->T * (d->D / 16) + (size_t)d->B * (d->D / 16) * 8;
+}
+
+// Reverse pass; the caller has run the checkpoint pass.  hscal: mamba3_head_scalar_floats() floats of scratch.
 mxb_status mamba3_head_bwd(const mxb_mamba3_desc* d, const void* x, const float* dt, const float* lam,
                            const float* theta, const float* a_log, const void* b, const void* c, const void* dy,
                            void* dx, float* ddt, float* dlam, float* dtheta, float* da_log, void* db, void* dc,
-                           float* pb, float* pc, float* ck_h, float* ck_phi, cudaStream_t st) {
+                           float* pb, float* pc, float* hscal, float* ck_h, float* ck_phi, cudaStream_t st) {
   M3HB q{};
   M3H& p = q.f;
   p.B = d->B; p.T = d->T; p.D = d->D; p.N = d->N; p.G = d->G; p.NH = d->nheads; p.P = d->D / d->nheads;
@@ -523,6 +572,8 @@ mxb_status mamba3_head_bwd(const mxb_mamba3_desc* d, const void* x, const float*
   p.x = x; p.dt = dt; p.lam = lam; p.theta = theta; p.a_log = a_log; p.b = b; p.c = c;
   p.ck_h = ck_h; p.ck_phi = ck_phi;
   q.dy = dy; q.dx = dx; q.ddt = ddt; q.dlam = dlam; q.dtheta = dtheta; q.da_log = da_log; q.db = db; q.dc = dc; q.pb = pb; q.pc = pc;
+  q.hpart = hscal;
+  q.dalpart = hscal + 3 * (size_t)d->B * d->T * (d->D / 16);
   const bool f32 = d->io_dtype == MXB_F32;
   if (d->N == 128) return f32 ? m3hb_launch<float, 16>(q, st) : m3hb_launch<__nv_bfloat16, 16>(q, st);
   return f32 ? m3hb_launch<float, 8>(q, st) : m3hb_launch<__nv_bfloat16, 8>(q, st);
