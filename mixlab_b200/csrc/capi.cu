@@ -646,8 +646,18 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
     while (d->B * nsplit < 16 && d->H % (2 * nsplit) == 0 && (size_t)(d->H / (2 * nsplit)) * dmin >= 1024) nsplit *= 2;
   }
   if (nsplit > 1) per = 1;
-  const int Hs = d->H / nsplit;
-  const int nslices = nsplit > 1 ? d->B * nsplit : (d->B + per - 1) / per;
+  const int Hs = d->H / nsplit;  // heads of the largest slice
+  struct Slice { int b0, nb, h0, hs; };
+  std::vector<Slice> slices;
+  if (nsplit > 1) {
+    // equal head groups: cutting the last group finer (to shorten the download that overlaps nothing) was slower,
+    // every extra slice pays the latency of the sequential state passes once more
+    for (int b0 = 0; b0 < d->B; ++b0)
+      for (int g = 0; g < nsplit; ++g) slices.push_back({b0, 1, g * Hs, Hs});
+  } else {
+    for (int b0 = 0; b0 < d->B; b0 += per) slices.push_back({b0, b0 + per <= d->B ? per : d->B - b0, 0, d->H});
+  }
+  const int nslices = (int)slices.size();
   // per-sequence element counts of a slice's tensors
   const size_t sk = (size_t)d->T * Hs * d->Dk, sv = (size_t)d->T * Hs * d->Dv, ss = (size_t)d->T * Hs;
   mxb_gdn_desc d1 = *d;
@@ -693,14 +703,14 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
   auto hpw = [](void* base, size_t off) { return static_cast<char*>(base) + off; };
   const cudaMemcpyKind H2D = cudaMemcpyHostToDevice, D2H = cudaMemcpyDeviceToHost;
   // a [rows][Hs][D] slice of a [.][H][D] tensor: one contiguous block, or rows of Hs*D elements at a pitch of H*D
-  auto up = [&](char* dst, const void* src, size_t off_bytes, size_t bytes, int D) -> cudaError_t {
+  auto up = [&](char* dst, const void* src, size_t off_bytes, size_t bytes, int D, int hs) -> cudaError_t {
     if (nsplit == 1) return cudaMemcpyAsync(dst, hp(src, off_bytes), bytes, H2D, c->s_h2d);
-    const size_t w = (size_t)Hs * D * es;
+    const size_t w = (size_t)hs * D * es;
     return cudaMemcpy2DAsync(dst, w, hp(src, off_bytes), (size_t)d->H * D * es, w, (size_t)d->T, H2D, c->s_h2d);
   };
-  auto down = [&](void* dst, size_t off_bytes, const char* src, size_t bytes, int D) -> cudaError_t {
+  auto down = [&](void* dst, size_t off_bytes, const char* src, size_t bytes, int D, int hs) -> cudaError_t {
     if (nsplit == 1) return cudaMemcpyAsync(hpw(dst, off_bytes), src, bytes, D2H, c->s_d2h);
-    const size_t w = (size_t)Hs * D * es;
+    const size_t w = (size_t)hs * D * es;
     return cudaMemcpy2DAsync(hpw(dst, off_bytes), (size_t)d->H * D * es, src, w, w, (size_t)d->T, D2H, c->s_d2h);
   };
   MXB_CUDA_TRY(cudaMemcpyAsync(f_beta, beta, nfull * 4, H2D, c->s_h2d));
@@ -708,20 +718,20 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
   MXB_CUDA_TRY(cudaEventRecord(c->bg_up, c->s_h2d));
   for (int bi = 0; bi < nslices; ++bi) {
     const int sl = bi & 1;
-    const int b0 = nsplit > 1 ? bi / nsplit : bi * per, h0 = nsplit > 1 ? (bi % nsplit) * Hs : 0;
-    const int nb = nsplit > 1 ? 1 : ((b0 + per <= d->B) ? per : d->B - b0);
-    const size_t ck = sk * nb * es, cvb = sv * nb * es;   // bytes of this slice
+    const int b0 = slices[bi].b0, nb = slices[bi].nb, h0 = slices[bi].h0, hs = slices[bi].hs;
+    const size_t ck = sk * nb * es, cvb = sv * nb * es;   // bytes of this slice (contiguous slices only)
     // element offsets of the slice's first row in the full tensors
     const size_t ok_ = ((size_t)b0 * d->T * d->H + h0) * d->Dk * es, ov_ = ((size_t)b0 * d->T * d->H + h0) * d->Dv * es;
     const size_t os_ = (size_t)b0 * d->T * d->H;
     df.B = db.B = nb;
+    df.H = db.H = hs;
     if (bi >= 2) MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_h2d, c->comp_done[sl], 0));  // slot inputs consumed
-    MXB_CUDA_TRY(up(i_q[sl], q, ok_, ck, d->Dk));
-    MXB_CUDA_TRY(up(i_k[sl], k, ok_, ck, d->Dk));
-    MXB_CUDA_TRY(up(i_v[sl], v, ov_, cvb, d->Dv));
+    MXB_CUDA_TRY(up(i_q[sl], q, ok_, ck, d->Dk, hs));
+    MXB_CUDA_TRY(up(i_k[sl], k, ok_, ck, d->Dk, hs));
+    MXB_CUDA_TRY(up(i_v[sl], v, ov_, cvb, d->Dv, hs));
     MXB_CUDA_TRY(cudaEventRecord(c->h2d_done[sl], c->s_h2d));
     if (bwd) {
-      MXB_CUDA_TRY(up(i_do[sl], d_out, ov_, cvb, d->Dv));
+      MXB_CUDA_TRY(up(i_do[sl], d_out, ov_, cvb, d->Dv, hs));
       MXB_CUDA_TRY(cudaEventRecord(c->do_done[sl], c->s_h2d));
     }
     cudaStream_t kst = sl ? c->stream2 : c->stream;
@@ -732,10 +742,10 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
     const float *sb = f_beta + os_, *sg = f_gate + os_;
     float *sdb = bwd ? f_dbeta + os_ : nullptr, *sdg = bwd ? f_dgate + os_ : nullptr;
     const size_t rows = (size_t)nb * d->T;
-    const int gblocks = (int)((rows * Hs + 255) / 256 < 592 ? (rows * Hs + 255) / 256 : 592);
+    const int gblocks = (int)((rows * hs + 255) / 256 < 592 ? (rows * hs + 255) / 256 : 592);
     if (nsplit > 1) {
-      MXB_LAUNCH("head_gather_kernel", kst, (head_gather_kernel<<<gblocks, 256, 0, kst>>>(sb, i_b[sl], rows, d->H, h0, Hs)));
-      MXB_LAUNCH("head_gather_kernel", kst, (head_gather_kernel<<<gblocks, 256, 0, kst>>>(sg, i_g[sl], rows, d->H, h0, Hs)));
+      MXB_LAUNCH("head_gather_kernel", kst, (head_gather_kernel<<<gblocks, 256, 0, kst>>>(sb, i_b[sl], rows, d->H, h0, hs)));
+      MXB_LAUNCH("head_gather_kernel", kst, (head_gather_kernel<<<gblocks, 256, 0, kst>>>(sg, i_g[sl], rows, d->H, h0, hs)));
       sb = i_b[sl]; sg = i_g[sl];
       sdb = o_b[sl]; sdg = o_g[sl];
     }
@@ -749,19 +759,19 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
       if (s != MXB_OK) return s;
       if (nsplit > 1) {
         MXB_LAUNCH("head_scatter_kernel", kst,
-                   (head_scatter_kernel<<<gblocks, 256, 0, kst>>>(o_b[sl], f_dbeta + os_, rows, d->H, h0, Hs)));
+                   (head_scatter_kernel<<<gblocks, 256, 0, kst>>>(o_b[sl], f_dbeta + os_, rows, d->H, h0, hs)));
         MXB_LAUNCH("head_scatter_kernel", kst,
-                   (head_scatter_kernel<<<gblocks, 256, 0, kst>>>(o_g[sl], f_dgate + os_, rows, d->H, h0, Hs)));
+                   (head_scatter_kernel<<<gblocks, 256, 0, kst>>>(o_g[sl], f_dgate + os_, rows, d->H, h0, hs)));
       }
     }
     MXB_CUDA_TRY(cudaEventRecord(c->comp_done[sl], kst));
     MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->fwd_done[sl], 0));
-    MXB_CUDA_TRY(down(out, ov_, o_out[sl], cvb, d->Dv));
+    MXB_CUDA_TRY(down(out, ov_, o_out[sl], cvb, d->Dv, hs));
     if (bwd) {
       MXB_CUDA_TRY(cudaStreamWaitEvent(c->s_d2h, c->comp_done[sl], 0));
-      MXB_CUDA_TRY(down(dq, ok_, o_q[sl], ck, d->Dk));
-      MXB_CUDA_TRY(down(dk, ok_, o_k[sl], ck, d->Dk));
-      MXB_CUDA_TRY(down(dv, ov_, o_v[sl], cvb, d->Dv));
+      MXB_CUDA_TRY(down(dq, ok_, o_q[sl], ck, d->Dk, hs));
+      MXB_CUDA_TRY(down(dk, ok_, o_k[sl], ck, d->Dk, hs));
+      MXB_CUDA_TRY(down(dv, ov_, o_v[sl], cvb, d->Dv, hs));
     }
     MXB_CUDA_TRY(cudaEventRecord(c->d2h_done[sl], c->s_d2h));
   }

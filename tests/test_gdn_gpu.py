@@ -623,11 +623,11 @@ print("IR_FLAGS_OK")
 
 
 def test_host_buffer_entry_point_head_groups_on_tensor_core_kernels(monkeypatch):
-    """Two sequences of four 128-wide bf16 heads: by default the call cuts every sequence into head groups (rows of a
-    group stay >= 1 KB) and must return what the device entry points return on the whole tensors."""
+    """Two sequences of eight 128-wide bf16 heads: by default the call cuts every sequence into two head groups (rows of
+    a group stay >= 1 KB) and must return what the device entry points return on the whole tensors."""
     import ctypes as C
     lib = mixlab_b200.lib()
-    B, T, H, K, V = 2, 200, 4, 128, 128
+    B, T, H, K, V = 2, 200, 8, 128, 128
     a = inputs.gdn_inputs(B, T, H, K, V, seed=8, io_dtype=torch.bfloat16, with_grad_out=True)
     dev = {n: _dev(a[n]) for n in ("q", "k", "v", "beta", "g", "d_out")}
     want_out = ops.gated_delta_scan(dev["q"], dev["k"], dev["v"], dev["beta"], dev["g"], 64, gate_is_log=True)
@@ -636,7 +636,7 @@ def test_host_buffer_entry_point_head_groups_on_tensor_core_kernels(monkeypatch)
     res = {n: torch.empty_like(host[m]).pin_memory() for n, m in
            (("out", "v"), ("dq", "q"), ("dk", "k"), ("dv", "v"), ("dbeta", "beta"), ("dgate", "g"))}
     p = lambda t: C.c_void_p(t.data_ptr())
-    for split in (None, "1"):
+    for split in (None, "1", "4"):
         if split is not None:
             monkeypatch.setenv("MXB_HOST_HEAD_SPLIT", split)
         ctx = C.c_void_p()
