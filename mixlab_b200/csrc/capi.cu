@@ -666,10 +666,8 @@ static mxb_status host_gdn_pipeline(mxb_host_ctx* c, const mxb_gdn_desc* d, cons
   mxb_gdn_desc df = d1, db = d1;
   // The slices' kernels stage their operands with per-thread copies where they have such a variant: this call is
   // bound by the two PCIe copy streams, which ran slower beside kernels fed by the tensor-copy engine.
-  if (!std::getenv("MXB_HOST_TMA")) {
-    df.flags |= MXB_GDN_NO_TMA;
-    db.flags |= MXB_GDN_NO_TMA;
-  }
+  df.flags |= MXB_GDN_NO_TMA;
+  db.flags |= MXB_GDN_NO_TMA;
   if (bwd) {  // keep the forward intermediates in the arena for the backward that follows
     df.flags |= MXB_GDN_SAVE_FOR_BWD;
     db.flags |= MXB_GDN_BWD_USE_SAVED;
