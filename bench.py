@@ -587,7 +587,7 @@ def main():
     ap.add_argument("--workload", default="gdn_train", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-extra", action="store_true", help="skip the short gdn_decode, mamba3_train and mamba3_ref_shape legs")
+    ap.add_argument("--no-extra", action="store_true", help="skip the short legs of the other workloads (decode, Mamba-3, block stages)")
     ap.add_argument("--fp32-path", action="store_true", help="force the CUDA-core fp32 kernels")
     ap.add_argument("--io", default="bf16", choices=["bf16", "f32"],
                     help="gdn_train only: float32 tensors (side measurement; the headline is bf16)")
@@ -619,7 +619,8 @@ def main():
     extra = None
     if args.workload == "gdn_train" and not args.no_extra and args.batch == 0 and not args.dims:
         extra = {}
-        for name, nsteps in (("gdn_decode", 3), ("mamba3_train", 5), ("mamba3_ref_shape", 5)):
+        for name, nsteps in (("gdn_decode", 3), ("mamba3_train", 5), ("mamba3_ref_shape", 5), ("gdn_block", 3),
+                             ("mamba3_block", 3)):
             w2 = BUILDERS[name](cx, 0)
             r = time_workload(cx, w2, nsteps, 3)
             rf = r["roofline"]

@@ -100,6 +100,7 @@ def test_long_sequence_phase_stability():
     (2, 50, 2, 16, 128, 1, torch.float32), (1, 97, 4, 16, 64, 2, torch.float32),
     (1, 40, 2, 64, 128, 1, torch.float32), (2, 64, 2, 32, 128, 2, torch.bfloat16),
     (1, 33, 1, 64, 128, 1, torch.bfloat16),
+    (1, 520, 8, 64, 128, 2, torch.float32),   # many windows, eight heads in two groups
 ])
 def test_head_cta_kernels(cfg):
     """CTA-per-head kernels (head-broadcast layout): forward and all gradients against the float64 oracle
