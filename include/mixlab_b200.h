@@ -416,7 +416,14 @@ MXB_API void mxb_host_ctx_destroy(mxb_host_ctx* ctx);
 
 /* Forward (+ backward when d_out != NULL) of OP_GATED_DELTA_SCAN on host
  * buffers: H2D of the inputs, the kernels, D2H of the results, then a stream
- * synchronise.  Gradient pointers are ignored when d_out is NULL. */
+ * synchronise.  Gradient pointers are ignored when d_out is NULL.  The batch is
+ * cut into slices (a sequence, or a group of heads of a sequence moved by strided
+ * copies) that are uploaded, computed and downloaded overlapped; beta, gate and
+ * their gradients cross once for the whole batch.  Pinned host buffers make the
+ * copies asynchronous.  The arena must hold 4 (8 with a backward) [B,T,H] float
+ * arrays, two slots of every slice tensor and two slice workspaces:
+ * MXB_ERR_WORKSPACE otherwise.  Environment: MXB_HOST_SLICE_SEQS (sequences per
+ * slice), MXB_HOST_HEAD_SPLIT (head groups per sequence) override the slicing. */
 MXB_API mxb_status mxb_host_gdn(mxb_host_ctx* ctx, const mxb_gdn_desc* d, const void* q,
                         const void* k, const void* v, const float* beta, const float* gate,
                         void* out, const void* d_out, void* dq, void* dk, void* dv,
