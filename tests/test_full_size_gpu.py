@@ -230,3 +230,40 @@ def test_mamba3_full_size_chunked_against_recurrent_kernels():
     assert_close(y, y_r.double(), 2e-2, "y")
     for name in M3_GRADS:
         assert_close(g[name], g_r[name].double(), 2e-2, name)
+
+
+def test_gdn_float32_tensors_on_tensor_core_kernels_full_size():
+    """MXB_GDN_F32_IO_BF16_OPERANDS at the benchmark size: float32 tensors give exactly what the bf16 entry gives on
+    the rounded tensors (outputs and every gradient, widened), through the saving forward and the saved backward."""
+    flag = _lib.MXB_GDN_F32_IO_BF16_OPERANDS
+    q, k, v, beta, glog, d_out = _gdn_full(B=4)
+    want_o = ops.gated_delta_scan(q, k, v, beta, glog, 64, gate_is_log=True)
+    want = ops.gated_delta_scan_backward(q, k, v, beta, glog, d_out, 64, gate_is_log=True)
+    qf, kf, vf, dof = (t.float() for t in (q, k, v, d_out))  # exactly representable: rounding them back is the identity
+    got_o = ops.gated_delta_scan(qf, kf, vf, beta, glog, 64, gate_is_log=True, flags=flag, save_for_backward=True)
+    got = ops.gated_delta_scan_backward(qf, kf, vf, beta, glog, dof, 64, gate_is_log=True, flags=flag, use_saved=True)
+    assert got_o.dtype == torch.float32 and torch.equal(got_o, want_o.float())
+    for name in ("dq", "dk", "dv", "dbeta", "dgate"):
+        assert torch.equal(got[name], want[name].float()), name
+
+
+def test_mamba3_channel_kernels_window_parallel_against_serial_walk_long():
+    """The reference's per-channel layout at T=4096 (256 windows), d_state 16, two groups: the window-parallel kernels
+    against the serial walk of the same recurrence (different summation orders: 1e-4), and bit-identical repeats."""
+    from oracle import inputs as oin
+    B, T, D, N, G = 2, 4096, 256, 16, 2
+    a = oin.mamba3_inputs(B, T, D, 1, N, G=G, seed=5, per_head=False)
+    names = ("x", "dt_raw", "lambda_raw", "theta", "a_log", "b", "c")
+    dev = [a[n].to(DEV).contiguous() for n in names]
+    dy = a["dy"].to(DEV).contiguous()
+    ys = ops.mamba3_selective_scan(*dev, flags=_lib.MXB_MAMBA3_SERIAL_WALK)
+    yw = ops.mamba3_selective_scan(*dev, flags=_lib.MXB_MAMBA3_WINDOW_PARALLEL)
+    assert_close(yw, ys.double(), 1e-4, "y")
+    gs = ops.mamba3_selective_scan_backward(*dev, dy, flags=_lib.MXB_MAMBA3_SERIAL_WALK)
+    gw = ops.mamba3_selective_scan_backward(*dev, dy, flags=_lib.MXB_MAMBA3_WINDOW_PARALLEL)
+    gw = {k2: v2.clone() for k2, v2 in gw.items()}
+    for name in ("dx", "ddt", "dlambda", "dtheta", "da_log", "db", "dc"):
+        assert_close(gw[name], gs[name].double(), 1e-4, name)
+    again = ops.mamba3_selective_scan_backward(*dev, dy, flags=_lib.MXB_MAMBA3_WINDOW_PARALLEL)
+    for name in gw:
+        assert torch.equal(gw[name], again[name]), name
